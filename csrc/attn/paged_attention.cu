@@ -1,0 +1,560 @@
+// Paged attention for sm_100a: split-KV decode (one query token per sequence, all query heads of a
+// KV head packed into one tensor-core tile) and varlen chunked-prefill flash attention reading the
+// paged cache.  Both support 16-bit or fp8-e4m3 KV (per-tensor scale), sliding windows and
+// logit soft-capping, head_dim 64/128/256, any block size.
+//
+// KV cache layout: [num_blocks, n_kv_heads, block_size, head_dim]; block id 0 is the null block.
+//
+// These are bandwidth-bound (decode) or a small share of prefill FLOPs for the served shapes, so
+// they use register-level mma.sync tiles with cp.async double buffering rather than TMEM.
+//
+// Counterpart in the reference: vllm/kernels/triton/paged_attention.py:306-759 (one program per
+// (sequence, query head), also used for prefill by expanding every query token into its own row,
+// vllm/engine/lite_engine.py:53-104).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <typename T> struct MmaT;
+template <> struct MmaT<__nv_bfloat16> {
+  static __device__ __forceinline__ void mma(float* d, const uint32_t* a, const uint32_t* b) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+  }
+  static __device__ __forceinline__ uint32_t pack(float x, float y) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16(v); }
+};
+template <> struct MmaT<__half> {
+  static __device__ __forceinline__ void mma(float* d, const uint32_t* a, const uint32_t* b) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+  }
+  static __device__ __forceinline__ uint32_t pack(float x, float y) {
+    __half2 h = __floats2half2_rn(x, y);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half(v); }
+};
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src),
+               "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N));
+}
+
+// Row-major [rows][HD] 16-bit tile with the 16-byte chunks of a row XOR-swizzled by (row & 7).
+template <int HD>
+__device__ __forceinline__ int tile_off(int row, int chunk) {  // in 16-bit elements
+  return row * HD + ((chunk ^ (row & 7)) << 3);
+}
+
+struct AttnParams {
+  const void* q;        // query rows: token t, head h at q + (t * q_stride + h * HD) elements
+  long q_stride;
+  const void* k_cache;
+  const void* v_cache;
+  void* out;            // [T, nh * HD]
+  const int* block_tables;  // [B, max_blocks]
+  const int* seq_lens;      // [B] KV length including this step's tokens
+  const int* cu_q;          // [B + 1] query token offsets (prefill); null for decode
+  float* ws_o;              // decode partials [B, nh, splits, HD]
+  float* ws_ml;             // decode partials [B, nh, splits, 2]
+  int max_blocks, block_size, nh, nkv, window;  // window <= 0: none
+  float sm_scale, softcap, k_scale, v_scale;
+  int kv_fp8, splits;
+};
+
+// Load `rows` KV tokens starting at token tok0 of sequence b / kv head kvh into a swizzled tile.
+// Tokens outside [lo, hi) are zero-filled.
+template <typename T, int HD, int ROWS, int THREADS>
+__device__ __forceinline__ void load_kv_tile(T* tile, const void* cache, const int* bt,
+                                             int block_size, int nkv, int kvh, int tok0, int lo,
+                                             int hi, bool fp8) {
+  constexpr int CPR = HD / 8;  // 16-byte chunks (of 16-bit elements) per row
+  if (!fp8) {
+    for (int i = threadIdx.x; i < ROWS * CPR; i += THREADS) {
+      const int r = i / CPR, c = i % CPR;
+      const int tok = tok0 + r;
+      const bool valid = tok >= lo && tok < hi;
+      const T* src = reinterpret_cast<const T*>(cache);
+      if (valid) {
+        const int blk = bt[tok / block_size];
+        src += ((static_cast<long>(blk) * nkv + kvh) * block_size + tok % block_size) * HD + c * 8;
+      }
+      cp_async16(tile + tile_off<HD>(r, c), src, valid);
+    }
+  } else {
+    // fp8: 16 values per 16-byte load, converted to two 16-byte chunks of T
+    constexpr int CPR8 = HD / 16;
+    for (int i = threadIdx.x; i < ROWS * CPR8; i += THREADS) {
+      const int r = i / CPR8, c = i % CPR8;
+      const int tok = tok0 + r;
+      const bool valid = tok >= lo && tok < hi;
+      uint4 raw = make_uint4(0, 0, 0, 0);
+      if (valid) {
+        const int blk = bt[tok / block_size];
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(cache) +
+                             ((static_cast<long>(blk) * nkv + kvh) * block_size + tok % block_size) * HD +
+                             c * 16;
+        raw = *reinterpret_cast<const uint4*>(src);
+      }
+      const __nv_fp8_e4m3* f8 = reinterpret_cast<const __nv_fp8_e4m3*>(&raw);
+      T tmp[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) tmp[j] = MmaT<T>::from_f(static_cast<float>(f8[j]));
+      *reinterpret_cast<uint4*>(tile + tile_off<HD>(r, 2 * c)) = *reinterpret_cast<uint4*>(&tmp[0]);
+      *reinterpret_cast<uint4*>(tile + tile_off<HD>(r, 2 * c + 1)) = *reinterpret_cast<uint4*>(&tmp[8]);
+    }
+  }
+}
+
+__device__ __forceinline__ float softcap_f(float s, float cap) {
+  return cap > 0.f ? cap * tanhf(s / cap) : s;
+}
+
+// ------------------------------------------------------------------------------ decode
+// grid (splits, nkv * head_groups, B); 128 threads.  Rows of the 16-row tile = query heads of one
+// KV head (up to 16 per group).  Each warp owns 16 of the 64 tokens of a chunk.
+template <typename T, int HD>
+__global__ void __launch_bounds__(128) paged_decode_kernel(const AttnParams p) {
+  constexpr int CH = 64;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  T* sQ = reinterpret_cast<T*>(smem_raw);        // [16][HD]
+  T* sK = sQ + 16 * HD;                          // [2][CH][HD]
+  T* sV = sK + 2 * CH * HD;                      // [2][CH][HD]
+  const int split = blockIdx.x;
+  const int G = p.nh / p.nkv;
+  const int groups = (G + 15) / 16;
+  const int kvh = blockIdx.y / groups;
+  const int grp = blockIdx.y % groups;
+  const int b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads_here = min(16, G - grp * 16);
+  const int head0 = kvh * G + grp * 16;
+  const int seq_len = p.seq_lens[b];
+  const int* bt = p.block_tables + static_cast<long>(b) * p.max_blocks;
+  const int lo = p.window > 0 ? max(0, seq_len - p.window) : 0;
+  const int first_chunk = lo / CH;
+  const int n_chunks = (seq_len + CH - 1) / CH - first_chunk;
+  const int per = (n_chunks + p.splits - 1) / p.splits;
+  const int c_begin = first_chunk + split * per;
+  const int c_end = min(first_chunk + n_chunks, c_begin + per);
+
+  // stage Q (zero rows beyond heads_here)
+  for (int i = threadIdx.x; i < 16 * (HD / 8); i += 128) {
+    const int r = i / (HD / 8), c = i % (HD / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < heads_here)
+      v = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.q) +
+                                          static_cast<long>(b) * p.q_stride +
+                                          static_cast<long>(head0 + r) * HD + c * 8);
+    *reinterpret_cast<uint4*>(sQ + tile_off<HD>(r, c)) = v;
+  }
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+  const float scale = p.sm_scale * (p.kv_fp8 ? p.k_scale : 1.f);
+
+  if (c_begin < c_end) {
+    load_kv_tile<T, HD, CH, 128>(sK, p.k_cache, bt, p.block_size, p.nkv, kvh, c_begin * CH, lo, seq_len, p.kv_fp8);
+    load_kv_tile<T, HD, CH, 128>(sV, p.v_cache, bt, p.block_size, p.nkv, kvh, c_begin * CH, lo, seq_len, p.kv_fp8);
+  }
+  cp_async_commit();
+  for (int c = c_begin; c < c_end; ++c) {
+    const int buf = (c - c_begin) & 1;
+    if (c + 1 < c_end) {
+      load_kv_tile<T, HD, CH, 128>(sK + (buf ^ 1) * CH * HD, p.k_cache, bt, p.block_size, p.nkv, kvh, (c + 1) * CH, lo, seq_len, p.kv_fp8);
+      load_kv_tile<T, HD, CH, 128>(sV + (buf ^ 1) * CH * HD, p.v_cache, bt, p.block_size, p.nkv, kvh, (c + 1) * CH, lo, seq_len, p.kv_fp8);
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const T* K = sK + buf * CH * HD;
+    const T* V = sV + buf * CH * HD;
+    const int tok_base = c * CH + warp * 16;
+    if (tok_base < seq_len && tok_base + 16 > lo) {
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        uint32_t a[4], kb[4];
+        // A (Q): matrices (rows 0-7,k 0-7) (rows 8-15,k 0-7) (rows 0-7,k 8-15) (rows 8-15,k 8-15)
+        ldsm_x4(a, smem_addr(sQ + tile_off<HD>((lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4))));
+        // B (K): matrices (tok 0-7,d 0-7) (tok 0-7,d 8-15) (tok 8-15,d 0-7) (tok 8-15,d 8-15)
+        ldsm_x4(kb, smem_addr(K + tile_off<HD>(warp * 16 + (lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1))));
+        MmaT<T>::mma(s[0], a, kb);
+        MmaT<T>::mma(s[1], a, kb + 2);
+      }
+      float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int tok = tok_base + j * 8 + (lane & 3) * 2 + (e & 1);
+          float v = softcap_f(s[j][e] * scale, p.softcap);
+          if (tok >= seq_len || tok < lo) v = -CUDART_INF_F;
+          s[j][e] = v;
+          if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+        }
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float nm0 = fmaxf(m0, mx0), nm1 = fmaxf(m1, mx1);
+      const float a0 = nm0 == -CUDART_INF_F ? 1.f : exp2f((m0 - nm0) * kLog2e);
+      const float a1 = nm1 == -CUDART_INF_F ? 1.f : exp2f((m1 - nm1) * kLog2e);
+      float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float nm = e < 2 ? nm0 : nm1;
+          const float pv = nm == -CUDART_INF_F ? 0.f : exp2f((s[j][e] - nm) * kLog2e);
+          s[j][e] = pv;
+          if (e < 2) rs0 += pv; else rs1 += pv;
+        }
+      }
+      l0 = l0 * a0 + rs0; l1 = l1 * a1 + rs1; m0 = nm0; m1 = nm1;
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) { o[i][0] *= a0; o[i][1] *= a0; o[i][2] *= a1; o[i][3] *= a1; }
+      uint32_t pa[4] = {MmaT<T>::pack(s[0][0], s[0][1]), MmaT<T>::pack(s[0][2], s[0][3]),
+                        MmaT<T>::pack(s[1][0], s[1][1]), MmaT<T>::pack(s[1][2], s[1][3])};
+#pragma unroll
+      for (int dp = 0; dp < HD / 16; ++dp) {
+        uint32_t vb[4];
+        // B (V, transposed): matrices (tok 0-7,d-tile 2dp) (tok 8-15,2dp) (tok 0-7,2dp+1) (tok 8-15,2dp+1)
+        ldsm_x4_t(vb, smem_addr(V + tile_off<HD>(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, dp * 2 + (lane >> 4))));
+        MmaT<T>::mma(o[2 * dp], pa, vb);
+        MmaT<T>::mma(o[2 * dp + 1], pa, vb + 2);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  // quad-reduce the row sums
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  // merge the four warps through shared memory (aliases the KV buffers)
+  __syncthreads();
+  float* mO = reinterpret_cast<float*>(sK);              // [4][16][HD]
+  float* mML = mO + 4 * 16 * HD;                         // [4][16][2]
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+      const int d = i * 8 + (lane & 3) * 2;
+      mO[(warp * 16 + r0) * HD + d] = o[i][0]; mO[(warp * 16 + r0) * HD + d + 1] = o[i][1];
+      mO[(warp * 16 + r1) * HD + d] = o[i][2]; mO[(warp * 16 + r1) * HD + d + 1] = o[i][3];
+    }
+    if ((lane & 3) == 0) {
+      mML[(warp * 16 + r0) * 2] = m0; mML[(warp * 16 + r0) * 2 + 1] = l0;
+      mML[(warp * 16 + r1) * 2] = m1; mML[(warp * 16 + r1) * 2 + 1] = l1;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < heads_here * HD; i += 128) {
+    const int r = i / HD, d = i % HD;
+    float m = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, mML[(w * 16 + r) * 2]);
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = mML[(w * 16 + r) * 2];
+      const float f = mw == -CUDART_INF_F ? 0.f : exp2f((mw - m) * kLog2e);
+      acc += f * mO[(w * 16 + r) * HD + d];
+      l += f * mML[(w * 16 + r) * 2 + 1];
+    }
+    const int head = head0 + r;
+    if (p.splits == 1) {
+      const float v = l > 0.f ? acc / l * (p.kv_fp8 ? p.v_scale : 1.f) : 0.f;
+      reinterpret_cast<T*>(p.out)[(static_cast<long>(b) * p.nh + head) * HD + d] = MmaT<T>::from_f(v);
+    } else {
+      const long base = (static_cast<long>(b) * p.nh + head) * p.splits + split;
+      p.ws_o[base * HD + d] = acc;
+      if (d == 0) { p.ws_ml[base * 2] = m; p.ws_ml[base * 2 + 1] = l; }
+    }
+  }
+}
+
+template <typename T, int HD>
+__global__ void decode_merge_kernel(const AttnParams p) {
+  const int b = blockIdx.y, head = blockIdx.x;
+  const long base = (static_cast<long>(b) * p.nh + head) * p.splits;
+  float m = -CUDART_INF_F;
+  for (int s = 0; s < p.splits; ++s) m = fmaxf(m, p.ws_ml[(base + s) * 2]);
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float acc = 0.f, l = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+      const float ms = p.ws_ml[(base + s) * 2];
+      const float f = ms == -CUDART_INF_F ? 0.f : exp2f((ms - m) * kLog2e);
+      acc += f * p.ws_o[(base + s) * HD + d];
+      l += f * p.ws_ml[(base + s) * 2 + 1];
+    }
+    const float v = l > 0.f ? acc / l * (p.kv_fp8 ? p.v_scale : 1.f) : 0.f;
+    reinterpret_cast<T*>(p.out)[(static_cast<long>(b) * p.nh + head) * HD + d] = MmaT<T>::from_f(v);
+  }
+}
+
+// ------------------------------------------------------------------------------ prefill
+// grid (q_tiles, nh, B); 128 threads; each warp owns 16 consecutive query tokens of the 64-token
+// tile; KV streamed in CH-token chunks shared by the four warps.
+template <typename T, int HD, int CH>
+__global__ void __launch_bounds__(128) paged_prefill_kernel(const AttnParams p) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  T* sQ = reinterpret_cast<T*>(smem_raw);   // [64][HD]
+  T* sK = sQ + 64 * HD;                     // [2][CH][HD]
+  T* sV = sK + 2 * CH * HD;                 // [2][CH][HD]
+  const int b = blockIdx.z, head = blockIdx.y;
+  const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
+  const int qt0 = blockIdx.x * 64;
+  if (qt0 >= q_len) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvh = head / (p.nh / p.nkv);
+  const int seq_len = p.seq_lens[b];
+  const int pos0 = seq_len - q_len;  // absolute position of query token 0
+  const int* bt = p.block_tables + static_cast<long>(b) * p.max_blocks;
+
+  for (int i = threadIdx.x; i < 64 * (HD / 8); i += 128) {
+    const int r = i / (HD / 8), c = i % (HD / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (qt0 + r < q_len)
+      v = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.q) +
+                                          static_cast<long>(q_begin + qt0 + r) * p.q_stride +
+                                          static_cast<long>(head) * HD + c * 8);
+    *reinterpret_cast<uint4*>(sQ + tile_off<HD>(r, c)) = v;
+  }
+  const int last_pos = pos0 + min(q_len, qt0 + 64) - 1;  // last query position of this tile
+  const int first_pos = pos0 + qt0;
+  const int lo_tile = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+  const int c_begin = lo_tile / CH;
+  const int c_end = last_pos / CH + 1;
+  const float scale = p.sm_scale * (p.kv_fp8 ? p.k_scale : 1.f);
+  const int row0 = qt0 + warp * 16 + (lane >> 2);  // query index (within the sequence's new tokens)
+  const int posr0 = pos0 + row0, posr1 = posr0 + 8;
+
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+
+  load_kv_tile<T, HD, CH, 128>(sK, p.k_cache, bt, p.block_size, p.nkv, kvh, c_begin * CH, 0, seq_len, p.kv_fp8);
+  load_kv_tile<T, HD, CH, 128>(sV, p.v_cache, bt, p.block_size, p.nkv, kvh, c_begin * CH, 0, seq_len, p.kv_fp8);
+  cp_async_commit();
+  for (int c = c_begin; c < c_end; ++c) {
+    const int buf = (c - c_begin) & 1;
+    if (c + 1 < c_end) {
+      load_kv_tile<T, HD, CH, 128>(sK + (buf ^ 1) * CH * HD, p.k_cache, bt, p.block_size, p.nkv, kvh, (c + 1) * CH, 0, seq_len, p.kv_fp8);
+      load_kv_tile<T, HD, CH, 128>(sV + (buf ^ 1) * CH * HD, p.v_cache, bt, p.block_size, p.nkv, kvh, (c + 1) * CH, 0, seq_len, p.kv_fp8);
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const T* K = sK + buf * CH * HD;
+    const T* V = sV + buf * CH * HD;
+    float s[CH / 8][4];
+#pragma unroll
+    for (int j = 0; j < CH / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      uint32_t a[4];
+      ldsm_x4(a, smem_addr(sQ + tile_off<HD>(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4))));
+#pragma unroll
+      for (int jp = 0; jp < CH / 16; ++jp) {
+        uint32_t kb[4];
+        ldsm_x4(kb, smem_addr(K + tile_off<HD>(jp * 16 + (lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1))));
+        MmaT<T>::mma(s[2 * jp], a, kb);
+        MmaT<T>::mma(s[2 * jp + 1], a, kb + 2);
+      }
+    }
+    float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
+#pragma unroll
+    for (int j = 0; j < CH / 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int tok = c * CH + j * 8 + (lane & 3) * 2 + (e & 1);
+        const int pr = e < 2 ? posr0 : posr1;
+        float v = softcap_f(s[j][e] * scale, p.softcap);
+        const bool masked = tok > pr || tok >= seq_len || (p.window > 0 && tok <= pr - p.window);
+        if (masked) v = -CUDART_INF_F;
+        s[j][e] = v;
+        if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float nm0 = fmaxf(m0, mx0), nm1 = fmaxf(m1, mx1);
+    const float a0 = nm0 == -CUDART_INF_F ? 1.f : exp2f((m0 - nm0) * kLog2e);
+    const float a1 = nm1 == -CUDART_INF_F ? 1.f : exp2f((m1 - nm1) * kLog2e);
+    float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < CH / 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float nm = e < 2 ? nm0 : nm1;
+        const float pv = nm == -CUDART_INF_F ? 0.f : exp2f((s[j][e] - nm) * kLog2e);
+        s[j][e] = pv;
+        if (e < 2) rs0 += pv; else rs1 += pv;
+      }
+    }
+    l0 = l0 * a0 + rs0; l1 = l1 * a1 + rs1; m0 = nm0; m1 = nm1;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) { o[i][0] *= a0; o[i][1] *= a0; o[i][2] *= a1; o[i][3] *= a1; }
+#pragma unroll
+    for (int kt = 0; kt < CH / 16; ++kt) {
+      uint32_t pa[4] = {MmaT<T>::pack(s[2 * kt][0], s[2 * kt][1]), MmaT<T>::pack(s[2 * kt][2], s[2 * kt][3]),
+                        MmaT<T>::pack(s[2 * kt + 1][0], s[2 * kt + 1][1]), MmaT<T>::pack(s[2 * kt + 1][2], s[2 * kt + 1][3])};
+#pragma unroll
+      for (int dp = 0; dp < HD / 16; ++dp) {
+        uint32_t vb[4];
+        ldsm_x4_t(vb, smem_addr(V + tile_off<HD>(kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, dp * 2 + (lane >> 4))));
+        MmaT<T>::mma(o[2 * dp], pa, vb);
+        MmaT<T>::mma(o[2 * dp + 1], pa, vb + 2);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const float vs = p.kv_fp8 ? p.v_scale : 1.f;
+  const float i0 = l0 > 0.f ? vs / l0 : 0.f, i1 = l1 > 0.f ? vs / l1 : 0.f;
+  T* out = reinterpret_cast<T*>(p.out);
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) {
+    const int d = i * 8 + (lane & 3) * 2;
+    if (row0 < q_len) {
+      const long off = (static_cast<long>(q_begin + row0) * p.nh + head) * HD + d;
+      *reinterpret_cast<uint32_t*>(out + off) = MmaT<T>::pack(o[i][0] * i0, o[i][1] * i0);
+    }
+    if (row0 + 8 < q_len) {
+      const long off = (static_cast<long>(q_begin + row0 + 8) * p.nh + head) * HD + d;
+      *reinterpret_cast<uint32_t*>(out + off) = MmaT<T>::pack(o[i][2] * i1, o[i][3] * i1);
+    }
+  }
+}
+
+template <typename T, int HD>
+int launch_decode(const AttnParams& p, int B, cudaStream_t s) {
+  const int G = p.nh / p.nkv;
+  const int groups = (G + 15) / 16;
+  const int kv_bytes = (16 * HD + 4 * 64 * HD) * 2;
+  const int merge_bytes = (4 * 16 * HD + 4 * 16 * 2) * 4 + 16 * HD * 2;
+  const int smem = kv_bytes > merge_bytes ? kv_bytes : merge_bytes;
+  auto kern = paged_decode_kernel<T, HD>;
+  static bool cfg = false;
+  if (!cfg) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cfg = true;
+  }
+  kern<<<dim3(p.splits, p.nkv * groups, B), 128, smem, s>>>(p);
+  if (p.splits > 1) decode_merge_kernel<T, HD><<<dim3(p.nh, B), HD >= 128 ? 128 : 64, 0, s>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <typename T, int HD, int CH>
+int launch_prefill(const AttnParams& p, int B, int max_q_len, cudaStream_t s) {
+  const int smem = (64 * HD + 4 * CH * HD) * 2;
+  auto kern = paged_prefill_kernel<T, HD, CH>;
+  static bool cfg = false;
+  if (!cfg) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cfg = true;
+  }
+  kern<<<dim3((max_q_len + 63) / 64, p.nh, B), 128, smem, s>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace
+
+// Decode scratch: ws_o needs B*nh*splits*hd floats, ws_ml B*nh*splits*2 floats (splits > 1 only).
+extern "C" int fi_paged_decode(const void* q, long q_stride, const void* k_cache,
+                               const void* v_cache, void* out, const int* block_tables,
+                               const int* seq_lens, float* ws_o, float* ws_ml, int B, int nh,
+                               int nkv, int hd, int max_blocks, int block_size, int window,
+                               float sm_scale, float softcap, int kv_fp8, float k_scale,
+                               float v_scale, int splits, int dtype, void* stream) {
+  if (B <= 0) return 0;
+  if (nh % nkv != 0 || splits < 1) return -10;
+  AttnParams p = {};
+  p.q = q; p.q_stride = q_stride; p.k_cache = k_cache; p.v_cache = v_cache; p.out = out;
+  p.block_tables = block_tables; p.seq_lens = seq_lens; p.cu_q = nullptr; p.ws_o = ws_o;
+  p.ws_ml = ws_ml; p.max_blocks = max_blocks; p.block_size = block_size; p.nh = nh; p.nkv = nkv;
+  p.window = window; p.sm_scale = sm_scale; p.softcap = softcap; p.k_scale = k_scale;
+  p.v_scale = v_scale; p.kv_fp8 = kv_fp8; p.splits = splits;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+#define FI_DEC(TT, HD) return launch_decode<TT, HD>(p, B, s)
+  if (dtype == 0) {
+    if (hd == 64) FI_DEC(__nv_bfloat16, 64);
+    if (hd == 128) FI_DEC(__nv_bfloat16, 128);
+    if (hd == 256) FI_DEC(__nv_bfloat16, 256);
+  } else if (dtype == 1) {
+    if (hd == 64) FI_DEC(__half, 64);
+    if (hd == 128) FI_DEC(__half, 128);
+    if (hd == 256) FI_DEC(__half, 256);
+  }
+#undef FI_DEC
+  return -11;
+}
+
+extern "C" int fi_paged_prefill(const void* q, long q_stride, const void* k_cache,
+                                const void* v_cache, void* out, const int* block_tables,
+                                const int* seq_lens, const int* cu_q, int B, int max_q_len, int nh,
+                                int nkv, int hd, int max_blocks, int block_size, int window,
+                                float sm_scale, float softcap, int kv_fp8, float k_scale,
+                                float v_scale, int dtype, void* stream) {
+  if (B <= 0 || max_q_len <= 0) return 0;
+  if (nh % nkv != 0) return -10;
+  AttnParams p = {};
+  p.q = q; p.q_stride = q_stride; p.k_cache = k_cache; p.v_cache = v_cache; p.out = out;
+  p.block_tables = block_tables; p.seq_lens = seq_lens; p.cu_q = cu_q; p.max_blocks = max_blocks;
+  p.block_size = block_size; p.nh = nh; p.nkv = nkv; p.window = window; p.sm_scale = sm_scale;
+  p.softcap = softcap; p.k_scale = k_scale; p.v_scale = v_scale; p.kv_fp8 = kv_fp8; p.splits = 1;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == 0) {
+    if (hd == 64) return launch_prefill<__nv_bfloat16, 64, 64>(p, B, max_q_len, s);
+    if (hd == 128) return launch_prefill<__nv_bfloat16, 128, 64>(p, B, max_q_len, s);
+    if (hd == 256) return launch_prefill<__nv_bfloat16, 256, 32>(p, B, max_q_len, s);
+  } else if (dtype == 1) {
+    if (hd == 64) return launch_prefill<__half, 64, 64>(p, B, max_q_len, s);
+    if (hd == 128) return launch_prefill<__half, 128, 64>(p, B, max_q_len, s);
+    if (hd == 256) return launch_prefill<__half, 256, 32>(p, B, max_q_len, s);
+  }
+  return -11;
+}

@@ -1,0 +1,402 @@
+// Dense 16-bit GEMM for sm_100a:  C[T, N] = X[T, K] * W[N, K]^T  (+ bias, + residual, or the
+// gated form act(X Wg^T) * (X Wu^T)).
+//
+// Design ("weights on the M side"): the weight matrix is the UMMA A operand (128 weight rows per
+// CTA, UMMA M = 128) and the activations are the B operand (BN tokens per CTA, UMMA N = BN), both
+// K-major, so decode batches of 16..64 tokens still fill a full 128-lane tensor-core tile and the
+// kernel streams the weights exactly once.  TMA (128-byte swizzle) feeds a multi-stage smem ring,
+// one elected thread issues tcgen05.mma into a TMEM accumulator, four epilogue warps read it back
+// with tcgen05.ld.  Split-K runs as a thread-block cluster along z: every CTA of the cluster parks
+// its fp32 partial tile in its own shared memory and the CTAs sum the partials through distributed
+// shared memory, so the reduction needs no global scratch and no atomics (bitwise deterministic).
+//
+// Replaces the library GEMM behind every unquantised linear of the reference
+// (vllm/model_executor/layers/lite_linear.py:60-62) and the silu-and-mul kernel
+// (vllm/kernels/triton/activation.py:42) that follows its gate/up projections.
+#include <cooperative_groups.h>
+
+#include "../common/ptx.cuh"
+#include "../common/tensormap.h"
+
+namespace cg = cooperative_groups;
+using namespace fi;
+
+namespace {
+
+constexpr int BM = 128;  // weight rows per CTA
+constexpr int BK = 64;   // 64 x 16-bit = one 128-byte swizzle row
+constexpr int kThreads = 192;
+
+enum Act : int { kActNone = 0, kActSilu = 1, kActGeluTanh = 2 };
+
+struct GemmParams {
+  void* C;
+  const void* bias;      // [N] or null (same 16-bit type as X)
+  const void* residual;  // [T, ldc] or null (same type as C when C is 16-bit)
+  int T, N, K;
+  int ldc;
+  int dual_rows;  // > 0: gated mode, W = [2 * dual_rows, K]; N == dual_rows
+  int act;
+  int out_fp32;
+  int is_fp16;
+  int splits;
+  int* status;
+};
+
+__device__ __forceinline__ float apply_act(float g, int act) {
+  if (act == kActSilu) return g / (1.f + __expf(-g));
+  if (act == kActGeluTanh) {
+    const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return g / (1.f + __expf(-2.f * inner));
+  }
+  return g;
+}
+
+__device__ __forceinline__ float ld16_as_float(const void* p, size_t i, int is_fp16) {
+  if (is_fp16) return __half2float(reinterpret_cast<const __half*>(p)[i]);
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+template <int BN, int STAGES, bool DUAL>
+__global__ void __launch_bounds__(kThreads)
+dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                  const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+  constexpr int A_BYTES = BM * 128;
+  constexpr int B_BYTES = BN * 128;
+  constexpr int STAGE_BYTES = A_BYTES * (DUAL ? 2 : 1) + B_BYTES;
+  constexpr int TMEM_COLS_NEED = DUAL ? 2 * BN : BN;
+  constexpr uint32_t TMEM_COLS =
+      TMEM_COLS_NEED <= 32 ? 32 : TMEM_COLS_NEED <= 64 ? 64 : TMEM_COLS_NEED <= 128 ? 128
+                            : TMEM_COLS_NEED <= 256 ? 256 : 512;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* stage_base = smem;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* accum_bar = empty_bar + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  volatile int* aborted = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // fp32 staging of the accumulator tile(s); aliases the pipeline ring once the main loop is done.
+  float* stage_f32 = reinterpret_cast<float*>(smem);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BM;
+  const int t0 = blockIdx.y * BN;
+  const int S = p.splits;
+  const int rank = (S > 1) ? static_cast<int>(blockIdx.z) : 0;
+
+  const int kb_total = (p.K + BK - 1) / BK;
+  const int kb_begin = static_cast<int>((static_cast<long long>(kb_total) * rank) / S);
+  const int kb_end = static_cast<int>((static_cast<long long>(kb_total) * (rank + 1)) / S);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(accum_bar, 1);
+    *aborted = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      tma_prefetch_desc(&tmap_w);
+      tma_prefetch_desc(&tmap_x);
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        const int it = kb - kb_begin;
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
+          set_status(p.status, kStatusTimeoutEmpty);
+          *aborted = 1;
+          break;
+        }
+        uint8_t* a = stage_base + s * STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        tma_load_2d(a, &tmap_w, &full_bar[s], kb * BK, n0);
+        if (DUAL) tma_load_2d(a + A_BYTES, &tmap_w, &full_bar[s], kb * BK, p.dual_rows + n0);
+        tma_load_2d(a + A_BYTES * (DUAL ? 2 : 1), &tmap_x, &full_bar[s], kb * BK, t0);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = umma_idesc_f16(p.is_fp16 ? 0 : 1, BM, BN);
+      bool ok = true;
+      for (int kb = kb_begin; kb < kb_end && ok; ++kb) {
+        const int it = kb - kb_begin;
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(&full_bar[s], ph)) {
+          set_status(p.status, kStatusTimeoutFull);
+          *aborted = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(stage_base + s * STAGE_BYTES);
+        const uint32_t b_addr = a_addr + A_BYTES * (DUAL ? 2 : 1);
+        const uint64_t da = umma_desc_sw128_kmajor(a_addr);
+        const uint64_t db = umma_desc_sw128_kmajor(b_addr);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k) {
+          const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+          // advancing 16 elements along K inside the swizzle atom = +32 bytes = +2 in the
+          // (address >> 4) field of the descriptor
+          umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, acc);
+          if (DUAL) {
+            const uint64_t da2 = umma_desc_sw128_kmajor(a_addr + A_BYTES);
+            umma_f16(tmem_base + BN, da2 + 2 * k, db + 2 * k, idesc, acc);
+          }
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      umma_commit(accum_bar);
+    }
+  }
+  // ---------------------------------------------------------------- epilogue part 1 (warps 2..5)
+  // Wait for the accumulator, then park it as fp32 in shared memory laid out [token][weight row].
+  if (warp >= 2) {
+    bool ok = mbar_wait(accum_bar, 0);
+    if (!ok) {
+      set_status(p.status, kStatusTimeoutAccum);
+      *aborted = 1;
+    }
+    tc_fence_after();
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int n_local = q * 32 + lane;
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    if (ok) {
+      const bool fuse_act_now = DUAL && (S == 1);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld_x16(taddr + c0, r);
+        if (DUAL) {
+          uint32_t u[16];
+          tmem_ld_x16(taddr + BN + c0, u);
+          tmem_ld_wait();
+          if (fuse_act_now) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              stage_f32[(c0 + j) * BM + n_local] =
+                  apply_act(__uint_as_float(r[j]), p.act) * __uint_as_float(u[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              stage_f32[(c0 + j) * BM + n_local] = __uint_as_float(r[j]);
+              stage_f32[BN * BM + (c0 + j) * BM + n_local] = __uint_as_float(u[j]);
+            }
+          }
+        } else {
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) stage_f32[(c0 + j) * BM + n_local] = __uint_as_float(r[j]);
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  cg::cluster_group cluster = cg::this_cluster();
+  if (S > 1) cluster.sync();
+
+  // ---------------------------------------------------------------- epilogue part 2 (all threads)
+  // Rows (tokens) rank, rank+S, ... of the tile belong to this CTA: sum the S partial tiles through
+  // distributed shared memory, apply the epilogue and store 8 outputs per thread.
+  if (!*aborted) {
+    const int rows_mine = (BN - rank + S - 1) / S;
+    for (int idx = threadIdx.x; idx < rows_mine * (BM / 8); idx += kThreads) {
+      const int tl = rank + (idx / (BM / 8)) * S;
+      const int nl = (idx % (BM / 8)) * 8;
+      const int t = t0 + tl;
+      const int n = n0 + nl;
+      if (t >= p.T || n >= p.N) continue;
+      float g[8], u[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { g[j] = 0.f; u[j] = 0.f; }
+      for (int pr = 0; pr < S; ++pr) {
+        const float* src = (S > 1) ? cluster.map_shared_rank(stage_f32, pr) : stage_f32;
+        const float4 a = *reinterpret_cast<const float4*>(src + tl * BM + nl);
+        const float4 b = *reinterpret_cast<const float4*>(src + tl * BM + nl + 4);
+        g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
+        g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+        if (DUAL && S > 1) {
+          const float4 c = *reinterpret_cast<const float4*>(src + BN * BM + tl * BM + nl);
+          const float4 d = *reinterpret_cast<const float4*>(src + BN * BM + tl * BM + nl + 4);
+          u[0] += c.x; u[1] += c.y; u[2] += c.z; u[3] += c.w;
+          u[4] += d.x; u[5] += d.y; u[6] += d.z; u[7] += d.w;
+        }
+      }
+      if (DUAL && S > 1) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] = apply_act(g[j], p.act) * u[j];
+      } else if (!DUAL && p.act != kActNone) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] = apply_act(g[j], p.act);
+      }
+      const int nvalid = min(8, p.N - n);
+      if (p.bias != nullptr) {
+        for (int j = 0; j < nvalid; ++j) g[j] += ld16_as_float(p.bias, n + j, p.is_fp16);
+      }
+      const size_t off = static_cast<size_t>(t) * p.ldc + n;
+      if (p.out_fp32) {
+        float* C = reinterpret_cast<float*>(p.C);
+        if (p.residual != nullptr)
+          for (int j = 0; j < nvalid; ++j) g[j] += reinterpret_cast<const float*>(p.residual)[off + j];
+        if (nvalid == 8) {
+          *reinterpret_cast<float4*>(C + off) = make_float4(g[0], g[1], g[2], g[3]);
+          *reinterpret_cast<float4*>(C + off + 4) = make_float4(g[4], g[5], g[6], g[7]);
+        } else {
+          for (int j = 0; j < nvalid; ++j) C[off + j] = g[j];
+        }
+      } else {
+        if (p.residual != nullptr)
+          for (int j = 0; j < nvalid; ++j) g[j] += ld16_as_float(p.residual, off + j, p.is_fp16);
+        uint32_t packed[4];
+        if (p.is_fp16) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            __half2 h = __floats2half2_rn(g[2 * j], g[2 * j + 1]);
+            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(g[2 * j], g[2 * j + 1]);
+            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        }
+        uint16_t* C = reinterpret_cast<uint16_t*>(p.C);
+        if (nvalid == 8) {
+          *reinterpret_cast<uint4*>(C + off) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        } else {
+          const uint16_t* ph = reinterpret_cast<const uint16_t*>(packed);
+          for (int j = 0; j < nvalid; ++j) C[off + j] = ph[j];
+        }
+      }
+    }
+  }
+  if (S > 1) cluster.sync();  // nobody leaves while a peer may still read its staging tile
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN, int STAGES, bool DUAL>
+constexpr int smem_bytes() {
+  return STAGES * (BM * 128 * (DUAL ? 2 : 1) + BN * 128) + (2 * STAGES + 1) * 8 + 16 + 1024;
+}
+
+template <int BN, int STAGES, bool DUAL>
+int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
+  auto kern = dense_gemm_kernel<BN, STAGES, DUAL>;
+  constexpr int smem = smem_bytes<BN, STAGES, DUAL>();
+  constexpr int ring = STAGES * (BM * 128 * (DUAL ? 2 : 1) + BN * 128);
+  static_assert(BN * BM * 4 <= ring, "fp32 staging tile must fit inside the pipeline ring");
+  if (BN * BM * 4 * ((DUAL && p.splits > 1) ? 2 : 1) > ring) return -12;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((p.N + BM - 1) / BM, (p.T + BN - 1) / BN, p.splits);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = p.splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, tw, tx, p));
+}
+
+template <bool DUAL>
+int dispatch(int bn, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p,
+             cudaStream_t s) {
+  switch (bn) {
+    case 16: return launch<16, DUAL ? 5 : 8, DUAL>(tw, tx, p, s);
+    case 32: return launch<32, DUAL ? 5 : 8, DUAL>(tw, tx, p, s);
+    case 64: return launch<64, DUAL ? 4 : 6, DUAL>(tw, tx, p, s);
+    case 128: return launch<128, DUAL ? 2 : 3, DUAL>(tw, tx, p, s);
+    default: return launch<256, DUAL ? 3 : 4, DUAL>(tw, tx, p, s);
+  }
+}
+
+}  // namespace
+
+// Token-tile choice: the smallest tile that covers T up to 128; 128 for everything larger (two CTAs
+// fit per SM and overlap each other's epilogue); 256 only on request.
+extern "C" int fi_dense_gemm_pick_bn(int T) {
+  if (T <= 16) return 16;
+  if (T <= 32) return 32;
+  if (T <= 64) return 64;
+  return 128;
+}
+
+// C = X W^T with optional epilogue.  All pointers are device pointers; nothing is allocated.
+//   dtype: 0 = bf16, 1 = fp16 (X, W, bias; C/residual too unless out_fp32)
+//   dual_rows > 0: gated mode, W holds [gate rows; up rows], N must equal dual_rows
+//   splits: 0 = choose automatically, else the split-K cluster size (1..8)
+//   bn: 0 = choose automatically
+// Returns 0 or a negative argument error / positive CUDA error code.
+extern "C" int fi_dense_gemm(const void* X, const void* W, void* C, const void* bias,
+                             const void* residual, int T, int N, int K, int ldx, int ldw, int ldc,
+                             int act, int dual_rows, int out_fp32, int dtype, int splits, int bn,
+                             int* status, void* stream) {
+  if (T <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K % 8) != 0 || (ldc % 8) != 0 || (reinterpret_cast<uintptr_t>(C) & 15) != 0) return -10;
+  if (dual_rows > 0 && N != dual_rows) return -11;
+  if (bn == 0) bn = fi_dense_gemm_pick_bn(T);
+  const int w_rows = dual_rows > 0 ? 2 * dual_rows : N;
+  CUtensorMap tw, tx;
+  int r = make_tmap_2d_16bit_sw128(&tw, W, w_rows, K, ldw, BM);
+  if (r != 0) return r * 100 - 1;
+  r = make_tmap_2d_16bit_sw128(&tx, X, T, K, ldx, bn);
+  if (r != 0) return r * 100 - 2;
+  const int kb_total = (K + BK - 1) / BK;
+  if (splits <= 0) {
+    const int tiles = ((N + BM - 1) / BM) * ((T + bn - 1) / bn);
+    splits = 1;
+    if (tiles < 100) {
+      splits = 148 / tiles;
+      if (splits > 8) splits = 8;
+      while (splits > 1 && kb_total / splits < 2) --splits;
+      if (splits < 1) splits = 1;
+    }
+  }
+  if (splits > 8) splits = 8;
+  if (splits > kb_total) splits = kb_total;
+  // The fp32 staging tile(s) alias the pipeline ring.  Gated mode with split-K parks two tiles
+  // (gate and up partials), which only fits for token tiles up to 64; large token tiles have
+  // plenty of CTAs anyway, so they never split.
+  if (bn >= 128 && (dual_rows > 0 || bn > 128)) splits = 1;
+  GemmParams p;
+  p.C = C; p.bias = bias; p.residual = residual;
+  p.T = T; p.N = N; p.K = K; p.ldc = ldc;
+  p.dual_rows = dual_rows; p.act = act; p.out_fp32 = out_fp32; p.is_fp16 = dtype == 1;
+  p.splits = splits; p.status = status;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (dual_rows > 0) return dispatch<true>(bn, tw, tx, p, s);
+  return dispatch<false>(bn, tw, tx, p, s);
+}

@@ -1,0 +1,450 @@
+// Memory-bound helper kernels for sm_100a: RMSNorm family, fused rotary-embedding + KV-cache write
+// (optionally with per-head q/k norm and fp8-e4m3 quantisation), embedding gather, gated
+// activation, slot mapping and greedy arg-max.  All use 16-byte vector accesses and fp32 math.
+//
+// Counterparts in the reference (all Triton or eager torch there):
+//   vllm/kernels/triton/rms_norm.py:29-125, vllm/model_executor/layers/layernorm.py:12-21,
+//   vllm/kernels/triton/reshape_and_cache.py:129-297,
+//   vllm/model_executor/layers/rotary_embedding/common.py:139-168 and mrope.py:11-127,
+//   vllm/kernels/triton/embedding.py:24-79, vllm/kernels/triton/activation.py:21-137,
+//   vllm/kernels/triton/compute_slot_mapping.py:23-73, vllm/engine/sampling/sampler.py:18-40.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace {
+
+template <typename T> struct Cvt;
+template <> struct Cvt<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16(v); }
+};
+template <> struct Cvt<__half> {
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half(v); }
+};
+template <> struct Cvt<float> {
+  static __device__ __forceinline__ float to_f(float v) { return v; }
+  static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  float t = (threadIdx.x < nw) ? red[threadIdx.x] : 0.f;
+  if (w == 0) {
+    t = warp_sum(t);
+    if (l == 0) red[0] = t;
+  }
+  __syncthreads();
+  t = red[0];
+  __syncthreads();
+  return t;
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// out[r, :] = x[r, :] * rsqrt(mean(x^2) + eps) * (w or 1+w or 1).  Optional residual:
+//   residual[r, :] += x[r, :] first (stored back), and the norm runs on the sum.
+// One block per row for wide rows; rows narrower than 1024 elements use one warp per row.
+template <typename T, bool WARP_ROWS>
+__global__ void rmsnorm_kernel(const T* __restrict__ x, T* __restrict__ residual,
+                               const T* __restrict__ w, T* __restrict__ out, int rows, int H,
+                               long ldx, long ldo, float eps, int w_mode, float out_scale) {
+  __shared__ float red[32];
+  constexpr int V = 16 / sizeof(T);
+  int row, tid, nthr;
+  if (WARP_ROWS) {
+    row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    tid = threadIdx.x & 31;
+    nthr = 32;
+    if (row >= rows) return;
+  } else {
+    row = blockIdx.x;
+    tid = threadIdx.x;
+    nthr = blockDim.x;
+  }
+  const T* xr = x + static_cast<long>(row) * ldx;
+  T* rr = residual ? residual + static_cast<long>(row) * ldx : nullptr;
+  T* orow = out + static_cast<long>(row) * ldo;
+  float ss = 0.f;
+  for (int i = tid * V; i < H; i += nthr * V) {
+    uint4 raw = *reinterpret_cast<const uint4*>(xr + i);
+    T* e = reinterpret_cast<T*>(&raw);
+    if (rr) {
+      uint4 rraw = *reinterpret_cast<const uint4*>(rr + i);
+      T* re = reinterpret_cast<T*>(&rraw);
+#pragma unroll
+      for (int j = 0; j < V; ++j) re[j] = Cvt<T>::from_f(Cvt<T>::to_f(e[j]) + Cvt<T>::to_f(re[j]));
+      *reinterpret_cast<uint4*>(rr + i) = rraw;
+#pragma unroll
+      for (int j = 0; j < V; ++j) { float f = Cvt<T>::to_f(re[j]); ss += f * f; }
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) { float f = Cvt<T>::to_f(e[j]); ss += f * f; }
+    }
+  }
+  if (WARP_ROWS) ss = warp_sum(ss); else ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / static_cast<float>(H) + eps) * out_scale;
+  const T* src = rr ? rr : xr;
+  for (int i = tid * V; i < H; i += nthr * V) {
+    uint4 raw = *reinterpret_cast<const uint4*>(src + i);
+    T* e = reinterpret_cast<T*>(&raw);
+    uint4 wraw = make_uint4(0, 0, 0, 0);
+    if (w_mode != 2) wraw = *reinterpret_cast<const uint4*>(w + i);
+    T* we = reinterpret_cast<T*>(&wraw);
+    uint4 oraw;
+    T* oe = reinterpret_cast<T*>(&oraw);
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      // the normalised value is rounded to the storage type before the weight multiply
+      float nv = Cvt<T>::to_f(Cvt<T>::from_f(Cvt<T>::to_f(e[j]) * inv));
+      float g = w_mode == 0 ? Cvt<T>::to_f(we[j]) : w_mode == 1 ? 1.f + Cvt<T>::to_f(we[j]) : 1.f;
+      oe[j] = Cvt<T>::from_f(nv * g);
+    }
+    *reinterpret_cast<uint4*>(orow + i) = oraw;
+  }
+}
+
+// ------------------------------------------------------------------ RoPE + KV-cache write
+// qkv: [T, (nh + 2*nkv) * hd] (q heads, then k heads, then v heads).  For each token:
+//   optional per-head RMSNorm on q and k (weights qw/kw of length hd; w_mode as above; v may get a
+//   weightless norm), neox-style rotation of the first rot_dim channels of q and k in place, then
+//   k and v rows are written to the paged cache [num_blocks, nkv, block_size, hd] at slot
+//   slot_mapping[t] (negative = skip), as 16-bit copies or as fp8 e4m3 of (value / scale).
+// cos_sin: fp32 [max_pos, rot_dim] = [cos(rot_dim/2) | sin(rot_dim/2)].
+// positions: [n_streams, T]; freq_stream[i] (optional) picks the position stream of frequency i
+// (multimodal rotary sections); null = stream 0.
+template <typename T>
+__global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                  const float* __restrict__ cos_sin,
+                                  const int* __restrict__ freq_stream,
+                                  const int* __restrict__ slot_mapping, void* __restrict__ k_cache,
+                                  void* __restrict__ v_cache, const T* __restrict__ qw,
+                                  const T* __restrict__ kw, int T_tokens, int nh, int nkv, int hd,
+                                  int rot_dim, int block_size, int kv_fp8, float k_scale,
+                                  float v_scale, float eps, int qk_norm_mode, int v_norm) {
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nwarps = blockDim.x >> 5;
+  const int total_heads = nh + 2 * nkv;
+  T* row = qkv + static_cast<long>(t) * total_heads * hd;
+  const int slot = slot_mapping ? slot_mapping[t] : -1;
+  const int half = rot_dim >> 1;
+  for (int h = warp; h < total_heads; h += nwarps) {
+    T* x = row + static_cast<long>(h) * hd;
+    const bool is_q = h < nh;
+    const bool is_k = !is_q && h < nh + nkv;
+    const bool is_v = !is_q && !is_k;
+    float inv = 1.f;
+    const bool do_norm = (qk_norm_mode >= 0 && !is_v) || (is_v && v_norm);
+    if (do_norm) {
+      float ss = 0.f;
+      for (int i = lane; i < hd; i += 32) { float f = Cvt<T>::to_f(x[i]); ss += f * f; }
+      ss = warp_sum(ss);
+      inv = rsqrtf(ss / static_cast<float>(hd) + eps);
+    }
+    const T* nw = is_q ? qw : kw;
+    auto load = [&](int i) -> float {
+      float f = Cvt<T>::to_f(x[i]);
+      if (do_norm) {
+        f = Cvt<T>::to_f(Cvt<T>::from_f(f * inv));
+        if (!is_v && nw != nullptr) {
+          float g = Cvt<T>::to_f(nw[i]);
+          f *= (qk_norm_mode == 1) ? (1.f + g) : g;
+        }
+        f = Cvt<T>::to_f(Cvt<T>::from_f(f));
+      }
+      return f;
+    };
+    const int kvh = is_k ? h - nh : h - nh - nkv;
+    long cache_off = 0;
+    if (!is_q && slot >= 0) {
+      const int blk = slot / block_size, off = slot % block_size;
+      cache_off = ((static_cast<long>(blk) * nkv + kvh) * block_size + off) * hd;
+    }
+    const float qscale = is_k ? 1.f / k_scale : 1.f / v_scale;
+    auto store_cache = [&](int i, float f) {
+      if (is_q || slot < 0) return;
+      void* base = is_k ? k_cache : v_cache;
+      if (kv_fp8) {
+        reinterpret_cast<__nv_fp8_e4m3*>(base)[cache_off + i] = __nv_fp8_e4m3(f * qscale);
+      } else {
+        reinterpret_cast<T*>(base)[cache_off + i] = Cvt<T>::from_f(f);
+      }
+    };
+    if (is_v) {
+      for (int i = lane; i < hd; i += 32) {
+        float f = load(i);
+        if (do_norm) x[i] = Cvt<T>::from_f(f);
+        store_cache(i, f);
+      }
+      continue;
+    }
+    // rotated part: pairs (i, i + half)
+    for (int i = lane; i < half; i += 32) {
+      const int stream = freq_stream ? freq_stream[i] : 0;
+      const int pos = positions[static_cast<long>(stream) * T_tokens + t];
+      const float c = cos_sin[static_cast<long>(pos) * rot_dim + i];
+      const float s = cos_sin[static_cast<long>(pos) * rot_dim + half + i];
+      const float a = load(i), b = load(i + half);
+      const float ra = Cvt<T>::to_f(Cvt<T>::from_f(a * c - b * s));
+      const float rb = Cvt<T>::to_f(Cvt<T>::from_f(b * c + a * s));
+      x[i] = Cvt<T>::from_f(ra);
+      x[i + half] = Cvt<T>::from_f(rb);
+      store_cache(i, ra);
+      store_cache(i + half, rb);
+    }
+    for (int i = rot_dim + lane; i < hd; i += 32) {
+      float f = load(i);
+      if (do_norm) x[i] = Cvt<T>::from_f(f);
+      store_cache(i, f);
+    }
+  }
+}
+
+// Plain cache write (no rotation): k/v rows [T, nkv, hd] with row pitch ld -> paged cache.
+template <typename T>
+__global__ void reshape_and_cache_kernel(const T* __restrict__ k, const T* __restrict__ v,
+                                         const int* __restrict__ slot_mapping,
+                                         void* __restrict__ k_cache, void* __restrict__ v_cache,
+                                         long ldk, long ldv, int nkv, int hd, int block_size,
+                                         int kv_fp8, float k_scale, float v_scale) {
+  const int t = blockIdx.x;
+  const int slot = slot_mapping[t];
+  if (slot < 0) return;
+  const int blk = slot / block_size, off = slot % block_size;
+  for (int i = threadIdx.x; i < nkv * hd; i += blockDim.x) {
+    const int h = i / hd, d = i % hd;
+    const long dst = ((static_cast<long>(blk) * nkv + h) * block_size + off) * hd + d;
+    const float kf = Cvt<T>::to_f(k[static_cast<long>(t) * ldk + i]);
+    const float vf = Cvt<T>::to_f(v[static_cast<long>(t) * ldv + i]);
+    if (kv_fp8) {
+      reinterpret_cast<__nv_fp8_e4m3*>(k_cache)[dst] = __nv_fp8_e4m3(kf / k_scale);
+      reinterpret_cast<__nv_fp8_e4m3*>(v_cache)[dst] = __nv_fp8_e4m3(vf / v_scale);
+    } else {
+      reinterpret_cast<T*>(k_cache)[dst] = Cvt<T>::from_f(kf);
+      reinterpret_cast<T*>(v_cache)[dst] = Cvt<T>::from_f(vf);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ embedding gather
+template <typename T>
+__global__ void embedding_kernel(const long* __restrict__ ids, const T* __restrict__ table,
+                                 T* __restrict__ out, int H, float scale, int vocab_start,
+                                 int vocab_end) {
+  constexpr int V = 16 / sizeof(T);
+  const long id = ids[blockIdx.x];
+  T* o = out + static_cast<long>(blockIdx.x) * H;
+  const bool mine = id >= vocab_start && id < vocab_end;
+  const T* src = table + (mine ? (id - vocab_start) : 0) * static_cast<long>(H);
+  for (int i = threadIdx.x * V; i < H; i += blockDim.x * V) {
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (mine) {
+      raw = *reinterpret_cast<const uint4*>(src + i);
+      if (scale != 1.f) {
+        T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+        for (int j = 0; j < V; ++j) e[j] = Cvt<T>::from_f(Cvt<T>::to_f(e[j]) * scale);
+      }
+    }
+    *reinterpret_cast<uint4*>(o + i) = raw;
+  }
+}
+
+// ------------------------------------------------------------------ act(gate) * up on [rows, 2d]
+template <typename T>
+__global__ void act_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int d, long ldx,
+                               int act) {
+  const long r = blockIdx.x;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float g = Cvt<T>::to_f(x[r * ldx + i]);
+    const float u = Cvt<T>::to_f(x[r * ldx + d + i]);
+    float a;
+    if (act == 1) a = g / (1.f + __expf(-g));
+    else if (act == 2) {
+      const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+      a = g / (1.f + __expf(-2.f * inner));
+    } else a = g;
+    out[r * d + i] = Cvt<T>::from_f(a * u);
+  }
+}
+
+// ------------------------------------------------------------------ slot mapping
+// slot[t] = block_tables[seq, pos / bs] * bs + pos % bs  (block id 0 is the null block -> -1).
+__global__ void slot_mapping_kernel(const int* __restrict__ positions,
+                                    const int* __restrict__ token_seq,
+                                    const int* __restrict__ block_tables, int max_blocks, int bs,
+                                    int* __restrict__ slots, int T) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  const int pos = positions[t];
+  const int seq = token_seq[t];
+  if (seq < 0 || pos < 0) { slots[t] = -1; return; }
+  const int blk = block_tables[static_cast<long>(seq) * max_blocks + pos / bs];
+  slots[t] = blk <= 0 ? -1 : blk * bs + pos % bs;
+}
+
+// ------------------------------------------------------------------ greedy arg-max
+// One block per row; ties resolve to the lowest index (matches torch.argmax on CPU).
+template <typename T>
+__global__ void argmax_kernel(const T* __restrict__ logits, long ld, int V, long* __restrict__ out,
+                              float softcap) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const T* row = logits + static_cast<long>(blockIdx.x) * ld;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float f = Cvt<T>::to_f(row[i]);
+    if (f > best || (f == best && i < bi)) { best = f; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) { sv[w] = best; si[w] = bi; }
+  __syncthreads();
+  if (w == 0) {
+    const int nw = blockDim.x >> 5;
+    best = l < nw ? sv[l] : -INFINITY;
+    bi = l < nw ? si[l] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (l == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+  }
+  (void)softcap;
+}
+
+template <typename F>
+int dispatch_dtype(int dtype, F&& f) {
+  if (dtype == 0) return f(static_cast<__nv_bfloat16*>(nullptr));
+  if (dtype == 1) return f(static_cast<__half*>(nullptr));
+  return -1;
+}
+
+}  // namespace
+
+#define FI_STREAM(s) reinterpret_cast<cudaStream_t>(s)
+
+// w_mode: 0 = x*w, 1 = x*(1+w), 2 = no weight.  residual may be null.  dtype 0 bf16 / 1 fp16.
+extern "C" int fi_rmsnorm(const void* x, void* residual, const void* w, void* out, int rows, int H,
+                          long ldx, long ldo, float eps, int w_mode, float out_scale, int dtype,
+                          void* stream) {
+  if (rows <= 0) return 0;
+  if (H % 8 != 0 || ldx % 8 != 0 || ldo % 8 != 0) return -10;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    if (H <= 1024) {
+      const int wpb = 4;
+      rmsnorm_kernel<T, true><<<(rows + wpb - 1) / wpb, wpb * 32, 0, FI_STREAM(stream)>>>(
+          (const T*)x, (T*)residual, (const T*)w, (T*)out, rows, H, ldx, ldo, eps, w_mode,
+          out_scale);
+    } else {
+      int threads = H / 8;
+      threads = threads > 1024 ? 1024 : ((threads + 31) / 32) * 32;
+      rmsnorm_kernel<T, false><<<rows, threads, 0, FI_STREAM(stream)>>>(
+          (const T*)x, (T*)residual, (const T*)w, (T*)out, rows, H, ldx, ldo, eps, w_mode,
+          out_scale);
+    }
+    return static_cast<int>(cudaGetLastError());
+  });
+}
+
+extern "C" int fi_rope_cache(void* qkv, const int* positions, const float* cos_sin,
+                             const int* freq_stream, const int* slot_mapping, void* k_cache,
+                             void* v_cache, const void* qw, const void* kw, int T, int nh, int nkv,
+                             int hd, int rot_dim, int block_size, int kv_fp8, float k_scale,
+                             float v_scale, float eps, int qk_norm_mode, int v_norm, int dtype,
+                             void* stream) {
+  if (T <= 0) return 0;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using Tt = std::remove_pointer_t<decltype(tag)>;
+    int warps = nh + 2 * nkv;
+    if (warps > 16) warps = 16;
+    rope_cache_kernel<Tt><<<T, warps * 32, 0, FI_STREAM(stream)>>>(
+        (Tt*)qkv, positions, cos_sin, freq_stream, slot_mapping, k_cache, v_cache, (const Tt*)qw,
+        (const Tt*)kw, T, nh, nkv, hd, rot_dim, block_size, kv_fp8, k_scale, v_scale, eps,
+        qk_norm_mode, v_norm);
+    return static_cast<int>(cudaGetLastError());
+  });
+}
+
+extern "C" int fi_reshape_and_cache(const void* k, const void* v, const int* slot_mapping,
+                                    void* k_cache, void* v_cache, int T, long ldk, long ldv,
+                                    int nkv, int hd, int block_size, int kv_fp8, float k_scale,
+                                    float v_scale, int dtype, void* stream) {
+  if (T <= 0) return 0;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using Tt = std::remove_pointer_t<decltype(tag)>;
+    reshape_and_cache_kernel<Tt><<<T, 256, 0, FI_STREAM(stream)>>>(
+        (const Tt*)k, (const Tt*)v, slot_mapping, k_cache, v_cache, ldk, ldv, nkv, hd, block_size,
+        kv_fp8, k_scale, v_scale);
+    return static_cast<int>(cudaGetLastError());
+  });
+}
+
+extern "C" int fi_embedding(const long* ids, const void* table, void* out, int T, int H,
+                            float scale, int vocab_start, int vocab_end, int dtype, void* stream) {
+  if (T <= 0) return 0;
+  if (H % 8 != 0) return -10;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using Tt = std::remove_pointer_t<decltype(tag)>;
+    int threads = H / 8 > 256 ? 256 : ((H / 8 + 31) / 32) * 32;
+    embedding_kernel<Tt><<<T, threads, 0, FI_STREAM(stream)>>>(
+        ids, (const Tt*)table, (Tt*)out, H, scale, vocab_start, vocab_end);
+    return static_cast<int>(cudaGetLastError());
+  });
+}
+
+extern "C" int fi_act_mul(const void* x, void* out, int rows, int d, long ldx, int act, int dtype,
+                          void* stream) {
+  if (rows <= 0) return 0;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using Tt = std::remove_pointer_t<decltype(tag)>;
+    act_mul_kernel<Tt><<<rows, 256, 0, FI_STREAM(stream)>>>((const Tt*)x, (Tt*)out, d, ldx, act);
+    return static_cast<int>(cudaGetLastError());
+  });
+}
+
+extern "C" int fi_slot_mapping(const int* positions, const int* token_seq, const int* block_tables,
+                               int max_blocks, int bs, int* slots, int T, void* stream) {
+  if (T <= 0) return 0;
+  slot_mapping_kernel<<<(T + 255) / 256, 256, 0, FI_STREAM(stream)>>>(
+      positions, token_seq, block_tables, max_blocks, bs, slots, T);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// dtype: 0 bf16, 1 fp16, 2 fp32
+extern "C" int fi_argmax(const void* logits, long ld, int rows, int V, long* out, int dtype,
+                         void* stream) {
+  if (rows <= 0) return 0;
+  if (dtype == 2) {
+    argmax_kernel<float><<<rows, 1024, 0, FI_STREAM(stream)>>>((const float*)logits, ld, V, out, 0.f);
+  } else if (dtype == 0) {
+    argmax_kernel<__nv_bfloat16><<<rows, 1024, 0, FI_STREAM(stream)>>>(
+        (const __nv_bfloat16*)logits, ld, V, out, 0.f);
+  } else {
+    argmax_kernel<__half><<<rows, 1024, 0, FI_STREAM(stream)>>>((const __half*)logits, ld, V, out,
+                                                                 0.f);
+  }
+  return static_cast<int>(cudaGetLastError());
+}

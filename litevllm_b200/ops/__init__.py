@@ -1,0 +1,281 @@
+"""Op layer: one Python function per hot op.
+
+CUDA tensors go to the hand-written sm_100a kernels (``csrc/``, bound through ctypes); CPU tensors
+go to the PyTorch fp32 reference in :mod:`litevllm_b200.ops.reference`, which doubles as the test
+oracle.  There is no eager fallback for CUDA tensors: a missing native library raises.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib, reference
+
+_ACT = {None: 0, "none": 0, "silu": 1, "gelu_tanh": 2, "gelu_pytorch_tanh": 2, "gelu": 2}
+_DT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+
+_status_words: dict[int, torch.Tensor] = {}
+_scratch: dict[tuple, torch.Tensor] = {}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 word that kernels set when a bounded wait runs out (0 = healthy)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    w = _status_words.get(idx)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[idx] = w
+    return w
+
+
+def check_status(device: torch.device) -> None:
+    """Synchronising read of the status word; raises if any kernel reported a timeout."""
+    code = int(status_word(device).item())
+    if code != 0:
+        status_word(device).zero_()
+        raise RuntimeError(f"a device kernel reported status {code} (bounded wait ran out)")
+
+
+def scratch(name: str, nbytes: int, device: torch.device) -> torch.Tensor:
+    """Grow-only cached byte buffer (stable pointer while it does not grow)."""
+    key = (name, device.index)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+# ---------------------------------------------------------------------------- GEMM
+def linear(x, w, bias=None, residual=None, act=None, out=None, out_dtype=None, splits=0, bn=0):
+    """``act(x @ w.T) + bias + residual``.  x: [T, K], w: [N, K] (same 16-bit dtype)."""
+    if not x.is_cuda:
+        y = reference.linear(x, w, bias, residual, act, out_dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    T, K = x.shape
+    N = w.shape[0]
+    out_dtype = out_dtype or x.dtype
+    if out is None:
+        out = torch.empty(T, N, dtype=out_dtype, device=x.device)
+    if T == 0:
+        return out
+    assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    rc = _lib.kernels().fi_dense_gemm(
+        _p(x), _p(w), _p(out), _p(bias), _p(residual), T, N, K, x.stride(0), w.stride(0),
+        out.stride(0), _ACT[act], 0, 1 if out.dtype == torch.float32 else 0, _DT[x.dtype], splits,
+        bn, _p(status_word(x.device)), _stream())
+    _lib.check(rc, "fi_dense_gemm")
+    return out
+
+
+def gated_linear(x, w_gate_up, act="silu", out=None, splits=0, bn=0):
+    """``act(x @ Wg.T) * (x @ Wu.T)`` with ``w_gate_up = [Wg; Wu]`` of shape [2*I, K] -> [T, I]."""
+    if not x.is_cuda:
+        y = reference.gated_linear(x, w_gate_up, act)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    T, K = x.shape
+    inter = w_gate_up.shape[0] // 2
+    if out is None:
+        out = torch.empty(T, inter, dtype=x.dtype, device=x.device)
+    if T == 0:
+        return out
+    rc = _lib.kernels().fi_dense_gemm(
+        _p(x), _p(w_gate_up), _p(out), None, None, T, inter, K, x.stride(0), w_gate_up.stride(0),
+        out.stride(0), _ACT[act], inter, 0, _DT[x.dtype], splits, bn,
+        _p(status_word(x.device)), _stream())
+    _lib.check(rc, "fi_dense_gemm(gated)")
+    return out
+
+
+# ---------------------------------------------------------------------------- norms
+def rmsnorm(x, w, eps, residual=None, w_mode=0, out=None, out_scale=1.0):
+    """RMSNorm over the last dim of a 2-D tensor.  With ``residual`` the sum x+residual is written
+    back into ``residual`` first (in place) and normalised.  Returns ``out``."""
+    if not x.is_cuda:
+        y, new_res = reference.rmsnorm(x, w, eps, residual, w_mode, out_scale)
+        if residual is not None:
+            residual.copy_(new_res)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    rows, H = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    if residual is not None:
+        assert residual.stride(0) == x.stride(0)
+    rc = _lib.kernels().fi_rmsnorm(_p(x), _p(residual), _p(w), _p(out), rows, H, x.stride(0),
+                                   out.stride(0), eps, w_mode, out_scale, _DT[x.dtype], _stream())
+    _lib.check(rc, "fi_rmsnorm")
+    return out
+
+
+# ---------------------------------------------------------------------------- rope + cache
+def rope_and_cache(qkv, positions, cos_sin, slot_mapping, k_cache, v_cache, nh, nkv, hd, rot_dim,
+                   freq_stream=None, q_norm_w=None, k_norm_w=None, qk_norm_mode=-1, v_norm=False,
+                   eps=1e-6, k_scale=1.0, v_scale=1.0):
+    if not qkv.is_cuda:
+        return reference.rope_and_cache(qkv, positions, cos_sin, slot_mapping, k_cache, v_cache, nh,
+                                        nkv, hd, rot_dim, freq_stream, q_norm_w, k_norm_w,
+                                        qk_norm_mode, v_norm, eps, k_scale, v_scale)
+    T = qkv.shape[0]
+    assert qkv.is_contiguous() and positions.dtype == torch.int32
+    assert slot_mapping.dtype == torch.int32
+    rc = _lib.kernels().fi_rope_cache(
+        _p(qkv), _p(positions), _p(cos_sin), _p(freq_stream), _p(slot_mapping), _p(k_cache),
+        _p(v_cache), _p(q_norm_w), _p(k_norm_w), T, nh, nkv, hd, rot_dim, k_cache.shape[2],
+        1 if k_cache.dtype == torch.float8_e4m3fn else 0, k_scale, v_scale, eps, qk_norm_mode,
+        1 if v_norm else 0, _DT[qkv.dtype], _stream())
+    _lib.check(rc, "fi_rope_cache")
+
+
+def reshape_and_cache(k, v, slot_mapping, k_cache, v_cache, k_scale=1.0, v_scale=1.0):
+    """k, v: [T, nkv, hd] (last two dims contiguous)."""
+    if not k.is_cuda:
+        return reference.reshape_and_cache(k, v, slot_mapping, k_cache, v_cache, k_scale, v_scale)
+    T, nkv, hd = k.shape
+    rc = _lib.kernels().fi_reshape_and_cache(
+        _p(k), _p(v), _p(slot_mapping), _p(k_cache), _p(v_cache), T, k.stride(0), v.stride(0), nkv,
+        hd, k_cache.shape[2], 1 if k_cache.dtype == torch.float8_e4m3fn else 0, k_scale, v_scale,
+        _DT[k.dtype], _stream())
+    _lib.check(rc, "fi_reshape_and_cache")
+
+
+# ---------------------------------------------------------------------------- attention
+def pick_decode_splits(B: int, nkv: int, max_kv_len: int, sm_count: int = 148) -> int:
+    chunks = max(1, (max_kv_len + 63) // 64)
+    ctas = max(1, B * nkv)
+    want = max(1, (2 * sm_count + ctas - 1) // ctas)
+    return int(max(1, min(want, chunks, 32)))
+
+
+def paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, nh, nkv, hd, sm_scale,
+                           window=0, softcap=0.0, k_scale=1.0, v_scale=1.0, out=None, splits=0,
+                           max_kv_len=None, cu_q=None):
+    """One query token per sequence.  q: [B, >= nh*hd] with row stride q.stride(0)."""
+    B = seq_lens.shape[0]
+    if not q.is_cuda:
+        cu = torch.arange(B + 1, dtype=torch.int32)
+        y = reference.paged_attention(q, k_cache, v_cache, block_tables, seq_lens, cu, nh, nkv, hd,
+                                      sm_scale, window, softcap, k_scale, v_scale)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    if out is None:
+        out = torch.empty(B, nh * hd, dtype=q.dtype, device=q.device)
+    if splits <= 0:
+        if max_kv_len is None:
+            max_kv_len = block_tables.shape[1] * k_cache.shape[2]
+        eff = min(max_kv_len, window) if window and window > 0 else max_kv_len
+        splits = pick_decode_splits(B, nkv, eff)
+    ws_o = ws_ml = None
+    if splits > 1:
+        n_o = B * nh * splits * hd
+        buf = scratch("decode_ws", (n_o + B * nh * splits * 2) * 4, q.device)
+        ws = buf.view(torch.float32)
+        ws_o, ws_ml = ws[:n_o], ws[n_o:]
+    rc = _lib.kernels().fi_paged_decode(
+        _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(block_tables), _p(seq_lens),
+        _p(ws_o), _p(ws_ml), B, nh, nkv, hd, block_tables.shape[1], k_cache.shape[2], int(window or 0),
+        sm_scale, float(softcap or 0.0), 1 if k_cache.dtype == torch.float8_e4m3fn else 0, k_scale,
+        v_scale, splits, _DT[q.dtype], _stream())
+    _lib.check(rc, "fi_paged_decode")
+    return out
+
+
+def paged_attention_prefill(q, k_cache, v_cache, block_tables, seq_lens, cu_q, max_q_len, nh, nkv,
+                            hd, sm_scale, window=0, softcap=0.0, k_scale=1.0, v_scale=1.0, out=None):
+    """Varlen causal attention of new tokens against the paged cache (which already holds them)."""
+    if not q.is_cuda:
+        y = reference.paged_attention(q, k_cache, v_cache, block_tables, seq_lens, cu_q, nh, nkv, hd,
+                                      sm_scale, window, softcap, k_scale, v_scale)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    T = q.shape[0]
+    B = seq_lens.shape[0]
+    if out is None:
+        out = torch.empty(T, nh * hd, dtype=q.dtype, device=q.device)
+    rc = _lib.kernels().fi_paged_prefill(
+        _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(block_tables), _p(seq_lens),
+        _p(cu_q), B, int(max_q_len), nh, nkv, hd, block_tables.shape[1], k_cache.shape[2],
+        int(window or 0), sm_scale, float(softcap or 0.0),
+        1 if k_cache.dtype == torch.float8_e4m3fn else 0, k_scale, v_scale, _DT[q.dtype], _stream())
+    _lib.check(rc, "fi_paged_prefill")
+    return out
+
+
+# ---------------------------------------------------------------------------- small ops
+def embedding(ids, table, scale=1.0, vocab_start=0, vocab_end=None, out=None):
+    if not table.is_cuda:
+        y = reference.embedding(ids, table, scale, vocab_start, vocab_end)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    T, H = ids.shape[0], table.shape[1]
+    vocab_end = vocab_start + table.shape[0] if vocab_end is None else vocab_end
+    if out is None:
+        out = torch.empty(T, H, dtype=table.dtype, device=table.device)
+    assert ids.dtype == torch.int64
+    rc = _lib.kernels().fi_embedding(_p(ids), _p(table), _p(out), T, H, scale, vocab_start,
+                                     vocab_end, _DT[table.dtype], _stream())
+    _lib.check(rc, "fi_embedding")
+    return out
+
+
+def act_mul(x, act="silu", out=None):
+    if not x.is_cuda:
+        return reference.act_mul(x, act)
+    rows, d2 = x.shape
+    if out is None:
+        out = torch.empty(rows, d2 // 2, dtype=x.dtype, device=x.device)
+    rc = _lib.kernels().fi_act_mul(_p(x), _p(out), rows, d2 // 2, x.stride(0), _ACT[act],
+                                   _DT[x.dtype], _stream())
+    _lib.check(rc, "fi_act_mul")
+    return out
+
+
+def slot_mapping(positions, token_seq, block_tables, block_size, out=None):
+    if not positions.is_cuda:
+        return reference.slot_mapping(positions, token_seq, block_tables, block_size)
+    T = positions.shape[0]
+    if out is None:
+        out = torch.empty(T, dtype=torch.int32, device=positions.device)
+    rc = _lib.kernels().fi_slot_mapping(_p(positions), _p(token_seq), _p(block_tables),
+                                        block_tables.shape[1], block_size, _p(out), T, _stream())
+    _lib.check(rc, "fi_slot_mapping")
+    return out
+
+
+def argmax(logits, out=None):
+    if not logits.is_cuda:
+        return reference.argmax(logits)
+    rows, V = logits.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int64, device=logits.device)
+    rc = _lib.kernels().fi_argmax(_p(logits), logits.stride(0), rows, V, _p(out),
+                                  _DT[logits.dtype], _stream())
+    _lib.check(rc, "fi_argmax")
+    return out
+
+
+def default_sm_scale(hd: int) -> float:
+    return 1.0 / math.sqrt(hd)

@@ -1,0 +1,200 @@
+"""CUDA kernels vs the PyTorch fp32 reference of the same op (small and odd shapes)."""
+import math
+
+import pytest
+import torch
+
+from litevllm_b200 import ops
+from litevllm_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _close(a, b, rtol, atol, what=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    bad = err > tol
+    assert not bool(bad.any()), (
+        f"{what}: {int(bad.sum())}/{bad.numel()} mismatches, max abs err {float(err.max()):.4g}, "
+        f"ref absmax {float(b.abs().max()):.4g}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T,N,K,splits", [
+    (1, 256, 128, 1), (16, 2560, 2048, 0), (32, 2048, 5632, 0), (32, 2048, 5632, 1),
+    (7, 384, 512, 0), (100, 384, 520, 2), (300, 1024, 1024, 0), (64, 128, 64, 1),
+    (129, 520, 1032, 0), (32, 32000, 2048, 0),
+])
+def test_dense_gemm(T, N, K, splits, dtype):
+    torch.manual_seed(0)
+    x = (torch.randn(T, K, device=DEV) * 0.5).to(dtype)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(dtype)
+    y = ops.linear(x, w, splits=splits)
+    _close(y, ref.linear(x, w, out_dtype=torch.float32), 2e-2, 2e-2, f"gemm {T}x{N}x{K}")
+    ops.check_status(x.device)
+
+
+def test_dense_gemm_epilogues():
+    torch.manual_seed(1)
+    T, N, K = 48, 1024, 768
+    x = (torch.randn(T, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
+    bias = torch.randn(N, device=DEV).bfloat16()
+    res = torch.randn(T, N, device=DEV).bfloat16()
+    y = ops.linear(x, w, bias=bias, residual=res)
+    _close(y, ref.linear(x, w, bias, res, out_dtype=torch.float32), 2e-2, 2e-2, "bias+residual")
+    y32 = ops.linear(x, w, out_dtype=torch.float32)
+    assert y32.dtype == torch.float32
+    _close(y32, ref.linear(x, w, out_dtype=torch.float32), 1e-3, 1e-3, "fp32 out")
+    # in-place residual accumulate (out aliases residual)
+    h = res.clone()
+    ops.linear(x, w, residual=h, out=h)
+    _close(h, ref.linear(x, w, None, res, out_dtype=torch.float32), 2e-2, 2e-2, "in-place residual")
+    # deterministic across runs (cluster split-K has a fixed summation order)
+    a = ops.linear(x, w, splits=4)
+    b = ops.linear(x, w, splits=4)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("T,I,K,act,splits", [(32, 5632, 2048, "silu", 0), (5, 256, 128, "gelu_tanh", 1),
+                                              (200, 640, 512, "silu", 0), (16, 1408, 1024, "gelu_tanh", 3)])
+def test_gated_gemm(T, I, K, act, splits):
+    torch.manual_seed(2)
+    x = (torch.randn(T, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(2 * I, K, device=DEV) * 0.05).bfloat16()
+    y = ops.gated_linear(x, w, act, splits=splits)
+    _close(y, ref.gated_linear(x, w, act, out_dtype=torch.float32), 3e-2, 2e-2, f"gated {T}x{I}x{K}")
+    ops.check_status(x.device)
+
+
+@pytest.mark.parametrize("rows,H", [(5, 2048), (33, 4096), (64, 128), (7, 256), (3, 2816)])
+@pytest.mark.parametrize("w_mode", [0, 1, 2])
+def test_rmsnorm(rows, H, w_mode):
+    torch.manual_seed(3)
+    x = torch.randn(rows, H, device=DEV).bfloat16()
+    w = (torch.randn(H, device=DEV) * 0.1 + 1).bfloat16()
+    y = ops.rmsnorm(x, w, 1e-5, w_mode=w_mode)
+    yr, _ = ref.rmsnorm(x, w, 1e-5, w_mode=w_mode)
+    _close(y, yr, 1e-2, 1e-2, "rmsnorm")
+    res = torch.randn(rows, H, device=DEV).bfloat16()
+    res2 = res.clone()
+    y = ops.rmsnorm(x, w, 1e-5, residual=res2, w_mode=w_mode)
+    yr, rr = ref.rmsnorm(x, w, 1e-5, residual=res, w_mode=w_mode)
+    _close(res2, rr, 1e-2, 1e-2, "residual out")
+    _close(y, yr, 2e-2, 2e-2, "fused add rmsnorm")
+
+
+def _make_cache(num_blocks, nkv, bs, hd, dtype, fp8):
+    shape = (num_blocks, nkv, bs, hd)
+    if fp8:
+        return (torch.zeros(shape, device=DEV, dtype=torch.float8_e4m3fn),
+                torch.zeros(shape, device=DEV, dtype=torch.float8_e4m3fn))
+    return torch.zeros(shape, device=DEV, dtype=dtype), torch.zeros(shape, device=DEV, dtype=dtype)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,rot,fp8,norm", [(32, 4, 64, 64, False, -1), (8, 2, 128, 64, True, 0),
+                                                    (4, 2, 256, 256, True, 1), (2, 1, 128, 128, False, -1)])
+def test_rope_cache(nh, nkv, hd, rot, fp8, norm):
+    torch.manual_seed(4)
+    T, bs, nb = 37, 16, 12
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV).bfloat16()
+    pos = torch.randint(0, 500, (T,), device=DEV, dtype=torch.int32)
+    cs = ref.build_cos_sin(rot, 512, 10000.0).to(DEV)
+    slots = torch.randperm((nb - 1) * bs, device=DEV)[:T].to(torch.int32) + bs
+    slots[3] = -1
+    qw = (torch.randn(hd, device=DEV) * 0.1 + 1).bfloat16() if norm >= 0 else None
+    kw = (torch.randn(hd, device=DEV) * 0.1 + 1).bfloat16() if norm >= 0 else None
+    kc, vc = _make_cache(nb, nkv, bs, hd, torch.bfloat16, fp8)
+    kcr, vcr = kc.clone(), vc.clone()
+    a, b = qkv.clone(), qkv.clone()
+    kw_args = dict(q_norm_w=qw, k_norm_w=kw, qk_norm_mode=norm, v_norm=(norm == 1), eps=1e-6,
+                   k_scale=0.5, v_scale=0.25)
+    ops.rope_and_cache(a, pos, cs, slots, kc, vc, nh, nkv, hd, rot, **kw_args)
+    ref.rope_and_cache(b, pos, cs, slots, kcr, vcr, nh, nkv, hd, rot, **kw_args)
+    _close(a, b, 2e-2, 2e-2, "rotated qkv")
+    _close(kc.float(), kcr.float(), 0.13 if fp8 else 2e-2, 2e-2, "k cache")
+    _close(vc.float(), vcr.float(), 0.13 if fp8 else 2e-2, 2e-2, "v cache")
+
+
+def _fill_paged(B, lens, nkv, hd, bs, fp8, dtype=torch.bfloat16):
+    max_blocks = (max(lens) + bs - 1) // bs + 1
+    nb = 1 + B * max_blocks
+    kc, vc = _make_cache(nb, nkv, bs, hd, dtype, fp8)
+    bt = torch.zeros(B, max_blocks, dtype=torch.int32, device=DEV)
+    perm = torch.randperm(nb - 1, device=DEV) + 1
+    used = 0
+    for b in range(B):
+        n = (lens[b] + bs - 1) // bs
+        bt[b, :n] = perm[used:used + n].to(torch.int32)
+        used += n
+    k = torch.randn(nb, nkv, bs, hd, device=DEV) * 0.7
+    v = torch.randn(nb, nkv, bs, hd, device=DEV) * 0.7
+    if fp8:
+        kc.copy_(ref.fp8_quant(k, 0.5)); vc.copy_(ref.fp8_quant(v, 0.5))
+    else:
+        kc.copy_(k.to(dtype)); vc.copy_(v.to(dtype))
+    return kc, vc, bt
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(32, 4, 64), (32, 8, 128), (16, 8, 256), (4, 4, 64), (40, 2, 128)])
+@pytest.mark.parametrize("fp8,window,softcap,splits", [(False, 0, 0.0, 1), (False, 0, 0.0, 0), (True, 100, 50.0, 3),
+                                                       (False, 64, 0.0, 2)])
+def test_paged_decode(nh, nkv, hd, fp8, window, softcap, splits):
+    torch.manual_seed(5)
+    lens = [1, 16, 17, 250, 129, 64]
+    B, bs = len(lens), 16
+    kc, vc, bt = _fill_paged(B, lens, nkv, hd, bs, fp8)
+    q = torch.randn(B, nh * hd, device=DEV).bfloat16()
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    ks = vs = 0.5 if fp8 else 1.0
+    y = ops.paged_attention_decode(q, kc, vc, bt, sl, nh, nkv, hd, scale, window, softcap, ks, vs,
+                                   splits=splits, max_kv_len=max(lens))
+    cu = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    yr = ref.paged_attention(q, kc, vc, bt, sl, cu, nh, nkv, hd, scale, window, softcap, ks, vs,
+                             out_dtype=torch.float32)
+    _close(y, yr, 2e-2, 2e-2, f"decode nh{nh} nkv{nkv} hd{hd}")
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 64), (8, 4, 128), (4, 2, 256)])
+@pytest.mark.parametrize("fp8,window,softcap", [(False, 0, 0.0), (True, 0, 30.0), (False, 48, 0.0)])
+def test_paged_prefill(nh, nkv, hd, fp8, window, softcap):
+    torch.manual_seed(6)
+    # (q_len, kv_len): fresh prompts, a chunk continuing a cached prefix, single-token rows
+    cases = [(70, 70), (1, 1), (130, 200), (16, 16), (33, 97), (1, 50)]
+    B, bs = len(cases), 16
+    lens = [c[1] for c in cases]
+    kc, vc, bt = _fill_paged(B, lens, nkv, hd, bs, fp8)
+    T = sum(c[0] for c in cases)
+    width = (nh + 2 * nkv) * hd
+    qkv = torch.randn(T, width, device=DEV).bfloat16()
+    cu = torch.tensor([0] + list(torch.tensor([c[0] for c in cases]).cumsum(0)), dtype=torch.int32, device=DEV)
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    ks = vs = 0.5 if fp8 else 1.0
+    y = ops.paged_attention_prefill(qkv, kc, vc, bt, sl, cu, max(c[0] for c in cases), nh, nkv, hd, scale,
+                                    window, softcap, ks, vs)
+    yr = ref.paged_attention(qkv, kc, vc, bt, sl, cu, nh, nkv, hd, scale, window, softcap, ks, vs,
+                             out_dtype=torch.float32)
+    _close(y, yr, 2e-2, 2e-2, f"prefill nh{nh} nkv{nkv} hd{hd}")
+
+
+def test_small_ops():
+    torch.manual_seed(7)
+    table = torch.randn(1000, 256, device=DEV).bfloat16()
+    ids = torch.randint(0, 1000, (77,), device=DEV)
+    _close(ops.embedding(ids, table, scale=16.0), ref.embedding(ids, table, scale=16.0), 1e-2, 1e-2, "embedding")
+    x = torch.randn(9, 2 * 704, device=DEV).bfloat16()
+    _close(ops.act_mul(x, "silu"), ref.act_mul(x, "silu"), 2e-2, 1e-2, "silu_mul")
+    _close(ops.act_mul(x, "gelu_tanh"), ref.act_mul(x, "gelu_tanh"), 2e-2, 1e-2, "gelu_mul")
+    logits = torch.randn(6, 32000, device=DEV)
+    logits[2, 100] = logits[2, 5000] = 99.0
+    assert torch.equal(ops.argmax(logits), ref.argmax(logits))
+    assert torch.equal(ops.argmax(logits.bfloat16()), ref.argmax(logits.bfloat16()))
+    bt = torch.randint(1, 50, (4, 8), device=DEV, dtype=torch.int32)
+    bt[1, 3] = 0
+    pos = torch.tensor([0, 5, 17, 50, 100, 127, 3], device=DEV, dtype=torch.int32)
+    seq = torch.tensor([0, 1, 2, 1, 3, 3, -1], device=DEV, dtype=torch.int32)
+    assert torch.equal(ops.slot_mapping(pos, seq, bt, 16), ref.slot_mapping(pos, seq, bt, 16))
