@@ -1,0 +1,264 @@
+"""Headline benchmark: decode tokens/s (aggregate over the batch) and p50 time-to-first-token for
+a TinyLlama-1.1B-shaped decoder in bf16, batch 32, prompt 1024 (+ up to 1024 generated tokens),
+random-init weights, uniform-random prompt token ids.
+
+One "step" = one decode step of the whole batch (32 new tokens).  After the prefill and W untimed
+warm-up steps, exactly K steps are timed twice:
+  * ``value``  : device-timed (CUDA events) replay of the engine's decode step with the sampled token
+                 fed back on the device (kernel-only view);
+  * ``e2e``    : the same K steps driven through the public engine API (``add_request`` + ``step``),
+                 where every step copies its inputs (token ids + batch metadata) from pinned host
+                 memory to the device and reads the sampled tokens back to the host.
+Multi-GPU (``--gpus N`` under torchrun): tensor parallel over N ranks, one process per GPU; times
+are the max over ranks.  ``--impl reference`` runs the unmodified reference project instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+BASELINE_TPS = 542.4   # reference README: TinyLlama-1.1B bf16, BS=32, 2048 ctx, aggregate tok/s (Radeon 8060S)
+METRIC = "decode tok/s aggregate + p50 TTFT at 1/2/4/8 B200, device-timed max over ranks"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="tinyllama-1.1b")
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--prompt-len", type=int, default=1024)
+    ap.add_argument("--comm-backend", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--profile-json", default=None, help="write per-phase timings here")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = Path(f"/tmp/fi_bench_clocks_{os.getpid()}.csv")
+
+    def start(self):
+        try:
+            self.fh = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=self.fh, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.fh.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.path.read_text().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            self.path.unlink()
+        except OSError:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def run_ours(args) -> dict:
+    import torch
+    import torch.distributed as dist
+
+    from litevllm_b200 import LLM, SamplingParams, ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torchrun for N>1")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    B, P, K, W = args.batch, args.prompt_len, args.steps, args.warmup
+    slack = (B + 7) // 8 + 2          # decode steps early finishers of the prefill run ahead
+    max_len = P + 1 + W + K + slack + 16
+    max_len = (max_len + 15) // 16 * 16
+
+    def make_llm(greedy_on_device: bool):
+        cfg = {"profile": "throughput",
+               "tuning_keyvals": {"FASTINFERENCE_GPU_GREEDY_SAMPLING": "1" if greedy_on_device else "0",
+                                  "FASTINFERENCE_KV_MAX_ACTIVE_REQUESTS": str(B),
+                                  "FASTINFERENCE_LITE_PREFILL_MICROBATCH": "8"}}
+        return LLM(f"synthetic:{args.model}", dtype="bfloat16", max_num_seqs=B, max_model_len=max_len,
+                   max_num_batched_tokens=max(8192, B * P), tensor_parallel_size=world,
+                   comm_backend=args.comm_backend, fastinference_config=cfg, device=f"cuda:{local_rank}")
+
+    llm = make_llm(False)
+    eng = llm.engine
+    vocab = eng.arch.vocab_size
+    g = torch.Generator().manual_seed(1234)
+    # prompts live in pinned host memory; the engine's batch builder copies them to the device
+    prompt_ids = torch.randint(0, vocab, (B, P), generator=g, dtype=torch.int64).pin_memory()
+    prompts = [row.tolist() for row in prompt_ids]
+    sp = SamplingParams(temperature=0.0, max_tokens=1 + W + K + slack, ignore_eos=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ------------------------------------------------------------------ warm the prefill path once
+    for i in range(min(B, 8)):
+        eng.add_request(f"warm-{i}", prompts[i], SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))
+    while eng.has_unfinished_requests():
+        eng.step()
+    barrier()
+
+    # ------------------------------------------------------------------ e2e: public API, H2D + D2H each step
+    t_submit = time.perf_counter()
+    for i in range(B):
+        eng.add_request(f"e2e-{i}", prompts[i], sp)
+    ttft = {}
+    n_first = 0
+    while n_first < B:
+        outs = eng.step()
+        now = time.perf_counter()
+        for o in outs:
+            if o is not None and o.request_id not in ttft:
+                ttft[o.request_id] = now - t_submit
+                n_first += 1
+    for _ in range(W):
+        eng.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = ops.launch_count()
+    replays0 = eng.decode_executor.graph_replays
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    n_tokens = 0
+    for _ in range(K):
+        outs = eng.step()
+        n_tokens += len(outs)
+    ev1.record()
+    barrier()
+    e2e_ms = max_over_ranks(ev0.elapsed_time(ev1))
+    clocks_e2e = sampler.stop()
+    eager_launches = ops.launch_count() - launches0
+    replays = eng.decode_executor.graph_replays - replays0
+    assert n_tokens == B * K, f"expected {B * K} tokens in the timed region, got {n_tokens}"
+    while eng.has_unfinished_requests():
+        eng.step()
+    ttft_p50_ms = max_over_ranks(statistics.median(ttft.values()) * 1e3)
+    bucket = eng.builder.bucket_for(B)
+    h2d_per_step = bucket * 8 + 4 * bucket * 4          # token ids (int64) + 4 x int32 metadata rows
+    d2h_per_step = B * 8                                 # sampled token ids (int64)
+
+    # ------------------------------------------------------------------ device-only: tokens fed back on device
+    # Same engine, same captured graph; the sampled token stays on the device between steps.
+    launches_cap0 = ops.launch_count()
+    eng2 = eng
+    eng2.backend.policy = type(eng2.backend.policy)(**{**eng2.backend.policy.__dict__, "gpu_greedy_sampling": True})
+    for i in range(B):
+        eng2.add_request(f"dev-{i}", prompts[i], sp)
+    n_first = 0
+    while any(eng2.scheduler.requests[f"dev-{i}"].is_prefill for i in range(B) if f"dev-{i}" in eng2.scheduler.requests):
+        eng2.step()
+    for _ in range(W):
+        eng2.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    replays1 = eng2.decode_executor.graph_replays
+    l1 = ops.launch_count()
+    ev0.record()
+    for _ in range(K):
+        eng2.step()
+    ev1.record()
+    barrier()
+    dev_ms = max_over_ranks(ev0.elapsed_time(ev1))
+    clocks = sampler.stop()
+    dev_replays = eng2.decode_executor.graph_replays - replays1
+    dev_eager = ops.launch_count() - l1
+    while eng2.has_unfinished_requests():
+        eng2.step()
+    ops.check_status(dev)
+    per_graph = getattr(eng2.decode_executor, "launches_per_graph", {}).get(bucket, 0)
+
+    value = B * K / (dev_ms / 1e3)
+    e2e_value = B * K / (e2e_ms / 1e3)
+    result = {
+        "metric": METRIC, "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": round(value / BASELINE_TPS, 2), "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": f"{args.model} (random init N(0,0.02))", "global_batch": B, "seq_len": P + 1 + W + K,
+                   "prompt_len": P, "parallelism": f"tp{world}", "comm_backend": args.comm_backend,
+                   "l2_policy": "inputs larger than L2 (2.2 GB weights + KV streamed every step)",
+                   "kv_cache": str(eng.kv_plan.dtype), "cuda_graph_decode": eng.decode_executor.use_cuda_graph},
+        "ttft_p50_ms": round(ttft_p50_ms, 2),
+        "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "ms_per_step": round(e2e_ms / K, 4),
+                "h2d_bytes_per_step": h2d_per_step, "d2h_bytes_per_step": d2h_per_step,
+                "api": "LiteEngine.add_request + LiteEngine.step (the loop inside LLM.generate)"},
+        "gpu_launches": int(dev_replays * per_graph + dev_eager),
+        "gpu_launches_detail": {"graph_replays": dev_replays, "kernels_per_graph": per_graph,
+                                "eager_native_launches": dev_eager},
+        "clocks": clocks, "clocks_e2e": clocks_e2e,
+    }
+    if args.profile_json and rank == 0:
+        Path(args.profile_json).write_text(json.dumps(result, indent=1))
+    llm.shutdown()
+    return result if rank == 0 else {}
+
+
+def run_reference(args) -> dict:
+    from baseline.run_reference import run_reference_bench
+    return run_reference_bench(args, METRIC, BASELINE_TPS)
+
+
+def main():
+    args = parse_args()
+    res = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if res:
+        print(json.dumps(res), flush=True)
+
+
+if __name__ == "__main__":
+    main()

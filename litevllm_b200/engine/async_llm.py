@@ -1,0 +1,110 @@
+"""Asynchronous engine front end used by the HTTP server.
+
+``submit`` validates and enqueues a request on a worker thread (admission errors surface before any
+streaming starts), ``stream`` yields outputs from the request's queue and aborts the request if the
+consumer leaves early, ``generate`` = submit + stream.  One ``RLock`` serialises engine access
+between submitters and the driver thread.  Reference: vllm/engine/async_llm.py:19-191."""
+from __future__ import annotations
+
+import asyncio
+from collections.abc import Iterable
+
+from ..loaders import get_tokenizer
+from .async_driver import AsyncDriver
+from .errors import EngineFatalError
+from .lite_engine import LiteEngine
+from .protocol import EngineClient
+
+
+class AsyncLLM(EngineClient):
+    def __init__(self, vllm_config, engine: LiteEngine | None = None, tokenizer=None, start_driver: bool = True):
+        self.vllm_config = vllm_config
+        self.engine = engine or LiteEngine(vllm_config)
+        self.engine_lock = self.engine.lock
+        mc = vllm_config.model_config
+        self.tokenizer = tokenizer or get_tokenizer(mc.tokenizer, mc.trust_remote_code, mc.revision,
+                                                    vocab_size=mc.arch.vocab_size)
+        self.engine.set_tokenizer(self.tokenizer)
+        self.driver = AsyncDriver(self.engine, self.engine_lock,
+                                  vllm_config.runtime_config.async_driver_min_step_interval_s)
+        self._start_driver = start_driver
+        self._closed = False
+
+    @classmethod
+    def from_vllm_config(cls, vllm_config, **kw) -> "AsyncLLM":
+        return cls(vllm_config, **kw)
+
+    def get_model_config(self):
+        return self.vllm_config.model_config
+
+    # ------------------------------------------------------------------ request path
+    def _submit_sync(self, request_id, prompt, sampling_params, lora_request, multi_modal_data, loop):
+        with self.engine_lock:
+            self.engine.add_request(request_id, prompt, sampling_params, lora_request=lora_request,
+                                    multi_modal_data=multi_modal_data, loop=loop)
+
+    async def submit(self, prompt, sampling_params, request_id: str, lora_request=None, multi_modal_data=None) -> None:
+        if self._closed:
+            raise EngineFatalError("engine is shut down")
+        loop = asyncio.get_running_loop()
+        await asyncio.to_thread(self._submit_sync, request_id, prompt, sampling_params, lora_request,
+                                multi_modal_data, loop)
+        if self._start_driver:
+            self.driver.notify_new_work()
+
+    async def stream(self, request_id: str):
+        finished = False
+        try:
+            async for out in self.engine.get_request_stream(request_id):
+                if getattr(out, "finished", False):
+                    finished = True
+                yield out
+        except BaseException:
+            finished = True   # the stream already delivered its terminal item (an exception)
+            raise
+        finally:
+            if not finished:
+                await self.abort(request_id)
+
+    async def generate(self, prompt, sampling_params, request_id: str, lora_request=None, multi_modal_data=None):
+        await self.submit(prompt, sampling_params, request_id, lora_request, multi_modal_data)
+        async for out in self.stream(request_id):
+            yield out
+
+    async def close_stream(self, request_id: str) -> None:
+        await self.abort(request_id)
+
+    async def abort(self, request_id: str | Iterable[str]) -> None:
+        ids = [request_id] if isinstance(request_id, str) else list(request_id)
+        def _do():
+            with self.engine_lock:
+                for rid in ids:
+                    self.engine.abort_request(rid)
+        await asyncio.to_thread(_do)
+
+    # ------------------------------------------------------------------ admin
+    def is_healthy(self) -> bool:
+        return not self._closed and self.engine.fatal_error is None
+
+    def stats(self) -> dict:
+        with self.engine_lock:
+            s = self.engine.stats()
+        s["async_driver"] = self.driver.stats()
+        return s
+
+    def reset_stats(self, clear_prefix_cache: bool = False) -> None:
+        with self.engine_lock:
+            self.engine.reset_stats(clear_prefix_cache)
+
+    def register_lora_adapter(self, lora_name: str, lora_path: str, lora_int_id: int | None = None):
+        with self.engine_lock:
+            return self.engine.register_lora_adapter(lora_name, lora_path, lora_int_id)
+
+    def unregister_lora_adapter(self, lora_name: str) -> bool:
+        with self.engine_lock:
+            return self.engine.unregister_lora_adapter(lora_name)
+
+    def shutdown(self) -> None:
+        self._closed = True
+        self.driver.shutdown()
+        self.engine.shutdown()

@@ -1,0 +1,179 @@
+"""Llama / Qwen2 / Qwen3 dense decoder (TinyLlama, the 9B AWQ config).
+
+Pre-norm blocks on a flattened varlen token stream ``[T, hidden]``:
+  RMSNorm -> merged QKV GEMM -> fused RoPE + KV-cache write -> paged attention ->
+  o_proj GEMM with the residual add in its epilogue -> RMSNorm -> gated gate|up GEMM
+  (SiLU*up in the epilogue) -> down GEMM (+residual).
+Only the last token of every sequence reaches the lm_head.
+Reference: vllm/model_executor/models/llama.py:30-319 (separate q/k/v and gate/up launches, paged
+decode kernel reused for prefill), vllm/model_executor/models/qwen2.py.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..layers.linear import LiteLinear
+from ..layers.rope import get_cos_sin
+from ..parallel import state as pstate
+from .arch import ModelArch
+
+
+class RMSNormWeight(nn.Module):
+    def __init__(self, dim: int, eps: float, dtype, plus_one: bool = False):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype), requires_grad=False)
+        self.eps = eps
+        self.w_mode = 1 if plus_one else 0
+
+    def forward(self, x, out=None):
+        return ops.rmsnorm(x, self.weight, self.eps, w_mode=self.w_mode, out=out)
+
+
+class LlamaAttention(nn.Module):
+    def __init__(self, arch: ModelArch, layer_idx: int, dtype, quant_config, prefix: str):
+        super().__init__()
+        tp = pstate.tp_size()
+        self.layer_idx = layer_idx
+        self.hd = arch.head_dim
+        self.total_heads, self.total_kv = arch.num_heads, arch.num_kv_heads
+        assert self.total_heads % tp == 0, "attention heads must divide the tensor-parallel size"
+        self.nh = self.total_heads // tp
+        self.kv_replicas = max(1, tp // self.total_kv)
+        self.nkv = max(1, self.total_kv // tp)
+        self.rot_dim = arch.rotary_dim or arch.head_dim
+        self.sm_scale = self.hd ** -0.5
+        self.window = arch.sliding_window if arch.layer_type(layer_idx) == "sliding" else 0
+        q_rows, kv_rows = self.total_heads * self.hd, self.total_kv * self.hd
+        # the merged weight is sharded by hand (KV heads may be replicated), so shard=None here
+        self.qkv_proj = LiteLinear(arch.hidden_size, (self.nh + 2 * self.nkv) * self.hd, bias=arch.attn_bias,
+                                   dtype=dtype, quant_config=quant_config, prefix=prefix + ".qkv_proj",
+                                   out_splits=[self.nh * self.hd, self.nkv * self.hd, self.nkv * self.hd])
+        self.o_proj = LiteLinear(q_rows, arch.hidden_size, bias=False, dtype=dtype, shard="row",
+                                 quant_config=quant_config, prefix=prefix + ".o_proj")
+        self.qk_norm = arch.qk_norm
+        if self.qk_norm:
+            self.q_norm = RMSNormWeight(self.hd, arch.rms_eps, dtype, arch.norm_plus_one)
+            self.k_norm = RMSNormWeight(self.hd, arch.rms_eps, dtype, arch.norm_plus_one)
+        self.eps = arch.rms_eps
+
+    def qkv_source_rows(self, which: str) -> tuple[int, int]:
+        """Row range of this rank inside the full q / k / v projection."""
+        r = pstate.tp_rank()
+        if which == "q":
+            return r * self.nh * self.hd, self.nh * self.hd
+        head0 = (r // self.kv_replicas) * self.nkv
+        return head0 * self.hd, self.nkv * self.hd
+
+    def forward(self, x, h, batch, kv, cos_sin):
+        qkv = self.qkv_proj(x, lora_mapping=batch.lora_mapping)
+        k_cache, v_cache = kv
+        cfg = batch.config
+        ops.rope_and_cache(qkv, batch.positions, cos_sin, batch.slot_mapping, k_cache, v_cache, self.nh,
+                           self.nkv, self.hd, self.rot_dim,
+                           q_norm_w=self.q_norm.weight if self.qk_norm else None,
+                           k_norm_w=self.k_norm.weight if self.qk_norm else None,
+                           qk_norm_mode=(self.q_norm.w_mode if self.qk_norm else -1), eps=self.eps,
+                           k_scale=cfg.k_scale, v_scale=cfg.v_scale)
+        if batch.is_decode:
+            attn = ops.paged_attention_decode(qkv, k_cache, v_cache, batch.block_tables, batch.seq_lens,
+                                              self.nh, self.nkv, self.hd, self.sm_scale, self.window, 0.0,
+                                              cfg.k_scale, cfg.v_scale, max_kv_len=batch.max_kv_len)
+        else:
+            attn = ops.paged_attention_prefill(qkv, k_cache, v_cache, batch.block_tables, batch.seq_lens,
+                                               batch.cu_q, batch.max_q_len, self.nh, self.nkv, self.hd,
+                                               self.sm_scale, self.window, 0.0, cfg.k_scale, cfg.v_scale)
+        return self.o_proj(attn, residual=h, out=h, lora_mapping=batch.lora_mapping)
+
+
+class LlamaMLP(nn.Module):
+    def __init__(self, arch: ModelArch, dtype, quant_config, prefix: str):
+        super().__init__()
+        inter = arch.intermediate_size
+        self.gate_up_proj = LiteLinear(arch.hidden_size, 2 * inter, dtype=dtype, shard="column",
+                                       quant_config=quant_config, prefix=prefix + ".gate_up_proj",
+                                       gated_act=arch.act, out_splits=[inter, inter])
+        self.down_proj = LiteLinear(inter, arch.hidden_size, dtype=dtype, shard="row",
+                                    quant_config=quant_config, prefix=prefix + ".down_proj")
+
+    def forward(self, x, h, batch):
+        a = self.gate_up_proj(x, lora_mapping=batch.lora_mapping)
+        return self.down_proj(a, residual=h, out=h, lora_mapping=batch.lora_mapping)
+
+
+class LlamaDecoderLayer(nn.Module):
+    def __init__(self, arch: ModelArch, layer_idx: int, dtype, quant_config):
+        super().__init__()
+        prefix = f"model.layers.{layer_idx}"
+        self.input_layernorm = RMSNormWeight(arch.hidden_size, arch.rms_eps, dtype, arch.norm_plus_one)
+        self.self_attn = LlamaAttention(arch, layer_idx, dtype, quant_config, prefix + ".self_attn")
+        self.post_attention_layernorm = RMSNormWeight(arch.hidden_size, arch.rms_eps, dtype, arch.norm_plus_one)
+        self.mlp = LlamaMLP(arch, dtype, quant_config, prefix + ".mlp")
+
+    def forward(self, h, batch, kv, cos_sin):
+        x = self.input_layernorm(h)
+        h = self.self_attn(x, h, batch, kv, cos_sin)
+        x = self.post_attention_layernorm(h)
+        return self.mlp(x, h, batch)
+
+
+class LlamaForCausalLM(nn.Module):
+    supports_lora = True
+    supports_multimodal = False
+
+    def __init__(self, vllm_config):
+        super().__init__()
+        mc = vllm_config.model_config
+        arch: ModelArch = mc.arch
+        self.arch, self.dtype = arch, mc.dtype
+        qc = vllm_config.quant_config
+        self.embed_tokens = nn.Parameter(torch.empty(arch.vocab_size, arch.hidden_size, dtype=mc.dtype),
+                                         requires_grad=False)
+        self.layers = nn.ModuleList([LlamaDecoderLayer(arch, i, mc.dtype, qc) for i in range(arch.num_layers)])
+        self.norm = RMSNormWeight(arch.hidden_size, arch.rms_eps, mc.dtype, arch.norm_plus_one)
+        self.tie = arch.tie_embeddings
+        if not self.tie:
+            self.lm_head = LiteLinear(arch.hidden_size, arch.vocab_size, dtype=mc.dtype, shard="column",
+                                      prefix="lm_head")
+        self.max_pos = max(mc.max_model_len, 16)
+        self._cos_sin = None
+
+    # ------------------------------------------------------------------ runtime
+    def cos_sin(self, device):
+        if self._cos_sin is None or self._cos_sin.device != device:
+            a = self.arch
+            self._cos_sin = get_cos_sin(a.rotary_dim or a.head_dim, self.max_pos, a.rope_theta,
+                                        a.rope_scaling, device)
+        return self._cos_sin
+
+    def kv_cache_specs(self):
+        """Per layer (n_kv_heads on this rank, head_dim)."""
+        return [(l.self_attn.nkv, l.self_attn.hd) for l in self.layers]
+
+    def embed(self, input_ids):
+        return ops.embedding(input_ids, self.embed_tokens, self.arch.embed_scale)
+
+    def forward(self, batch, kv_caches, inputs_embeds=None):
+        h = inputs_embeds if inputs_embeds is not None else self.embed(batch.input_ids)
+        cs = self.cos_sin(h.device)
+        for i, layer in enumerate(self.layers):
+            h = layer(h, batch, kv_caches[i], cs)
+        return self.compute_logits(h, batch)
+
+    def compute_logits(self, h, batch):
+        last = h if batch.logits_indices is None else h.index_select(0, batch.logits_indices)
+        x = self.norm(last)
+        if self.tie:
+            logits = ops.linear(x, self.embed_tokens, out_dtype=torch.float32)
+        else:
+            logits = self.lm_head(x, out_dtype=torch.float32)
+            if self.lm_head.tp > 1:
+                logits = pstate.all_gather_last_dim(logits)
+        return logits
+
+    # ------------------------------------------------------------------ loading
+    def load_weights(self, weights):
+        """weights: iterable of (hf_name, tensor).  Returns the set of consumed names."""
+        from ..loaders.weight_utils import load_llama_style
+        return load_llama_style(self, weights)

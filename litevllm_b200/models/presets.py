@@ -1,0 +1,66 @@
+"""HF-style config dicts for the architectures the benchmarks name.  ``synthetic:<name>`` as a model
+path builds one of these with random-init weights (no checkpoint files needed)."""
+from __future__ import annotations
+
+import copy
+
+PRESETS: dict[str, dict] = {
+    # TinyLlama-1.1B: 22 layers, hidden 2048, 32 q / 4 kv heads, head_dim 64, FFN 5632, vocab 32000
+    "tinyllama-1.1b": {
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": 2048,
+        "num_hidden_layers": 22, "num_attention_heads": 32, "num_key_value_heads": 4,
+        "intermediate_size": 5632, "vocab_size": 32000, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+        "max_position_embeddings": 4096, "hidden_act": "silu", "tie_word_embeddings": False,
+        "eos_token_id": 2, "bos_token_id": 1,
+    },
+    # 9B dense GQA decoder with zero-point AWQ int4 (group 128)
+    "dense-9b-awq": {
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": 4096,
+        "num_hidden_layers": 36, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+        "intermediate_size": 12288, "vocab_size": 151936, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+        "max_position_embeddings": 4096, "hidden_act": "silu", "tie_word_embeddings": False,
+        "eos_token_id": 151645,
+        "quantization_config": {"quant_method": "awq", "bits": 4, "group_size": 128, "zero_point": True},
+    },
+    # Gemma4-26B-A4B-shaped MoE
+    "gemma4-26b-a4b": {
+        "architectures": ["Gemma4ForConditionalGeneration"], "model_type": "gemma4",
+        "text_config": {
+            "model_type": "gemma4_text", "hidden_size": 2816, "num_hidden_layers": 30,
+            "num_attention_heads": 16, "num_key_value_heads": 8, "head_dim": 256,
+            "intermediate_size": 2112, "vocab_size": 262144, "rms_norm_eps": 1e-6,
+            "sliding_window": 1024, "sliding_window_pattern": 6, "attn_logit_softcapping": 50.0,
+            "final_logit_softcapping": 30.0, "rope_local_base_freq": 10000.0,
+            "rope_global_base_freq": 1000000.0, "max_position_embeddings": 4096,
+            "num_experts": 128, "top_k_experts": 8, "moe_intermediate_size": 704,
+            "hidden_activation": "gelu_pytorch_tanh", "tie_word_embeddings": True, "eos_token_id": 1,
+        },
+        "quantization_config": {"quant_method": "compressed-tensors", "format": "pack-quantized",
+                                "config_groups": {"group_0": {"weights": {"num_bits": 4, "group_size": 32,
+                                                                           "symmetric": True}}}},
+    },
+    # DeepSeek-V3-style MLA + MoE (GGUF-quantised in the named config)
+    "deepseek-mla-moe": {
+        "architectures": ["DeepseekV3ForCausalLM"], "model_type": "deepseek_v3", "hidden_size": 4096,
+        "num_hidden_layers": 43, "num_attention_heads": 64, "num_key_value_heads": 64,
+        "q_lora_rank": 1024, "kv_lora_rank": 512, "qk_rope_head_dim": 64, "qk_nope_head_dim": 128,
+        "v_head_dim": 128, "intermediate_size": 2048, "moe_intermediate_size": 2048,
+        "n_routed_experts": 256, "num_experts_per_tok": 6, "n_shared_experts": 1,
+        "scoring_func": "sigmoid", "norm_topk_prob": True, "routed_scaling_factor": 1.0,
+        "first_k_dense_replace": 0, "vocab_size": 129280, "rms_norm_eps": 1e-6, "rope_theta": 10000.0,
+        "max_position_embeddings": 4096, "eos_token_id": 1,
+        "quantization_config": {"quant_method": "gguf"},
+    },
+}
+
+# Small variants for tests (same code paths, seconds on a CPU).
+PRESETS["tiny-llama-test"] = dict(PRESETS["tinyllama-1.1b"], hidden_size=256, num_hidden_layers=2,
+                                  num_attention_heads=4, num_key_value_heads=2, intermediate_size=256,
+                                  vocab_size=512, max_position_embeddings=512)
+
+
+def get_preset(name: str) -> dict:
+    key = name.lower()
+    if key not in PRESETS:
+        raise KeyError(f"unknown synthetic preset {name!r}; known: {sorted(PRESETS)}")
+    return copy.deepcopy(PRESETS[key])

@@ -16,6 +16,18 @@ _ACT = {None: 0, "none": 0, "silu": 1, "gelu_tanh": 2, "gelu_pytorch_tanh": 2, "
 _DT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 
 _status_words: dict[int, torch.Tensor] = {}
+_launches = [0]
+
+
+def launch_count() -> int:
+    """Number of native kernel launches issued by this process through the op layer (launches
+    recorded while a CUDA graph is being captured count once; replays are counted by the caller)."""
+    return _launches[0]
+
+
+def _count(n: int = 1) -> None:
+    _launches[0] += n
+
 _scratch: dict[tuple, torch.Tensor] = {}
 
 
@@ -77,6 +89,7 @@ def linear(x, w, bias=None, residual=None, act=None, out=None, out_dtype=None, s
         out.stride(0), _ACT[act], 0, 1 if out.dtype == torch.float32 else 0, _DT[x.dtype], splits,
         bn, _p(status_word(x.device)), _stream())
     _lib.check(rc, "fi_dense_gemm")
+    _count()
     return out
 
 
@@ -99,6 +112,7 @@ def gated_linear(x, w_gate_up, act="silu", out=None, splits=0, bn=0):
         out.stride(0), _ACT[act], inter, 0, _DT[x.dtype], splits, bn,
         _p(status_word(x.device)), _stream())
     _lib.check(rc, "fi_dense_gemm(gated)")
+    _count()
     return out
 
 
@@ -122,6 +136,7 @@ def rmsnorm(x, w, eps, residual=None, w_mode=0, out=None, out_scale=1.0):
     rc = _lib.kernels().fi_rmsnorm(_p(x), _p(residual), _p(w), _p(out), rows, H, x.stride(0),
                                    out.stride(0), eps, w_mode, out_scale, _DT[x.dtype], _stream())
     _lib.check(rc, "fi_rmsnorm")
+    _count()
     return out
 
 
@@ -142,6 +157,7 @@ def rope_and_cache(qkv, positions, cos_sin, slot_mapping, k_cache, v_cache, nh, 
         1 if k_cache.dtype == torch.float8_e4m3fn else 0, k_scale, v_scale, eps, qk_norm_mode,
         1 if v_norm else 0, _DT[qkv.dtype], _stream())
     _lib.check(rc, "fi_rope_cache")
+    _count()
 
 
 def reshape_and_cache(k, v, slot_mapping, k_cache, v_cache, k_scale=1.0, v_scale=1.0):
@@ -154,6 +170,7 @@ def reshape_and_cache(k, v, slot_mapping, k_cache, v_cache, k_scale=1.0, v_scale
         hd, k_cache.shape[2], 1 if k_cache.dtype == torch.float8_e4m3fn else 0, k_scale, v_scale,
         _DT[k.dtype], _stream())
     _lib.check(rc, "fi_reshape_and_cache")
+    _count()
 
 
 # ---------------------------------------------------------------------------- attention
@@ -196,6 +213,7 @@ def paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, nh, nkv,
         sm_scale, float(softcap or 0.0), 1 if k_cache.dtype == torch.float8_e4m3fn else 0, k_scale,
         v_scale, splits, _DT[q.dtype], _stream())
     _lib.check(rc, "fi_paged_decode")
+    _count(2 if splits > 1 else 1)
     return out
 
 
@@ -219,6 +237,7 @@ def paged_attention_prefill(q, k_cache, v_cache, block_tables, seq_lens, cu_q, m
         int(window or 0), sm_scale, float(softcap or 0.0),
         1 if k_cache.dtype == torch.float8_e4m3fn else 0, k_scale, v_scale, _DT[q.dtype], _stream())
     _lib.check(rc, "fi_paged_prefill")
+    _count()
     return out
 
 
@@ -238,6 +257,7 @@ def embedding(ids, table, scale=1.0, vocab_start=0, vocab_end=None, out=None):
     rc = _lib.kernels().fi_embedding(_p(ids), _p(table), _p(out), T, H, scale, vocab_start,
                                      vocab_end, _DT[table.dtype], _stream())
     _lib.check(rc, "fi_embedding")
+    _count()
     return out
 
 
@@ -250,6 +270,7 @@ def act_mul(x, act="silu", out=None):
     rc = _lib.kernels().fi_act_mul(_p(x), _p(out), rows, d2 // 2, x.stride(0), _ACT[act],
                                    _DT[x.dtype], _stream())
     _lib.check(rc, "fi_act_mul")
+    _count()
     return out
 
 
@@ -262,6 +283,7 @@ def slot_mapping(positions, token_seq, block_tables, block_size, out=None):
     rc = _lib.kernels().fi_slot_mapping(_p(positions), _p(token_seq), _p(block_tables),
                                         block_tables.shape[1], block_size, _p(out), T, _stream())
     _lib.check(rc, "fi_slot_mapping")
+    _count()
     return out
 
 
@@ -274,6 +296,7 @@ def argmax(logits, out=None):
     rc = _lib.kernels().fi_argmax(_p(logits), logits.stride(0), rows, V, _p(out),
                                   _DT[logits.dtype], _stream())
     _lib.check(rc, "fi_argmax")
+    _count()
     return out
 
 
