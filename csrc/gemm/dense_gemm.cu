@@ -303,19 +303,64 @@ constexpr int smem_bytes() {
   return STAGES * (BM * 128 * (DUAL ? 2 : 1) + BN * 128) + (2 * STAGES + 1) * 8 + 16 + 1024;
 }
 
+// Split-K choice.  A cluster of S CTAs must be co-scheduled inside one GPC, so the number of
+// clusters that can run at once drops quickly with S (the runtime reports it); the pick minimises
+//   waves * (fixed cost + bytes per wave / achievable bandwidth)
+// where a lone CTA can pull roughly kPerCtaGBs and the whole chip kChipGBs.
 template <int BN, int STAGES, bool DUAL>
-int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
+int pick_splits(const GemmParams& p, int smem) {
+  constexpr float kPerCtaGBs = 110.f, kChipGBs = 6400.f, kFixedUs = 3.5f, kClusterUs = 1.0f;
+  static int max_active[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+  auto kern = dense_gemm_kernel<BN, STAGES, DUAL>;
+  const int tiles = ((p.N + BM - 1) / BM) * ((p.T + BN - 1) / BN);
+  const int kb_total = (p.K + BK - 1) / BK;
+  constexpr int ring = STAGES * (BM * 128 * (DUAL ? 2 : 1) + BN * 128);
+  const float tile_bytes = static_cast<float>(kb_total) * (BM * 128 * (DUAL ? 2 : 1) + BN * 128);
+  int best = 1;
+  float best_t = 1e30f;
+  for (int S = 1; S <= 8; ++S) {
+    if (S > 1 && kb_total / S < 2) break;
+    if (BN * BM * 4 * ((DUAL && S > 1) ? 2 : 1) > ring) break;
+    if (max_active[S] == 0) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(148, 1, S);
+      cfg.blockDim = dim3(kThreads);
+      cfg.dynamicSmemBytes = smem;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = S;
+      cfg.attrs = attr; cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = S == 1 ? 148 : (148 / S) * 3 / 4;
+      }
+      max_active[S] = n;
+    }
+    const int waves = (tiles + max_active[S] - 1) / max_active[S];
+    const int ctas_per_wave = (tiles < max_active[S] ? tiles : max_active[S]) * S;
+    const float gbs = fminf(kChipGBs, ctas_per_wave * kPerCtaGBs);
+    const float bytes_per_wave = tile_bytes * (tiles < max_active[S] ? tiles : max_active[S]);
+    const float t = waves * (kFixedUs + (S > 1 ? kClusterUs : 0.f) + bytes_per_wave / (gbs * 1e3f));
+    if (t < best_t) { best_t = t; best = S; }
+  }
+  return best;
+}
+
+template <int BN, int STAGES, bool DUAL>
+int launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams p, cudaStream_t stream) {
   auto kern = dense_gemm_kernel<BN, STAGES, DUAL>;
   constexpr int smem = smem_bytes<BN, STAGES, DUAL>();
   constexpr int ring = STAGES * (BM * 128 * (DUAL ? 2 : 1) + BN * 128);
   static_assert(BN * BM * 4 <= ring, "fp32 staging tile must fit inside the pipeline ring");
-  if (BN * BM * 4 * ((DUAL && p.splits > 1) ? 2 : 1) > ring) return -12;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
+  if (p.splits <= 0) p.splits = pick_splits<BN, STAGES, DUAL>(p, smem);
+  if (BN * BM * 4 * ((DUAL && p.splits > 1) ? 2 : 1) > ring) return -12;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((p.N + BM - 1) / BM, (p.T + BN - 1) / BN, p.splits);
   cfg.blockDim = dim3(kThreads);
@@ -375,16 +420,6 @@ extern "C" int fi_dense_gemm(const void* X, const void* W, void* C, const void* 
   r = make_tmap_2d_16bit_sw128(&tx, X, T, K, ldx, bn);
   if (r != 0) return r * 100 - 2;
   const int kb_total = (K + BK - 1) / BK;
-  if (splits <= 0) {
-    const int tiles = ((N + BM - 1) / BM) * ((T + bn - 1) / bn);
-    splits = 1;
-    if (tiles < 100) {
-      splits = 148 / tiles;
-      if (splits > 8) splits = 8;
-      while (splits > 1 && kb_total / splits < 2) --splits;
-      if (splits < 1) splits = 1;
-    }
-  }
   if (splits > 8) splits = 8;
   if (splits > kb_total) splits = kb_total;
   // The fp32 staging tile(s) alias the pipeline ring.  Gated mode with split-K parks two tiles
