@@ -17,6 +17,7 @@
 #include <cuda_runtime.h>
 #include <math_constants.h>
 #include <stdint.h>
+#include <stdio.h>
 
 namespace {
 
@@ -557,4 +558,64 @@ extern "C" int fi_paged_prefill(const void* q, long q_stride, const void* k_cach
     if (hd == 256) return launch_prefill<__half, 256, 32>(p, B, max_q_len, s);
   }
   return -11;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant of the split-KV decode entry point (declared in paged_attention_noalloc.h).
+//
+// fi_paged_decode takes its split-KV partial buffers from the caller.  Some callers have no way to
+// provide them: a C or C++ host that links this library without a tensor allocator, or a serving
+// process that committed its whole device-memory budget to the KV pool at start-up, where a later
+// cudaMalloc may fail, fragment the pool's neighbourhood or stall every stream while the driver
+// synchronises.  For them the partials live in the fixed device array below, which every GPU that
+// loads this library holds until the process exits.
+//
+// * Capacity: kNoAllocScratchFloats floats (8 MiB).  A call needs B * nh * splits * (hd + 2) floats;
+//   a larger request is refused with -20 and a message on stderr, nothing is launched.
+// * The first call on each device looks up the array's device address (cudaGetSymbolAddress with
+//   that device current) and caches it; make that first call before any stream capture begins.
+// * Every call reuses the same array and leaves its partials behind.  Nothing has to start at zero:
+//   each launch writes every partial it later reads (a split with no tokens writes m = -inf, l = 0).
+//   Two calls that overlap on the GPU (different streams, or another thread) race on the array.
+// * No cudaMalloc, cudaFree or other allocating call is made here.
+namespace {
+constexpr size_t kNoAllocScratchFloats = 2u * 1024u * 1024u;
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" int fi_paged_decode_noalloc(const void* q, long q_stride, const void* k_cache,
+                                       const void* v_cache, void* out, const int* block_tables,
+                                       const int* seq_lens, int B, int nh, int nkv, int hd,
+                                       int max_blocks, int block_size, int window, float sm_scale,
+                                       float softcap, int kv_fp8, float k_scale, float v_scale,
+                                       int splits, int dtype, void* stream) {
+  if (B <= 0) return 0;
+  if (splits < 1 || nh <= 0 || hd <= 0) return -10;
+  const size_t n_o = static_cast<size_t>(B) * nh * splits * hd;
+  const size_t n_ml = static_cast<size_t>(B) * nh * splits * 2;
+  if (n_o + n_ml > kNoAllocScratchFloats) {
+    fprintf(stderr,
+            "fi_paged_decode_noalloc: B*nh*splits*(hd+2) = %zu floats exceeds the built-in scratch "
+            "of %zu floats; lower splits or the batch, or use fi_paged_decode with caller buffers\n",
+            n_o + n_ml, kNoAllocScratchFloats);
+    return -20;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return -21;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // In host code the array's name is only a handle; the kernel needs its address on this device.
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) return e != cudaSuccess ? static_cast<int>(e) : -22;
+    g_noalloc_ptr[dev] = p;
+  }
+  float* ws_o = g_noalloc_ptr[dev];
+  float* ws_ml = ws_o + n_o;
+  return fi_paged_decode(q, q_stride, k_cache, v_cache, out, block_tables, seq_lens, ws_o, ws_ml, B,
+                         nh, nkv, hd, max_blocks, block_size, window, sm_scale, softcap, kv_fp8,
+                         k_scale, v_scale, splits, dtype, stream);
 }
