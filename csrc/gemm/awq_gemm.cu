@@ -1,0 +1,545 @@
+// Int4 weight-only GEMM for sm_100a:  C[T, N] = X[T, K] * dequant(Wq)[N, K]^T  with group-wise
+// scales and optional zero points (AWQ zero-point group-128 and compressed-tensors symmetric
+// group-32), plus the same epilogues as the dense kernel (bias, residual, fp32 out, gated act(g)*u).
+//
+// Structure = the dense tcgen05 kernel with one more pipeline stage.  TMA brings the *packed* int4
+// tile (128 rows x 32 bytes) and the token tile into a deep raw ring; the four epilogue warps spend
+// the main loop as dequantisers: each thread owns one weight row, expands its 64 nibbles to 16-bit
+// values with the magic-number trick ((q | 0x4300) is the bf16 128+q), applies (q - z) * s and
+// writes the row into a 128-byte-swizzled K-major A tile that `tcgen05.mma` consumes.  So the
+// weights cross HBM once at 4 bits and never exist in dense form in global memory.
+//
+// Runtime weight layout (produced once at load by litevllm_b200/ops/awq.py from the checkpoint's
+// qweight/scales/qzeros, which are read unchanged):
+//   qw      int32 [N, K/8]   nibble order inside a word re-arranged so that (w >> 4i) & 0x000F000F
+//                            yields columns (8c + 2i, 8c + 2i + 1) of the word's 8 columns
+//   scales  T     [K/G, N]   (transposed: coalesced per-row reads)
+//   zeros   uint8 [K/G, N]   or null for symmetric (zero point 8)
+//
+// Replaces the reference's Triton family vllm/kernels/triton/awq_fused_gemm.py (K10-K18: tiled
+// GEMM, split-K with atomics, M=1 GEMVs, fused QKV and fused gate-up variants) with one kernel.
+#include <cooperative_groups.h>
+
+#include "../common/ptx.cuh"
+#include "../common/tensormap.h"
+
+namespace cg = cooperative_groups;
+using namespace fi;
+
+namespace {
+
+constexpr int BM = 128;  // weight rows per CTA
+constexpr int BK = 64;   // 64 x 16-bit = one 128-byte swizzle row
+constexpr int kThreads = 192;
+
+enum Act : int { kActNone = 0, kActSilu = 1, kActGeluTanh = 2 };
+
+struct GemmParams {
+  void* C;
+  const void* bias;      // [N] or null (same 16-bit type as X)
+  const void* residual;  // [T, ldc] or null (same type as C when C is 16-bit)
+  int T, N, K;
+  int ldc;
+  int dual_rows;  // > 0: gated mode, W = [2 * dual_rows, K]; N == dual_rows
+  int act;
+  int out_fp32;
+  int is_fp16;
+  int splits;
+  int* status;
+  const void* scales;        // [K/G, N]
+  const uint8_t* zeros;      // [K/G, N] or null
+  int group;                 // 32, 64 or 128
+  int n_rows_total;          // rows of the scale/zero tables (N, or 2N in gated mode)
+};
+
+__device__ __forceinline__ float apply_act(float g, int act) {
+  if (act == kActSilu) return g / (1.f + __expf(-g));
+  if (act == kActGeluTanh) {
+    const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return g / (1.f + __expf(-2.f * inner));
+  }
+  return g;
+}
+
+__device__ __forceinline__ float ld16_as_float(const void* p, size_t i, int is_fp16) {
+  if (is_fp16) return __half2float(reinterpret_cast<const __half*>(p)[i]);
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+template <typename T> struct Pack;
+template <> struct Pack<__nv_bfloat16> {
+  using v2 = __nv_bfloat162;
+  static constexpr uint32_t kMagic2 = 0x43004300u;   // bf16 128.0 in both halves: (q | magic) = 128 + q
+  static constexpr float kMagicF = 128.f;
+  static __device__ __forceinline__ v2 dup(float f) { return __float2bfloat162_rn(f); }
+  static __device__ __forceinline__ uint32_t sub_mul(uint32_t v, v2 z, v2 s) {
+    v2 x = *reinterpret_cast<v2*>(&v);
+    x = __hmul2(__hsub2(x, z), s);
+    return *reinterpret_cast<uint32_t*>(&x);
+  }
+};
+template <> struct Pack<__half> {
+  using v2 = __half2;
+  static constexpr uint32_t kMagic2 = 0x64006400u;   // fp16 1024.0: (q | magic) = 1024 + q
+  static constexpr float kMagicF = 1024.f;
+  static __device__ __forceinline__ v2 dup(float f) { return __float2half2_rn(f); }
+  static __device__ __forceinline__ uint32_t sub_mul(uint32_t v, v2 z, v2 s) {
+    v2 x = *reinterpret_cast<v2*>(&v);
+    x = __hmul2(__hsub2(x, z), s);
+    return *reinterpret_cast<uint32_t*>(&x);
+  }
+};
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
+
+// RST raw stages (packed weights + tokens via TMA), AST dequantised A stages.
+template <typename T, int BN, int RST, int AST, bool DUAL>
+__global__ void __launch_bounds__(kThreads)
+awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+  constexpr int NA = DUAL ? 2 : 1;
+  constexpr int A_BYTES = BM * 128;           // dequantised tile
+  constexpr int Q_BYTES = BM * 32;            // packed tile: 128 rows x 8 int32
+  constexpr int B_BYTES = BN * 128;
+  constexpr int RAW_BYTES = Q_BYTES * NA + B_BYTES;
+  constexpr int TMEM_COLS_NEED = DUAL ? 2 * BN : BN;
+  constexpr uint32_t TMEM_COLS =
+      TMEM_COLS_NEED <= 32 ? 32 : TMEM_COLS_NEED <= 64 ? 64 : TMEM_COLS_NEED <= 128 ? 128
+                            : TMEM_COLS_NEED <= 256 ? 256 : 512;
+  constexpr int STAGES = RST;  // name used by the shared epilogue text
+  (void)STAGES;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* a_ring = smem;                                   // AST * NA * A_BYTES
+  uint8_t* raw_ring = smem + AST * NA * A_BYTES;            // RST * RAW_BYTES (B tiles 1024-aligned)
+  uint64_t* raw_full = reinterpret_cast<uint64_t*>(raw_ring + RST * RAW_BYTES);
+  uint64_t* raw_empty = raw_full + RST;
+  uint64_t* a_full = raw_empty + RST;
+  uint64_t* a_empty = a_full + AST;
+  uint64_t* accum_bar = a_empty + AST;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  volatile int* aborted = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* stage_f32 = reinterpret_cast<float*>(smem);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BM;
+  const int t0 = blockIdx.y * BN;
+  const int S = p.splits;
+  const int rank = (S > 1) ? static_cast<int>(blockIdx.z) : 0;
+  const int kb_total = (p.K + BK - 1) / BK;
+  const int kb_begin = static_cast<int>((static_cast<long long>(kb_total) * rank) / S);
+  const int kb_end = static_cast<int>((static_cast<long long>(kb_total) * (rank + 1)) / S);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < RST; ++s) {
+      mbar_init(&raw_full[s], 1);
+      mbar_init(&raw_empty[s], 1 + 4);   // MMA commit (token tile) + one arrival per dequant warp
+    }
+    for (int s = 0; s < AST; ++s) {
+      mbar_init(&a_full[s], 4);          // one arrival per dequant warp
+      mbar_init(&a_empty[s], 1);
+    }
+    mbar_init(accum_bar, 1);
+    *aborted = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      tma_prefetch_desc(&tmap_w);
+      tma_prefetch_desc(&tmap_x);
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        const int it = kb - kb_begin;
+        const int s = it % RST;
+        const uint32_t ph = (it / RST) & 1;
+        if (!mbar_wait(&raw_empty[s], ph ^ 1)) {
+          set_status(p.status, kStatusTimeoutEmpty);
+          *aborted = 1;
+          break;
+        }
+        uint8_t* r = raw_ring + s * RAW_BYTES;
+        mbar_expect_tx(&raw_full[s], RAW_BYTES);
+        // token tile first (keeps it 1024-byte aligned), packed weight tile(s) behind it
+        tma_load_2d(r, &tmap_x, &raw_full[s], kb * BK, t0);
+        tma_load_2d(r + B_BYTES, &tmap_w, &raw_full[s], kb * 8, n0);
+        if (DUAL) tma_load_2d(r + B_BYTES + Q_BYTES, &tmap_w, &raw_full[s], kb * 8, p.dual_rows + n0);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = umma_idesc_f16(p.is_fp16 ? 0 : 1, BM, BN);
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        const int it = kb - kb_begin;
+        const int s = it % RST, j = it % AST;
+        if (!mbar_wait(&raw_full[s], (it / RST) & 1) || !mbar_wait(&a_full[j], (it / AST) & 1)) {
+          set_status(p.status, kStatusTimeoutFull);
+          *aborted = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(a_ring + j * NA * A_BYTES);
+        const uint32_t b_addr = smem_u32(raw_ring + s * RAW_BYTES);
+        const uint64_t da = umma_desc_sw128_kmajor(a_addr);
+        const uint64_t db = umma_desc_sw128_kmajor(b_addr);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k) {
+          const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+          umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, acc);
+          if (DUAL) {
+            const uint64_t da2 = umma_desc_sw128_kmajor(a_addr + A_BYTES);
+            umma_f16(tmem_base + BN, da2 + 2 * k, db + 2 * k, idesc, acc);
+          }
+        }
+        umma_commit(&raw_empty[s]);
+        umma_commit(&a_empty[j]);
+      }
+      umma_commit(accum_bar);
+    }
+  } else {
+    // ------------------------------------------------------------ dequantisers (warps 2..5)
+    // thread -> weight row; per k-block: 8 packed words -> 64 values -> one swizzled 128-byte row
+    const int row = (warp - 2) * 32 + lane;
+    const T* scales = reinterpret_cast<const T*>(p.scales);
+    // scale / zero-point of this thread's row(s) for the two 32-value halves of a k-block,
+    // fetched one k-block ahead so the L2 latency hides behind the dequant arithmetic
+    float sf[NA][2], zf[NA][2], sf_n[NA][2], zf_n[NA][2];
+    auto fetch = [&](int kb, float (&so)[NA][2], float (&zo)[NA][2]) {
+#pragma unroll
+      for (int a = 0; a < NA; ++a) {
+        const int grow = (a == 0 ? n0 : p.dual_rows + n0) + row;
+#pragma unroll
+        for (int gi = 0; gi < 2; ++gi) {
+          so[a][gi] = 0.f;
+          zo[a][gi] = 8.f;
+          if (grow < p.n_rows_total && kb < kb_end) {
+            const size_t idx = static_cast<size_t>((kb * BK + gi * 32) / p.group) * p.n_rows_total + grow;
+            so[a][gi] = to_float(scales[idx]);
+            if (p.zeros != nullptr) zo[a][gi] = static_cast<float>(p.zeros[idx]);
+          }
+        }
+      }
+    };
+    fetch(kb_begin, sf_n, zf_n);
+    bool ok = true;
+    for (int kb = kb_begin; kb < kb_end && ok; ++kb) {
+      const int it = kb - kb_begin;
+      const int s = it % RST, j = it % AST;
+#pragma unroll
+      for (int a = 0; a < NA; ++a) {
+        sf[a][0] = sf_n[a][0]; sf[a][1] = sf_n[a][1]; zf[a][0] = zf_n[a][0]; zf[a][1] = zf_n[a][1];
+      }
+      fetch(kb + 1, sf_n, zf_n);
+      if (!mbar_wait(&raw_full[s], (it / RST) & 1) || !mbar_wait(&a_empty[j], ((it / AST) & 1) ^ 1)) {
+        set_status(p.status, kStatusTimeoutFull);
+        *aborted = 1;
+        ok = false;
+        break;
+      }
+#pragma unroll
+      for (int a = 0; a < NA; ++a) {
+        const uint4* q = reinterpret_cast<const uint4*>(raw_ring + s * RAW_BYTES + B_BYTES + a * Q_BYTES + row * 32);
+        const uint4 w0 = q[0], w1 = q[1];
+        const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        uint8_t* dst = a_ring + (j * NA + a) * A_BYTES;
+#pragma unroll
+        for (int gi = 0; gi < 2; ++gi) {
+          const typename Pack<T>::v2 s2 = Pack<T>::dup(sf[a][gi]);
+          const typename Pack<T>::v2 z2 = Pack<T>::dup(Pack<T>::kMagicF + zf[a][gi]);
+#pragma unroll
+          for (int c = gi * 4; c < gi * 4 + 4; ++c) {
+            uint32_t o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t v = ((words[c] >> (4 * i)) & 0x000F000Fu) | Pack<T>::kMagic2;
+              o[i] = Pack<T>::sub_mul(v, z2, s2);
+            }
+            *reinterpret_cast<uint4*>(dst + sw128_offset(row, c)) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+      }
+      fence_proxy_async_smem();   // generic-proxy smem writes -> visible to the tensor-core proxy
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&a_full[j]);
+        mbar_arrive(&raw_empty[s]);
+      }
+    }
+  }
+  // ---------------------------------------------------------------- epilogue part 1 (warps 2..5)
+  // Wait for the accumulator, then park it as fp32 in shared memory laid out [token][weight row].
+  if (warp >= 2) {
+    bool ok = mbar_wait(accum_bar, 0);
+    if (!ok) {
+      set_status(p.status, kStatusTimeoutAccum);
+      *aborted = 1;
+    }
+    tc_fence_after();
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int n_local = q * 32 + lane;
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    if (ok) {
+      const bool fuse_act_now = DUAL && (S == 1);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld_x16(taddr + c0, r);
+        if (DUAL) {
+          uint32_t u[16];
+          tmem_ld_x16(taddr + BN + c0, u);
+          tmem_ld_wait();
+          if (fuse_act_now) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              stage_f32[(c0 + j) * BM + n_local] =
+                  apply_act(__uint_as_float(r[j]), p.act) * __uint_as_float(u[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              stage_f32[(c0 + j) * BM + n_local] = __uint_as_float(r[j]);
+              stage_f32[BN * BM + (c0 + j) * BM + n_local] = __uint_as_float(u[j]);
+            }
+          }
+        } else {
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) stage_f32[(c0 + j) * BM + n_local] = __uint_as_float(r[j]);
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  cg::cluster_group cluster = cg::this_cluster();
+  if (S > 1) cluster.sync();
+
+  // ---------------------------------------------------------------- epilogue part 2 (all threads)
+  // Rows (tokens) rank, rank+S, ... of the tile belong to this CTA: sum the S partial tiles through
+  // distributed shared memory, apply the epilogue and store 8 outputs per thread.
+  if (!*aborted) {
+    const int rows_mine = (BN - rank + S - 1) / S;
+    for (int idx = threadIdx.x; idx < rows_mine * (BM / 8); idx += kThreads) {
+      const int tl = rank + (idx / (BM / 8)) * S;
+      const int nl = (idx % (BM / 8)) * 8;
+      const int t = t0 + tl;
+      const int n = n0 + nl;
+      if (t >= p.T || n >= p.N) continue;
+      float g[8], u[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { g[j] = 0.f; u[j] = 0.f; }
+      for (int pr = 0; pr < S; ++pr) {
+        const float* src = (S > 1) ? cluster.map_shared_rank(stage_f32, pr) : stage_f32;
+        const float4 a = *reinterpret_cast<const float4*>(src + tl * BM + nl);
+        const float4 b = *reinterpret_cast<const float4*>(src + tl * BM + nl + 4);
+        g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
+        g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+        if (DUAL && S > 1) {
+          const float4 c = *reinterpret_cast<const float4*>(src + BN * BM + tl * BM + nl);
+          const float4 d = *reinterpret_cast<const float4*>(src + BN * BM + tl * BM + nl + 4);
+          u[0] += c.x; u[1] += c.y; u[2] += c.z; u[3] += c.w;
+          u[4] += d.x; u[5] += d.y; u[6] += d.z; u[7] += d.w;
+        }
+      }
+      if (DUAL && S > 1) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] = apply_act(g[j], p.act) * u[j];
+      } else if (!DUAL && p.act != kActNone) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] = apply_act(g[j], p.act);
+      }
+      const int nvalid = min(8, p.N - n);
+      if (p.bias != nullptr) {
+        for (int j = 0; j < nvalid; ++j) g[j] += ld16_as_float(p.bias, n + j, p.is_fp16);
+      }
+      const size_t off = static_cast<size_t>(t) * p.ldc + n;
+      if (p.out_fp32) {
+        float* C = reinterpret_cast<float*>(p.C);
+        if (p.residual != nullptr)
+          for (int j = 0; j < nvalid; ++j) g[j] += reinterpret_cast<const float*>(p.residual)[off + j];
+        if (nvalid == 8) {
+          *reinterpret_cast<float4*>(C + off) = make_float4(g[0], g[1], g[2], g[3]);
+          *reinterpret_cast<float4*>(C + off + 4) = make_float4(g[4], g[5], g[6], g[7]);
+        } else {
+          for (int j = 0; j < nvalid; ++j) C[off + j] = g[j];
+        }
+      } else {
+        if (p.residual != nullptr)
+          for (int j = 0; j < nvalid; ++j) g[j] += ld16_as_float(p.residual, off + j, p.is_fp16);
+        uint32_t packed[4];
+        if (p.is_fp16) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            __half2 h = __floats2half2_rn(g[2 * j], g[2 * j + 1]);
+            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(g[2 * j], g[2 * j + 1]);
+            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        }
+        uint16_t* C = reinterpret_cast<uint16_t*>(p.C);
+        if (nvalid == 8) {
+          *reinterpret_cast<uint4*>(C + off) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        } else {
+          const uint16_t* ph = reinterpret_cast<const uint16_t*>(packed);
+          for (int j = 0; j < nvalid; ++j) C[off + j] = ph[j];
+        }
+      }
+    }
+  }
+  if (S > 1) cluster.sync();  // nobody leaves while a peer may still read its staging tile
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN, int RST, int AST, bool DUAL>
+constexpr int ring_bytes() {
+  return AST * (DUAL ? 2 : 1) * BM * 128 + RST * (BM * 32 * (DUAL ? 2 : 1) + BN * 128);
+}
+template <int BN, int RST, int AST, bool DUAL>
+constexpr int smem_bytes() {
+  return ring_bytes<BN, RST, AST, DUAL>() + (2 * RST + 2 * AST + 1) * 8 + 16 + 1024;
+}
+
+template <typename T, int BN, int RST, int AST, bool DUAL>
+int launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams p, cudaStream_t stream) {
+  auto kern = awq_gemm_kernel<T, BN, RST, AST, DUAL>;
+  constexpr int smem = smem_bytes<BN, RST, AST, DUAL>();
+  constexpr int ring = ring_bytes<BN, RST, AST, DUAL>();
+  static_assert(BN * BM * 4 <= ring, "fp32 staging tile must fit inside the rings");
+  static bool configured = false;
+  static int max_active[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  const int tiles = ((p.N + BM - 1) / BM) * ((p.T + BN - 1) / BN);
+  const int kb_total = (p.K + BK - 1) / BK;
+  if (p.splits <= 0) {
+    // same cost model as the dense kernel, with 4-bit weight bytes
+    const float tile_bytes = static_cast<float>(kb_total) * (BM * 32 * (DUAL ? 2 : 1) + BN * 128);
+    int best = 1;
+    float best_t = 1e30f;
+    for (int S = 1; S <= 8; ++S) {
+      if (S > 1 && kb_total / S < 2) break;
+      if (BN * BM * 4 * ((DUAL && S > 1) ? 2 : 1) > ring) break;
+      if (max_active[S] == 0) {
+        cudaLaunchConfig_t c = {};
+        c.gridDim = dim3(148, 1, S); c.blockDim = dim3(kThreads); c.dynamicSmemBytes = smem;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 1; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = S;
+        c.attrs = at; c.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &c) != cudaSuccess || n <= 0) {
+          cudaGetLastError();
+          n = S == 1 ? 148 : (148 / S) * 3 / 4;
+        }
+        max_active[S] = n;
+      }
+      const int act = tiles < max_active[S] ? tiles : max_active[S];
+      const int waves = (tiles + max_active[S] - 1) / max_active[S];
+      const float gbs = fminf(6400.f, act * S * 60.f);
+      const float t = waves * (3.5f + (S > 1 ? 1.f : 0.f) + tile_bytes * act / (gbs * 1e3f));
+      if (t < best_t) { best_t = t; best = S; }
+    }
+    p.splits = best;
+  }
+  if (BN * BM * 4 * ((DUAL && p.splits > 1) ? 2 : 1) > ring) return -12;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((p.N + BM - 1) / BM, (p.T + BN - 1) / BN, p.splits);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = p.splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, tw, tx, p));
+}
+
+template <typename T, bool DUAL>
+int dispatch(int bn, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t s) {
+  switch (bn) {
+    case 16: return launch<T, 16, 10, 3, DUAL>(tw, tx, p, s);
+    case 32: return launch<T, 32, 8, 3, DUAL>(tw, tx, p, s);
+    case 64: return launch<T, 64, 6, 3, DUAL>(tw, tx, p, s);
+    default: return launch<T, 128, 3, DUAL ? 2 : 3, DUAL>(tw, tx, p, s);
+  }
+}
+
+// Packed weights as a 2-D int32 tensor [rows, K/8]; box = 8 words x 128 rows, no swizzle.
+inline int make_tmap_packed(CUtensorMap* out, const void* base, uint64_t rows, uint64_t k_words) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (enc == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || ((k_words * 4) & 15) != 0) return -2;
+  cuuint64_t dims[2] = {k_words, rows};
+  cuuint64_t strides[1] = {k_words * 4};
+  cuuint32_t box[2] = {8, 128};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<void*>(base), dims, strides, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+}  // namespace
+
+// C = X dequant(Wq)^T with optional epilogue.  qw/scales/zeros in the runtime layout described at
+// the top of this file.  dtype: 0 bf16, 1 fp16 (X, scales, bias, C unless out_fp32).
+// dual_rows > 0: gated mode, the weight holds [gate rows; up rows] and N == dual_rows.
+extern "C" int fi_awq_gemm(const void* X, const void* qw, const void* scales, const void* zeros, void* C,
+                           const void* bias, const void* residual, int T, int N, int K, int group,
+                           int ldx, int ldc, int act, int dual_rows, int out_fp32, int dtype,
+                           int splits, int bn, int* status, void* stream) {
+  if (T <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K % 64) != 0 || (ldc % 8) != 0 || (reinterpret_cast<uintptr_t>(C) & 15) != 0) return -10;
+  if (group != 32 && group != 64 && group != 128 && !(group > 128 && group % 64 == 0)) return -13;
+  if (dual_rows > 0 && N != dual_rows) return -11;
+  if (bn == 0) bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128;
+  const int w_rows = dual_rows > 0 ? 2 * dual_rows : N;
+  CUtensorMap tw, tx;
+  int r = make_tmap_packed(&tw, qw, w_rows, K / 8);
+  if (r != 0) return r * 100 - 1;
+  r = make_tmap_2d_16bit_sw128(&tx, X, T, K, ldx, bn);
+  if (r != 0) return r * 100 - 2;
+  const int kb_total = K / BK;
+  if (splits > 8) splits = 8;
+  if (splits > kb_total) splits = kb_total;
+  if (bn >= 128 && dual_rows > 0) splits = 1;
+  GemmParams p;
+  p.C = C; p.bias = bias; p.residual = residual;
+  p.T = T; p.N = N; p.K = K; p.ldc = ldc;
+  p.dual_rows = dual_rows; p.act = act; p.out_fp32 = out_fp32; p.is_fp16 = dtype == 1;
+  p.splits = splits; p.status = status;
+  p.scales = scales; p.zeros = reinterpret_cast<const uint8_t*>(zeros); p.group = group;
+  p.n_rows_total = w_rows;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == 1) {
+    if (dual_rows > 0) return dispatch<__half, true>(bn, tw, tx, p, s);
+    return dispatch<__half, false>(bn, tw, tx, p, s);
+  }
+  if (dual_rows > 0) return dispatch<__nv_bfloat16, true>(bn, tw, tx, p, s);
+  return dispatch<__nv_bfloat16, false>(bn, tw, tx, p, s);
+}

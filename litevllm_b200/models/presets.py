@@ -57,6 +57,11 @@ PRESETS: dict[str, dict] = {
 PRESETS["tiny-llama-test"] = dict(PRESETS["tinyllama-1.1b"], hidden_size=256, num_hidden_layers=2,
                                   num_attention_heads=4, num_key_value_heads=2, intermediate_size=256,
                                   vocab_size=512, max_position_embeddings=512)
+PRESETS["tiny-llama-awq-test"] = dict(PRESETS["tiny-llama-test"], quantization_config={
+    "quant_method": "awq", "bits": 4, "group_size": 128, "zero_point": True})
+PRESETS["tiny-llama-ct-test"] = dict(PRESETS["tiny-llama-test"], quantization_config={
+    "quant_method": "compressed-tensors", "format": "pack-quantized",
+    "config_groups": {"group_0": {"weights": {"num_bits": 4, "group_size": 32, "symmetric": True}}}})
 
 
 def get_preset(name: str) -> dict:

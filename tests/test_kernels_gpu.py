@@ -198,3 +198,41 @@ def test_small_ops():
     pos = torch.tensor([0, 5, 17, 50, 100, 127, 3], device=DEV, dtype=torch.int32)
     seq = torch.tensor([0, 1, 2, 1, 3, 3, -1], device=DEV, dtype=torch.int32)
     assert torch.equal(ops.slot_mapping(pos, seq, bt, 16), ref.slot_mapping(pos, seq, bt, 16))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T,N,K,G,zp,splits", [(16, 512, 512, 128, True, 1), (1, 256, 256, 32, False, 0),
+                                               (33, 1280, 1024, 128, True, 0), (200, 384, 512, 32, False, 0),
+                                               (16, 6144, 4096, 128, True, 0), (7, 200, 320, 64, True, 2)])
+def test_int4_gemm(T, N, K, G, zp, splits, dtype):
+    from litevllm_b200.ops import awq
+    torch.manual_seed(8)
+    nib = torch.randint(0, 16, (N, K), device=DEV, dtype=torch.uint8)
+    scales = (torch.randn(N, K // G, device=DEV).abs() * 0.01 + 1e-3).to(dtype)
+    zeros = torch.randint(0, 16, (N, K // G), device=DEV, dtype=torch.uint8) if zp else None
+    w = awq.Int4Weight(nib, scales, zeros, G, dtype, keep_reference=True)
+    x = (torch.randn(T, K, device=DEV) * 0.5).to(dtype)
+    y = awq.int4_linear(x, w, splits=splits)
+    dense = awq.dequantize(nib, scales, zeros, G)
+    _close(y, ref.linear(x, dense, out_dtype=torch.float32), 3e-2, 3e-2, f"int4 gemm {T}x{N}x{K} g{G}")
+    ops.check_status(x.device)
+
+
+def test_int4_gated_and_layout_roundtrip():
+    from litevllm_b200.ops import awq
+    torch.manual_seed(9)
+    T, I, K, G = 24, 640, 512, 32
+    nib = torch.randint(0, 16, (2 * I, K), device=DEV, dtype=torch.uint8)
+    scales = (torch.randn(2 * I, K // G, device=DEV).abs() * 0.01 + 1e-3).bfloat16()
+    w = awq.Int4Weight(nib, scales, None, G, torch.bfloat16, keep_reference=True)
+    x = (torch.randn(T, K, device=DEV) * 0.5).bfloat16()
+    y = awq.int4_linear(x, w, gated_act="gelu_tanh")
+    dense = awq.dequantize(nib, scales, None, G)
+    _close(y, ref.gated_linear(x, dense, "gelu_tanh", out_dtype=torch.float32), 4e-2, 3e-2, "int4 gated")
+    # packing helpers are inverses; AutoAWQ layout converts to the same nibbles
+    assert torch.equal(awq.unpack_nibbles(awq.pack_nibbles(nib)), nib)
+    order = [0, 2, 4, 6, 1, 3, 5, 7]
+    kn = nib.t().contiguous()                                   # [K, N]
+    inter = kn.reshape(K, 2 * I // 8, 8)[:, :, order].reshape(K, 2 * I)
+    back, s2, _ = awq.autoawq_to_rowmajor(awq.pack_nibbles(inter), scales.t().contiguous(), None)
+    assert torch.equal(back, nib) and torch.equal(s2, scales)
