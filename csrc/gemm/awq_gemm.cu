@@ -18,53 +18,14 @@
 //
 // Replaces the reference's Triton family vllm/kernels/triton/awq_fused_gemm.py (K10-K18: tiled
 // GEMM, split-K with atomics, M=1 GEMVs, fused QKV and fused gate-up variants) with one kernel.
-#include <cooperative_groups.h>
-
-#include "../common/ptx.cuh"
 #include "../common/tensormap.h"
+#include "comm_desc.h"
+#include "epilogue.cuh"
 
-namespace cg = cooperative_groups;
 using namespace fi;
 
 namespace {
 
-constexpr int BM = 128;  // weight rows per CTA
-constexpr int BK = 64;   // 64 x 16-bit = one 128-byte swizzle row
-constexpr int kThreads = 192;
-
-enum Act : int { kActNone = 0, kActSilu = 1, kActGeluTanh = 2 };
-
-struct GemmParams {
-  void* C;
-  const void* bias;      // [N] or null (same 16-bit type as X)
-  const void* residual;  // [T, ldc] or null (same type as C when C is 16-bit)
-  int T, N, K;
-  int ldc;
-  int dual_rows;  // > 0: gated mode, W = [2 * dual_rows, K]; N == dual_rows
-  int act;
-  int out_fp32;
-  int is_fp16;
-  int splits;
-  int* status;
-  const void* scales;        // [K/G, N]
-  const uint8_t* zeros;      // [K/G, N] or null
-  int group;                 // 32, 64 or 128
-  int n_rows_total;          // rows of the scale/zero tables (N, or 2N in gated mode)
-};
-
-__device__ __forceinline__ float apply_act(float g, int act) {
-  if (act == kActSilu) return g / (1.f + __expf(-g));
-  if (act == kActGeluTanh) {
-    const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
-    return g / (1.f + __expf(-2.f * inner));
-  }
-  return g;
-}
-
-__device__ __forceinline__ float ld16_as_float(const void* p, size_t i, int is_fp16) {
-  if (is_fp16) return __half2float(reinterpret_cast<const __half*>(p)[i]);
-  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
-}
 
 template <typename T> struct Pack;
 template <> struct Pack<__nv_bfloat16> {
@@ -96,7 +57,7 @@ __device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
 template <typename T, int BN, int RST, int AST, bool DUAL>
 __global__ void __launch_bounds__(kThreads)
 awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
-                const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+                const __grid_constant__ TokenMaps tmaps_x, const GemmParams p) {
   constexpr int NA = DUAL ? 2 : 1;
   constexpr int A_BYTES = BM * 128;           // dequantised tile
   constexpr int Q_BYTES = BM * 32;            // packed tile: 128 rows x 8 int32
@@ -154,12 +115,20 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const unsigned int epoch_now = (p.comm_mode != kCommNone || p.ag_world > 1) ? *p.epoch + 1u : 0u;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (elect_one()) {
+      int x_map = 0, x_row = t0;
+      token_tile_source(p, t0, &x_map, &x_row);
+      const CUtensorMap* tmap_x_ptr = &tmaps_x.m[x_map];
       tma_prefetch_desc(&tmap_w);
-      tma_prefetch_desc(&tmap_x);
+      tma_prefetch_desc(tmap_x_ptr);
+      if (!ag_handshake(p, x_map, epoch_now)) {
+        set_status(p.status, kStatusTimeoutPeer);
+        *aborted = 1;
+      }
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         const int it = kb - kb_begin;
         const int s = it % RST;
@@ -172,7 +141,7 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
         uint8_t* r = raw_ring + s * RAW_BYTES;
         mbar_expect_tx(&raw_full[s], RAW_BYTES);
         // token tile first (keeps it 1024-byte aligned), packed weight tile(s) behind it
-        tma_load_2d(r, &tmap_x, &raw_full[s], kb * BK, t0);
+        tma_load_2d(r, tmap_x_ptr, &raw_full[s], kb * BK, x_row);
         tma_load_2d(r + B_BYTES, &tmap_w, &raw_full[s], kb * 8, n0);
         if (DUAL) tma_load_2d(r + B_BYTES + Q_BYTES, &tmap_w, &raw_full[s], kb * 8, p.dual_rows + n0);
       }
@@ -278,130 +247,10 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       }
     }
   }
-  // ---------------------------------------------------------------- epilogue part 1 (warps 2..5)
-  // Wait for the accumulator, then park it as fp32 in shared memory laid out [token][weight row].
-  if (warp >= 2) {
-    bool ok = mbar_wait(accum_bar, 0);
-    if (!ok) {
-      set_status(p.status, kStatusTimeoutAccum);
-      *aborted = 1;
-    }
-    tc_fence_after();
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
-    const int n_local = q * 32 + lane;
-    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-    if (ok) {
-      const bool fuse_act_now = DUAL && (S == 1);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        uint32_t r[16];
-        tmem_ld_x16(taddr + c0, r);
-        if (DUAL) {
-          uint32_t u[16];
-          tmem_ld_x16(taddr + BN + c0, u);
-          tmem_ld_wait();
-          if (fuse_act_now) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              stage_f32[(c0 + j) * BM + n_local] =
-                  apply_act(__uint_as_float(r[j]), p.act) * __uint_as_float(u[j]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              stage_f32[(c0 + j) * BM + n_local] = __uint_as_float(r[j]);
-              stage_f32[BN * BM + (c0 + j) * BM + n_local] = __uint_as_float(u[j]);
-            }
-          }
-        } else {
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) stage_f32[(c0 + j) * BM + n_local] = __uint_as_float(r[j]);
-        }
-      }
-    }
-    tc_fence_before();
-  }
+  // ---------------------------------------------------------------- epilogue (epilogue.cuh)
+  if (warp >= 2) epilogue_tmem_to_smem<BN, DUAL>(p, accum_bar, tmem_base, stage_f32, aborted, warp, lane);
   __syncthreads();
-  cg::cluster_group cluster = cg::this_cluster();
-  if (S > 1) cluster.sync();
-
-  // ---------------------------------------------------------------- epilogue part 2 (all threads)
-  // Rows (tokens) rank, rank+S, ... of the tile belong to this CTA: sum the S partial tiles through
-  // distributed shared memory, apply the epilogue and store 8 outputs per thread.
-  if (!*aborted) {
-    const int rows_mine = (BN - rank + S - 1) / S;
-    for (int idx = threadIdx.x; idx < rows_mine * (BM / 8); idx += kThreads) {
-      const int tl = rank + (idx / (BM / 8)) * S;
-      const int nl = (idx % (BM / 8)) * 8;
-      const int t = t0 + tl;
-      const int n = n0 + nl;
-      if (t >= p.T || n >= p.N) continue;
-      float g[8], u[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) { g[j] = 0.f; u[j] = 0.f; }
-      for (int pr = 0; pr < S; ++pr) {
-        const float* src = (S > 1) ? cluster.map_shared_rank(stage_f32, pr) : stage_f32;
-        const float4 a = *reinterpret_cast<const float4*>(src + tl * BM + nl);
-        const float4 b = *reinterpret_cast<const float4*>(src + tl * BM + nl + 4);
-        g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
-        g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
-        if (DUAL && S > 1) {
-          const float4 c = *reinterpret_cast<const float4*>(src + BN * BM + tl * BM + nl);
-          const float4 d = *reinterpret_cast<const float4*>(src + BN * BM + tl * BM + nl + 4);
-          u[0] += c.x; u[1] += c.y; u[2] += c.z; u[3] += c.w;
-          u[4] += d.x; u[5] += d.y; u[6] += d.z; u[7] += d.w;
-        }
-      }
-      if (DUAL && S > 1) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) g[j] = apply_act(g[j], p.act) * u[j];
-      } else if (!DUAL && p.act != kActNone) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) g[j] = apply_act(g[j], p.act);
-      }
-      const int nvalid = min(8, p.N - n);
-      if (p.bias != nullptr) {
-        for (int j = 0; j < nvalid; ++j) g[j] += ld16_as_float(p.bias, n + j, p.is_fp16);
-      }
-      const size_t off = static_cast<size_t>(t) * p.ldc + n;
-      if (p.out_fp32) {
-        float* C = reinterpret_cast<float*>(p.C);
-        if (p.residual != nullptr)
-          for (int j = 0; j < nvalid; ++j) g[j] += reinterpret_cast<const float*>(p.residual)[off + j];
-        if (nvalid == 8) {
-          *reinterpret_cast<float4*>(C + off) = make_float4(g[0], g[1], g[2], g[3]);
-          *reinterpret_cast<float4*>(C + off + 4) = make_float4(g[4], g[5], g[6], g[7]);
-        } else {
-          for (int j = 0; j < nvalid; ++j) C[off + j] = g[j];
-        }
-      } else {
-        if (p.residual != nullptr)
-          for (int j = 0; j < nvalid; ++j) g[j] += ld16_as_float(p.residual, off + j, p.is_fp16);
-        uint32_t packed[4];
-        if (p.is_fp16) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            __half2 h = __floats2half2_rn(g[2 * j], g[2 * j + 1]);
-            packed[j] = *reinterpret_cast<uint32_t*>(&h);
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(g[2 * j], g[2 * j + 1]);
-            packed[j] = *reinterpret_cast<uint32_t*>(&h);
-          }
-        }
-        uint16_t* C = reinterpret_cast<uint16_t*>(p.C);
-        if (nvalid == 8) {
-          *reinterpret_cast<uint4*>(C + off) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        } else {
-          const uint16_t* ph = reinterpret_cast<const uint16_t*>(packed);
-          for (int j = 0; j < nvalid; ++j) C[off + j] = ph[j];
-        }
-      }
-    }
-  }
-  if (S > 1) cluster.sync();  // nobody leaves while a peer may still read its staging tile
+  epilogue_reduce_store<BN, DUAL>(p, stage_f32, aborted, n0, t0, epoch_now);
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
@@ -419,7 +268,7 @@ constexpr int smem_bytes() {
 }
 
 template <typename T, int BN, int RST, int AST, bool DUAL>
-int launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams p, cudaStream_t stream) {
+int launch(const CUtensorMap& tw, const TokenMaps& tx, GemmParams p, cudaStream_t stream) {
   auto kern = awq_gemm_kernel<T, BN, RST, AST, DUAL>;
   constexpr int smem = smem_bytes<BN, RST, AST, DUAL>();
   constexpr int ring = ring_bytes<BN, RST, AST, DUAL>();
@@ -480,7 +329,7 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams p, cudaStrea
 }
 
 template <typename T, bool DUAL>
-int dispatch(int bn, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t s) {
+int dispatch(int bn, const CUtensorMap& tw, const TokenMaps& tx, const GemmParams& p, cudaStream_t s) {
   switch (bn) {
     case 16: return launch<T, 16, 10, 3, DUAL>(tw, tx, p, s);
     case 32: return launch<T, 32, 8, 3, DUAL>(tw, tx, p, s);
@@ -509,21 +358,34 @@ inline int make_tmap_packed(CUtensorMap* out, const void* base, uint64_t rows, u
 // C = X dequant(Wq)^T with optional epilogue.  qw/scales/zeros in the runtime layout described at
 // the top of this file.  dtype: 0 bf16, 1 fp16 (X, scales, bias, C unless out_fp32).
 // dual_rows > 0: gated mode, the weight holds [gate rows; up rows] and N == dual_rows.
-extern "C" int fi_awq_gemm(const void* X, const void* qw, const void* scales, const void* zeros, void* C,
+static int fi_awq_gemm_impl(const void* X, const void* qw, const void* scales, const void* zeros, void* C,
                            const void* bias, const void* residual, int T, int N, int K, int group,
                            int ldx, int ldc, int act, int dual_rows, int out_fp32, int dtype,
-                           int splits, int bn, int* status, void* stream) {
+                           int splits, int bn, int* status, void* stream,
+                             const FiComm* comm) {
   if (T <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 64) != 0 || (ldc % 8) != 0 || (reinterpret_cast<uintptr_t>(C) & 15) != 0) return -10;
   if (group != 32 && group != 64 && group != 128 && !(group > 128 && group % 64 == 0)) return -13;
   if (dual_rows > 0 && N != dual_rows) return -11;
   if (bn == 0) bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128;
   const int w_rows = dual_rows > 0 ? 2 * dual_rows : N;
-  CUtensorMap tw, tx;
+  CUtensorMap tw;
+  TokenMaps tx;
   int r = make_tmap_packed(&tw, qw, w_rows, K / 8);
   if (r != 0) return r * 100 - 1;
-  r = make_tmap_2d_16bit_sw128(&tx, X, T, K, ldx, bn);
-  if (r != 0) return r * 100 - 2;
+  if (comm != nullptr && comm->ag_world > 1) {
+    if (comm->ag_rows_per_rank % bn != 0) return -14;
+    for (int d = 0; d < comm->ag_world; ++d) {
+      int rows = T - d * comm->ag_rows_per_rank;
+      rows = rows < 0 ? 0 : (rows > comm->ag_rows_per_rank ? comm->ag_rows_per_rank : rows);
+      r = make_tmap_2d_16bit_sw128(&tx.m[d], reinterpret_cast<const void*>(comm->x_peers[d]),
+                                   rows > 0 ? rows : 1, K, ldx, bn);
+      if (r != 0) return r * 100 - 2;
+    }
+  } else {
+    r = make_tmap_2d_16bit_sw128(&tx.m[0], X, T, K, ldx, bn);
+    if (r != 0) return r * 100 - 2;
+  }
   const int kb_total = K / BK;
   if (splits > 8) splits = 8;
   if (splits > kb_total) splits = kb_total;
@@ -535,6 +397,24 @@ extern "C" int fi_awq_gemm(const void* X, const void* qw, const void* scales, co
   p.splits = splits; p.status = status;
   p.scales = scales; p.zeros = reinterpret_cast<const uint8_t*>(zeros); p.group = group;
   p.n_rows_total = w_rows;
+  p.comm_mode = 0; p.world = 1; p.rank = 0; p.rows_per_rank = 0; p.xfer_16bit = 0;
+  p.ag_world = 1; p.ag_rows_per_rank = 0; p.slab_elems = 0; p.epoch = nullptr; p.done = nullptr;
+  for (int d = 0; d < kMaxRanks; ++d) { p.recv[d] = 0; p.flags[d] = 0; p.ready[d] = 0; }
+  if (comm != nullptr) {
+    if (comm->world > kMaxRanks || comm->ag_world > kMaxRanks) return -15;
+    if (comm->mode != 0 && dual_rows > 0) return -16;   // a gated epilogue needs the full K sum
+    p.comm_mode = comm->mode; p.world = comm->world; p.rank = comm->rank;
+    p.rows_per_rank = comm->rows_per_rank; p.xfer_16bit = comm->xfer_16bit;
+    p.ag_world = comm->ag_world > 1 ? comm->ag_world : 1; p.ag_rows_per_rank = comm->ag_rows_per_rank;
+    p.slab_elems = comm->slab_elems;
+    p.epoch = reinterpret_cast<unsigned int*>(comm->epoch);
+    p.done = reinterpret_cast<unsigned int*>(comm->done);
+    for (int d = 0; d < kMaxRanks; ++d) { p.recv[d] = comm->recv[d]; p.flags[d] = comm->flags[d]; p.ready[d] = comm->ready[d]; }
+    if (comm->mode == kCommReduceScatter && (comm->rows_per_rank % bn) != 0) return -17;
+    const long tiles = static_cast<long>((N + BM - 1) / BM) * ((T + bn - 1) / bn);
+    if (comm->mode != 0 && tiles > kMaxCommTiles) return -18;
+    if (comm->mode != 0 && (N % 8) != 0) return -19;
+  }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == 1) {
     if (dual_rows > 0) return dispatch<__half, true>(bn, tw, tx, p, s);
@@ -542,4 +422,20 @@ extern "C" int fi_awq_gemm(const void* X, const void* qw, const void* scales, co
   }
   if (dual_rows > 0) return dispatch<__nv_bfloat16, true>(bn, tw, tx, p, s);
   return dispatch<__nv_bfloat16, false>(bn, tw, tx, p, s);
+}
+
+extern "C" int fi_awq_gemm(const void* X, const void* qw, const void* scales, const void* zeros, void* C,
+                           const void* bias, const void* residual, int T, int N, int K, int group,
+                           int ldx, int ldc, int act, int dual_rows, int out_fp32, int dtype,
+                           int splits, int bn, int* status, void* stream) {
+  return fi_awq_gemm_impl(X, qw, scales, zeros, C, bias, residual, T, N, K, group, ldx, ldc, act, dual_rows, out_fp32, dtype, splits, bn, status, stream, nullptr);
+}
+
+// Same GEMM with a fused collective and/or an all-gathered token operand (see comm_desc.h).
+extern "C" int fi_awq_gemm_comm(const void* X, const void* qw, const void* scales, const void* zeros, void* C,
+                           const void* bias, const void* residual, int T, int N, int K, int group,
+                           int ldx, int ldc, int act, int dual_rows, int out_fp32, int dtype,
+                           int splits, int bn, int* status, void* stream,
+                             const FiComm* comm) {
+  return fi_awq_gemm_impl(X, qw, scales, zeros, C, bias, residual, T, N, K, group, ldx, ldc, act, dual_rows, out_fp32, dtype, splits, bn, status, stream, comm);
 }

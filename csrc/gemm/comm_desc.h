@@ -1,0 +1,22 @@
+// Host-side description of the fused collective of one GEMM call (filled by Python through ctypes).
+#pragma once
+
+extern "C" {
+struct FiComm {
+  int mode;              // 0 none, 1 all-reduce, 2 reduce-scatter (output rows owned by rank)
+  int world;
+  int rank;
+  int rows_per_rank;     // reduce-scatter: rows of the output shard (multiple of the token tile)
+  int xfer_16bit;        // send partials as 16-bit values instead of fp32
+  int ag_world;          // > 1: the token operand is the concatenation of every rank's shard
+  int ag_rows_per_rank;  // rows of one token shard
+  int reserved;
+  long slab_elems;       // elements of one (parity, source rank) receive slab
+  unsigned long long recv[8];     // receive area of rank d, as mapped into this process
+  unsigned long long flags[8];    // flag words of rank d
+  unsigned long long ready[8];    // all-gather ready words of rank d
+  unsigned long long x_peers[8];  // token shard of rank d (all-gather mode)
+  unsigned long long epoch;       // local device word: completed fused calls
+  unsigned long long done;        // local device word: finished CTAs of the running call
+};
+}

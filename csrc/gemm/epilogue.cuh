@@ -1,0 +1,390 @@
+// Shared epilogue of the tcgen05 GEMM kernels (dense 16-bit and int4 weight-only).
+//
+// Part 1 (four epilogue warps): accumulator TMEM -> fp32 staging tile in shared memory, laid out
+//   [token][weight row].
+// Part 2 (all threads): split-K reduction of the cluster's partial tiles through distributed shared
+//   memory, then EITHER the local epilogue (activation, bias, residual, store) OR the fused
+//   collective: the reduced partial rows are pushed with plain peer stores over NVLink into the
+//   receive area of every other rank (all-reduce) or of the owning rank (reduce-scatter), a
+//   per-(tile, source rank, cluster part) flag word is released with the call's epoch, the CTA waits
+//   (bounded) for the matching flags of its peers, sums the partials in rank order (bitwise identical
+//   on every rank), adds bias/residual and stores.  One kernel = GEMM + collective + residual.
+//
+// Collective bookkeeping lives on the device so CUDA-graph replays work: `epoch` counts completed
+// fused calls (every rank runs the same call sequence), the last CTA of a call bumps it; receive
+// slabs are double-buffered by epoch parity, which is enough because a rank cannot finish call k+1
+// before every peer has pushed its call-k+1 partials, i.e. after those peers finished reading call k.
+#pragma once
+#include <cooperative_groups.h>
+
+#include "../common/ptx.cuh"
+
+namespace fi {
+
+constexpr int BM = 128;  // weight rows per CTA
+constexpr int BK = 64;   // 64 x 16-bit = one 128-byte swizzle row
+constexpr int kThreads = 192;
+constexpr int kMaxRanks = 8;
+constexpr int kFlagParts = 8;       // flag words per (tile, source rank): one per cluster part
+constexpr int kMaxCommTiles = 8192; // tiles per call that the flag area can describe
+
+enum Act : int { kActNone = 0, kActSilu = 1, kActGeluTanh = 2 };
+enum CommMode : int { kCommNone = 0, kCommAllReduce = 1, kCommReduceScatter = 2 };
+
+struct GemmParams {
+  void* C;
+  const void* bias;      // [N] or null (same 16-bit type as X)
+  const void* residual;  // [T, ldc] or null (same type as C when C is 16-bit)
+  int T, N, K;
+  int ldc;
+  int dual_rows;  // > 0: gated mode, W = [2 * dual_rows, K]; N == dual_rows
+  int act;
+  int out_fp32;
+  int is_fp16;
+  int splits;
+  int* status;
+  // int4 weight-only extras (unused by the dense kernel)
+  const void* scales;   // [K/G, rows]
+  const uint8_t* zeros; // [K/G, rows] or null
+  int group;
+  int n_rows_total;
+  // fused collective (comm_mode != 0) and all-gathered token operand (ag_world > 1)
+  int comm_mode;
+  int world, rank;
+  int rows_per_rank;     // reduce-scatter: token t belongs to rank t / rows_per_rank
+  int xfer_16bit;        // partials cross NVLink as 16-bit values instead of fp32
+  int ag_world;          // > 1: token tile t0 is read from rank t0 / ag_rows_per_rank
+  int ag_rows_per_rank;
+  long slab_elems;       // elements of one (parity, source) receive slab
+  unsigned long long recv[kMaxRanks];   // receive area of rank d as mapped in this process
+  unsigned long long flags[kMaxRanks];  // flag words of rank d as mapped in this process
+  unsigned long long ready[kMaxRanks];  // all-gather ready words of rank d as mapped here
+  unsigned int* epoch;   // local: completed fused calls
+  unsigned int* done;    // local: CTAs of the current call that have finished
+};
+
+struct TokenMaps {
+  CUtensorMap m[kMaxRanks];
+};
+
+__device__ __forceinline__ float apply_act(float g, int act) {
+  if (act == kActSilu) return g / (1.f + __expf(-g));
+  if (act == kActGeluTanh) {
+    const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return g / (1.f + __expf(-2.f * inner));
+  }
+  return g;
+}
+
+__device__ __forceinline__ float ld16_as_float(const void* p, size_t i, int is_fp16) {
+  if (is_fp16) return __half2float(reinterpret_cast<const __half*>(p)[i]);
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded wait for a flag word to reach `want` (epochs only grow).
+__device__ __forceinline__ bool wait_flag(const unsigned int* p, unsigned int want) {
+  const long long t0 = clock64();
+  while (static_cast<int>(ld_acquire_sys(p) - want) < 0) {
+    if (clock64() - t0 > FI_WAIT_CYCLES) return false;
+  }
+  return true;
+}
+
+__device__ __forceinline__ void pack8(const float* g, int is_fp16, uint32_t* packed) {
+  if (is_fp16) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __half2 h = __floats2half2_rn(g[2 * j], g[2 * j + 1]);
+      packed[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(g[2 * j], g[2 * j + 1]);
+      packed[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+  }
+}
+__device__ __forceinline__ void unpack8(const uint4 raw, int is_fp16, float* g) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (is_fp16) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+      g[2 * j] = f.x; g[2 * j + 1] = f.y;
+    } else {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+      g[2 * j] = f.x; g[2 * j + 1] = f.y;
+    }
+  }
+}
+
+// Bias + residual + store of 8 consecutive outputs of token row `trow` (row index in C).
+__device__ __forceinline__ void finalize_store8(const GemmParams& p, float* g, int trow, int n) {
+  const int nvalid = min(8, p.N - n);
+  if (p.bias != nullptr) {
+    for (int j = 0; j < nvalid; ++j) g[j] += ld16_as_float(p.bias, n + j, p.is_fp16);
+  }
+  const size_t off = static_cast<size_t>(trow) * p.ldc + n;
+  if (p.out_fp32) {
+    float* C = reinterpret_cast<float*>(p.C);
+    if (p.residual != nullptr)
+      for (int j = 0; j < nvalid; ++j) g[j] += reinterpret_cast<const float*>(p.residual)[off + j];
+    if (nvalid == 8) {
+      *reinterpret_cast<float4*>(C + off) = make_float4(g[0], g[1], g[2], g[3]);
+      *reinterpret_cast<float4*>(C + off + 4) = make_float4(g[4], g[5], g[6], g[7]);
+    } else {
+      for (int j = 0; j < nvalid; ++j) C[off + j] = g[j];
+    }
+  } else {
+    if (p.residual != nullptr)
+      for (int j = 0; j < nvalid; ++j) g[j] += ld16_as_float(p.residual, off + j, p.is_fp16);
+    uint32_t packed[4];
+    pack8(g, p.is_fp16, packed);
+    uint16_t* C = reinterpret_cast<uint16_t*>(p.C);
+    if (nvalid == 8) {
+      *reinterpret_cast<uint4*>(C + off) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    } else {
+      const uint16_t* ph = reinterpret_cast<const uint16_t*>(packed);
+      for (int j = 0; j < nvalid; ++j) C[off + j] = ph[j];
+    }
+  }
+}
+
+// Part 1: warps 2..5.  Returns false when the accumulator never arrived.
+template <int BN, bool DUAL>
+__device__ __forceinline__ void epilogue_tmem_to_smem(const GemmParams& p, uint64_t* accum_bar,
+                                                      uint32_t tmem_base, float* stage_f32,
+                                                      volatile int* aborted, int warp, int lane) {
+  bool ok = mbar_wait(accum_bar, 0);
+  if (!ok) {
+    set_status(p.status, kStatusTimeoutAccum);
+    *aborted = 1;
+  }
+  tc_fence_after();
+  const int q = warp & 3;  // TMEM lane quarter this warp may read
+  const int n_local = q * 32 + lane;
+  const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+  if (ok) {
+    const bool fuse_act_now = DUAL && (p.splits == 1);
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 16) {
+      uint32_t r[16];
+      tmem_ld_x16(taddr + c0, r);
+      if (DUAL) {
+        uint32_t u[16];
+        tmem_ld_x16(taddr + BN + c0, u);
+        tmem_ld_wait();
+        if (fuse_act_now) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            stage_f32[(c0 + j) * BM + n_local] =
+                apply_act(__uint_as_float(r[j]), p.act) * __uint_as_float(u[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            stage_f32[(c0 + j) * BM + n_local] = __uint_as_float(r[j]);
+            stage_f32[BN * BM + (c0 + j) * BM + n_local] = __uint_as_float(u[j]);
+          }
+        }
+      } else {
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) stage_f32[(c0 + j) * BM + n_local] = __uint_as_float(r[j]);
+      }
+    }
+  }
+  tc_fence_before();
+}
+
+// Part 2: every thread of the CTA.  Must be called by all CTAs of the cluster (it contains the
+// cluster barriers).  `n0`, `t0`: first weight row / token of the tile.
+template <int BN, bool DUAL>
+__device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float* stage_f32,
+                                                      volatile int* aborted, int n0, int t0,
+                                                      unsigned int epoch_now) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int S = p.splits;
+  const int rank = (S > 1) ? static_cast<int>(blockIdx.z) : 0;   // rank inside the split-K cluster
+  if (S > 1) cluster.sync();
+  const bool comm = p.comm_mode != kCommNone;
+  const int rows_mine = (BN - rank + S - 1) / S;
+  const int owner = p.comm_mode == kCommReduceScatter ? t0 / p.rows_per_rank : -1;
+  const int parity = static_cast<int>(epoch_now & 1u);
+  const int row_base = p.comm_mode == kCommReduceScatter ? p.rank * p.rows_per_rank : 0;
+
+  if (!*aborted) {
+    for (int idx = threadIdx.x; idx < rows_mine * (BM / 8); idx += kThreads) {
+      const int tl = rank + (idx / (BM / 8)) * S;
+      const int nl = (idx % (BM / 8)) * 8;
+      const int t = t0 + tl;
+      const int n = n0 + nl;
+      if (t >= p.T || n >= p.N) continue;
+      float g[8], u[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { g[j] = 0.f; u[j] = 0.f; }
+      for (int pr = 0; pr < S; ++pr) {
+        const float* src = (S > 1) ? cluster.map_shared_rank(stage_f32, pr) : stage_f32;
+        const float4 a = *reinterpret_cast<const float4*>(src + tl * BM + nl);
+        const float4 b = *reinterpret_cast<const float4*>(src + tl * BM + nl + 4);
+        g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
+        g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+        if (DUAL && S > 1) {
+          const float4 c = *reinterpret_cast<const float4*>(src + BN * BM + tl * BM + nl);
+          const float4 d = *reinterpret_cast<const float4*>(src + BN * BM + tl * BM + nl + 4);
+          u[0] += c.x; u[1] += c.y; u[2] += c.z; u[3] += c.w;
+          u[4] += d.x; u[5] += d.y; u[6] += d.z; u[7] += d.w;
+        }
+      }
+      if (DUAL && S > 1) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] = apply_act(g[j], p.act) * u[j];
+      } else if (!DUAL && p.act != kActNone && !comm) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] = apply_act(g[j], p.act);
+      }
+      if (!comm) {
+        finalize_store8(p, g, t, n);
+        continue;
+      }
+      // ---- fused collective, phase A: keep my partial in my own staging rows, push it to peers
+      *reinterpret_cast<float4*>(stage_f32 + tl * BM + nl) = make_float4(g[0], g[1], g[2], g[3]);
+      *reinterpret_cast<float4*>(stage_f32 + tl * BM + nl + 4) = make_float4(g[4], g[5], g[6], g[7]);
+      const long trow = (p.comm_mode == kCommReduceScatter) ? (t - owner * p.rows_per_rank) : t;
+      const long off = (static_cast<long>(parity) * p.world + p.rank) * p.slab_elems + trow * p.N + n;
+      for (int d = 0; d < p.world; ++d) {
+        if (d == p.rank || (owner >= 0 && d != owner)) continue;
+        if (p.xfer_16bit) {
+          uint32_t packed[4];
+          pack8(g, p.is_fp16, packed);
+          *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.recv[d]) + off) =
+              make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        } else {
+          float* dst = reinterpret_cast<float*>(p.recv[d]) + off;
+          *reinterpret_cast<float4*>(dst) = make_float4(g[0], g[1], g[2], g[3]);
+          *reinterpret_cast<float4*>(dst + 4) = make_float4(g[4], g[5], g[6], g[7]);
+        }
+      }
+    }
+  }
+  if (comm) {
+    const unsigned int tile = blockIdx.y * gridDim.x + blockIdx.x;
+    __threadfence_system();
+    __syncthreads();
+    const bool i_own = owner < 0 || owner == p.rank;
+    if (!*aborted && threadIdx.x < p.world && static_cast<int>(threadIdx.x) != p.rank) {
+      const int d = threadIdx.x;
+      if (owner < 0 || d == owner) {
+        unsigned int* f = reinterpret_cast<unsigned int*>(p.flags[d]) +
+                          (static_cast<size_t>(tile) * p.world + p.rank) * kFlagParts + rank;
+        st_release_sys(f, epoch_now);
+      }
+      if (i_own) {
+        const unsigned int* mine = reinterpret_cast<const unsigned int*>(p.flags[p.rank]) +
+                                   (static_cast<size_t>(tile) * p.world + d) * kFlagParts + rank;
+        if (!wait_flag(mine, epoch_now)) {
+          set_status(p.status, kStatusTimeoutPeer);
+          *aborted = 1;
+        }
+      }
+    }
+    __syncthreads();
+    // ---- phase C: sum the partials of all ranks in rank order, finish the epilogue, store
+    if (!*aborted && i_own) {
+      for (int idx = threadIdx.x; idx < rows_mine * (BM / 8); idx += kThreads) {
+        const int tl = rank + (idx / (BM / 8)) * S;
+        const int nl = (idx % (BM / 8)) * 8;
+        const int t = t0 + tl;
+        const int n = n0 + nl;
+        if (t >= p.T || n >= p.N) continue;
+        const long trow = t - row_base;
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int s = 0; s < p.world; ++s) {
+          float v[8];
+          if (s == p.rank) {
+            const float4 a = *reinterpret_cast<const float4*>(stage_f32 + tl * BM + nl);
+            const float4 b = *reinterpret_cast<const float4*>(stage_f32 + tl * BM + nl + 4);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+            if (p.xfer_16bit) {   // round my own partial like the ones that crossed the link
+              uint32_t packed[4];
+              pack8(v, p.is_fp16, packed);
+              unpack8(make_uint4(packed[0], packed[1], packed[2], packed[3]), p.is_fp16, v);
+            }
+          } else {
+            const long off = (static_cast<long>(parity) * p.world + s) * p.slab_elems + trow * p.N + n;
+            if (p.xfer_16bit) {
+              unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.recv[p.rank]) + off),
+                      p.is_fp16, v);
+            } else {
+              const float* src = reinterpret_cast<const float*>(p.recv[p.rank]) + off;
+              const float4 a = *reinterpret_cast<const float4*>(src);
+              const float4 b = *reinterpret_cast<const float4*>(src + 4);
+              v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += v[j];
+        }
+        if (!DUAL && p.act != kActNone) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = apply_act(acc[j], p.act);
+        }
+        finalize_store8(p, acc, static_cast<int>(trow), n);
+      }
+    }
+  }
+  if (comm || p.ag_world > 1) {
+    // the last CTA of the call publishes the new epoch for the next fused call
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int total = gridDim.x * gridDim.y * gridDim.z;
+      __threadfence();
+      if (atomicAdd(p.done, 1u) == total - 1) {
+        *p.done = 0;
+        __threadfence();
+        *reinterpret_cast<volatile unsigned int*>(p.epoch) = epoch_now;
+      }
+    }
+  }
+  if (S > 1) cluster.sync();  // nobody leaves while a peer may still read its staging tile
+}
+
+// Source of the token tile starting at token t0: which tensor map and which row inside it.
+__device__ __forceinline__ void token_tile_source(const GemmParams& p, int t0, int* map_idx, int* row) {
+  if (p.ag_world > 1) {
+    *map_idx = t0 / p.ag_rows_per_rank;
+    *row = t0 - (*map_idx) * p.ag_rows_per_rank;
+  } else {
+    *map_idx = 0;
+    *row = t0;
+  }
+}
+
+// All-gather handshake run by the TMA producer thread before its first remote load: CTA (0,0,0)
+// tells every peer that this rank's token shard of the current call is complete; every producer
+// waits (bounded) until the rank it reads from has said the same.
+__device__ __forceinline__ bool ag_handshake(const GemmParams& p, int src, unsigned int epoch_now) {
+  if (p.ag_world <= 1) return true;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+    __threadfence_system();
+    for (int d = 0; d < p.ag_world; ++d) {
+      if (d == p.rank) continue;
+      st_release_sys(reinterpret_cast<unsigned int*>(p.ready[d]) + p.rank, epoch_now);
+    }
+  }
+  if (src == p.rank) return true;
+  return wait_flag(reinterpret_cast<const unsigned int*>(p.ready[p.rank]) + src, epoch_now);
+}
+
+}  // namespace fi

@@ -53,12 +53,14 @@ class LiteLinear(nn.Module):
             y = self.lora.apply(self, x, y, lora_mapping)
         return y
 
-    def _matmul(self, x, residual=None, out=None, out_dtype=None):
+    def _matmul(self, x, residual=None, out=None, out_dtype=None, use_bias: bool = True):
         if self.quant_method is not None:
-            return self.quant_method.apply(self, x, residual=residual, out=out, out_dtype=out_dtype)
+            return self.quant_method.apply(self, x, residual=residual, out=out, out_dtype=out_dtype,
+                                           use_bias=use_bias)
         if self.gated_act is not None:
             return ops.gated_linear(x, self.weight, self.gated_act, out=out)
-        return ops.linear(x, self.weight, self.bias, residual, out=out, out_dtype=out_dtype)
+        return ops.linear(x, self.weight, self.bias if use_bias else None, residual, out=out,
+                          out_dtype=out_dtype)
 
     def _row_parallel(self, x, residual, out):
         from ..parallel import fused_ops

@@ -9,8 +9,10 @@ def get_quantization_config(quant_spec, hf_cfg: dict | None = None):
         return None
     if method == "awq":
         from .awq import AWQConfig
+        q = (hf_cfg or {}).get("quantization_config") or {}
+        layout = "autoawq" if str(q.get("version", "")).lower() == "gemm" else "auto"
         return AWQConfig(bits=quant_spec.bits, group_size=quant_spec.group_size,
-                         zero_point=quant_spec.zero_point)
+                         zero_point=quant_spec.zero_point, layout=layout)
     if method == "compressed-tensors":
         from .compressed_tensors import CompressedTensorsConfig
         return CompressedTensorsConfig(bits=quant_spec.bits, group_size=quant_spec.group_size,

@@ -12,10 +12,23 @@ from ...parallel import state as pstate
 class Int4LinearMethod:
     """Collects the checkpoint pieces of a (merged, TP-sharded) layer, then repacks once."""
 
-    def __init__(self, bits: int, group_size: int, zero_point: bool):
+    def __init__(self, bits: int, group_size: int, zero_point: bool, layout: str = "auto"):
         assert bits == 4, "only 4-bit weights are supported"
         self.group = group_size
         self.zero_point = zero_point
+        self.layout = layout     # "rowmajor" | "autoawq" | "auto" (by shape, row-major when ambiguous)
+
+    def _is_autoawq(self, layer, name: str, t: torch.Tensor) -> bool:
+        if self.layout != "auto":
+            return self.layout == "autoawq"
+        K, G = layer.full_in, self.group
+        if name == "qweight":
+            return t.shape[1] * 8 != K and t.shape[0] == K
+        if name == "scales":
+            return t.shape[1] != K // G and t.shape[0] == K // G
+        if name == "qzeros":
+            return t.shape[1] != (K // G + 7) // 8 and t.shape[0] == K // G
+        return False
 
     def create_weights(self, layer, dtype) -> None:
         N, K = layer.out_features, layer.in_features
@@ -43,7 +56,7 @@ class Int4LinearMethod:
         dev = layer._q_nib.device
         if name == "qweight":
             t = tensor.to(dev)
-            if t.shape[0] != full_rows:      # AutoAWQ [K, N/8] orientation
+            if self._is_autoawq(layer, name, t):      # AutoAWQ [K, N/8] orientation
                 layer._autoawq = getattr(layer, "_autoawq", {})
                 layer._autoawq[(piece, "qweight")] = t
                 return self._try_autoawq(layer, piece, src_rows)
@@ -51,14 +64,14 @@ class Int4LinearMethod:
             layer._q_nib[dst0:dst0 + n].copy_(self._k_slice(layer, nib, 1))
         elif name == "scales":
             t = tensor.to(dev)
-            if t.shape[0] != full_rows:
+            if self._is_autoawq(layer, name, t):
                 layer._autoawq = getattr(layer, "_autoawq", {})
                 layer._autoawq[(piece, "scales")] = t
                 return self._try_autoawq(layer, piece, src_rows)
             layer._q_scales[dst0:dst0 + n].copy_(self._k_slice(layer, t[start:start + n], self.group).to(layer._q_scales.dtype))
         elif name == "qzeros":
             t = tensor.to(dev)
-            if t.shape[0] != full_rows:
+            if self._is_autoawq(layer, name, t):
                 layer._autoawq = getattr(layer, "_autoawq", {})
                 layer._autoawq[(piece, "qzeros")] = t
                 return self._try_autoawq(layer, piece, src_rows)
@@ -94,7 +107,8 @@ class Int4LinearMethod:
         if layer._q_nib.is_cuda:
             layer._q_nib = layer._q_scales = layer._q_zeros = None
 
-    def apply(self, layer, x, residual=None, out=None, out_dtype=None, ungated: bool = False):
+    def apply(self, layer, x, residual=None, out=None, out_dtype=None, ungated: bool = False,
+              use_bias: bool = True):
         if layer.int4 is None:
             self.process_weights_after_loading(layer)
         gated = None if ungated else layer.gated_act
@@ -102,7 +116,7 @@ class Int4LinearMethod:
             # rare path (LoRA on a gated layer): run the merged weight as a plain [2I, K] GEMM
             w = layer.int4
             return awq_ops.int4_linear(x, w, out_dtype=out_dtype)
-        return awq_ops.int4_linear(x, layer.int4, bias=layer.bias, residual=residual, gated_act=gated,
+        return awq_ops.int4_linear(x, layer.int4, bias=layer.bias if use_bias else None, residual=residual, gated_act=gated,
                                    out=out, out_dtype=out_dtype)
 
 
@@ -110,14 +124,15 @@ class AWQConfig:
     name = "awq"
 
     def __init__(self, bits: int = 4, group_size: int = 128, zero_point: bool = True,
-                 skip_modules: tuple[str, ...] = ("lm_head",)):
+                 skip_modules: tuple[str, ...] = ("lm_head",), layout: str = "auto"):
         self.bits, self.group_size, self.zero_point = bits, group_size, zero_point
         self.skip_modules = skip_modules
+        self.layout = layout
 
     def get_method(self, layer):
         if any(s in layer.prefix for s in self.skip_modules) or not layer.prefix:
             return None
-        return Int4LinearMethod(self.bits, self.group_size, self.zero_point)
+        return Int4LinearMethod(self.bits, self.group_size, self.zero_point, self.layout)
 
     def __repr__(self) -> str:
         return f"AWQConfig(bits={self.bits}, group_size={self.group_size}, zero_point={self.zero_point})"

@@ -44,7 +44,8 @@ def status_word(device: torch.device) -> torch.Tensor:
     idx = device.index if device.index is not None else torch.cuda.current_device()
     w = _status_words.get(idx)
     if w is None:
-        w = torch.zeros(1, dtype=torch.int32, device=device)
+        with torch.inference_mode(False):   # a normal tensor: it is reset in place from any context
+            w = torch.zeros(1, dtype=torch.int32, device=device)
         _status_words[idx] = w
     return w
 

@@ -1,0 +1,126 @@
+"""Tensor-parallel linear ops.
+
+``row_parallel_linear``: every rank holds a K-slice of the weight; the partial products must be
+summed over ranks and the residual added once.
+  * ``comm_backend = "fused"`` (default on GPUs): ONE kernel does GEMM + all-reduce + residual: the
+    tcgen05 GEMM epilogue pushes its partial tile into every peer's receive slab over NVLink,
+    flags it, waits for the peers' tiles and finishes the sum (csrc/gemm/epilogue.cuh).
+  * ``comm_backend = "nccl"`` (baseline, also the CPU/gloo path): GEMM, then ``all_reduce``, then
+    the residual add.
+The reference has no tensor parallelism (vllm/model_executor/layers/linear.py:7-11 aliases every
+parallel linear to the plain one).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import ops
+from ..ops import _lib
+from . import state as pstate
+
+_parity = [0]
+
+
+def _fused_available(x: torch.Tensor) -> bool:
+    st = pstate.get_state()
+    return x.is_cuda and st.comm_backend == "fused" and st.symm is not None
+
+
+def row_parallel_linear(layer, x: torch.Tensor, residual: torch.Tensor | None, out: torch.Tensor | None):
+    st = pstate.get_state()
+    T = x.shape[0]
+    N = layer.out_features
+    if _fused_available(x):
+        heap = st.symm
+        xfer16 = T > 256
+        elem = 2 if xfer16 else 4
+        if heap.fits_recv(T, N, elem) and T > 0:
+            return _fused_gemm_allreduce(layer, x, residual, out, heap, xfer16)
+    # baseline: library collective around the local GEMM
+    partial = layer._matmul(x, None, None, None, use_bias=pstate.tp_rank() == 0)   # bias enters the sum once
+    pstate.all_reduce(partial)
+    if residual is not None:
+        partial = partial + residual
+    if out is not None:
+        out.copy_(partial)
+        return out
+    return partial
+
+
+def _fused_gemm_allreduce(layer, x, residual, out, heap, xfer16: bool):
+    T, K = x.shape
+    N = layer.out_features
+    if out is None:
+        out = torch.empty(T, N, dtype=x.dtype, device=x.device)
+    comm = heap.comm_desc(mode=1, T=T, N=N, xfer_16bit=xfer16)
+    lib = _lib.kernels()
+    dt = ops._DT[x.dtype]
+    bias = layer.bias if pstate.tp_rank() == 0 else None
+    if layer.quant_method is None:
+        w = layer.weight
+        rc = lib.fi_dense_gemm_comm(ops._p(x), ops._p(w), ops._p(out), ops._p(bias), ops._p(residual), T, N, K,
+                                    x.stride(0), w.stride(0), out.stride(0), 0, 0, 0, dt, 0, 0,
+                                    ops._p(ops.status_word(x.device)), ops._stream(), ctypes.byref(comm))
+        _lib.check(rc, "fi_dense_gemm_comm")
+    else:
+        if layer.int4 is None:
+            layer.quant_method.process_weights_after_loading(layer)
+        w = layer.int4
+        rc = lib.fi_awq_gemm_comm(ops._p(x), ops._p(w.qw), ops._p(w.scales_t), ops._p(w.zeros_t), ops._p(out),
+                                  ops._p(bias), ops._p(residual), T, N, K, w.group, x.stride(0), out.stride(0),
+                                  0, 0, 0, dt, 0, 0, ops._p(ops.status_word(x.device)), ops._stream(),
+                                  ctypes.byref(comm))
+        _lib.check(rc, "fi_awq_gemm_comm")
+    ops._count()
+    return out
+
+
+# --------------------------------------------------------------------------- sequence-parallel forms
+def gemm_reduce_scatter(x: torch.Tensor, w: torch.Tensor, residual_shard: torch.Tensor | None,
+                        rows_per_rank: int, out_shard: torch.Tensor | None = None,
+                        xfer_16bit: bool = True) -> torch.Tensor:
+    """``(x @ w.T)`` summed over ranks, each rank keeping token rows
+    ``[rank*rows_per_rank, (rank+1)*rows_per_rank)`` (+ its residual shard).  One fused kernel."""
+    st = pstate.get_state()
+    heap = st.symm
+    T, K = x.shape
+    N = w.shape[0]
+    if out_shard is None:
+        out_shard = torch.empty(rows_per_rank, N, dtype=x.dtype, device=x.device)
+    comm = heap.comm_desc(mode=2, T=T, N=N, xfer_16bit=xfer_16bit, rows_per_rank=rows_per_rank)
+    rc = _lib.kernels().fi_dense_gemm_comm(
+        ops._p(x), ops._p(w), ops._p(out_shard), None, ops._p(residual_shard), T, N, K, x.stride(0), w.stride(0),
+        out_shard.stride(0), 0, 0, 0, ops._DT[x.dtype], 0, 0, ops._p(ops.status_word(x.device)), ops._stream(),
+        ctypes.byref(comm))
+    _lib.check(rc, "fi_dense_gemm_comm(reduce_scatter)")
+    ops._count()
+    return out_shard
+
+
+def allgather_gemm(x_shard: torch.Tensor, w: torch.Tensor, T_total: int, rows_per_rank: int,
+                   out: torch.Tensor | None = None, gated_act: str | None = None) -> torch.Tensor:
+    """``concat_over_ranks(x_shard) @ w.T`` without materialising the gathered activations: every
+    rank parks its shard in the symmetric token buffer and the GEMM's TMA producer reads each token
+    tile straight from the rank that owns it (plain, non-multicast TMA loads over NVLink)."""
+    st = pstate.get_state()
+    heap = st.symm
+    K = x_shard.shape[1]
+    parity = _parity[0] & 1
+    _parity[0] += 1
+    buf = heap.xbuf(parity, rows_per_rank, K, x_shard.dtype)
+    buf[: x_shard.shape[0]].copy_(x_shard)
+    inter = w.shape[0] // 2 if gated_act else 0
+    N = inter if gated_act else w.shape[0]
+    if out is None:
+        out = torch.empty(T_total, N, dtype=x_shard.dtype, device=x_shard.device)
+    comm = heap.comm_desc(mode=0, T=T_total, N=N, xfer_16bit=False, ag_world=st.world_size,
+                          ag_rows_per_rank=rows_per_rank, x_parity=parity)
+    rc = _lib.kernels().fi_dense_gemm_comm(
+        ops._p(buf), ops._p(w), ops._p(out), None, None, T_total, N, K, buf.stride(0), w.stride(0), out.stride(0),
+        ops._ACT[gated_act] if gated_act else 0, inter, 0, ops._DT[x_shard.dtype], 0, 0,
+        ops._p(ops.status_word(x_shard.device)), ops._stream(), ctypes.byref(comm))
+    _lib.check(rc, "fi_dense_gemm_comm(all_gather)")
+    ops._count()
+    return out

@@ -1,0 +1,80 @@
+"""Multi-GPU bring-up: one process per GPU (torchrun style env: RANK, LOCAL_RANK, WORLD_SIZE,
+MASTER_ADDR, MASTER_PORT).  Every rank runs the same engine on the same request stream (SPMD control
+plane): scheduling is deterministic and sampled tokens are identical on all ranks because the logits
+are all-gathered and the fused collectives sum in a fixed rank order, so no per-step plan broadcast
+is needed for offline generation.  Servers broadcast new requests from rank 0 through
+:class:`ControlChannel`.  ``spawn`` starts local worker processes for tests and examples.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.multiprocessing as mp
+
+from ..logger import init_logger
+from . import state as pstate
+
+logger = init_logger(__name__)
+
+
+class DistributedHandle:
+    def __init__(self, st):
+        self.state = st
+        self.engine = None
+
+    def attach(self, engine) -> None:
+        self.engine = engine
+
+    def shutdown(self) -> None:
+        """Drop captured CUDA graphs (they hold collective kernels), quiesce, then leave the group.
+        The NCCL communicator itself is left to process exit: tearing it down while graph-captured
+        collectives exist was observed to block in ``destroy_process_group``."""
+        import gc
+
+        import torch.distributed as dist
+        eng = self.engine
+        if eng is not None and hasattr(eng, "decode_executor"):
+            getattr(eng.decode_executor, "_graphs", {}).clear()
+            eng.decode_executor._pool = None
+        gc.collect()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        if dist.is_initialized():
+            try:
+                dist.barrier()
+            except Exception:
+                pass
+        pstate.destroy_parallel(destroy_group=not torch.cuda.is_available())
+
+
+def init_distributed_engine(vllm_config) -> DistributedHandle:
+    pc = vllm_config.parallel_config
+    st = pstate.init_parallel(pc.tensor_parallel_size, pc.expert_parallel_size, pc.comm_backend)
+    if st.world_size > 1 and torch.cuda.is_available() and pc.comm_backend == "fused":
+        from .symm import SymmetricHeap
+        dev = torch.device("cuda", st.local_rank)
+        try:
+            st.symm = SymmetricHeap(st.rank, st.world_size, dev)
+            logger.info("rank %d: symmetric heap ready (%d peers)", st.rank, st.world_size)
+        except Exception as e:  # pragma: no cover - depends on the platform
+            logger.warning("symmetric memory unavailable (%r): falling back to NCCL collectives", e)
+            st.symm = None
+            st.comm_backend = "nccl"
+    if torch.cuda.is_available():
+        vllm_config.device = f"cuda:{st.local_rank}"
+    return DistributedHandle(st)
+
+
+def _worker(rank: int, world: int, port: int, fn, args):
+    os.environ["RANK"] = str(rank)
+    os.environ["LOCAL_RANK"] = str(rank)
+    os.environ["WORLD_SIZE"] = str(world)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    fn(rank, world, *args)
+
+
+def spawn(fn, world: int, args: tuple = (), port: int = 29531, join: bool = True):
+    """Run ``fn(rank, world, *args)`` in ``world`` local processes."""
+    return mp.spawn(_worker, args=(world, port, fn, args), nprocs=world, join=join)

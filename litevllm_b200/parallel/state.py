@@ -89,14 +89,14 @@ def init_parallel(tp: int = 1, ep: int = 1, comm_backend: str = "fused", backend
     return _STATE
 
 
-def destroy_parallel() -> None:
+def destroy_parallel(destroy_group: bool = True) -> None:
     global _STATE
     if _STATE.symm is not None:
         try:
             _STATE.symm.close()
         except Exception:
             pass
-    if dist.is_initialized():
+    if destroy_group and dist.is_initialized():
         dist.destroy_process_group()
     _STATE = ParallelState()
 

@@ -236,3 +236,35 @@ def test_int4_gated_and_layout_roundtrip():
     inter = kn.reshape(K, 2 * I // 8, 8)[:, :, order].reshape(K, 2 * I)
     back, s2, _ = awq.autoawq_to_rowmajor(awq.pack_nibbles(inter), scales.t().contiguous(), None)
     assert torch.equal(back, nib) and torch.equal(s2, scales)
+
+
+def test_fused_collective_wait_is_bounded():
+    """World of 2 emulated on one GPU with a peer that never signals: the kernel must give up after
+    its cycle budget, report status 4 (peer timeout) and leave the context usable."""
+    import ctypes
+    from litevllm_b200.ops import _lib
+    from litevllm_b200.parallel.symm import FiComm
+    T, N, K = 8, 128, 64
+    x = torch.randn(T, K, device=DEV).bfloat16()
+    w = torch.randn(N, K, device=DEV).bfloat16()
+    out = torch.zeros(T, N, device=DEV).bfloat16()
+    recv = torch.zeros(2 * 2 * T * N, device=DEV, dtype=torch.float32)
+    flags = torch.zeros(8192 * 8 * 8 // 64, device=DEV, dtype=torch.int32)   # tile 0 only is touched
+    ready = torch.zeros(64, device=DEV, dtype=torch.int32)
+    ctl = torch.zeros(64, device=DEV, dtype=torch.int32)
+    c = FiComm()
+    c.mode, c.world, c.rank, c.slab_elems = 1, 2, 0, T * N
+    for d in range(2):
+        c.recv[d], c.flags[d], c.ready[d] = recv.data_ptr(), flags.data_ptr(), ready.data_ptr()
+    c.epoch, c.done = ctl.data_ptr(), ctl.data_ptr() + 64
+    ops.status_word(x.device).zero_()
+    rc = _lib.kernels().fi_dense_gemm_comm(x.data_ptr(), w.data_ptr(), out.data_ptr(), None, None, T, N, K,
+                                           K, K, N, 0, 0, 0, 0, 1, 0, ops.status_word(x.device).data_ptr(),
+                                           torch.cuda.current_stream().cuda_stream, ctypes.byref(c))
+    assert rc == 0
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="status 4"):
+        ops.check_status(x.device)
+    # the context still works
+    y = ops.linear(x, w)
+    _close(y, ref.linear(x, w, out_dtype=torch.float32), 3e-2, 3e-2, "gemm after timeout")
