@@ -15,6 +15,8 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
+
+#include "../common/launch.cuh"
 #include <math_constants.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -151,6 +153,8 @@ __device__ __forceinline__ float softcap_f(float s, float cap) {
 // KV head (up to 16 per group).  Each warp owns 16 of the 64 tokens of a chunk.
 template <typename T, int HD>
 __global__ void __launch_bounds__(128) paged_decode_kernel(const AttnParams p) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
   constexpr int CH = 64;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   T* sQ = reinterpret_cast<T*>(smem_raw);        // [16][HD]
@@ -314,6 +318,8 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const AttnParams p) {
 
 template <typename T, int HD>
 __global__ void decode_merge_kernel(const AttnParams p) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
   const int b = blockIdx.y, head = blockIdx.x;
   const long base = (static_cast<long>(b) * p.nh + head) * p.splits;
   float m = -CUDART_INF_F;
@@ -336,6 +342,8 @@ __global__ void decode_merge_kernel(const AttnParams p) {
 // tile; KV streamed in CH-token chunks shared by the four warps.
 template <typename T, int HD, int CH>
 __global__ void __launch_bounds__(128) paged_prefill_kernel(const AttnParams p) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
   extern __shared__ __align__(128) uint8_t smem_raw[];
   T* sQ = reinterpret_cast<T*>(smem_raw);   // [64][HD]
   T* sK = sQ + 64 * HD;                     // [2][CH][HD]
@@ -484,8 +492,8 @@ int launch_decode(const AttnParams& p, int B, cudaStream_t s) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     cfg = true;
   }
-  kern<<<dim3(p.splits, p.nkv * groups, B), 128, smem, s>>>(p);
-  if (p.splits > 1) decode_merge_kernel<T, HD><<<dim3(p.nh, B), HD >= 128 ? 128 : 64, 0, s>>>(p);
+  fi::launch_kernel(kern, dim3(p.splits, p.nkv * groups, B), dim3(128), smem, s, 0, p);
+  if (p.splits > 1) fi::launch_kernel(decode_merge_kernel<T, HD>, dim3(p.nh, B), dim3(HD >= 128 ? 128 : 64), 0, s, 0, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -498,7 +506,7 @@ int launch_prefill(const AttnParams& p, int B, int max_q_len, cudaStream_t s) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     cfg = true;
   }
-  kern<<<dim3((max_q_len + 63) / 64, p.nh, B), 128, smem, s>>>(p);
+  fi::launch_kernel(kern, dim3((max_q_len + 63) / 64, p.nh, B), dim3(128), smem, s, 0, p);
   return static_cast<int>(cudaGetLastError());
 }
 

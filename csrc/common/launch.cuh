@@ -1,0 +1,53 @@
+// Programmatic dependent launch (PDL) helpers.
+//
+// Every kernel of the decode step is launched with the programmatic-stream-serialization attribute:
+// the next kernel's CTAs may be scheduled while the current kernel is still running, do their
+// set-up (barrier init, TMEM allocation, descriptor prefetch, weight prefetch) and then block in
+// `pdl_wait()` until the predecessor has completed and its writes are visible.  Each kernel calls
+// `pdl_launch_dependents()` early and `pdl_wait()` before it touches memory a predecessor wrote;
+// since every kernel waits, completion is transitive along the stream.  Works inside CUDA graphs.
+#pragma once
+#include <cuda_runtime.h>
+
+namespace fi {
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+#ifndef FI_NO_PDL
+constexpr bool kUsePdl = true;
+#else
+constexpr bool kUsePdl = false;
+#endif
+
+// Launch with optional cluster size along z and the PDL attribute.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, int cluster_z, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (cluster_z > 0) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 1;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = cluster_z;
+    ++n;
+  }
+  if (kUsePdl) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+}  // namespace fi

@@ -18,6 +18,7 @@
 //
 // Replaces the reference's Triton family vllm/kernels/triton/awq_fused_gemm.py (K10-K18: tiled
 // GEMM, split-K with atomics, M=1 GEMVs, fused QKV and fused gate-up variants) with one kernel.
+#include "../common/launch.cuh"
 #include "../common/tensormap.h"
 #include "comm_desc.h"
 #include "epilogue.cuh"
@@ -115,6 +116,8 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) pdl_launch_dependents();
+  if (warp != 0) pdl_wait();   // the producer waits later, after prefetching weight tiles
   const unsigned int epoch_now = (p.comm_mode != kCommNone || p.ag_world > 1) ? *p.epoch + 1u : 0u;
 
   if (warp == 0) {
@@ -125,11 +128,21 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const CUtensorMap* tmap_x_ptr = &tmaps_x.m[x_map];
       tma_prefetch_desc(&tmap_w);
       tma_prefetch_desc(tmap_x_ptr);
+      const int n_pre = min(RST, kb_end - kb_begin);
+      for (int it = 0; it < n_pre; ++it) {   // packed weights first: they do not depend on the previous kernel
+        uint8_t* r = raw_ring + it * RAW_BYTES;
+        mbar_expect_tx(&raw_full[it], RAW_BYTES);
+        tma_load_2d(r + B_BYTES, &tmap_w, &raw_full[it], (kb_begin + it) * 8, n0);
+        if (DUAL) tma_load_2d(r + B_BYTES + Q_BYTES, &tmap_w, &raw_full[it], (kb_begin + it) * 8, p.dual_rows + n0);
+      }
+      pdl_wait();
       if (!ag_handshake(p, x_map, epoch_now)) {
         set_status(p.status, kStatusTimeoutPeer);
         *aborted = 1;
       }
-      for (int kb = kb_begin; kb < kb_end; ++kb) {
+      for (int it = 0; it < n_pre; ++it)
+        tma_load_2d(raw_ring + it * RAW_BYTES, tmap_x_ptr, &raw_full[it], (kb_begin + it) * BK, x_row);
+      for (int kb = kb_begin + n_pre; kb < kb_end; ++kb) {
         const int it = kb - kb_begin;
         const int s = it % RST;
         const uint32_t ph = (it / RST) & 1;
@@ -313,19 +326,8 @@ int launch(const CUtensorMap& tw, const TokenMaps& tx, GemmParams p, cudaStream_
     p.splits = best;
   }
   if (BN * BM * 4 * ((DUAL && p.splits > 1) ? 2 : 1) > ring) return -12;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((p.N + BM - 1) / BM, (p.T + BN - 1) / BN, p.splits);
-  cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = p.splits;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, tw, tx, p));
+  return static_cast<int>(launch_kernel(kern, dim3((p.N + BM - 1) / BM, (p.T + BN - 1) / BN, p.splits),
+                                        dim3(kThreads), smem, stream, p.splits, tw, tx, p));
 }
 
 template <typename T, bool DUAL>

@@ -13,6 +13,7 @@
 // Replaces the library GEMM behind every unquantised linear of the reference
 // (vllm/model_executor/layers/lite_linear.py:60-62) and the silu-and-mul kernel
 // (vllm/kernels/triton/activation.py:42) that follows its gate/up projections.
+#include "../common/launch.cuh"
 #include "../common/tensormap.h"
 #include "comm_desc.h"
 #include "epilogue.cuh"
@@ -74,6 +75,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) pdl_launch_dependents();
+  if (warp != 0) pdl_wait();   // the producer waits later, after prefetching weight tiles
   const unsigned int epoch_now = (p.comm_mode != kCommNone || p.ag_world > 1) ? *p.epoch + 1u : 0u;
 
   if (warp == 0) {
@@ -84,11 +87,25 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const CUtensorMap* tmap_x_ptr = &tmaps_x.m[x_map];
       tma_prefetch_desc(&tmap_w);
       tma_prefetch_desc(tmap_x_ptr);
+      // Weights do not depend on the previous kernel: start streaming them for the first stages
+      // before blocking on the programmatic dependency, then add the token tiles.
+      const int n_pre = min(STAGES, kb_end - kb_begin);
+      for (int it = 0; it < n_pre; ++it) {
+        uint8_t* a = stage_base + it * STAGE_BYTES;
+        mbar_expect_tx(&full_bar[it], STAGE_BYTES);
+        tma_load_2d(a, &tmap_w, &full_bar[it], (kb_begin + it) * BK, n0);
+        if (DUAL) tma_load_2d(a + A_BYTES, &tmap_w, &full_bar[it], (kb_begin + it) * BK, p.dual_rows + n0);
+      }
+      pdl_wait();
       if (!ag_handshake(p, x_map, epoch_now)) {
         set_status(p.status, kStatusTimeoutPeer);
         *aborted = 1;
       }
-      for (int kb = kb_begin; kb < kb_end; ++kb) {
+      for (int it = 0; it < n_pre; ++it) {
+        uint8_t* a = stage_base + it * STAGE_BYTES;
+        tma_load_2d(a + A_BYTES * (DUAL ? 2 : 1), tmap_x_ptr, &full_bar[it], (kb_begin + it) * BK, x_row);
+      }
+      for (int kb = kb_begin + n_pre; kb < kb_end; ++kb) {
         const int it = kb - kb_begin;
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
@@ -214,19 +231,8 @@ int launch(const CUtensorMap& tw, const TokenMaps& tx, GemmParams p, cudaStream_
   }
   if (p.splits <= 0) p.splits = pick_splits<BN, STAGES, DUAL>(p, smem);
   if (BN * BM * 4 * ((DUAL && p.splits > 1) ? 2 : 1) > ring) return -12;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((p.N + BM - 1) / BM, (p.T + BN - 1) / BN, p.splits);
-  cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = p.splits;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, tw, tx, p));
+  return static_cast<int>(launch_kernel(kern, dim3((p.N + BM - 1) / BM, (p.T + BN - 1) / BN, p.splits),
+                                        dim3(kThreads), smem, stream, p.splits, tw, tx, p));
 }
 
 template <bool DUAL>

@@ -12,6 +12,8 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
+
+#include "../common/launch.cuh"
 #include <stdint.h>
 
 namespace {
@@ -61,6 +63,8 @@ template <typename T, bool WARP_ROWS>
 __global__ void rmsnorm_kernel(const T* __restrict__ x, T* __restrict__ residual,
                                const T* __restrict__ w, T* __restrict__ out, int rows, int H,
                                long ldx, long ldo, float eps, int w_mode, float out_scale) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
   __shared__ float red[32];
   constexpr int V = 16 / sizeof(T);
   int row, tid, nthr;
@@ -134,6 +138,8 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   const T* __restrict__ kw, int T_tokens, int nh, int nkv, int hd,
                                   int rot_dim, int block_size, int kv_fp8, float k_scale,
                                   float v_scale, float eps, int qk_norm_mode, int v_norm) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nwarps = blockDim.x >> 5;
@@ -220,6 +226,8 @@ __global__ void reshape_and_cache_kernel(const T* __restrict__ k, const T* __res
                                          void* __restrict__ k_cache, void* __restrict__ v_cache,
                                          long ldk, long ldv, int nkv, int hd, int block_size,
                                          int kv_fp8, float k_scale, float v_scale) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
   const int t = blockIdx.x;
   const int slot = slot_mapping[t];
   if (slot < 0) return;
@@ -244,6 +252,8 @@ template <typename T>
 __global__ void embedding_kernel(const long* __restrict__ ids, const T* __restrict__ table,
                                  T* __restrict__ out, int H, float scale, int vocab_start,
                                  int vocab_end) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
   constexpr int V = 16 / sizeof(T);
   const long id = ids[blockIdx.x];
   T* o = out + static_cast<long>(blockIdx.x) * H;
@@ -267,6 +277,8 @@ __global__ void embedding_kernel(const long* __restrict__ ids, const T* __restri
 template <typename T>
 __global__ void act_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int d, long ldx,
                                int act) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
   const long r = blockIdx.x;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     const float g = Cvt<T>::to_f(x[r * ldx + i]);
@@ -287,6 +299,8 @@ __global__ void slot_mapping_kernel(const int* __restrict__ positions,
                                     const int* __restrict__ token_seq,
                                     const int* __restrict__ block_tables, int max_blocks, int bs,
                                     int* __restrict__ slots, int T) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= T) return;
   const int pos = positions[t];
@@ -301,6 +315,8 @@ __global__ void slot_mapping_kernel(const int* __restrict__ positions,
 template <typename T>
 __global__ void argmax_kernel(const T* __restrict__ logits, long ld, int V, long* __restrict__ out,
                               float softcap) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
   __shared__ float sv[32];
   __shared__ int si[32];
   const T* row = logits + static_cast<long>(blockIdx.x) * ld;
@@ -355,13 +371,13 @@ extern "C" int fi_rmsnorm(const void* x, void* residual, const void* w, void* ou
     using T = std::remove_pointer_t<decltype(tag)>;
     if (H <= 1024) {
       const int wpb = 4;
-      rmsnorm_kernel<T, true><<<(rows + wpb - 1) / wpb, wpb * 32, 0, FI_STREAM(stream)>>>(
+      fi::launch_kernel(rmsnorm_kernel<T, true>, dim3((rows + wpb - 1) / wpb), dim3(wpb * 32), 0, FI_STREAM(stream), 0, 
           (const T*)x, (T*)residual, (const T*)w, (T*)out, rows, H, ldx, ldo, eps, w_mode,
           out_scale);
     } else {
       int threads = H / 8;
       threads = threads > 1024 ? 1024 : ((threads + 31) / 32) * 32;
-      rmsnorm_kernel<T, false><<<rows, threads, 0, FI_STREAM(stream)>>>(
+      fi::launch_kernel(rmsnorm_kernel<T, false>, dim3(rows), dim3(threads), 0, FI_STREAM(stream), 0, 
           (const T*)x, (T*)residual, (const T*)w, (T*)out, rows, H, ldx, ldo, eps, w_mode,
           out_scale);
     }
@@ -380,7 +396,7 @@ extern "C" int fi_rope_cache(void* qkv, const int* positions, const float* cos_s
     using Tt = std::remove_pointer_t<decltype(tag)>;
     int warps = nh + 2 * nkv;
     if (warps > 16) warps = 16;
-    rope_cache_kernel<Tt><<<T, warps * 32, 0, FI_STREAM(stream)>>>(
+    fi::launch_kernel(rope_cache_kernel<Tt>, dim3(T), dim3(warps * 32), 0, FI_STREAM(stream), 0, 
         (Tt*)qkv, positions, cos_sin, freq_stream, slot_mapping, k_cache, v_cache, (const Tt*)qw,
         (const Tt*)kw, T, nh, nkv, hd, rot_dim, block_size, kv_fp8, k_scale, v_scale, eps,
         qk_norm_mode, v_norm);
@@ -395,7 +411,7 @@ extern "C" int fi_reshape_and_cache(const void* k, const void* v, const int* slo
   if (T <= 0) return 0;
   return dispatch_dtype(dtype, [&](auto* tag) {
     using Tt = std::remove_pointer_t<decltype(tag)>;
-    reshape_and_cache_kernel<Tt><<<T, 256, 0, FI_STREAM(stream)>>>(
+    fi::launch_kernel(reshape_and_cache_kernel<Tt>, dim3(T), dim3(256), 0, FI_STREAM(stream), 0, 
         (const Tt*)k, (const Tt*)v, slot_mapping, k_cache, v_cache, ldk, ldv, nkv, hd, block_size,
         kv_fp8, k_scale, v_scale);
     return static_cast<int>(cudaGetLastError());
@@ -409,7 +425,7 @@ extern "C" int fi_embedding(const long* ids, const void* table, void* out, int T
   return dispatch_dtype(dtype, [&](auto* tag) {
     using Tt = std::remove_pointer_t<decltype(tag)>;
     int threads = H / 8 > 256 ? 256 : ((H / 8 + 31) / 32) * 32;
-    embedding_kernel<Tt><<<T, threads, 0, FI_STREAM(stream)>>>(
+    fi::launch_kernel(embedding_kernel<Tt>, dim3(T), dim3(threads), 0, FI_STREAM(stream), 0, 
         ids, (const Tt*)table, (Tt*)out, H, scale, vocab_start, vocab_end);
     return static_cast<int>(cudaGetLastError());
   });
@@ -420,7 +436,7 @@ extern "C" int fi_act_mul(const void* x, void* out, int rows, int d, long ldx, i
   if (rows <= 0) return 0;
   return dispatch_dtype(dtype, [&](auto* tag) {
     using Tt = std::remove_pointer_t<decltype(tag)>;
-    act_mul_kernel<Tt><<<rows, 256, 0, FI_STREAM(stream)>>>((const Tt*)x, (Tt*)out, d, ldx, act);
+    fi::launch_kernel(act_mul_kernel<Tt>, dim3(rows), dim3(256), 0, FI_STREAM(stream), 0, (const Tt*)x, (Tt*)out, d, ldx, act);
     return static_cast<int>(cudaGetLastError());
   });
 }
@@ -428,7 +444,7 @@ extern "C" int fi_act_mul(const void* x, void* out, int rows, int d, long ldx, i
 extern "C" int fi_slot_mapping(const int* positions, const int* token_seq, const int* block_tables,
                                int max_blocks, int bs, int* slots, int T, void* stream) {
   if (T <= 0) return 0;
-  slot_mapping_kernel<<<(T + 255) / 256, 256, 0, FI_STREAM(stream)>>>(
+  fi::launch_kernel(slot_mapping_kernel, dim3((T + 255) / 256), dim3(256), 0, FI_STREAM(stream), 0, 
       positions, token_seq, block_tables, max_blocks, bs, slots, T);
   return static_cast<int>(cudaGetLastError());
 }
@@ -438,12 +454,12 @@ extern "C" int fi_argmax(const void* logits, long ld, int rows, int V, long* out
                          void* stream) {
   if (rows <= 0) return 0;
   if (dtype == 2) {
-    argmax_kernel<float><<<rows, 1024, 0, FI_STREAM(stream)>>>((const float*)logits, ld, V, out, 0.f);
+    fi::launch_kernel(argmax_kernel<float>, dim3(rows), dim3(1024), 0, FI_STREAM(stream), 0, (const float*)logits, ld, V, out, 0.f);
   } else if (dtype == 0) {
-    argmax_kernel<__nv_bfloat16><<<rows, 1024, 0, FI_STREAM(stream)>>>(
+    fi::launch_kernel(argmax_kernel<__nv_bfloat16>, dim3(rows), dim3(1024), 0, FI_STREAM(stream), 0, 
         (const __nv_bfloat16*)logits, ld, V, out, 0.f);
   } else {
-    argmax_kernel<__half><<<rows, 1024, 0, FI_STREAM(stream)>>>((const __half*)logits, ld, V, out,
+    fi::launch_kernel(argmax_kernel<__half>, dim3(rows), dim3(1024), 0, FI_STREAM(stream), 0, (const __half*)logits, ld, V, out,
                                                                  0.f);
   }
   return static_cast<int>(cudaGetLastError());

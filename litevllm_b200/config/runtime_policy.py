@@ -20,3 +20,4 @@ class BackendRuntimePolicy:
     gpu_greedy_max_tokens_only: bool = True
     gpu_greedy_ignore_eos: bool = False
     cuda_graph_decode: bool = True
+    async_decode: bool = True                 # pipelined decode: launch step k+1 before reading step k

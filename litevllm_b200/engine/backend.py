@@ -36,6 +36,9 @@ class LiteGpuBackend:
         self.lora_registry = lora_registry
         self.on_release = on_release
         self.greedy_device_steps = 0
+        self.pipeline = None
+        self.pipelined_steps = 0
+        self.async_decode = getattr(backend_policy, "async_decode", True)
 
     # ------------------------------------------------------------------ KV growth
     def ensure_kv_blocks(self, plan: StepPlan) -> None:
@@ -86,7 +89,7 @@ class LiteGpuBackend:
         if not plan.prefills:
             return []
         states = self.scheduler.requests
-        outs = []
+        outs = self.drain_pipeline()
         # exact prefix hits sample their first token from the cached logits without a forward pass
         items = []
         for it in plan.prefills:
@@ -127,13 +130,90 @@ class LiteGpuBackend:
         self.observer.on_prefill_executed(len(items), sum(i.chunk_len for i in items), time.perf_counter() - t0)
         return outs
 
+    # ------------------------------------------------------------------ pipelined decode
+    def _pipeline_ok(self, reqs, plan: StepPlan) -> bool:
+        ex = self.decode_executor
+        if not self.async_decode or not hasattr(ex, "replay_or_capture") or ex.builder.device.type != "cuda":
+            return False
+        if hasattr(ex.model, "prepare_batch") or plan.prefills:
+            return False
+        from .decode_pipeline import DecodePipeline
+        return all(DecodePipeline.eligible(st) for st in reqs)
+
+    def _consume_tokens(self, reqs, tokens, outs: list) -> bool:
+        """Feed one step's tokens to the output pipeline; returns True if any request finished."""
+        any_finished = False
+        for st, tok in zip(reqs, tokens):
+            if st.finished or st.request_id not in self.scheduler.requests:
+                continue
+            out = self._process_completion(st, int(tok))
+            if out is not None:
+                outs.append(out)
+                any_finished |= out.finished
+        return any_finished
+
+    def drain_pipeline(self) -> list:
+        """Collect every in-flight step (used when the request set is about to change)."""
+        outs: list = []
+        pipe = self.pipeline
+        if pipe is None or not pipe.active:
+            return outs
+        reqs = list(pipe.reqs)
+        while pipe.inflight:
+            self._consume_tokens(reqs, pipe.collect_oldest(), outs)
+        pipe.stop()
+        return outs
+
+    def _run_decodes_pipelined(self, reqs) -> list:
+        from .decode_pipeline import DecodePipeline
+        if self.pipeline is None:
+            self.pipeline = DecodePipeline(self.decode_executor, self.decode_executor.builder, self.kv)
+        pipe = self.pipeline
+        outs: list = []
+        key = tuple(st.request_id for st in reqs)
+        if pipe.active and pipe.key != key:
+            outs += self.drain_pipeline()
+            reqs = [st for st in reqs if not st.finished and st.request_id in self.scheduler.requests]
+            if not reqs:
+                return outs
+        if not pipe.active:
+            for st in reqs:
+                self._flush_pending(st)
+            pipe.start(reqs)
+        if pipe.can_launch():
+            pipe.launch()
+            self.pipelined_steps += 1
+            # keep one step in flight: look at the step before the one just launched
+            if len(pipe.inflight) > 1:
+                if self._consume_tokens(pipe.reqs, pipe.collect_oldest(), outs):
+                    outs += self.drain_pipeline()
+        else:
+            outs += self.drain_pipeline()
+        return outs
+
     def run_decodes(self, plan: StepPlan) -> list:
         if not plan.decodes:
+            if self.pipeline is not None and self.pipeline.active:
+                return self.drain_pipeline()
             return []
         states = self.scheduler.requests
         reqs = [states[r] for r in plan.decodes if r in states and not states[r].finished]
         if not reqs:
             return []
+        if self._pipeline_ok(reqs, plan):
+            t0 = time.perf_counter()
+            outs = self._run_decodes_pipelined(reqs)
+            self.observer.on_decode_executed(len(reqs), time.perf_counter() - t0)
+            return outs
+        if self.pipeline is not None and self.pipeline.active:
+            pre = self.drain_pipeline()
+            reqs = [st for st in reqs if not st.finished and st.request_id in states]
+            if not reqs:
+                return pre
+            return pre + self._run_decodes_sync(reqs, states)
+        return self._run_decodes_sync(reqs, states)
+
+    def _run_decodes_sync(self, reqs, states) -> list:
         t0 = time.perf_counter()
         try:
             on_device = all(st.last_token_tensor is not None for st in reqs)
@@ -209,6 +289,10 @@ class LiteGpuBackend:
         self.release_request(st.request_id)
 
     def release_request(self, request_id: str) -> None:
+        pipe = self.pipeline
+        if pipe is not None and pipe.active and request_id in pipe.key and pipe.inflight:
+            # an in-flight step still writes this request's KV blocks: let it finish first
+            torch.cuda.current_stream().synchronize()
         self.kv.release(request_id)
         st = self.scheduler.release(request_id)
         if st is not None and self.on_release is not None:
@@ -216,6 +300,7 @@ class LiteGpuBackend:
 
     def stats(self) -> dict:
         return {"kv": self.kv.stats(), "greedy_device_steps": self.greedy_device_steps,
+                "pipelined_decode_steps": self.pipelined_steps,
                 "graph_replays": getattr(self.decode_executor, "graph_replays", 0),
                 "eager_decode_steps": getattr(self.decode_executor, "eager_steps", 0),
                 "prefix_cache": self.prefix_cache.stats() if self.prefix_cache else {"enabled": False},

@@ -121,5 +121,26 @@ class DecodeExecutor:
         ops.check_status(self.builder.device)
         return graph, out, full_ctx
 
+    @torch.inference_mode()
+    def replay_or_capture(self, bucket: int, reqs: list[RequestState], max_kv_len: int) -> torch.Tensor:
+        """Run the decode forward on the persistent bucket buffers (already filled by the caller)
+        and return the logits tensor ``[bucket, vocab]``."""
+        d = self.builder._decode_buffers(bucket)
+        batch = ForwardBatch(
+            input_ids=d["ids"], positions=d["meta"][0], slot_mapping=d["meta"][1], block_tables=d["block_tables"],
+            seq_lens=d["meta"][2], cu_q=None, logits_indices=None, num_seqs=bucket, num_tokens=bucket, max_q_len=1,
+            max_kv_len=max_kv_len, is_decode=True, config=self.builder.cfg,
+            request_ids=[st.request_id for st in reqs], extras={"num_real": len(reqs), "bucket": bucket})
+        if not self.use_cuda_graph:
+            self.eager_steps += 1
+            return self._run(batch)
+        entry = self._graphs.get(bucket)
+        if entry is None:
+            entry = self._capture(batch)
+            self._graphs[bucket] = entry
+        entry[0].replay()
+        self.graph_replays += 1
+        return entry[1]
+
     def execute_sync_fast(self, st: RequestState, device_tokens=None) -> LogitsResult:
         return self.execute_batch([st], device_tokens=device_tokens)

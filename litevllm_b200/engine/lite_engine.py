@@ -198,6 +198,7 @@ class LiteEngine:
         return self.scheduler.has_unfinished()
 
     # ------------------------------------------------------------------ stepping
+    @torch.inference_mode()
     def step(self) -> list:
         with self.lock:
             if self.fatal_error is not None:

@@ -1,0 +1,193 @@
+"""Control-plane units with hand-rolled fakes (no GPU, no model)."""
+import asyncio
+import time
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from litevllm_b200.config.runtime_policy import SchedulerRuntimePolicy
+from litevllm_b200.engine.block_allocator import BlockAllocator
+from litevllm_b200.engine.errors import InvalidRequestError, RequestRejectedError
+from litevllm_b200.engine.kv_block_manager import KVBlockManager
+from litevllm_b200.engine.kv_cache import FlatKVCache, KVLayerSpec
+from litevllm_b200.engine.planners import AdmissionPlanner, BudgetComputer, DecodePrefillPlanner
+from litevllm_b200.engine.prefix_cache import PrefixCache
+from litevllm_b200.engine.request_scheduler import RequestScheduler
+from litevllm_b200.engine.request_state import RequestState
+from litevllm_b200.engine.step_plan import PrefillItem, StepPlan
+from litevllm_b200.engine.step_scheduler import StepScheduler
+from litevllm_b200.sampling_params import SamplingParams
+
+
+def _req(rid, n_prompt=10, **kw):
+    return RequestState(request_id=rid, prompt=None, prompt_token_ids=list(range(1, n_prompt + 1)),
+                        sampling_params=SamplingParams(**kw))
+
+
+# ----------------------------------------------------------------------------- block allocator
+def test_block_allocator_reserves_null_block_and_detects_double_free():
+    a = BlockAllocator(5)
+    got = a.allocate(4)
+    assert sorted(got) == [1, 2, 3, 4] and a.num_free == 0
+    with pytest.raises(MemoryError):
+        a.allocate(1)
+    a.free([2, 0])            # freeing the null block is a no-op
+    assert a.num_free == 1
+    with pytest.raises(ValueError):
+        a.free([2])
+    assert a.allocate(1) == [2]
+
+
+def test_flat_kv_cache_views_do_not_overlap():
+    specs = [KVLayerSpec(2, 64), KVLayerSpec(1, 128)]
+    kv = FlatKVCache(specs, num_blocks=4, block_size=16, dtype=torch.float32, device=torch.device("cpu"))
+    for i, (k, v) in enumerate(kv.layers):
+        k.fill_(i + 1)
+        v.fill_(-(i + 1))
+    for i, (k, v) in enumerate(kv.layers):
+        assert float(k.min()) == float(k.max()) == i + 1
+        assert float(v.min()) == float(v.max()) == -(i + 1)
+    assert kv.layers[0][0].shape == (4, 2, 16, 64) and kv.layers[1][0].shape == (4, 1, 16, 128)
+
+
+def test_kv_block_manager_grows_and_releases():
+    alloc = BlockAllocator(1 + 2 * 4)
+    m = KVBlockManager(alloc, 16, max_active=2, blocks_per_seq=4, device=torch.device("cpu"))
+    m.register("a", 0)
+    assert m.ensure_blocks("a", 1) and len(m.blocks_of("a")) == 1
+    assert m.ensure_blocks("a", 16) == []          # still one block
+    assert len(m.ensure_blocks("a", 17)) == 1
+    m.flush()
+    assert m.block_tables[0, :2].tolist() == m.blocks_of("a") and m.block_tables[0, 2:].sum() == 0
+    with pytest.raises(ValueError):
+        m.ensure_blocks("a", 16 * 4 + 1)
+    m.release("a")
+    m.release("a")                                  # idempotent
+    m.flush()
+    assert alloc.num_free == 8 and int(m.block_tables.sum()) == 0
+
+
+# ----------------------------------------------------------------------------- request scheduler
+def test_scheduler_fifo_slots_and_capacity():
+    s = RequestScheduler(max_active=2, queue_capacity=3)
+    for i in range(3):
+        s.enqueue_request(_req(f"r{i}"))
+    with pytest.raises(RequestRejectedError):
+        s.enqueue_request(_req("r3"))
+    with pytest.raises(InvalidRequestError):
+        s.enqueue_request(_req("r0"))
+    a = s.admit("r0")
+    b = s.admit("r1")
+    assert {a.slot_idx, b.slot_idx} == {0, 1} and not s.free_slots
+    a.is_prefill = False
+    pre, dec = s.classify_requests()
+    assert [r.request_id for r in pre] == ["r1"] and [r.request_id for r in dec] == ["r0"]
+    assert s.release("r0") is not None and s.release("r0") is None
+    assert list(s.free_slots) == [0]
+    assert s.gauges()["queued"] == 1
+
+
+def test_scheduler_queue_timeout_expires_oldest_first():
+    s = RequestScheduler(max_active=1, queue_timeout_s=10.0)
+    old, new = _req("old"), _req("new")
+    old.arrival_time -= 11.0
+    s.enqueue_request(old)
+    s.enqueue_request(new)
+    expired = s.expire_queued()
+    assert [e.request_id for e in expired] == ["old"] and list(s.queued) == ["new"]
+
+
+def test_stream_gets_exactly_one_terminal_item():
+    async def run():
+        s = RequestScheduler(max_active=1)
+        loop = asyncio.get_running_loop()
+        s.enqueue_request(_req("x"), loop)
+        s.publish_output("x", SimpleNamespace(finished=False, n=1))
+        s.publish_output("x", SimpleNamespace(finished=True, n=2))
+        s.publish_output("x", SimpleNamespace(finished=True, n=3))     # ignored: already terminal
+        s.publish_output("x", RuntimeError("late"))                     # ignored too
+        got = [o.n async for o in s.get_request_stream("x")]
+        return got
+    assert asyncio.run(run()) == [1, 2]
+
+
+def test_stream_raises_published_exception():
+    async def run():
+        s = RequestScheduler(max_active=1)
+        s.enqueue_request(_req("x"), asyncio.get_running_loop())
+        s.publish_output("x", RequestRejectedError("nope", "queue_timeout"))
+        with pytest.raises(RequestRejectedError):
+            async for _ in s.get_request_stream("x"):
+                pass
+    asyncio.run(run())
+
+
+# ----------------------------------------------------------------------------- planners
+def test_admission_is_fifo_and_capped():
+    p = AdmissionPlanner(2)
+    assert p.plan(["a", "b", "c"], free_slots=5) == ["a", "b"]
+    assert p.plan(["a", "b", "c"], free_slots=1) == ["a"]
+    assert p.plan([], free_slots=3) == []
+
+
+def test_budget_decode_priority_and_catchup():
+    b = BudgetComputer(1000, decode_priority=True, catchup_ratio=0.25, reserve_backlog=2, min_chunk=64)
+    r = b.compute(n_decode=10, n_prefill=1, backlog=1, force_prefill=False)
+    assert r.decode_tokens == 10 and r.prefill_tokens == 250
+    r = b.compute(10, 1, backlog=4, force_prefill=False)        # backlog above the reserve: larger share
+    assert r.prefill_tokens == 750
+    r = b.compute(10, 1, 1, force_prefill=True)
+    assert r.prefill_tokens == 990 and r.starvation_override
+    r = b.compute(0, 2, 2, False)
+    assert r.prefill_tokens == 1000
+
+
+def test_prefill_plan_is_varlen_and_respects_budget():
+    p = DecodePrefillPlanner(chunk_size=64, microbatch=3, min_chunk=16)
+    a, b, c = _req("a", 100), _req("b", 30), _req("c", 500)
+    a.seq_len = 64                                   # already processed one chunk
+    items = p.build_prefill_plan([a, b, c], budget_tokens=90)
+    assert [(i.request_id, i.start, i.chunk_len) for i in items] == [("a", 64, 36), ("b", 0, 30), ("c", 0, 24)]
+    assert p.build_decode_plan([a, b, c], 2) == ["a", "b"]
+    v = DecodePrefillPlanner(64, 2, verified_decode_batch_sizes=(1, 4))
+    assert v.build_decode_plan([a, b, c], 10) == ["a"]
+
+
+def test_step_scheduler_fast_path_and_starvation_guard():
+    s = RequestScheduler(max_active=4)
+    ss = StepScheduler(step_token_budget=256, prefill_chunk_size=64, prefill_microbatch=1,
+                       policy=SchedulerRuntimePolicy(max_decode_streak=2, max_prefill_deferrals=10),
+                       catchup_ratio=0.0, min_chunk=1, max_active=4)
+    d = _req("d")
+    s.enqueue_request(d)
+    s.admit("d")
+    d.is_prefill = False
+    plan = ss.build_plan(s)
+    assert plan.fast_path and plan.decodes == ["d"]
+    # a long prompt arrives; with a zero catch-up share the prefill only gets min_chunk tokens
+    s.enqueue_request(_req("p", 200))
+    plan = ss.build_plan(s)
+    assert plan.admissions == ["p"] and plan.decodes == ["d"] and plan.prefills[0].chunk_len >= 1
+    wire = StepPlan.from_wire(plan.to_wire())
+    assert wire.decodes == plan.decodes and wire.prefills[0].chunk_len == plan.prefills[0].chunk_len
+
+
+# ----------------------------------------------------------------------------- prefix cache
+def test_prefix_cache_longest_match_lru_and_budget():
+    pc = PrefixCache(max_entries=2, max_bytes=10_000)
+    blocks = [(torch.zeros(2, 4), torch.zeros(2, 4))]
+    a = _req("a", 48)
+    pc.store(a, 32, blocks)
+    pc.store(a, 16, blocks)
+    hit = pc.lookup(_req("b", 40))
+    assert hit is not None and hit.num_tokens == 32
+    other = _req("c", 20)
+    other.prompt_token_ids = [9] * 20
+    assert pc.lookup(other) is None
+    pc.store(other, 16, blocks)                      # evicts the least recently used entry
+    assert pc.stats()["entries"] == 2 and pc.stats()["evictions"] == 1
+    big = PrefixCache(max_entries=4, max_bytes=8)
+    big.store(a, 16, blocks)                         # larger than the byte budget: not stored
+    assert big.stats()["entries"] == 0
+    assert not PrefixCache(0).enabled
