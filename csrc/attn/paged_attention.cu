@@ -316,6 +316,234 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const AttnParams p) {
   }
 }
 
+// ------------------------------------------------------------------------------ decode, v2
+// Same math and grid as paged_decode_kernel, different data movement: every warp runs its OWN
+// multi-stage cp.async pipeline over 16-token groups (one KV block slice each), so the main loop has
+// no CTA-wide barrier and each SM keeps tens of KB of KV reads in flight.  Block-table entries are
+// fetched 32 groups at a time into registers and handed out by shuffle.  Needs block_size % 16 == 0.
+template <typename T, int HD, int NST>
+__global__ void __launch_bounds__(128) paged_decode_v2_kernel(const AttnParams p) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  constexpr int TILE = 16 * HD;                      // elements of one 16-token tile
+  T* sQ = reinterpret_cast<T*>(smem_raw);            // [16][HD]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool fp8 = p.kv_fp8 != 0;
+  // per-warp regions: raw K/V stages (+ conversion tiles when the cache is fp8)
+  const int raw_tile_bytes = fp8 ? TILE : TILE * 2;
+  const int warp_bytes = NST * 2 * raw_tile_bytes + (fp8 ? 2 * TILE * 2 : 0);
+  uint8_t* wbase = smem_raw + 16 * HD * 2 + warp * warp_bytes;
+  uint8_t* rawK = wbase;
+  uint8_t* rawV = wbase + NST * raw_tile_bytes;
+  T* convK = reinterpret_cast<T*>(wbase + NST * 2 * raw_tile_bytes);
+  T* convV = convK + TILE;
+
+  const int split = blockIdx.x;
+  const int G = p.nh / p.nkv;
+  const int groups = (G + 15) / 16;
+  const int kvh = blockIdx.y / groups;
+  const int grp = blockIdx.y % groups;
+  const int b = blockIdx.z;
+  const int heads_here = min(16, G - grp * 16);
+  const int head0 = kvh * G + grp * 16;
+  const int seq_len = p.seq_lens[b];
+  const int* bt = p.block_tables + static_cast<long>(b) * p.max_blocks;
+  const int lo = p.window > 0 ? max(0, seq_len - p.window) : 0;
+  // 16-token groups of this CTA: [g_begin, g_end), dealt round-robin to the four warps
+  const int first_g = lo / 16;
+  const int n_groups = (seq_len + 15) / 16 - first_g;
+  const int per = ((n_groups + p.splits - 1) / p.splits + 3) / 4 * 4;
+  const int g_begin = first_g + split * per;
+  const int g_end = min(first_g + n_groups, g_begin + per);
+  const int my_n = (g_end - g_begin - warp + 3) / 4;   // groups of this warp (may be <= 0)
+
+  for (int i = threadIdx.x; i < 16 * (HD / 8); i += 128) {
+    const int r = i / (HD / 8), c = i % (HD / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < heads_here)
+      v = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.q) + static_cast<long>(b) * p.q_stride +
+                                          static_cast<long>(head0 + r) * HD + c * 8);
+    *reinterpret_cast<uint4*>(sQ + tile_off<HD>(r, c)) = v;
+  }
+  __syncthreads();
+
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+  const float scale = p.sm_scale * (fp8 ? p.k_scale : 1.f);
+  const int bpb = p.block_size / 16;                 // 16-token groups per KV block
+
+  int bt_reg = 0;
+  auto refill_bt = [&](int k0) {   // block ids of this warp's groups k0 .. k0+31
+    const int g = g_begin + warp + 4 * (k0 + lane);
+    bt_reg = (k0 + lane < my_n) ? bt[g / bpb] : 0;
+  };
+  auto issue = [&](int k) {        // start loading this warp's k-th group into stage k % NST
+    if (k < my_n) {
+      const int g = g_begin + warp + 4 * k;
+      const int blk = __shfl_sync(0xffffffffu, bt_reg, k & 31);
+      const long base = ((static_cast<long>(blk) * p.nkv + kvh) * p.block_size + (g % bpb) * 16) * HD;
+      const int st = k % NST;
+      if (!fp8) {
+        const T* ksrc = reinterpret_cast<const T*>(p.k_cache) + base;
+        const T* vsrc = reinterpret_cast<const T*>(p.v_cache) + base;
+        T* kd = reinterpret_cast<T*>(rawK + st * raw_tile_bytes);
+        T* vd = reinterpret_cast<T*>(rawV + st * raw_tile_bytes);
+#pragma unroll
+        for (int i = lane; i < 16 * (HD / 8); i += 32) {
+          const int r = i / (HD / 8), c = i % (HD / 8);
+          cp_async16(kd + tile_off<HD>(r, c), ksrc + i * 8, true);
+          cp_async16(vd + tile_off<HD>(r, c), vsrc + i * 8, true);
+        }
+      } else {
+        const uint8_t* ksrc = reinterpret_cast<const uint8_t*>(p.k_cache) + base;
+        const uint8_t* vsrc = reinterpret_cast<const uint8_t*>(p.v_cache) + base;
+#pragma unroll
+        for (int i = lane; i < 16 * (HD / 16); i += 32) {   // linear copy of the raw bytes
+          cp_async16(rawK + st * raw_tile_bytes + i * 16, ksrc + i * 16, true);
+          cp_async16(rawV + st * raw_tile_bytes + i * 16, vsrc + i * 16, true);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+
+  if (my_n > 0) refill_bt(0);
+#pragma unroll
+  for (int k = 0; k < NST - 1; ++k) issue(k);
+  for (int k = 0; k < my_n; ++k) {
+    if (((k + NST - 1) & 31) == 0 && k + NST - 1 < my_n) refill_bt(k + NST - 1);
+    issue(k + NST - 1);
+    cp_async_wait<NST - 1>();
+    __syncwarp();
+    const int st = k % NST;
+    const T* K;
+    const T* V;
+    if (!fp8) {
+      K = reinterpret_cast<const T*>(rawK + st * raw_tile_bytes);
+      V = reinterpret_cast<const T*>(rawV + st * raw_tile_bytes);
+    } else {
+      // expand the raw e4m3 bytes of this group into swizzled 16-bit tiles
+      for (int i = lane; i < 16 * (HD / 16); i += 32) {
+        const int r = i / (HD / 16), c = i % (HD / 16);
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          const uint4 raw = *reinterpret_cast<const uint4*>((which ? rawV : rawK) + st * raw_tile_bytes + i * 16);
+          const __nv_fp8_e4m3* f8 = reinterpret_cast<const __nv_fp8_e4m3*>(&raw);
+          T tmp[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) tmp[j] = MmaT<T>::from_f(static_cast<float>(f8[j]));
+          T* dst = which ? convV : convK;
+          *reinterpret_cast<uint4*>(dst + tile_off<HD>(r, 2 * c)) = *reinterpret_cast<uint4*>(&tmp[0]);
+          *reinterpret_cast<uint4*>(dst + tile_off<HD>(r, 2 * c + 1)) = *reinterpret_cast<uint4*>(&tmp[8]);
+        }
+      }
+      __syncwarp();
+      K = convK;
+      V = convV;
+    }
+    const int tok_base = (g_begin + warp + 4 * k) * 16;
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      uint32_t a[4], kb[4];
+      ldsm_x4(a, smem_addr(sQ + tile_off<HD>((lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4))));
+      ldsm_x4(kb, smem_addr(K + tile_off<HD>((lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1))));
+      MmaT<T>::mma(s[0], a, kb);
+      MmaT<T>::mma(s[1], a, kb + 2);
+    }
+    float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int tok = tok_base + j * 8 + (lane & 3) * 2 + (e & 1);
+        float v = softcap_f(s[j][e] * scale, p.softcap);
+        if (tok >= seq_len || tok < lo) v = -CUDART_INF_F;
+        s[j][e] = v;
+        if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float nm0 = fmaxf(m0, mx0), nm1 = fmaxf(m1, mx1);
+    const float a0 = nm0 == -CUDART_INF_F ? 1.f : exp2f((m0 - nm0) * kLog2e);
+    const float a1 = nm1 == -CUDART_INF_F ? 1.f : exp2f((m1 - nm1) * kLog2e);
+    float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float nm = e < 2 ? nm0 : nm1;
+        // tokens past seq_len inside a valid block hold stale cache data: their weight is exactly 0
+        const float pv = nm == -CUDART_INF_F ? 0.f : exp2f((s[j][e] - nm) * kLog2e);
+        s[j][e] = pv;
+        if (e < 2) rs0 += pv; else rs1 += pv;
+      }
+    }
+    l0 = l0 * a0 + rs0; l1 = l1 * a1 + rs1; m0 = nm0; m1 = nm1;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) { o[i][0] *= a0; o[i][1] *= a0; o[i][2] *= a1; o[i][3] *= a1; }
+    uint32_t pa[4] = {MmaT<T>::pack(s[0][0], s[0][1]), MmaT<T>::pack(s[0][2], s[0][3]),
+                      MmaT<T>::pack(s[1][0], s[1][1]), MmaT<T>::pack(s[1][2], s[1][3])};
+#pragma unroll
+    for (int dp = 0; dp < HD / 16; ++dp) {
+      uint32_t vb[4];
+      ldsm_x4_t(vb, smem_addr(V + tile_off<HD>((lane & 7) + ((lane >> 3) & 1) * 8, dp * 2 + (lane >> 4))));
+      MmaT<T>::mma(o[2 * dp], pa, vb);
+      MmaT<T>::mma(o[2 * dp + 1], pa, vb + 2);
+    }
+    __syncwarp();
+  }
+  cp_async_wait<0>();
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  __syncthreads();
+  float* mO = reinterpret_cast<float*>(smem_raw + 16 * HD * 2);   // [4][16][HD], aliases the pipelines
+  float* mML = mO + 4 * 16 * HD;                                  // [4][16][2]
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+      const int d = i * 8 + (lane & 3) * 2;
+      mO[(warp * 16 + r0) * HD + d] = o[i][0]; mO[(warp * 16 + r0) * HD + d + 1] = o[i][1];
+      mO[(warp * 16 + r1) * HD + d] = o[i][2]; mO[(warp * 16 + r1) * HD + d + 1] = o[i][3];
+    }
+    if ((lane & 3) == 0) {
+      mML[(warp * 16 + r0) * 2] = m0; mML[(warp * 16 + r0) * 2 + 1] = l0;
+      mML[(warp * 16 + r1) * 2] = m1; mML[(warp * 16 + r1) * 2 + 1] = l1;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < heads_here * HD; i += 128) {
+    const int r = i / HD, d = i % HD;
+    float m = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, mML[(w * 16 + r) * 2]);
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = mML[(w * 16 + r) * 2];
+      const float f = mw == -CUDART_INF_F ? 0.f : exp2f((mw - m) * kLog2e);
+      acc += f * mO[(w * 16 + r) * HD + d];
+      l += f * mML[(w * 16 + r) * 2 + 1];
+    }
+    const int head = head0 + r;
+    if (p.splits == 1) {
+      const float v = l > 0.f ? acc / l * (fp8 ? p.v_scale : 1.f) : 0.f;
+      reinterpret_cast<T*>(p.out)[(static_cast<long>(b) * p.nh + head) * HD + d] = MmaT<T>::from_f(v);
+    } else {
+      const long base = (static_cast<long>(b) * p.nh + head) * p.splits + split;
+      p.ws_o[base * HD + d] = acc;
+      if (d == 0) { p.ws_ml[base * 2] = m; p.ws_ml[base * 2 + 1] = l; }
+    }
+  }
+}
+
 template <typename T, int HD>
 __global__ void decode_merge_kernel(const AttnParams p) {
   fi::pdl_launch_dependents();
@@ -483,16 +711,32 @@ template <typename T, int HD>
 int launch_decode(const AttnParams& p, int B, cudaStream_t s) {
   const int G = p.nh / p.nkv;
   const int groups = (G + 15) / 16;
-  const int kv_bytes = (16 * HD + 4 * 64 * HD) * 2;
-  const int merge_bytes = (4 * 16 * HD + 4 * 16 * 2) * 4 + 16 * HD * 2;
-  const int smem = kv_bytes > merge_bytes ? kv_bytes : merge_bytes;
-  auto kern = paged_decode_kernel<T, HD>;
-  static bool cfg = false;
-  if (!cfg) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    cfg = true;
+  if (p.block_size % 16 == 0) {
+    constexpr int NST = HD <= 64 ? 4 : HD <= 128 ? 3 : 2;
+    const int tile = 16 * HD;
+    const int raw = p.kv_fp8 ? tile : tile * 2;
+    const int pipe_bytes = 4 * (NST * 2 * raw + (p.kv_fp8 ? 2 * tile * 2 : 0));
+    const int merge_bytes = (4 * 16 * HD + 4 * 16 * 2) * 4;
+    const int smem = 16 * HD * 2 + (pipe_bytes > merge_bytes ? pipe_bytes : merge_bytes);
+    auto kern = paged_decode_v2_kernel<T, HD, NST>;
+    static int cfg_bytes = 0;
+    if (smem > cfg_bytes) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      cfg_bytes = smem;
+    }
+    fi::launch_kernel(kern, dim3(p.splits, p.nkv * groups, B), dim3(128), smem, s, 0, p);
+  } else {
+    const int kv_bytes = (16 * HD + 4 * 64 * HD) * 2;
+    const int merge_bytes = (4 * 16 * HD + 4 * 16 * 2) * 4 + 16 * HD * 2;
+    const int smem = kv_bytes > merge_bytes ? kv_bytes : merge_bytes;
+    auto kern = paged_decode_kernel<T, HD>;
+    static bool cfg = false;
+    if (!cfg) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      cfg = true;
+    }
+    fi::launch_kernel(kern, dim3(p.splits, p.nkv * groups, B), dim3(128), smem, s, 0, p);
   }
-  fi::launch_kernel(kern, dim3(p.splits, p.nkv * groups, B), dim3(128), smem, s, 0, p);
   if (p.splits > 1) fi::launch_kernel(decode_merge_kernel<T, HD>, dim3(p.nh, B), dim3(HD >= 128 ? 128 : 64), 0, s, 0, p);
   return static_cast<int>(cudaGetLastError());
 }
