@@ -88,7 +88,15 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BM;
-  const int t0 = blockIdx.y * BN;
+  // grouped (MoE) mode: the tile table says which expert and which sorted rows this CTA handles
+  const bool grouped = p.tile_expert != nullptr;
+  if (grouped) {
+    pdl_wait();   // the table was written by the preceding kernel
+    if (static_cast<int>(blockIdx.y) >= *p.n_tiles) return;   // uniform for the whole cluster
+  }
+  const int t0 = grouped ? p.tile_row0[blockIdx.y] : static_cast<int>(blockIdx.y) * BN;
+  const int t_end = grouped ? t0 + p.tile_rows[blockIdx.y] : p.T;
+  const int w_row0 = grouped ? p.tile_expert[blockIdx.y] * p.expert_rows : 0;   // first weight row of the expert
   const int S = p.splits;
   const int rank = (S > 1) ? static_cast<int>(blockIdx.z) : 0;
   const int kb_total = (p.K + BK - 1) / BK;
@@ -132,8 +140,8 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       for (int it = 0; it < n_pre; ++it) {   // packed weights first: they do not depend on the previous kernel
         uint8_t* r = raw_ring + it * RAW_BYTES;
         mbar_expect_tx(&raw_full[it], RAW_BYTES);
-        tma_load_2d(r + B_BYTES, &tmap_w, &raw_full[it], (kb_begin + it) * 8, n0);
-        if (DUAL) tma_load_2d(r + B_BYTES + Q_BYTES, &tmap_w, &raw_full[it], (kb_begin + it) * 8, p.dual_rows + n0);
+        tma_load_2d(r + B_BYTES, &tmap_w, &raw_full[it], (kb_begin + it) * 8, w_row0 + n0);
+        if (DUAL) tma_load_2d(r + B_BYTES + Q_BYTES, &tmap_w, &raw_full[it], (kb_begin + it) * 8, w_row0 + p.dual_rows + n0);
       }
       pdl_wait();
       if (!ag_handshake(p, x_map, epoch_now)) {
@@ -155,8 +163,8 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
         mbar_expect_tx(&raw_full[s], RAW_BYTES);
         // token tile first (keeps it 1024-byte aligned), packed weight tile(s) behind it
         tma_load_2d(r, tmap_x_ptr, &raw_full[s], kb * BK, x_row);
-        tma_load_2d(r + B_BYTES, &tmap_w, &raw_full[s], kb * 8, n0);
-        if (DUAL) tma_load_2d(r + B_BYTES + Q_BYTES, &tmap_w, &raw_full[s], kb * 8, p.dual_rows + n0);
+        tma_load_2d(r + B_BYTES, &tmap_w, &raw_full[s], kb * 8, w_row0 + n0);
+        if (DUAL) tma_load_2d(r + B_BYTES + Q_BYTES, &tmap_w, &raw_full[s], kb * 8, w_row0 + p.dual_rows + n0);
       }
     }
   } else if (warp == 1) {
@@ -201,7 +209,7 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     auto fetch = [&](int kb, float (&so)[NA][2], float (&zo)[NA][2]) {
 #pragma unroll
       for (int a = 0; a < NA; ++a) {
-        const int grow = (a == 0 ? n0 : p.dual_rows + n0) + row;
+        const int grow = w_row0 + (a == 0 ? n0 : p.dual_rows + n0) + row;
 #pragma unroll
         for (int gi = 0; gi < 2; ++gi) {
           so[a][gi] = 0.f;
@@ -263,7 +271,7 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   // ---------------------------------------------------------------- epilogue (epilogue.cuh)
   if (warp >= 2) epilogue_tmem_to_smem<BN, DUAL>(p, accum_bar, tmem_base, stage_f32, aborted, warp, lane);
   __syncthreads();
-  epilogue_reduce_store<BN, DUAL>(p, stage_f32, aborted, n0, t0, epoch_now);
+  epilogue_reduce_store<BN, DUAL>(p, stage_f32, aborted, n0, t0, epoch_now, t_end);
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
@@ -326,7 +334,7 @@ int launch(const CUtensorMap& tw, const TokenMaps& tx, GemmParams p, cudaStream_
     p.splits = best;
   }
   if (BN * BM * 4 * ((DUAL && p.splits > 1) ? 2 : 1) > ring) return -12;
-  return static_cast<int>(launch_kernel(kern, dim3((p.N + BM - 1) / BM, (p.T + BN - 1) / BN, p.splits),
+  return static_cast<int>(launch_kernel(kern, dim3((p.N + BM - 1) / BM, p.grid_tiles > 0 ? p.grid_tiles : (p.T + BN - 1) / BN, p.splits),
                                         dim3(kThreads), smem, stream, p.splits, tw, tx, p));
 }
 
@@ -364,13 +372,14 @@ static int fi_awq_gemm_impl(const void* X, const void* qw, const void* scales, c
                            const void* bias, const void* residual, int T, int N, int K, int group,
                            int ldx, int ldc, int act, int dual_rows, int out_fp32, int dtype,
                            int splits, int bn, int* status, void* stream,
-                             const FiComm* comm) {
+                             const FiComm* comm, const FiGrouped* grp) {
   if (T <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 64) != 0 || (ldc % 8) != 0 || (reinterpret_cast<uintptr_t>(C) & 15) != 0) return -10;
   if (group != 32 && group != 64 && group != 128 && !(group > 128 && group % 64 == 0)) return -13;
   if (dual_rows > 0 && N != dual_rows) return -11;
   if (bn == 0) bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128;
-  const int w_rows = dual_rows > 0 ? 2 * dual_rows : N;
+  int w_rows = dual_rows > 0 ? 2 * dual_rows : N;
+  if (grp != nullptr) w_rows = grp->num_experts * grp->expert_rows;
   CUtensorMap tw;
   TokenMaps tx;
   int r = make_tmap_packed(&tw, qw, w_rows, K / 8);
@@ -399,6 +408,7 @@ static int fi_awq_gemm_impl(const void* X, const void* qw, const void* scales, c
   p.splits = splits; p.status = status;
   p.scales = scales; p.zeros = reinterpret_cast<const uint8_t*>(zeros); p.group = group;
   p.n_rows_total = w_rows;
+  p.tile_expert = nullptr; p.tile_row0 = nullptr; p.tile_rows = nullptr; p.n_tiles = nullptr; p.expert_rows = 0; p.grid_tiles = 0;
   p.comm_mode = 0; p.world = 1; p.rank = 0; p.rows_per_rank = 0; p.xfer_16bit = 0;
   p.ag_world = 1; p.ag_rows_per_rank = 0; p.slab_elems = 0; p.epoch = nullptr; p.done = nullptr;
   for (int d = 0; d < kMaxRanks; ++d) { p.recv[d] = 0; p.flags[d] = 0; p.ready[d] = 0; }
@@ -417,6 +427,12 @@ static int fi_awq_gemm_impl(const void* X, const void* qw, const void* scales, c
     if (comm->mode != 0 && tiles > kMaxCommTiles) return -18;
     if (comm->mode != 0 && (N % 8) != 0) return -19;
   }
+  if (grp != nullptr) {
+    if (comm != nullptr && comm->mode != 0) return -20;
+    p.tile_expert = grp->tile_expert; p.tile_row0 = grp->tile_row0; p.tile_rows = grp->tile_rows;
+    p.n_tiles = grp->n_tiles; p.expert_rows = grp->expert_rows; p.splits = 1;
+    p.grid_tiles = grp->max_tiles;
+  }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == 1) {
     if (dual_rows > 0) return dispatch<__half, true>(bn, tw, tx, p, s);
@@ -430,7 +446,7 @@ extern "C" int fi_awq_gemm(const void* X, const void* qw, const void* scales, co
                            const void* bias, const void* residual, int T, int N, int K, int group,
                            int ldx, int ldc, int act, int dual_rows, int out_fp32, int dtype,
                            int splits, int bn, int* status, void* stream) {
-  return fi_awq_gemm_impl(X, qw, scales, zeros, C, bias, residual, T, N, K, group, ldx, ldc, act, dual_rows, out_fp32, dtype, splits, bn, status, stream, nullptr);
+  return fi_awq_gemm_impl(X, qw, scales, zeros, C, bias, residual, T, N, K, group, ldx, ldc, act, dual_rows, out_fp32, dtype, splits, bn, status, stream, nullptr, nullptr);
 }
 
 // Same GEMM with a fused collective and/or an all-gathered token operand (see comm_desc.h).
@@ -439,5 +455,14 @@ extern "C" int fi_awq_gemm_comm(const void* X, const void* qw, const void* scale
                            int ldx, int ldc, int act, int dual_rows, int out_fp32, int dtype,
                            int splits, int bn, int* status, void* stream,
                              const FiComm* comm) {
-  return fi_awq_gemm_impl(X, qw, scales, zeros, C, bias, residual, T, N, K, group, ldx, ldc, act, dual_rows, out_fp32, dtype, splits, bn, status, stream, comm);
+  return fi_awq_gemm_impl(X, qw, scales, zeros, C, bias, residual, T, N, K, group, ldx, ldc, act, dual_rows, out_fp32, dtype, splits, bn, status, stream, comm, nullptr);
+}
+
+// Grouped expert GEMM: X holds the expert-sorted activation rows, qw/scales/zeros the stacked experts.
+extern "C" int fi_awq_gemm_grouped(const void* X, const void* qw, const void* scales, const void* zeros, void* C,
+                           const void* bias, const void* residual, int T, int N, int K, int group,
+                           int ldx, int ldc, int act, int dual_rows, int out_fp32, int dtype,
+                           int splits, int bn, int* status, void* stream,
+                             const FiGrouped* grp) {
+  return fi_awq_gemm_impl(X, qw, scales, zeros, C, bias, residual, T, N, K, group, ldx, ldc, act, dual_rows, out_fp32, dtype, splits, bn, status, stream, nullptr, grp);
 }

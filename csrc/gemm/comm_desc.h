@@ -19,4 +19,17 @@ struct FiComm {
   unsigned long long epoch;       // local device word: completed fused calls
   unsigned long long done;        // local device word: finished CTAs of the running call
 };
+
+// Grouped (mixture-of-experts) launch: activations are sorted by expert, a device-side tile table
+// (built by fi_moe_align) tells each CTA its expert and rows; weights of all experts are stacked.
+struct FiGrouped {
+  const int* tile_expert;
+  const int* tile_row0;
+  const int* tile_rows;
+  const int* n_tiles;
+  int max_tiles;       // grid size along the tile axis (upper bound of *n_tiles)
+  int num_experts;     // experts stacked in the weight tensor
+  int expert_rows;     // weight rows per expert (N, or 2N in gated mode)
+  int reserved;
+};
 }

@@ -160,7 +160,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   // ---------------------------------------------------------------- epilogue (epilogue.cuh)
   if (warp >= 2) epilogue_tmem_to_smem<BN, DUAL>(p, accum_bar, tmem_base, stage_f32, aborted, warp, lane);
   __syncthreads();
-  epilogue_reduce_store<BN, DUAL>(p, stage_f32, aborted, n0, t0, epoch_now);
+  epilogue_reduce_store<BN, DUAL>(p, stage_f32, aborted, n0, t0, epoch_now, p.T);
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
@@ -303,6 +303,7 @@ static int fi_dense_gemm_impl(const void* X, const void* W, void* C, const void*
   p.T = T; p.N = N; p.K = K; p.ldc = ldc;
   p.dual_rows = dual_rows; p.act = act; p.out_fp32 = out_fp32; p.is_fp16 = dtype == 1;
   p.splits = splits; p.status = status;
+  p.tile_expert = nullptr; p.tile_row0 = nullptr; p.tile_rows = nullptr; p.n_tiles = nullptr; p.expert_rows = 0; p.grid_tiles = 0;
   p.comm_mode = 0; p.world = 1; p.rank = 0; p.rows_per_rank = 0; p.xfer_16bit = 0;
   p.ag_world = 1; p.ag_rows_per_rank = 0; p.slab_elems = 0; p.epoch = nullptr; p.done = nullptr;
   for (int d = 0; d < kMaxRanks; ++d) { p.recv[d] = 0; p.flags[d] = 0; p.ready[d] = 0; }

@@ -61,6 +61,13 @@ struct GemmParams {
   unsigned long long ready[kMaxRanks];  // all-gather ready words of rank d as mapped here
   unsigned int* epoch;   // local: completed fused calls
   unsigned int* done;    // local: CTAs of the current call that have finished
+  // grouped (mixture-of-experts) mode: blockIdx.y indexes a tile table built on the device
+  const int* tile_expert;   // expert of each token tile (null = plain GEMM)
+  const int* tile_row0;     // first row of the tile in the expert-sorted activation matrix
+  const int* tile_rows;     // valid rows of the tile
+  const int* n_tiles;       // number of valid tiles (CTAs beyond it leave at once)
+  int expert_rows;          // weight rows per expert (N, or 2N in gated mode)
+  int grid_tiles;           // grid size along y in grouped mode (0 = derive from T)
 };
 
 struct TokenMaps {
@@ -210,7 +217,7 @@ __device__ __forceinline__ void epilogue_tmem_to_smem(const GemmParams& p, uint6
 template <int BN, bool DUAL>
 __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float* stage_f32,
                                                       volatile int* aborted, int n0, int t0,
-                                                      unsigned int epoch_now) {
+                                                      unsigned int epoch_now, int t_end) {
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   const int S = p.splits;
@@ -228,7 +235,7 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
       const int nl = (idx % (BM / 8)) * 8;
       const int t = t0 + tl;
       const int n = n0 + nl;
-      if (t >= p.T || n >= p.N) continue;
+      if (t >= t_end || n >= p.N) continue;
       float g[8], u[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) { g[j] = 0.f; u[j] = 0.f; }
@@ -305,7 +312,7 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
         const int nl = (idx % (BM / 8)) * 8;
         const int t = t0 + tl;
         const int n = n0 + nl;
-        if (t >= p.T || n >= p.N) continue;
+        if (t >= t_end || n >= p.N) continue;
         const long trow = t - row_base;
         float acc[8];
 #pragma unroll

@@ -1,0 +1,282 @@
+// GGUF block-format kernels for sm_100a (Q8_0, Q2_K, IQ2_XXS): dense dequantisation, a
+// weight-streaming GEMV for up to 8 activation rows, and the routed-expert variants (gate|up with
+// the clamped SiLU gate, down projection) that read the raw expert payloads in place.
+//
+// One warp per output row; lanes walk the row's blocks, keep one fp32 accumulator per activation
+// row and reduce by shuffle.  Activations are staged once per CTA in shared memory as fp32.
+// The bytes are exactly the file's: 34 / 84 / 66-byte blocks, read with 2- or 4-byte loads.
+// Reference counterparts (Triton, one program per row): vllm/kernels/triton/deepseek_v4_flash/
+// q8_linear.py:10-96, q2_iq2_moe.py:123-1000.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../common/launch.cuh"
+#include "iq2_tables.h"
+
+namespace {
+
+constexpr int kMaxM = 8;
+
+__device__ __forceinline__ float h2f(const uint8_t* p) {
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(p[0] | (p[1] << 8))));
+}
+
+__constant__ uint64_t c_grid[256];
+__constant__ uint8_t c_signs[128];
+bool g_tables_ready[64] = {false};
+
+int ensure_tables() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return -1;
+  if (!g_tables_ready[dev]) {
+    cudaError_t e = cudaMemcpyToSymbol(c_grid, kIq2xxsGrid, sizeof(kIq2xxsGrid));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(c_signs, kIq2xsSigns, sizeof(kIq2xsSigns));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    g_tables_ready[dev] = true;
+  }
+  return 0;
+}
+
+// Decode `n` consecutive values starting at value index v0 (multiple of 8) of one block into out[].
+template <int TYPE>
+__device__ __forceinline__ void decode8(const uint8_t* blk, int v0, float* out) {
+  if (TYPE == 8) {   // Q8_0: 32 values per block
+    const float d = h2f(blk);
+    const int8_t* q = reinterpret_cast<const int8_t*>(blk + 2 + v0);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[j] = d * static_cast<float>(q[j]);
+  } else if (TYPE == 10) {   // Q2_K: value v -> half n = v/128, shift s = (v%128)/32, byte l = v%32
+    const int n = v0 >> 7, s = (v0 & 127) >> 5, l = v0 & 31;
+    const int sub = n * 8 + s * 2 + (l >> 4);
+    const uint8_t sc = blk[sub];
+    const float dl = h2f(blk + 80) * static_cast<float>(sc & 0x0F);
+    const float ml = h2f(blk + 82) * static_cast<float>(sc >> 4);
+    const uint8_t* q = blk + 16 + n * 32 + l;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[j] = dl * static_cast<float>((q[j] >> (2 * s)) & 3) - ml;
+  } else {   // IQ2_XXS: group ib = v/32, row l = (v%32)/8
+    const int ib = v0 >> 5, l = (v0 & 31) >> 3;
+    const uint8_t* q = blk + 2 + ib * 8;
+    const uint32_t word = q[4] | (q[5] << 8) | (q[6] << 16) | (static_cast<uint32_t>(q[7]) << 24);
+    const float db = h2f(blk) * (0.5f + static_cast<float>(word >> 28)) * 0.25f;
+    const uint64_t g = c_grid[q[l]];
+    const uint8_t sg = c_signs[(word >> (7 * l)) & 127];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float mag = static_cast<float>((g >> (8 * j)) & 0xFF);
+      out[j] = db * ((sg >> j) & 1 ? -mag : mag);
+    }
+  }
+}
+
+template <int TYPE> struct Blk;
+template <> struct Blk<8> { static constexpr int kVals = 32, kBytes = 34; };
+template <> struct Blk<10> { static constexpr int kVals = 256, kBytes = 84; };
+template <> struct Blk<16> { static constexpr int kVals = 256, kBytes = 66; };
+
+template <int TYPE, typename T>
+__global__ void dequant_kernel(const uint8_t* __restrict__ raw, long row_stride, int K, T* __restrict__ out) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  const long row = blockIdx.x;
+  const uint8_t* r = raw + row * row_stride;
+  for (int v0 = threadIdx.x * 8; v0 < K; v0 += blockDim.x * 8) {
+    float v[8];
+    decode8<TYPE>(r + (v0 / Blk<TYPE>::kVals) * Blk<TYPE>::kBytes, v0 % Blk<TYPE>::kVals, v);
+    T o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = static_cast<T>(v[j]);
+    *reinterpret_cast<uint4*>(out + row * K + v0) = *reinterpret_cast<uint4*>(o);
+  }
+}
+
+// Dot products of one weight row with M activation rows (fp32 in shared memory, row pitch K).
+template <int TYPE>
+__device__ __forceinline__ void row_dot(const uint8_t* r, int K, const float* xs, int M, int lane, float* acc) {
+  for (int v0 = lane * 8; v0 < K; v0 += 32 * 8) {
+    float w[8];
+    decode8<TYPE>(r + (v0 / Blk<TYPE>::kVals) * Blk<TYPE>::kBytes, v0 % Blk<TYPE>::kVals, w);
+#pragma unroll
+    for (int m = 0; m < kMaxM; ++m) {
+      if (m < M) {
+        const float4 a = *reinterpret_cast<const float4*>(xs + m * K + v0);
+        const float4 b = *reinterpret_cast<const float4*>(xs + m * K + v0 + 4);
+        acc[m] += w[0] * a.x + w[1] * a.y + w[2] * a.z + w[3] * a.w + w[4] * b.x + w[5] * b.y + w[6] * b.z + w[7] * b.w;
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < kMaxM; ++m)
+    for (int o = 16; o > 0; o >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], o);
+}
+
+template <typename T>
+__device__ __forceinline__ void stage_x(const T* x, long ldx, int M, int K, float* xs) {
+  for (int i = threadIdx.x; i < M * K; i += blockDim.x) xs[i] = static_cast<float>(x[(i / K) * ldx + (i % K)]);
+  __syncthreads();
+}
+
+template <int TYPE, typename T>
+__global__ void gemv_kernel(const T* __restrict__ x, long ldx, const uint8_t* __restrict__ raw, long row_stride,
+                            int M, int N, int K, void* __restrict__ out, long ldo, const T* __restrict__ residual,
+                            int out_fp32) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  extern __shared__ float xs[];
+  stage_x(x, ldx, M, K, xs);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (row >= N) return;
+  float acc[kMaxM];
+#pragma unroll
+  for (int m = 0; m < kMaxM; ++m) acc[m] = 0.f;
+  row_dot<TYPE>(raw + static_cast<long>(row) * row_stride, K, xs, M, lane, acc);
+  if (lane == 0) {
+    for (int m = 0; m < M; ++m) {
+      float v = acc[m];
+      if (residual) v += static_cast<float>(residual[m * ldo + row]);
+      if (out_fp32) reinterpret_cast<float*>(out)[m * ldo + row] = v;
+      else reinterpret_cast<T*>(out)[m * ldo + row] = static_cast<T>(v);
+    }
+  }
+}
+
+// Routed experts.  route r = (token r / top_k, expert ids[r]); expert payloads are stacked with a
+// byte stride.  Gate|up: a[r, i] = silu(min(g, clamp)) * clamp(u) (clamp <= 0: plain silu * u).
+template <int TG, int TU, typename T>
+__global__ void moe_gate_up_kernel(const T* __restrict__ x, long ldx, const uint8_t* __restrict__ gate,
+                                   const uint8_t* __restrict__ up, long expert_stride_g, long expert_stride_u,
+                                   long row_stride_g, long row_stride_u, const int* __restrict__ ids, int top_k,
+                                   int e_lo, int e_hi, int I, int K, float clamp, T* __restrict__ a) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  extern __shared__ float xs[];
+  const int r = blockIdx.y;
+  const int e = ids[r];
+  if (e < e_lo || e >= e_hi) return;   // not this rank's expert
+  stage_x(x + static_cast<long>(r / top_k) * ldx, ldx, 1, K, xs);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (row >= I) return;
+  float g[kMaxM] = {0.f}, u[kMaxM] = {0.f};
+  row_dot<TG>(gate + (e - e_lo) * expert_stride_g + static_cast<long>(row) * row_stride_g, K, xs, 1, lane, g);
+  row_dot<TU>(up + (e - e_lo) * expert_stride_u + static_cast<long>(row) * row_stride_u, K, xs, 1, lane, u);
+  if (lane == 0) {
+    float gv = g[0], uv = u[0];
+    if (clamp > 0.f) { gv = fminf(gv, clamp); uv = fminf(fmaxf(uv, -clamp), clamp); }
+    a[static_cast<long>(r) * I + row] = static_cast<T>(gv / (1.f + __expf(-gv)) * uv);
+  }
+}
+
+template <int TD, typename T>
+__global__ void moe_down_kernel(const T* __restrict__ a, const uint8_t* __restrict__ down, long expert_stride,
+                                long row_stride, const int* __restrict__ ids, int e_lo, int e_hi, int H, int I,
+                                T* __restrict__ y) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  extern __shared__ float xs[];
+  const int r = blockIdx.y;
+  const int e = ids[r];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (e < e_lo || e >= e_hi) {
+    if (row < H && lane == 0) y[static_cast<long>(r) * H + row] = static_cast<T>(0.f);
+    return;
+  }
+  stage_x(a + static_cast<long>(r) * I, I, 1, I, xs);
+  if (row >= H) return;
+  float acc[kMaxM] = {0.f};
+  row_dot<TD>(down + (e - e_lo) * expert_stride + static_cast<long>(row) * row_stride, I, xs, 1, lane, acc);
+  if (lane == 0) y[static_cast<long>(r) * H + row] = static_cast<T>(acc[0]);
+}
+
+}  // namespace
+
+#define FI_STREAM(s) reinterpret_cast<cudaStream_t>(s)
+#define FI_TYPE_SWITCH(type, ...)                       \
+  switch (type) {                                       \
+    case 8: { constexpr int TY = 8; __VA_ARGS__; break; }   \
+    case 10: { constexpr int TY = 10; __VA_ARGS__; break; } \
+    case 16: { constexpr int TY = 16; __VA_ARGS__; break; } \
+    default: return -11;                                \
+  }
+
+extern "C" int fi_gguf_dequant(const void* raw, int type, int rows, int K, long row_stride, void* out, int dtype,
+                               void* stream) {
+  if (rows <= 0) return 0;
+  if (K % 256 != 0 && !(type == 8 && K % 32 == 0)) return -10;
+  if (int rc = ensure_tables()) return rc;
+  const uint8_t* r = static_cast<const uint8_t*>(raw);
+  FI_TYPE_SWITCH(type, {
+    if (dtype == 0) fi::launch_kernel(dequant_kernel<TY, __nv_bfloat16>, dim3(rows), dim3(128), 0, FI_STREAM(stream), 0, r, row_stride, K, (__nv_bfloat16*)out);
+    else fi::launch_kernel(dequant_kernel<TY, __half>, dim3(rows), dim3(128), 0, FI_STREAM(stream), 0, r, row_stride, K, (__half*)out);
+  });
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fi_gguf_gemv(const void* x, long ldx, const void* raw, long row_stride, int type, int M, int N, int K,
+                            void* out, long ldo, const void* residual, int out_fp32, int dtype, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > kMaxM || K % 8 != 0) return -10;
+  if (int rc = ensure_tables()) return rc;
+  const size_t smem = static_cast<size_t>(M) * K * sizeof(float);
+  const uint8_t* r = static_cast<const uint8_t*>(raw);
+  const int wpb = 8;
+  FI_TYPE_SWITCH(type, {
+    if (dtype == 0) {
+      auto k = gemv_kernel<TY, __nv_bfloat16>;
+      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      fi::launch_kernel(k, dim3((N + wpb - 1) / wpb), dim3(wpb * 32), smem, FI_STREAM(stream), 0,
+                        (const __nv_bfloat16*)x, ldx, r, row_stride, M, N, K, out, ldo, (const __nv_bfloat16*)residual, out_fp32);
+    } else {
+      auto k = gemv_kernel<TY, __half>;
+      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      fi::launch_kernel(k, dim3((N + wpb - 1) / wpb), dim3(wpb * 32), smem, FI_STREAM(stream), 0,
+                        (const __half*)x, ldx, r, row_stride, M, N, K, out, ldo, (const __half*)residual, out_fp32);
+    }
+  });
+  return static_cast<int>(cudaGetLastError());
+}
+
+// gate/up payloads: [E_local, I rows, row bytes]; type_g/type_u among {8, 10, 16} (bf16 activations)
+extern "C" int fi_gguf_moe_gate_up(const void* x, long ldx, const void* gate, const void* up, int type_g, int type_u,
+                                   long row_stride_g, long row_stride_u, const int* ids, int n_routes, int top_k,
+                                   int e_lo, int e_hi, int I, int K, float clamp, void* a, void* stream) {
+  if (n_routes <= 0) return 0;
+  if (int rc = ensure_tables()) return rc;
+  const size_t smem = static_cast<size_t>(K) * sizeof(float);
+  const int wpb = 8;
+  const dim3 grid((I + wpb - 1) / wpb, n_routes);
+  const uint8_t* g = static_cast<const uint8_t*>(gate);
+  const uint8_t* u = static_cast<const uint8_t*>(up);
+  const long sg = row_stride_g * I, su = row_stride_u * I;
+#define FI_GU(TG, TU)                                                                                          \
+  fi::launch_kernel(moe_gate_up_kernel<TG, TU, __nv_bfloat16>, grid, dim3(wpb * 32), smem, FI_STREAM(stream), 0, \
+                    (const __nv_bfloat16*)x, ldx, g, u, sg, su, row_stride_g, row_stride_u, ids, top_k, e_lo,  \
+                    e_hi, I, K, clamp, (__nv_bfloat16*)a)
+  if (type_g == 16 && type_u == 16) FI_GU(16, 16);
+  else if (type_g == 10 && type_u == 10) FI_GU(10, 10);
+  else if (type_g == 8 && type_u == 8) FI_GU(8, 8);
+  else return -11;
+#undef FI_GU
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fi_gguf_moe_down(const void* a, const void* down, int type_d, long row_stride, const int* ids,
+                                int n_routes, int e_lo, int e_hi, int H, int I, void* y, void* stream) {
+  if (n_routes <= 0) return 0;
+  if (int rc = ensure_tables()) return rc;
+  const size_t smem = static_cast<size_t>(I) * sizeof(float);
+  const int wpb = 8;
+  const dim3 grid((H + wpb - 1) / wpb, n_routes);
+  const uint8_t* d = static_cast<const uint8_t*>(down);
+  const long sd = row_stride * H;
+  FI_TYPE_SWITCH(type_d, {
+    fi::launch_kernel(moe_down_kernel<TY, __nv_bfloat16>, grid, dim3(wpb * 32), smem, FI_STREAM(stream), 0,
+                      (const __nv_bfloat16*)a, d, sd, row_stride, ids, e_lo, e_hi, H, I, (__nv_bfloat16*)y);
+  });
+  return static_cast<int>(cudaGetLastError());
+}

@@ -62,7 +62,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 template <typename T, bool WARP_ROWS>
 __global__ void rmsnorm_kernel(const T* __restrict__ x, T* __restrict__ residual,
                                const T* __restrict__ w, T* __restrict__ out, int rows, int H,
-                               long ldx, long ldo, float eps, int w_mode, float out_scale) {
+                               long ldx, long ldo, float eps, int w_mode, float out_scale,
+                               const T* __restrict__ addend) {
   fi::pdl_launch_dependents();
   fi::pdl_wait();
   __shared__ float red[32];
@@ -81,6 +82,7 @@ __global__ void rmsnorm_kernel(const T* __restrict__ x, T* __restrict__ residual
   const T* xr = x + static_cast<long>(row) * ldx;
   T* rr = residual ? residual + static_cast<long>(row) * ldx : nullptr;
   T* orow = out + static_cast<long>(row) * ldo;
+  const T* arow = addend ? addend + static_cast<long>(row) * ldo : nullptr;   // out = norm(x) * w + addend
   float ss = 0.f;
   for (int i = tid * V; i < H; i += nthr * V) {
     uint4 raw = *reinterpret_cast<const uint4*>(xr + i);
@@ -109,12 +111,17 @@ __global__ void rmsnorm_kernel(const T* __restrict__ x, T* __restrict__ residual
     T* we = reinterpret_cast<T*>(&wraw);
     uint4 oraw;
     T* oe = reinterpret_cast<T*>(&oraw);
+    uint4 araw = make_uint4(0, 0, 0, 0);
+    if (arow) araw = *reinterpret_cast<const uint4*>(arow + i);
+    const T* ae = reinterpret_cast<const T*>(&araw);
 #pragma unroll
     for (int j = 0; j < V; ++j) {
       // the normalised value is rounded to the storage type before the weight multiply
       float nv = Cvt<T>::to_f(Cvt<T>::from_f(Cvt<T>::to_f(e[j]) * inv));
       float g = w_mode == 0 ? Cvt<T>::to_f(we[j]) : w_mode == 1 ? 1.f + Cvt<T>::to_f(we[j]) : 1.f;
-      oe[j] = Cvt<T>::from_f(nv * g);
+      float r = nv * g;
+      if (arow) r = Cvt<T>::to_f(Cvt<T>::from_f(r)) + Cvt<T>::to_f(ae[j]);
+      oe[j] = Cvt<T>::from_f(r);
     }
     *reinterpret_cast<uint4*>(orow + i) = oraw;
   }
@@ -364,7 +371,7 @@ int dispatch_dtype(int dtype, F&& f) {
 // w_mode: 0 = x*w, 1 = x*(1+w), 2 = no weight.  residual may be null.  dtype 0 bf16 / 1 fp16.
 extern "C" int fi_rmsnorm(const void* x, void* residual, const void* w, void* out, int rows, int H,
                           long ldx, long ldo, float eps, int w_mode, float out_scale, int dtype,
-                          void* stream) {
+                          void* stream, const void* addend) {
   if (rows <= 0) return 0;
   if (H % 8 != 0 || ldx % 8 != 0 || ldo % 8 != 0) return -10;
   return dispatch_dtype(dtype, [&](auto* tag) {
@@ -373,13 +380,13 @@ extern "C" int fi_rmsnorm(const void* x, void* residual, const void* w, void* ou
       const int wpb = 4;
       fi::launch_kernel(rmsnorm_kernel<T, true>, dim3((rows + wpb - 1) / wpb), dim3(wpb * 32), 0, FI_STREAM(stream), 0, 
           (const T*)x, (T*)residual, (const T*)w, (T*)out, rows, H, ldx, ldo, eps, w_mode,
-          out_scale);
+          out_scale, (const T*)addend);
     } else {
       int threads = H / 8;
       threads = threads > 1024 ? 1024 : ((threads + 31) / 32) * 32;
       fi::launch_kernel(rmsnorm_kernel<T, false>, dim3(rows), dim3(threads), 0, FI_STREAM(stream), 0, 
           (const T*)x, (T*)residual, (const T*)w, (T*)out, rows, H, ldx, ldo, eps, w_mode,
-          out_scale);
+          out_scale, (const T*)addend);
     }
     return static_cast<int>(cudaGetLastError());
   });

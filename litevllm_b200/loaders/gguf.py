@@ -1,0 +1,242 @@
+"""GGUF checkpoints: reader (native header parser in csrc/host/gguf_reader.cpp + zero-copy numpy
+memory maps for the payloads), a writer for synthetic files, the GGUF -> HF config translation and
+the GGUF -> engine tensor-name mapping.
+
+Quantised tensors are yielded as :class:`GGUFTensor` (raw block bytes + type + logical shape) and are
+consumed in place by the GGUF kernels; F32/F16/BF16 tensors are yielded as ordinary torch tensors.
+Reference: vllm/model_executor/models/deepseek_v4_flash/gguf_reader.py:13-366 and weight_store.py
+(semantic tensor binding), vllm/model_executor/model_loader/__init__.py:55-338 (generic GGUF path).
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+import struct
+from dataclasses import dataclass
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from ..ops import _lib
+from ..ops.gguf_quant import BLOCK, GGML_TYPES, TYPE_NAMES
+
+_NP = {0: np.float32, 1: np.float16, 26: np.int32}
+
+
+@dataclass
+class GGUFTensor:
+    """A quantised GGUF tensor: ``raw`` is uint8 [..., rows, row_bytes]; ``shape`` the logical shape
+    (outermost first), ``ggml_type`` the block format id."""
+    raw: torch.Tensor
+    ggml_type: int
+    shape: tuple
+
+    @property
+    def K(self) -> int:
+        return self.shape[-1]
+
+
+class GGUFFile:
+    def __init__(self, path: str | Path):
+        self.path = str(path)
+        lib = _lib.host()
+        err = ctypes.create_string_buffer(256)
+        lib.fi_gguf_open.restype = ctypes.c_void_p
+        h = lib.fi_gguf_open(self.path.encode(), err, 256)
+        if not h:
+            raise ValueError(f"cannot read GGUF file {self.path}: {err.value.decode()}")
+        try:
+            n = lib.fi_gguf_meta_json_len(ctypes.c_void_p(h))
+            buf = ctypes.create_string_buffer(n + 1)
+            lib.fi_gguf_meta_json(ctypes.c_void_p(h), buf, n + 1)
+            self.metadata: dict = json.loads(buf.value.decode("utf-8", errors="replace"))
+            self.alignment = int(lib.fi_gguf_alignment(ctypes.c_void_p(h)))
+            self.tensors: dict[str, dict] = {}
+            name = ctypes.create_string_buffer(512)
+            dims = (ctypes.c_long * 4)()
+            info = (ctypes.c_int * 2)()
+            sizes = (ctypes.c_long * 2)()
+            for i in range(lib.fi_gguf_num_tensors(ctypes.c_void_p(h))):
+                rc = lib.fi_gguf_tensor_info(ctypes.c_void_p(h), i, name, 512, dims, info, sizes)
+                if rc != 0:
+                    raise ValueError(f"bad tensor record {i} in {self.path}")
+                nd = info[0]
+                shape = tuple(int(dims[d]) for d in range(nd))[::-1]     # outermost first
+                self.tensors[name.value.decode()] = {"shape": shape, "type": int(info[1]),
+                                                     "offset": int(sizes[0]), "nbytes": int(sizes[1])}
+        finally:
+            lib.fi_gguf_close(ctypes.c_void_p(h))
+
+    def arch(self) -> str:
+        return str(self.metadata.get("general.architecture", ""))
+
+    def get(self, key: str, default=None):
+        a = self.arch()
+        return self.metadata.get(f"{a}.{key}", self.metadata.get(key, default))
+
+    def load(self, name: str):
+        """-> torch tensor (float types) or GGUFTensor (block-quantised), backed by the memory map."""
+        t = self.tensors[name]
+        ty, shape = t["type"], t["shape"]
+        if ty in _NP:
+            arr = np.memmap(self.path, dtype=_NP[ty], mode="r", offset=t["offset"], shape=shape)
+            return torch.from_numpy(np.ascontiguousarray(arr))
+        if ty == 30:
+            arr = np.memmap(self.path, dtype=np.int16, mode="r", offset=t["offset"], shape=shape)
+            return torch.from_numpy(np.ascontiguousarray(arr)).view(torch.bfloat16)
+        if ty in BLOCK:
+            vals, nb = BLOCK[ty]
+            raw_shape = shape[:-1] + (shape[-1] // vals * nb,)
+            arr = np.memmap(self.path, dtype=np.uint8, mode="r", offset=t["offset"], shape=raw_shape)
+            return GGUFTensor(torch.from_numpy(np.ascontiguousarray(arr)), ty, shape)
+        raise ValueError(f"tensor {name}: unsupported GGML type {ty} ({TYPE_NAMES.get(ty, '?')})")
+
+
+# ----------------------------------------------------------------------------- writer
+_KV = {"u32": (4, "<I"), "i32": (5, "<i"), "f32": (6, "<f"), "bool": (7, "<B"), "u64": (10, "<Q")}
+
+
+def _kv_bytes(key: str, value) -> bytes:
+    out = struct.pack("<Q", len(key.encode())) + key.encode()
+    if isinstance(value, bool):
+        return out + struct.pack("<I", 7) + struct.pack("<B", int(value))
+    if isinstance(value, int):
+        return out + (struct.pack("<I", 4) + struct.pack("<I", value) if 0 <= value < 2 ** 32
+                      else struct.pack("<I", 11) + struct.pack("<q", value))
+    if isinstance(value, float):
+        return out + struct.pack("<I", 6) + struct.pack("<f", value)
+    if isinstance(value, str):
+        b = value.encode()
+        return out + struct.pack("<I", 8) + struct.pack("<Q", len(b)) + b
+    if isinstance(value, (list, tuple)):
+        if all(isinstance(v, int) for v in value):
+            body = b"".join(struct.pack("<i", v) for v in value)
+            return out + struct.pack("<I", 9) + struct.pack("<I", 5) + struct.pack("<Q", len(value)) + body
+        if all(isinstance(v, float) for v in value):
+            body = b"".join(struct.pack("<f", v) for v in value)
+            return out + struct.pack("<I", 9) + struct.pack("<I", 6) + struct.pack("<Q", len(value)) + body
+    raise TypeError(f"unsupported metadata value for {key}: {type(value).__name__}")
+
+
+def write_gguf(path: str | Path, metadata: dict, tensors: dict, alignment: int = 32) -> None:
+    """tensors: name -> torch tensor (F32/F16/BF16/I32) or GGUFTensor."""
+    metadata = dict(metadata)
+    metadata.setdefault("general.alignment", alignment)
+    head = struct.pack("<IIQQ", 0x46554747, 3, len(tensors), len(metadata))
+    head += b"".join(_kv_bytes(k, v) for k, v in metadata.items())
+    infos, blobs, off = b"", [], 0
+    for name, t in tensors.items():
+        if isinstance(t, GGUFTensor):
+            ty, shape, data = t.ggml_type, t.shape, t.raw.contiguous().numpy().tobytes()
+        else:
+            ty = {torch.float32: 0, torch.float16: 1, torch.int32: 26, torch.bfloat16: 30}[t.dtype]
+            shape = tuple(t.shape)
+            data = (t.view(torch.int16) if t.dtype == torch.bfloat16 else t).contiguous().numpy().tobytes()
+        nb = name.encode()
+        infos += struct.pack("<Q", len(nb)) + nb + struct.pack("<I", len(shape))
+        infos += b"".join(struct.pack("<Q", d) for d in shape[::-1])
+        infos += struct.pack("<I", ty) + struct.pack("<Q", off)
+        blobs.append((off, data))
+        off = (off + len(data) + alignment - 1) // alignment * alignment
+    pre = head + infos
+    pad = (-len(pre)) % alignment
+    with open(path, "wb") as f:
+        f.write(pre + b"\0" * pad)
+        base = f.tell()
+        for o, data in blobs:
+            f.seek(base + o)
+            f.write(data)
+        f.truncate(base + off if blobs else base)
+
+
+# ----------------------------------------------------------------------------- config translation
+def hf_config_from_gguf(path: str | Path) -> dict:
+    g = GGUFFile(path)
+    a = g.arch()
+    heads = int(g.get("attention.head_count", 32))
+    hidden = int(g.get("embedding_length"))
+    cfg = {
+        "hidden_size": hidden, "num_hidden_layers": int(g.get("block_count")), "num_attention_heads": heads,
+        "num_key_value_heads": int(g.get("attention.head_count_kv", heads)),
+        "intermediate_size": int(g.get("feed_forward_length", 4 * hidden)),
+        "rms_norm_eps": float(g.get("attention.layer_norm_rms_epsilon", 1e-5)),
+        "rope_theta": float(g.get("rope.freq_base", 10000.0)),
+        "max_position_embeddings": int(g.get("context_length", 4096)),
+        "vocab_size": int(g.get("vocab_size", 0)) or g.tensors.get("token_embd.weight", {"shape": (32000,)})["shape"][0],
+        "quantization_config": {"quant_method": "gguf"},
+        "eos_token_id": g.metadata.get("tokenizer.ggml.eos_token_id"),
+        "bos_token_id": g.metadata.get("tokenizer.ggml.bos_token_id"),
+        "tie_word_embeddings": "output.weight" not in g.tensors,
+    }
+    if a in ("deepseek2", "deepseek3", "deepseek_v3"):
+        cfg.update({
+            "architectures": ["DeepseekV3ForCausalLM"], "model_type": "deepseek_v3",
+            "q_lora_rank": int(g.get("attention.q_lora_rank", 0)) or None,
+            "kv_lora_rank": int(g.get("attention.kv_lora_rank", 512)),
+            "qk_rope_head_dim": int(g.get("rope.dimension_count", 64)),
+            "qk_nope_head_dim": int(g.get("attention.key_length", 192)) - int(g.get("rope.dimension_count", 64)),
+            "v_head_dim": int(g.get("attention.value_length", 128)),
+            "n_routed_experts": int(g.get("expert_count", 0)), "num_experts_per_tok": int(g.get("expert_used_count", 6)),
+            "n_shared_experts": int(g.get("expert_shared_count", 1)),
+            "moe_intermediate_size": int(g.get("expert_feed_forward_length", 2048)),
+            "first_k_dense_replace": int(g.get("leading_dense_block_count", 0)),
+            "routed_scaling_factor": float(g.get("expert_weights_scale", 1.0)),
+            "norm_topk_prob": bool(g.get("expert_weights_norm", True)),
+            "scoring_func": "sigmoid" if int(g.get("expert_gating_func", 2)) == 2 else "softmax",
+        })
+    elif a == "deepseek4":
+        cfg.update({"architectures": ["DeepseekV4FlashForCausalLM"], "model_type": "deepseek_v4_flash"})
+    elif a.startswith("qwen2"):
+        cfg.update({"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2"})
+    else:
+        cfg.update({"architectures": ["LlamaForCausalLM"], "model_type": "llama"})
+    return cfg
+
+
+# GGUF tensor name -> HF-style module path used by the model classes
+_LAYER_MAP = {
+    "attn_norm": "input_layernorm", "ffn_norm": "post_attention_layernorm",
+    "attn_q": "self_attn.q_proj", "attn_k": "self_attn.k_proj", "attn_v": "self_attn.v_proj",
+    "attn_output": "self_attn.o_proj", "ffn_gate": "mlp.gate_proj", "ffn_up": "mlp.up_proj",
+    "ffn_down": "mlp.down_proj",
+    "attn_q_a": "self_attn.q_a_proj", "attn_q_a_norm": "self_attn.q_a_layernorm", "attn_q_b": "self_attn.q_b_proj",
+    "attn_kv_a_mqa": "self_attn.kv_a_proj_with_mqa", "attn_kv_a_norm": "self_attn.kv_a_layernorm",
+    "attn_kv_b": "self_attn.kv_b_proj",
+    "ffn_gate_inp": "mlp.gate", "exp_probs_b": "mlp.gate.e_score_correction_bias",
+    "ffn_gate_exps": "mlp.experts.gate_proj", "ffn_up_exps": "mlp.experts.up_proj",
+    "ffn_down_exps": "mlp.experts.down_proj",
+    "ffn_gate_shexp": "mlp.shared_experts.gate_proj", "ffn_up_shexp": "mlp.shared_experts.up_proj",
+    "ffn_down_shexp": "mlp.shared_experts.down_proj",
+}
+
+
+def gguf_to_hf_name(name: str) -> str | None:
+    if name == "token_embd.weight":
+        return "model.embed_tokens.weight"
+    if name == "output_norm.weight":
+        return "model.norm.weight"
+    if name == "output.weight":
+        return "lm_head.weight"
+    parts = name.split(".")
+    if parts[0] == "blk" and len(parts) >= 4:
+        mod = _LAYER_MAP.get(parts[2])
+        if mod is None:
+            return None
+        suffix = parts[3]
+        if parts[2] == "exp_probs_b":
+            return f"model.layers.{parts[1]}.{mod}"
+        return f"model.layers.{parts[1]}.{mod}.{suffix}"
+    return None
+
+
+def iter_gguf_weights(path: str | Path, arch=None):
+    p = Path(path)
+    if p.is_dir():
+        p = sorted(p.glob("*.gguf"))[0]
+    g = GGUFFile(p)
+    for name in g.tensors:
+        hf = gguf_to_hf_name(name)
+        if hf is None:
+            continue
+        yield hf, g.load(name)

@@ -75,3 +75,91 @@ def iter_llama_weights(arch: ModelArch, seed: int = 0, dtype=torch.float32, devi
                 yield p + f"self_attn.{n}_proj.bias", normal(p + n + "b", (r,), seed, dtype=dtype, device=device)
     if not arch.tie_embeddings:
         yield "lm_head.weight", normal("lm_head", (V, H), seed, dtype=dtype, device=device)
+
+
+def iter_gemma4_weights(arch: ModelArch, seed: int = 0, dtype=torch.bfloat16, device="cpu") -> Iterator[tuple[str, torch.Tensor]]:
+    """Gemma4 (dense or MoE) with compressed-tensors style int4 tensors when the arch is quantised."""
+    H, V = arch.hidden_size, arch.vocab_size
+    quant = arch.quant.method != "none"
+    G = arch.quant.group_size if quant else 32
+    sdt = torch.float16 if dtype == torch.float32 else dtype
+
+    def lin(name, out_f, in_f):
+        if quant:
+            pieces = awq_pieces(name, out_f, in_f, G, seed, False, device, sdt)
+            yield f"{name}.weight_packed", pieces["qweight"]
+            yield f"{name}.weight_scale", pieces["scales"]
+        else:
+            yield f"{name}.weight", normal(name, (out_f, in_f), seed, dtype=dtype, device=device)
+
+    yield "model.embed_tokens.weight", normal("model.embed_tokens", (V, H), seed, dtype=dtype, device=device)
+    for i in range(arch.num_layers):
+        p = f"model.layers.{i}."
+        nkv, hd = arch.kv_shape(i)
+        yield from lin(p + "self_attn.q_proj", arch.num_heads * hd, H)
+        yield from lin(p + "self_attn.k_proj", nkv * hd, H)
+        yield from lin(p + "self_attn.v_proj", nkv * hd, H)
+        yield from lin(p + "self_attn.o_proj", H, arch.num_heads * hd)
+        if arch.moe.num_experts:
+            E, I = arch.moe.num_experts, arch.moe.expert_intermediate
+            sh = arch.moe.shared_intermediate or arch.intermediate_size
+            mp = p + "mlp.shared_mlp."
+            yield p + "mlp.router.proj.weight", normal(p + "router", (E, H), seed, dtype=dtype, device=device)
+            gu = awq_pieces(p + "experts.gu", E * 2 * I, H, G, seed, False, device, sdt)
+            dn = awq_pieces(p + "experts.dn", E * H, I, G, seed, False, device, sdt)
+            yield p + "mlp.experts.gate_up_proj.weight_packed", gu["qweight"].view(E, 2 * I, H // 8)
+            yield p + "mlp.experts.gate_up_proj.weight_scale", gu["scales"].view(E, 2 * I, H // G)
+            yield p + "mlp.experts.down_proj.weight_packed", dn["qweight"].view(E, H, I // 8)
+            yield p + "mlp.experts.down_proj.weight_scale", dn["scales"].view(E, H, I // G)
+        else:
+            sh = arch.intermediate_size
+            mp = p + "mlp."
+        yield from lin(mp + "gate_proj", sh, H)
+        yield from lin(mp + "up_proj", sh, H)
+        yield from lin(mp + "down_proj", H, sh)
+    if not arch.tie_embeddings:
+        yield "lm_head.weight", normal("lm_head", (V, H), seed, dtype=dtype, device=device)
+
+
+def iter_deepseek_weights(arch: ModelArch, seed: int = 0, dtype=torch.bfloat16, device="cpu") -> Iterator[tuple[str, object]]:
+    """DeepSeek MLA+MoE in GGUF block formats: routed experts IQ2_XXS (gate, up) and Q2_K (down),
+    every other matrix Q8_0, norms and router in float."""
+    from ..loaders.gguf import GGUFTensor
+    from ..ops import gguf_quant as gq
+    H, V, m, mo = arch.hidden_size, arch.vocab_size, arch.mla, arch.moe
+    qk = m.qk_nope_dim + m.qk_rope_dim
+
+    def q8(name, rows, K, scale=0.004):
+        return GGUFTensor(gq.random_blocks(8, rows, K, zlib.crc32(name.encode()) + seed, scale, device), 8, (rows, K))
+
+    def blocks(name, ty, E, rows, K, scale):
+        raw = gq.random_blocks(ty, E * rows, K, zlib.crc32(name.encode()) + seed, scale, device)
+        return GGUFTensor(raw.view(E, rows, -1), ty, (E, rows, K))
+
+    yield "model.embed_tokens.weight", normal("embed", (V, H), seed, dtype=dtype, device=device)
+    for i in range(arch.num_layers):
+        p = f"model.layers.{i}."
+        if m.q_lora_rank:
+            yield p + "self_attn.q_a_proj.weight", q8(p + "qa", m.q_lora_rank, H)
+            yield p + "self_attn.q_b_proj.weight", q8(p + "qb", arch.num_heads * qk, m.q_lora_rank)
+        else:
+            yield p + "self_attn.q_proj.weight", q8(p + "q", arch.num_heads * qk, H)
+        yield p + "self_attn.kv_a_proj_with_mqa.weight", q8(p + "kva", m.kv_lora_rank + m.qk_rope_dim, H)
+        yield p + "self_attn.kv_b_proj.weight", q8(p + "kvb", arch.num_heads * (m.qk_nope_dim + m.v_head_dim), m.kv_lora_rank)
+        yield p + "self_attn.o_proj.weight", q8(p + "o", H, arch.num_heads * m.v_head_dim)
+        if mo.num_experts and i >= mo.first_dense_layers:
+            yield p + "mlp.gate.weight", normal(p + "router", (mo.num_experts, H), seed, dtype=torch.float32, device=device)
+            yield p + "mlp.gate.e_score_correction_bias", normal(p + "rb", (mo.num_experts,), seed, 0.01, torch.float32, device)
+            I = mo.expert_intermediate
+            yield p + "mlp.experts.gate_proj.weight", blocks(p + "eg", 16, mo.num_experts, I, H, 0.02)
+            yield p + "mlp.experts.up_proj.weight", blocks(p + "eu", 16, mo.num_experts, I, H, 0.02)
+            yield p + "mlp.experts.down_proj.weight", blocks(p + "ed", 10, mo.num_experts, H, I, 0.02)
+            if mo.shared_intermediate:
+                yield p + "mlp.shared_experts.gate_proj.weight", q8(p + "sg", mo.shared_intermediate, H)
+                yield p + "mlp.shared_experts.up_proj.weight", q8(p + "su", mo.shared_intermediate, H)
+                yield p + "mlp.shared_experts.down_proj.weight", q8(p + "sd", H, mo.shared_intermediate)
+        else:
+            yield p + "mlp.gate_proj.weight", q8(p + "g", arch.intermediate_size, H)
+            yield p + "mlp.up_proj.weight", q8(p + "u", arch.intermediate_size, H)
+            yield p + "mlp.down_proj.weight", q8(p + "d", H, arch.intermediate_size)
+    yield "lm_head.weight", q8("lm_head", V, H)

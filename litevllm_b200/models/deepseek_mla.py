@@ -1,0 +1,301 @@
+"""DeepSeek-V2/V3-style decoder: multi-head latent attention (MLA) + mixture of experts.
+
+Attention: ``q = q_b(norm(q_a(x)))`` (or a direct q projection), ``[latent | k_rope] = kv_a(x)``,
+``[k_nope | v] = kv_b(norm(latent))``; rotary on the 64 rope channels of q and of the shared k_rope;
+softmax scale ``1/sqrt(nope + rope)``.  This implementation materialises per-head keys/values into
+the paged cache (head layout ``[rope | nope | pad]`` so the rotary kernel's "first rot_dim channels"
+convention applies; keys and values are padded to a common 256-wide head) and reuses the paged
+attention kernels; the latent-absorbed cache form is a later optimisation.
+MoE: router ``gate`` with sigmoid (or softmax) scoring, selection bias, top-k, renormalisation and
+routed scaling; routed experts stay in their GGUF block formats (IQ2_XXS / Q2_K / Q8_0) and run
+through the routed-expert kernels; shared experts and the leading dense layers are ordinary gated
+MLPs.  Experts are sharded over expert-parallel ranks, attention over tensor-parallel ranks.
+Reference: the reference serves only the V4-Flash variant (vllm/model_executor/models/
+deepseek_v4_flash/*); its MoE numerics (sigmoid/softplus scoring, shared expert, clamp) are followed.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..layers.linear import LiteLinear
+from ..layers.rope import get_cos_sin
+from ..ops import gguf_quant as gq
+from ..ops import moe as moe_ops
+from ..ops import _lib, _p, _stream, _count, scratch
+from ..parallel import state as pstate
+from .arch import ModelArch
+from .llama import RMSNormWeight
+
+PAD_HD = 256
+
+
+class MLAAttention(nn.Module):
+    def __init__(self, arch: ModelArch, i: int, dtype, qc, prefix: str):
+        super().__init__()
+        m = arch.mla
+        tp = pstate.tp_size()
+        self.nh_total, self.nh = arch.num_heads, arch.num_heads // tp
+        self.nope, self.rope, self.vd, self.kv_lora, self.q_lora = m.qk_nope_dim, m.qk_rope_dim, m.v_head_dim, m.kv_lora_rank, m.q_lora_rank
+        self.qk = self.nope + self.rope
+        assert self.qk <= PAD_HD and self.vd <= PAD_HD
+        H = arch.hidden_size
+        if self.q_lora:
+            self.q_a_proj = LiteLinear(H, self.q_lora, dtype=dtype, quant_config=qc, prefix=prefix + ".q_a_proj")
+            self.q_a_layernorm = RMSNormWeight(self.q_lora, arch.rms_eps, dtype)
+            self.q_b_proj = LiteLinear(self.q_lora, self.nh_total * self.qk, dtype=dtype, shard="column",
+                                       quant_config=qc, prefix=prefix + ".q_b_proj")
+        else:
+            self.q_proj = LiteLinear(H, self.nh_total * self.qk, dtype=dtype, shard="column", quant_config=qc,
+                                     prefix=prefix + ".q_proj")
+        self.kv_a_proj_with_mqa = LiteLinear(H, self.kv_lora + self.rope, dtype=dtype, quant_config=qc,
+                                             prefix=prefix + ".kv_a_proj_with_mqa")
+        self.kv_a_layernorm = RMSNormWeight(self.kv_lora, arch.rms_eps, dtype)
+        self.kv_b_proj = LiteLinear(self.kv_lora, self.nh_total * (self.nope + self.vd), dtype=dtype, shard="column",
+                                    quant_config=qc, prefix=prefix + ".kv_b_proj")
+        self.o_proj = LiteLinear(self.nh_total * self.vd, H, dtype=dtype, shard="row", quant_config=qc,
+                                 prefix=prefix + ".o_proj")
+        self.sm_scale = self.qk ** -0.5
+        self.rope_theta, self.rope_scaling = arch.rope_theta, arch.rope_scaling
+        self._cos_sin = None
+
+    def cos_sin(self, device, max_pos):
+        if self._cos_sin is None or self._cos_sin.device != device:
+            self._cos_sin = get_cos_sin(self.rope, max_pos, self.rope_theta, None, device)
+        return self._cos_sin
+
+    def forward(self, x, h, batch, kv, max_pos):
+        T = x.shape[0]
+        if self.q_lora:
+            q = self.q_b_proj(self.q_a_layernorm(self.q_a_proj(x)))
+        else:
+            q = self.q_proj(x)
+        q = q.view(T, self.nh, self.qk)
+        kva = self.kv_a_proj_with_mqa(x)
+        latent = self.kv_a_layernorm(kva[:, : self.kv_lora].contiguous())
+        k_rope = kva[:, self.kv_lora:]
+        kvb = self.kv_b_proj(latent).view(T, self.nh, self.nope + self.vd)
+        # assemble [q | k | v] with padded heads laid out [rope | nope | 0]
+        buf = torch.zeros(T, 3 * self.nh, PAD_HD, dtype=x.dtype, device=x.device)
+        buf[:, : self.nh, : self.rope] = q[..., self.nope:]
+        buf[:, : self.nh, self.rope:self.qk] = q[..., : self.nope]
+        buf[:, self.nh:2 * self.nh, : self.rope] = k_rope[:, None, :]
+        buf[:, self.nh:2 * self.nh, self.rope:self.qk] = kvb[..., : self.nope]
+        buf[:, 2 * self.nh:, : self.vd] = kvb[..., self.nope:]
+        qkv = buf.view(T, 3 * self.nh * PAD_HD)
+        k_cache, v_cache = kv
+        cfg = batch.config
+        ops.rope_and_cache(qkv, batch.positions, self.cos_sin(x.device, max_pos), batch.slot_mapping, k_cache, v_cache,
+                           self.nh, self.nh, PAD_HD, self.rope, k_scale=cfg.k_scale, v_scale=cfg.v_scale)
+        if batch.is_decode:
+            attn = ops.paged_attention_decode(qkv, k_cache, v_cache, batch.block_tables, batch.seq_lens, self.nh,
+                                              self.nh, PAD_HD, self.sm_scale, 0, 0.0, cfg.k_scale, cfg.v_scale,
+                                              max_kv_len=batch.max_kv_len)
+        else:
+            attn = ops.paged_attention_prefill(qkv, k_cache, v_cache, batch.block_tables, batch.seq_lens, batch.cu_q,
+                                               batch.max_q_len, self.nh, self.nh, PAD_HD, self.sm_scale, 0, 0.0,
+                                               cfg.k_scale, cfg.v_scale)
+        o_in = attn.view(T, self.nh, PAD_HD)[..., : self.vd].reshape(T, self.nh * self.vd)
+        return self.o_proj(o_in, residual=h, out=h)
+
+
+class GatedMLP(nn.Module):
+    def __init__(self, H: int, inter: int, dtype, qc, prefix: str, act: str = "silu"):
+        super().__init__()
+        self.gate_up_proj = LiteLinear(H, 2 * inter, dtype=dtype, shard="column", quant_config=qc,
+                                       prefix=prefix + ".gate_up_proj", gated_act=act, out_splits=[inter, inter])
+        self.down_proj = LiteLinear(inter, H, dtype=dtype, shard="row", quant_config=qc, prefix=prefix + ".down_proj")
+
+    def forward(self, x, residual=None):
+        return self.down_proj(self.gate_up_proj(x), residual=residual, out=residual)
+
+
+class RoutedExperts(nn.Module):
+    """Routed experts kept as raw GGUF blocks: gate/up ``[E, I, row bytes]``, down ``[E, H, row bytes]``."""
+
+    def __init__(self, arch: ModelArch, dtype):
+        super().__init__()
+        ep, r = pstate.ep_size(), pstate.ep_rank()
+        self.E, self.I, self.H, self.top_k = arch.moe.num_experts, arch.moe.expert_intermediate, arch.hidden_size, arch.moe.top_k
+        self.e_local = self.E // ep
+        self.e_lo = r * self.e_local
+        self.device = torch.empty(0).device
+        self.dtype = dtype
+        self.raw: dict[str, torch.Tensor] = {}
+        self.types: dict[str, int] = {}
+        self.clamp = float(arch.extra.get("swiglu_clamp", 0.0))
+
+    def load(self, which: str, t) -> None:
+        from ..loaders.gguf import GGUFTensor
+        if isinstance(t, GGUFTensor):
+            self.raw[which] = t.raw[self.e_lo:self.e_lo + self.e_local].contiguous().to(self.device)
+            self.types[which] = t.ggml_type
+        else:   # float experts: store as Q8_0 blocks so one code path serves them
+            w = t[self.e_lo:self.e_lo + self.e_local].float()
+            E, R, K = w.shape
+            self.raw[which] = gq.quantize_q8_0(w.reshape(E * R, K)).view(E, R, -1).to(self.device)
+            self.types[which] = 8
+
+    def forward(self, x, ids, weights):
+        T, H = x.shape
+        K = ids.shape[1]
+        n = T * K
+        if not x.is_cuda:
+            out = torch.zeros(T, H, dtype=torch.float32)
+            g = gq.dequantize(self.raw["gate"].reshape(-1, self.raw["gate"].shape[-1]), self.types["gate"], H).view(self.e_local, self.I, H)
+            u = gq.dequantize(self.raw["up"].reshape(-1, self.raw["up"].shape[-1]), self.types["up"], H).view(self.e_local, self.I, H)
+            d = gq.dequantize(self.raw["down"].reshape(-1, self.raw["down"].shape[-1]), self.types["down"], self.I).view(self.e_local, H, self.I)
+            xf = x.float()
+            for e in range(self.e_local):
+                tok, slot = torch.nonzero(ids == e + self.e_lo, as_tuple=True)
+                if tok.numel() == 0:
+                    continue
+                gv, uv = xf[tok] @ g[e].t(), xf[tok] @ u[e].t()
+                if self.clamp > 0:
+                    gv, uv = gv.clamp(max=self.clamp), uv.clamp(-self.clamp, self.clamp)
+                a = (torch.nn.functional.silu(gv) * uv).to(x.dtype).float()
+                y = (a @ d[e].t()).to(x.dtype).float()
+                out.index_add_(0, tok, y * weights[tok, slot][:, None])
+            out = out.to(x.dtype)
+        else:
+            lib = _lib.kernels()
+            esz = x.element_size()
+            buf = scratch("ds_moe", n * (self.I + H) * esz + 4 * n + 256, x.device)
+            a = buf[: n * self.I * esz].view(x.dtype).view(n, self.I)
+            y = buf[n * self.I * esz: n * (self.I + H) * esz].view(x.dtype).view(n, H)
+            slot_of = buf[n * (self.I + H) * esz: n * (self.I + H) * esz + 4 * n].view(torch.int32)
+            if getattr(self, "_arange_n", 0) != n:
+                self._arange = torch.arange(n, dtype=torch.int32, device=x.device)
+                self._arange_n = n
+            slot_of.copy_(self._arange)
+            e_hi = self.e_lo + self.e_local
+            ids_flat = ids.reshape(-1)
+            rc = lib.fi_gguf_moe_gate_up(_p(x), x.stride(0), _p(self.raw["gate"]), _p(self.raw["up"]),
+                                         self.types["gate"], self.types["up"], self.raw["gate"].shape[-1],
+                                         self.raw["up"].shape[-1], _p(ids_flat), n, K, self.e_lo, e_hi, self.I, H,
+                                         self.clamp, _p(a), _stream())
+            _lib.check(rc, "fi_gguf_moe_gate_up")
+            rc = lib.fi_gguf_moe_down(_p(a), _p(self.raw["down"]), self.types["down"], self.raw["down"].shape[-1],
+                                      _p(ids_flat), n, self.e_lo, e_hi, H, self.I, _p(y), _stream())
+            _lib.check(rc, "fi_gguf_moe_down")
+            out = torch.empty(T, H, dtype=x.dtype, device=x.device)
+            rc = lib.fi_moe_combine(_p(y), _p(slot_of), _p(weights), None, _p(out), T, K, H, ops._DT[x.dtype], _stream())
+            _lib.check(rc, "fi_moe_combine")
+            _count(3)
+        if pstate.ep_size() > 1:
+            from ..parallel import fused_ops
+            out = fused_ops.all_reduce_activations(out)
+        return out
+
+
+class DeepseekMoE(nn.Module):
+    def __init__(self, arch: ModelArch, dtype, qc, prefix: str):
+        super().__init__()
+        E, H = arch.moe.num_experts, arch.hidden_size
+        self.gate = nn.Parameter(torch.empty(E, H, dtype=dtype), requires_grad=False)
+        self.e_score_correction_bias = nn.Parameter(torch.zeros(E, dtype=torch.float32), requires_grad=False)
+        self.experts = RoutedExperts(arch, dtype)
+        self.mode, self.renorm, self.scale, self.top_k = arch.moe.router, arch.moe.renormalize, arch.moe.routed_scaling, arch.moe.top_k
+        self.shared_experts = GatedMLP(H, arch.moe.shared_intermediate, dtype, qc, prefix + ".shared_experts") \
+            if arch.moe.shared_intermediate else None
+
+    def forward(self, x, h):
+        logits = ops.linear(x, self.gate, out_dtype=torch.float32)
+        bias = self.e_score_correction_bias if self.mode != "softmax" else None
+        ids, w = moe_ops.route(logits, self.top_k, self.mode, bias, None, self.renorm, self.scale)
+        routed = self.experts(x, ids, w)
+        if self.shared_experts is not None:
+            h = self.shared_experts(x, residual=h)
+        return h.add_(routed) if h.is_cuda or True else h + routed
+
+
+class DeepseekDecoderLayer(nn.Module):
+    def __init__(self, arch: ModelArch, i: int, dtype, qc):
+        super().__init__()
+        p = f"model.layers.{i}"
+        self.input_layernorm = RMSNormWeight(arch.hidden_size, arch.rms_eps, dtype)
+        self.post_attention_layernorm = RMSNormWeight(arch.hidden_size, arch.rms_eps, dtype)
+        self.self_attn = MLAAttention(arch, i, dtype, qc, p + ".self_attn")
+        self.is_moe = arch.moe.num_experts > 0 and i >= arch.moe.first_dense_layers
+        if self.is_moe:
+            self.mlp = DeepseekMoE(arch, dtype, qc, p + ".mlp")
+        else:
+            self.mlp = GatedMLP(arch.hidden_size, arch.intermediate_size, dtype, qc, p + ".mlp")
+
+    def forward(self, h, batch, kv, max_pos):
+        h = self.self_attn(self.input_layernorm(h), h, batch, kv, max_pos)
+        x = self.post_attention_layernorm(h)
+        if self.is_moe:
+            return self.mlp(x, h)
+        return self.mlp(x, residual=h)
+
+
+class DeepseekMLAForCausalLM(nn.Module):
+    supports_lora = False
+    supports_multimodal = False
+
+    def __init__(self, vllm_config):
+        super().__init__()
+        mc = vllm_config.model_config
+        arch: ModelArch = mc.arch
+        self.arch, self.dtype = arch, mc.dtype
+        qc = vllm_config.quant_config
+        self.embed_tokens = nn.Parameter(torch.empty(arch.vocab_size, arch.hidden_size, dtype=mc.dtype), requires_grad=False)
+        self.layers = nn.ModuleList([DeepseekDecoderLayer(arch, i, mc.dtype, qc) for i in range(arch.num_layers)])
+        self.norm = RMSNormWeight(arch.hidden_size, arch.rms_eps, mc.dtype)
+        self.lm_head = LiteLinear(arch.hidden_size, arch.vocab_size, dtype=mc.dtype, shard="column",
+                                  quant_config=qc, prefix="lm_head")
+        self.max_pos = max(mc.max_model_len, 16)
+
+    def kv_cache_specs(self):
+        return [(l.self_attn.nh, PAD_HD) for l in self.layers]
+
+    def forward(self, batch, kv_caches, inputs_embeds=None):
+        h = inputs_embeds if inputs_embeds is not None else ops.embedding(batch.input_ids, self.embed_tokens)
+        for i, layer in enumerate(self.layers):
+            h = layer(h, batch, kv_caches[i], self.max_pos)
+        last = h if batch.logits_indices is None else h.index_select(0, batch.logits_indices)
+        logits = self.lm_head(self.norm(last), out_dtype=torch.float32)
+        if self.lm_head.tp > 1:
+            logits = pstate.all_gather_last_dim(logits)
+        return logits
+
+    def load_weights(self, weights):
+        from ..loaders.gguf import GGUFTensor
+        from ..loaders.weight_utils import finalize_quantized, load_mapped
+        m: dict = {"model.norm": ("norm", self.norm), "lm_head": ("linear", self.lm_head, 0, None)}
+
+        def load_embed(suffix, t):
+            w = gq.dequantize(t.raw, t.ggml_type, t.shape[-1]) if isinstance(t, GGUFTensor) else t
+            self.embed_tokens.data.copy_(w.to(self.embed_tokens.dtype))
+        m["model.embed_tokens"] = ("custom", load_embed)
+        for i, L in enumerate(self.layers):
+            p = f"model.layers.{i}."
+            at = L.self_attn
+            m[p + "input_layernorm"] = ("norm", L.input_layernorm)
+            m[p + "post_attention_layernorm"] = ("norm", L.post_attention_layernorm)
+            for n in ("q_a_proj", "q_b_proj", "q_proj", "kv_a_proj_with_mqa", "kv_b_proj", "o_proj"):
+                if hasattr(at, n):
+                    m[p + "self_attn." + n] = ("linear", getattr(at, n), 0, None)
+            if at.q_lora:
+                m[p + "self_attn.q_a_layernorm"] = ("norm", at.q_a_layernorm)
+            m[p + "self_attn.kv_a_layernorm"] = ("norm", at.kv_a_layernorm)
+            if L.is_moe:
+                mo = L.mlp
+                m[p + "mlp.gate"] = ("custom", lambda s, t, mo=mo: (mo.gate.data.copy_(t.to(mo.gate.dtype)) if s == "weight"
+                                                                   else mo.e_score_correction_bias.data.copy_(t.float())))
+                for w in ("gate", "up", "down"):
+                    m[p + f"mlp.experts.{w}_proj"] = ("custom", lambda s, t, X=mo.experts, w=w: X.load(w, t))
+                if mo.shared_experts is not None:
+                    se = mo.shared_experts
+                    m[p + "mlp.shared_experts.gate_proj"] = ("linear", se.gate_up_proj, 0, None)
+                    m[p + "mlp.shared_experts.up_proj"] = ("linear", se.gate_up_proj, 1, None)
+                    m[p + "mlp.shared_experts.down_proj"] = ("linear", se.down_proj, 0, None)
+            else:
+                m[p + "mlp.gate_proj"] = ("linear", L.mlp.gate_up_proj, 0, None)
+                m[p + "mlp.up_proj"] = ("linear", L.mlp.gate_up_proj, 1, None)
+                m[p + "mlp.down_proj"] = ("linear", L.mlp.down_proj, 0, None)
+        consumed = load_mapped(m, weights)
+        finalize_quantized(self)
+        return consumed

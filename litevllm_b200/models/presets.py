@@ -62,6 +62,23 @@ PRESETS["tiny-llama-awq-test"] = dict(PRESETS["tiny-llama-test"], quantization_c
 PRESETS["tiny-llama-ct-test"] = dict(PRESETS["tiny-llama-test"], quantization_config={
     "quant_method": "compressed-tensors", "format": "pack-quantized",
     "config_groups": {"group_0": {"weights": {"num_bits": 4, "group_size": 32, "symmetric": True}}}})
+PRESETS["tiny-gemma4-moe-test"] = {
+    "architectures": ["Gemma4ForConditionalGeneration"], "model_type": "gemma4",
+    "text_config": {"model_type": "gemma4_text", "hidden_size": 256, "num_hidden_layers": 3,
+                    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 192,
+                    "vocab_size": 512, "rms_norm_eps": 1e-6, "sliding_window": 32, "sliding_window_pattern": 3,
+                    "attn_logit_softcapping": 50.0, "final_logit_softcapping": 30.0, "rope_local_base_freq": 10000.0,
+                    "rope_global_base_freq": 1000000.0, "max_position_embeddings": 512, "num_experts": 8,
+                    "top_k_experts": 2, "moe_intermediate_size": 128, "tie_word_embeddings": True, "eos_token_id": 1},
+    "quantization_config": {"quant_method": "compressed-tensors", "format": "pack-quantized",
+                            "config_groups": {"group_0": {"weights": {"num_bits": 4, "group_size": 32,
+                                                                       "symmetric": True}}}},
+}
+PRESETS["tiny-deepseek-test"] = dict(PRESETS["deepseek-mla-moe"], hidden_size=256, num_hidden_layers=2,
+                                     num_attention_heads=4, num_key_value_heads=4, q_lora_rank=64, kv_lora_rank=64,
+                                     qk_rope_head_dim=64, qk_nope_head_dim=64, v_head_dim=64, intermediate_size=256,
+                                     moe_intermediate_size=256, n_routed_experts=8, num_experts_per_tok=2,
+                                     vocab_size=512, max_position_embeddings=512)
 
 
 def get_preset(name: str) -> dict:

@@ -118,11 +118,14 @@ def gated_linear(x, w_gate_up, act="silu", out=None, splits=0, bn=0):
 
 
 # ---------------------------------------------------------------------------- norms
-def rmsnorm(x, w, eps, residual=None, w_mode=0, out=None, out_scale=1.0):
+def rmsnorm(x, w, eps, residual=None, w_mode=0, out=None, out_scale=1.0, addend=None):
     """RMSNorm over the last dim of a 2-D tensor.  With ``residual`` the sum x+residual is written
-    back into ``residual`` first (in place) and normalised.  Returns ``out``."""
+    back into ``residual`` first (in place) and normalised.  With ``addend`` the result is
+    ``norm(x) * w + addend`` (sandwich-norm residual add).  Returns ``out``."""
     if not x.is_cuda:
         y, new_res = reference.rmsnorm(x, w, eps, residual, w_mode, out_scale)
+        if addend is not None:
+            y = (y.float() + addend.float()).to(y.dtype)
         if residual is not None:
             residual.copy_(new_res)
         if out is not None:
@@ -135,7 +138,7 @@ def rmsnorm(x, w, eps, residual=None, w_mode=0, out=None, out_scale=1.0):
     if residual is not None:
         assert residual.stride(0) == x.stride(0)
     rc = _lib.kernels().fi_rmsnorm(_p(x), _p(residual), _p(w), _p(out), rows, H, x.stride(0),
-                                   out.stride(0), eps, w_mode, out_scale, _DT[x.dtype], _stream())
+                                   out.stride(0), eps, w_mode, out_scale, _DT[x.dtype], _stream(), _p(addend))
     _lib.check(rc, "fi_rmsnorm")
     _count()
     return out

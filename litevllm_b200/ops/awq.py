@@ -104,6 +104,8 @@ def int4_linear(x: torch.Tensor, w: Int4Weight, bias=None, residual=None, act=No
             out.copy_(y)
             return out
         return y
+    if w.qw is None:
+        raise RuntimeError("int4 weight is not in the device runtime layout (was it loaded on the CPU?)")
     T, K = x.shape
     N = w.N // 2 if gated_act else w.N
     out_dtype = out_dtype or x.dtype

@@ -124,3 +124,8 @@ def allgather_gemm(x_shard: torch.Tensor, w: torch.Tensor, T_total: int, rows_pe
     _lib.check(rc, "fi_dense_gemm_comm(all_gather)")
     ops._count()
     return out
+
+
+def all_reduce_activations(x: torch.Tensor) -> torch.Tensor:
+    """Sum a replicated-layout activation over the ranks (expert-parallel combine)."""
+    return pstate.all_reduce(x)

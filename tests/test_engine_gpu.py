@@ -80,3 +80,33 @@ def test_sampling_with_seed_is_reproducible():
     a = [o.outputs[0].token_ids for o in llm.generate(p, sp)]
     b = [o.outputs[0].token_ids for o in llm.generate(p, sp)]
     assert a == b
+
+
+def _prefill_logits(llm, prompts):
+    eng = llm.engine
+    eng._build_lazy()
+    for i, p in enumerate(prompts):
+        eng.add_request(f"lg{i}", p, SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))
+    plan = eng.step_scheduler.build_plan(eng.scheduler)
+    eng.controller._admit(plan)
+    eng.backend.ensure_kv_blocks(plan)
+    with torch.inference_mode():
+        res = eng.prefill_executor.execute(plan.prefills, eng.scheduler.requests)
+    return res.logits.float().cpu()
+
+
+@pytest.mark.parametrize("preset,min_cos", [("tiny-gemma4-moe-test", 0.96), ("tiny-llama-awq-test", 0.99),
+                                             ("tiny-llama-ct-test", 0.99), ("tiny-deepseek-test", 0.97)])
+def test_quantised_models_match_cpu_oracle(preset, min_cos):
+    """int4 weights (+ fp8 KV, MoE routing for Gemma4): GPU kernels vs the CPU fp32 path on the same
+    synthetic checkpoint."""
+    kw = dict(max_num_seqs=4, max_model_len=128)
+    prompts = _prompts(512, (40, 7, 64))
+    gpu = LLM(f"synthetic:{preset}", dtype="bfloat16", device="cuda:0", **kw)
+    cpu = LLM(f"synthetic:{preset}", dtype="float32", device="cpu", **kw)
+    a, b = _prefill_logits(gpu, prompts), _prefill_logits(cpu, prompts)
+    cos = torch.nn.functional.cosine_similarity(a, b, dim=-1)
+    assert float(cos.min()) > min_cos, cos
+    outs = gpu.generate(_prompts(512, (9, 33)), SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    assert all(len(o.outputs[0].token_ids) == 8 for o in outs)
+    ops.check_status(torch.device("cuda:0"))

@@ -1,0 +1,97 @@
+"""GGUF reader/writer round trip and header validation (CPU)."""
+import struct
+
+import pytest
+import torch
+
+from litevllm_b200.loaders.gguf import GGUFFile, GGUFTensor, gguf_to_hf_name, hf_config_from_gguf, write_gguf
+from litevllm_b200.ops import gguf_quant as gq
+
+
+def test_round_trip(tmp_path):
+    raw = gq.random_blocks(gq.GGML_TYPES["Q2_K"], 6, 512, seed=1)
+    tensors = {"token_embd.weight": torch.randn(10, 8), "blk.0.attn_q.weight": GGUFTensor(raw, 10, (6, 512)),
+               "blk.0.ffn_down_exps.weight": GGUFTensor(gq.random_blocks(16, 2 * 4, 256, 2).view(2, 4, -1), 16, (2, 4, 256)),
+               "blk.0.attn_norm.weight": torch.ones(8, dtype=torch.float16)}
+    meta = {"general.architecture": "llama", "llama.block_count": 1, "llama.embedding_length": 8,
+            "llama.attention.head_count": 2, "llama.rope.freq_base": 10000.0, "general.name": "t",
+            "llama.some_list": [1, 2, 3]}
+    f = tmp_path / "m.gguf"
+    write_gguf(f, meta, tensors)
+    g = GGUFFile(f)
+    assert g.arch() == "llama" and g.metadata["llama.some_list"] == [1, 2, 3]
+    assert torch.equal(g.load("token_embd.weight"), tensors["token_embd.weight"])
+    q = g.load("blk.0.attn_q.weight")
+    assert q.ggml_type == 10 and q.shape == (6, 512) and torch.equal(q.raw, raw)
+    e = g.load("blk.0.ffn_down_exps.weight")
+    assert e.shape == (2, 4, 256) and e.raw.shape == (2, 4, 66)
+    cfg = hf_config_from_gguf(f)
+    assert cfg["hidden_size"] == 8 and cfg["architectures"] == ["LlamaForCausalLM"]
+    assert gguf_to_hf_name("blk.3.ffn_gate_exps.weight") == "model.layers.3.mlp.experts.gate_proj.weight"
+    assert gguf_to_hf_name("blk.3.exp_probs_b.bias") == "model.layers.3.mlp.gate.e_score_correction_bias"
+
+
+def test_rejects_bad_files(tmp_path):
+    bad = tmp_path / "bad.gguf"
+    bad.write_bytes(b"NOPE" + b"\0" * 64)
+    with pytest.raises(ValueError, match="magic"):
+        GGUFFile(bad)
+    v2 = tmp_path / "v2.gguf"
+    v2.write_bytes(struct.pack("<IIQQ", 0x46554747, 2, 0, 0) + b"\0" * 32)
+    with pytest.raises(ValueError, match="version 3"):
+        GGUFFile(v2)
+    trunc = tmp_path / "trunc.gguf"
+    write_gguf(trunc, {"general.architecture": "llama"}, {"a.weight": torch.randn(64, 64)})
+    data = trunc.read_bytes()
+    trunc.write_bytes(data[: len(data) - 4096])
+    with pytest.raises(ValueError, match="past the end"):
+        GGUFFile(trunc)
+
+
+def _hf_to_gguf_name(name: str) -> str:
+    from litevllm_b200.loaders.gguf import _LAYER_MAP
+    if name == "model.embed_tokens.weight":
+        return "token_embd.weight"
+    if name == "lm_head.weight":
+        return "output.weight"
+    if name == "model.norm.weight":
+        return "output_norm.weight"
+    parts = name.split(".")
+    layer, rest = parts[2], ".".join(parts[3:])
+    inv = {v: k for k, v in _LAYER_MAP.items()}
+    if rest == "mlp.gate.e_score_correction_bias":
+        return f"blk.{layer}.exp_probs_b.bias"
+    mod, _, suffix = rest.rpartition(".")
+    return f"blk.{layer}.{inv[mod]}.{suffix}"
+
+
+def test_deepseek_gguf_file_end_to_end(tmp_path):
+    """A synthetic DeepSeek-style GGUF file (Q8_0 / IQ2_XXS / Q2_K tensors under GGUF names) loads
+    through ``LLM(path)`` and generates exactly what the in-memory synthetic model generates."""
+    from litevllm_b200 import LLM, SamplingParams
+    from litevllm_b200.loaders import synth
+    from litevllm_b200.models.arch import arch_from_hf_config
+    from litevllm_b200.models.presets import get_preset
+    cfg = get_preset("tiny-deepseek-test")
+    arch = arch_from_hf_config(cfg)
+    tensors = {_hf_to_gguf_name(n): t for n, t in synth.iter_deepseek_weights(arch, 0, torch.float32, "cpu")}
+    meta = {"general.architecture": "deepseek2", "deepseek2.block_count": 2, "deepseek2.embedding_length": 256,
+            "deepseek2.attention.head_count": 4, "deepseek2.attention.head_count_kv": 4,
+            "deepseek2.feed_forward_length": 256, "deepseek2.attention.layer_norm_rms_epsilon": 1e-6,
+            "deepseek2.rope.freq_base": 10000.0, "deepseek2.context_length": 512, "deepseek2.vocab_size": 512,
+            "deepseek2.attention.q_lora_rank": 64, "deepseek2.attention.kv_lora_rank": 64,
+            "deepseek2.rope.dimension_count": 64, "deepseek2.attention.key_length": 128,
+            "deepseek2.attention.value_length": 64, "deepseek2.expert_count": 8, "deepseek2.expert_used_count": 2,
+            "deepseek2.expert_shared_count": 1, "deepseek2.expert_feed_forward_length": 256,
+            "deepseek2.leading_dense_block_count": 0, "deepseek2.expert_weights_scale": 1.0,
+            "deepseek2.expert_weights_norm": True, "deepseek2.expert_gating_func": 2,
+            "tokenizer.ggml.eos_token_id": 1}
+    f = tmp_path / "tiny-deepseek.gguf"
+    write_gguf(f, meta, tensors)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (5, 20)]
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+    kw = dict(dtype="float32", device="cpu", max_num_seqs=2, max_model_len=64)
+    from_file = [o.outputs[0].token_ids for o in LLM(str(f), **kw).generate(prompts, sp)]
+    in_memory = [o.outputs[0].token_ids for o in LLM("synthetic:tiny-deepseek-test", **kw).generate(prompts, sp)]
+    assert from_file == in_memory

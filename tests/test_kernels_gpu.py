@@ -268,3 +268,67 @@ def test_fused_collective_wait_is_bounded():
     # the context still works
     y = ops.linear(x, w)
     _close(y, ref.linear(x, w, out_dtype=torch.float32), 3e-2, 3e-2, "gemm after timeout")
+
+
+@pytest.mark.parametrize("mode,E,K", [("softmax", 128, 8), ("sigmoid", 256, 6), ("sqrt_softplus", 64, 4), ("softmax", 8, 2)])
+def test_moe_route(mode, E, K):
+    from litevllm_b200.ops import moe
+    torch.manual_seed(10)
+    logits = torch.randn(37, E, device=DEV)
+    bias = torch.randn(E, device=DEV) * 0.1 if mode != "softmax" else None
+    scale = torch.rand(E, device=DEV) + 0.5 if mode == "softmax" else None
+    ids, w = moe.route(logits, K, mode, bias, scale, True, 1.5)
+    ids_r, w_r = moe.route(logits.cpu(), K, mode, None if bias is None else bias.cpu(),
+                           None if scale is None else scale.cpu(), True, 1.5)
+    assert torch.equal(ids.cpu().sort(-1).values, ids_r.sort(-1).values)
+    order = ids.cpu().argsort(-1), ids_r.argsort(-1)
+    _close(torch.gather(w.cpu(), 1, order[0]), torch.gather(w_r, 1, order[1]), 1e-4, 1e-5, "router weights")
+
+
+@pytest.mark.parametrize("T,E,K,H,I,e_lo,e_n", [(1, 16, 4, 256, 128, 0, 16), (32, 16, 4, 512, 192, 0, 16),
+                                                (200, 8, 2, 256, 704, 0, 8), (24, 16, 4, 256, 128, 4, 8)])
+def test_fused_experts_int4(T, E, K, H, I, e_lo, e_n):
+    from litevllm_b200.ops import awq, moe
+    torch.manual_seed(11)
+    G = 32
+    x = (torch.randn(T, H, device=DEV) * 0.5).bfloat16()
+    logits = torch.randn(T, E, device=DEV)
+    ids, w = moe.route(logits, K, "softmax")
+
+    def mk(rows, cols):
+        nib = torch.randint(0, 16, (rows, cols), device=DEV, dtype=torch.uint8)
+        sc = (torch.randn(rows, cols // G, device=DEV).abs() * 0.02 + 2e-3).bfloat16()
+        return nib, sc
+    gu_nib, gu_sc = mk(e_n * 2 * I, H)
+    dn_nib, dn_sc = mk(e_n * H, I)
+    wg = awq.Int4Weight(gu_nib, gu_sc, None, G, torch.bfloat16, keep_reference=True)
+    wd = awq.Int4Weight(dn_nib, dn_sc, None, G, torch.bfloat16, keep_reference=True)
+    y = moe.fused_experts(x, wg, wd, ids, w, e_n, e_lo, "gelu_tanh")
+    wg_c = awq.Int4Weight(gu_nib.cpu(), gu_sc.cpu(), None, G, torch.bfloat16)
+    wd_c = awq.Int4Weight(dn_nib.cpu(), dn_sc.cpu(), None, G, torch.bfloat16)
+    yr = moe.fused_experts(x.cpu(), wg_c, wd_c, ids.cpu(), w.cpu(), e_n, e_lo, "gelu_tanh")
+    _close(y.cpu(), yr, 5e-2, 5e-2, f"fused experts T{T} E{E}")
+    ops.check_status(x.device)
+
+
+@pytest.mark.parametrize("tname", ["Q8_0", "Q2_K", "IQ2_XXS"])
+def test_gguf_dequant_and_gemv(tname):
+    from litevllm_b200.ops import gguf_quant as gq
+    ty = gq.GGML_TYPES[tname]
+    rows, K = 304, 1024
+    raw = gq.random_blocks(ty, rows, K, seed=3, scale=0.02).to(DEV)
+    want = gq.dequantize(raw.cpu(), ty, K)
+    got = gq.dequantize_cuda(raw, ty, K, torch.bfloat16)
+    _close(got.cpu(), want, 1e-2, 1e-3, f"dequant {tname}")
+    for M in (1, 5, 8, 40):
+        x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+        y = gq.gguf_linear(x, raw, ty, K, out_dtype=torch.float32)
+        _close(y.cpu(), x.float().cpu() @ want.t(), 3e-2, 3e-2 * float(want.abs().max()) * 8, f"gemv {tname} M{M}")
+
+
+def test_q8_0_quantize_roundtrip():
+    from litevllm_b200.ops import gguf_quant as gq
+    w = torch.randn(16, 256)
+    raw = gq.quantize_q8_0(w)
+    back = gq.dequantize(raw, 8, 256)
+    assert float((back - w).abs().max()) < float(w.abs().max()) / 127 + 1e-3
