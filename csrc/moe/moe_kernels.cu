@@ -181,7 +181,8 @@ __global__ void moe_combine_kernel(const T* __restrict__ y_sorted, const int* __
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     for (int k = 0; k < K; ++k) {
-      const int slot = slot_of[static_cast<long>(t) * K + k];
+      // a null map means the rows are already in (token, k) order
+      const int slot = slot_of ? slot_of[static_cast<long>(t) * K + k] : t * K + k;
       if (slot < 0) continue;
       const float w = topk_w[static_cast<long>(t) * K + k];
       uint4 raw = *reinterpret_cast<const uint4*>(y_sorted + static_cast<long>(slot) * H + c * 8);

@@ -38,6 +38,7 @@ def clear_cache() -> None:
     from . import ops
     rope.clear_cache()
     ops._scratch.clear()
+    ops._retired.clear()
     if torch.cuda.is_available():
         torch.cuda.empty_cache()
 

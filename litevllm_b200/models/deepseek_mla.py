@@ -161,14 +161,9 @@ class RoutedExperts(nn.Module):
         else:
             lib = _lib.kernels()
             esz = x.element_size()
-            buf = scratch("ds_moe", n * (self.I + H) * esz + 4 * n + 256, x.device)
+            buf = scratch("ds_moe", n * (self.I + H) * esz + 256, x.device)
             a = buf[: n * self.I * esz].view(x.dtype).view(n, self.I)
             y = buf[n * self.I * esz: n * (self.I + H) * esz].view(x.dtype).view(n, H)
-            slot_of = buf[n * (self.I + H) * esz: n * (self.I + H) * esz + 4 * n].view(torch.int32)
-            if getattr(self, "_arange_n", 0) != n:
-                self._arange = torch.arange(n, dtype=torch.int32, device=x.device)
-                self._arange_n = n
-            slot_of.copy_(self._arange)
             e_hi = self.e_lo + self.e_local
             ids_flat = ids.reshape(-1)
             rc = lib.fi_gguf_moe_gate_up(_p(x), x.stride(0), _p(self.raw["gate"]), _p(self.raw["up"]),
@@ -180,7 +175,7 @@ class RoutedExperts(nn.Module):
                                       _p(ids_flat), n, self.e_lo, e_hi, H, self.I, _p(y), _stream())
             _lib.check(rc, "fi_gguf_moe_down")
             out = torch.empty(T, H, dtype=x.dtype, device=x.device)
-            rc = lib.fi_moe_combine(_p(y), _p(slot_of), _p(weights), None, _p(out), T, K, H, ops._DT[x.dtype], _stream())
+            rc = lib.fi_moe_combine(_p(y), None, _p(weights), None, _p(out), T, K, H, ops._DT[x.dtype], _stream())
             _lib.check(rc, "fi_moe_combine")
             _count(3)
         if pstate.ep_size() > 1:

@@ -58,12 +58,21 @@ def check_status(device: torch.device) -> None:
         raise RuntimeError(f"a device kernel reported status {code} (bounded wait ran out)")
 
 
+_retired: list[torch.Tensor] = []
+
+
 def scratch(name: str, nbytes: int, device: torch.device) -> torch.Tensor:
-    """Grow-only cached byte buffer (stable pointer while it does not grow)."""
+    """Grow-only cached byte buffer.  The pointer is stable while the buffer does not grow; when it
+    has to grow it at least doubles, and the outgrown buffer is kept alive because CUDA graphs
+    captured earlier still hold its address."""
     key = (name, device.index)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        if buf is not None:
+            _retired.append(buf)
+        size = max(nbytes, 1 << 20, 2 * buf.numel() if buf is not None else 0)
+        with torch.inference_mode(False):
+            buf = torch.empty(size, dtype=torch.uint8, device=device)
         _scratch[key] = buf
     return buf
 
