@@ -50,6 +50,7 @@ class LiteEngine:
         self.fatal_error: BaseException | None = None
         self.lock = threading.RLock()
         self._lazy_built = False
+        self.pre_step_hook = None
         self._init_before_model_load()
         self.model = model if model is not None else get_model(vllm_config, self.device)
         self._init_after_model_load()
@@ -203,6 +204,8 @@ class LiteEngine:
         with self.lock:
             if self.fatal_error is not None:
                 raise EngineFatalError(f"engine stopped after a fatal error: {self.fatal_error!r}")
+            if self.pre_step_hook is not None:
+                self.pre_step_hook()
             return self.controller.step()
 
     def handle_background_error(self, exc: BaseException) -> None:

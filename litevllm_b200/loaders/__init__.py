@@ -51,7 +51,7 @@ def synthetic_weights(vllm_config, device) -> Iterator[tuple[str, torch.Tensor]]
     # small models draw on the CPU (bit-identical across devices and ranks); big ones on the device
     big = mc.arch.hidden_size * mc.arch.num_layers >= 4096 * 30
     gen_dev = str(device) if (big and device.type == "cuda") else "cpu"
-    if fam in ("llama", "qwen2"):
+    if fam in ("llama", "qwen2", "qwen2_vl"):
         return synth.iter_llama_weights(mc.arch, mc.seed, torch.float32 if not big else mc.dtype, gen_dev)
     if fam == "gemma4":
         return synth.iter_gemma4_weights(mc.arch, mc.seed, mc.dtype, gen_dev)

@@ -163,3 +163,36 @@ def iter_deepseek_weights(arch: ModelArch, seed: int = 0, dtype=torch.bfloat16, 
             yield p + "mlp.up_proj.weight", q8(p + "u", arch.intermediate_size, H)
             yield p + "mlp.down_proj.weight", q8(p + "d", H, arch.intermediate_size)
     yield "lm_head.weight", q8("lm_head", V, H)
+
+
+def iter_qwen35_weights(arch: ModelArch, seed: int = 0, dtype=torch.float32, device="cpu") -> Iterator[tuple[str, torch.Tensor]]:
+    e = arch.extra
+    nk, nv = int(e.get("linear_num_key_heads", 4)), int(e.get("linear_num_value_heads", 8))
+    dk, dv, kw = int(e.get("linear_key_head_dim", 64)), int(e.get("linear_value_head_dim", 64)), int(e.get("linear_conv_kernel_dim", 4))
+    H, I, V, hd = arch.hidden_size, arch.intermediate_size, arch.vocab_size, arch.head_dim
+    gated = bool(e.get("attn_output_gate", True))
+
+    def w(name, *shape, std=0.02):
+        return normal(name, shape, seed, std, dtype, device)
+    yield "model.embed_tokens.weight", w("embed", V, H)
+    for i in range(arch.num_layers):
+        p = f"model.layers.{i}."
+        if arch.layer_type(i) == "linear":
+            C = 2 * nk * dk + nv * dv
+            yield p + "linear_attn.in_proj_qkv.weight", w(p + "qkv", C, H)
+            yield p + "linear_attn.in_proj_z.weight", w(p + "z", nv * dv, H)
+            yield p + "linear_attn.in_proj_b.weight", w(p + "b", nv, H)
+            yield p + "linear_attn.in_proj_a.weight", w(p + "a", nv, H)
+            yield p + "linear_attn.conv1d.weight", w(p + "conv", C, 1, kw, std=0.3)
+            yield p + "linear_attn.A_log", w(p + "alog", nv, std=0.5).float()
+            yield p + "linear_attn.dt_bias", w(p + "dt", nv, std=0.5).float()
+            yield p + "linear_attn.out_proj.weight", w(p + "o", H, nv * dv)
+        else:
+            yield p + "self_attn.q_proj.weight", w(p + "q", arch.num_heads * hd * (2 if gated else 1), H)
+            yield p + "self_attn.k_proj.weight", w(p + "k", arch.num_kv_heads * hd, H)
+            yield p + "self_attn.v_proj.weight", w(p + "v", arch.num_kv_heads * hd, H)
+            yield p + "self_attn.o_proj.weight", w(p + "o", H, arch.num_heads * hd)
+        yield p + "mlp.gate_proj.weight", w(p + "g", I, H)
+        yield p + "mlp.up_proj.weight", w(p + "u", I, H)
+        yield p + "mlp.down_proj.weight", w(p + "d", H, I)
+    yield "lm_head.weight", w("lm_head", V, H)

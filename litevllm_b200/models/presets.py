@@ -79,6 +79,17 @@ PRESETS["tiny-deepseek-test"] = dict(PRESETS["deepseek-mla-moe"], hidden_size=25
                                      qk_rope_head_dim=64, qk_nope_head_dim=64, v_head_dim=64, intermediate_size=256,
                                      moe_intermediate_size=256, n_routed_experts=8, num_experts_per_tok=2,
                                      vocab_size=512, max_position_embeddings=512)
+PRESETS["tiny-qwen35-test"] = {
+    "architectures": ["Qwen3_5ForCausalLM"], "model_type": "qwen3_5", "hidden_size": 256, "num_hidden_layers": 4,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 256, "vocab_size": 512,
+    "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "max_position_embeddings": 512, "partial_rotary_factor": 0.25,
+    "full_attention_interval": 4, "linear_num_key_heads": 2, "linear_num_value_heads": 4, "linear_key_head_dim": 32,
+    "linear_value_head_dim": 32, "linear_conv_kernel_dim": 4, "attn_output_gate": True, "eos_token_id": 1,
+}
+PRESETS["tiny-qwen2vl-test"] = dict(PRESETS["tiny-llama-test"], architectures=["Qwen2VLForConditionalGeneration"],
+                                    model_type="qwen2_vl", attention_bias=True,
+                                    vision_config={"patch_size": 14, "hidden_size": 64, "num_hidden_layers": 1,
+                                                   "num_attention_heads": 2, "tokens_per_image": 4})
 
 
 def get_preset(name: str) -> dict:

@@ -24,7 +24,37 @@ class DistributedHandle:
         self.engine = None
 
     def attach(self, engine) -> None:
+        """Hook liveness checks into the engine: between steps (at most once per heartbeat interval)
+        rank liveness is read from the store and the device status word is decoded, so a missing
+        peer or a timed-out fused collective surfaces as an exception before the next launch."""
+        import time
+
+        import torch.distributed as dist
+
+        from .fault import Heartbeat, decode_status
         self.engine = engine
+        if self.state.world_size <= 1 or not dist.is_initialized():
+            return
+        rc = engine.rc
+        store = dist.distributed_c10d._get_default_store()
+        self.heartbeat = Heartbeat(store, self.state.rank, self.state.world_size, rc.heartbeat_interval_s,
+                                   rc.heartbeat_timeout_s)
+        self.heartbeat.start()
+        last = [time.monotonic()]
+
+        def pre_step():
+            now = time.monotonic()
+            if now - last[0] < rc.heartbeat_interval_s:
+                return
+            last[0] = now
+            self.heartbeat.raise_if_dead()
+            if torch.cuda.is_available() and self.state.symm is not None:
+                from .. import ops
+                code = int(ops.status_word(engine.device).item())
+                if code:
+                    ops.status_word(engine.device).zero_()
+                    decode_status(code)
+        engine.pre_step_hook = pre_step
 
     def shutdown(self) -> None:
         """Drop captured CUDA graphs (they hold collective kernels), quiesce, then leave the group.
@@ -33,6 +63,9 @@ class DistributedHandle:
         import gc
 
         import torch.distributed as dist
+        hb = getattr(self, "heartbeat", None)
+        if hb is not None:
+            hb.stop()
         eng = self.engine
         if eng is not None and hasattr(eng, "decode_executor"):
             getattr(eng.decode_executor, "_graphs", {}).clear()
