@@ -218,6 +218,19 @@ def run_ours(args) -> dict:
     clocks = sampler.stop()
     dev_replays = eng.decode_executor.graph_replays - replays1
     dev_eager = ops.launch_count() - l1
+    # diagnostic only (not a valid decode: the inputs do not advance): the captured step replayed back
+    # to back with no host work in between = the pure GPU time of one step
+    entry = eng.decode_executor._graphs.get(bucket)
+    graph_only_ms = None
+    if entry is not None and world == 1:
+        g = entry[0]
+        torch.cuda.synchronize()
+        ev0.record()
+        for _ in range(32):
+            g.replay()
+        ev1.record()
+        torch.cuda.synchronize()
+        graph_only_ms = ev0.elapsed_time(ev1) / 32
     pipe.stop()
     for i in range(B):
         eng.abort_request(f"dev-{i}")
@@ -243,6 +256,8 @@ def run_ours(args) -> dict:
         "gpu_launches_detail": {"graph_replays": dev_replays, "kernels_per_graph": per_graph,
                                 "eager_native_launches": dev_eager},
         "clocks": clocks, "clocks_e2e": clocks_e2e,
+        "diag": {"graph_replay_only_ms_per_step": round(graph_only_ms, 4) if graph_only_ms else None,
+                 "pdl": os.environ.get("FI_USE_PDL", "1") != "0"},
     }
     if args.profile_json and rank == 0:
         Path(args.profile_json).write_text(json.dumps(result, indent=1))

@@ -7,7 +7,7 @@ struct FiComm {
   int world;
   int rank;
   int rows_per_rank;     // reduce-scatter: rows of the output shard (multiple of the token tile)
-  int xfer_16bit;        // send partials as 16-bit values instead of fp32
+  int xfer_16bit;        // 0: fp32 + flags, 1: 16-bit values + flags, 2: fp32 with inline epoch flags (8 B per value)
   int ag_world;          // > 1: the token operand is the concatenation of every rank's shard
   int ag_rows_per_rank;  // rows of one token shard
   int reserved;
@@ -18,6 +18,7 @@ struct FiComm {
   unsigned long long x_peers[8];  // token shard of rank d (all-gather mode)
   unsigned long long epoch;       // local device word: completed fused calls
   unsigned long long done;        // local device word: finished CTAs of the running call
+  unsigned long long trace;       // optional device array [64][8] of phase timestamps (0 = off), see trace_mark()
 };
 
 // Grouped (mixture-of-experts) launch: activations are sorted by expert, a device-side tile table

@@ -76,8 +76,12 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) pdl_launch_dependents();
-  if (warp != 0) pdl_wait();   // the producer waits later, after prefetching weight tiles
+  // the producer waits later, after prefetching weight tiles (a fused collective reads its epoch
+  // word below, which the previous call writes, so there every warp waits first)
+  const bool fused_call = p.comm_mode != kCommNone || p.ag_world > 1;
+  if (warp != 0 || fused_call) pdl_wait();
   const unsigned int epoch_now = (p.comm_mode != kCommNone || p.ag_world > 1) ? *p.epoch + 1u : 0u;
+  trace_mark(p.trace, epoch_now, 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -304,7 +308,7 @@ static int fi_dense_gemm_impl(const void* X, const void* W, void* C, const void*
   p.dual_rows = dual_rows; p.act = act; p.out_fp32 = out_fp32; p.is_fp16 = dtype == 1;
   p.splits = splits; p.status = status;
   p.tile_expert = nullptr; p.tile_row0 = nullptr; p.tile_rows = nullptr; p.n_tiles = nullptr; p.expert_rows = 0; p.grid_tiles = 0;
-  p.comm_mode = 0; p.world = 1; p.rank = 0; p.rows_per_rank = 0; p.xfer_16bit = 0;
+  p.comm_mode = 0; p.world = 1; p.rank = 0; p.rows_per_rank = 0; p.xfer_16bit = 0; p.trace = nullptr;
   p.ag_world = 1; p.ag_rows_per_rank = 0; p.slab_elems = 0; p.epoch = nullptr; p.done = nullptr;
   for (int d = 0; d < kMaxRanks; ++d) { p.recv[d] = 0; p.flags[d] = 0; p.ready[d] = 0; }
   if (comm != nullptr) {
@@ -316,6 +320,7 @@ static int fi_dense_gemm_impl(const void* X, const void* W, void* C, const void*
     p.slab_elems = comm->slab_elems;
     p.epoch = reinterpret_cast<unsigned int*>(comm->epoch);
     p.done = reinterpret_cast<unsigned int*>(comm->done);
+    p.trace = reinterpret_cast<unsigned long long*>(comm->trace);
     for (int d = 0; d < kMaxRanks; ++d) { p.recv[d] = comm->recv[d]; p.flags[d] = comm->flags[d]; p.ready[d] = comm->ready[d]; }
     if (comm->mode == kCommReduceScatter && (comm->rows_per_rank % bn) != 0) return -17;
     const long tiles = static_cast<long>((N + BM - 1) / BM) * ((T + bn - 1) / bn);

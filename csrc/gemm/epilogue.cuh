@@ -26,6 +26,7 @@ constexpr int BK = 64;   // 64 x 16-bit = one 128-byte swizzle row
 constexpr int kThreads = 192;
 constexpr int kMaxRanks = 8;
 constexpr int kFlagParts = 8;       // flag words per (tile, source rank): one per cluster part
+constexpr int kXferInlineFlags = 2;  // GemmParams::xfer_16bit value: fp32 values with the epoch in every 8-byte word
 constexpr int kMaxCommTiles = 8192; // tiles per call that the flag area can describe
 
 enum Act : int { kActNone = 0, kActSilu = 1, kActGeluTanh = 2 };
@@ -52,7 +53,7 @@ struct GemmParams {
   int comm_mode;
   int world, rank;
   int rows_per_rank;     // reduce-scatter: token t belongs to rank t / rows_per_rank
-  int xfer_16bit;        // partials cross NVLink as 16-bit values instead of fp32
+  int xfer_16bit;        // 0: fp32 + flags, 1: 16-bit values + flags, 2: fp32 with inline epoch flags (8 B per value)
   int ag_world;          // > 1: token tile t0 is read from rank t0 / ag_rows_per_rank
   int ag_rows_per_rank;
   long slab_elems;       // elements of one (parity, source) receive slab
@@ -60,6 +61,7 @@ struct GemmParams {
   unsigned long long flags[kMaxRanks];  // flag words of rank d as mapped in this process
   unsigned long long ready[kMaxRanks];  // all-gather ready words of rank d as mapped here
   unsigned int* epoch;   // local: completed fused calls
+  unsigned long long* trace;   // optional phase timestamps of CTA (0,0,0): [epoch % 64][8]
   unsigned int* done;    // local: CTAs of the current call that have finished
   // grouped (mixture-of-experts) mode: blockIdx.y indexes a tile table built on the device
   const int* tile_expert;   // expert of each token tile (null = plain GEMM)
@@ -95,6 +97,26 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
   unsigned int v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
+}
+__device__ __forceinline__ void st_volatile_v4(uint4* p, uint4 v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+// Debug aid: CTA (0,0,0) records the global timer at a few phases of a fused call when the caller
+// passed a trace array (phase 0 start, 1 accumulators staged, 2 partials pushed, 3 peers' flags
+// seen, 4 reduced tile stored, 5 exit).
+__device__ __forceinline__ void trace_mark(unsigned long long* trace, unsigned int epoch_now, int phase) {
+  if (trace != nullptr && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    trace[(epoch_now & 63u) * 8 + phase] = t;
+  }
 }
 // Bounded wait for a flag word to reach `want` (epochs only grow).
 __device__ __forceinline__ bool wait_flag(const unsigned int* p, unsigned int want) {
@@ -228,6 +250,7 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
   const int owner = p.comm_mode == kCommReduceScatter ? t0 / p.rows_per_rank : -1;
   const int parity = static_cast<int>(epoch_now & 1u);
   const int row_base = p.comm_mode == kCommReduceScatter ? p.rank * p.rows_per_rank : 0;
+  trace_mark(p.trace, epoch_now, 1);
 
   if (!*aborted) {
     for (int idx = threadIdx.x; idx < rows_mine * (BM / 8); idx += kThreads) {
@@ -270,7 +293,15 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
       const long off = (static_cast<long>(parity) * p.world + p.rank) * p.slab_elems + trow * p.N + n;
       for (int d = 0; d < p.world; ++d) {
         if (d == p.rank || (owner >= 0 && d != owner)) continue;
-        if (p.xfer_16bit) {
+        if (p.xfer_16bit == kXferInlineFlags) {
+          // low-latency form: every 8-byte word carries one fp32 value and the epoch, so the
+          // receiver needs no fence and no separate flag (one NVLink crossing instead of three)
+          uint4* dst = reinterpret_cast<uint4*>(p.recv[d]) + (off >> 1);
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            st_volatile_v4(dst + q, make_uint4(__float_as_uint(g[2 * q]), epoch_now,
+                                               __float_as_uint(g[2 * q + 1]), epoch_now));
+        } else if (p.xfer_16bit) {
           uint32_t packed[4];
           pack8(g, p.is_fp16, packed);
           *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.recv[d]) + off) =
@@ -283,12 +314,14 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
       }
     }
   }
+  trace_mark(p.trace, epoch_now, 2);
   if (comm) {
     const unsigned int tile = blockIdx.y * gridDim.x + blockIdx.x;
-    __threadfence_system();
+    const bool inline_flags = p.xfer_16bit == kXferInlineFlags;
+    if (!inline_flags) __threadfence_system();
     __syncthreads();
     const bool i_own = owner < 0 || owner == p.rank;
-    if (!*aborted && threadIdx.x < p.world && static_cast<int>(threadIdx.x) != p.rank) {
+    if (!inline_flags && !*aborted && threadIdx.x < p.world && static_cast<int>(threadIdx.x) != p.rank) {
       const int d = threadIdx.x;
       if (owner < 0 || d == owner) {
         unsigned int* f = reinterpret_cast<unsigned int*>(p.flags[d]) +
@@ -305,6 +338,7 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
       }
     }
     __syncthreads();
+    trace_mark(p.trace, epoch_now, 3);
     // ---- phase C: sum the partials of all ranks in rank order, finish the epilogue, store
     if (!*aborted && i_own) {
       for (int idx = threadIdx.x; idx < rows_mine * (BM / 8); idx += kThreads) {
@@ -323,14 +357,31 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
             const float4 a = *reinterpret_cast<const float4*>(stage_f32 + tl * BM + nl);
             const float4 b = *reinterpret_cast<const float4*>(stage_f32 + tl * BM + nl + 4);
             v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-            if (p.xfer_16bit) {   // round my own partial like the ones that crossed the link
+            if (p.xfer_16bit == 1) {   // round my own partial like the ones that crossed the link
               uint32_t packed[4];
               pack8(v, p.is_fp16, packed);
               unpack8(make_uint4(packed[0], packed[1], packed[2], packed[3]), p.is_fp16, v);
             }
           } else {
             const long off = (static_cast<long>(parity) * p.world + s) * p.slab_elems + trow * p.N + n;
-            if (p.xfer_16bit) {
+            if (inline_flags) {
+              const uint4* src = reinterpret_cast<const uint4*>(p.recv[p.rank]) + (off >> 1);
+              const long long w0 = clock64();
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 wv = ld_volatile_v4(src + q);
+                while (wv.y != epoch_now || wv.w != epoch_now) {
+                  if (*aborted || clock64() - w0 > FI_WAIT_CYCLES) {
+                    set_status(p.status, kStatusTimeoutPeer);
+                    *aborted = 1;
+                    break;
+                  }
+                  wv = ld_volatile_v4(src + q);
+                }
+                v[2 * q] = __uint_as_float(wv.x);
+                v[2 * q + 1] = __uint_as_float(wv.z);
+              }
+            } else if (p.xfer_16bit) {
               unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.recv[p.rank]) + off),
                       p.is_fp16, v);
             } else {
@@ -347,13 +398,14 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
 #pragma unroll
           for (int j = 0; j < 8; ++j) acc[j] = apply_act(acc[j], p.act);
         }
-        finalize_store8(p, acc, static_cast<int>(trow), n);
+        if (!*aborted) finalize_store8(p, acc, static_cast<int>(trow), n);
       }
     }
   }
   if (comm || p.ag_world > 1) {
     // the last CTA of the call publishes the new epoch for the next fused call
     __syncthreads();
+    trace_mark(p.trace, epoch_now, 4);
     if (threadIdx.x == 0) {
       const unsigned int total = gridDim.x * gridDim.y * gridDim.z;
       __threadfence();
@@ -365,6 +417,7 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
     }
   }
   if (S > 1) cluster.sync();  // nobody leaves while a peer may still read its staging tile
+  trace_mark(p.trace, epoch_now, 5);
 }
 
 // Source of the token tile starting at token t0: which tensor map and which row inside it.

@@ -50,10 +50,8 @@ class Gemma4VisionTower(nn.Module):
         with torch.no_grad():
             g = torch.Generator().manual_seed(1234)
             for p in self.parameters():
-                if p.dim() > 1:
-                    p.copy_((torch.randn(p.shape, generator=g) * 0.02).to(p.dtype))
-                elif "ln" in "".join(n for n, q in self.named_parameters() if q is p) and p.numel() == self.dim:
-                    pass
+                if p.dim() > 1:      # deterministic default init; real checkpoints overwrite it
+                    p.copy_((torch.randn(p.shape, generator=g, device="cpu") * 0.02).to(p.dtype))
 
     def forward(self, pixel_patches: torch.Tensor, position_ids: torch.Tensor, patches_per_image: list[int]):
         """pixel_patches [P, 3*patch*patch] in [-1, 1]; position_ids [P, 2] (row, col);

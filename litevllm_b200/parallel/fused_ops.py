@@ -34,6 +34,8 @@ def row_parallel_linear(layer, x: torch.Tensor, residual: torch.Tensor | None, o
     N = layer.out_features
     if _fused_available(x):
         heap = st.symm
+        if T > 0 and T <= 256 and heap.fits_low_latency(T, N):
+            return _fused_gemm_allreduce(layer, x, residual, out, heap, 2)     # decode: one NVLink crossing
         xfer16 = T > 256
         elem = 2 if xfer16 else 4
         if heap.fits_recv(T, N, elem) and T > 0:
@@ -49,7 +51,7 @@ def row_parallel_linear(layer, x: torch.Tensor, residual: torch.Tensor | None, o
     return partial
 
 
-def _fused_gemm_allreduce(layer, x, residual, out, heap, xfer16: bool):
+def _fused_gemm_allreduce(layer, x, residual, out, heap, xfer16: bool | int):
     T, K = x.shape
     N = layer.out_features
     if out is None:

@@ -30,7 +30,7 @@ class FiComm(ctypes.Structure):
                 ("ag_rows_per_rank", ctypes.c_int), ("reserved", ctypes.c_int), ("slab_elems", ctypes.c_long),
                 ("recv", ctypes.c_ulonglong * 8), ("flags", ctypes.c_ulonglong * 8),
                 ("ready", ctypes.c_ulonglong * 8), ("x_peers", ctypes.c_ulonglong * 8),
-                ("epoch", ctypes.c_ulonglong), ("done", ctypes.c_ulonglong)]
+                ("epoch", ctypes.c_ulonglong), ("done", ctypes.c_ulonglong), ("trace", ctypes.c_ulonglong)]
 
 
 class _RawCudaBuffer:
@@ -43,7 +43,7 @@ class _RawCudaBuffer:
 
 class SymmetricHeap:
     def __init__(self, rank: int, world: int, device: torch.device, recv_bytes: int = 512 << 20,
-                 xbuf_bytes: int = 64 << 20, group=None):
+                 xbuf_bytes: int = 64 << 20, group=None, ll_elems: int = 512 * 1024):
         from ..ops import _lib
         self.rank, self.world, self.device = rank, world, device
         self.flag_bytes = MAX_COMM_TILES * MAX_RANKS * FLAG_PARTS * 4
@@ -56,7 +56,11 @@ class SymmetricHeap:
         self.off_ready = self.off_flags + self.flag_bytes
         self.off_ctl = self.off_ready + self.ready_bytes
         self.off_xbuf = (self.off_ctl + self.ctl_bytes + 1023) // 1024 * 1024
-        total = self.off_xbuf + 2 * self.xbuf_bytes
+        # low-latency slabs (fp32 value + epoch per 8-byte word), kept apart from the flagged slabs so
+        # that no other transfer format ever writes there: 2 parities x world sources
+        self.ll_elems = ll_elems
+        self.off_ll = self.off_xbuf + 2 * self.xbuf_bytes
+        total = self.off_ll + 2 * world * ll_elems * 8
         self.total_bytes = total
         lib = self._lib = _lib.kernels()
         torch.cuda.set_device(device)
@@ -81,6 +85,7 @@ class SymmetricHeap:
             self.peer_ptr.append(int(out.value))
             self._opened.append(int(out.value))
         self.buffer = torch.as_tensor(_RawCudaBuffer(self.base, total), device=device)
+        self.trace_ptr = 0           # set to a device int64[64*8] array to record kernel phase timestamps
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
@@ -95,22 +100,27 @@ class SymmetricHeap:
     def fits_recv(self, T: int, N: int, elem: int) -> bool:
         return 2 * self.world * T * N * elem <= self.recv_bytes
 
-    def comm_desc(self, mode: int, T: int, N: int, xfer_16bit: bool, rows_per_rank: int = 0,
+    def fits_low_latency(self, T: int, N: int) -> bool:
+        return T * N <= self.ll_elems
+
+    def comm_desc(self, mode: int, T: int, N: int, xfer_16bit: bool | int, rows_per_rank: int = 0,
                   ag_world: int = 1, ag_rows_per_rank: int = 0, x_parity: int = 0) -> FiComm:
         c = FiComm()
         c.mode, c.world, c.rank = mode, self.world, self.rank
         c.rows_per_rank = rows_per_rank
-        c.xfer_16bit = 1 if xfer_16bit else 0
+        c.xfer_16bit = int(xfer_16bit)          # 0 fp32 + flags, 1 16-bit + flags, 2 fp32 with inline epochs
+        recv_off = self.off_ll if c.xfer_16bit == 2 else self.off_recv
         c.ag_world, c.ag_rows_per_rank = ag_world, ag_rows_per_rank
         slab_rows = rows_per_rank if mode == 2 else T
         c.slab_elems = slab_rows * N
         for d in range(self.world):
-            c.recv[d] = self.peer_ptr[d] + self.off_recv
+            c.recv[d] = self.peer_ptr[d] + recv_off
             c.flags[d] = self.peer_ptr[d] + self.off_flags
             c.ready[d] = self.peer_ptr[d] + self.off_ready
             c.x_peers[d] = self.peer_ptr[d] + self.off_xbuf + x_parity * self.xbuf_bytes
         c.epoch = self.peer_ptr[self.rank] + self.off_ctl
         c.done = self.peer_ptr[self.rank] + self.off_ctl + 64
+        c.trace = self.trace_ptr
         return c
 
     def epoch_value(self) -> int:

@@ -43,11 +43,12 @@ def _kernel_worker(rank, world, out_dir):
         want = (x.float() @ w.float().t())
         dist.all_reduce(want)
         want = want + res.float()
-        for rep in range(2):
-            got = fused_ops._fused_gemm_allreduce(layer, x, res, None, st.symm, xfer16=T > 256)
+        # transfer formats: 2 = fp32 with inline epochs (decode), 0 = fp32 + flags, 1 = 16-bit + flags
+        for rep, mode in enumerate([2, 2, 0] if T <= 256 else [1, 1]):
+            got = fused_ops._fused_gemm_allreduce(layer, x, res, None, st.symm, mode)
             torch.cuda.synchronize()
             ok, err = close(got, want)
-            report[f"ar_{T}x{N}x{K}_{rep}"] = [ok, err]
+            report[f"ar_{T}x{N}x{K}_{rep}_mode{mode}"] = [ok, err]
         # identical on every rank (fixed summation order)
         mine = got.clone()
         other = got.clone()
