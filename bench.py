@@ -123,6 +123,9 @@ def run_ours(args) -> dict:
                    max_num_batched_tokens=max(8192, B * P), tensor_parallel_size=world,
                    comm_backend=args.comm_backend, fastinference_config=cfg, device=f"cuda:{local_rank}")
 
+    if args.profile_json:
+        from litevllm_b200.utils.profiling import PROFILER
+        PROFILER.configure(True, nvtx=True)      # event pairs are resolved after the timed regions
     llm = make_llm(False)
     eng = llm.engine
     vocab = eng.arch.vocab_size
@@ -260,7 +263,9 @@ def run_ours(args) -> dict:
                  "pdl": os.environ.get("FI_USE_PDL", "1") != "0"},
     }
     if args.profile_json and rank == 0:
-        Path(args.profile_json).write_text(json.dumps(result, indent=1))
+        from litevllm_b200.utils.profiling import PROFILER
+        Path(args.profile_json).write_text(json.dumps({"result": result, "spans": PROFILER.summary(),
+                                                       "engine_stats": eng.stats()}, indent=1, default=str))
     llm.shutdown()
     return result if rank == 0 else {}
 

@@ -300,6 +300,24 @@ __global__ void act_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int
   }
 }
 
+// plain elementwise activation (act: 1 SiLU, 2 tanh-GELU) over a [rows, d] tensor
+template <typename T>
+__global__ void act_kernel(const T* __restrict__ x, T* __restrict__ out, int d, long ldx, long ldo, int act) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  const long r = blockIdx.x;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float g = Cvt<T>::to_f(x[r * ldx + i]);
+    float a;
+    if (act == 1) a = g / (1.f + __expf(-g));
+    else if (act == 2) {
+      const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+      a = g / (1.f + __expf(-2.f * inner));
+    } else a = g;
+    out[r * ldo + i] = Cvt<T>::from_f(a);
+  }
+}
+
 // ------------------------------------------------------------------ slot mapping
 // slot[t] = block_tables[seq, pos / bs] * bs + pos % bs  (block id 0 is the null block -> -1).
 __global__ void slot_mapping_kernel(const int* __restrict__ positions,
@@ -444,6 +462,16 @@ extern "C" int fi_act_mul(const void* x, void* out, int rows, int d, long ldx, i
   return dispatch_dtype(dtype, [&](auto* tag) {
     using Tt = std::remove_pointer_t<decltype(tag)>;
     fi::launch_kernel(act_mul_kernel<Tt>, dim3(rows), dim3(256), 0, FI_STREAM(stream), 0, (const Tt*)x, (Tt*)out, d, ldx, act);
+    return static_cast<int>(cudaGetLastError());
+  });
+}
+
+extern "C" int fi_act(const void* x, void* out, int rows, int d, long ldx, long ldo, int act, int dtype,
+                      void* stream) {
+  if (rows <= 0) return 0;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using Tt = std::remove_pointer_t<decltype(tag)>;
+    fi::launch_kernel(act_kernel<Tt>, dim3(rows), dim3(256), 0, FI_STREAM(stream), 0, (const Tt*)x, (Tt*)out, d, ldx, ldo, act);
     return static_cast<int>(cudaGetLastError());
   });
 }

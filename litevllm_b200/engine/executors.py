@@ -11,6 +11,8 @@ from dataclasses import dataclass
 
 import torch
 
+from ..utils.profiling import span
+
 from .. import ops
 from .input_batch import ForwardBatch, InputBatchBuilder
 from .request_state import RequestState
@@ -48,7 +50,8 @@ class PrefillExecutor:
             embeds = self.multimodal.embed_for_prefill(self.model, batch, items, states)
         if hasattr(self.model, "prepare_batch"):
             self.model.prepare_batch(batch, states)
-        logits = self.model(batch, self.kv_cache, inputs_embeds=embeds)
+        with span("prefill_forward"):
+            logits = self.model(batch, self.kv_cache, inputs_embeds=embeds)
         if hasattr(self.model, "finish_batch"):
             self.model.finish_batch(batch, states)
         return LogitsResult(logits, batch.request_ids)
@@ -78,7 +81,8 @@ class DecodeExecutor:
             self.model.prepare_batch(batch, states or {r.request_id: r for r in reqs})
         if not self.use_cuda_graph or lora_mapping is not None or stateful:
             self.eager_steps += 1
-            logits = self._run(batch)
+            with span("decode_forward_eager"):
+                logits = self._run(batch)
             if stateful:
                 self.model.finish_batch(batch, states or {r.request_id: r for r in reqs})
             return LogitsResult(logits, batch.request_ids)
@@ -93,7 +97,8 @@ class DecodeExecutor:
             entry = self._capture(batch)
             self._graphs[bucket] = entry
             graph, out, max_kv_cap = entry
-        graph.replay()
+        with span("decode_graph_replay"):
+            graph.replay()
         self.graph_replays += 1
         return LogitsResult(out, batch.request_ids)
 
@@ -138,7 +143,8 @@ class DecodeExecutor:
         if entry is None:
             entry = self._capture(batch)
             self._graphs[bucket] = entry
-        entry[0].replay()
+        with span("decode_graph_replay"):
+            entry[0].replay()
         self.graph_replays += 1
         return entry[1]
 

@@ -19,21 +19,12 @@ from ..config.loadtime_policy import estimate_param_bytes, select_loadtime_polic
 from ..loaders import get_model, resolve_device
 from ..logger import init_logger
 from ..sampling_params import SamplingParams
-from .backend import LiteGpuBackend
-from .block_allocator import BlockAllocator
 from .errors import EngineFatalError, InvalidRequestError, RequestAbortedError, RequestRejectedError
-from .executors import DecodeExecutor, PrefillExecutor
-from .input_batch import InputBatchBuilder
-from .kv_block_manager import KVBlockManager
-from .kv_cache import FlatKVCache, KVLayerSpec
+from .initialization import LiteRuntimeAssembler, MemoryAuditor
 from .observer import InMemoryRuntimeObserver
-from .output_pipeline import GenerationPolicies, OutputPipeline
 from .request_builder import LiteRequestBuilder
-from .request_scheduler import RequestScheduler
-from .runtime_controller import RuntimeController
+from .runtime_factory import LiteRuntimeFactory
 from .runtime_planner import RuntimePlanner
-from .sampling_driver import SamplingDriver
-from .step_scheduler import StepScheduler
 
 logger = init_logger(__name__)
 
@@ -65,6 +56,9 @@ class LiteEngine:
             fusion_level=self.rc.fusion_level, nvtx=self.rc.profile_nvtx,
             profile_spans=self.rc.profile_step_events)
         self.adapter.install_tuning_config(self.rc, self.inf_config)
+        if self.inf_config.profile_spans or self.inf_config.nvtx:
+            from ..utils.profiling import PROFILER
+            PROFILER.configure(self.inf_config.profile_spans, self.inf_config.nvtx)
 
     def _device_total_bytes(self) -> int | None:
         if self.device.type == "cuda":
@@ -76,11 +70,8 @@ class LiteEngine:
         total = self._device_total_bytes()
         self.loadtime_policy = select_loadtime_policy(estimate_param_bytes(self.model), total, self.rc.policy_mode)
         planner = RuntimePlanner(self.rc, self.model_policy)
-        self.plan = planner.build_execution_plan(total)
-        custom = self.adapter.build_executors(self)
-        specs = [KVLayerSpec(*s) if not isinstance(s, KVLayerSpec) else s for s in self.model.kv_cache_specs()]
-        self.kv_plan = planner.build_kv_cache_plan(self.plan, specs, self.model_config.dtype,
-                                                   self.model_policy.force_kv_cache_dtype)
+        ctx = LiteRuntimeAssembler.assemble(self, planner, total)
+        self.plan, self.kv_plan = ctx.plan, ctx.kv_plan
         if total is not None:
             free, _ = torch.cuda.mem_get_info(self.device)
             budget = int(free - (1.0 - self.vllm_config.cache_config.gpu_memory_utilization) * total)
@@ -89,49 +80,21 @@ class LiteEngine:
                     f"KV cache needs {self.kv_plan.bytes_total / 2**30:.1f} GiB for "
                     f"{self.plan.max_active_requests} x {self.plan.max_model_len} tokens but only "
                     f"{budget / 2**30:.1f} GiB are available; lower max_num_seqs or max_model_len")
-        self.kv_cache = FlatKVCache(specs, self.plan.num_total_blocks, self.plan.block_size,
-                                    self.kv_plan.dtype, self.device)
-        self.allocator = BlockAllocator(self.plan.num_total_blocks)
-        self.kv_manager = KVBlockManager(self.allocator, self.plan.block_size, self.plan.max_active_requests,
-                                         self.plan.num_blocks_per_seq, self.device, self.kv_cache)
-        if custom is not None and getattr(custom, "kv_block_manager", None) is not None:
-            self.kv_manager = custom.kv_block_manager
-        self.scheduler = RequestScheduler(self.plan.max_active_requests, self.rc.queue_timeout_s)
-        self.builder = InputBatchBuilder(self.kv_manager, self.plan.max_active_requests,
-                                         self.plan.step_token_budget, self.device, self.inf_config)
-        from .lora_runtime import LoRARuntimeRegistry
-        self.lora_registry = LoRARuntimeRegistry(self.model, self.device) if self.capabilities.supports_lora else None
-        self.multimodal = None
-        if self.capabilities.supports_multimodal:
-            from .multimodal_processor import MultimodalProcessor
-            self.multimodal = MultimodalProcessor(self.arch, self.model)
-        self.prefill_executor = (custom.prefill_executor if custom and custom.prefill_executor else
-                                 PrefillExecutor(self.model, self.kv_cache, self.builder, self.multimodal))
-        self.decode_executor = (custom.decode_executor if custom and custom.decode_executor else
-                                DecodeExecutor(self.model, self.kv_cache, self.builder,
-                                               self.rc.backend_policy.cuda_graph_decode and
-                                               self.capabilities.supports_cuda_graph))
-        self.step_scheduler = StepScheduler(
-            self.plan.step_token_budget, self.plan.prefill_chunk_size, self.plan.prefill_microbatch,
-            self.rc.scheduler_policy, self.rc.enable_decode_priority, self.rc.prefill_catchup_ratio,
-            self.rc.prefill_reserved_tokens, self.rc.prefill_reserve_backlog, self.rc.min_prefill_chunk_size,
-            self.rc.max_prefill_chunk_size, self.model_policy.verified_decode_batch_sizes,
-            self.plan.max_active_requests)
-        from .prefix_cache import PrefixCache
-        self.prefix_cache = PrefixCache(self.rc.backend_policy.max_prefix_cache_entries,
-                                        self.rc.backend_policy.max_prefix_cache_bytes)
-        self.sampling_driver = SamplingDriver(self.arch.vocab_size)
-        self.output_pipeline = OutputPipeline(None, self.plan.max_model_len, GenerationPolicies())
-        self.backend = LiteGpuBackend(self.scheduler, self.kv_manager, self.prefill_executor, self.decode_executor,
-                                      self.sampling_driver, self.output_pipeline, self.observer,
-                                      self.rc.backend_policy, self.prefix_cache, self.lora_registry,
-                                      on_release=self._on_release)
-        self.controller = RuntimeController(self.scheduler, self.step_scheduler, self.backend, self.observer)
+        parts = LiteRuntimeFactory.build(ctx)
+        for name, value in vars(parts).items():      # kv_cache, allocator, kv_manager, scheduler, builder, ...
+            setattr(self, name, value)
+        self.memory = MemoryAuditor().snapshot(self.model, self.kv_cache, self.device)
+        logger.info("memory: %s", self.memory.report())
         from .model_surface import resolve_model_surface
         self.observer.on_model_surface(resolve_model_surface(self.model_config.model, self.arch))
         logger.info("engine ready: %d slots x %d tokens, %d KV blocks (%s, %.2f GiB), chunk %d",
                     self.plan.max_active_requests, self.plan.max_model_len, self.plan.num_total_blocks,
                     self.kv_plan.dtype, self.kv_cache.total_bytes / 2 ** 30, self.plan.prefill_chunk_size)
+
+    @staticmethod
+    def _span_summary() -> dict:
+        from ..utils.profiling import PROFILER
+        return PROFILER.summary() if PROFILER.enabled else {}
 
     @property
     def max_active_requests(self) -> int:
@@ -226,6 +189,7 @@ class LiteEngine:
                  "plan": self.plan.__dict__, "loadtime_policy": self.loadtime_policy.name,
                  "lora": self.lora_registry.stats() if self.lora_registry else {},
                  "multimodal": self.multimodal.stats() if self.multimodal else {},
+                 "memory": self.memory.as_dict(), "profile_spans": self._span_summary(),
                  "parallel": {"tp": self.rc.tensor_parallel_size, "ep": self.rc.expert_parallel_size,
                               "comm_backend": self.rc.comm_backend}}
         return self.controller.stats(extra)

@@ -287,6 +287,19 @@ def act_mul(x, act="silu", out=None):
     return out
 
 
+def activation(x, act="silu", out=None):
+    """Elementwise SiLU / tanh-GELU over a 2-D tensor."""
+    if not x.is_cuda:
+        return reference.apply_act(x.float(), act).to(x.dtype)
+    rows, d = x.shape
+    if out is None:
+        out = torch.empty(rows, d, dtype=x.dtype, device=x.device)
+    rc = _lib.kernels().fi_act(_p(x), _p(out), rows, d, x.stride(0), out.stride(0), _ACT[act], _DT[x.dtype], _stream())
+    _lib.check(rc, "fi_act")
+    _count()
+    return out
+
+
 def slot_mapping(positions, token_seq, block_tables, block_size, out=None):
     if not positions.is_cuda:
         return reference.slot_mapping(positions, token_seq, block_tables, block_size)

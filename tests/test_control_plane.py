@@ -191,3 +191,60 @@ def test_prefix_cache_longest_match_lru_and_budget():
     big.store(a, 16, blocks)                         # larger than the byte budget: not stored
     assert big.stats()["entries"] == 0
     assert not PrefixCache(0).enabled
+
+
+def test_generic_moe_activation_layers_and_sniffer_cpu():
+    import torch
+    from litevllm_b200.debug import ActivationSniffer
+    from litevllm_b200.layers.activation import GeluAndMul, Silu, SiluAndMul, get_act_fn
+    from litevllm_b200.layers.fused_moe import fused_moe
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(5, 16, generator=g)
+    assert torch.allclose(Silu()(x), torch.nn.functional.silu(x), atol=1e-6)
+    assert torch.allclose(SiluAndMul()(x), torch.nn.functional.silu(x[:, :8]) * x[:, 8:], atol=1e-6)
+    assert GeluAndMul()(x).shape == (5, 8) and isinstance(get_act_fn("gelu_pytorch_tanh"), torch.nn.Module)
+    E, H, I, k = 4, 16, 8, 2
+    w1, w2 = torch.randn(E, 2 * I, H, generator=g) * 0.2, torch.randn(E, H, I, generator=g) * 0.2
+    logits = torch.randn(5, E, generator=g)
+    got = fused_moe(x, w1, w2, logits, k)
+    probs = torch.softmax(logits, -1)
+    tw, ti = probs.topk(k, -1)
+    tw = tw / tw.sum(-1, keepdim=True)
+    want = torch.zeros(5, H)
+    for t in range(5):
+        for j in range(k):
+            e = int(ti[t, j])
+            h = x[t] @ w1[e].t()
+            want[t] += tw[t, j] * ((torch.nn.functional.silu(h[:I]) * h[I:]) @ w2[e].t())
+    assert torch.allclose(got, want, atol=1e-4)
+    lin = torch.nn.Sequential(torch.nn.Linear(16, 16), torch.nn.ReLU())
+    with ActivationSniffer(lin) as s:
+        lin(x)
+    assert "0" in s.stats and s.stats["0"].calls == 1 and "absmax" in s.report()
+
+
+def test_memory_auditor_and_runtime_factory_are_used():
+    from litevllm_b200 import LLM
+    llm = LLM("synthetic:tiny-llama-test", dtype="float32", device="cpu", max_num_seqs=2, max_model_len=64)
+    mem = llm.engine.memory
+    assert mem.param_bytes_by_dtype.get("float32", 0) > 0 and mem.kv_cache_bytes == llm.engine.kv_cache.total_bytes
+    assert mem.weight_bytes >= mem.param_bytes_by_dtype["float32"]
+    from litevllm_b200.engine.runtime_factory import RuntimeComponents
+    assert set(RuntimeComponents.__dataclass_fields__) <= set(vars(llm.engine))
+
+
+def test_span_profiler_accumulates_and_is_free_when_off():
+    from litevllm_b200.utils.profiling import SpanProfiler
+    p = SpanProfiler()
+    with p.span("x"):
+        pass
+    assert p.summary() == {}
+    p.configure(True)
+    for _ in range(3):
+        with p.span("step"):
+            pass
+    p.count("tokens", 5)
+    s = p.summary()
+    assert s["step"]["count"] == 3 and s["counters"]["tokens"] == 5
+    p.reset()
+    assert p.summary() == {}
