@@ -201,6 +201,20 @@ __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---------------------------------------------------------------- peer-memory words
+// 16-byte volatile accesses used by the inline-flag transfer format (value, epoch, value, epoch):
+// each 8-byte half is written atomically, so a reader that sees the epoch also sees the value.
+__device__ __forceinline__ void st_volatile_v4(uint4* p, uint4 v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
 // ---------------------------------------------------------------- misc
 __device__ __forceinline__ void set_status(int* status, int code) {
   if (status != nullptr) atomicCAS(status, 0, code);

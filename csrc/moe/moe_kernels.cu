@@ -23,6 +23,8 @@
 #include <stdint.h>
 
 #include "../common/launch.cuh"
+#include "../common/ptx.cuh"
+#include "../gemm/comm_desc.h"
 
 namespace {
 
@@ -204,9 +206,137 @@ __global__ void moe_combine_kernel(const T* __restrict__ y_sorted, const int* __
   }
 }
 
+// Expert-parallel combine fused with the all-reduce: every rank sums the routed outputs of ITS
+// experts for a token, pushes that fp32 partial straight into every peer's receive slab over NVLink
+// (each 8-byte word = one value + the call's epoch, so the receiver needs neither a fence nor a
+// separate flag), then adds the peers' partials in rank order (bitwise identical on all ranks) plus
+// the residual and writes the token.  One CTA per token; waits are bounded.
+struct CombineComm {
+  int world, rank;
+  long slab_elems;                  // values per (parity, source rank) slab
+  unsigned long long recv[8];       // low-latency receive area of rank d, as mapped here
+  unsigned int* epoch;              // local: completed fused calls
+  unsigned int* done;               // local: finished CTAs of this call
+  int* status;
+};
+
+template <typename T>
+__global__ void moe_combine_allreduce_kernel(const T* __restrict__ y_sorted, const int* __restrict__ slot_of,
+                                             const float* __restrict__ topk_w, const T* __restrict__ residual,
+                                             T* __restrict__ out, int K, int H, const CombineComm c) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  __shared__ volatile int aborted;
+  if (threadIdx.x == 0) aborted = 0;
+  __syncthreads();
+  const unsigned int epoch_now = *c.epoch + 1u;
+  const long parity = epoch_now & 1u;
+  const int t = blockIdx.x;
+  for (int ch = threadIdx.x; ch < H / 8; ch += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int k = 0; k < K; ++k) {
+      const int slot = slot_of ? slot_of[static_cast<long>(t) * K + k] : t * K + k;
+      if (slot < 0) continue;   // routed to an expert of another rank
+      const float w = topk_w[static_cast<long>(t) * K + k];
+      uint4 raw = *reinterpret_cast<const uint4*>(y_sorted + static_cast<long>(slot) * H + ch * 8);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += w * static_cast<float>(e[j]);
+    }
+    const long elem = static_cast<long>(t) * H + ch * 8;
+    const long my_off = (parity * c.world + c.rank) * c.slab_elems + elem;
+    for (int d = 0; d < c.world; ++d) {
+      if (d == c.rank) continue;
+      uint4* dst = reinterpret_cast<uint4*>(c.recv[d]) + (my_off >> 1);
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        fi::st_volatile_v4(dst + q, make_uint4(__float_as_uint(acc[2 * q]), epoch_now,
+                                               __float_as_uint(acc[2 * q + 1]), epoch_now));
+    }
+    float sum[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sum[j] = 0.f;
+    for (int s = 0; s < c.world; ++s) {
+      float v[8];
+      if (s == c.rank) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = acc[j];
+      } else {
+        const long off = (parity * c.world + s) * c.slab_elems + elem;
+        const uint4* src = reinterpret_cast<const uint4*>(c.recv[c.rank]) + (off >> 1);
+        const long long w0 = clock64();
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 wv = fi::ld_volatile_v4(src + q);
+          while (wv.y != epoch_now || wv.w != epoch_now) {
+            if (aborted || clock64() - w0 > FI_WAIT_CYCLES) {
+              fi::set_status(c.status, fi::kStatusTimeoutPeer);
+              aborted = 1;
+              break;
+            }
+            wv = fi::ld_volatile_v4(src + q);
+          }
+          v[2 * q] = __uint_as_float(wv.x);
+          v[2 * q + 1] = __uint_as_float(wv.z);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sum[j] += v[j];
+    }
+    if (residual != nullptr) {
+      uint4 raw = *reinterpret_cast<const uint4*>(residual + elem);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sum[j] += static_cast<float>(e[j]);
+    }
+    if (!aborted) {
+      uint4 o;
+      T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) oe[j] = static_cast<T>(sum[j]);
+      *reinterpret_cast<uint4*>(out + elem) = o;
+    }
+  }
+  // the last CTA of the call publishes the new epoch for the next fused call
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(c.done, 1u) == gridDim.x - 1) {
+      *c.done = 0;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned int*>(c.epoch) = epoch_now;
+    }
+  }
+}
+
 }  // namespace
 
 #define FI_STREAM(s) reinterpret_cast<cudaStream_t>(s)
+
+// comm: the FiComm descriptor of the symmetric heap with recv[] pointing at the low-latency slabs
+extern "C" int fi_moe_combine_allreduce(const void* y_sorted, const int* slot_of, const float* topk_w,
+                                        const void* residual, void* out, int T, int K, int H, int dtype,
+                                        int* status, void* stream, const FiComm* comm) {
+  if (T <= 0) return 0;
+  if (H % 8 != 0 || comm == nullptr || comm->world < 2 || comm->world > 8) return -10;
+  if (static_cast<long>(T) * H > comm->slab_elems) return -11;
+  CombineComm c;
+  c.world = comm->world; c.rank = comm->rank; c.slab_elems = comm->slab_elems;
+  for (int d = 0; d < 8; ++d) c.recv[d] = comm->recv[d];
+  c.epoch = reinterpret_cast<unsigned int*>(comm->epoch);
+  c.done = reinterpret_cast<unsigned int*>(comm->done);
+  c.status = status;
+  if (dtype == 0)
+    fi::launch_kernel(moe_combine_allreduce_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, FI_STREAM(stream), 0,
+                      (const __nv_bfloat16*)y_sorted, slot_of, topk_w, (const __nv_bfloat16*)residual,
+                      (__nv_bfloat16*)out, K, H, c);
+  else
+    fi::launch_kernel(moe_combine_allreduce_kernel<__half>, dim3(T), dim3(128), 0, FI_STREAM(stream), 0,
+                      (const __half*)y_sorted, slot_of, topk_w, (const __half*)residual, (__half*)out, K, H, c);
+  return static_cast<int>(cudaGetLastError());
+}
 
 extern "C" int fi_moe_route(const float* logits, const float* bias, const float* expert_scale,
                             int* topk_ids, float* topk_w, int T, int E, int K, int mode, int renorm,

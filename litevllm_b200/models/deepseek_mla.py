@@ -175,6 +175,19 @@ class RoutedExperts(nn.Module):
                                       _p(ids_flat), n, self.e_lo, e_hi, H, self.I, _p(y), _stream())
             _lib.check(rc, "fi_gguf_moe_down")
             out = torch.empty(T, H, dtype=x.dtype, device=x.device)
+            heap = None
+            if pstate.ep_size() > 1:
+                from ..parallel import fused_ops
+                heap = fused_ops.ep_heap(x)
+            if heap is not None and heap.fits_low_latency(T, H):
+                # expert parallel: combine + sum over ranks in one kernel (routes of other ranks are zero rows)
+                import ctypes
+                comm = heap.comm_desc(mode=1, T=T, N=H, xfer_16bit=2)
+                rc = lib.fi_moe_combine_allreduce(_p(y), None, _p(weights), None, _p(out), T, K, H, ops._DT[x.dtype],
+                                                  _p(ops.status_word(x.device)), _stream(), ctypes.byref(comm))
+                _lib.check(rc, "fi_moe_combine_allreduce")
+                _count(3)
+                return out
             rc = lib.fi_moe_combine(_p(y), None, _p(weights), None, _p(out), T, K, H, ops._DT[x.dtype], _stream())
             _lib.check(rc, "fi_moe_combine")
             _count(3)

@@ -146,9 +146,13 @@ class Gemma4Experts(nn.Module):
 
     def forward(self, x, ids, weights):
         self.finalize()
-        out = moe_ops.fused_experts(x, self.w_gate_up, self.w_down, ids, weights, self.e_local, self.e_lo, "gelu_tanh")
+        heap = None
         if pstate.ep_size() > 1:
             from ..parallel import fused_ops
+            heap = fused_ops.ep_heap(x)
+        out = moe_ops.fused_experts(x, self.w_gate_up, self.w_down, ids, weights, self.e_local, self.e_lo, "gelu_tanh",
+                                    ep_heap=heap)
+        if pstate.ep_size() > 1 and heap is None:
             out = fused_ops.all_reduce_activations(out)
         return out
 

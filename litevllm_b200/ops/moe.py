@@ -78,10 +78,11 @@ def _reference_experts(x, w_gate_up: Int4Weight, w_down: Int4Weight, ids, weight
 
 def fused_experts(x: torch.Tensor, w_gate_up: Int4Weight, w_down: Int4Weight, ids: torch.Tensor,
                   weights: torch.Tensor, num_experts_local: int, e_lo: int, act: str = "gelu_tanh",
-                  residual: torch.Tensor | None = None) -> torch.Tensor:
+                  residual: torch.Tensor | None = None, ep_heap=None) -> torch.Tensor:
     """x [T, H]; stacked int4 experts (``w_gate_up``: [E_local * 2I, H], ``w_down``: [E_local * H, I]);
     ids/weights from :func:`route` (global expert ids).  Returns sum_k w * expert(x) [+ residual]
-    over the local experts ``[e_lo, e_lo + num_experts_local)``."""
+    over the local experts ``[e_lo, e_lo + num_experts_local)``.  With ``ep_heap`` (the symmetric
+    heap of an expert-parallel group, GPU only) the result is also summed over the ranks."""
     T, H = x.shape
     K = ids.shape[1]
     e_hi = e_lo + num_experts_local
@@ -131,7 +132,18 @@ def fused_experts(x: torch.Tensor, w_gate_up: Int4Weight, w_down: Int4Weight, id
                                  st, ctypes.byref(g2))
     _lib.check(rc, "fi_awq_gemm_grouped(down)")
     out = torch.empty(T, H, dtype=x.dtype, device=dev)
+    if ep_heap is not None and ep_heap.fits_low_latency(T, H):
+        # expert parallel: the combine also sums the ranks' partial outputs (one kernel, peer stores)
+        comm = ep_heap.comm_desc(mode=1, T=T, N=H, xfer_16bit=2)
+        rc = lib.fi_moe_combine_allreduce(_p(y_sorted), _p(slot_of), _p(weights), _p(residual), _p(out), T, K, H,
+                                          _DT[x.dtype], sw, st, ctypes.byref(comm))
+        _lib.check(rc, "fi_moe_combine_allreduce")
+        _count(5)
+        return out
     rc = lib.fi_moe_combine(_p(y_sorted), _p(slot_of), _p(weights), _p(residual), _p(out), T, K, H, _DT[x.dtype], st)
     _lib.check(rc, "fi_moe_combine")
     _count(5)
+    if ep_heap is not None:       # too large for the low-latency slabs: library collective
+        from ..parallel import state as pstate
+        pstate.all_reduce(out)
     return out

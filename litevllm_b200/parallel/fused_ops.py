@@ -128,6 +128,12 @@ def allgather_gemm(x_shard: torch.Tensor, w: torch.Tensor, T_total: int, rows_pe
     return out
 
 
+def ep_heap(x: torch.Tensor):
+    """Symmetric heap to use for fused expert-parallel combines of ``x`` (None -> library collectives)."""
+    st = pstate.get_state()
+    return st.symm if (x.is_cuda and st.comm_backend == "fused" and st.symm is not None) else None
+
+
 def all_reduce_activations(x: torch.Tensor) -> torch.Tensor:
     """Sum a replicated-layout activation over the ranks (expert-parallel combine)."""
     return pstate.all_reduce(x)
