@@ -248,3 +248,35 @@ def test_span_profiler_accumulates_and_is_free_when_off():
     assert s["step"]["count"] == 3 and s["counters"]["tokens"] == 5
     p.reset()
     assert p.summary() == {}
+
+
+def test_tokenizer_helpers_and_incremental_detokenizer():
+    from litevllm_b200.tokenizers import IncrementalDetokenizer, TokenizerLike, TokenizerRegistry, get_tokenizer
+    from litevllm_b200.transformers_utils.config import build_fallback_hf_config, is_gguf_path
+
+    class ByteTok:
+        eos_token_id, bos_token_id = None, None
+
+        def encode(self, text, add_special_tokens=True):
+            return list(text.encode())
+
+        def decode(self, ids, skip_special_tokens=True):
+            return bytes(ids).decode("utf-8", errors="replace")
+
+        def __len__(self):
+            return 256
+
+    tok = ByteTok()
+    assert isinstance(tok, TokenizerLike)
+    det = IncrementalDetokenizer(tok)
+    text = "héllo ✓"
+    deltas = [det.push(t) for t in tok.encode(text)]
+    assert "".join(deltas) == text and "�" not in "".join(deltas) and "" in deltas   # multi-byte chars wait
+    TokenizerRegistry.register("bytes", lambda path, **kw: tok)
+    assert get_tokenizer("anything", tokenizer_mode="bytes") is tok
+    dummy = get_tokenizer("/nonexistent/path", vocab_size=100)
+    assert len(dummy) == 100 and get_tokenizer("/nonexistent/path", vocab_size=100) is dummy   # cached
+    flat = build_fallback_hf_config({"architectures": ["Gemma4ForConditionalGeneration"],
+                                     "text_config": {"hidden_size": 8, "model_type": "gemma4_text"},
+                                     "vision_config": {"patch_size": 16}})
+    assert flat["hidden_size"] == 8 and flat["vision_config"]["patch_size"] == 16 and is_gguf_path("a/b.GGUF")
