@@ -26,7 +26,8 @@ namespace {
 template <int BN, int STAGES, bool DUAL>
 __global__ void __launch_bounds__(kThreads)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
-                  const __grid_constant__ TokenMaps tmaps_x, const GemmParams p) {
+                  const __grid_constant__ TokenMaps tmaps_x, const GemmParams p_in) {
+  GemmParams p = p_in;
   constexpr int A_BYTES = BM * 128;
   constexpr int B_BYTES = BN * 128;
   constexpr int STAGE_BYTES = A_BYTES * (DUAL ? 2 : 1) + B_BYTES;
@@ -44,6 +45,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   uint64_t* accum_bar = empty_bar + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
   volatile int* aborted = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  p.row_ss = reinterpret_cast<float*>(tmem_slot + 2);   // [BN] floats after the control words
+  const bool rms = p.rms_eps > 0.f;
   // fp32 staging of the accumulator tile(s); aliases the pipeline ring once the main loop is done.
   float* stage_f32 = reinterpret_cast<float*>(smem);
 
@@ -61,7 +64,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
+      mbar_init(&empty_bar[s], rms ? 1 + 4 : 1);   // MMA commit (+ the four warps that read the token tile)
     }
     mbar_init(accum_bar, 1);
     *aborted = 0;
@@ -94,6 +97,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       // Weights do not depend on the previous kernel: start streaming them for the first stages
       // before blocking on the programmatic dependency, then add the token tiles.
       const int n_pre = min(STAGES, kb_end - kb_begin);
+      if (p.w_dynamic) pdl_wait();   // the weights come from the preceding kernel: nothing may be read yet
       for (int it = 0; it < n_pre; ++it) {
         uint8_t* a = stage_base + it * STAGE_BYTES;
         mbar_expect_tx(&full_bar[it], STAGE_BYTES);
@@ -161,6 +165,61 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       umma_commit(accum_bar);
     }
   }
+  else if (rms) {
+    // ------------------------------------------------------------ warps 2..5: sum of squares per token
+    // The token tile of every stage is [BN rows][64 values] in the 128-byte swizzle; 128 threads
+    // read it as 16-byte chunks (chunk c: row c / 8), eight neighbouring threads share a row.
+    const int tid = threadIdx.x - 64;
+    constexpr int kChunks = BN * 8;
+    constexpr int kPerThread = (kChunks + 127) / 128;
+    float ss[kPerThread];
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) ss[i] = 0.f;
+    bool ok = true;
+    for (int kb = kb_begin; kb < kb_end && ok; ++kb) {
+      const int it = kb - kb_begin;
+      const int s = it % STAGES;
+      const uint32_t ph = (it / STAGES) & 1;
+      if (!mbar_wait(&full_bar[s], ph)) {
+        set_status(p.status, kStatusTimeoutFull);
+        *aborted = 1;
+        ok = false;
+        break;
+      }
+      const uint8_t* b = stage_base + s * STAGE_BYTES + A_BYTES * (DUAL ? 2 : 1);
+#pragma unroll
+      for (int i = 0; i < kPerThread; ++i) {
+        const int c = tid + i * 128;
+        if (c < kChunks) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(b + sw128_offset(c >> 3, c & 7));
+          const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float lo, hi;
+            if (p.is_fp16) {
+              const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+              lo = __low2float(h); hi = __high2float(h);
+            } else {
+              lo = __uint_as_float(w[j] << 16); hi = __uint_as_float(w[j] & 0xffff0000u);
+            }
+            ss[i] += lo * lo + hi * hi;
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
+    }
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) {
+      float v = ss[i];
+      v += __shfl_xor_sync(0xffffffffu, v, 1);
+      v += __shfl_xor_sync(0xffffffffu, v, 2);
+      v += __shfl_xor_sync(0xffffffffu, v, 4);
+      const int c = tid + i * 128;
+      if ((c & 7) == 0 && c < kChunks) p.row_ss[c >> 3] = v;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");   // the four warps: row_ss complete before it is used
+  }
   // ---------------------------------------------------------------- epilogue (epilogue.cuh)
   if (warp >= 2) epilogue_tmem_to_smem<BN, DUAL>(p, accum_bar, tmem_base, stage_f32, aborted, warp, lane);
   __syncthreads();
@@ -174,7 +233,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
 
 template <int BN, int STAGES, bool DUAL>
 constexpr int smem_bytes() {
-  return STAGES * (BM * 128 * (DUAL ? 2 : 1) + BN * 128) + (2 * STAGES + 1) * 8 + 16 + 1024;
+  return STAGES * (BM * 128 * (DUAL ? 2 : 1) + BN * 128) + (2 * STAGES + 1) * 8 + 16 + BN * 4 + 1024;
 }
 
 // Split-K choice.  A cluster of S CTAs must be co-scheduled inside one GPC, so the number of
@@ -272,8 +331,9 @@ static int fi_dense_gemm_impl(const void* X, const void* W, void* C, const void*
                              const void* residual, int T, int N, int K, int ldx, int ldw, int ldc,
                              int act, int dual_rows, int out_fp32, int dtype, int splits, int bn,
                              int* status, void* stream,
-                             const FiComm* comm) {
+                             const FiComm* comm, float rms_eps = 0.f, int w_dynamic = 0) {
   if (T <= 0 || N <= 0 || K <= 0) return 0;
+  if (rms_eps > 0.f && (K % BK) != 0) return -21;   // the sum of squares reads whole 64-wide K blocks
   if ((K % 8) != 0 || (ldc % 8) != 0 || (reinterpret_cast<uintptr_t>(C) & 15) != 0) return -10;
   if (dual_rows > 0 && N != dual_rows) return -11;
   if (bn == 0) bn = fi_dense_gemm_pick_bn(T);
@@ -309,6 +369,7 @@ static int fi_dense_gemm_impl(const void* X, const void* W, void* C, const void*
   p.splits = splits; p.status = status;
   p.tile_expert = nullptr; p.tile_row0 = nullptr; p.tile_rows = nullptr; p.n_tiles = nullptr; p.expert_rows = 0; p.grid_tiles = 0;
   p.comm_mode = 0; p.world = 1; p.rank = 0; p.rows_per_rank = 0; p.xfer_16bit = 0; p.trace = nullptr;
+  p.rms_eps = rms_eps; p.row_ss = nullptr; p.w_dynamic = w_dynamic;
   p.ag_world = 1; p.ag_rows_per_rank = 0; p.slab_elems = 0; p.epoch = nullptr; p.done = nullptr;
   for (int d = 0; d < kMaxRanks; ++d) { p.recv[d] = 0; p.flags[d] = 0; p.ready[d] = 0; }
   if (comm != nullptr) {
@@ -337,6 +398,27 @@ extern "C" int fi_dense_gemm(const void* X, const void* W, void* C, const void* 
                              int act, int dual_rows, int out_fp32, int dtype, int splits, int bn,
                              int* status, void* stream) {
   return fi_dense_gemm_impl(X, W, C, bias, residual, T, N, K, ldx, ldw, ldc, act, dual_rows, out_fp32, dtype, splits, bn, status, stream, nullptr);
+}
+
+// RMSNorm fused in front of the GEMM: C = (X W'^T) * rsqrt(mean_k(X^2) + eps), W' = W * diag(norm weight)
+// folded by the caller.  The kernel takes the per-token sum of squares from the token tiles it stages
+// anyway, so the normalised activations never exist in memory.  K must be a multiple of 64.
+extern "C" int fi_dense_gemm_rmsnorm(const void* X, const void* W, void* C, const void* bias,
+                             const void* residual, int T, int N, int K, int ldx, int ldw, int ldc,
+                             int act, int dual_rows, int out_fp32, int dtype, int splits, int bn,
+                             float eps, int* status, void* stream) {
+  if (!(eps > 0.f)) return -20;
+  return fi_dense_gemm_impl(X, W, C, bias, residual, T, N, K, ldx, ldw, ldc, act, dual_rows, out_fp32, dtype, splits, bn, status, stream, nullptr, eps);
+}
+
+// Same as fi_dense_gemm for a weight matrix that the preceding kernel on the stream produced (for
+// example a dequantised scratch copy): the producer warp then reads nothing before the
+// programmatic-launch wait.  fi_dense_gemm itself assumes weights that never change.
+extern "C" int fi_dense_gemm_dynw(const void* X, const void* W, void* C, const void* bias,
+                             const void* residual, int T, int N, int K, int ldx, int ldw, int ldc,
+                             int act, int dual_rows, int out_fp32, int dtype, int splits, int bn,
+                             int* status, void* stream) {
+  return fi_dense_gemm_impl(X, W, C, bias, residual, T, N, K, ldx, ldw, ldc, act, dual_rows, out_fp32, dtype, splits, bn, status, stream, nullptr, 0.f, 1);
 }
 
 // Same GEMM with a fused collective and/or an all-gathered token operand (see comm_desc.h).

@@ -44,6 +44,12 @@ struct GemmParams {
   int is_fp16;
   int splits;
   int* status;
+  // fused RMSNorm of the token operand (rms_eps > 0): out = (W' . x) * rsqrt(mean(x^2) + eps) with the
+  // norm weight folded into W' at load time; the sum of squares is taken from the token tiles in
+  // shared memory while the main loop runs
+  float rms_eps;
+  int w_dynamic;         // 1: the weight operand was written by the preceding kernel (no prefetch before the PDL wait)
+  float* row_ss;         // shared-memory array [BN]: sum of squares of this CTA's K range per token
   // int4 weight-only extras (unused by the dense kernel)
   const void* scales;   // [K/G, rows]
   const uint8_t* zeros; // [K/G, rows] or null
@@ -194,14 +200,27 @@ __device__ __forceinline__ void epilogue_tmem_to_smem(const GemmParams& p, uint6
   const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
   if (ok) {
     const bool fuse_act_now = DUAL && (p.splits == 1);
+    const bool norm_now = p.rms_eps > 0.f && p.splits == 1;   // with split-K the scale is applied after the sum
+    const float inv_k = 1.f / static_cast<float>(p.K);
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 16) {
       uint32_t r[16];
       tmem_ld_x16(taddr + c0, r);
+      if (norm_now) {
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          r[j] = __float_as_uint(__uint_as_float(r[j]) * rsqrtf(p.row_ss[c0 + j] * inv_k + p.rms_eps));
+      }
       if (DUAL) {
         uint32_t u[16];
         tmem_ld_x16(taddr + BN + c0, u);
         tmem_ld_wait();
+        if (norm_now) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            u[j] = __float_as_uint(__uint_as_float(u[j]) * rsqrtf(p.row_ss[c0 + j] * inv_k + p.rms_eps));
+        }
         if (fuse_act_now) {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
@@ -264,6 +283,13 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
           u[0] += c.x; u[1] += c.y; u[2] += c.z; u[3] += c.w;
           u[4] += d.x; u[5] += d.y; u[6] += d.z; u[7] += d.w;
         }
+      }
+      if (p.rms_eps > 0.f && S > 1) {
+        float ss = 0.f;
+        for (int pr = 0; pr < S; ++pr) ss += cluster.map_shared_rank(p.row_ss, pr)[tl];
+        const float rstd = rsqrtf(ss / static_cast<float>(p.K) + p.rms_eps);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { g[j] *= rstd; u[j] *= rstd; }
       }
       if (DUAL && S > 1) {
 #pragma unroll

@@ -44,23 +44,40 @@ class LiteLinear(nn.Module):
 
     # ------------------------------------------------------------------ forward
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None,
-                out: torch.Tensor | None = None, out_dtype=None, lora_mapping=None) -> torch.Tensor:
-        """x: [T, in].  With ``residual`` the result is ``x W^T + residual`` (fused epilogue)."""
+                out: torch.Tensor | None = None, out_dtype=None, lora_mapping=None,
+                norm_eps: float = 0.0, lora_x: torch.Tensor | None = None) -> torch.Tensor:
+        """x: [T, in].  With ``residual`` the result is ``x W^T + residual`` (fused epilogue).  With
+        ``norm_eps`` the rows of x are RMS-normalised inside the GEMM (the norm weight must have been
+        folded into this layer with :meth:`fold_input_norm`)."""
         if self.shard == "row" and self.tp > 1:
             return self._row_parallel(x, residual, out)
-        y = self._matmul(x, residual, out, out_dtype)
+        y = self._matmul(x, residual, out, out_dtype, norm_eps=norm_eps)
         if self.lora is not None and lora_mapping is not None:
-            y = self.lora.apply(self, x, y, lora_mapping)
+            # with a folded input norm the adapters still see the normalised, weighted activations
+            y = self.lora.apply(self, lora_x if lora_x is not None else x, y, lora_mapping)
         return y
 
-    def _matmul(self, x, residual=None, out=None, out_dtype=None, use_bias: bool = True):
+    def _matmul(self, x, residual=None, out=None, out_dtype=None, use_bias: bool = True, norm_eps: float = 0.0):
         if self.quant_method is not None:
+            assert norm_eps == 0.0, "the fused input norm needs an unquantised weight"
             return self.quant_method.apply(self, x, residual=residual, out=out, out_dtype=out_dtype,
                                            use_bias=use_bias)
         if self.gated_act is not None:
-            return ops.gated_linear(x, self.weight, self.gated_act, out=out)
+            return ops.gated_linear(x, self.weight, self.gated_act, out=out, rms_eps=norm_eps)
         return ops.linear(x, self.weight, self.bias if use_bias else None, residual, out=out,
-                          out_dtype=out_dtype)
+                          out_dtype=out_dtype, rms_eps=norm_eps)
+
+    def fold_input_norm(self, norm_weight: torch.Tensor, plus_one: bool = False) -> bool:
+        """Multiply the weight columns by the RMSNorm weight of the layer's input (in place), so the
+        norm in front of this layer reduces to a per-row scale that the GEMM kernel applies itself.
+        Returns False (and changes nothing) for quantised layers and input widths the kernel cannot
+        take."""
+        if self.quant_method is not None or self.in_features % 64 != 0 or self.shard == "row":
+            return False
+        g = norm_weight.float() + (1.0 if plus_one else 0.0)
+        self.weight.data = (self.weight.data.float() * g.to(self.weight.device)[None, :]).to(self.weight.dtype)
+        self.input_norm_folded = True
+        return True
 
     def _row_parallel(self, x, residual, out):
         from ..parallel import fused_ops

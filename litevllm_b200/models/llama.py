@@ -26,9 +26,14 @@ class RMSNormWeight(nn.Module):
         self.weight = nn.Parameter(torch.ones(dim, dtype=dtype), requires_grad=False)
         self.eps = eps
         self.w_mode = 1 if plus_one else 0
+        self.folded = False      # True: the weight lives in the following linear layers (w_mode 2 = no weight)
 
     def forward(self, x, out=None):
-        return ops.rmsnorm(x, self.weight, self.eps, w_mode=self.w_mode, out=out)
+        return ops.rmsnorm(x, self.weight, self.eps, w_mode=2 if self.folded else self.w_mode, out=out)
+
+    def weighted(self, x):
+        """The full norm including its weight, whether or not the weight was folded away."""
+        return ops.rmsnorm(x, self.weight, self.eps, w_mode=self.w_mode)
 
 
 class LlamaAttention(nn.Module):
@@ -66,8 +71,8 @@ class LlamaAttention(nn.Module):
         head0 = (r // self.kv_replicas) * self.nkv
         return head0 * self.hd, self.nkv * self.hd
 
-    def forward(self, x, h, batch, kv, cos_sin):
-        qkv = self.qkv_proj(x, lora_mapping=batch.lora_mapping)
+    def forward(self, x, h, batch, kv, cos_sin, norm_eps: float = 0.0, lora_x=None):
+        qkv = self.qkv_proj(x, lora_mapping=batch.lora_mapping, norm_eps=norm_eps, lora_x=lora_x)
         k_cache, v_cache = kv
         cfg = batch.config
         ops.rope_and_cache(qkv, batch.positions, cos_sin, batch.slot_mapping, k_cache, v_cache, self.nh,
@@ -97,8 +102,8 @@ class LlamaMLP(nn.Module):
         self.down_proj = LiteLinear(inter, arch.hidden_size, dtype=dtype, shard="row",
                                     quant_config=quant_config, prefix=prefix + ".down_proj")
 
-    def forward(self, x, h, batch):
-        a = self.gate_up_proj(x, lora_mapping=batch.lora_mapping)
+    def forward(self, x, h, batch, norm_eps: float = 0.0, lora_x=None):
+        a = self.gate_up_proj(x, lora_mapping=batch.lora_mapping, norm_eps=norm_eps, lora_x=lora_x)
         return self.down_proj(a, residual=h, out=h, lora_mapping=batch.lora_mapping)
 
 
@@ -111,11 +116,30 @@ class LlamaDecoderLayer(nn.Module):
         self.post_attention_layernorm = RMSNormWeight(arch.hidden_size, arch.rms_eps, dtype, arch.norm_plus_one)
         self.mlp = LlamaMLP(arch, dtype, quant_config, prefix + ".mlp")
 
+        self.fused_norm = False
+
+    def fold_norms(self) -> None:
+        """Move both RMSNorm weights into the linear layers they feed, so that on a GPU the norms run
+        inside the qkv and gate|up GEMM kernels (two launches fewer per layer)."""
+        if self.input_layernorm.folded or self.post_attention_layernorm.folded:
+            return
+        qkv, gu = self.self_attn.qkv_proj, self.mlp.gate_up_proj
+        if qkv.quant_method is not None or gu.quant_method is not None or qkv.in_features % 64 or gu.in_features % 64:
+            return
+        qkv.fold_input_norm(self.input_layernorm.weight, self.input_layernorm.w_mode == 1)
+        gu.fold_input_norm(self.post_attention_layernorm.weight, self.post_attention_layernorm.w_mode == 1)
+        self.input_layernorm.folded = self.post_attention_layernorm.folded = True
+        self.fused_norm = True
+
     def forward(self, h, batch, kv, cos_sin):
+        if self.fused_norm and h.is_cuda and batch.lora_mapping is None:
+            h = self.self_attn(h, h, batch, kv, cos_sin, norm_eps=self.input_layernorm.eps)
+            return self.mlp(h, h, batch, norm_eps=self.post_attention_layernorm.eps)
+        lora = batch.lora_mapping is not None and self.fused_norm
         x = self.input_layernorm(h)
-        h = self.self_attn(x, h, batch, kv, cos_sin)
+        h = self.self_attn(x, h, batch, kv, cos_sin, lora_x=self.input_layernorm.weighted(h) if lora else None)
         x = self.post_attention_layernorm(h)
-        return self.mlp(x, h, batch)
+        return self.mlp(x, h, batch, lora_x=self.post_attention_layernorm.weighted(h) if lora else None)
 
 
 class LlamaForCausalLM(nn.Module):
@@ -133,6 +157,9 @@ class LlamaForCausalLM(nn.Module):
         self.layers = nn.ModuleList([LlamaDecoderLayer(arch, i, mc.dtype, qc) for i in range(arch.num_layers)])
         self.norm = RMSNormWeight(arch.hidden_size, arch.rms_eps, mc.dtype, arch.norm_plus_one)
         self.tie = arch.tie_embeddings
+        import os
+        # RMSNorm inside the qkv / gate|up GEMMs (dense 16-bit weights only); FI_FUSE_RMSNORM=0 keeps the norms apart
+        self.fuse_rmsnorm = os.environ.get("FI_FUSE_RMSNORM", "1") != "0" and mc.dtype in (torch.bfloat16, torch.float16)
         if not self.tie:
             self.lm_head = LiteLinear(arch.hidden_size, arch.vocab_size, dtype=mc.dtype, shard="column",
                                       prefix="lm_head")
@@ -176,4 +203,8 @@ class LlamaForCausalLM(nn.Module):
     def load_weights(self, weights):
         """weights: iterable of (hf_name, tensor).  Returns the set of consumed names."""
         from ..loaders.weight_utils import load_llama_style
-        return load_llama_style(self, weights)
+        loaded = load_llama_style(self, weights)
+        if self.fuse_rmsnorm:
+            for layer in self.layers:
+                layer.fold_norms()
+        return loaded

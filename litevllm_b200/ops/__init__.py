@@ -78,9 +78,21 @@ def scratch(name: str, nbytes: int, device: torch.device) -> torch.Tensor:
 
 
 # ---------------------------------------------------------------------------- GEMM
-def linear(x, w, bias=None, residual=None, act=None, out=None, out_dtype=None, splits=0, bn=0):
-    """``act(x @ w.T) + bias + residual``.  x: [T, K], w: [N, K] (same 16-bit dtype)."""
+def _rms_scaled(x, eps):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+
+
+def linear(x, w, bias=None, residual=None, act=None, out=None, out_dtype=None, splits=0, bn=0, rms_eps=0.0,
+           static_weight=True):
+    """``act(x @ w.T) + bias + residual``.  x: [T, K], w: [N, K] (same 16-bit dtype).  With
+    ``rms_eps > 0`` the rows of ``x`` are RMS-normalised (no weight: fold it into ``w``) inside the
+    GEMM kernel.  ``static_weight=False`` is REQUIRED when ``w`` was written by a kernel earlier on
+    the stream (a dequantised scratch copy, a computed matrix): the kernel otherwise starts reading
+    weight tiles before its predecessor has finished."""
     if not x.is_cuda:
+        if rms_eps > 0:
+            x = _rms_scaled(x, rms_eps)
         y = reference.linear(x, w, bias, residual, act, out_dtype)
         if out is not None:
             out.copy_(y)
@@ -94,18 +106,29 @@ def linear(x, w, bias=None, residual=None, act=None, out=None, out_dtype=None, s
     if T == 0:
         return out
     assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
-    rc = _lib.kernels().fi_dense_gemm(
-        _p(x), _p(w), _p(out), _p(bias), _p(residual), T, N, K, x.stride(0), w.stride(0),
-        out.stride(0), _ACT[act], 0, 1 if out.dtype == torch.float32 else 0, _DT[x.dtype], splits,
-        bn, _p(status_word(x.device)), _stream())
+    if rms_eps > 0:
+        rc = _lib.kernels().fi_dense_gemm_rmsnorm(
+            _p(x), _p(w), _p(out), _p(bias), _p(residual), T, N, K, x.stride(0), w.stride(0),
+            out.stride(0), _ACT[act], 0, 1 if out.dtype == torch.float32 else 0, _DT[x.dtype], splits,
+            bn, float(rms_eps), _p(status_word(x.device)), _stream())
+        _lib.check(rc, "fi_dense_gemm_rmsnorm")
+        _count()
+        return out
+    fn = _lib.kernels().fi_dense_gemm if static_weight else _lib.kernels().fi_dense_gemm_dynw
+    rc = fn(_p(x), _p(w), _p(out), _p(bias), _p(residual), T, N, K, x.stride(0), w.stride(0),
+            out.stride(0), _ACT[act], 0, 1 if out.dtype == torch.float32 else 0, _DT[x.dtype], splits,
+            bn, _p(status_word(x.device)), _stream())
     _lib.check(rc, "fi_dense_gemm")
     _count()
     return out
 
 
-def gated_linear(x, w_gate_up, act="silu", out=None, splits=0, bn=0):
-    """``act(x @ Wg.T) * (x @ Wu.T)`` with ``w_gate_up = [Wg; Wu]`` of shape [2*I, K] -> [T, I]."""
+def gated_linear(x, w_gate_up, act="silu", out=None, splits=0, bn=0, rms_eps=0.0):
+    """``act(x @ Wg.T) * (x @ Wu.T)`` with ``w_gate_up = [Wg; Wu]`` of shape [2*I, K] -> [T, I]
+    (``rms_eps > 0``: rows of ``x`` RMS-normalised inside the kernel)."""
     if not x.is_cuda:
+        if rms_eps > 0:
+            x = _rms_scaled(x, rms_eps)
         y = reference.gated_linear(x, w_gate_up, act)
         if out is not None:
             out.copy_(y)
@@ -117,10 +140,16 @@ def gated_linear(x, w_gate_up, act="silu", out=None, splits=0, bn=0):
         out = torch.empty(T, inter, dtype=x.dtype, device=x.device)
     if T == 0:
         return out
-    rc = _lib.kernels().fi_dense_gemm(
-        _p(x), _p(w_gate_up), _p(out), None, None, T, inter, K, x.stride(0), w_gate_up.stride(0),
-        out.stride(0), _ACT[act], inter, 0, _DT[x.dtype], splits, bn,
-        _p(status_word(x.device)), _stream())
+    if rms_eps > 0:
+        rc = _lib.kernels().fi_dense_gemm_rmsnorm(
+            _p(x), _p(w_gate_up), _p(out), None, None, T, inter, K, x.stride(0), w_gate_up.stride(0),
+            out.stride(0), _ACT[act], inter, 0, _DT[x.dtype], splits, bn, float(rms_eps),
+            _p(status_word(x.device)), _stream())
+    else:
+        rc = _lib.kernels().fi_dense_gemm(
+            _p(x), _p(w_gate_up), _p(out), None, None, T, inter, K, x.stride(0), w_gate_up.stride(0),
+            out.stride(0), _ACT[act], inter, 0, _DT[x.dtype], splits, bn,
+            _p(status_word(x.device)), _stream())
     _lib.check(rc, "fi_dense_gemm(gated)")
     _count()
     return out

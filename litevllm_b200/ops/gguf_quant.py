@@ -156,4 +156,4 @@ def gguf_linear(x: torch.Tensor, raw: torch.Tensor, ggml_type: int, K: int, out=
         return out
     dense = scratch("gguf_dense", N * K * 2, x.device)[: N * K * 2].view(x.dtype).view(N, K)
     dequantize_cuda(raw, ggml_type, K, x.dtype, out=dense)
-    return linear(x, dense, residual=residual, out=out, out_dtype=out_dtype)
+    return linear(x, dense, residual=residual, out=out, out_dtype=out_dtype, static_weight=False)

@@ -332,3 +332,49 @@ def test_q8_0_quantize_roundtrip():
     raw = gq.quantize_q8_0(w)
     back = gq.dequantize(raw, 8, 256)
     assert float((back - w).abs().max()) < float(w.abs().max()) / 127 + 1e-3
+
+
+@pytest.mark.parametrize("T,N,K,splits", [(32, 2560, 2048, 0), (1, 256, 512, 1), (7, 384, 1024, 4), (300, 512, 2048, 0),
+                                          (64, 1024, 4096, 2)])
+@pytest.mark.parametrize("gated", [False, True])
+def test_gemm_with_fused_rmsnorm(T, N, K, splits, gated):
+    """RMSNorm folded into the GEMM (norm weight in the weight columns, per-row scale taken from the
+    token tiles in shared memory) vs norm-then-matmul in fp32."""
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(T * 7 + N)
+    x = (torch.randn(T, K, generator=g, device=dev) * 3.0 + 0.5).bfloat16()
+    gamma = (1.0 + 0.3 * torch.randn(K, generator=g, device=dev))
+    rows = 2 * N if gated else N
+    w = (torch.randn(rows, K, generator=g, device=dev) * 0.03).bfloat16()
+    w_folded = (w.float() * gamma[None, :]).bfloat16()
+    eps = 1e-5
+    xn = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + eps)
+    if gated:
+        h = xn @ w_folded.float().t()
+        want = torch.nn.functional.silu(h[:, :N]) * h[:, N:]
+        got = ops.gated_linear(x, w_folded, "silu", splits=splits, rms_eps=eps)
+    else:
+        res = torch.randn(T, N, generator=g, device=dev).bfloat16()
+        want = xn @ w_folded.float().t() + res.float()
+        got = ops.linear(x, w_folded, None, res, splits=splits, rms_eps=eps)
+    torch.cuda.synchronize()
+    ops.check_status(dev)
+    err = (got.float() - want).abs().max().item()
+    assert err < 0.03 * max(1.0, want.abs().max().item()), err
+
+
+def test_gemm_on_weights_written_by_the_previous_kernel():
+    """A scratch weight matrix that is rewritten before every GEMM (the GGUF dequantise -> GEMM path for
+    more than 8 rows): with programmatic dependent launch the GEMM must not read weight tiles before
+    the dequantise kernel has finished, whatever the scratch held before."""
+    from litevllm_b200.ops import gguf_quant as gq
+    ty, rows, K, M = gq.GGML_TYPES["Q8_0"], 2048, 2048, 32
+    x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    raws = [gq.random_blocks(ty, rows, K, seed=10 + i, scale=0.02).to(DEV) for i in range(6)]
+    wants = [x.float().cpu() @ gq.dequantize(r.cpu(), ty, K).t() for r in raws]
+    for rep in range(3):
+        outs = [gq.gguf_linear(x, r, ty, K, out_dtype=torch.float32) for r in raws]   # back to back, same scratch
+        torch.cuda.synchronize()
+        for i, (o, w) in enumerate(zip(outs, wants)):
+            _close(o.cpu(), w, 3e-2, 0.5, f"dynamic weights rep {rep} matrix {i}")
+    ops.check_status(DEV)
