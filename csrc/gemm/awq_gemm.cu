@@ -413,7 +413,7 @@ static int fi_awq_gemm_impl(const void* X, const void* qw, const void* scales, c
   p.n_rows_total = w_rows;
   p.tile_expert = nullptr; p.tile_row0 = nullptr; p.tile_rows = nullptr; p.n_tiles = nullptr; p.expert_rows = 0; p.grid_tiles = 0;
   p.comm_mode = 0; p.world = 1; p.rank = 0; p.rows_per_rank = 0; p.xfer_16bit = 0; p.trace = nullptr;
-  p.rms_eps = 0.f; p.row_ss = nullptr; p.w_dynamic = 0;
+  p.rms_eps = 0.f; p.w_dynamic = 0;
   p.ag_world = 1; p.ag_rows_per_rank = 0; p.slab_elems = 0; p.epoch = nullptr; p.done = nullptr;
   for (int d = 0; d < kMaxRanks; ++d) { p.recv[d] = 0; p.flags[d] = 0; p.ready[d] = 0; }
   if (comm != nullptr) {

@@ -26,8 +26,7 @@ namespace {
 template <int BN, int STAGES, bool DUAL>
 __global__ void __launch_bounds__(kThreads)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
-                  const __grid_constant__ TokenMaps tmaps_x, const GemmParams p_in) {
-  GemmParams p = p_in;
+                  const __grid_constant__ TokenMaps tmaps_x, const GemmParams p) {
   constexpr int A_BYTES = BM * 128;
   constexpr int B_BYTES = BN * 128;
   constexpr int STAGE_BYTES = A_BYTES * (DUAL ? 2 : 1) + B_BYTES;
@@ -45,7 +44,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   uint64_t* accum_bar = empty_bar + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
   volatile int* aborted = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  p.row_ss = reinterpret_cast<float*>(tmem_slot + 2);   // [BN] floats after the control words
+  float* row_ss = reinterpret_cast<float*>(tmem_slot + 2);   // [BN] floats after the control words: sum of squares per token
   const bool rms = p.rms_eps > 0.f;
   // fp32 staging of the accumulator tile(s); aliases the pipeline ring once the main loop is done.
   float* stage_f32 = reinterpret_cast<float*>(smem);
@@ -216,14 +215,14 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       v += __shfl_xor_sync(0xffffffffu, v, 2);
       v += __shfl_xor_sync(0xffffffffu, v, 4);
       const int c = tid + i * 128;
-      if ((c & 7) == 0 && c < kChunks) p.row_ss[c >> 3] = v;
+      if ((c & 7) == 0 && c < kChunks) row_ss[c >> 3] = v;
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");   // the four warps: row_ss complete before it is used
   }
   // ---------------------------------------------------------------- epilogue (epilogue.cuh)
-  if (warp >= 2) epilogue_tmem_to_smem<BN, DUAL>(p, accum_bar, tmem_base, stage_f32, aborted, warp, lane);
+  if (warp >= 2) epilogue_tmem_to_smem<BN, DUAL>(p, accum_bar, tmem_base, stage_f32, aborted, warp, lane, row_ss);
   __syncthreads();
-  epilogue_reduce_store<BN, DUAL>(p, stage_f32, aborted, n0, t0, epoch_now, p.T);
+  epilogue_reduce_store<BN, DUAL>(p, stage_f32, aborted, n0, t0, epoch_now, p.T, row_ss);
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
@@ -369,7 +368,7 @@ static int fi_dense_gemm_impl(const void* X, const void* W, void* C, const void*
   p.splits = splits; p.status = status;
   p.tile_expert = nullptr; p.tile_row0 = nullptr; p.tile_rows = nullptr; p.n_tiles = nullptr; p.expert_rows = 0; p.grid_tiles = 0;
   p.comm_mode = 0; p.world = 1; p.rank = 0; p.rows_per_rank = 0; p.xfer_16bit = 0; p.trace = nullptr;
-  p.rms_eps = rms_eps; p.row_ss = nullptr; p.w_dynamic = w_dynamic;
+  p.rms_eps = rms_eps; p.w_dynamic = w_dynamic;
   p.ag_world = 1; p.ag_rows_per_rank = 0; p.slab_elems = 0; p.epoch = nullptr; p.done = nullptr;
   for (int d = 0; d < kMaxRanks; ++d) { p.recv[d] = 0; p.flags[d] = 0; p.ready[d] = 0; }
   if (comm != nullptr) {

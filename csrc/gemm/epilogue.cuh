@@ -49,7 +49,6 @@ struct GemmParams {
   // shared memory while the main loop runs
   float rms_eps;
   int w_dynamic;         // 1: the weight operand was written by the preceding kernel (no prefetch before the PDL wait)
-  float* row_ss;         // shared-memory array [BN]: sum of squares of this CTA's K range per token
   // int4 weight-only extras (unused by the dense kernel)
   const void* scales;   // [K/G, rows]
   const uint8_t* zeros; // [K/G, rows] or null
@@ -188,7 +187,8 @@ __device__ __forceinline__ void finalize_store8(const GemmParams& p, float* g, i
 template <int BN, bool DUAL>
 __device__ __forceinline__ void epilogue_tmem_to_smem(const GemmParams& p, uint64_t* accum_bar,
                                                       uint32_t tmem_base, float* stage_f32,
-                                                      volatile int* aborted, int warp, int lane) {
+                                                      volatile int* aborted, int warp, int lane,
+                                                      const float* row_ss = nullptr) {
   bool ok = mbar_wait(accum_bar, 0);
   if (!ok) {
     set_status(p.status, kStatusTimeoutAccum);
@@ -210,7 +210,7 @@ __device__ __forceinline__ void epilogue_tmem_to_smem(const GemmParams& p, uint6
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 16; ++j)
-          r[j] = __float_as_uint(__uint_as_float(r[j]) * rsqrtf(p.row_ss[c0 + j] * inv_k + p.rms_eps));
+          r[j] = __float_as_uint(__uint_as_float(r[j]) * rsqrtf(row_ss[c0 + j] * inv_k + p.rms_eps));
       }
       if (DUAL) {
         uint32_t u[16];
@@ -219,7 +219,7 @@ __device__ __forceinline__ void epilogue_tmem_to_smem(const GemmParams& p, uint6
         if (norm_now) {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
-            u[j] = __float_as_uint(__uint_as_float(u[j]) * rsqrtf(p.row_ss[c0 + j] * inv_k + p.rms_eps));
+            u[j] = __float_as_uint(__uint_as_float(u[j]) * rsqrtf(row_ss[c0 + j] * inv_k + p.rms_eps));
         }
         if (fuse_act_now) {
 #pragma unroll
@@ -248,7 +248,8 @@ __device__ __forceinline__ void epilogue_tmem_to_smem(const GemmParams& p, uint6
 template <int BN, bool DUAL>
 __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float* stage_f32,
                                                       volatile int* aborted, int n0, int t0,
-                                                      unsigned int epoch_now, int t_end) {
+                                                      unsigned int epoch_now, int t_end,
+                                                      float* row_ss = nullptr) {
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   const int S = p.splits;
@@ -286,7 +287,7 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
       }
       if (p.rms_eps > 0.f && S > 1) {
         float ss = 0.f;
-        for (int pr = 0; pr < S; ++pr) ss += cluster.map_shared_rank(p.row_ss, pr)[tl];
+        for (int pr = 0; pr < S; ++pr) ss += cluster.map_shared_rank(row_ss, pr)[tl];
         const float rstd = rsqrtf(ss / static_cast<float>(p.K) + p.rms_eps);
 #pragma unroll
         for (int j = 0; j < 8; ++j) { g[j] *= rstd; u[j] *= rstd; }

@@ -109,15 +109,13 @@ class DecodePipeline:
         hm[3, n:] = 0
         d = self.dec
         d["meta"].copy_(self.buf["h_meta"][ring], non_blocking=True)
-        if not self._first:
-            d["ids"].copy_(self.buf["next_ids"], non_blocking=True)
         self._first = False
         self.kv.flush()
-        torch.index_select(self.kv.block_tables, 0, d["meta"][3].long(), out=d["block_tables"])
-        logits = self.ex.replay_or_capture(self.bucket, self.reqs, int(pos.max()) + 1)
-        ops.argmax(logits, out=self.buf["next_ids"])
+        # the captured step gathers the block tables, runs the model and leaves the greedy tokens in
+        # d["ids"], which is also where the next step reads its input ids
+        self.ex.replay_or_capture(self.bucket, self.reqs, int(pos.max()) + 1)
         if read_back:
-            self.buf["h_tok"][ring].copy_(self.buf["next_ids"], non_blocking=True)
+            self.buf["h_tok"][ring].copy_(d["ids"], non_blocking=True)
             ev = torch.cuda.Event()
             ev.record()
             self.inflight.append((ev, ring, n))
@@ -137,7 +135,7 @@ class DecodePipeline:
         ev, ring, n = self.inflight.pop(0)
         if ev is None:
             torch.cuda.current_stream().synchronize()
-            self.buf["h_tok"][ring].copy_(self.buf["next_ids"])
+            self.buf["h_tok"][ring].copy_(self.dec["ids"])
         else:
             ev.synchronize()
         return self.buf["h_tok"][ring][:n].tolist()

@@ -71,6 +71,18 @@ class DecodeExecutor:
     def _run(self, batch: ForwardBatch) -> torch.Tensor:
         return self.model(batch, self.kv_cache)
 
+    def _step_body(self, batch: ForwardBatch) -> torch.Tensor:
+        """What one captured decode step consists of: gather the block-table rows of the batch's
+        slots, run the model, and leave the greedy token of every row in the input-id buffer (the
+        next pipelined step reads its ids from there; other callers overwrite the buffer anyway).
+        Keeping all three inside the graph leaves one host-to-device and one device-to-host copy
+        per step outside it."""
+        d = self.builder._decode_buffers(batch.num_seqs)
+        torch.index_select(self.builder.kv.block_tables, 0, d["meta"][3].long(), out=d["block_tables"])
+        logits = self._run(batch)
+        ops.argmax(logits, out=d["ids"])
+        return logits
+
     @torch.inference_mode()
     def execute_batch(self, reqs: list[RequestState], states: dict[str, RequestState] | None = None,
                       device_tokens: torch.Tensor | None = None, lora_mapping=None) -> LogitsResult:
@@ -110,15 +122,17 @@ class DecodeExecutor:
         # warm up outside capture (lazy allocations, scratch growth, kernel attribute setup)
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
+        ids_saved = batch.input_ids.clone()
         with torch.cuda.stream(side):
             for _ in range(2):
-                self._run(batch)
+                self._step_body(batch)
+                batch.input_ids.copy_(ids_saved)      # the body leaves the greedy tokens in the id buffer
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         n0 = ops.launch_count()
         with torch.cuda.graph(graph, pool=self._pool):
-            out = self._run(batch)
+            out = self._step_body(batch)
         self.launches_per_graph[batch.num_seqs] = ops.launch_count() - n0
         if self._pool is None:
             self._pool = graph.pool()
@@ -138,7 +152,7 @@ class DecodeExecutor:
             request_ids=[st.request_id for st in reqs], extras={"num_real": len(reqs), "bucket": bucket})
         if not self.use_cuda_graph:
             self.eager_steps += 1
-            return self._run(batch)
+            return self._step_body(batch)
         entry = self._graphs.get(bucket)
         if entry is None:
             entry = self._capture(batch)

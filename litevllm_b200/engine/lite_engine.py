@@ -87,6 +87,12 @@ class LiteEngine:
         logger.info("memory: %s", self.memory.report())
         from .model_surface import resolve_model_surface
         self.observer.on_model_surface(resolve_model_surface(self.model_config.model, self.arch))
+        # Everything built so far (weights' Python wrappers, tokenizer tables, configs) lives as long as the
+        # engine: park it in the permanent generation so the collector's full passes, which would
+        # otherwise stall a decode step for tens of milliseconds now and then, have little to scan.
+        import gc
+        gc.collect()
+        gc.freeze()
         logger.info("engine ready: %d slots x %d tokens, %d KV blocks (%s, %.2f GiB), chunk %d",
                     self.plan.max_active_requests, self.plan.max_model_len, self.plan.num_total_blocks,
                     self.kv_plan.dtype, self.kv_cache.total_bytes / 2 ** 30, self.plan.prefill_chunk_size)

@@ -132,7 +132,8 @@ class LlamaDecoderLayer(nn.Module):
         self.fused_norm = True
 
     def forward(self, h, batch, kv, cos_sin):
-        if self.fused_norm and h.is_cuda and batch.lora_mapping is None:
+        # decode-sized batches: norms inside the GEMMs; prefill tiles are compute-bound and keep the norm kernel
+        if self.fused_norm and h.is_cuda and batch.lora_mapping is None and h.shape[0] <= 64:
             h = self.self_attn(h, h, batch, kv, cos_sin, norm_eps=self.input_layernorm.eps)
             return self.mlp(h, h, batch, norm_eps=self.post_attention_layernorm.eps)
         lora = batch.lora_mapping is not None and self.fused_norm

@@ -344,7 +344,11 @@ def slot_mapping(positions, token_seq, block_tables, block_size, out=None):
 
 def argmax(logits, out=None):
     if not logits.is_cuda:
-        return reference.argmax(logits)
+        r = reference.argmax(logits)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
     rows, V = logits.shape
     if out is None:
         out = torch.empty(rows, dtype=torch.int64, device=logits.device)
