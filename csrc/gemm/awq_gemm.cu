@@ -94,7 +94,7 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     pdl_wait();   // the table was written by the preceding kernel
     if (static_cast<int>(blockIdx.y) >= *p.n_tiles) return;   // uniform for the whole cluster
   }
-  const int t0 = grouped ? p.tile_row0[blockIdx.y] : static_cast<int>(blockIdx.y) * BN;
+  const int t0 = grouped ? p.tile_row0[blockIdx.y] : token_tile_index<BN>(p, blockIdx.y) * BN;
   const int t_end = grouped ? t0 + p.tile_rows[blockIdx.y] : p.T;
   const int w_row0 = grouped ? p.tile_expert[blockIdx.y] * p.expert_rows : 0;   // first weight row of the expert
   const int S = p.splits;
@@ -414,6 +414,7 @@ static int fi_awq_gemm_impl(const void* X, const void* qw, const void* scales, c
   p.tile_expert = nullptr; p.tile_row0 = nullptr; p.tile_rows = nullptr; p.n_tiles = nullptr; p.expert_rows = 0; p.grid_tiles = 0;
   p.comm_mode = 0; p.world = 1; p.rank = 0; p.rows_per_rank = 0; p.xfer_16bit = 0; p.trace = nullptr;
   p.rms_eps = 0.f; p.w_dynamic = 0;
+  p.x_full = nullptr; p.ag_flags = nullptr; p.copy_rows = 0;
   p.ag_world = 1; p.ag_rows_per_rank = 0; p.slab_elems = 0; p.epoch = nullptr; p.done = nullptr;
   for (int d = 0; d < kMaxRanks; ++d) { p.recv[d] = 0; p.flags[d] = 0; p.ready[d] = 0; }
   if (comm != nullptr) {

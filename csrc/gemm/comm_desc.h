@@ -19,6 +19,9 @@ struct FiComm {
   unsigned long long epoch;       // local device word: completed fused calls
   unsigned long long done;        // local device word: finished CTAs of the running call
   unsigned long long trace;       // optional device array [64][8] of phase timestamps (0 = off), see trace_mark()
+  unsigned long long x_full;      // all-gather mode: local staging buffer [T, K] that remote shards are copied into
+                                  // once (0 = every CTA reads its token tiles from the owner's memory)
+  unsigned long long ag_flags;    // local words [token tile][part]: staged copy of that part is complete
 };
 
 // Grouped (mixture-of-experts) launch: activations are sorted by expert, a device-side tile table

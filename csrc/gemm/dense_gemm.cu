@@ -52,7 +52,11 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BM;
-  const int t0 = blockIdx.y * BN;
+  if (p.copy_rows > 0 && static_cast<int>(blockIdx.y) < p.copy_rows) {   // staged all-gather: copier CTA
+    ag_copier<BN>(p);
+    return;
+  }
+  const int t0 = token_tile_index<BN>(p, static_cast<int>(blockIdx.y) - p.copy_rows) * BN;
   const int S = p.splits;
   const int rank = (S > 1) ? static_cast<int>(blockIdx.z) : 0;
 
@@ -104,7 +108,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
         if (DUAL) tma_load_2d(a + A_BYTES, &tmap_w, &full_bar[it], (kb_begin + it) * BK, p.dual_rows + n0);
       }
       pdl_wait();
-      if (!ag_handshake(p, x_map, epoch_now)) {
+      if (!ag_handshake(p, x_map, epoch_now) ||
+          (x_map == kStagedMap && !ag_wait_staged<BN>(p, t0, epoch_now))) {
         set_status(p.status, kStatusTimeoutPeer);
         *aborted = 1;
       }
@@ -293,7 +298,11 @@ int launch(const CUtensorMap& tw, const TokenMaps& tx, GemmParams p, cudaStream_
   }
   if (p.splits <= 0) p.splits = pick_splits<BN, STAGES, DUAL>(p, smem);
   if (BN * BM * 4 * ((DUAL && p.splits > 1) ? 2 : 1) > ring) return -12;
-  return static_cast<int>(launch_kernel(kern, dim3((p.N + BM - 1) / BM, (p.T + BN - 1) / BN, p.splits),
+  const int nx = (p.N + BM - 1) / BM;
+  if (p.x_full != nullptr) {   // staged all-gather: about 32 copier CTAs in the first rows of the grid
+    p.copy_rows = (32 + nx * p.splits - 1) / (nx * p.splits);
+  }
+  return static_cast<int>(launch_kernel(kern, dim3(nx, (p.T + BN - 1) / BN + p.copy_rows, p.splits),
                                         dim3(kThreads), smem, stream, p.splits, tw, tx, p));
 }
 
@@ -350,6 +359,11 @@ static int fi_dense_gemm_impl(const void* X, const void* W, void* C, const void*
                                    rows > 0 ? rows : 1, K, ldx, bn);
       if (r != 0) return r * 100 - 2;
     }
+    if (comm->x_full != 0) {
+      if (T != comm->ag_world * comm->ag_rows_per_rank || ldx != K || (bn % 8) != 0) return -22;
+      r = make_tmap_2d_16bit_sw128(&tx.m[kStagedMap], reinterpret_cast<const void*>(comm->x_full), T, K, K, bn);
+      if (r != 0) return r * 100 - 3;
+    }
   } else {
     r = make_tmap_2d_16bit_sw128(&tx.m[0], X, T, K, ldx, bn);
     if (r != 0) return r * 100 - 2;
@@ -369,6 +383,8 @@ static int fi_dense_gemm_impl(const void* X, const void* W, void* C, const void*
   p.tile_expert = nullptr; p.tile_row0 = nullptr; p.tile_rows = nullptr; p.n_tiles = nullptr; p.expert_rows = 0; p.grid_tiles = 0;
   p.comm_mode = 0; p.world = 1; p.rank = 0; p.rows_per_rank = 0; p.xfer_16bit = 0; p.trace = nullptr;
   p.rms_eps = rms_eps; p.w_dynamic = w_dynamic;
+  p.x_full = nullptr; p.ag_flags = nullptr; p.copy_rows = 0;
+  for (int d = 0; d < kMaxRanks; ++d) p.x_peers[d] = 0;
   p.ag_world = 1; p.ag_rows_per_rank = 0; p.slab_elems = 0; p.epoch = nullptr; p.done = nullptr;
   for (int d = 0; d < kMaxRanks; ++d) { p.recv[d] = 0; p.flags[d] = 0; p.ready[d] = 0; }
   if (comm != nullptr) {
@@ -381,6 +397,11 @@ static int fi_dense_gemm_impl(const void* X, const void* W, void* C, const void*
     p.epoch = reinterpret_cast<unsigned int*>(comm->epoch);
     p.done = reinterpret_cast<unsigned int*>(comm->done);
     p.trace = reinterpret_cast<unsigned long long*>(comm->trace);
+    if (comm->ag_world > 1 && comm->x_full != 0) {
+      p.x_full = reinterpret_cast<void*>(comm->x_full);
+      p.ag_flags = reinterpret_cast<unsigned int*>(comm->ag_flags);
+      for (int d = 0; d < kMaxRanks; ++d) p.x_peers[d] = comm->x_peers[d];
+    }
     for (int d = 0; d < kMaxRanks; ++d) { p.recv[d] = comm->recv[d]; p.flags[d] = comm->flags[d]; p.ready[d] = comm->ready[d]; }
     if (comm->mode == kCommReduceScatter && (comm->rows_per_rank % bn) != 0) return -17;
     const long tiles = static_cast<long>((N + BM - 1) / BM) * ((T + bn - 1) / bn);

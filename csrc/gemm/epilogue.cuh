@@ -68,6 +68,12 @@ struct GemmParams {
   unsigned int* epoch;   // local: completed fused calls
   unsigned long long* trace;   // optional phase timestamps of CTA (0,0,0): [epoch % 64][8]
   unsigned int* done;    // local: CTAs of the current call that have finished
+  // staged all-gather: the first copy_rows rows of the grid (blockIdx.y) are copier CTAs that pull
+  // the peers' token shards into x_full once; GEMM CTAs read remote tiles from there
+  unsigned long long x_peers[kMaxRanks];   // token shard of rank d as mapped here
+  void* x_full;
+  unsigned int* ag_flags;
+  int copy_rows;
   // grouped (mixture-of-experts) mode: blockIdx.y indexes a tile table built on the device
   const int* tile_expert;   // expert of each token tile (null = plain GEMM)
   const int* tile_row0;     // first row of the tile in the expert-sorted activation matrix
@@ -77,8 +83,10 @@ struct GemmParams {
   int grid_tiles;           // grid size along y in grouped mode (0 = derive from T)
 };
 
+constexpr int kStagedMap = kMaxRanks;   // TokenMaps slot of the locally staged, gathered token matrix
+constexpr int kAgParts = 8;             // copy units (and flags) per staged token tile
 struct TokenMaps {
-  CUtensorMap m[kMaxRanks];
+  CUtensorMap m[kMaxRanks + 1];
 };
 
 __device__ __forceinline__ float apply_act(float g, int act) {
@@ -333,7 +341,7 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
   }
   trace_mark(p.trace, epoch_now, 2);
   if (comm) {
-    const unsigned int tile = blockIdx.y * gridDim.x + blockIdx.x;
+    const unsigned int tile = static_cast<unsigned int>(t0 / BN) * gridDim.x + blockIdx.x;
     const bool inline_flags = p.xfer_16bit == kXferInlineFlags;
     if (!inline_flags) __threadfence_system();
     __syncthreads();
@@ -437,11 +445,33 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
   trace_mark(p.trace, epoch_now, 5);
 }
 
+// Order in which the token tiles of a fused collective are worked on (blockIdx.y -> tile index).
+// Reduce-scatter: every rank starts with the tiles owned by the NEXT rank and ends with its own, so
+// the partials a rank has to wait for were produced first everywhere and have crossed NVLink by the
+// time it reaches its own tiles.  All-gather: own shard first, the peers' shards (which have to be
+// fetched) afterwards.  Only when the token count is exactly world * rows_per_rank.
+template <int BN>
+__device__ __forceinline__ int token_tile_index(const GemmParams& p, int y) {
+  if (p.comm_mode == kCommReduceScatter && p.rows_per_rank % BN == 0 && p.T == p.world * p.rows_per_rank) {
+    const int per = p.rows_per_rank / BN;
+    return (y + (p.rank + 1) * per) % (p.world * per);
+  }
+  if (p.ag_world > 1 && p.ag_rows_per_rank % BN == 0 && p.T == p.ag_world * p.ag_rows_per_rank) {
+    const int per = p.ag_rows_per_rank / BN;
+    return (y + p.rank * per) % (p.ag_world * per);
+  }
+  return y;
+}
+
 // Source of the token tile starting at token t0: which tensor map and which row inside it.
 __device__ __forceinline__ void token_tile_source(const GemmParams& p, int t0, int* map_idx, int* row) {
   if (p.ag_world > 1) {
     *map_idx = t0 / p.ag_rows_per_rank;
     *row = t0 - (*map_idx) * p.ag_rows_per_rank;
+    if (p.x_full != nullptr && *map_idx != p.rank) {   // remote shard: read the local staged copy
+      *map_idx = kStagedMap;
+      *row = t0;
+    }
   } else {
     *map_idx = 0;
     *row = t0;
@@ -451,8 +481,92 @@ __device__ __forceinline__ void token_tile_source(const GemmParams& p, int t0, i
 // All-gather handshake run by the TMA producer thread before its first remote load: CTA (0,0,0)
 // tells every peer that this rank's token shard of the current call is complete; every producer
 // waits (bounded) until the rank it reads from has said the same.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Staged all-gather, consumer side: wait until every part of the token tile at t0 has been copied.
+template <int BN>
+__device__ __forceinline__ bool ag_wait_staged(const GemmParams& p, int t0, unsigned int epoch_now) {
+  const unsigned int* f = p.ag_flags + static_cast<size_t>(t0 / BN) * kAgParts;
+  for (int i = 0; i < kAgParts; ++i) {
+    const long long w0 = clock64();
+    unsigned int v;
+    do {
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f + i) : "memory");
+      if (v == epoch_now) break;
+    } while (clock64() - w0 <= FI_WAIT_CYCLES);
+    if (v != epoch_now) return false;
+  }
+  fence_proxy_async_all();   // the copy was made with generic stores; the TMA engine reads it next
+  return true;
+}
+
+// Staged all-gather, copier side (whole CTA): announce this rank's shard, then copy the units
+// (token tile, part) assigned to this CTA from the owners' memory into x_full and flag them.
+// Units are ordered as the GEMM CTAs will need them (the next rank's shard first).
+template <int BN>
+__device__ __forceinline__ void ag_copier(const GemmParams& p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const unsigned int epoch_now = *p.epoch + 1u;
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = 0;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
+    __threadfence_system();
+    for (int d = 0; d < p.ag_world; ++d)
+      if (d != p.rank) st_release_sys(reinterpret_cast<unsigned int*>(p.ready[d]) + p.rank, epoch_now);
+  }
+  __syncthreads();
+  const int n_cta = gridDim.x * p.copy_rows * gridDim.z;
+  const int me = (blockIdx.z * p.copy_rows + blockIdx.y) * gridDim.x + blockIdx.x;
+  const int per = p.ag_rows_per_rank / BN;                 // token tiles per shard
+  const int n_units = (p.ag_world - 1) * per * kAgParts;
+  const int rows_part = BN / kAgParts;
+  const size_t row_bytes = static_cast<size_t>(p.K) * 2;
+  for (int u = me; u < n_units; u += n_cta) {
+    const int part = u % kAgParts;
+    const int tt = (u / kAgParts) % per;
+    const int src = (p.rank + 1 + u / (kAgParts * per)) % p.ag_world;
+    if (threadIdx.x == 0 &&
+        !wait_flag(reinterpret_cast<const unsigned int*>(p.ready[p.rank]) + src, epoch_now)) {
+      set_status(p.status, kStatusTimeoutPeer);
+      failed = 1;
+    }
+    __syncthreads();
+    if (failed) break;
+    const int row0 = tt * BN + part * rows_part;           // row inside the shard
+    const uint4* from = reinterpret_cast<const uint4*>(p.x_peers[src] + row0 * row_bytes);
+    uint4* to = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.x_full) +
+                                         (static_cast<size_t>(src) * p.ag_rows_per_rank + row0) * row_bytes);
+    const int n16 = static_cast<int>(rows_part * row_bytes / 16);
+    int i = threadIdx.x;
+    for (; i + 3 * kThreads < n16; i += 4 * kThreads) {     // four loads in flight per thread
+      const uint4 a = from[i], b = from[i + kThreads], c = from[i + 2 * kThreads], d = from[i + 3 * kThreads];
+      to[i] = a; to[i + kThreads] = b; to[i + 2 * kThreads] = c; to[i + 3 * kThreads] = d;
+    }
+    for (; i < n16; i += kThreads) to[i] = from[i];
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned int* f = p.ag_flags + (static_cast<size_t>(src) * per + tt) * kAgParts + part;
+      asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(f), "r"(epoch_now) : "memory");
+    }
+  }
+  // take part in the end-of-call bookkeeping like every other CTA of the grid
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int total = gridDim.x * gridDim.y * gridDim.z;
+    __threadfence();
+    if (atomicAdd(p.done, 1u) == total - 1) {
+      *p.done = 0;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned int*>(p.epoch) = epoch_now;
+    }
+  }
+}
+
 __device__ __forceinline__ bool ag_handshake(const GemmParams& p, int src, unsigned int epoch_now) {
   if (p.ag_world <= 1) return true;
+  if (p.x_full != nullptr) return true;   // staged mode: the copier CTAs talk to the peers
   if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
     __threadfence_system();
     for (int d = 0; d < p.ag_world; ++d) {

@@ -102,10 +102,16 @@ def gemm_reduce_scatter(x: torch.Tensor, w: torch.Tensor, residual_shard: torch.
 
 
 def allgather_gemm(x_shard: torch.Tensor, w: torch.Tensor, T_total: int, rows_per_rank: int,
-                   out: torch.Tensor | None = None, gated_act: str | None = None) -> torch.Tensor:
-    """``concat_over_ranks(x_shard) @ w.T`` without materialising the gathered activations: every
-    rank parks its shard in the symmetric token buffer and the GEMM's TMA producer reads each token
-    tile straight from the rank that owns it (plain, non-multicast TMA loads over NVLink)."""
+                   out: torch.Tensor | None = None, gated_act: str | None = None,
+                   staged: bool | None = None) -> torch.Tensor:
+    """``concat_over_ranks(x_shard) @ w.T`` in one kernel: every rank parks its shard in the
+    symmetric token buffer; a few copier CTAs at the front of the GEMM's grid pull the peers' shards
+    into a local staging matrix once (each remote byte crosses NVLink once) and flag every piece,
+    while the GEMM CTAs start with the local shard and pick up the staged tiles as they land
+    (``staged=True``, the default when the token count is ``world * rows_per_rank``).  With
+    ``staged=False`` every CTA's TMA producer reads its token tiles straight from the owner's
+    memory instead (plain, non-multicast TMA loads over NVLink): simpler, but a remote tile is
+    re-read once per weight tile."""
     st = pstate.get_state()
     heap = st.symm
     K = x_shard.shape[1]
@@ -117,8 +123,10 @@ def allgather_gemm(x_shard: torch.Tensor, w: torch.Tensor, T_total: int, rows_pe
     N = inter if gated_act else w.shape[0]
     if out is None:
         out = torch.empty(T_total, N, dtype=x_shard.dtype, device=x_shard.device)
+    if staged is None:
+        staged = T_total == st.world_size * rows_per_rank
     comm = heap.comm_desc(mode=0, T=T_total, N=N, xfer_16bit=False, ag_world=st.world_size,
-                          ag_rows_per_rank=rows_per_rank, x_parity=parity)
+                          ag_rows_per_rank=rows_per_rank, x_parity=parity, staged=staged)
     rc = _lib.kernels().fi_dense_gemm_comm(
         ops._p(buf), ops._p(w), ops._p(out), None, None, T_total, N, K, buf.stride(0), w.stride(0), out.stride(0),
         ops._ACT[gated_act] if gated_act else 0, inter, 0, ops._DT[x_shard.dtype], 0, 0,

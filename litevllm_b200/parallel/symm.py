@@ -22,6 +22,7 @@ import torch.distributed as dist
 MAX_RANKS = 8
 FLAG_PARTS = 8
 MAX_COMM_TILES = 8192
+AG_PARTS = 8
 
 
 class FiComm(ctypes.Structure):
@@ -30,7 +31,8 @@ class FiComm(ctypes.Structure):
                 ("ag_rows_per_rank", ctypes.c_int), ("reserved", ctypes.c_int), ("slab_elems", ctypes.c_long),
                 ("recv", ctypes.c_ulonglong * 8), ("flags", ctypes.c_ulonglong * 8),
                 ("ready", ctypes.c_ulonglong * 8), ("x_peers", ctypes.c_ulonglong * 8),
-                ("epoch", ctypes.c_ulonglong), ("done", ctypes.c_ulonglong), ("trace", ctypes.c_ulonglong)]
+                ("epoch", ctypes.c_ulonglong), ("done", ctypes.c_ulonglong), ("trace", ctypes.c_ulonglong),
+                ("x_full", ctypes.c_ulonglong), ("ag_flags", ctypes.c_ulonglong)]
 
 
 class _RawCudaBuffer:
@@ -60,7 +62,12 @@ class SymmetricHeap:
         # that no other transfer format ever writes there: 2 parities x world sources
         self.ll_elems = ll_elems
         self.off_ll = self.off_xbuf + 2 * self.xbuf_bytes
-        total = self.off_ll + 2 * world * ll_elems * 8
+        # all-gather staging: the gathered token matrix (world shards) and its per-(tile, part) flags
+        self.off_xfull = self.off_ll + 2 * world * ll_elems * 8
+        self.xfull_bytes = world * self.xbuf_bytes
+        self.off_agflags = self.off_xfull + self.xfull_bytes
+        self.agflag_bytes = MAX_COMM_TILES * AG_PARTS * 4
+        total = self.off_agflags + self.agflag_bytes
         self.total_bytes = total
         lib = self._lib = _lib.kernels()
         torch.cuda.set_device(device)
@@ -104,7 +111,7 @@ class SymmetricHeap:
         return T * N <= self.ll_elems
 
     def comm_desc(self, mode: int, T: int, N: int, xfer_16bit: bool | int, rows_per_rank: int = 0,
-                  ag_world: int = 1, ag_rows_per_rank: int = 0, x_parity: int = 0) -> FiComm:
+                  ag_world: int = 1, ag_rows_per_rank: int = 0, x_parity: int = 0, staged: bool = False) -> FiComm:
         c = FiComm()
         c.mode, c.world, c.rank = mode, self.world, self.rank
         c.rows_per_rank = rows_per_rank
@@ -121,6 +128,8 @@ class SymmetricHeap:
         c.epoch = self.peer_ptr[self.rank] + self.off_ctl
         c.done = self.peer_ptr[self.rank] + self.off_ctl + 64
         c.trace = self.trace_ptr
+        c.x_full = self.base + self.off_xfull if staged else 0
+        c.ag_flags = self.base + self.off_agflags
         return c
 
     def epoch_value(self) -> int:

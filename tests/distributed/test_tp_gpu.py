@@ -74,10 +74,23 @@ def _kernel_worker(rank, world, out_dir):
     gathered = [torch.empty_like(xs) for _ in range(world)]
     dist.all_gather(gathered, xs)
     want = torch.cat(gathered).float() @ w.float().t()
-    for rep in range(2):
-        got = fused_ops.allgather_gemm(xs, w, rpr * world, rpr)
+    for rep, staged in enumerate([True, True, False, True]):   # staged copy (default) and direct remote reads
+        got = fused_ops.allgather_gemm(xs, w, rpr * world, rpr, staged=staged)
         torch.cuda.synchronize()
-        report[f"ag_{rep}"] = list(close(got, want))
+        report[f"ag_{rep}_{'staged' if staged else 'direct'}"] = list(close(got, want))
+    # a larger, gated case: several token tiles per shard, split over the copier CTAs
+    rpr2, K2, I2 = 512, 1024, 768
+    g = torch.Generator(device=dev).manual_seed(310 + rank)
+    xs2 = (torch.randn(rpr2, K2, generator=g, device=dev) * 0.5).bfloat16()
+    w2 = (torch.randn(2 * I2, K2, generator=g3, device=dev) * 0.05).bfloat16()
+    gathered = [torch.empty_like(xs2) for _ in range(world)]
+    dist.all_gather(gathered, xs2)
+    hfull = torch.cat(gathered).float() @ w2.float().t()
+    want2 = torch.nn.functional.silu(hfull[:, :I2]) * hfull[:, I2:]
+    for rep in range(2):
+        got = fused_ops.allgather_gemm(xs2, w2, rpr2 * world, rpr2, gated_act="silu")
+        torch.cuda.synchronize()
+        report[f"ag_gated_{rep}"] = list(close(got, want2, 4e-2))
     ops.check_status(dev)
     report["epoch"] = st.symm.epoch_value()
     with open(os.path.join(out_dir, f"k{rank}.json"), "w") as f:
