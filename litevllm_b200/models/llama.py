@@ -166,6 +166,8 @@ class LlamaForCausalLM(nn.Module):
                                       prefix="lm_head")
         self.max_pos = max(mc.max_model_len, 16)
         self._cos_sin = None
+        # prefill batches of at least this many tokens run sequence-parallel under tensor parallelism
+        self.sp_min_tokens = int(os.environ.get("FI_SP_MIN_TOKENS", "2048"))
 
     # ------------------------------------------------------------------ runtime
     def cos_sin(self, device):
@@ -185,9 +187,74 @@ class LlamaForCausalLM(nn.Module):
     def forward(self, batch, kv_caches, inputs_embeds=None):
         h = inputs_embeds if inputs_embeds is not None else self.embed(batch.input_ids)
         cs = self.cos_sin(h.device)
+        if self._sequence_parallel_ok(h, batch):
+            return self._forward_sequence_parallel(h, batch, kv_caches, cs)
         for i, layer in enumerate(self.layers):
             h = layer(h, batch, kv_caches[i], cs)
         return self.compute_logits(h, batch)
+
+    # ------------------------------------------------------------------ sequence-parallel prefill
+    def _sequence_parallel_ok(self, h, batch) -> bool:
+        """Tensor-parallel prefill of a large batch on GPUs with the fused collectives: the residual
+        stream is then kept sharded by token rows between the attention and MLP blocks."""
+        if batch.is_decode or not h.is_cuda or batch.lora_mapping is not None:
+            return False
+        st = pstate.get_state()
+        if st.tp_size <= 1 or st.comm_backend != "fused" or st.symm is None:
+            return False
+        if h.shape[0] < self.sp_min_tokens:
+            return False
+        l0 = self.layers[0]
+        lin = (l0.self_attn.qkv_proj, l0.self_attn.o_proj, l0.mlp.gate_up_proj, l0.mlp.down_proj)
+        if any(m.quant_method is not None or m.bias is not None for m in lin):
+            return False
+        w = st.tp_size
+        rpr = (h.shape[0] + w * 128 - 1) // (w * 128) * 128
+        elem = h.element_size()
+        return rpr * h.shape[1] * elem <= st.symm.xbuf_bytes and st.symm.fits_recv(rpr, h.shape[1], elem)
+
+    def _forward_sequence_parallel(self, h_full, batch, kv_caches, cs):
+        """One prefill forward with the hidden states sharded by token rows over the TP ranks:
+
+            norm(shard) -> all-gather->GEMM (qkv, all tokens x local heads) -> rotary + cache + attention
+            -> GEMM->reduce-scatter (+ residual shard) -> norm(shard) -> all-gather->GEMM (gate|up, gated)
+            -> GEMM->reduce-scatter (+ residual shard)
+
+        so every collective of the layer is fused into the GEMM next to it and the norms, residual adds
+        and the staging copies touch 1/world of the tokens.  Tokens are padded to world x 128 rows."""
+        from ..parallel import fused_ops
+        st = pstate.get_state()
+        w, r = st.tp_size, st.tp_rank()
+        T, H = h_full.shape
+        rpr = (T + w * 128 - 1) // (w * 128) * 128
+        Tpad = rpr * w
+        dev, dt = h_full.device, h_full.dtype
+        h = torch.zeros(rpr, H, dtype=dt, device=dev)                 # this rank's rows of the residual stream
+        lo, hi = r * rpr, min((r + 1) * rpr, T)
+        if hi > lo:
+            h[: hi - lo].copy_(h_full[lo:hi])
+        l0 = self.layers[0].self_attn
+        attn = torch.zeros(Tpad, l0.nh * l0.hd, dtype=dt, device=dev)  # rows beyond T stay zero
+        cfg = batch.config
+        for i, layer in enumerate(self.layers):
+            at, mlp = layer.self_attn, layer.mlp
+            x = layer.input_layernorm(h)
+            qkv = fused_ops.allgather_gemm(x, at.qkv_proj.weight, Tpad, rpr)[:T]
+            k_cache, v_cache = kv_caches[i]
+            ops.rope_and_cache(qkv, batch.positions, cs, batch.slot_mapping, k_cache, v_cache, at.nh, at.nkv, at.hd,
+                               at.rot_dim, q_norm_w=at.q_norm.weight if at.qk_norm else None,
+                               k_norm_w=at.k_norm.weight if at.qk_norm else None,
+                               qk_norm_mode=(at.q_norm.w_mode if at.qk_norm else -1), eps=at.eps,
+                               k_scale=cfg.k_scale, v_scale=cfg.v_scale)
+            ops.paged_attention_prefill(qkv, k_cache, v_cache, batch.block_tables, batch.seq_lens, batch.cu_q,
+                                        batch.max_q_len, at.nh, at.nkv, at.hd, at.sm_scale, at.window, 0.0,
+                                        cfg.k_scale, cfg.v_scale, out=attn[:T])
+            fused_ops.gemm_reduce_scatter(attn, at.o_proj.weight, h, rpr, out_shard=h)
+            x = layer.post_attention_layernorm(h)
+            a = fused_ops.allgather_gemm(x, mlp.gate_up_proj.weight, Tpad, rpr, gated_act=mlp.gate_up_proj.gated_act)
+            fused_ops.gemm_reduce_scatter(a, mlp.down_proj.weight, h, rpr, out_shard=h)
+        full = pstate.all_gather_rows(h)[:T]
+        return self.compute_logits(full, batch)
 
     def compute_logits(self, h, batch):
         last = h if batch.logits_indices is None else h.index_select(0, batch.logits_indices)

@@ -1,0 +1,176 @@
+"""Serving surface, configuration contract, async runtime and LoRA on the CPU (no GPU, no network)."""
+import asyncio
+import json
+
+import pytest
+import torch
+
+from litevllm_b200 import LLM, SamplingParams
+
+
+# --------------------------------------------------------------------------- configuration contract
+def test_toml_config_validation_and_profiles(tmp_path):
+    from litevllm_b200.config.fastinference_config import config_from_mapping, load_fastinference_config
+    from litevllm_b200.config.runtime_profile import RuntimeProfileRegistry
+    cfg = config_from_mapping({"profile": "throughput", "kv_type": "fp8",
+                               "parallel": {"tensor_parallel_size": 2, "comm_backend": "nccl"},
+                               "tuning_keyvals": {"FASTINFERENCE_LITE_PREFILL_MICROBATCH": "4"}})
+    assert cfg.profile == "throughput" and cfg.parallel.tensor_parallel_size == 2 and cfg.parallel.comm_backend == "nccl"
+    for bad in ({"nonsense": 1}, {"profile": "warp-speed"}, {"tuning_keyvals": {"NOT_A_KEY": "1"}},
+                {"model": {"trust_remote_code": True}}, {"parallel": {"tensor_parallel_size": 0}}):
+        with pytest.raises(ValueError):
+            config_from_mapping(bad)
+    f = tmp_path / "fi.toml"
+    f.write_text('profile = "latency"\nkv_type = "fp16"\n[parallel]\nexpert_parallel_size = 4\n')
+    loaded = load_fastinference_config(f)
+    assert loaded.profile == "latency" and loaded.parallel.expert_parallel_size == 4
+    prof = RuntimeProfileRegistry.resolve("throughput", "auto")
+    assert prof.effective_name == "throughput" and prof.prefill_microbatch_size >= 8 and isinstance(prof.stats(), dict)
+
+
+def test_env_registry_scopes():
+    from litevllm_b200.config import env_registry as er
+    assert er.is_registered("FASTINFERENCE_CONFIG") and not er.is_registered("FASTINFERENCE_DOES_NOT_EXIST")
+    assert er.is_usable_tuning_key("FASTINFERENCE_LITE_PREFILL_MICROBATCH")
+    assert not er.is_usable_tuning_key("FASTINFERENCE_BENCH_POLICY_MODE")     # removed names are refused
+
+
+def test_adapter_policies():
+    from litevllm_b200.adapters.registry import get_model_adapter
+    from litevllm_b200.config.config_builder import build_vllm_config
+    vc = build_vllm_config("synthetic:tiny-gemma4-moe-test", dtype="float32", device="cpu")
+    pol = get_model_adapter(vc.model_config.arch).runtime_policy(vc.runtime_config)
+    assert pol.force_kv_cache_dtype == "fp8" and pol.model_policy["moe"] is True
+    vc = build_vllm_config("synthetic:tiny-llama-test", dtype="float32", device="cpu")
+    assert get_model_adapter(vc.model_config.arch).name == "llama"
+
+
+# --------------------------------------------------------------------------- engine on the CPU (oracle path)
+def test_cpu_engine_greedy_is_deterministic_and_batch_invariant():
+    llm = LLM("synthetic:tiny-llama-test", dtype="float32", device="cpu", max_num_seqs=4, max_model_len=192)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 512, (128,), generator=g).tolist() for _ in range(4)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    together = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    alone = [llm.generate([p], sp)[0].outputs[0].token_ids for p in prompts]
+    assert together == alone and all(len(t) == 8 for t in together)
+    st = llm.stats()
+    assert st["memory"]["weight_bytes"] > 0 and "plan" in st
+
+
+def test_request_validation_errors():
+    from litevllm_b200.engine.errors import InvalidRequestError
+    llm = LLM("synthetic:tiny-llama-test", dtype="float32", device="cpu", max_num_seqs=2, max_model_len=32)
+    with pytest.raises(InvalidRequestError):
+        llm.generate([[1] * 64], SamplingParams(max_tokens=4))            # longer than the context
+    with pytest.raises(InvalidRequestError):
+        llm.generate([[600]], SamplingParams(max_tokens=4))               # token id outside the vocabulary
+    with pytest.raises((InvalidRequestError, ValueError)):
+        llm.generate([[1, 2]], SamplingParams(max_tokens=4, n=2))
+
+
+# --------------------------------------------------------------------------- async runtime
+def test_async_llm_streams_and_aborts():
+    from litevllm_b200.config.config_builder import build_vllm_config
+    from litevllm_b200.engine.async_llm import AsyncLLM
+    from litevllm_b200.engine.errors import LiteRuntimeError
+
+    async def run():
+        eng = AsyncLLM(build_vllm_config("synthetic:tiny-llama-test", dtype="float32", device="cpu", max_num_seqs=2,
+                                         max_model_len=64))
+        try:
+            sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+            outs = [o async for o in eng.generate({"prompt_token_ids": [3, 4, 5]}, sp, "a")]
+            assert outs[-1].finished and len(outs[-1].outputs[0].token_ids) == 5
+            # duplicate ids are rejected, aborting twice is harmless
+            await eng.submit({"prompt_token_ids": [1, 2]}, SamplingParams(max_tokens=50, ignore_eos=True), "b")
+            with pytest.raises(LiteRuntimeError):
+                await eng.submit({"prompt_token_ids": [1, 2]}, sp, "b")
+            await eng.abort("b")
+            await eng.abort("b")
+            assert eng.is_healthy() and eng.stats()["scheduler"]["running"] == 0
+        finally:
+            eng.shutdown()
+
+    asyncio.run(run())
+
+
+# --------------------------------------------------------------------------- HTTP semantics
+def test_http_endpoints_without_and_with_engine():
+    from fastapi.testclient import TestClient
+    from litevllm_b200.entrypoints.openai import api_server as srv
+    client = TestClient(srv.app)
+    saved = (srv.engine, srv.served_model, srv.debug_endpoints_enabled)
+    try:
+        srv.engine = None
+        assert client.get("/healthz").status_code == 200
+        assert client.get("/readyz").status_code == 503 and client.get("/v1/models").status_code == 503
+        assert client.post("/v1/chat/completions", json={"model": "m", "messages": []}).status_code == 503
+        srv.engine = srv.build_engine("synthetic:tiny-llama-test", dtype="float32", device="cpu", max_num_seqs=2,
+                                      max_model_len=128)
+        srv.served_model, srv.debug_endpoints_enabled = "tiny", False
+        assert client.get("/readyz").status_code == 200
+        assert client.get("/v1/models").json()["data"][0]["id"] == "tiny"
+        assert client.get("/debug/runtime_stats").status_code == 404          # gated
+        body = {"model": "tiny", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "temperature": 0}
+        r = client.post("/v1/chat/completions", json=body)
+        assert r.status_code == 200 and r.json()["usage"]["completion_tokens"] == 4
+        assert client.post("/v1/chat/completions", json=dict(body, model="other")).status_code == 400
+        assert client.post("/v1/chat/completions", json=dict(body, n=2)).status_code == 400
+        assert client.post("/v1/chat/completions", content=b"[1,2]",
+                           headers={"content-type": "application/json"}).status_code == 400
+        with client.stream("POST", "/v1/chat/completions", json=dict(body, stream=True)) as s:
+            lines = [l for l in s.iter_lines() if l.startswith("data:")]
+        assert lines[-1] == "data: [DONE]" and json.loads(lines[0][5:])["choices"][0]["delta"] == {"role": "assistant"}
+        tok = client.post("/tokenize", json={"model": "tiny", "prompt": "abc"})
+        assert tok.status_code == 200 and tok.json()["count"] == len(tok.json()["tokens"])
+    finally:
+        if srv.engine is not None:
+            srv.engine.shutdown()
+        srv.engine, srv.served_model, srv.debug_endpoints_enabled = saved
+
+
+# --------------------------------------------------------------------------- LoRA
+def test_lora_adapter_changes_outputs_per_request(tmp_path):
+    from safetensors.torch import save_file
+    from litevllm_b200.engine.lora_runtime import LoRARequest
+    llm = LLM("synthetic:tiny-llama-test", dtype="float32", device="cpu", max_num_seqs=2, max_model_len=64)
+    arch = llm.engine.arch
+    H, r = arch.hidden_size, 4
+    g = torch.Generator().manual_seed(1)
+    qkv_out = (arch.num_heads + 2 * arch.num_kv_heads) * arch.head_dim
+    tensors = {}
+    for i in range(arch.num_layers):
+        pre = f"base_model.model.model.layers.{i}.self_attn.q_proj"
+        tensors[pre + ".lora_A.weight"] = torch.randn(r, H, generator=g) * 0.5
+        tensors[pre + ".lora_B.weight"] = torch.randn(arch.num_heads * arch.head_dim, r, generator=g) * 0.5
+    (tmp_path / "adapter_config.json").write_text(json.dumps({"r": r, "lora_alpha": 8, "target_modules": ["q_proj"]}))
+    save_file(tensors, str(tmp_path / "adapter_model.safetensors"))
+    llm.register_lora_adapter("a1", str(tmp_path))
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    prompt = [5, 9, 33, 7, 100, 42]
+    base = llm.generate([prompt], sp)[0].outputs[0].token_ids
+    lora = llm.generate([prompt], sp, lora_request=LoRARequest("a1", 1, str(tmp_path)))[0].outputs[0].token_ids
+    again = llm.generate([prompt], sp)[0].outputs[0].token_ids
+    assert base == again and lora != base
+    assert llm.unregister_lora_adapter("a1") and llm.stats()["lora"].get("registered", 0) in (0, [])
+
+
+# --------------------------------------------------------------------------- governance
+def test_sources_do_not_use_closed_calls_or_foreign_backends():
+    """Source-tree rules: no batched-memcpy runtime calls, no cluster-multicast TMA loads, no Triton or
+    torch.compile in the package."""
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    banned_cu = ["MemcpyBatchAsync", "Memcpy3DBatchAsync", ".multicast::cluster"]
+    for f in list((root / "csrc").rglob("*.cu*")) + list((root / "csrc").rglob("*.h")) + list((root / "csrc").rglob("*.cpp")):
+        text = f.read_text()
+        for b in banned_cu:
+            if b == ".multicast::cluster":
+                bad = [ln for ln in text.splitlines() if b in ln and "cp.async.bulk" in ln]
+                assert not bad, f"{f}: cluster-multicast bulk load"
+            else:
+                assert b not in text, f"{f}: {b}"
+    for f in (root / "litevllm_b200").rglob("*.py"):
+        text = f.read_text()
+        assert "import triton" not in text and "torch.compile(" not in text, f
