@@ -415,6 +415,8 @@ static int fi_awq_gemm_impl(const void* X, const void* qw, const void* scales, c
   p.comm_mode = 0; p.world = 1; p.rank = 0; p.rows_per_rank = 0; p.xfer_16bit = 0; p.trace = nullptr;
   p.rms_eps = 0.f; p.w_dynamic = 0;
   p.x_full = nullptr; p.ag_flags = nullptr; p.copy_rows = 0;
+  p.rope_cs = nullptr; p.rope_pos = nullptr; p.rope_slots = nullptr; p.k_cache = nullptr; p.v_cache = nullptr;
+  p.rope_nh = p.rope_nkv = p.rope_hd = p.rope_bs = 0;
   p.ag_world = 1; p.ag_rows_per_rank = 0; p.slab_elems = 0; p.epoch = nullptr; p.done = nullptr;
   for (int d = 0; d < kMaxRanks; ++d) { p.recv[d] = 0; p.flags[d] = 0; p.ready[d] = 0; }
   if (comm != nullptr) {

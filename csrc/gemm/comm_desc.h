@@ -24,6 +24,16 @@ struct FiComm {
   unsigned long long ag_flags;    // local words [token tile][part]: staged copy of that part is complete
 };
 
+// Rotary embedding + KV-cache write fused into the epilogue of a merged q|k|v projection.
+struct FiRope {
+  const float* cos_sin;      // fp32 [max_pos, head_dim] = [cos(head_dim/2) | sin(head_dim/2)]
+  const int* positions;      // [T]
+  const int* slot_mapping;   // [T] flat cache slot, < 0 = skip
+  void* k_cache;             // [blocks, num_kv_heads, block_size, head_dim], same 16-bit type as the output
+  void* v_cache;
+  int num_heads, num_kv_heads, head_dim, block_size;
+};
+
 // Grouped (mixture-of-experts) launch: activations are sorted by expert, a device-side tile table
 // (built by fi_moe_align) tells each CTA its expert and rows; weights of all experts are stacked.
 struct FiGrouped {

@@ -339,7 +339,8 @@ static int fi_dense_gemm_impl(const void* X, const void* W, void* C, const void*
                              const void* residual, int T, int N, int K, int ldx, int ldw, int ldc,
                              int act, int dual_rows, int out_fp32, int dtype, int splits, int bn,
                              int* status, void* stream,
-                             const FiComm* comm, float rms_eps = 0.f, int w_dynamic = 0) {
+                             const FiComm* comm, float rms_eps = 0.f, int w_dynamic = 0,
+                             const FiRope* rope = nullptr) {
   if (T <= 0 || N <= 0 || K <= 0) return 0;
   if (rms_eps > 0.f && (K % BK) != 0) return -21;   // the sum of squares reads whole 64-wide K blocks
   if ((K % 8) != 0 || (ldc % 8) != 0 || (reinterpret_cast<uintptr_t>(C) & 15) != 0) return -10;
@@ -385,6 +386,17 @@ static int fi_dense_gemm_impl(const void* X, const void* W, void* C, const void*
   p.rms_eps = rms_eps; p.w_dynamic = w_dynamic;
   p.x_full = nullptr; p.ag_flags = nullptr; p.copy_rows = 0;
   for (int d = 0; d < kMaxRanks; ++d) p.x_peers[d] = 0;
+  p.rope_cs = nullptr; p.rope_pos = nullptr; p.rope_slots = nullptr; p.k_cache = nullptr; p.v_cache = nullptr;
+  p.rope_nh = p.rope_nkv = p.rope_hd = p.rope_bs = 0;
+  if (rope != nullptr) {
+    const int hd = rope->head_dim;
+    if ((hd != 64 && hd != 128) || N != (rope->num_heads + 2 * rope->num_kv_heads) * hd || dual_rows > 0 ||
+        out_fp32 || residual != nullptr || comm != nullptr || act != 0 || rope->block_size <= 0)
+      return -23;
+    p.rope_cs = rope->cos_sin; p.rope_pos = rope->positions; p.rope_slots = rope->slot_mapping;
+    p.k_cache = rope->k_cache; p.v_cache = rope->v_cache;
+    p.rope_nh = rope->num_heads; p.rope_nkv = rope->num_kv_heads; p.rope_hd = hd; p.rope_bs = rope->block_size;
+  }
   p.ag_world = 1; p.ag_rows_per_rank = 0; p.slab_elems = 0; p.epoch = nullptr; p.done = nullptr;
   for (int d = 0; d < kMaxRanks; ++d) { p.recv[d] = 0; p.flags[d] = 0; p.ready[d] = 0; }
   if (comm != nullptr) {
@@ -429,6 +441,17 @@ extern "C" int fi_dense_gemm_rmsnorm(const void* X, const void* W, void* C, cons
                              float eps, int* status, void* stream) {
   if (!(eps > 0.f)) return -20;
   return fi_dense_gemm_impl(X, W, C, bias, residual, T, N, K, ldx, ldw, ldc, act, dual_rows, out_fp32, dtype, splits, bn, status, stream, nullptr, eps);
+}
+
+// Merged q|k|v projection with the rotary embedding and the KV-cache write in the epilogue (and,
+// with eps > 0, the RMSNorm of the input rows in front): replaces GEMM + rotary/cache kernel for
+// models with full-width rotary embedding, head_dim 64 or 128, no q/k norm and a 16-bit cache.
+extern "C" int fi_dense_gemm_rope(const void* X, const void* W, void* C, const void* bias, int T, int N, int K,
+                             int ldx, int ldw, int ldc, int dtype, int splits, int bn, float rms_eps,
+                             const FiRope* rope, int* status, void* stream) {
+  if (rope == nullptr) return -23;
+  return fi_dense_gemm_impl(X, W, C, bias, nullptr, T, N, K, ldx, ldw, ldc, 0, 0, 0, dtype, splits, bn, status,
+                            stream, nullptr, rms_eps, 0, rope);
 }
 
 // Same as fi_dense_gemm for a weight matrix that the preceding kernel on the stream produced (for

@@ -68,6 +68,15 @@ struct GemmParams {
   unsigned int* epoch;   // local: completed fused calls
   unsigned long long* trace;   // optional phase timestamps of CTA (0,0,0): [epoch % 64][8]
   unsigned int* done;    // local: CTAs of the current call that have finished
+  // rotary embedding + KV-cache write fused behind a merged q|k|v projection (rope_cs != nullptr):
+  // the epilogue rotates q and k (pairs d, d + hd/2, full-width rotary), stores q|k|v into C and the
+  // new k and v rows into the paged cache [blocks, nkv, block_size, hd] (same 16-bit type as C)
+  const float* rope_cs;    // [max_pos, hd] = [cos(hd/2) | sin(hd/2)]
+  const int* rope_pos;     // [T]
+  const int* rope_slots;   // [T] flat cache slot (block * block_size + offset), < 0 = do not cache
+  void* k_cache;
+  void* v_cache;
+  int rope_nh, rope_nkv, rope_hd, rope_bs;
   // staged all-gather: the first copy_rows rows of the grid (blockIdx.y) are copier CTAs that pull
   // the peers' token shards into x_full once; GEMM CTAs read remote tiles from there
   unsigned long long x_peers[kMaxRanks];   // token shard of rank d as mapped here
@@ -308,7 +317,16 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
         for (int j = 0; j < 8; ++j) g[j] = apply_act(g[j], p.act);
       }
       if (!comm) {
-        finalize_store8(p, g, t, n);
+        if (p.rope_cs != nullptr) {   // park the finished values (with bias); the rotary pass below pairs them up
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) g[j] += ld16_as_float(p.bias, n + j, p.is_fp16);
+          }
+          *reinterpret_cast<float4*>(stage_f32 + tl * BM + nl) = make_float4(g[0], g[1], g[2], g[3]);
+          *reinterpret_cast<float4*>(stage_f32 + tl * BM + nl + 4) = make_float4(g[4], g[5], g[6], g[7]);
+        } else {
+          finalize_store8(p, g, t, n);
+        }
         continue;
       }
       // ---- fused collective, phase A: keep my partial in my own staging rows, push it to peers
@@ -335,6 +353,49 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
           float* dst = reinterpret_cast<float*>(p.recv[d]) + off;
           *reinterpret_cast<float4*>(dst) = make_float4(g[0], g[1], g[2], g[3]);
           *reinterpret_cast<float4*>(dst + 4) = make_float4(g[4], g[5], g[6], g[7]);
+        }
+      }
+    }
+  }
+  if (p.rope_cs != nullptr && !comm) {
+    __syncthreads();
+    if (!*aborted) {
+      const int hd = p.rope_hd, half = hd >> 1;
+      const int q_end = p.rope_nh * hd, k_end = q_end + p.rope_nkv * hd;
+      for (int idx = threadIdx.x; idx < rows_mine * (BM / 8); idx += kThreads) {
+        const int tl = rank + (idx / (BM / 8)) * S;
+        const int nl = (idx % (BM / 8)) * 8;
+        const int t = t0 + tl;
+        const int n = n0 + nl;
+        if (t >= t_end || n >= p.N) continue;
+        const float* own = stage_f32 + tl * BM + nl;
+        float x[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = own[j];
+        const int sec = n < q_end ? 0 : (n < k_end ? 1 : 2);
+        if (sec != 2) {
+          const int d = n & (hd - 1);
+          const bool lower = d < half;
+          const float* other = lower ? own + half : own - half;
+          const float* cs = p.rope_cs + static_cast<size_t>(p.rope_pos[t]) * hd + (d & (half - 1));
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float c = cs[j], sn = cs[half + j];
+            x[j] = lower ? x[j] * c - other[j] * sn : x[j] * c + other[j] * sn;
+          }
+        }
+        uint32_t packed[4];
+        pack8(x, p.is_fp16, packed);
+        const uint4 v16 = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.C) + static_cast<size_t>(t) * p.ldc + n) = v16;
+        if (sec != 0) {
+          const int slot = p.rope_slots[t];
+          if (slot >= 0) {
+            const int blk = slot / p.rope_bs, off = slot - blk * p.rope_bs;
+            const int hn = n - (sec == 1 ? q_end : k_end);
+            const size_t addr = ((static_cast<size_t>(blk) * p.rope_nkv + hn / hd) * p.rope_bs + off) * hd + (hn & (hd - 1));
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(sec == 1 ? p.k_cache : p.v_cache) + addr) = v16;
+          }
         }
       }
     }

@@ -58,6 +58,8 @@ class LlamaAttention(nn.Module):
         self.o_proj = LiteLinear(q_rows, arch.hidden_size, bias=False, dtype=dtype, shard="row",
                                  quant_config=quant_config, prefix=prefix + ".o_proj")
         self.qk_norm = arch.qk_norm
+        import os
+        self.fuse_rope = os.environ.get("FI_FUSE_ROPE", "1") != "0"
         if self.qk_norm:
             self.q_norm = RMSNormWeight(self.hd, arch.rms_eps, dtype, arch.norm_plus_one)
             self.k_norm = RMSNormWeight(self.hd, arch.rms_eps, dtype, arch.norm_plus_one)
@@ -71,16 +73,27 @@ class LlamaAttention(nn.Module):
         head0 = (r // self.kv_replicas) * self.nkv
         return head0 * self.hd, self.nkv * self.hd
 
+    def _fused_rope_ok(self, x, batch, k_cache) -> bool:
+        """Decode-sized batches of plain Llama attention: rotary + cache write ride in the qkv GEMM."""
+        qp = self.qkv_proj
+        return (self.fuse_rope and batch.is_decode and batch.lora_mapping is None and qp.quant_method is None
+                and not self.qk_norm and batch.positions.dim() == 1
+                and ops.qkv_rope_cache_supported(x, qp.weight, k_cache, self.nh, self.nkv, self.hd, self.rot_dim))
+
     def forward(self, x, h, batch, kv, cos_sin, norm_eps: float = 0.0, lora_x=None):
-        qkv = self.qkv_proj(x, lora_mapping=batch.lora_mapping, norm_eps=norm_eps, lora_x=lora_x)
         k_cache, v_cache = kv
         cfg = batch.config
-        ops.rope_and_cache(qkv, batch.positions, cos_sin, batch.slot_mapping, k_cache, v_cache, self.nh,
-                           self.nkv, self.hd, self.rot_dim,
-                           q_norm_w=self.q_norm.weight if self.qk_norm else None,
-                           k_norm_w=self.k_norm.weight if self.qk_norm else None,
-                           qk_norm_mode=(self.q_norm.w_mode if self.qk_norm else -1), eps=self.eps,
-                           k_scale=cfg.k_scale, v_scale=cfg.v_scale)
+        if self._fused_rope_ok(x, batch, k_cache):
+            qkv = ops.linear_rope_cache(x, self.qkv_proj.weight, self.qkv_proj.bias, batch.positions, cos_sin,
+                                        batch.slot_mapping, k_cache, v_cache, self.nh, self.nkv, self.hd, norm_eps)
+        else:
+            qkv = self.qkv_proj(x, lora_mapping=batch.lora_mapping, norm_eps=norm_eps, lora_x=lora_x)
+            ops.rope_and_cache(qkv, batch.positions, cos_sin, batch.slot_mapping, k_cache, v_cache, self.nh,
+                               self.nkv, self.hd, self.rot_dim,
+                               q_norm_w=self.q_norm.weight if self.qk_norm else None,
+                               k_norm_w=self.k_norm.weight if self.qk_norm else None,
+                               qk_norm_mode=(self.q_norm.w_mode if self.qk_norm else -1), eps=self.eps,
+                               k_scale=cfg.k_scale, v_scale=cfg.v_scale)
         if batch.is_decode:
             attn = ops.paged_attention_decode(qkv, k_cache, v_cache, batch.block_tables, batch.seq_lens,
                                               self.nh, self.nkv, self.hd, self.sm_scale, self.window, 0.0,

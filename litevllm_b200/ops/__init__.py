@@ -8,6 +8,8 @@ from __future__ import annotations
 
 import math
 
+import ctypes
+
 import torch
 
 from . import _lib, reference
@@ -119,6 +121,39 @@ def linear(x, w, bias=None, residual=None, act=None, out=None, out_dtype=None, s
             out.stride(0), _ACT[act], 0, 1 if out.dtype == torch.float32 else 0, _DT[x.dtype], splits,
             bn, _p(status_word(x.device)), _stream())
     _lib.check(rc, "fi_dense_gemm")
+    _count()
+    return out
+
+
+class FiRope(ctypes.Structure):
+    _fields_ = [("cos_sin", ctypes.c_void_p), ("positions", ctypes.c_void_p), ("slot_mapping", ctypes.c_void_p),
+                ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p), ("num_heads", ctypes.c_int),
+                ("num_kv_heads", ctypes.c_int), ("head_dim", ctypes.c_int), ("block_size", ctypes.c_int)]
+
+
+def qkv_rope_cache_supported(x, w, k_cache, nh, nkv, hd, rot_dim) -> bool:
+    """Whether :func:`linear_rope_cache` can replace GEMM + rotary/cache kernel for these operands."""
+    return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and k_cache.dtype == x.dtype and hd in (64, 128)
+            and rot_dim == hd and w.shape[0] == (nh + 2 * nkv) * hd and x.shape[1] % 8 == 0)
+
+
+def linear_rope_cache(x, w, bias, positions, cos_sin, slot_mapping, k_cache, v_cache, nh, nkv, hd, rms_eps=0.0,
+                      out=None):
+    """Merged q|k|v projection whose epilogue applies the rotary embedding to q and k and writes the
+    new k / v rows into the paged cache (optionally with the RMSNorm of ``x`` fused in front).
+    Returns the [T, (nh + 2 nkv) * hd] buffer holding rotated q, rotated k and v."""
+    T, K = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(T, N, dtype=x.dtype, device=x.device)
+    if T == 0:
+        return out
+    rope = FiRope(_p(cos_sin), _p(positions), _p(slot_mapping), _p(k_cache), _p(v_cache), nh, nkv, hd,
+                  k_cache.shape[2])
+    rc = _lib.kernels().fi_dense_gemm_rope(_p(x), _p(w), _p(out), _p(bias), T, N, K, x.stride(0), w.stride(0),
+                                           out.stride(0), _DT[x.dtype], 0, 0, float(rms_eps), ctypes.byref(rope),
+                                           _p(status_word(x.device)), _stream())
+    _lib.check(rc, "fi_dense_gemm_rope")
     _count()
     return out
 

@@ -378,3 +378,31 @@ def test_gemm_on_weights_written_by_the_previous_kernel():
         for i, (o, w) in enumerate(zip(outs, wants)):
             _close(o.cpu(), w, 3e-2, 0.5, f"dynamic weights rep {rep} matrix {i}")
     ops.check_status(DEV)
+
+
+@pytest.mark.parametrize("T,nh,nkv,hd,K,eps", [(32, 32, 4, 64, 2048, 1e-5), (5, 8, 2, 128, 1024, 0.0), (64, 4, 4, 64, 512, 0.0)])
+def test_qkv_gemm_with_rotary_and_cache_write_in_the_epilogue(T, nh, nkv, hd, K, eps):
+    """One kernel (projection + rotary + cache write) against GEMM followed by the rotary/cache kernel."""
+    dev = DEV
+    g = torch.Generator(device=dev).manual_seed(T + nh)
+    N = (nh + 2 * nkv) * hd
+    x = (torch.randn(T, K, generator=g, device=dev) * 0.7).bfloat16()
+    w = (torch.randn(N, K, generator=g, device=dev) * 0.03).bfloat16()
+    bias = (torch.randn(N, generator=g, device=dev) * 0.1).bfloat16()
+    bs, nblk = 16, 40
+    cos_sin = ref.build_cos_sin(hd, 512, 10000.0).to(dev)
+    positions = torch.randint(0, 500, (T,), generator=g, device=dev, dtype=torch.int32)
+    slots = (torch.randperm(nblk * bs - bs, generator=g, device=dev)[:T] + bs).to(torch.int32)
+    slots[0] = -1                                                    # a padded row: nothing is cached
+    kc1, vc1 = torch.zeros(nblk, nkv, bs, hd, device=dev, dtype=torch.bfloat16), torch.zeros(nblk, nkv, bs, hd, device=dev, dtype=torch.bfloat16)
+    kc2, vc2 = torch.zeros_like(kc1), torch.zeros_like(vc1)
+    assert ops.qkv_rope_cache_supported(x, w, kc1, nh, nkv, hd, hd)
+    got = ops.linear_rope_cache(x, w, bias, positions, cos_sin, slots, kc1, vc1, nh, nkv, hd, rms_eps=eps)
+    want = ops.linear(x, w, bias, rms_eps=eps)
+    ops.rope_and_cache(want, positions, cos_sin, slots, kc2, vc2, nh, nkv, hd, hd)
+    torch.cuda.synchronize()
+    ops.check_status(dev)
+    _close(got.float().cpu(), want.float().cpu(), 3e-2, 3e-2, "qkv buffer")
+    _close(kc1.float().cpu(), kc2.float().cpu(), 3e-2, 3e-2, "k cache")
+    _close(vc1.float().cpu(), vc2.float().cpu(), 3e-2, 3e-2, "v cache")
+    assert float(kc1[0].abs().max()) == 0.0                          # the null block stays untouched
