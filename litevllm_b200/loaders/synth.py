@@ -73,6 +73,15 @@ def iter_llama_weights(arch: ModelArch, seed: int = 0, dtype=torch.float32, devi
         if arch.attn_bias:
             for n, r in (("q", q_rows), ("k", kv_rows), ("v", kv_rows)):
                 yield p + f"self_attn.{n}_proj.bias", normal(p + n + "b", (r,), seed, dtype=dtype, device=device)
+        if V <= 1024:   # the tiny test shapes get non-trivial norm weights (the benchmark shapes keep ones)
+            base = 0.0 if arch.norm_plus_one else 1.0
+            for n in ("input_layernorm", "post_attention_layernorm"):
+                yield p + n + ".weight", (base + 10.0 * normal(p + n, (H,), seed, dtype=torch.float32, device=device)).to(dtype)
+            if arch.qk_norm:
+                for n in ("q_norm", "k_norm"):
+                    yield p + f"self_attn.{n}.weight", (base + 10.0 * normal(p + n, (arch.head_dim,), seed, dtype=torch.float32, device=device)).to(dtype)
+    if V <= 1024:
+        yield "model.norm.weight", (1.0 + 10.0 * normal("model.norm", (H,), seed, dtype=torch.float32, device=device)).to(dtype)
     if not arch.tie_embeddings:
         yield "lm_head.weight", normal("lm_head", (V, H), seed, dtype=dtype, device=device)
 

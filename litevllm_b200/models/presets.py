@@ -86,6 +86,8 @@ PRESETS["tiny-qwen35-test"] = {
     "full_attention_interval": 4, "linear_num_key_heads": 2, "linear_num_value_heads": 4, "linear_key_head_dim": 32,
     "linear_value_head_dim": 32, "linear_conv_kernel_dim": 4, "attn_output_gate": True, "eos_token_id": 1,
 }
+PRESETS["tiny-qwen3-test"] = dict(PRESETS["tiny-llama-test"], architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+                                  head_dim=64)
 PRESETS["tiny-qwen2vl-test"] = dict(PRESETS["tiny-llama-test"], architectures=["Qwen2VLForConditionalGeneration"],
                                     model_type="qwen2_vl", attention_bias=True,
                                     vision_config={"patch_size": 14, "hidden_size": 64, "num_hidden_layers": 1,
