@@ -131,10 +131,18 @@ __device__ __forceinline__ void trace_mark(unsigned long long* trace, unsigned i
   }
 }
 // Bounded wait for a flag word to reach `want` (epochs only grow).
-__device__ __forceinline__ bool wait_flag(const unsigned int* p, unsigned int want) {
+// `status` (optional): the call's status word; once any wait of the process has timed out, later
+// waits give up after a short grace period instead of a full budget each, so a broken exchange ends
+// in about one budget overall rather than one per tile.
+__device__ __forceinline__ bool wait_flag(const unsigned int* p, unsigned int want, const int* status = nullptr) {
   const long long t0 = clock64();
+  long long budget = FI_WAIT_CYCLES;
+  unsigned int spins = 0;
   while (static_cast<int>(ld_acquire_sys(p) - want) < 0) {
-    if (clock64() - t0 > FI_WAIT_CYCLES) return false;
+    if (clock64() - t0 > budget) return false;
+    if (status != nullptr && (++spins & 1023u) == 0 &&
+        *reinterpret_cast<const volatile int*>(status) != 0)
+      budget = FI_WAIT_CYCLES >> 10;
   }
   return true;
 }
@@ -417,7 +425,7 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
       if (i_own) {
         const unsigned int* mine = reinterpret_cast<const unsigned int*>(p.flags[p.rank]) +
                                    (static_cast<size_t>(tile) * p.world + d) * kFlagParts + rank;
-        if (!wait_flag(mine, epoch_now)) {
+        if (!wait_flag(mine, epoch_now, p.status)) {
           set_status(p.status, kStatusTimeoutPeer);
           *aborted = 1;
         }
@@ -457,7 +465,9 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
               for (int q = 0; q < 4; ++q) {
                 uint4 wv = ld_volatile_v4(src + q);
                 while (wv.y != epoch_now || wv.w != epoch_now) {
-                  if (*aborted || clock64() - w0 > FI_WAIT_CYCLES) {
+                  if (*aborted || clock64() - w0 > FI_WAIT_CYCLES ||
+                      (p.status != nullptr && clock64() - w0 > (FI_WAIT_CYCLES >> 10) &&
+                       *reinterpret_cast<const volatile int*>(p.status) != 0)) {
                     set_status(p.status, kStatusTimeoutPeer);
                     *aborted = 1;
                     break;
@@ -554,6 +564,8 @@ __device__ __forceinline__ bool ag_wait_staged(const GemmParams& p, int t0, unsi
     do {
       asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f + i) : "memory");
       if (v == epoch_now) break;
+      if (p.status != nullptr && clock64() - w0 > (FI_WAIT_CYCLES >> 10) &&
+          *reinterpret_cast<const volatile int*>(p.status) != 0) break;
     } while (clock64() - w0 <= FI_WAIT_CYCLES);
     if (v != epoch_now) return false;
   }
@@ -588,7 +600,7 @@ __device__ __forceinline__ void ag_copier(const GemmParams& p) {
     const int tt = (u / kAgParts) % per;
     const int src = (p.rank + 1 + u / (kAgParts * per)) % p.ag_world;
     if (threadIdx.x == 0 &&
-        !wait_flag(reinterpret_cast<const unsigned int*>(p.ready[p.rank]) + src, epoch_now)) {
+        !wait_flag(reinterpret_cast<const unsigned int*>(p.ready[p.rank]) + src, epoch_now, p.status)) {
       set_status(p.status, kStatusTimeoutPeer);
       failed = 1;
     }
@@ -636,7 +648,7 @@ __device__ __forceinline__ bool ag_handshake(const GemmParams& p, int src, unsig
     }
   }
   if (src == p.rank) return true;
-  return wait_flag(reinterpret_cast<const unsigned int*>(p.ready[p.rank]) + src, epoch_now);
+  return wait_flag(reinterpret_cast<const unsigned int*>(p.ready[p.rank]) + src, epoch_now, p.status);
 }
 
 }  // namespace fi
