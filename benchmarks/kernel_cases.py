@@ -168,10 +168,12 @@ def main():
     for _ in range(3):
         fn()
     torch.cuda.synchronize()
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)     # larger than L2
+    # L2 flush: READ a buffer larger than the 126 MB L2 (a write would leave dirty lines whose
+    # write-back is then charged to the kernel under test)
+    flush = torch.zeros(512 << 20, dtype=torch.uint8, device=dev).view(torch.int64)
     times = []
     for _ in range(args.iters):
-        flush.zero_()
+        flush.sum()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         fn()
@@ -185,7 +187,7 @@ def main():
     res = {"case": args.case, "note": note, "median_us": round(us, 2), "min_us": round(times[0], 2),
            "gbs": round(nbytes / us / 1e3, 1), "frac_of_hbm": round(nbytes / us / 1e3 / hbm, 3),
            "tflops": round(flops / us / 1e6, 1), "frac_of_bf16_peak": round(flops / us / 1e6 / tflops, 3),
-           "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": src}, "l2": "flushed between iterations"}
+           "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": src}, "l2": "flushed (512 MB read) between iterations"}
     print(json.dumps(res))
     if args.json:
         Path(args.json).write_text(json.dumps(res, indent=1))
