@@ -206,35 +206,42 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     // thread -> weight row; per k-block: 8 packed words -> 64 values -> one swizzled 128-byte row
     const int row = (warp - 2) * 32 + lane;
     const T* scales = reinterpret_cast<const T*>(p.scales);
-    // scale / zero-point of this thread's row(s) for the two 32-value halves of a k-block,
-    // fetched one k-block ahead so the L2 latency hides behind the dequant arithmetic
-    float sf[NA][2], zf[NA][2], sf_n[NA][2], zf_n[NA][2];
-    auto fetch = [&](int kb, float (&so)[NA][2], float (&zo)[NA][2]) {
+    // scale / zero-point of this thread's row(s) for the two 32-value halves of a k-block.  The raw
+    // words are loaded one k-block ahead and only converted when their block comes up: a warp
+    // issues in order, so touching a loaded value earlier would park the whole warp for the L2
+    // latency in front of the dequant arithmetic of the current block.
+    T s_raw[NA][2];
+    uint8_t z_raw[NA][2];
+    float sf[NA][2], zf[NA][2];
+    const bool one_group = p.group >= BK;   // both halves of a k-block share one group
+    auto fetch = [&](int kb) {
 #pragma unroll
       for (int a = 0; a < NA; ++a) {
         const int grow = w_row0 + (a == 0 ? n0 : p.dual_rows + n0) + row;
 #pragma unroll
         for (int gi = 0; gi < 2; ++gi) {
-          so[a][gi] = 0.f;
-          zo[a][gi] = 8.f;
+          if (gi == 1 && one_group) { s_raw[a][1] = s_raw[a][0]; z_raw[a][1] = z_raw[a][0]; continue; }
+          s_raw[a][gi] = static_cast<T>(0.f);
+          z_raw[a][gi] = 8;
           if (grow < p.n_rows_total && kb < kb_end) {
             const size_t idx = static_cast<size_t>((kb * BK + gi * 32) / p.group) * p.n_rows_total + grow;
-            so[a][gi] = to_float(scales[idx]);
-            if (p.zeros != nullptr) zo[a][gi] = static_cast<float>(p.zeros[idx]);
+            s_raw[a][gi] = scales[idx];
+            if (p.zeros != nullptr) z_raw[a][gi] = p.zeros[idx];
           }
         }
       }
     };
-    fetch(kb_begin, sf_n, zf_n);
+    fetch(kb_begin);
     bool ok = true;
     for (int kb = kb_begin; kb < kb_end && ok; ++kb) {
       const int it = kb - kb_begin;
       const int s = it % RST, j = it % AST;
 #pragma unroll
       for (int a = 0; a < NA; ++a) {
-        sf[a][0] = sf_n[a][0]; sf[a][1] = sf_n[a][1]; zf[a][0] = zf_n[a][0]; zf[a][1] = zf_n[a][1];
+#pragma unroll
+        for (int gi = 0; gi < 2; ++gi) { sf[a][gi] = to_float(s_raw[a][gi]); zf[a][gi] = static_cast<float>(z_raw[a][gi]); }
       }
-      fetch(kb + 1, sf_n, zf_n);
+      fetch(kb + 1);
       if (!mbar_wait(&raw_full[s], (it / RST) & 1) || !mbar_wait(&a_empty[j], ((it / AST) & 1) ^ 1)) {
         set_status(p.status, kStatusTimeoutFull);
         *aborted = 1;

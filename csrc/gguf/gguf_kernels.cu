@@ -144,8 +144,146 @@ __global__ void gemv_kernel(const T* __restrict__ x, long ldx, const uint8_t* __
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Streaming GEMV (M <= 8 activation rows): the whole x is staged once per CTA as 16-bit values, the
+// CTAs stride over the weight rows, and every warp pulls its row through shared memory in chunks
+// with a three-deep cp.async pipeline (16-byte copies; the ragged 2-byte-aligned head and tail of a
+// chunk go through plain loads), so the 34/66/84-byte blocks are fetched with full-width
+// transactions and decoded from shared memory.
+template <int TYPE> struct Chunk {
+  static constexpr int kVals = TYPE == 8 ? 1024 : 4096;                       // values per chunk
+  static constexpr int kBytes = kVals / Blk<TYPE>::kVals * Blk<TYPE>::kBytes;
+  static constexpr int kBuf = (kBytes + 16 + 15) / 16 * 16;                   // + room to keep the 16-byte phase
+};
+constexpr int kGemvWarps = 16;
+constexpr int kGemvDepth = 3;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Copy nbytes (2-byte aligned source) into buf so that the copy keeps the source's 16-byte phase;
+// returns where the first byte landed.
+__device__ __forceinline__ const uint8_t* stage_chunk(const uint8_t* g, int nbytes, uint8_t* buf, int lane) {
+  const int mis = static_cast<int>(reinterpret_cast<uintptr_t>(g) & 15);
+  uint8_t* d = buf + mis;
+  const int head = mis ? min(16 - mis, nbytes) : 0;
+  for (int i = lane * 2; i < head; i += 64)
+    *reinterpret_cast<uint16_t*>(d + i) = *reinterpret_cast<const uint16_t*>(g + i);
+  const int body = (nbytes - head) & ~15;
+  for (int i = lane * 16; i < body; i += 512) cp_async16(d + head + i, g + head + i);
+  for (int i = head + body + lane * 2; i < nbytes; i += 64)
+    *reinterpret_cast<uint16_t*>(d + i) = *reinterpret_cast<const uint16_t*>(g + i);
+  return d;
+}
+
+template <typename T>
+__device__ __forceinline__ void unpack8_16bit(const uint4 raw, float* f) {
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) f[j] = static_cast<float>(e[j]);
+}
+
+template <int TYPE, typename T>
+__global__ void __launch_bounds__(kGemvWarps * 32)
+gemv_stream_kernel(const T* __restrict__ x, long ldx, const uint8_t* __restrict__ raw, long row_stride, int M, int N,
+                   int K, void* __restrict__ out, long ldo, const T* __restrict__ residual, int out_fp32) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  extern __shared__ __align__(16) uint8_t sm[];
+  T* xs = reinterpret_cast<T*>(sm);                                  // [M][K]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* wbuf = sm + ((static_cast<size_t>(M) * K * sizeof(T) + 15) & ~static_cast<size_t>(15)) +
+                  static_cast<size_t>(warp) * kGemvDepth * Chunk<TYPE>::kBuf;
+  for (int i = threadIdx.x * 8; i < M * K; i += blockDim.x * 8) {
+    const int m = i / K, k = i - m * K;
+    *reinterpret_cast<uint4*>(xs + i) = *reinterpret_cast<const uint4*>(x + m * ldx + k);
+  }
+  __syncthreads();
+  const int nch = (K + Chunk<TYPE>::kVals - 1) / Chunk<TYPE>::kVals;
+  const int row_step = gridDim.x * kGemvWarps;
+  const int row_first = blockIdx.x * kGemvWarps + warp;
+  const uint8_t* landed[kGemvDepth];
+  // item = (row, chunk); `issue` starts the copy of one item (an empty group past the last row)
+  int i_row = row_first, i_ch = 0, i_slot = 0;
+  auto issue = [&]() {
+    if (i_row < N) {
+      const int k0 = i_ch * Chunk<TYPE>::kVals;
+      const int nv = min(Chunk<TYPE>::kVals, K - k0);
+      const uint8_t* g = raw + static_cast<long>(i_row) * row_stride +
+                         static_cast<long>(k0 / Blk<TYPE>::kVals) * Blk<TYPE>::kBytes;
+      landed[i_slot] = stage_chunk(g, nv / Blk<TYPE>::kVals * Blk<TYPE>::kBytes, wbuf + i_slot * Chunk<TYPE>::kBuf, lane);
+    }
+    cp_async_commit();
+    i_slot = (i_slot + 1) % kGemvDepth;
+    if (++i_ch == nch) { i_ch = 0; i_row += row_step; }
+  };
+#pragma unroll
+  for (int d = 0; d < kGemvDepth - 1; ++d) issue();
+  float acc[kMaxM];
+#pragma unroll
+  for (int m = 0; m < kMaxM; ++m) acc[m] = 0.f;
+  int slot = 0;
+  for (int row = row_first; row < N; row += row_step) {
+    for (int ch = 0; ch < nch; ++ch) {
+      issue();
+      cp_async_wait<kGemvDepth - 1>();
+      __syncwarp();
+      const uint8_t* d = landed[slot];
+      const int k0 = ch * Chunk<TYPE>::kVals;
+      const int nv = min(Chunk<TYPE>::kVals, K - k0);
+      for (int v = lane * 8; v < nv; v += 256) {
+        float w[8];
+        decode8<TYPE>(d + (v / Blk<TYPE>::kVals) * Blk<TYPE>::kBytes, v % Blk<TYPE>::kVals, w);
+#pragma unroll
+        for (int m = 0; m < kMaxM; ++m) {
+          if (m < M) {
+            float a[8];
+            unpack8_16bit<T>(*reinterpret_cast<const uint4*>(xs + m * K + k0 + v), a);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[m] += w[j] * a[j];
+          }
+        }
+      }
+      __syncwarp();
+      slot = (slot + 1) % kGemvDepth;
+    }
+#pragma unroll
+    for (int m = 0; m < kMaxM; ++m) {
+      float v = acc[m];
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0 && m < M) {
+        if (residual) v += static_cast<float>(residual[m * ldo + row]);
+        if (out_fp32) reinterpret_cast<float*>(out)[m * ldo + row] = v;
+        else reinterpret_cast<T*>(out)[m * ldo + row] = static_cast<T>(v);
+      }
+      acc[m] = 0.f;
+    }
+  }
+  cp_async_wait<0>();
+}
+
 // Routed experts.  route r = (token r / top_k, expert ids[r]); expert payloads are stacked with a
 // byte stride.  Gate|up: a[r, i] = silu(min(g, clamp)) * clamp(u) (clamp <= 0: plain silu * u).
+// Every warp carries kMoeRows rows; a row is copied into the warp's shared-memory buffer with
+// 16-byte transactions (stage_chunk) and decoded from there.
+constexpr int kMoeRows = 4;      // rows per warp
+constexpr int kMoeWarps = 8;
+
+template <int TYPE>
+__device__ __forceinline__ const uint8_t* stage_row(const uint8_t* g, int K, uint8_t* buf, int lane) {
+  const uint8_t* d = stage_chunk(g, K / Blk<TYPE>::kVals * Blk<TYPE>::kBytes, buf, lane);
+  cp_async_commit();
+  return d;
+}
+__host__ __device__ constexpr int row_buf_bytes(int type, int K) {
+  return ((K / (type == 8 ? 32 : 256)) * (type == 8 ? 34 : type == 10 ? 84 : 66) + 16 + 15) / 16 * 16;
+}
+
 template <int TG, int TU, typename T>
 __global__ void moe_gate_up_kernel(const T* __restrict__ x, long ldx, const uint8_t* __restrict__ gate,
                                    const uint8_t* __restrict__ up, long expert_stride_g, long expert_stride_u,
@@ -153,21 +291,32 @@ __global__ void moe_gate_up_kernel(const T* __restrict__ x, long ldx, const uint
                                    int e_lo, int e_hi, int I, int K, float clamp, T* __restrict__ a) {
   fi::pdl_launch_dependents();
   fi::pdl_wait();
-  extern __shared__ float xs[];
+  extern __shared__ __align__(16) float xs[];
   const int r = blockIdx.y;
   const int e = ids[r];
   if (e < e_lo || e >= e_hi) return;   // not this rank's expert
   stage_x(x + static_cast<long>(r / top_k) * ldx, ldx, 1, K, xs);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (row >= I) return;
-  float g[kMaxM] = {0.f}, u[kMaxM] = {0.f};
-  row_dot<TG>(gate + (e - e_lo) * expert_stride_g + static_cast<long>(row) * row_stride_g, K, xs, 1, lane, g);
-  row_dot<TU>(up + (e - e_lo) * expert_stride_u + static_cast<long>(row) * row_stride_u, K, xs, 1, lane, u);
-  if (lane == 0) {
-    float gv = g[0], uv = u[0];
-    if (clamp > 0.f) { gv = fminf(gv, clamp); uv = fminf(fmaxf(uv, -clamp), clamp); }
-    a[static_cast<long>(r) * I + row] = static_cast<T>(gv / (1.f + __expf(-gv)) * uv);
+  uint8_t* bufs = reinterpret_cast<uint8_t*>(xs + K);
+  const int bg = row_buf_bytes(TG, K), bu = row_buf_bytes(TU, K);
+  uint8_t* gbuf = bufs + static_cast<size_t>(warp) * (bg + bu);
+  uint8_t* ubuf = gbuf + bg;
+  for (int rr = 0; rr < kMoeRows; ++rr) {
+    const int row = (blockIdx.x * kMoeRows + rr) * kMoeWarps + warp;
+    if (row >= I) break;
+    const uint8_t* gd = stage_row<TG>(gate + (e - e_lo) * expert_stride_g + static_cast<long>(row) * row_stride_g, K, gbuf, lane);
+    const uint8_t* ud = stage_row<TU>(up + (e - e_lo) * expert_stride_u + static_cast<long>(row) * row_stride_u, K, ubuf, lane);
+    cp_async_wait<0>();
+    __syncwarp();
+    float g[kMaxM] = {0.f}, u[kMaxM] = {0.f};
+    row_dot<TG>(gd, K, xs, 1, lane, g);
+    row_dot<TU>(ud, K, xs, 1, lane, u);
+    __syncwarp();
+    if (lane == 0) {
+      float gv = g[0], uv = u[0];
+      if (clamp > 0.f) { gv = fminf(gv, clamp); uv = fminf(fmaxf(uv, -clamp), clamp); }
+      a[static_cast<long>(r) * I + row] = static_cast<T>(gv / (1.f + __expf(-gv)) * uv);
+    }
   }
 }
 
@@ -177,20 +326,30 @@ __global__ void moe_down_kernel(const T* __restrict__ a, const uint8_t* __restri
                                 T* __restrict__ y) {
   fi::pdl_launch_dependents();
   fi::pdl_wait();
-  extern __shared__ float xs[];
+  extern __shared__ __align__(16) float xs[];
   const int r = blockIdx.y;
   const int e = ids[r];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
   if (e < e_lo || e >= e_hi) {
-    if (row < H && lane == 0) y[static_cast<long>(r) * H + row] = static_cast<T>(0.f);
+    for (int rr = 0; rr < kMoeRows; ++rr) {
+      const int row = (blockIdx.x * kMoeRows + rr) * kMoeWarps + warp;
+      if (row < H && lane == 0) y[static_cast<long>(r) * H + row] = static_cast<T>(0.f);
+    }
     return;
   }
   stage_x(a + static_cast<long>(r) * I, I, 1, I, xs);
-  if (row >= H) return;
-  float acc[kMaxM] = {0.f};
-  row_dot<TD>(down + (e - e_lo) * expert_stride + static_cast<long>(row) * row_stride, I, xs, 1, lane, acc);
-  if (lane == 0) y[static_cast<long>(r) * H + row] = static_cast<T>(acc[0]);
+  uint8_t* buf = reinterpret_cast<uint8_t*>(xs + I) + static_cast<size_t>(warp) * row_buf_bytes(TD, I);
+  for (int rr = 0; rr < kMoeRows; ++rr) {
+    const int row = (blockIdx.x * kMoeRows + rr) * kMoeWarps + warp;
+    if (row >= H) break;
+    const uint8_t* d = stage_row<TD>(down + (e - e_lo) * expert_stride + static_cast<long>(row) * row_stride, I, buf, lane);
+    cp_async_wait<0>();
+    __syncwarp();
+    float acc[kMaxM] = {0.f};
+    row_dot<TD>(d, I, xs, 1, lane, acc);
+    __syncwarp();
+    if (lane == 0) y[static_cast<long>(r) * H + row] = static_cast<T>(acc[0]);
+  }
 }
 
 }  // namespace
@@ -222,8 +381,29 @@ extern "C" int fi_gguf_gemv(const void* x, long ldx, const void* raw, long row_s
   if (M <= 0 || N <= 0) return 0;
   if (M > kMaxM || K % 8 != 0) return -10;
   if (int rc = ensure_tables()) return rc;
-  const size_t smem = static_cast<size_t>(M) * K * sizeof(float);
   const uint8_t* r = static_cast<const uint8_t*>(raw);
+  // streaming kernel: x (16-bit) must fit next to the per-warp chunk buffers, rows 2-byte aligned
+  const size_t x_bytes = (static_cast<size_t>(M) * K * 2 + 15) & ~static_cast<size_t>(15);
+  if (x_bytes <= 160 * 1024 && (K % 256) == 0 && (ldx % 8) == 0 && (row_stride % 2) == 0 &&
+      (reinterpret_cast<uintptr_t>(raw) % 2) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0) {
+    const int grid = N < 148 * kGemvWarps * 2 ? (N + kGemvWarps * 2 - 1) / (kGemvWarps * 2) : 148;
+    FI_TYPE_SWITCH(type, {
+      const size_t smem = x_bytes + static_cast<size_t>(kGemvWarps) * kGemvDepth * Chunk<TY>::kBuf;
+      if (dtype == 0) {
+        auto k = gemv_stream_kernel<TY, __nv_bfloat16>;
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        fi::launch_kernel(k, dim3(grid), dim3(kGemvWarps * 32), smem, FI_STREAM(stream), 0, (const __nv_bfloat16*)x, ldx,
+                          r, row_stride, M, N, K, out, ldo, (const __nv_bfloat16*)residual, out_fp32);
+      } else {
+        auto k = gemv_stream_kernel<TY, __half>;
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        fi::launch_kernel(k, dim3(grid), dim3(kGemvWarps * 32), smem, FI_STREAM(stream), 0, (const __half*)x, ldx, r,
+                          row_stride, M, N, K, out, ldo, (const __half*)residual, out_fp32);
+      }
+    });
+    return static_cast<int>(cudaGetLastError());
+  }
+  const size_t smem = static_cast<size_t>(M) * K * sizeof(float);
   const int wpb = 8;
   FI_TYPE_SWITCH(type, {
     if (dtype == 0) {
@@ -247,19 +427,24 @@ extern "C" int fi_gguf_moe_gate_up(const void* x, long ldx, const void* gate, co
                                    int e_lo, int e_hi, int I, int K, float clamp, void* a, void* stream) {
   if (n_routes <= 0) return 0;
   if (int rc = ensure_tables()) return rc;
-  const size_t smem = static_cast<size_t>(K) * sizeof(float);
-  const int wpb = 8;
-  const dim3 grid((I + wpb - 1) / wpb, n_routes);
+  if (K % 256 != 0) return -10;
+  const size_t smem = static_cast<size_t>(K) * sizeof(float) +
+                      static_cast<size_t>(kMoeWarps) * (row_buf_bytes(type_g, K) + row_buf_bytes(type_u, K));
+  const int wpb = kMoeWarps;
+  const int rows_per_cta = kMoeWarps * kMoeRows;
+  const dim3 grid((I + rows_per_cta - 1) / rows_per_cta, n_routes);
   const uint8_t* g = static_cast<const uint8_t*>(gate);
   const uint8_t* u = static_cast<const uint8_t*>(up);
   const long sg = row_stride_g * I, su = row_stride_u * I;
 #define FI_GU(TG, TU)                                                                                          \
+  cudaFuncSetAttribute(moe_gate_up_kernel<TG, TU, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
   fi::launch_kernel(moe_gate_up_kernel<TG, TU, __nv_bfloat16>, grid, dim3(wpb * 32), smem, FI_STREAM(stream), 0, \
                     (const __nv_bfloat16*)x, ldx, g, u, sg, su, row_stride_g, row_stride_u, ids, top_k, e_lo,  \
                     e_hi, I, K, clamp, (__nv_bfloat16*)a)
-  if (type_g == 16 && type_u == 16) FI_GU(16, 16);
-  else if (type_g == 10 && type_u == 10) FI_GU(10, 10);
-  else if (type_g == 8 && type_u == 8) FI_GU(8, 8);
+  if (smem > 200 * 1024) return -12;
+  if (type_g == 16 && type_u == 16) { FI_GU(16, 16); }
+  else if (type_g == 10 && type_u == 10) { FI_GU(10, 10); }
+  else if (type_g == 8 && type_u == 8) { FI_GU(8, 8); }
   else return -11;
 #undef FI_GU
   return static_cast<int>(cudaGetLastError());
@@ -269,12 +454,15 @@ extern "C" int fi_gguf_moe_down(const void* a, const void* down, int type_d, lon
                                 int n_routes, int e_lo, int e_hi, int H, int I, void* y, void* stream) {
   if (n_routes <= 0) return 0;
   if (int rc = ensure_tables()) return rc;
-  const size_t smem = static_cast<size_t>(I) * sizeof(float);
-  const int wpb = 8;
-  const dim3 grid((H + wpb - 1) / wpb, n_routes);
+  if (I % 256 != 0) return -10;
+  const size_t smem = static_cast<size_t>(I) * sizeof(float) + static_cast<size_t>(kMoeWarps) * row_buf_bytes(type_d, I);
+  const int wpb = kMoeWarps;
+  const int rows_per_cta = kMoeWarps * kMoeRows;
+  const dim3 grid((H + rows_per_cta - 1) / rows_per_cta, n_routes);
   const uint8_t* d = static_cast<const uint8_t*>(down);
   const long sd = row_stride * H;
   FI_TYPE_SWITCH(type_d, {
+    cudaFuncSetAttribute(moe_down_kernel<TY, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     fi::launch_kernel(moe_down_kernel<TY, __nv_bfloat16>, grid, dim3(wpb * 32), smem, FI_STREAM(stream), 0,
                       (const __nv_bfloat16*)a, d, sd, row_stride, ids, e_lo, e_hi, H, I, (__nv_bfloat16*)y);
   });
