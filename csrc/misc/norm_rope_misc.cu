@@ -347,9 +347,31 @@ __global__ void argmax_kernel(const T* __restrict__ logits, long ld, int V, long
   const T* row = logits + static_cast<long>(blockIdx.x) * ld;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    float f = Cvt<T>::to_f(row[i]);
-    if (f > best || (f == best && i < bi)) { best = f; bi = i; }
+  if (sizeof(T) == 4 && (V & 3) == 0 && (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+    // fp32 logits: 16-byte loads, four independent loads in flight per thread
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    const int n4 = V >> 2;
+    for (int i0 = threadIdx.x; i0 < n4; i0 += 4 * blockDim.x) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        v[u] = i < n4 ? row4[i] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int base = (i0 + u * blockDim.x) * 4;
+        const float f[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (f[j] > best || (f[j] == best && base + j < bi)) { best = f[j]; bi = base + j; }
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      float f = Cvt<T>::to_f(row[i]);
+      if (f > best || (f == best && i < bi)) { best = f; bi = i; }
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
