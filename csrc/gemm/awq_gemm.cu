@@ -55,8 +55,13 @@ __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162f
 __device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
 
 // RST raw stages (packed weights + tokens via TMA), AST dequantised A stages.
+// Threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 dequantisers (warps 2..5 also run the
+// TMEM -> shared-memory part of the epilogue, every thread the final reduce/store).
+constexpr int kDequantWarps = 8;
+constexpr int kAwqThreads = 64 + kDequantWarps * 32;
+
 template <typename T, int BN, int RST, int AST, bool DUAL>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kAwqThreads)
 awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 const __grid_constant__ TokenMaps tmaps_x, const GemmParams p) {
   constexpr int NA = DUAL ? 2 : 1;
@@ -106,10 +111,10 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   if (threadIdx.x == 0) {
     for (int s = 0; s < RST; ++s) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&raw_empty[s], 1 + 4);   // MMA commit (token tile) + one arrival per dequant warp
+      mbar_init(&raw_empty[s], 1 + kDequantWarps);   // MMA commit (token tile) + one arrival per dequant warp
     }
     for (int s = 0; s < AST; ++s) {
-      mbar_init(&a_full[s], 4);          // one arrival per dequant warp
+      mbar_init(&a_full[s], kDequantWarps);   // one arrival per dequant warp
       mbar_init(&a_empty[s], 1);
     }
     mbar_init(accum_bar, 1);
@@ -202,32 +207,30 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       umma_commit(accum_bar);
     }
   } else {
-    // ------------------------------------------------------------ dequantisers (warps 2..5)
-    // thread -> weight row; per k-block: 8 packed words -> 64 values -> one swizzled 128-byte row
-    const int row = (warp - 2) * 32 + lane;
+    // ------------------------------------------------------------ dequantisers (warps 2..9)
+    // thread -> (weight row, half of the k-block): 4 packed words -> 32 values -> four 16-byte chunks
+    // of the row's swizzled 128-byte line.  Eight warps keep two conversion chains per scheduler in
+    // flight; one chain per scheduler left the arithmetic latency-bound.
+    const int dw = warp - 2;
+    const int row = (dw & 3) * 32 + lane;
+    const int half = dw >> 2;
     const T* scales = reinterpret_cast<const T*>(p.scales);
-    // scale / zero-point of this thread's row(s) for the two 32-value halves of a k-block.  The raw
-    // words are loaded one k-block ahead and only converted when their block comes up: a warp
-    // issues in order, so touching a loaded value earlier would park the whole warp for the L2
-    // latency in front of the dequant arithmetic of the current block.
-    T s_raw[NA][2];
-    uint8_t z_raw[NA][2];
-    float sf[NA][2], zf[NA][2];
-    const bool one_group = p.group >= BK;   // both halves of a k-block share one group
+    // scale / zero-point of this thread's row(s) for its 32-value half of a k-block.  The raw words
+    // are loaded one k-block ahead and only converted when their block comes up: a warp issues in
+    // order, so touching a loaded value earlier would park the whole warp for the L2 latency in
+    // front of the dequant arithmetic of the current block.
+    T s_raw[NA];
+    uint8_t z_raw[NA];
     auto fetch = [&](int kb) {
 #pragma unroll
       for (int a = 0; a < NA; ++a) {
         const int grow = w_row0 + (a == 0 ? n0 : p.dual_rows + n0) + row;
-#pragma unroll
-        for (int gi = 0; gi < 2; ++gi) {
-          if (gi == 1 && one_group) { s_raw[a][1] = s_raw[a][0]; z_raw[a][1] = z_raw[a][0]; continue; }
-          s_raw[a][gi] = static_cast<T>(0.f);
-          z_raw[a][gi] = 8;
-          if (grow < p.n_rows_total && kb < kb_end) {
-            const size_t idx = static_cast<size_t>((kb * BK + gi * 32) / p.group) * p.n_rows_total + grow;
-            s_raw[a][gi] = scales[idx];
-            if (p.zeros != nullptr) z_raw[a][gi] = p.zeros[idx];
-          }
+        s_raw[a] = static_cast<T>(0.f);
+        z_raw[a] = 8;
+        if (grow < p.n_rows_total && kb < kb_end) {
+          const size_t idx = static_cast<size_t>((kb * BK + half * 32) / p.group) * p.n_rows_total + grow;
+          s_raw[a] = scales[idx];
+          if (p.zeros != nullptr) z_raw[a] = p.zeros[idx];
         }
       }
     };
@@ -236,11 +239,9 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     for (int kb = kb_begin; kb < kb_end && ok; ++kb) {
       const int it = kb - kb_begin;
       const int s = it % RST, j = it % AST;
+      float sf[NA], zf[NA];
 #pragma unroll
-      for (int a = 0; a < NA; ++a) {
-#pragma unroll
-        for (int gi = 0; gi < 2; ++gi) { sf[a][gi] = to_float(s_raw[a][gi]); zf[a][gi] = static_cast<float>(z_raw[a][gi]); }
-      }
+      for (int a = 0; a < NA; ++a) { sf[a] = to_float(s_raw[a]); zf[a] = static_cast<float>(z_raw[a]); }
       fetch(kb + 1);
       if (!mbar_wait(&raw_full[s], (it / RST) & 1) || !mbar_wait(&a_empty[j], ((it / AST) & 1) ^ 1)) {
         set_status(p.status, kStatusTimeoutFull);
@@ -250,24 +251,20 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       }
 #pragma unroll
       for (int a = 0; a < NA; ++a) {
-        const uint4* q = reinterpret_cast<const uint4*>(raw_ring + s * RAW_BYTES + B_BYTES + a * Q_BYTES + row * 32);
-        const uint4 w0 = q[0], w1 = q[1];
-        const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        const uint4 w4 = *reinterpret_cast<const uint4*>(raw_ring + s * RAW_BYTES + B_BYTES + a * Q_BYTES + row * 32 + half * 16);
+        const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
         uint8_t* dst = a_ring + (j * NA + a) * A_BYTES;
+        const typename Pack<T>::v2 s2 = Pack<T>::dup(sf[a]);
+        const typename Pack<T>::v2 z2 = Pack<T>::dup(Pack<T>::kMagicF + zf[a]);
 #pragma unroll
-        for (int gi = 0; gi < 2; ++gi) {
-          const typename Pack<T>::v2 s2 = Pack<T>::dup(sf[a][gi]);
-          const typename Pack<T>::v2 z2 = Pack<T>::dup(Pack<T>::kMagicF + zf[a][gi]);
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[4];
 #pragma unroll
-          for (int c = gi * 4; c < gi * 4 + 4; ++c) {
-            uint32_t o[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const uint32_t v = ((words[c] >> (4 * i)) & 0x000F000Fu) | Pack<T>::kMagic2;
-              o[i] = Pack<T>::sub_mul(v, z2, s2);
-            }
-            *reinterpret_cast<uint4*>(dst + sw128_offset(row, c)) = make_uint4(o[0], o[1], o[2], o[3]);
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t v = ((words[c] >> (4 * i)) & 0x000F000Fu) | Pack<T>::kMagic2;
+            o[i] = Pack<T>::sub_mul(v, z2, s2);
           }
+          *reinterpret_cast<uint4*>(dst + sw128_offset(row, half * 4 + c)) = make_uint4(o[0], o[1], o[2], o[3]);
         }
       }
       fence_proxy_async_smem();   // generic-proxy smem writes -> visible to the tensor-core proxy
@@ -279,7 +276,7 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     }
   }
   // ---------------------------------------------------------------- epilogue (epilogue.cuh)
-  if (warp >= 2) epilogue_tmem_to_smem<BN, DUAL>(p, accum_bar, tmem_base, stage_f32, aborted, warp, lane);
+  if (warp >= 2 && warp < 6) epilogue_tmem_to_smem<BN, DUAL>(p, accum_bar, tmem_base, stage_f32, aborted, warp, lane);
   __syncthreads();
   epilogue_reduce_store<BN, DUAL>(p, stage_f32, aborted, n0, t0, epoch_now, t_end);
   __syncthreads();
@@ -323,7 +320,7 @@ int launch(const CUtensorMap& tw, const TokenMaps& tx, GemmParams p, cudaStream_
       if (BN * BM * 4 * ((DUAL && S > 1) ? 2 : 1) > ring) break;
       if (max_active[S] == 0) {
         cudaLaunchConfig_t c = {};
-        c.gridDim = dim3(148, 1, S); c.blockDim = dim3(kThreads); c.dynamicSmemBytes = smem;
+        c.gridDim = dim3(148, 1, S); c.blockDim = dim3(kAwqThreads); c.dynamicSmemBytes = smem;
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeClusterDimension;
         at[0].val.clusterDim.x = 1; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = S;
@@ -345,7 +342,7 @@ int launch(const CUtensorMap& tw, const TokenMaps& tx, GemmParams p, cudaStream_
   }
   if (BN * BM * 4 * ((DUAL && p.splits > 1) ? 2 : 1) > ring) return -12;
   return static_cast<int>(launch_kernel(kern, dim3((p.N + BM - 1) / BM, p.grid_tiles > 0 ? p.grid_tiles : (p.T + BN - 1) / BN, p.splits),
-                                        dim3(kThreads), smem, stream, p.splits, tw, tx, p));
+                                        dim3(kAwqThreads), smem, stream, p.splits, tw, tx, p));
 }
 
 template <typename T, bool DUAL>

@@ -288,7 +288,7 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
   trace_mark(p.trace, epoch_now, 1);
 
   if (!*aborted) {
-    for (int idx = threadIdx.x; idx < rows_mine * (BM / 8); idx += kThreads) {
+    for (int idx = threadIdx.x; idx < rows_mine * (BM / 8); idx += blockDim.x) {
       const int tl = rank + (idx / (BM / 8)) * S;
       const int nl = (idx % (BM / 8)) * 8;
       const int t = t0 + tl;
@@ -370,7 +370,7 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
     if (!*aborted) {
       const int hd = p.rope_hd, half = hd >> 1;
       const int q_end = p.rope_nh * hd, k_end = q_end + p.rope_nkv * hd;
-      for (int idx = threadIdx.x; idx < rows_mine * (BM / 8); idx += kThreads) {
+      for (int idx = threadIdx.x; idx < rows_mine * (BM / 8); idx += blockDim.x) {
         const int tl = rank + (idx / (BM / 8)) * S;
         const int nl = (idx % (BM / 8)) * 8;
         const int t = t0 + tl;
@@ -435,7 +435,7 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
     trace_mark(p.trace, epoch_now, 3);
     // ---- phase C: sum the partials of all ranks in rank order, finish the epilogue, store
     if (!*aborted && i_own) {
-      for (int idx = threadIdx.x; idx < rows_mine * (BM / 8); idx += kThreads) {
+      for (int idx = threadIdx.x; idx < rows_mine * (BM / 8); idx += blockDim.x) {
         const int tl = rank + (idx / (BM / 8)) * S;
         const int nl = (idx % (BM / 8)) * 8;
         const int t = t0 + tl;
