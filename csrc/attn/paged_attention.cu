@@ -98,6 +98,9 @@ struct AttnParams {
   int max_blocks, block_size, nh, nkv, window;  // window <= 0: none
   float sm_scale, softcap, k_scale, v_scale;
   int kv_fp8, splits;
+  // optional [B * gridDim.y] zero-initialised tickets: the split CTA that arrives last merges the
+  // partials itself (and resets the ticket), so no separate merge launch is needed
+  unsigned int* merge_tickets;
 };
 
 // Load `rows` KV tokens starting at token tok0 of sequence b / kv head kvh into a swizzled tile.
@@ -542,6 +545,38 @@ __global__ void __launch_bounds__(128) paged_decode_v2_kernel(const AttnParams p
       if (d == 0) { p.ws_ml[base * 2] = m; p.ws_ml[base * 2 + 1] = l; }
     }
   }
+  if (p.splits > 1 && p.merge_tickets != nullptr) {
+    // last split CTA of this (sequence, head group) merges: every CTA publishes its partials, takes
+    // a ticket, and the one that draws the last ticket reads all of them back (L2) and finishes
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned int* ticket = p.merge_tickets + static_cast<long>(b) * gridDim.y + blockIdx.y;
+      const unsigned int prev = atomicAdd(ticket, 1u);
+      is_last = prev == static_cast<unsigned int>(p.splits) - 1u;
+      if (is_last) *ticket = 0u;
+    }
+    __syncthreads();
+    if (is_last) {
+      __threadfence();
+      for (int i = threadIdx.x; i < heads_here * HD; i += 128) {
+        const int r = i / HD, d = i % HD;
+        const long base = (static_cast<long>(b) * p.nh + head0 + r) * p.splits;
+        float m = -CUDART_INF_F;
+        for (int sidx = 0; sidx < p.splits; ++sidx) m = fmaxf(m, __ldcg(p.ws_ml + (base + sidx) * 2));
+        float acc = 0.f, l = 0.f;
+        for (int sidx = 0; sidx < p.splits; ++sidx) {
+          const float ms = __ldcg(p.ws_ml + (base + sidx) * 2);
+          const float f = ms == -CUDART_INF_F ? 0.f : exp2f((ms - m) * kLog2e);
+          acc += f * __ldcg(p.ws_o + (base + sidx) * HD + d);
+          l += f * __ldcg(p.ws_ml + (base + sidx) * 2 + 1);
+        }
+        const float v = l > 0.f ? acc / l * (fp8 ? p.v_scale : 1.f) : 0.f;
+        reinterpret_cast<T*>(p.out)[(static_cast<long>(b) * p.nh + head0 + r) * HD + d] = MmaT<T>::from_f(v);
+      }
+    }
+  }
 }
 
 template <typename T, int HD>
@@ -737,7 +772,9 @@ int launch_decode(const AttnParams& p, int B, cudaStream_t s) {
     }
     fi::launch_kernel(kern, dim3(p.splits, p.nkv * groups, B), dim3(128), smem, s, 0, p);
   }
-  if (p.splits > 1) fi::launch_kernel(decode_merge_kernel<T, HD>, dim3(p.nh, B), dim3(HD >= 128 ? 128 : 64), 0, s, 0, p);
+  const bool merged_in_kernel = p.merge_tickets != nullptr && p.block_size % 16 == 0;
+  if (p.splits > 1 && !merged_in_kernel)
+    fi::launch_kernel(decode_merge_kernel<T, HD>, dim3(p.nh, B), dim3(HD >= 128 ? 128 : 64), 0, s, 0, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -771,6 +808,38 @@ extern "C" int fi_paged_decode(const void* q, long q_stride, const void* k_cache
   p.ws_ml = ws_ml; p.max_blocks = max_blocks; p.block_size = block_size; p.nh = nh; p.nkv = nkv;
   p.window = window; p.sm_scale = sm_scale; p.softcap = softcap; p.k_scale = k_scale;
   p.v_scale = v_scale; p.kv_fp8 = kv_fp8; p.splits = splits;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+#define FI_DEC(TT, HD) return launch_decode<TT, HD>(p, B, s)
+  if (dtype == 0) {
+    if (hd == 64) FI_DEC(__nv_bfloat16, 64);
+    if (hd == 128) FI_DEC(__nv_bfloat16, 128);
+    if (hd == 256) FI_DEC(__nv_bfloat16, 256);
+  } else if (dtype == 1) {
+    if (hd == 64) FI_DEC(__half, 64);
+    if (hd == 128) FI_DEC(__half, 128);
+    if (hd == 256) FI_DEC(__half, 256);
+  }
+#undef FI_DEC
+  return -11;
+}
+
+// Same as fi_paged_decode with the merge of the split partials done by the last split CTA of every
+// (sequence, KV head group) instead of a second launch.  `tickets`: at least B * nkv * ceil(G / 16)
+// zero-initialised 32-bit words that stay owned by this op (each call leaves them zero again).
+extern "C" int fi_paged_decode_merged(const void* q, long q_stride, const void* k_cache,
+                               const void* v_cache, void* out, const int* block_tables,
+                               const int* seq_lens, float* ws_o, float* ws_ml, unsigned int* tickets, int B, int nh,
+                               int nkv, int hd, int max_blocks, int block_size, int window,
+                               float sm_scale, float softcap, int kv_fp8, float k_scale,
+                               float v_scale, int splits, int dtype, void* stream) {
+  if (B <= 0) return 0;
+  if (nh % nkv != 0 || splits < 1) return -10;
+  AttnParams p = {};
+  p.q = q; p.q_stride = q_stride; p.k_cache = k_cache; p.v_cache = v_cache; p.out = out;
+  p.block_tables = block_tables; p.seq_lens = seq_lens; p.cu_q = nullptr; p.ws_o = ws_o;
+  p.ws_ml = ws_ml; p.max_blocks = max_blocks; p.block_size = block_size; p.nh = nh; p.nkv = nkv;
+  p.window = window; p.sm_scale = sm_scale; p.softcap = softcap; p.k_scale = k_scale;
+  p.v_scale = v_scale; p.kv_fp8 = kv_fp8; p.splits = splits; p.merge_tickets = tickets;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 #define FI_DEC(TT, HD) return launch_decode<TT, HD>(p, B, s)
   if (dtype == 0) {

@@ -251,6 +251,21 @@ def reshape_and_cache(k, v, slot_mapping, k_cache, v_cache, k_scale=1.0, v_scale
 
 
 # ---------------------------------------------------------------------------- attention
+_MERGE_TICKETS = 1 << 16
+_merge_ticket_buf: dict[int, torch.Tensor] = {}
+
+
+def _merge_tickets(device: torch.device) -> torch.Tensor:
+    """Zero-initialised ticket words of the in-kernel decode merge (the kernel leaves them zero)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _merge_ticket_buf.get(idx)
+    if t is None:
+        with torch.inference_mode(False):
+            t = torch.zeros(_MERGE_TICKETS, dtype=torch.int32, device=device)
+        _merge_ticket_buf[idx] = t
+    return t
+
+
 def pick_decode_splits(B: int, nkv: int, max_kv_len: int, sm_count: int = 148) -> int:
     chunks = max(1, (max_kv_len + 63) // 64)
     ctas = max(1, B * nkv)
@@ -284,6 +299,17 @@ def paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, nh, nkv,
         buf = scratch("decode_ws", (n_o + B * nh * splits * 2) * 4, q.device)
         ws = buf.view(torch.float32)
         ws_o, ws_ml = ws[:n_o], ws[n_o:]
+    groups = nkv * ((nh // nkv + 15) // 16)
+    if splits > 1 and k_cache.shape[2] % 16 == 0 and B * groups <= _MERGE_TICKETS:
+        # the last split CTA merges: one launch instead of two
+        rc = _lib.kernels().fi_paged_decode_merged(
+            _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(block_tables), _p(seq_lens),
+            _p(ws_o), _p(ws_ml), _p(_merge_tickets(q.device)), B, nh, nkv, hd, block_tables.shape[1],
+            k_cache.shape[2], int(window or 0), sm_scale, float(softcap or 0.0),
+            1 if k_cache.dtype == torch.float8_e4m3fn else 0, k_scale, v_scale, splits, _DT[q.dtype], _stream())
+        _lib.check(rc, "fi_paged_decode_merged")
+        _count()
+        return out
     rc = _lib.kernels().fi_paged_decode(
         _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(block_tables), _p(seq_lens),
         _p(ws_o), _p(ws_ml), B, nh, nkv, hd, block_tables.shape[1], k_cache.shape[2], int(window or 0),
