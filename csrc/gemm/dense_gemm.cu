@@ -299,8 +299,8 @@ int launch(const CUtensorMap& tw, const TokenMaps& tx, GemmParams p, cudaStream_
   if (p.splits <= 0) p.splits = pick_splits<BN, STAGES, DUAL>(p, smem);
   if (BN * BM * 4 * ((DUAL && p.splits > 1) ? 2 : 1) > ring) return -12;
   const int nx = (p.N + BM - 1) / BM;
-  if (p.x_full != nullptr) {   // staged all-gather: about 32 copier CTAs in the first rows of the grid
-    p.copy_rows = (32 + nx * p.splits - 1) / (nx * p.splits);
+  if (p.x_full != nullptr) {   // staged all-gather: about 64 copier CTAs in the first rows of the grid
+    p.copy_rows = (64 + nx * p.splits - 1) / (nx * p.splits);   // (x 192 threads x 8 loads of 16 bytes in flight)
   }
   return static_cast<int>(launch_kernel(kern, dim3(nx, (p.T + BN - 1) / BN + p.copy_rows, p.splits),
                                         dim3(kThreads), smem, stream, p.splits, tw, tx, p));

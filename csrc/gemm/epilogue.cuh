@@ -286,8 +286,14 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
   const int parity = static_cast<int>(epoch_now & 1u);
   const int row_base = p.comm_mode == kCommReduceScatter ? p.rank * p.rows_per_rank : 0;
   trace_mark(p.trace, epoch_now, 1);
+  // does this CTA send its tile to anybody?  (reduce-scatter: only tiles owned by another rank)
+  const bool i_own_tile = owner < 0 || owner == p.rank;
+  const bool pushes = comm && (owner < 0 ? p.world > 1 : owner != p.rank);
+  // an owned tile without split-K has nothing to do before the final sum: its partial already sits
+  // in the staging tile and nobody else wants it
+  const bool skip_first_pass = comm && S == 1 && !pushes;
 
-  if (!*aborted) {
+  if (!*aborted && !skip_first_pass) {
     for (int idx = threadIdx.x; idx < rows_mine * (BM / 8); idx += blockDim.x) {
       const int tl = rank + (idx / (BM / 8)) * S;
       const int nl = (idx % (BM / 8)) * 8;
@@ -337,9 +343,12 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
         }
         continue;
       }
-      // ---- fused collective, phase A: keep my partial in my own staging rows, push it to peers
-      *reinterpret_cast<float4*>(stage_f32 + tl * BM + nl) = make_float4(g[0], g[1], g[2], g[3]);
-      *reinterpret_cast<float4*>(stage_f32 + tl * BM + nl + 4) = make_float4(g[4], g[5], g[6], g[7]);
+      // ---- fused collective, phase A: keep my partial in my own staging rows (only needed when it
+      // was just reduced over the split-K cluster and this CTA does the final sum), push it to peers
+      if (S > 1 && i_own_tile) {
+        *reinterpret_cast<float4*>(stage_f32 + tl * BM + nl) = make_float4(g[0], g[1], g[2], g[3]);
+        *reinterpret_cast<float4*>(stage_f32 + tl * BM + nl + 4) = make_float4(g[4], g[5], g[6], g[7]);
+      }
       const long trow = (p.comm_mode == kCommReduceScatter) ? (t - owner * p.rows_per_rank) : t;
       const long off = (static_cast<long>(parity) * p.world + p.rank) * p.slab_elems + trow * p.N + n;
       for (int d = 0; d < p.world; ++d) {
@@ -412,9 +421,9 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
   if (comm) {
     const unsigned int tile = static_cast<unsigned int>(t0 / BN) * gridDim.x + blockIdx.x;
     const bool inline_flags = p.xfer_16bit == kXferInlineFlags;
-    if (!inline_flags) __threadfence_system();
+    if (!inline_flags && pushes) __threadfence_system();
     __syncthreads();
-    const bool i_own = owner < 0 || owner == p.rank;
+    const bool i_own = i_own_tile;
     if (!inline_flags && !*aborted && threadIdx.x < p.world && static_cast<int>(threadIdx.x) != p.rank) {
       const int d = threadIdx.x;
       if (owner < 0 || d == owner) {
@@ -612,9 +621,12 @@ __device__ __forceinline__ void ag_copier(const GemmParams& p) {
                                          (static_cast<size_t>(src) * p.ag_rows_per_rank + row0) * row_bytes);
     const int n16 = static_cast<int>(rows_part * row_bytes / 16);
     int i = threadIdx.x;
-    for (; i + 3 * kThreads < n16; i += 4 * kThreads) {     // four loads in flight per thread
-      const uint4 a = from[i], b = from[i + kThreads], c = from[i + 2 * kThreads], d = from[i + 3 * kThreads];
-      to[i] = a; to[i + kThreads] = b; to[i + 2 * kThreads] = c; to[i + 3 * kThreads] = d;
+    for (; i + 7 * kThreads < n16; i += 8 * kThreads) {     // eight 16-byte loads in flight per thread
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = from[i + u * kThreads];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) to[i + u * kThreads] = v[u];
     }
     for (; i < n16; i += kThreads) to[i] = from[i];
     __threadfence();
