@@ -237,7 +237,7 @@ class LlamaForCausalLM(nn.Module):
         and the staging copies touch 1/world of the tokens.  Tokens are padded to world x 128 rows."""
         from ..parallel import fused_ops
         st = pstate.get_state()
-        w, r = st.tp_size, st.tp_rank()
+        w, r = st.tp_size, pstate.tp_rank()
         T, H = h_full.shape
         rpr = (T + w * 128 - 1) // (w * 128) * 128
         Tpad = rpr * w
