@@ -55,6 +55,19 @@ __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162f
 __device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
 
 // RST raw stages (packed weights + tokens via TMA), AST dequantised A stages.
+// Packed weights are fetched SUBS k-blocks (of 64) at a time so that every weight row contributes
+// 32 * SUBS contiguous bytes per TMA box: 32-byte fragments (one k-block) kept HBM at a fraction of
+// its rate.  Decode-sized token tiles take 4 k-blocks (128 bytes per row), 64 tokens 2, larger 1.
+__host__ __device__ constexpr int raw_subs(int bn) { return bn <= 32 ? 4 : (bn <= 64 ? 2 : 1); }
+// 16-byte chunk of row `row` where logical chunk c of the packed tile lives: the TMA swizzle mode
+// that matches the row pitch (128 B: 128B swizzle, 64 B: 64B swizzle, 32 B: none).
+template <int SUBS>
+__device__ __forceinline__ int raw_swizzle_chunk(int row, int c) {
+  if (SUBS == 4) return c ^ (row & 7);
+  if (SUBS == 2) return c ^ ((row >> 1) & 3);
+  return c;
+}
+
 // Threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 dequantisers (warps 2..5 also run the
 // TMEM -> shared-memory part of the epilogue, every thread the final reduce/store).
 constexpr int kDequantWarps = 8;
@@ -65,10 +78,12 @@ __global__ void __launch_bounds__(kAwqThreads)
 awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 const __grid_constant__ TokenMaps tmaps_x, const GemmParams p) {
   constexpr int NA = DUAL ? 2 : 1;
-  constexpr int A_BYTES = BM * 128;           // dequantised tile
-  constexpr int Q_BYTES = BM * 32;            // packed tile: 128 rows x 8 int32
-  constexpr int B_BYTES = BN * 128;
-  constexpr int RAW_BYTES = Q_BYTES * NA + B_BYTES;
+  constexpr int SUBS = raw_subs(BN);          // 64-wide k-blocks per raw stage
+  constexpr int A_BYTES = BM * 128;           // dequantised tile of one k-block
+  constexpr int QROW = 32 * SUBS;             // packed bytes per weight row and raw stage
+  constexpr int Q_BYTES = BM * QROW;          // packed tile: 128 rows x 8*SUBS int32
+  constexpr int B_BYTES = BN * 128;           // token tile of one k-block
+  constexpr int RAW_BYTES = Q_BYTES * NA + B_BYTES * SUBS;   // [token sub-tiles][packed tile(s)]
   constexpr int TMEM_COLS_NEED = DUAL ? 2 * BN : BN;
   constexpr uint32_t TMEM_COLS =
       TMEM_COLS_NEED <= 32 ? 32 : TMEM_COLS_NEED <= 64 ? 64 : TMEM_COLS_NEED <= 128 ? 128
@@ -144,35 +159,41 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const CUtensorMap* tmap_x_ptr = &tmaps_x.m[x_map];
       tma_prefetch_desc(&tmap_w);
       tma_prefetch_desc(tmap_x_ptr);
-      const int n_pre = min(RST, kb_end - kb_begin);
-      for (int it = 0; it < n_pre; ++it) {   // packed weights first: they do not depend on the previous kernel
-        uint8_t* r = raw_ring + it * RAW_BYTES;
-        mbar_expect_tx(&raw_full[it], RAW_BYTES);
-        tma_load_2d(r + B_BYTES, &tmap_w, &raw_full[it], (kb_begin + it) * 8, w_row0 + n0);
-        if (DUAL) tma_load_2d(r + B_BYTES + Q_BYTES, &tmap_w, &raw_full[it], (kb_begin + it) * 8, w_row0 + p.dual_rows + n0);
+      const int n_rs = (kb_end - kb_begin + SUBS - 1) / SUBS;   // raw stages of this CTA's K range
+      const int n_pre = min(RST, n_rs);
+      for (int rs = 0; rs < n_pre; ++rs) {   // packed weights first: they do not depend on the previous kernel
+        uint8_t* r = raw_ring + rs * RAW_BYTES;
+        mbar_expect_tx(&raw_full[rs], RAW_BYTES);
+        const int kb0 = kb_begin + rs * SUBS;
+        tma_load_2d(r + SUBS * B_BYTES, &tmap_w, &raw_full[rs], kb0 * 8, w_row0 + n0);
+        if (DUAL) tma_load_2d(r + SUBS * B_BYTES + Q_BYTES, &tmap_w, &raw_full[rs], kb0 * 8, w_row0 + p.dual_rows + n0);
       }
       pdl_wait();
       if (!ag_handshake(p, x_map, epoch_now)) {
         set_status(p.status, kStatusTimeoutPeer);
         *aborted = 1;
       }
-      for (int it = 0; it < n_pre; ++it)
-        tma_load_2d(raw_ring + it * RAW_BYTES, tmap_x_ptr, &raw_full[it], (kb_begin + it) * BK, x_row);
-      for (int kb = kb_begin + n_pre; kb < kb_end; ++kb) {
-        const int it = kb - kb_begin;
-        const int s = it % RST;
-        const uint32_t ph = (it / RST) & 1;
+      for (int rs = 0; rs < n_pre; ++rs)
+#pragma unroll
+        for (int sub = 0; sub < SUBS; ++sub)   // k-blocks past K read zeros (out-of-bounds fill) and are never used
+          tma_load_2d(raw_ring + rs * RAW_BYTES + sub * B_BYTES, tmap_x_ptr, &raw_full[rs],
+                      (kb_begin + rs * SUBS + sub) * BK, x_row);
+      for (int rs = n_pre; rs < n_rs; ++rs) {
+        const int s = rs % RST;
+        const uint32_t ph = (rs / RST) & 1;
         if (!mbar_wait(&raw_empty[s], ph ^ 1)) {
           set_status(p.status, kStatusTimeoutEmpty);
           *aborted = 1;
           break;
         }
         uint8_t* r = raw_ring + s * RAW_BYTES;
+        const int kb0 = kb_begin + rs * SUBS;
         mbar_expect_tx(&raw_full[s], RAW_BYTES);
-        // token tile first (keeps it 1024-byte aligned), packed weight tile(s) behind it
-        tma_load_2d(r, tmap_x_ptr, &raw_full[s], kb * BK, x_row);
-        tma_load_2d(r + B_BYTES, &tmap_w, &raw_full[s], kb * 8, w_row0 + n0);
-        if (DUAL) tma_load_2d(r + B_BYTES + Q_BYTES, &tmap_w, &raw_full[s], kb * 8, w_row0 + p.dual_rows + n0);
+#pragma unroll
+        for (int sub = 0; sub < SUBS; ++sub)
+          tma_load_2d(r + sub * B_BYTES, tmap_x_ptr, &raw_full[s], (kb0 + sub) * BK, x_row);
+        tma_load_2d(r + SUBS * B_BYTES, &tmap_w, &raw_full[s], kb0 * 8, w_row0 + n0);
+        if (DUAL) tma_load_2d(r + SUBS * B_BYTES + Q_BYTES, &tmap_w, &raw_full[s], kb0 * 8, w_row0 + p.dual_rows + n0);
       }
     }
   } else if (warp == 1) {
@@ -181,15 +202,16 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const uint32_t idesc = umma_idesc_f16(p.is_fp16 ? 0 : 1, BM, BN);
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         const int it = kb - kb_begin;
-        const int s = it % RST, j = it % AST;
-        if (!mbar_wait(&raw_full[s], (it / RST) & 1) || !mbar_wait(&a_full[j], (it / AST) & 1)) {
+        const int rs = it / SUBS, sub = it % SUBS;
+        const int s = rs % RST, j = it % AST;
+        if (!mbar_wait(&raw_full[s], (rs / RST) & 1) || !mbar_wait(&a_full[j], (it / AST) & 1)) {
           set_status(p.status, kStatusTimeoutFull);
           *aborted = 1;
           break;
         }
         tc_fence_after();
         const uint32_t a_addr = smem_u32(a_ring + j * NA * A_BYTES);
-        const uint32_t b_addr = smem_u32(raw_ring + s * RAW_BYTES);
+        const uint32_t b_addr = smem_u32(raw_ring + s * RAW_BYTES + sub * B_BYTES);
         const uint64_t da = umma_desc_sw128_kmajor(a_addr);
         const uint64_t db = umma_desc_sw128_kmajor(b_addr);
 #pragma unroll
@@ -201,7 +223,7 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
             umma_f16(tmem_base + BN, da2 + 2 * k, db + 2 * k, idesc, acc);
           }
         }
-        umma_commit(&raw_empty[s]);
+        if (sub == SUBS - 1 || kb == kb_end - 1) umma_commit(&raw_empty[s]);   // last k-block of the raw stage
         umma_commit(&a_empty[j]);
       }
       umma_commit(accum_bar);
@@ -238,12 +260,13 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     bool ok = true;
     for (int kb = kb_begin; kb < kb_end && ok; ++kb) {
       const int it = kb - kb_begin;
-      const int s = it % RST, j = it % AST;
+      const int rs = it / SUBS, sub = it % SUBS;
+      const int s = rs % RST, j = it % AST;
       float sf[NA], zf[NA];
 #pragma unroll
       for (int a = 0; a < NA; ++a) { sf[a] = to_float(s_raw[a]); zf[a] = static_cast<float>(z_raw[a]); }
       fetch(kb + 1);
-      if (!mbar_wait(&raw_full[s], (it / RST) & 1) || !mbar_wait(&a_empty[j], ((it / AST) & 1) ^ 1)) {
+      if (!mbar_wait(&raw_full[s], (rs / RST) & 1) || !mbar_wait(&a_empty[j], ((it / AST) & 1) ^ 1)) {
         set_status(p.status, kStatusTimeoutFull);
         *aborted = 1;
         ok = false;
@@ -251,7 +274,9 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       }
 #pragma unroll
       for (int a = 0; a < NA; ++a) {
-        const uint4 w4 = *reinterpret_cast<const uint4*>(raw_ring + s * RAW_BYTES + B_BYTES + a * Q_BYTES + row * 32 + half * 16);
+        // the packed tile was written by TMA with the swizzle that matches its row pitch (raw_swizzle_chunk)
+        const uint4 w4 = *reinterpret_cast<const uint4*>(raw_ring + s * RAW_BYTES + SUBS * B_BYTES + a * Q_BYTES +
+                                                         row * QROW + raw_swizzle_chunk<SUBS>(row, sub * 2 + half) * 16);
         const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
         uint8_t* dst = a_ring + (j * NA + a) * A_BYTES;
         const typename Pack<T>::v2 s2 = Pack<T>::dup(sf[a]);
@@ -271,7 +296,7 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&a_full[j]);
-        mbar_arrive(&raw_empty[s]);
+        if (sub == SUBS - 1 || kb == kb_end - 1) mbar_arrive(&raw_empty[s]);
       }
     }
   }
@@ -288,7 +313,7 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
 
 template <int BN, int RST, int AST, bool DUAL>
 constexpr int ring_bytes() {
-  return AST * (DUAL ? 2 : 1) * BM * 128 + RST * (BM * 32 * (DUAL ? 2 : 1) + BN * 128);
+  return AST * (DUAL ? 2 : 1) * BM * 128 + RST * raw_subs(BN) * (BM * 32 * (DUAL ? 2 : 1) + BN * 128);
 }
 template <int BN, int RST, int AST, bool DUAL>
 constexpr int smem_bytes() {
@@ -348,24 +373,27 @@ int launch(const CUtensorMap& tw, const TokenMaps& tx, GemmParams p, cudaStream_
 template <typename T, bool DUAL>
 int dispatch(int bn, const CUtensorMap& tw, const TokenMaps& tx, const GemmParams& p, cudaStream_t s) {
   switch (bn) {
-    case 16: return launch<T, 16, 10, 3, DUAL>(tw, tx, p, s);
-    case 32: return launch<T, 32, 8, 3, DUAL>(tw, tx, p, s);
-    case 64: return launch<T, 64, 6, 3, DUAL>(tw, tx, p, s);
+    // raw stages hold raw_subs(BN) k-blocks each; sizes keep two CTAs per SM where possible
+    case 16: return launch<T, 16, 2, DUAL ? 2 : 3, DUAL>(tw, tx, p, s);
+    case 32: return launch<T, 32, 2, DUAL ? 2 : 3, DUAL>(tw, tx, p, s);
+    case 64: return launch<T, 64, 2, DUAL ? 2 : 3, DUAL>(tw, tx, p, s);
     default: return launch<T, 128, 3, DUAL ? 2 : 3, DUAL>(tw, tx, p, s);
   }
 }
 
 // Packed weights as a 2-D int32 tensor [rows, K/8]; box = 8 words x 128 rows, no swizzle.
-inline int make_tmap_packed(CUtensorMap* out, const void* base, uint64_t rows, uint64_t k_words) {
+inline int make_tmap_packed(CUtensorMap* out, const void* base, uint64_t rows, uint64_t k_words, int subs) {
   EncodeTiledFn enc = get_encode_tiled();
   if (enc == nullptr) return -1;
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || ((k_words * 4) & 15) != 0) return -2;
   cuuint64_t dims[2] = {k_words, rows};
   cuuint64_t strides[1] = {k_words * 4};
-  cuuint32_t box[2] = {8, 128};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(8 * subs), 128};
   cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapSwizzle swz = subs == 4 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                           : (subs == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE);
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<void*>(base), dims, strides, box,
-                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -3;
 }
@@ -389,7 +417,7 @@ static int fi_awq_gemm_impl(const void* X, const void* qw, const void* scales, c
   if (grp != nullptr) w_rows = grp->num_experts * grp->expert_rows;
   CUtensorMap tw;
   TokenMaps tx;
-  int r = make_tmap_packed(&tw, qw, w_rows, K / 8);
+  int r = make_tmap_packed(&tw, qw, w_rows, K / 8, raw_subs(bn));
   if (r != 0) return r * 100 - 1;
   if (comm != nullptr && comm->ag_world > 1) {
     if (comm->ag_rows_per_rank % bn != 0) return -14;
