@@ -65,11 +65,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   asm volatile(
       "{\n"
       ".reg .pred P;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n"
+      // the last operand is a suspend-time hint (ns): a waiting warp sleeps in hardware until the
+      // phase completes instead of spinning through issue slots that working warps could use
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n"
       "selp.u32 %0, 1, 0, P;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(200000u)
       : "memory");
   return ok != 0;
 }

@@ -232,41 +232,61 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     // ------------------------------------------------------------ dequantisers (warps 2..9)
     // thread -> (weight row, half of the k-block): 4 packed words -> 32 values -> four 16-byte chunks
     // of the row's swizzled 128-byte line.  Eight warps keep two conversion chains per scheduler in
-    // flight; one chain per scheduler left the arithmetic latency-bound.
+    // flight.  Everything that does not depend on the k-block is computed once up front (swizzled
+    // offsets, scale pointers); scale and zero point stay 16-bit / integer (no float conversions);
+    // ring positions are running counters, not divisions: the loop body is issue-bound otherwise.
     const int dw = warp - 2;
     const int row = (dw & 3) * 32 + lane;
     const int half = dw >> 2;
-    const T* scales = reinterpret_cast<const T*>(p.scales);
-    // scale / zero-point of this thread's row(s) for its 32-value half of a k-block.  The raw words
-    // are loaded one k-block ahead and only converted when their block comes up: a warp issues in
-    // order, so touching a loaded value earlier would park the whole warp for the L2 latency in
-    // front of the dequant arithmetic of the current block.
-    T s_raw[NA];
+    uint32_t st_off[4], ld_off[SUBS];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) st_off[c] = sw128_offset(row, half * 4 + c);
+#pragma unroll
+    for (int sub = 0; sub < SUBS; ++sub)
+      ld_off[sub] = SUBS * B_BYTES + row * QROW + raw_swizzle_chunk<SUBS>(row, sub * 2 + half) * 16;
+    const bool pow2 = (p.group & (p.group - 1)) == 0;
+    const int gshift = 31 - __clz(p.group);
+    const uint16_t* scales16 = reinterpret_cast<const uint16_t*>(p.scales);
+    const uint16_t* sptr[NA];
+    const uint8_t* zptr[NA];
+    bool rvalid[NA];
+#pragma unroll
+    for (int a = 0; a < NA; ++a) {
+      const int grow = w_row0 + (a == 0 ? n0 : p.dual_rows + n0) + row;
+      rvalid[a] = grow < p.n_rows_total;
+      sptr[a] = scales16 + (rvalid[a] ? grow : 0);
+      zptr[a] = p.zeros != nullptr ? p.zeros + (rvalid[a] ? grow : 0) : nullptr;
+    }
+    // scale / zero point are loaded one k-block ahead and only used when their block comes up: a
+    // warp issues in order, so touching a loaded value earlier would park it for the L2 latency.
+    uint16_t s_raw[NA];
     uint8_t z_raw[NA];
     auto fetch = [&](int kb) {
+      const int k = kb * BK + half * 32;
+      const size_t g = static_cast<size_t>(pow2 ? (k >> gshift) : (k / p.group)) * p.n_rows_total;
 #pragma unroll
       for (int a = 0; a < NA; ++a) {
-        const int grow = w_row0 + (a == 0 ? n0 : p.dual_rows + n0) + row;
-        s_raw[a] = static_cast<T>(0.f);
+        s_raw[a] = 0;
         z_raw[a] = 8;
-        if (grow < p.n_rows_total && kb < kb_end) {
-          const size_t idx = static_cast<size_t>((kb * BK + half * 32) / p.group) * p.n_rows_total + grow;
-          s_raw[a] = scales[idx];
-          if (p.zeros != nullptr) z_raw[a] = p.zeros[idx];
+        if (rvalid[a] && kb < kb_end) {
+          s_raw[a] = sptr[a][g];
+          if (zptr[a] != nullptr) z_raw[a] = zptr[a][g];
         }
       }
     };
     fetch(kb_begin);
     bool ok = true;
+    int s = 0, sub = 0, j = 0;                 // raw stage, k-block inside it, A stage
+    uint32_t raw_ph = 0, a_ph = 1;             // parities to wait for
     for (int kb = kb_begin; kb < kb_end && ok; ++kb) {
-      const int it = kb - kb_begin;
-      const int rs = it / SUBS, sub = it % SUBS;
-      const int s = rs % RST, j = it % AST;
-      float sf[NA], zf[NA];
+      uint32_t s2[NA], z2[NA];
 #pragma unroll
-      for (int a = 0; a < NA; ++a) { sf[a] = to_float(s_raw[a]); zf[a] = static_cast<float>(z_raw[a]); }
+      for (int a = 0; a < NA; ++a) {           // (scale, scale) and (magic + zero, magic + zero) as 16-bit pairs
+        s2[a] = static_cast<uint32_t>(s_raw[a]) * 0x00010001u;
+        z2[a] = Pack<T>::kMagic2 + static_cast<uint32_t>(z_raw[a]) * 0x00010001u;
+      }
       fetch(kb + 1);
-      if (!mbar_wait(&raw_full[s], (rs / RST) & 1) || !mbar_wait(&a_empty[j], ((it / AST) & 1) ^ 1)) {
+      if (!mbar_wait(&raw_full[s], raw_ph) || !mbar_wait(&a_empty[j], a_ph)) {
         set_status(p.status, kStatusTimeoutFull);
         *aborted = 1;
         ok = false;
@@ -274,29 +294,33 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       }
 #pragma unroll
       for (int a = 0; a < NA; ++a) {
-        // the packed tile was written by TMA with the swizzle that matches its row pitch (raw_swizzle_chunk)
-        const uint4 w4 = *reinterpret_cast<const uint4*>(raw_ring + s * RAW_BYTES + SUBS * B_BYTES + a * Q_BYTES +
-                                                         row * QROW + raw_swizzle_chunk<SUBS>(row, sub * 2 + half) * 16);
+        const uint4 w4 = *reinterpret_cast<const uint4*>(raw_ring + s * RAW_BYTES + a * Q_BYTES + ld_off[sub]);
         const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
         uint8_t* dst = a_ring + (j * NA + a) * A_BYTES;
-        const typename Pack<T>::v2 s2 = Pack<T>::dup(sf[a]);
-        const typename Pack<T>::v2 z2 = Pack<T>::dup(Pack<T>::kMagicF + zf[a]);
+        const typename Pack<T>::v2 sv = *reinterpret_cast<const typename Pack<T>::v2*>(&s2[a]);
+        const typename Pack<T>::v2 zv = *reinterpret_cast<const typename Pack<T>::v2*>(&z2[a]);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t o[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const uint32_t v = ((words[c] >> (4 * i)) & 0x000F000Fu) | Pack<T>::kMagic2;
-            o[i] = Pack<T>::sub_mul(v, z2, s2);
+            o[i] = Pack<T>::sub_mul(v, zv, sv);
           }
-          *reinterpret_cast<uint4*>(dst + sw128_offset(row, half * 4 + c)) = make_uint4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<uint4*>(dst + st_off[c]) = make_uint4(o[0], o[1], o[2], o[3]);
         }
       }
       fence_proxy_async_smem();   // generic-proxy smem writes -> visible to the tensor-core proxy
       __syncwarp();
+      const bool raw_done = sub == SUBS - 1 || kb == kb_end - 1;
       if (lane == 0) {
         mbar_arrive(&a_full[j]);
-        if (sub == SUBS - 1 || kb == kb_end - 1) mbar_arrive(&raw_empty[s]);
+        if (raw_done) mbar_arrive(&raw_empty[s]);
+      }
+      if (++j == AST) { j = 0; a_ph ^= 1; }
+      if (++sub == SUBS) {
+        sub = 0;
+        if (++s == RST) { s = 0; raw_ph ^= 1; }
       }
     }
   }
