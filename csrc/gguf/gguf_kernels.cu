@@ -40,9 +40,31 @@ int ensure_tables() {
   return 0;
 }
 
+// The IQ2_XXS codebook (256 x 8 magnitudes) and sign table are indexed with a different value by
+// every lane: constant memory would serialise those reads, so each CTA copies them into shared
+// memory once (2 KB + 128 B) and decodes from there.
+struct Iq2Tables {
+  const uint64_t* grid;
+  const uint8_t* signs;
+};
+template <bool NEEDED>
+__device__ __forceinline__ Iq2Tables load_iq2_tables() {
+  Iq2Tables t = {nullptr, nullptr};
+  if (NEEDED) {
+    __shared__ uint64_t s_grid[256];
+    __shared__ uint8_t s_signs[128];
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) s_grid[i] = c_grid[i];
+    for (int i = threadIdx.x; i < 128; i += blockDim.x) s_signs[i] = c_signs[i];
+    __syncthreads();
+    t.grid = s_grid;
+    t.signs = s_signs;
+  }
+  return t;
+}
+
 // Decode `n` consecutive values starting at value index v0 (multiple of 8) of one block into out[].
 template <int TYPE>
-__device__ __forceinline__ void decode8(const uint8_t* blk, int v0, float* out) {
+__device__ __forceinline__ void decode8(const uint8_t* blk, int v0, float* out, const Iq2Tables& tab) {
   if (TYPE == 8) {   // Q8_0: 32 values per block
     const float d = h2f(blk);
     const int8_t* q = reinterpret_cast<const int8_t*>(blk + 2 + v0);
@@ -62,8 +84,8 @@ __device__ __forceinline__ void decode8(const uint8_t* blk, int v0, float* out) 
     const uint8_t* q = blk + 2 + ib * 8;
     const uint32_t word = q[4] | (q[5] << 8) | (q[6] << 16) | (static_cast<uint32_t>(q[7]) << 24);
     const float db = h2f(blk) * (0.5f + static_cast<float>(word >> 28)) * 0.25f;
-    const uint64_t g = c_grid[q[l]];
-    const uint8_t sg = c_signs[(word >> (7 * l)) & 127];
+    const uint64_t g = tab.grid[q[l]];
+    const uint8_t sg = tab.signs[(word >> (7 * l)) & 127];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float mag = static_cast<float>((g >> (8 * j)) & 0xFF);
@@ -81,11 +103,12 @@ template <int TYPE, typename T>
 __global__ void dequant_kernel(const uint8_t* __restrict__ raw, long row_stride, int K, T* __restrict__ out) {
   fi::pdl_launch_dependents();
   fi::pdl_wait();
+  const Iq2Tables tab = load_iq2_tables<TYPE == 16>();
   const long row = blockIdx.x;
   const uint8_t* r = raw + row * row_stride;
   for (int v0 = threadIdx.x * 8; v0 < K; v0 += blockDim.x * 8) {
     float v[8];
-    decode8<TYPE>(r + (v0 / Blk<TYPE>::kVals) * Blk<TYPE>::kBytes, v0 % Blk<TYPE>::kVals, v);
+    decode8<TYPE>(r + (v0 / Blk<TYPE>::kVals) * Blk<TYPE>::kBytes, v0 % Blk<TYPE>::kVals, v, tab);
     T o[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) o[j] = static_cast<T>(v[j]);
@@ -95,10 +118,11 @@ __global__ void dequant_kernel(const uint8_t* __restrict__ raw, long row_stride,
 
 // Dot products of one weight row with M activation rows (fp32 in shared memory, row pitch K).
 template <int TYPE>
-__device__ __forceinline__ void row_dot(const uint8_t* r, int K, const float* xs, int M, int lane, float* acc) {
+__device__ __forceinline__ void row_dot(const uint8_t* r, int K, const float* xs, int M, int lane, float* acc,
+                                        const Iq2Tables& tab) {
   for (int v0 = lane * 8; v0 < K; v0 += 32 * 8) {
     float w[8];
-    decode8<TYPE>(r + (v0 / Blk<TYPE>::kVals) * Blk<TYPE>::kBytes, v0 % Blk<TYPE>::kVals, w);
+    decode8<TYPE>(r + (v0 / Blk<TYPE>::kVals) * Blk<TYPE>::kBytes, v0 % Blk<TYPE>::kVals, w, tab);
 #pragma unroll
     for (int m = 0; m < kMaxM; ++m) {
       if (m < M) {
@@ -126,6 +150,7 @@ __global__ void gemv_kernel(const T* __restrict__ x, long ldx, const uint8_t* __
   fi::pdl_launch_dependents();
   fi::pdl_wait();
   extern __shared__ float xs[];
+  const Iq2Tables tab = load_iq2_tables<TYPE == 16>();
   stage_x(x, ldx, M, K, xs);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -133,7 +158,7 @@ __global__ void gemv_kernel(const T* __restrict__ x, long ldx, const uint8_t* __
   float acc[kMaxM];
 #pragma unroll
   for (int m = 0; m < kMaxM; ++m) acc[m] = 0.f;
-  row_dot<TYPE>(raw + static_cast<long>(row) * row_stride, K, xs, M, lane, acc);
+  row_dot<TYPE>(raw + static_cast<long>(row) * row_stride, K, xs, M, lane, acc, tab);
   if (lane == 0) {
     for (int m = 0; m < M; ++m) {
       float v = acc[m];
@@ -195,6 +220,7 @@ gemv_stream_kernel(const T* __restrict__ x, long ldx, const uint8_t* __restrict_
   fi::pdl_launch_dependents();
   fi::pdl_wait();
   extern __shared__ __align__(16) uint8_t sm[];
+  const Iq2Tables tab = load_iq2_tables<TYPE == 16>();
   T* xs = reinterpret_cast<T*>(sm);                                  // [M][K]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* wbuf = sm + ((static_cast<size_t>(M) * K * sizeof(T) + 15) & ~static_cast<size_t>(15)) +
@@ -238,7 +264,7 @@ gemv_stream_kernel(const T* __restrict__ x, long ldx, const uint8_t* __restrict_
       const int nv = min(Chunk<TYPE>::kVals, K - k0);
       for (int v = lane * 8; v < nv; v += 256) {
         float w[8];
-        decode8<TYPE>(d + (v / Blk<TYPE>::kVals) * Blk<TYPE>::kBytes, v % Blk<TYPE>::kVals, w);
+        decode8<TYPE>(d + (v / Blk<TYPE>::kVals) * Blk<TYPE>::kBytes, v % Blk<TYPE>::kVals, w, tab);
 #pragma unroll
         for (int m = 0; m < kMaxM; ++m) {
           if (m < M) {
@@ -292,6 +318,7 @@ __global__ void moe_gate_up_kernel(const T* __restrict__ x, long ldx, const uint
   fi::pdl_launch_dependents();
   fi::pdl_wait();
   extern __shared__ __align__(16) float xs[];
+  const Iq2Tables tab = load_iq2_tables<TG == 16 || TU == 16>();
   const int r = blockIdx.y;
   const int e = ids[r];
   if (e < e_lo || e >= e_hi) return;   // not this rank's expert
@@ -309,8 +336,8 @@ __global__ void moe_gate_up_kernel(const T* __restrict__ x, long ldx, const uint
     cp_async_wait<0>();
     __syncwarp();
     float g[kMaxM] = {0.f}, u[kMaxM] = {0.f};
-    row_dot<TG>(gd, K, xs, 1, lane, g);
-    row_dot<TU>(ud, K, xs, 1, lane, u);
+    row_dot<TG>(gd, K, xs, 1, lane, g, tab);
+    row_dot<TU>(ud, K, xs, 1, lane, u, tab);
     __syncwarp();
     if (lane == 0) {
       float gv = g[0], uv = u[0];
@@ -327,6 +354,7 @@ __global__ void moe_down_kernel(const T* __restrict__ a, const uint8_t* __restri
   fi::pdl_launch_dependents();
   fi::pdl_wait();
   extern __shared__ __align__(16) float xs[];
+  const Iq2Tables tab = load_iq2_tables<TD == 16>();
   const int r = blockIdx.y;
   const int e = ids[r];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -346,7 +374,7 @@ __global__ void moe_down_kernel(const T* __restrict__ a, const uint8_t* __restri
     cp_async_wait<0>();
     __syncwarp();
     float acc[kMaxM] = {0.f};
-    row_dot<TD>(d, I, xs, 1, lane, acc);
+    row_dot<TD>(d, I, xs, 1, lane, acc, tab);
     __syncwarp();
     if (lane == 0) y[static_cast<long>(r) * H + row] = static_cast<T>(acc[0]);
   }
