@@ -647,6 +647,12 @@ __global__ void __launch_bounds__(128) paged_prefill_kernel(const AttnParams p) 
   load_kv_tile<T, HD, CH, 128>(sK, p.k_cache, bt, p.block_size, p.nkv, kvh, c_begin * CH, 0, seq_len, p.kv_fp8);
   load_kv_tile<T, HD, CH, 128>(sV, p.v_cache, bt, p.block_size, p.nkv, kvh, c_begin * CH, 0, seq_len, p.kv_fp8);
   cp_async_commit();
+  // the warp's 16 query rows stay in registers for the whole KV sweep
+  __syncthreads();   // sQ was staged with plain stores by all threads
+  uint32_t qa[HD / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < HD / 16; ++ks)
+    ldsm_x4(qa[ks], smem_addr(sQ + tile_off<HD>(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4))));
   for (int c = c_begin; c < c_end; ++c) {
     const int buf = (c - c_begin) & 1;
     if (c + 1 < c_end) {
@@ -663,28 +669,42 @@ __global__ void __launch_bounds__(128) paged_prefill_kernel(const AttnParams p) 
     for (int j = 0; j < CH / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
 #pragma unroll
     for (int ks = 0; ks < HD / 16; ++ks) {
-      uint32_t a[4];
-      ldsm_x4(a, smem_addr(sQ + tile_off<HD>(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4))));
 #pragma unroll
       for (int jp = 0; jp < CH / 16; ++jp) {
         uint32_t kb[4];
         ldsm_x4(kb, smem_addr(K + tile_off<HD>(jp * 16 + (lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1))));
-        MmaT<T>::mma(s[2 * jp], a, kb);
-        MmaT<T>::mma(s[2 * jp + 1], a, kb + 2);
+        MmaT<T>::mma(s[2 * jp], qa[ks], kb);
+        MmaT<T>::mma(s[2 * jp + 1], qa[ks], kb + 2);
       }
     }
     float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
+    // chunks that lie entirely below every query row of this warp (and inside the window and the
+    // sequence) need no per-element mask
+    const bool interior = (c + 1) * CH - 1 <= posr0 && (c + 1) * CH <= seq_len &&
+                          (p.window <= 0 || c * CH > posr1 - p.window);
+    if (interior) {
 #pragma unroll
-    for (int j = 0; j < CH / 8; ++j) {
+      for (int j = 0; j < CH / 8; ++j) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int tok = c * CH + j * 8 + (lane & 3) * 2 + (e & 1);
-        const int pr = e < 2 ? posr0 : posr1;
-        float v = softcap_f(s[j][e] * scale, p.softcap);
-        const bool masked = tok > pr || tok >= seq_len || (p.window > 0 && tok <= pr - p.window);
-        if (masked) v = -CUDART_INF_F;
-        s[j][e] = v;
-        if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+        for (int e = 0; e < 4; ++e) {
+          const float v = softcap_f(s[j][e] * scale, p.softcap);
+          s[j][e] = v;
+          if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < CH / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int tok = c * CH + j * 8 + (lane & 3) * 2 + (e & 1);
+          const int pr = e < 2 ? posr0 : posr1;
+          float v = softcap_f(s[j][e] * scale, p.softcap);
+          const bool masked = tok > pr || tok >= seq_len || (p.window > 0 && tok <= pr - p.window);
+          if (masked) v = -CUDART_INF_F;
+          s[j][e] = v;
+          if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+        }
       }
     }
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));

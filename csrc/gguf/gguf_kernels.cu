@@ -412,19 +412,19 @@ extern "C" int fi_gguf_gemv(const void* x, long ldx, const void* raw, long row_s
   const uint8_t* r = static_cast<const uint8_t*>(raw);
   // streaming kernel: x (16-bit) must fit next to the per-warp chunk buffers, rows 2-byte aligned
   const size_t x_bytes = (static_cast<size_t>(M) * K * 2 + 15) & ~static_cast<size_t>(15);
-  if (x_bytes <= 160 * 1024 && (K % 256) == 0 && (ldx % 8) == 0 && (row_stride % 2) == 0 &&
+  if (x_bytes <= 150 * 1024 && (K % 256) == 0 && (ldx % 8) == 0 && (row_stride % 2) == 0 &&
       (reinterpret_cast<uintptr_t>(raw) % 2) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0) {
     const int grid = N < 148 * kGemvWarps * 2 ? (N + kGemvWarps * 2 - 1) / (kGemvWarps * 2) : 148;
     FI_TYPE_SWITCH(type, {
       const size_t smem = x_bytes + static_cast<size_t>(kGemvWarps) * kGemvDepth * Chunk<TY>::kBuf;
       if (dtype == 0) {
         auto k = gemv_stream_kernel<TY, __nv_bfloat16>;
-        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 223 * 1024);   // + static tables <= 227 KB
         fi::launch_kernel(k, dim3(grid), dim3(kGemvWarps * 32), smem, FI_STREAM(stream), 0, (const __nv_bfloat16*)x, ldx,
                           r, row_stride, M, N, K, out, ldo, (const __nv_bfloat16*)residual, out_fp32);
       } else {
         auto k = gemv_stream_kernel<TY, __half>;
-        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 223 * 1024);   // + static tables <= 227 KB
         fi::launch_kernel(k, dim3(grid), dim3(kGemvWarps * 32), smem, FI_STREAM(stream), 0, (const __half*)x, ldx, r,
                           row_stride, M, N, K, out, ldo, (const __half*)residual, out_fp32);
       }
