@@ -94,9 +94,95 @@ def init_distributed_engine(vllm_config) -> DistributedHandle:
             logger.warning("symmetric memory unavailable (%r): falling back to NCCL collectives", e)
             st.symm = None
             st.comm_backend = "nccl"
+    if st.symm is not None:
+        _self_test_fused(st)
     if torch.cuda.is_available():
         vllm_config.device = f"cuda:{st.local_rank}"
     return DistributedHandle(st)
+
+
+def _self_test_fused(st) -> None:
+    """Start-up check of the in-kernel collectives on this job's actual world size: one small call of
+    each fused form against the library collectives.  Every rank learns the verdict of all ranks; a
+    failed decode-size all-reduce switches the whole job to the NCCL path, a failed sequence-parallel
+    form (reduce-scatter, all-gather) only switches the sequence-parallel prefill off.  A wait that
+    runs out shows up as a status code, not as a hang (device waits are bounded)."""
+    import torch.distributed as dist
+
+    from .. import ops
+    from . import fused_ops
+    dev = torch.device("cuda", st.local_rank)
+    w = st.world_size
+
+    class _Layer:
+        quant_method, bias = None, None
+
+    def agree(ok: bool) -> bool:
+        t = torch.tensor([1 if ok else 0], device=dev, dtype=torch.int32)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=st.group)
+        return bool(t.item())
+
+    def status_ok() -> bool:
+        word = ops.status_word(dev)
+        bad = int(word.item()) != 0
+        if bad:
+            word.zero_()
+        return not bad
+
+    def close(a, b) -> bool:
+        a, b = a.float(), b.float()
+        return bool(torch.isfinite(a).all()) and bool(((a - b).abs() <= 0.05 + 0.05 * b.abs()).all())
+
+    g = torch.Generator(device=dev).manual_seed(1234 + st.rank)
+    ok_ar = ok_sp = True
+    try:
+        T, N, K = 32, 512, 256
+        x = (torch.randn(T, K, generator=g, device=dev) * 0.5).bfloat16()
+        wt = (torch.randn(N, K, generator=g, device=dev) * 0.05).bfloat16()
+        layer = _Layer()
+        layer.weight, layer.out_features = wt, N
+        want = x.float() @ wt.float().t()
+        dist.all_reduce(want, group=st.group)
+        for _ in range(2):      # twice: both slab parities
+            got = fused_ops._fused_gemm_allreduce(layer, x, None, None, st.symm, 2)
+        torch.cuda.synchronize(dev)
+        ok_ar = status_ok() and close(got, want)
+    except Exception as e:  # pragma: no cover - platform dependent
+        logger.warning("fused all-reduce self-test raised %r", e)
+        ok_ar = False
+    if not agree(ok_ar):
+        logger.warning("rank %d: fused collectives failed their start-up check; using NCCL collectives", st.rank)
+        st.symm = None
+        st.comm_backend = "nccl"
+        return
+    try:
+        rpr, K, N = 128, 256, 256
+        x = (torch.randn(rpr * w, K, generator=g, device=dev) * 0.5).bfloat16()
+        wt = (torch.randn(N, K, generator=g, device=dev) * 0.05).bfloat16()
+        full = x.float() @ wt.float().t()
+        dist.all_reduce(full, group=st.group)
+        res = torch.zeros(rpr, N, device=dev, dtype=torch.bfloat16)
+        for _ in range(2):
+            got = fused_ops.gemm_reduce_scatter(x, wt, res, rpr)
+        torch.cuda.synchronize(dev)
+        ok_sp = status_ok() and close(got, full[st.rank * rpr:(st.rank + 1) * rpr])
+        xs = (torch.randn(rpr, K, generator=g, device=dev) * 0.5).bfloat16()
+        g2 = torch.Generator(device=dev).manual_seed(99)
+        wc = (torch.randn(N, K, generator=g2, device=dev) * 0.05).bfloat16()
+        gathered = [torch.empty_like(xs) for _ in range(w)]
+        dist.all_gather(gathered, xs, group=st.group)
+        want = torch.cat(gathered).float() @ wc.float().t()
+        for _ in range(2):
+            got = fused_ops.allgather_gemm(xs, wc, rpr * w, rpr)
+        torch.cuda.synchronize(dev)
+        ok_sp = ok_sp and status_ok() and close(got, want)
+    except Exception as e:  # pragma: no cover - platform dependent
+        logger.warning("sequence-parallel self-test raised %r", e)
+        ok_sp = False
+    st.sequence_parallel_ok = agree(ok_sp)
+    if not st.sequence_parallel_ok:
+        logger.warning("rank %d: fused reduce-scatter / all-gather failed their start-up check; "
+                       "sequence-parallel prefill is off", st.rank)
 
 
 def _worker(rank: int, world: int, port: int, fn, args):

@@ -25,6 +25,7 @@ class ParallelState:
     comm_backend: str = "nccl"
     group: object | None = None
     symm: object | None = None      # SymmetricHeap when the fused backend is up
+    sequence_parallel_ok: bool = True   # cleared when the fused reduce-scatter / all-gather start-up check fails
 
     @property
     def tp_rank(self) -> int:
