@@ -127,9 +127,7 @@ def run_ours(args) -> dict:
                                   "FASTINFERENCE_KV_MAX_ACTIVE_REQUESTS": str(B),
                                   "FASTINFERENCE_LITE_PREFILL_MICROBATCH": "8"}}
         return LLM(f"synthetic:{args.model}", dtype="bfloat16", max_num_seqs=B, max_model_len=max_len,
-                   # one prefill micro-batch (8 prompts) plus the running decodes per engine step, so first
-                   # tokens leave micro-batch by micro-batch instead of after the whole batch
-                   max_num_batched_tokens=max(8192, min(B * P, 8 * P + B)),
+                   max_num_batched_tokens=max(8192, B * P),
                    tensor_parallel_size=world if args.parallel == "tp" else 1,
                    expert_parallel_size=world if args.parallel == "ep" else 1,
                    comm_backend=args.comm_backend, fastinference_config=cfg, device=f"cuda:{local_rank}")
