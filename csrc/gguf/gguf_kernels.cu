@@ -213,9 +213,7 @@ __device__ __forceinline__ void unpack8_16bit(const uint4 raw, float* f) {
   for (int j = 0; j < 8; ++j) f[j] = static_cast<float>(e[j]);
 }
 
-// XF32: x is staged as fp32 (when M * K * 4 bytes fit), which removes the 16-bit unpacking from the
-// inner loop: with M rows of x per weight value that unpacking is most of the instructions.
-template <int TYPE, typename T, bool XF32>
+template <int TYPE, typename T>
 __global__ void __launch_bounds__(kGemvWarps * 32)
 gemv_stream_kernel(const T* __restrict__ x, long ldx, const uint8_t* __restrict__ raw, long row_stride, int M, int N,
                    int K, void* __restrict__ out, long ldo, const T* __restrict__ residual, int out_fp32) {
@@ -223,23 +221,13 @@ gemv_stream_kernel(const T* __restrict__ x, long ldx, const uint8_t* __restrict_
   fi::pdl_wait();
   extern __shared__ __align__(16) uint8_t sm[];
   const Iq2Tables tab = load_iq2_tables<TYPE == 16>();
-  T* xs = reinterpret_cast<T*>(sm);                                  // [M][K] (16-bit form)
-  float* xf = reinterpret_cast<float*>(sm);                          // [M][K] (fp32 form)
+  T* xs = reinterpret_cast<T*>(sm);                                  // [M][K]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr size_t kXElem = XF32 ? sizeof(float) : sizeof(T);
-  uint8_t* wbuf = sm + ((static_cast<size_t>(M) * K * kXElem + 15) & ~static_cast<size_t>(15)) +
+  uint8_t* wbuf = sm + ((static_cast<size_t>(M) * K * sizeof(T) + 15) & ~static_cast<size_t>(15)) +
                   static_cast<size_t>(warp) * kGemvDepth * Chunk<TYPE>::kBuf;
   for (int i = threadIdx.x * 8; i < M * K; i += blockDim.x * 8) {
     const int m = i / K, k = i - m * K;
-    const uint4 raw8 = *reinterpret_cast<const uint4*>(x + m * ldx + k);
-    if (XF32) {
-      float f[8];
-      unpack8_16bit<T>(raw8, f);
-      *reinterpret_cast<float4*>(xf + i) = make_float4(f[0], f[1], f[2], f[3]);
-      *reinterpret_cast<float4*>(xf + i + 4) = make_float4(f[4], f[5], f[6], f[7]);
-    } else {
-      *reinterpret_cast<uint4*>(xs + i) = raw8;
-    }
+    *reinterpret_cast<uint4*>(xs + i) = *reinterpret_cast<const uint4*>(x + m * ldx + k);
   }
   __syncthreads();
   const int nch = (K + Chunk<TYPE>::kVals - 1) / Chunk<TYPE>::kVals;
@@ -281,13 +269,7 @@ gemv_stream_kernel(const T* __restrict__ x, long ldx, const uint8_t* __restrict_
         for (int m = 0; m < kMaxM; ++m) {
           if (m < M) {
             float a[8];
-            if (XF32) {
-              const float4 a0 = *reinterpret_cast<const float4*>(xf + m * K + k0 + v);
-              const float4 a1 = *reinterpret_cast<const float4*>(xf + m * K + k0 + v + 4);
-              a[0] = a0.x; a[1] = a0.y; a[2] = a0.z; a[3] = a0.w; a[4] = a1.x; a[5] = a1.y; a[6] = a1.z; a[7] = a1.w;
-            } else {
-              unpack8_16bit<T>(*reinterpret_cast<const uint4*>(xs + m * K + k0 + v), a);
-            }
+            unpack8_16bit<T>(*reinterpret_cast<const uint4*>(xs + m * K + k0 + v), a);
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[m] += w[j] * a[j];
           }
@@ -422,16 +404,6 @@ extern "C" int fi_gguf_dequant(const void* raw, int type, int rows, int K, long 
   return static_cast<int>(cudaGetLastError());
 }
 
-template <int TY, typename TT, bool XF>
-static void launch_gemv_stream(int grid, size_t smem, void* stream, const void* x, long ldx, const uint8_t* r,
-                               long row_stride, int M, int N, int K, void* out, long ldo, const void* residual,
-                               int out_fp32) {
-  auto k = gemv_stream_kernel<TY, TT, XF>;
-  cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 223 * 1024);   // + static tables <= 227 KB
-  fi::launch_kernel(k, dim3(grid), dim3(kGemvWarps * 32), smem, FI_STREAM(stream), 0, (const TT*)x, ldx, r, row_stride,
-                    M, N, K, out, ldo, (const TT*)residual, out_fp32);
-}
-
 extern "C" int fi_gguf_gemv(const void* x, long ldx, const void* raw, long row_stride, int type, int M, int N, int K,
                             void* out, long ldo, const void* residual, int out_fp32, int dtype, void* stream) {
   if (M <= 0 || N <= 0) return 0;
@@ -439,19 +411,22 @@ extern "C" int fi_gguf_gemv(const void* x, long ldx, const void* raw, long row_s
   if (int rc = ensure_tables()) return rc;
   const uint8_t* r = static_cast<const uint8_t*>(raw);
   // streaming kernel: x (16-bit) must fit next to the per-warp chunk buffers, rows 2-byte aligned
-  const bool xf32 = static_cast<size_t>(M) * K * 4 <= 150 * 1024;     // fp32 copy of x when it fits
-  const size_t x_bytes = (static_cast<size_t>(M) * K * (xf32 ? 4 : 2) + 15) & ~static_cast<size_t>(15);
+  const size_t x_bytes = (static_cast<size_t>(M) * K * 2 + 15) & ~static_cast<size_t>(15);
   if (x_bytes <= 150 * 1024 && (K % 256) == 0 && (ldx % 8) == 0 && (row_stride % 2) == 0 &&
       (reinterpret_cast<uintptr_t>(raw) % 2) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0) {
     const int grid = N < 148 * kGemvWarps * 2 ? (N + kGemvWarps * 2 - 1) / (kGemvWarps * 2) : 148;
     FI_TYPE_SWITCH(type, {
       const size_t smem = x_bytes + static_cast<size_t>(kGemvWarps) * kGemvDepth * Chunk<TY>::kBuf;
-if (dtype == 0) {
-        if (xf32) launch_gemv_stream<TY, __nv_bfloat16, true>(grid, smem, stream, x, ldx, r, row_stride, M, N, K, out, ldo, residual, out_fp32);
-        else launch_gemv_stream<TY, __nv_bfloat16, false>(grid, smem, stream, x, ldx, r, row_stride, M, N, K, out, ldo, residual, out_fp32);
+      if (dtype == 0) {
+        auto k = gemv_stream_kernel<TY, __nv_bfloat16>;
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 223 * 1024);   // + static tables <= 227 KB
+        fi::launch_kernel(k, dim3(grid), dim3(kGemvWarps * 32), smem, FI_STREAM(stream), 0, (const __nv_bfloat16*)x, ldx,
+                          r, row_stride, M, N, K, out, ldo, (const __nv_bfloat16*)residual, out_fp32);
       } else {
-        if (xf32) launch_gemv_stream<TY, __half, true>(grid, smem, stream, x, ldx, r, row_stride, M, N, K, out, ldo, residual, out_fp32);
-        else launch_gemv_stream<TY, __half, false>(grid, smem, stream, x, ldx, r, row_stride, M, N, K, out, ldo, residual, out_fp32);
+        auto k = gemv_stream_kernel<TY, __half>;
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 223 * 1024);   // + static tables <= 227 KB
+        fi::launch_kernel(k, dim3(grid), dim3(kGemvWarps * 32), smem, FI_STREAM(stream), 0, (const __half*)x, ldx, r,
+                          row_stride, M, N, K, out, ldo, (const __half*)residual, out_fp32);
       }
     });
     return static_cast<int>(cudaGetLastError());
