@@ -15,6 +15,29 @@ from ..request_state import RequestState
 
 
 class Sampler:
+    def __init__(self):
+        import os
+        # the native kernel (threshold selection instead of a sort); FI_NATIVE_SAMPLER=0 keeps the PyTorch form
+        self.native = os.environ.get("FI_NATIVE_SAMPLER", "1") != "0"
+
+    def _sample_native(self, logits: torch.Tensor, reqs: list[RequestState], sps) -> torch.Tensor:
+        """One kernel for the whole batch: per-row parameters go up in one small copy, each sampled row
+        draws one uniform number from its request's own generator (greedy rows pass temperature 0)."""
+        n = logits.shape[0]
+        dev = logits.device
+        host = torch.empty(4, n, dtype=torch.float32)
+        for i, sp in enumerate(sps):
+            host[0, i] = 0.0 if sp.is_greedy else max(sp.temperature, 1e-6)
+            host[1, i] = float(sp.top_k) if sp.top_k and sp.top_k > 0 else 0.0
+            host[2, i] = sp.top_p
+            host[3, i] = sp.min_p
+        par = host.to(dev, non_blocking=True)
+        uni = torch.zeros(n, dtype=torch.float32, device=dev)
+        for i, st in enumerate(reqs):
+            if not sps[i].is_greedy:
+                uni[i:i + 1] = torch.rand(1, generator=st.rng, device=dev, dtype=torch.float32)
+        return ops.sample(logits, par[0], par[1].to(torch.int32), par[2], par[3], uni)
+
     def sample(self, logits: torch.Tensor, reqs: list[RequestState]) -> torch.Tensor:
         """logits [n, V] float32 -> int64 [n] on the same device."""
         sps = [st.sampling_params for st in reqs]
@@ -22,6 +45,8 @@ class Sampler:
             return ops.argmax(logits)
         n, V = logits.shape
         dev = logits.device
+        if logits.is_cuda and logits.dtype == torch.float32 and self.native:
+            return self._sample_native(logits, reqs, sps)
         greedy_tokens = ops.argmax(logits)
         temps = torch.tensor([max(sp.temperature, 1e-6) for sp in sps], device=dev, dtype=torch.float32)[:, None]
         scaled = logits / temps

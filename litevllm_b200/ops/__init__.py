@@ -424,5 +424,20 @@ def argmax(logits, out=None):
     return out
 
 
+def sample(logits, temperature, top_k, top_p, min_p, uniform, out=None):
+    """One token per row of fp32 ``logits`` [n, V] with per-row temperature (<= 0: arg-max), top-k
+    (<= 0: off), top-p (>= 1: off), min-p (<= 0: off) and one uniform number in [0, 1) per row;
+    all parameters are device tensors of length n.  Native kernel, no sort of the vocabulary."""
+    n, V = logits.shape
+    assert logits.is_cuda and logits.dtype == torch.float32 and logits.stride(1) == 1
+    if out is None:
+        out = torch.empty(n, dtype=torch.int64, device=logits.device)
+    rc = _lib.kernels().fi_sample(_p(logits), logits.stride(0), n, V, _p(temperature), _p(top_k), _p(top_p), _p(min_p),
+                                  _p(uniform), _p(out), _stream())
+    _lib.check(rc, "fi_sample")
+    _count()
+    return out
+
+
 def default_sm_scale(hd: int) -> float:
     return 1.0 / math.sqrt(hd)

@@ -427,3 +427,42 @@ def test_qkv_gemm_with_rotary_and_cache_write_in_the_epilogue(T, nh, nkv, hd, K,
     _close(kc1.float().cpu(), kc2.float().cpu(), 3e-2, 3e-2, "k cache")
     _close(vc1.float().cpu(), vc2.float().cpu(), 3e-2, 3e-2, "v cache")
     assert float(kc1[0].abs().max()) == 0.0                          # the null block stays untouched
+
+
+def test_native_sampler_thresholds_and_distribution():
+    """The sampling kernel against the sort-based definition: with top-k / top-p / min-p the drawn token
+    must lie in the kept set, the empirical distribution over many uniform numbers must match the
+    renormalised probabilities, greedy rows return the arg-max, and a fixed uniform number is reproducible."""
+    dev = torch.device(DEV, 0)
+    g = torch.Generator(device=dev).manual_seed(3)
+    V, n = 1000, 4096
+    base = torch.randn(V, generator=g, device=dev) * 2.0
+    logits = base[None, :].expand(n, V).contiguous()
+    temp, k, p, mp = 0.7, 50, 0.8, 0.02
+    scaled = base / temp
+    srt, idx = torch.sort(scaled, descending=True)
+    mask = torch.arange(V, device=dev) >= k
+    probs = torch.softmax(srt.masked_fill(mask, float("-inf")), -1)
+    cum = probs.cumsum(-1)
+    mask |= (cum - probs) >= p
+    mask |= probs < mp * probs[0]
+    mask[0] = False
+    final = torch.softmax(srt.masked_fill(mask, float("-inf")), -1)
+    want = torch.zeros(V, device=dev)
+    want[idx] = final
+    u = torch.rand(n, generator=g, device=dev)
+    args = (torch.full((n,), temp, device=dev), torch.full((n,), k, device=dev, dtype=torch.int32),
+            torch.full((n,), p, device=dev), torch.full((n,), mp, device=dev))
+    tok = ops.sample(logits, *args, u)
+    assert bool((want[tok] > 0).all()), "a token outside the kept set was drawn"
+    freq = torch.bincount(tok, minlength=V).float() / n
+    assert float((freq - want).abs().max()) < 0.03
+    assert torch.equal(tok, ops.sample(logits, *args, u))                      # same numbers, same tokens
+    greedy = ops.sample(logits[:8], torch.zeros(8, device=dev), args[1][:8], args[2][:8], args[3][:8], u[:8])
+    assert torch.equal(greedy, torch.full((8,), int(base.argmax()), device=dev))
+    # no filters: plain temperature sampling over the whole vocabulary
+    off = (torch.ones(n, device=dev), torch.zeros(n, device=dev, dtype=torch.int32), torch.ones(n, device=dev),
+           torch.zeros(n, device=dev))
+    tok = ops.sample(logits, *off, u)
+    freq = torch.bincount(tok, minlength=V).float() / n
+    assert float((freq - torch.softmax(base, -1)).abs().max()) < 0.03
