@@ -466,3 +466,35 @@ def test_native_sampler_thresholds_and_distribution():
     tok = ops.sample(logits, *off, u)
     freq = torch.bincount(tok, minlength=V).float() / n
     assert float((freq - torch.softmax(base, -1)).abs().max()) < 0.03
+
+
+@pytest.mark.parametrize("T,N,K", [(1024, 256, 512), (1500, 2560, 2048), (4096, 640, 1088), (2048, 129 * 8, 72)])
+@pytest.mark.parametrize("mode", ["plain", "bias_residual", "gated"])
+def test_persistent_prefill_gemm(T, N, K, mode):
+    """The persistent double-accumulator GEMM (prefill sizes) against fp32 matmul, including ragged token
+    and row counts and more tiles than SMs."""
+    dev = torch.device(DEV, 0)
+    g = torch.Generator(device=dev).manual_seed(T + N + K)
+    x = (torch.randn(T, K, generator=g, device=dev) * 0.5).bfloat16()
+    if mode == "gated":
+        w = (torch.randn(2 * N, K, generator=g, device=dev) * 0.05).bfloat16()
+        h = x.float() @ w.float().t()
+        want = torch.nn.functional.silu(h[:, :N]) * h[:, N:]
+        got = ops.gated_linear(x, w, "silu")
+    else:
+        w = (torch.randn(N, K, generator=g, device=dev) * 0.05).bfloat16()
+        bias = (torch.randn(N, generator=g, device=dev) * 0.1).bfloat16() if mode == "bias_residual" else None
+        res = torch.randn(T, N, generator=g, device=dev).bfloat16() if mode == "bias_residual" else None
+        want = x.float() @ w.float().t()
+        if bias is not None:
+            want = want + bias.float() + res.float()
+        import litevllm_b200.ops as O
+        saved, O._PERSISTENT_PLAIN = O._PERSISTENT_PLAIN, True      # plain products take this kernel only on request
+        try:
+            got = ops.linear(x, w, bias, res)
+        finally:
+            O._PERSISTENT_PLAIN = saved
+    torch.cuda.synchronize()
+    ops.check_status(dev)
+    err = (got.float() - want).abs().max().item()
+    assert err < 0.03 * max(1.0, want.abs().max().item()), err
