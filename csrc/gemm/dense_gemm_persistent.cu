@@ -84,6 +84,7 @@ dense_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const _
   uint64_t* acc_empty = acc_full + 2;         // [2] epilogue -> MMA
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* aborted = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* stage = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(tmem_slot) + 16);   // [4 warps][16 tokens][32 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_launch_dependents();
@@ -192,38 +193,81 @@ dense_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const _
       const int t0 = (tile / p.n_tiles_n) * BN;
       const bool gated = p.dual_rows > 0;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(b * ACC_COLS);
+      // Each thread owns one weight row of the accumulator (a TMEM lane) but the output is
+      // token-major: a batch of 16 tokens x 32 rows goes through this warp's shared-memory patch as
+      // fp32 and comes back as 8-row vectors, so bias / residual / store are 16-byte accesses.
+      float* patch = stage + (warp - 2) * (16 * 32);
+      const int vc = lane & 3;                // which 8-row chunk of the warp's 32 rows this lane finishes
+      const int vj = lane >> 2;               // tokens vj and vj + 8 of the batch
       // gated: one output row per thread (gate and up combined); plain wide tile: two rows, 128 apart
       const int halves = (DUAL && !gated) ? 2 : 1;
       for (int hh = 0; hh < halves; ++hh) {
-        const int n = n0 + hh * BM + n_local;
-        const bool n_ok = n < p.N;
-        const float bias = (p.bias != nullptr && n_ok) ? ld16(p.bias, n, p.is_fp16) : 0.f;
+        const int nv = n0 + hh * BM + q * 32 + vc * 8;      // first of the 8 rows this lane stores
+        const bool nv_ok = nv < p.N;
+        float bias8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) bias8[e] = (p.bias != nullptr && nv_ok) ? ld16(p.bias, nv + e, p.is_fp16) : 0.f;
+        // the residual values of a batch are requested one batch ahead, so their latency hides behind
+        // the TMEM read and the transposition of the batch in front
+        auto load_res = [&](int c0, uint4 (&dst)[2]) {
+#pragma unroll
+          for (int rep = 0; rep < 2; ++rep) {
+            const int t = t0 + c0 + vj + rep * 8;
+            dst[rep] = make_uint4(0, 0, 0, 0);
+            if (p.residual != nullptr && nv_ok && c0 < BN && t < p.T)
+              dst[rep] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.residual) +
+                                                         static_cast<size_t>(t) * p.ldc + nv);
+          }
+        };
+        uint4 res_cur[2], res_next[2];
+        load_res(0, res_cur);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
           uint32_t r[16], u[16];
           tmem_ld_x16(taddr + hh * BN + c0, r);
           if (DUAL && gated) tmem_ld_x16(taddr + BN + c0, u);
-          // the residual may alias the output: fetch the 16 values of this batch before any store
-          float res[16];
+          load_res(c0 + 16, res_next);
+          tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int t = t0 + c0 + j;
-            res[j] = (p.residual != nullptr && n_ok && t < p.T)
-                         ? ld16(p.residual, static_cast<size_t>(t) * p.ldc + n, p.is_fp16) : 0.f;
+            float v = __uint_as_float(r[j]);
+            if (DUAL && gated) v = act_f(v, p.act) * __uint_as_float(u[j]);
+            else v = act_f(v, p.act);
+            patch[j * 32 + lane] = v;
           }
-          tmem_ld_wait();
-          if (n_ok) {
+          __syncwarp();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int t = t0 + c0 + j;
-              if (t < p.T) {
-                float v = __uint_as_float(r[j]);
-                if (DUAL && gated) v = act_f(v, p.act) * __uint_as_float(u[j]);
-                else v = act_f(v, p.act);
-                st16(p.C, static_cast<size_t>(t) * p.ldc + n, v + bias + res[j], p.is_fp16);
+          for (int rep = 0; rep < 2; ++rep) {
+            const int j = vj + rep * 8;
+            const int t = t0 + c0 + j;
+            if (nv_ok && t < p.T) {
+              const float4 a0 = *reinterpret_cast<const float4*>(patch + j * 32 + vc * 8);
+              const float4 a1 = *reinterpret_cast<const float4*>(patch + j * 32 + vc * 8 + 4);
+              float v[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+              const size_t off = static_cast<size_t>(t) * p.ldc + nv;
+              const uint4 raw = res_cur[rep];
+              const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+              uint32_t ow[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float lo = v[2 * e] + bias8[2 * e], hi = v[2 * e + 1] + bias8[2 * e + 1];
+                if (p.is_fp16) {
+                  const __half2 rr = *reinterpret_cast<const __half2*>(&rw[e]);
+                  lo += __low2float(rr); hi += __high2float(rr);
+                  const __half2 o = __floats2half2_rn(lo, hi);
+                  ow[e] = *reinterpret_cast<const uint32_t*>(&o);
+                } else {
+                  lo += __uint_as_float(rw[e] << 16); hi += __uint_as_float(rw[e] & 0xffff0000u);
+                  const __nv_bfloat162 o = __floats2bfloat162_rn(lo, hi);
+                  ow[e] = *reinterpret_cast<const uint32_t*>(&o);
+                }
               }
+              *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.C) + off) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
             }
           }
+          __syncwarp();
+          res_cur[0] = res_next[0];
+          res_cur[1] = res_next[1];
         }
       }
       tc_fence_before();
@@ -242,7 +286,7 @@ dense_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const _
 template <int STAGES, bool DUAL>
 int launch(const CUtensorMap& tw, const CUtensorMap& tx, const PParams& p, cudaStream_t stream) {
   auto kern = dense_gemm_persistent_kernel<STAGES, DUAL>;
-  constexpr int smem = STAGES * (BM * 128 * (DUAL ? 2 : 1) + BN * 128) + (2 * STAGES + 4) * 8 + 16 + 1024;
+  constexpr int smem = STAGES * (BM * 128 * (DUAL ? 2 : 1) + BN * 128) + (2 * STAGES + 4) * 8 + 16 + 4 * 16 * 32 * 4 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -269,7 +313,9 @@ extern "C" int fi_dense_gemm_persistent(const void* X, const void* W, void* C, c
                                         int T, int N, int K, int ldx, int ldw, int ldc, int act, int dual_rows,
                                         int dtype, int* status, void* stream) {
   if (T <= 0 || N <= 0 || K <= 0) return 0;
-  if ((K % 8) != 0 || (ldx % 8) != 0 || (ldw % 8) != 0) return -10;
+  if ((K % 8) != 0 || (ldx % 8) != 0 || (ldw % 8) != 0 || (N % 8) != 0 || (ldc % 8) != 0 ||
+      (reinterpret_cast<uintptr_t>(C) & 15) != 0 || (residual != nullptr && (reinterpret_cast<uintptr_t>(residual) & 15) != 0))
+    return -10;
   if (dual_rows > 0 && N != dual_rows) return -11;
   const int w_rows = dual_rows > 0 ? 2 * dual_rows : N;
   CUtensorMap tw, tx;

@@ -84,11 +84,8 @@ def scratch(name: str, nbytes: int, device: torch.device) -> torch.Tensor:
 # prefill-sized GEMMs take the persistent kernel (FI_PERSISTENT_GEMM=0 keeps the one-tile-per-CTA kernel)
 _PERSISTENT_GEMM = os.environ.get("FI_PERSISTENT_GEMM", "1") != "0"
 _PERSISTENT_MIN_T = int(os.environ.get("FI_PERSISTENT_MIN_T", "1024"))
-# Plain (non-gated) products stay on the one-tile kernel by default: the persistent kernel's epilogue
-# (one output row per thread, 2-byte accesses) is slower than its main loop there (measured 549-568
-# TFLOP/s against 774 at T=8192, K=2048); the gated form does twice the math per stored value and wins
-# (444 -> 272 us for T=8192, I=5632, K=2048).
-_PERSISTENT_PLAIN = os.environ.get("FI_PERSISTENT_PLAIN", "0") == "1"
+# Plain (non-gated) products use it too, with 256-row tiles (FI_PERSISTENT_PLAIN=0 keeps the one-tile kernel)
+_PERSISTENT_PLAIN = _PERSISTENT_GEMM and os.environ.get("FI_PERSISTENT_PLAIN", "1") != "0"
 
 
 def _rms_scaled(x, eps):
@@ -127,7 +124,7 @@ def linear(x, w, bias=None, residual=None, act=None, out=None, out_dtype=None, s
         _lib.check(rc, "fi_dense_gemm_rmsnorm")
         _count()
         return out
-    if _PERSISTENT_PLAIN and T >= _PERSISTENT_MIN_T and splits == 0 and bn == 0 and out.dtype == x.dtype:
+    if _PERSISTENT_PLAIN and T >= _PERSISTENT_MIN_T and splits == 0 and bn == 0 and out.dtype == x.dtype and N % 8 == 0:
         # prefill-sized: persistent CTAs with two TMEM accumulators (epilogue overlaps the next main loop)
         rc = _lib.kernels().fi_dense_gemm_persistent(
             _p(x), _p(w), _p(out), _p(bias), _p(residual), T, N, K, x.stride(0), w.stride(0), out.stride(0),
@@ -194,7 +191,7 @@ def gated_linear(x, w_gate_up, act="silu", out=None, splits=0, bn=0, rms_eps=0.0
         out = torch.empty(T, inter, dtype=x.dtype, device=x.device)
     if T == 0:
         return out
-    if rms_eps <= 0 and _PERSISTENT_GEMM and T >= _PERSISTENT_MIN_T and splits == 0 and bn == 0:
+    if rms_eps <= 0 and _PERSISTENT_GEMM and T >= _PERSISTENT_MIN_T and splits == 0 and bn == 0 and inter % 8 == 0:
         rc = _lib.kernels().fi_dense_gemm_persistent(
             _p(x), _p(w_gate_up), _p(out), None, None, T, inter, K, x.stride(0), w_gate_up.stride(0), out.stride(0),
             _ACT[act], inter, _DT[x.dtype], _p(status_word(x.device)), _stream())
