@@ -498,3 +498,55 @@ def test_persistent_prefill_gemm(T, N, K, mode):
     ops.check_status(dev)
     err = (got.float() - want).abs().max().item()
     assert err < 0.03 * max(1.0, want.abs().max().item()), err
+
+
+def test_fused_collective_epilogue_loopback_world1():
+    """The collective epilogue of the tcgen05 GEMMs on ONE GPU (world size 1, the rank is its own and
+    only peer): all three transfer formats of GEMM->all-reduce and the reduce-scatter form must equal
+    GEMM + residual.  Covers the tile/flag/epoch logic without NVLink."""
+    import os
+    import torch.distributed as dist
+    from litevllm_b200.parallel import fused_ops, state as pstate
+    from litevllm_b200.parallel.symm import SymmetricHeap
+    dev = torch.device(DEV, 0)
+    created = False
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29671")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+        created = True
+    saved = pstate._STATE
+    heap = None
+    try:
+        st = pstate.ParallelState(rank=0, world_size=1, tp_size=1, ep_size=1, local_rank=0, comm_backend="fused",
+                                  group=dist.group.WORLD)
+        pstate._STATE = st
+        heap = st.symm = SymmetricHeap(0, 1, dev, recv_bytes=64 << 20, xbuf_bytes=8 << 20)
+
+        class L:
+            quant_method, bias = None, None
+
+        g = torch.Generator(device=dev).manual_seed(21)
+        for T, N, K in [(32, 512, 256), (300, 384, 320), (1024, 256, 128)]:
+            x = (torch.randn(T, K, generator=g, device=dev) * 0.5).bfloat16()
+            w = (torch.randn(N, K, generator=g, device=dev) * 0.05).bfloat16()
+            res = torch.randn(T, N, generator=g, device=dev).bfloat16()
+            want = x.float() @ w.float().t() + res.float()
+            layer = L()
+            layer.weight, layer.out_features = w, N
+            for mode in ([2, 0] if T <= 256 else [1]):
+                for _ in range(2):      # both slab parities
+                    got = fused_ops._fused_gemm_allreduce(layer, x, res, None, heap, mode)
+                _close(got.float(), want, 3e-2, 3e-2, f"loopback all-reduce T{T} mode{mode}")
+            if T % 128 == 0:
+                got = fused_ops.gemm_reduce_scatter(x, w, res, T)
+                _close(got.float(), want, 3e-2, 3e-2, f"loopback reduce-scatter T{T}")
+        torch.cuda.synchronize()
+        ops.check_status(dev)
+        assert heap.epoch_value() > 0
+    finally:
+        pstate._STATE = saved
+        if heap is not None:
+            heap.close()
+        if created:
+            dist.destroy_process_group()
