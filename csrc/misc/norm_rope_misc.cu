@@ -422,8 +422,11 @@ extern "C" int fi_rmsnorm(const void* x, void* residual, const void* w, void* ou
           (const T*)x, (T*)residual, (const T*)w, (T*)out, rows, H, ldx, ldo, eps, w_mode,
           out_scale, (const T*)addend);
     } else {
-      int threads = H / 8;
-      threads = threads > 1024 ? 1024 : ((threads + 31) / 32) * 32;
+      // few rows (decode): one 16-byte chunk per thread for the shortest latency; many rows (prefill):
+      // four chunks per thread, so a quarter of the threads keeps four times the bytes in flight per
+      // thread and more rows are resident per SM
+      int threads = rows >= 512 ? H / 32 : H / 8;
+      threads = threads > 1024 ? 1024 : (threads < 64 ? 64 : ((threads + 31) / 32) * 32);
       fi::launch_kernel(rmsnorm_kernel<T, false>, dim3(rows), dim3(threads), 0, FI_STREAM(stream), 0, 
           (const T*)x, (T*)residual, (const T*)w, (T*)out, rows, H, ldx, ldo, eps, w_mode,
           out_scale, (const T*)addend);
