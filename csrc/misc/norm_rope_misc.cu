@@ -226,6 +226,58 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ p
   }
 }
 
+// Fast path of the rotary + cache kernel for the common case (full-width rotary, no q/k/v norms, one
+// position stream, 16-bit cache): every thread moves 8 low and 8 high channels of a head with 16-byte
+// accesses (the general kernel walks single channels).
+template <typename T>
+__global__ void rope_cache_vec_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                      const float* __restrict__ cos_sin, const int* __restrict__ slot_mapping,
+                                      T* __restrict__ k_cache, T* __restrict__ v_cache, int nh, int nkv, int hd,
+                                      int block_size) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  const int t = blockIdx.x;
+  T* row = qkv + static_cast<long>(t) * (nh + 2 * nkv) * hd;
+  const int slot = slot_mapping ? slot_mapping[t] : -1;
+  const int half = hd >> 1, cph = half >> 3;          // 8-channel chunks per half head
+  const float* cs = cos_sin + static_cast<long>(positions[t]) * hd;
+  const long blk = slot >= 0 ? slot / block_size : 0, off = slot >= 0 ? slot % block_size : 0;
+  const int n_rot = (nh + nkv) * cph;
+  for (int item = threadIdx.x; item < n_rot; item += blockDim.x) {
+    const int h = item / cph, c = item - h * cph;
+    T* x = row + static_cast<long>(h) * hd;
+    uint4 lo = *reinterpret_cast<const uint4*>(x + c * 8);
+    uint4 hi = *reinterpret_cast<const uint4*>(x + half + c * 8);
+    const float4 c0 = *reinterpret_cast<const float4*>(cs + c * 8), c1 = *reinterpret_cast<const float4*>(cs + c * 8 + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(cs + half + c * 8), s1 = *reinterpret_cast<const float4*>(cs + half + c * 8 + 4);
+    const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    T* le = reinterpret_cast<T*>(&lo);
+    T* he = reinterpret_cast<T*>(&hi);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float a = Cvt<T>::to_f(le[j]), b = Cvt<T>::to_f(he[j]);
+      le[j] = Cvt<T>::from_f(a * cc[j] - b * sn[j]);
+      he[j] = Cvt<T>::from_f(b * cc[j] + a * sn[j]);
+    }
+    *reinterpret_cast<uint4*>(x + c * 8) = lo;
+    *reinterpret_cast<uint4*>(x + half + c * 8) = hi;
+    if (h >= nh && slot >= 0) {
+      T* dst = k_cache + ((blk * nkv + (h - nh)) * block_size + off) * hd;
+      *reinterpret_cast<uint4*>(dst + c * 8) = lo;
+      *reinterpret_cast<uint4*>(dst + half + c * 8) = hi;
+    }
+  }
+  if (slot >= 0) {
+    const int cpv = hd >> 3;
+    for (int item = threadIdx.x; item < nkv * cpv; item += blockDim.x) {
+      const int h = item / cpv, c = item - h * cpv;
+      const uint4 v = *reinterpret_cast<const uint4*>(row + static_cast<long>(nh + nkv + h) * hd + c * 8);
+      *reinterpret_cast<uint4*>(v_cache + ((blk * nkv + h) * block_size + off) * hd + c * 8) = v;
+    }
+  }
+}
+
 // Plain cache write (no rotation): k/v rows [T, nkv, hd] with row pitch ld -> paged cache.
 template <typename T>
 __global__ void reshape_and_cache_kernel(const T* __restrict__ k, const T* __restrict__ v,
@@ -444,6 +496,14 @@ extern "C" int fi_rope_cache(void* qkv, const int* positions, const float* cos_s
   if (T <= 0) return 0;
   return dispatch_dtype(dtype, [&](auto* tag) {
     using Tt = std::remove_pointer_t<decltype(tag)>;
+    if (qk_norm_mode < 0 && !v_norm && rot_dim == hd && freq_stream == nullptr && !kv_fp8 && hd % 16 == 0 &&
+        (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 && (reinterpret_cast<uintptr_t>(cos_sin) & 15) == 0) {
+      const int items = (nh + nkv) * (hd / 16);
+      const int threads = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
+      fi::launch_kernel(rope_cache_vec_kernel<Tt>, dim3(T), dim3(threads), 0, FI_STREAM(stream), 0, (Tt*)qkv, positions,
+                        cos_sin, slot_mapping, (Tt*)k_cache, (Tt*)v_cache, nh, nkv, hd, block_size);
+      return static_cast<int>(cudaGetLastError());
+    }
     int warps = nh + 2 * nkv;
     if (warps > 16) warps = 16;
     fi::launch_kernel(rope_cache_kernel<Tt>, dim3(T), dim3(warps * 32), 0, FI_STREAM(stream), 0, 
