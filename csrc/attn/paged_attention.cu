@@ -17,6 +17,8 @@
 #include <cuda_runtime.h>
 
 #include "../common/launch.cuh"
+#include "paged_attention_noalloc.h"
+#include <atomic>
 #include <math_constants.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -774,22 +776,16 @@ int launch_decode(const AttnParams& p, int B, cudaStream_t s) {
     const int merge_bytes = (4 * 16 * HD + 4 * 16 * 2) * 4;
     const int smem = 16 * HD * 2 + (pipe_bytes > merge_bytes ? pipe_bytes : merge_bytes);
     auto kern = paged_decode_v2_kernel<T, HD, NST>;
-    static int cfg_bytes = 0;
-    if (smem > cfg_bytes) {
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      cfg_bytes = smem;
-    }
+    cudaError_t ce = fi::ensure_dynamic_smem(kern, smem);
+    if (ce != cudaSuccess) return static_cast<int>(ce);
     fi::launch_kernel(kern, dim3(p.splits, p.nkv * groups, B), dim3(128), smem, s, 0, p);
   } else {
     const int kv_bytes = (16 * HD + 4 * 64 * HD) * 2;
     const int merge_bytes = (4 * 16 * HD + 4 * 16 * 2) * 4 + 16 * HD * 2;
     const int smem = kv_bytes > merge_bytes ? kv_bytes : merge_bytes;
     auto kern = paged_decode_kernel<T, HD>;
-    static bool cfg = false;
-    if (!cfg) {
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      cfg = true;
-    }
+    cudaError_t ce = fi::ensure_dynamic_smem(kern, smem);
+    if (ce != cudaSuccess) return static_cast<int>(ce);
     fi::launch_kernel(kern, dim3(p.splits, p.nkv * groups, B), dim3(128), smem, s, 0, p);
   }
   const bool merged_in_kernel = p.merge_tickets != nullptr && p.block_size % 16 == 0;
@@ -802,11 +798,8 @@ template <typename T, int HD, int CH>
 int launch_prefill(const AttnParams& p, int B, int max_q_len, cudaStream_t s) {
   const int smem = (64 * HD + 4 * CH * HD) * 2;
   auto kern = paged_prefill_kernel<T, HD, CH>;
-  static bool cfg = false;
-  if (!cfg) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    cfg = true;
-  }
+  cudaError_t ce = fi::ensure_dynamic_smem(kern, smem);
+  if (ce != cudaSuccess) return static_cast<int>(ce);
   fi::launch_kernel(kern, dim3((max_q_len + 63) / 64, p.nh, B), dim3(128), smem, s, 0, p);
   return static_cast<int>(cudaGetLastError());
 }
@@ -821,7 +814,7 @@ extern "C" int fi_paged_decode(const void* q, long q_stride, const void* k_cache
                                float sm_scale, float softcap, int kv_fp8, float k_scale,
                                float v_scale, int splits, int dtype, void* stream) {
   if (B <= 0) return 0;
-  if (nh % nkv != 0 || splits < 1) return -10;
+  if (nkv <= 0 || nh <= 0 || nh % nkv != 0 || splits < 1) return -10;
   AttnParams p = {};
   p.q = q; p.q_stride = q_stride; p.k_cache = k_cache; p.v_cache = v_cache; p.out = out;
   p.block_tables = block_tables; p.seq_lens = seq_lens; p.cu_q = nullptr; p.ws_o = ws_o;
@@ -853,7 +846,7 @@ extern "C" int fi_paged_decode_merged(const void* q, long q_stride, const void* 
                                float sm_scale, float softcap, int kv_fp8, float k_scale,
                                float v_scale, int splits, int dtype, void* stream) {
   if (B <= 0) return 0;
-  if (nh % nkv != 0 || splits < 1) return -10;
+  if (nkv <= 0 || nh <= 0 || nh % nkv != 0 || splits < 1) return -10;
   AttnParams p = {};
   p.q = q; p.q_stride = q_stride; p.k_cache = k_cache; p.v_cache = v_cache; p.out = out;
   p.block_tables = block_tables; p.seq_lens = seq_lens; p.cu_q = nullptr; p.ws_o = ws_o;
@@ -882,7 +875,7 @@ extern "C" int fi_paged_prefill(const void* q, long q_stride, const void* k_cach
                                 float sm_scale, float softcap, int kv_fp8, float k_scale,
                                 float v_scale, int dtype, void* stream) {
   if (B <= 0 || max_q_len <= 0) return 0;
-  if (nh % nkv != 0) return -10;
+  if (nkv <= 0 || nh <= 0 || nh % nkv != 0) return -10;
   AttnParams p = {};
   p.q = q; p.q_stride = q_stride; p.k_cache = k_cache; p.v_cache = v_cache; p.out = out;
   p.block_tables = block_tables; p.seq_lens = seq_lens; p.cu_q = cu_q; p.max_blocks = max_blocks;
@@ -911,8 +904,9 @@ extern "C" int fi_paged_prefill(const void* q, long q_stride, const void* k_cach
 // synchronises.  For them the partials live in the fixed device array below, which every GPU that
 // loads this library holds until the process exits.
 //
-// * Capacity: kNoAllocScratchFloats floats (8 MiB).  A call needs B * nh * splits * (hd + 2) floats;
-//   a larger request is refused with -20 and a message on stderr, nothing is launched.
+// * Capacity: kNoAllocScratchFloats floats (8 MiB).  A call with splits > 1 needs
+//   B * nh * splits * (hd + 2) floats; a larger request is refused with -20 and a message on stderr,
+//   nothing is launched.  With splits == 1 there are no partials and no limit applies.
 // * The first call on each device looks up the array's device address (cudaGetSymbolAddress with
 //   that device current) and caches it; make that first call before any stream capture begins.
 // * Every call reuses the same array and leaves its partials behind.  Nothing has to start at zero:
@@ -923,7 +917,7 @@ namespace {
 constexpr size_t kNoAllocScratchFloats = 2u * 1024u * 1024u;
 static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
 constexpr int kMaxDevices = 64;
-float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+std::atomic<float*> g_noalloc_ptr[kMaxDevices];   // zero-initialised; one slot per device, written once
 }  // namespace
 
 extern "C" int fi_paged_decode_noalloc(const void* q, long q_stride, const void* k_cache,
@@ -933,7 +927,11 @@ extern "C" int fi_paged_decode_noalloc(const void* q, long q_stride, const void*
                                        float softcap, int kv_fp8, float k_scale, float v_scale,
                                        int splits, int dtype, void* stream) {
   if (B <= 0) return 0;
-  if (splits < 1 || nh <= 0 || hd <= 0) return -10;
+  if (splits < 1 || nh <= 0 || nkv <= 0 || hd <= 0 || nh % nkv != 0) return -10;
+  if (splits == 1)   // one split writes straight to `out`: no partials, so no scratch and no size limit
+    return fi_paged_decode(q, q_stride, k_cache, v_cache, out, block_tables, seq_lens, nullptr, nullptr, B,
+                           nh, nkv, hd, max_blocks, block_size, window, sm_scale, softcap, kv_fp8,
+                           k_scale, v_scale, 1, dtype, stream);
   const size_t n_o = static_cast<size_t>(B) * nh * splits * hd;
   const size_t n_ml = static_cast<size_t>(B) * nh * splits * 2;
   if (n_o + n_ml > kNoAllocScratchFloats) {
@@ -947,14 +945,16 @@ extern "C" int fi_paged_decode_noalloc(const void* q, long q_stride, const void*
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return static_cast<int>(e);
   if (dev < 0 || dev >= kMaxDevices) return -21;
-  if (g_noalloc_ptr[dev] == nullptr) {
+  float* ws_o = g_noalloc_ptr[dev].load(std::memory_order_acquire);
+  if (ws_o == nullptr) {
     // In host code the array's name is only a handle; the kernel needs its address on this device.
+    // Two threads racing here resolve the same address, so the duplicate store is harmless.
     float* p = nullptr;
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch);
     if (e != cudaSuccess || p == nullptr) return e != cudaSuccess ? static_cast<int>(e) : -22;
-    g_noalloc_ptr[dev] = p;
+    g_noalloc_ptr[dev].store(p, std::memory_order_release);
+    ws_o = p;
   }
-  float* ws_o = g_noalloc_ptr[dev];
   float* ws_ml = ws_o + n_o;
   return fi_paged_decode(q, q_stride, k_cache, v_cache, out, block_tables, seq_lens, ws_o, ws_ml, B,
                          nh, nkv, hd, max_blocks, block_size, window, sm_scale, softcap, kv_fp8,

@@ -7,8 +7,9 @@
 // memory budget is already fully committed to the KV pool) can still use split-KV decode.
 //
 // Limits and rules
-//   * B * nh * splits * (hd + 2) must not exceed 2 * 1024 * 1024 floats; otherwise the call returns
-//     -20, prints the reason to stderr and launches nothing.
+//   * With splits > 1, B * nh * splits * (hd + 2) must not exceed 2 * 1024 * 1024 floats; otherwise the
+//     call returns -20, prints the reason to stderr and launches nothing.  With splits == 1 the kernel
+//     writes straight to `out`, needs no scratch, and no size limit applies.
 //   * The first call on a device resolves the array's device address; make it before any stream
 //     capture starts on that device.
 //   * All calls share the array; calls that overlap on the GPU race.  The array keeps the previous

@@ -8,7 +8,10 @@
 // since every kernel waits, completion is transitive along the stream.  Works inside CUDA graphs.
 #pragma once
 #include <cuda_runtime.h>
+#include <cstdint>
 #include <cstdlib>
+#include <mutex>
+#include <unordered_map>
 
 namespace fi {
 
@@ -25,6 +28,25 @@ inline bool use_pdl() {
     return v == nullptr || v[0] == '\0' || v[0] != '0';
   }();
   return on;
+}
+
+// Opt a kernel in to `bytes` of dynamic shared memory on the CURRENT device.  The attribute belongs
+// to the (kernel, device) pair, so the record is kept per pair: a process that drives several GPUs
+// sets it once on each.  Thread safe; the fast path is one hash lookup under a mutex.
+template <typename K>
+inline cudaError_t ensure_dynamic_smem(K kernel, int bytes) {
+  static std::mutex mu;
+  static std::unordered_map<uint64_t, int> done;   // (kernel address, device) -> bytes configured
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const uint64_t key = (static_cast<uint64_t>(reinterpret_cast<uintptr_t>(kernel)) << 6) ^ static_cast<uint64_t>(dev);
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = done.find(key);
+  if (it != done.end() && it->second >= bytes) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done[key] = bytes;
+  return e;
 }
 
 // Launch with optional cluster size along z and the PDL attribute.

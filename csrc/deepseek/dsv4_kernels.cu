@@ -189,11 +189,7 @@ extern "C" int fi_dsv4_indexer_scores(const float* q, const float* w, const floa
   if (n_rows <= 0) return 0;
   const size_t smem = static_cast<size_t>(H) * 129 * sizeof(float);
   if (smem > 200 * 1024) return -10;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(indexer_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    attr_set = true;
-  }
+  if (cudaError_t e = fi::ensure_dynamic_smem(indexer_scores_kernel, 200 * 1024); e != cudaSuccess) return static_cast<int>(e);
   const int blocks = n_rows < 8 * 148 ? (n_rows + 7) / 8 : 148;
   fi::launch_kernel(indexer_scores_kernel, dim3(blocks), dim3(256), smem, FI_STREAM(stream), 0, q, w, rows, n_rows, H,
                     scale, out);

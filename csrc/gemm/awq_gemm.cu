@@ -350,12 +350,10 @@ int launch(const CUtensorMap& tw, const TokenMaps& tx, GemmParams p, cudaStream_
   constexpr int smem = smem_bytes<BN, RST, AST, DUAL>();
   constexpr int ring = ring_bytes<BN, RST, AST, DUAL>();
   static_assert(BN * BM * 4 <= ring, "fp32 staging tile must fit inside the rings");
-  static bool configured = false;
   static int max_active[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  {
+    cudaError_t e = fi::ensure_dynamic_smem(kern, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
   }
   const int tiles = ((p.N + BM - 1) / BM) * ((p.T + BN - 1) / BN);
   const int kb_total = (p.K + BK - 1) / BK;

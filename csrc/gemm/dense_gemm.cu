@@ -290,11 +290,9 @@ int launch(const CUtensorMap& tw, const TokenMaps& tx, GemmParams p, cudaStream_
   constexpr int smem = smem_bytes<BN, STAGES, DUAL>();
   constexpr int ring = STAGES * (BM * 128 * (DUAL ? 2 : 1) + BN * 128);
   static_assert(BN * BM * 4 <= ring, "fp32 staging tile must fit inside the pipeline ring");
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  {
+    cudaError_t e = fi::ensure_dynamic_smem(kern, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
   }
   if (p.splits <= 0) p.splits = pick_splits<BN, STAGES, DUAL>(p, smem);
   if (BN * BM * 4 * ((DUAL && p.splits > 1) ? 2 : 1) > ring) return -12;

@@ -287,11 +287,9 @@ template <int STAGES, bool DUAL>
 int launch(const CUtensorMap& tw, const CUtensorMap& tx, const PParams& p, cudaStream_t stream) {
   auto kern = dense_gemm_persistent_kernel<STAGES, DUAL>;
   constexpr int smem = STAGES * (BM * 128 * (DUAL ? 2 : 1) + BN * 128) + (2 * STAGES + 4) * 8 + 16 + 4 * 16 * 32 * 4 + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  {
+    cudaError_t e = fi::ensure_dynamic_smem(kern, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
   }
   static int sms = 0;
   if (sms == 0) {

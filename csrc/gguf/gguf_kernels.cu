@@ -419,12 +419,12 @@ extern "C" int fi_gguf_gemv(const void* x, long ldx, const void* raw, long row_s
       const size_t smem = x_bytes + static_cast<size_t>(kGemvWarps) * kGemvDepth * Chunk<TY>::kBuf;
       if (dtype == 0) {
         auto k = gemv_stream_kernel<TY, __nv_bfloat16>;
-        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 223 * 1024);   // + static tables <= 227 KB
+        fi::ensure_dynamic_smem(k, 223 * 1024);   // + static tables <= 227 KB
         fi::launch_kernel(k, dim3(grid), dim3(kGemvWarps * 32), smem, FI_STREAM(stream), 0, (const __nv_bfloat16*)x, ldx,
                           r, row_stride, M, N, K, out, ldo, (const __nv_bfloat16*)residual, out_fp32);
       } else {
         auto k = gemv_stream_kernel<TY, __half>;
-        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 223 * 1024);   // + static tables <= 227 KB
+        fi::ensure_dynamic_smem(k, 223 * 1024);   // + static tables <= 227 KB
         fi::launch_kernel(k, dim3(grid), dim3(kGemvWarps * 32), smem, FI_STREAM(stream), 0, (const __half*)x, ldx, r,
                           row_stride, M, N, K, out, ldo, (const __half*)residual, out_fp32);
       }
@@ -436,12 +436,12 @@ extern "C" int fi_gguf_gemv(const void* x, long ldx, const void* raw, long row_s
   FI_TYPE_SWITCH(type, {
     if (dtype == 0) {
       auto k = gemv_kernel<TY, __nv_bfloat16>;
-      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      fi::ensure_dynamic_smem(k, 200 * 1024);
       fi::launch_kernel(k, dim3((N + wpb - 1) / wpb), dim3(wpb * 32), smem, FI_STREAM(stream), 0,
                         (const __nv_bfloat16*)x, ldx, r, row_stride, M, N, K, out, ldo, (const __nv_bfloat16*)residual, out_fp32);
     } else {
       auto k = gemv_kernel<TY, __half>;
-      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      fi::ensure_dynamic_smem(k, 200 * 1024);
       fi::launch_kernel(k, dim3((N + wpb - 1) / wpb), dim3(wpb * 32), smem, FI_STREAM(stream), 0,
                         (const __half*)x, ldx, r, row_stride, M, N, K, out, ldo, (const __half*)residual, out_fp32);
     }
@@ -465,7 +465,7 @@ extern "C" int fi_gguf_moe_gate_up(const void* x, long ldx, const void* gate, co
   const uint8_t* u = static_cast<const uint8_t*>(up);
   const long sg = row_stride_g * I, su = row_stride_u * I;
 #define FI_GU(TG, TU)                                                                                          \
-  cudaFuncSetAttribute(moe_gate_up_kernel<TG, TU, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+  fi::ensure_dynamic_smem(moe_gate_up_kernel<TG, TU, __nv_bfloat16>, 200 * 1024); \
   fi::launch_kernel(moe_gate_up_kernel<TG, TU, __nv_bfloat16>, grid, dim3(wpb * 32), smem, FI_STREAM(stream), 0, \
                     (const __nv_bfloat16*)x, ldx, g, u, sg, su, row_stride_g, row_stride_u, ids, top_k, e_lo,  \
                     e_hi, I, K, clamp, (__nv_bfloat16*)a)
@@ -490,7 +490,7 @@ extern "C" int fi_gguf_moe_down(const void* a, const void* down, int type_d, lon
   const uint8_t* d = static_cast<const uint8_t*>(down);
   const long sd = row_stride * H;
   FI_TYPE_SWITCH(type_d, {
-    cudaFuncSetAttribute(moe_down_kernel<TY, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    fi::ensure_dynamic_smem(moe_down_kernel<TY, __nv_bfloat16>, 200 * 1024);
     fi::launch_kernel(moe_down_kernel<TY, __nv_bfloat16>, grid, dim3(wpb * 32), smem, FI_STREAM(stream), 0,
                       (const __nv_bfloat16*)a, d, sd, row_stride, ids, e_lo, e_hi, H, I, (__nv_bfloat16*)y);
   });

@@ -11,6 +11,7 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <new>
 #include <string>
 #include <vector>
 
@@ -43,14 +44,15 @@ struct Cursor {
   bool ok = true;
   template <typename T> T get() {
     T v{};
-    if (p + sizeof(T) > end) { ok = false; return v; }
+    if (!ok || sizeof(T) > static_cast<size_t>(end - p)) { ok = false; return v; }
     memcpy(&v, p, sizeof(T));
     p += sizeof(T);
     return v;
   }
   std::string str() {
     uint64_t n = get<uint64_t>();
-    if (!ok || p + n > end) { ok = false; return ""; }
+    // sizes are compared, never pointers: a length near 2^64 must not wrap `p + n` past `end`
+    if (!ok || n > static_cast<uint64_t>(end - p)) { ok = false; return ""; }
     std::string s(reinterpret_cast<const char*>(p), n);
     p += n;
     return s;
@@ -127,8 +129,25 @@ uint64_t type_nbytes(uint32_t type, uint64_t n_elems) {
 
 extern "C" {
 
+static void* gguf_open_impl(const char* path, char* err, int err_cap, Gguf* g);
+
+// The file is untrusted input: every size in it is checked with overflow-aware arithmetic and no C++
+// exception (a huge length reaching std::string, a failed reserve) may cross this C boundary.
 void* fi_gguf_open(const char* path, char* err, int err_cap) {
-  Gguf* g = new Gguf();
+  Gguf* g = new (std::nothrow) Gguf();
+  if (g == nullptr) return nullptr;
+  try {
+    return gguf_open_impl(path, err, err_cap, g);
+  } catch (...) {
+    if (err && err_cap > 0) snprintf(err, err_cap, "%s", "malformed GGUF file (allocation or length error while parsing)");
+    if (g->base) munmap(g->base, g->size);
+    if (g->fd >= 0) close(g->fd);
+    delete g;
+    return nullptr;
+  }
+}
+
+static void* gguf_open_impl(const char* path, char* err, int err_cap, Gguf* g) {
   auto fail = [&](const char* msg) -> void* {
     if (err && err_cap > 0) snprintf(err, err_cap, "%s", msg);
     if (g->base) munmap(g->base, g->size);
@@ -149,7 +168,9 @@ void* fi_gguf_open(const char* path, char* err, int err_cap) {
   if (g->version != 3) return fail("only GGUF version 3 is supported");
   const uint64_t n_tensors = c.get<uint64_t>();
   const uint64_t n_kv = c.get<uint64_t>();
-  if (n_tensors > (1u << 24) || n_kv > (1u << 20)) return fail("implausible header counts");
+  // a directory entry takes at least 32 bytes and a key/value at least 13, so the file size bounds both
+  if (n_tensors > (1u << 24) || n_kv > (1u << 20) || n_tensors > g->size / 32 || n_kv > g->size / 13)
+    return fail("implausible header counts");
   g->meta_json = "{";
   for (uint64_t i = 0; i < n_kv; ++i) {
     std::string key = c.str();
@@ -177,7 +198,12 @@ void* fi_gguf_open(const char* path, char* err, int err_cap) {
     if (!c.ok || t.n_dims == 0 || t.n_dims > 4) return fail("bad tensor rank");
     uint64_t n = 1;
     for (uint32_t d = 0; d < 4; ++d) t.dims[d] = 1;
-    for (uint32_t d = 0; d < t.n_dims; ++d) { t.dims[d] = c.get<uint64_t>(); n *= t.dims[d]; }
+    bool overflow = false;
+    for (uint32_t d = 0; d < t.n_dims; ++d) {
+      t.dims[d] = c.get<uint64_t>();
+      overflow |= __builtin_mul_overflow(n, t.dims[d], &n);
+    }
+    if (overflow || n > (1ull << 48)) return fail("tensor element count overflows");
     t.type = c.get<uint32_t>();
     t.offset = c.get<uint64_t>();
     if (!c.ok) return fail("truncated tensor directory");
@@ -189,7 +215,10 @@ void* fi_gguf_open(const char* path, char* err, int err_cap) {
   g->data_start = (pos + g->alignment - 1) / g->alignment * g->alignment;
   for (const auto& t : g->tensors) {
     if (t.offset % g->alignment != 0) return fail("tensor offset is not aligned");
-    if (g->data_start + t.offset + t.nbytes > g->size) return fail("tensor payload runs past the end of the file");
+    uint64_t end_off = 0;
+    if (__builtin_add_overflow(g->data_start, t.offset, &end_off) ||
+        __builtin_add_overflow(end_off, t.nbytes, &end_off) || end_off > g->size)
+      return fail("tensor payload runs past the end of the file");
   }
   return g;
 }

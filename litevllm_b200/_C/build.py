@@ -2,8 +2,8 @@
 ``libfi_kernels.so``; every ``csrc/host/*.cpp`` is compiled with g++ into ``libfi_host.so``.
 
 The libraries expose ``extern "C"`` entry points taking raw device pointers and a stream, so they
-are bound with ``ctypes`` and never allocate device memory themselves.  Object files are cached by
-source mtime + flags so repeated builds are cheap.
+are bound with ``ctypes`` and never allocate device memory themselves.  Object files are cached by a
+hash of the source, every header under ``csrc/`` and the flags, so repeated builds are cheap.
 """
 from __future__ import annotations
 
@@ -37,7 +37,11 @@ def _nvcc() -> str:
 def _stamp(src: Path, flags: list[str]) -> str:
     h = hashlib.sha1()
     h.update(src.read_bytes())
-    for inc in sorted((CSRC / "common").glob("*")):
+    # every header of the tree: a .cu file may include headers from any directory (the shared GEMM
+    # epilogue, the collective descriptor, codebook tables), and a stale object would silently keep the
+    # old struct layouts
+    for inc in sorted(p for p in CSRC.rglob("*") if p.suffix in (".h", ".cuh", ".hpp", ".inc")):
+        h.update(str(inc.relative_to(CSRC)).encode())
         h.update(inc.read_bytes())
     h.update(" ".join(flags).encode())
     return h.hexdigest()[:16]

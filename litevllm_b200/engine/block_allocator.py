@@ -1,8 +1,8 @@
 """Paged-KV block id allocator.  Ids 1..N-1 are allocatable; id 0 is the permanent null block that
 pads block tables and is never written (reference: vllm/engine/block_allocator.py:8-49).
 
-The hot path (alloc/free of a handful of ids per step) runs in the C++ host library when it is
-built (csrc/host/block_allocator.cpp); the Python deque version below has identical behaviour.
+A step allocates or frees a handful of ids, so a deque plus a set is all this needs; the block
+tables themselves live on the device (``kv_block_manager``).
 """
 from __future__ import annotations
 

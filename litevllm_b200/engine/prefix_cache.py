@@ -18,18 +18,63 @@ class PrefixEntry:
     nbytes: int
 
 
-def _namespace(st) -> str:
+def _content_digest(h, value) -> None:
+    """Feed the full content of one multimodal value into ``h``.  Two requests may share a cache entry
+    only if their images are byte-identical: a type name, a ``repr`` (which holds a memory address) or
+    the first bytes of a data URL (JPEG headers and quantisation tables repeat) do not identify an image."""
+    if value is None or isinstance(value, (bool, int, float)):
+        h.update(repr(value).encode())
+    elif isinstance(value, str):
+        h.update(b"s")
+        h.update(value.encode("utf-8", "surrogatepass"))
+    elif isinstance(value, (bytes, bytearray, memoryview)):
+        h.update(b"b")
+        h.update(bytes(value))
+    elif isinstance(value, (list, tuple)):
+        h.update(f"l{len(value)}".encode())
+        for item in value:
+            _content_digest(h, item)
+    elif isinstance(value, dict):
+        h.update(f"d{len(value)}".encode())
+        for k in sorted(value, key=str):
+            h.update(str(k).encode())
+            _content_digest(h, value[k])
+    elif hasattr(value, "tobytes") and hasattr(value, "size") and hasattr(value, "mode"):   # PIL image
+        h.update(f"pil{value.size}{value.mode}".encode())
+        h.update(value.tobytes())
+    elif hasattr(value, "detach") and hasattr(value, "cpu"):                                   # torch tensor
+        import torch
+        t = value.detach().cpu().contiguous()
+        h.update(f"t{tuple(t.shape)}{t.dtype}".encode())
+        h.update(t.reshape(-1).view(torch.uint8).numpy().tobytes())
+    elif hasattr(value, "tobytes") and hasattr(value, "shape"):                                # numpy array
+        h.update(f"n{tuple(value.shape)}{getattr(value, 'dtype', '')}".encode())
+        h.update(value.tobytes())
+    else:
+        raise TypeError(f"cannot identify multimodal content of type {type(value).__name__}")
+
+
+def _namespace(st) -> str | None:
+    """Cache namespace of a request: digest of its multimodal content plus its LoRA name.  ``None``
+    means the content could not be identified and the request must bypass the cache."""
     mm = st.multi_modal_data
     if not mm:
         ns = ""
     else:
-        h = hashlib.sha1()
-        for k in sorted(mm):
-            h.update(repr((k, mm[k] if isinstance(mm[k], (str, int)) else str(type(mm[k])))).encode())
-            if isinstance(mm[k], (list, tuple)):
-                for item in mm[k]:
-                    h.update(str(item)[:256].encode())
-        ns = h.hexdigest()
+        ns = getattr(st, "_mm_digest", False)      # hashed once per request: images can be megabytes
+        if ns is False:
+            h = hashlib.sha1()
+            try:
+                _content_digest(h, mm)
+                ns = h.hexdigest()
+            except Exception:
+                ns = None
+            try:
+                st._mm_digest = ns
+            except AttributeError:
+                pass
+        if ns is None:
+            return None
     lora = getattr(st.lora_request, "lora_name", "") if st.lora_request is not None else ""
     return f"{ns}|{lora}"
 
@@ -51,12 +96,16 @@ class PrefixCache:
         return (_namespace(st), *st.prompt_token_ids[:n])
 
     def contains(self, st, n: int) -> bool:
-        return self._key(st, n) in self._entries
+        key = self._key(st, n)
+        return key[0] is None or key in self._entries      # unidentifiable content: never stored, so report "present"
 
     def lookup(self, st) -> PrefixEntry | None:
         if not self.enabled:
             return None
         ns = _namespace(st)
+        if ns is None:
+            self.misses += 1
+            return None
         ids = st.prompt_token_ids
         best = None
         for key in self._by_first.get((ns, ids[0]), ()):
@@ -80,6 +129,8 @@ class PrefixCache:
         if nbytes > self.max_bytes:
             return
         key = self._key(st, n)
+        if key[0] is None:
+            return
         self._drop(key)
         e = PrefixEntry(tuple(st.prompt_token_ids[:n]), n, blocks, logits, nbytes)
         self._entries[key] = e

@@ -193,6 +193,39 @@ def test_prefix_cache_longest_match_lru_and_budget():
     assert not PrefixCache(0).enabled
 
 
+def test_prefix_cache_keeps_different_images_apart():
+    """Same prompt ids, same placeholder count, images of equal size but different pixels: the two
+    requests must not share KV blocks or first-token logits."""
+    import base64
+
+    import numpy as np
+    from PIL import Image
+    pc = PrefixCache(max_entries=8, max_bytes=1 << 20)
+    blocks = [(torch.zeros(2, 4), torch.zeros(2, 4))]
+    rng = np.random.default_rng(0)
+    img_a = Image.fromarray(rng.integers(0, 255, (8, 8, 3), dtype=np.uint8))
+    img_b = Image.fromarray(rng.integers(0, 255, (8, 8, 3), dtype=np.uint8))
+    a, b, a2 = _req("a", 32), _req("b", 32), _req("a2", 32)
+    a.multi_modal_data, b.multi_modal_data = {"image": img_a}, {"image": img_b}
+    a2.multi_modal_data = {"image": img_a.copy()}
+    pc.store(a, 32, blocks, torch.ones(4))
+    assert pc.lookup(b) is None
+    assert pc.lookup(a2) is not None                       # byte-identical image: same entry
+    # data URLs with a long common head and a different tail
+    head = base64.b64encode(bytes(600)).decode()
+    u1, u2 = _req("u1", 32), _req("u2", 32)
+    u1.multi_modal_data = {"image": ["data:image/jpeg;base64," + head + "AAAA"]}
+    u2.multi_modal_data = {"image": ["data:image/jpeg;base64," + head + "BBBB"]}
+    pc.store(u1, 32, blocks)
+    assert pc.lookup(u2) is None and pc.lookup(u1) is not None
+    # content that cannot be identified bypasses the cache in both directions
+    odd = _req("odd", 32)
+    odd.multi_modal_data = {"image": object()}
+    n0 = pc.stats()["entries"]
+    pc.store(odd, 32, blocks)
+    assert pc.stats()["entries"] == n0 and pc.lookup(odd) is None
+
+
 def test_generic_moe_activation_layers_and_sniffer_cpu():
     import torch
     from litevllm_b200.debug import ActivationSniffer

@@ -48,6 +48,38 @@ def test_rejects_bad_files(tmp_path):
         GGUFFile(trunc)
 
 
+def _gguf_str(b: bytes) -> bytes:
+    return struct.pack("<Q", len(b)) + b
+
+
+def test_rejects_overflowing_sizes(tmp_path):
+    """Sizes taken from an untrusted file must not wrap a pointer or a 64-bit product."""
+    head = struct.pack("<IIQQ", 0x46554747, 3, 1, 0)
+    # (a) a tensor name whose length field is close to 2^64
+    f = tmp_path / "hugestr.gguf"
+    f.write_bytes(head + struct.pack("<Q", 0xFFFFFFFFFFFFFFF0) + b"x" * 64)
+    with pytest.raises(ValueError):
+        GGUFFile(f)
+    # (b) dims whose product wraps to a small number
+    f = tmp_path / "hugedims.gguf"
+    f.write_bytes(head + _gguf_str(b"a.weight") + struct.pack("<I", 2) + struct.pack("<QQ", 1 << 63, 4) +
+                  struct.pack("<IQ", 0, 0) + b"\0" * 64)
+    with pytest.raises(ValueError, match="overflow"):
+        GGUFFile(f)
+    # (c) offset = UINT64_MAX with alignment 1: data_start + offset + nbytes must not wrap below the file size
+    kv = _gguf_str(b"general.alignment") + struct.pack("<II", 4, 1)
+    f = tmp_path / "hugeoff.gguf"
+    f.write_bytes(struct.pack("<IIQQ", 0x46554747, 3, 1, 1) + kv + _gguf_str(b"a.weight") + struct.pack("<I", 1) +
+                  struct.pack("<Q", 8) + struct.pack("<IQ", 0, 0xFFFFFFFFFFFFFFFF) + b"\0" * 64)
+    with pytest.raises(ValueError, match="past the end"):
+        GGUFFile(f)
+    # (d) a tensor count that the file cannot possibly hold
+    f = tmp_path / "manytensors.gguf"
+    f.write_bytes(struct.pack("<IIQQ", 0x46554747, 3, 1 << 23, 0) + b"\0" * 64)
+    with pytest.raises(ValueError, match="implausible"):
+        GGUFFile(f)
+
+
 def _hf_to_gguf_name(name: str) -> str:
     from litevllm_b200.loaders.gguf import _LAYER_MAP
     if name == "model.embed_tokens.weight":

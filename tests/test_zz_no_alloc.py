@@ -27,7 +27,7 @@ def _call_noalloc(lib, q, kc, vc, out, bt, sl, nh, nkv, hd, scale, splits, windo
 
 def test_noalloc_decode_matches_regular_entry_point():
     from litevllm_b200 import ops
-    from litevllm_b200.ops import _lib
+    from litevllm_b200.ops import _lib, reference
     lib = _lib.kernels()
     assert isinstance(lib, ctypes.CDLL) and hasattr(lib, "fi_paged_decode_noalloc")
     dev = "cuda"
@@ -58,6 +58,13 @@ def test_noalloc_decode_matches_regular_entry_point():
         err = (got.float() - want.float()).abs()
         tol = 2e-2 + 2e-2 * want.float().abs()
         assert bool((err <= tol).all()), f"round {round_idx}: max abs err {float(err.max())}"
+        # second oracle: the plain PyTorch fp32 attention over the same paged cache (the regular entry
+        # point runs the same kernel, so agreeing with it alone would not catch a shared mistake)
+        cu = torch.arange(B + 1, dtype=torch.int32)
+        oracle = reference.paged_attention(q.cpu(), kc.cpu(), vc.cpu(), bt.cpu(), sl.cpu(), cu, nh, nkv, hd, scale,
+                                           0, 0.0, 1.0, 1.0).float()
+        err = (got.float().cpu() - oracle).abs()
+        assert bool((err <= 2e-2 + 2e-2 * oracle.abs()).all()), f"round {round_idx}: vs fp32 oracle {float(err.max())}"
 
 
 def test_noalloc_decode_rejects_oversized_request():
@@ -75,3 +82,34 @@ def test_noalloc_decode_rejects_oversized_request():
                                      splits, 0, torch.cuda.current_stream().cuda_stream)
     assert rc == -20
     torch.cuda.synchronize()
+
+
+def test_noalloc_decode_single_split_has_no_size_limit():
+    """With one split the kernel writes straight to the output and uses no scratch, so a batch whose
+    B * nh * (hd + 2) exceeds the built-in array is still served (short contexts keep it cheap)."""
+    from litevllm_b200 import ops
+    from litevllm_b200.ops import _lib
+    lib = _lib.kernels()
+    dev = "cuda"
+    torch.manual_seed(5)
+    B, nh, nkv, hd, bs = 600, 32, 4, 128, 16
+    assert B * nh * (hd + 2) > 2 * 1024 * 1024
+    scale = 1.0 / math.sqrt(hd)
+    lens = [1 + (i * 7) % 40 for i in range(B)]
+    max_blocks = 3
+    nb = 1 + B * max_blocks
+    kc = (torch.randn(nb, nkv, bs, hd, device=dev) * 0.5).bfloat16()
+    vc = (torch.randn(nb, nkv, bs, hd, device=dev) * 0.5).bfloat16()
+    bt = (1 + torch.arange(B * max_blocks, device=dev, dtype=torch.int32)).view(B, max_blocks).contiguous()
+    q = torch.randn(B, nh * hd, device=dev).bfloat16()
+    sl = torch.tensor(lens, dtype=torch.int32, device=dev)
+    want = ops.paged_attention_decode(q, kc, vc, bt, sl, nh, nkv, hd, scale, splits=1, max_kv_len=max(lens))
+    got = torch.full_like(want, float("nan"))
+    rc = _call_noalloc(lib, q, kc, vc, got, bt, sl, nh, nkv, hd, scale, 1)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert bool(((got.float() - want.float()).abs() <= 2e-2 + 2e-2 * want.float().abs()).all())
+    # bad head counts are an argument error, not a crash on the host
+    assert lib.fi_paged_decode_noalloc(q.data_ptr(), q.stride(0), kc.data_ptr(), vc.data_ptr(), got.data_ptr(),
+                                       bt.data_ptr(), sl.data_ptr(), B, nh, 0, hd, max_blocks, bs, 0, scale, 0.0, 0,
+                                       1.0, 1.0, 2, 0, torch.cuda.current_stream().cuda_stream) == -10
