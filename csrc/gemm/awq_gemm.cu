@@ -466,7 +466,7 @@ static int fi_awq_gemm_impl(const void* X, const void* qw, const void* scales, c
   p.scales = scales; p.zeros = reinterpret_cast<const uint8_t*>(zeros); p.group = group;
   p.n_rows_total = w_rows;
   p.tile_expert = nullptr; p.tile_row0 = nullptr; p.tile_rows = nullptr; p.n_tiles = nullptr; p.expert_rows = 0; p.grid_tiles = 0;
-  p.comm_mode = 0; p.world = 1; p.rank = 0; p.rows_per_rank = 0; p.xfer_16bit = 0; p.trace = nullptr;
+  p.comm_mode = 0; p.world = 1; p.rank = 0; p.rows_per_rank = 0; p.xfer_16bit = 0; p.comm_phases = 0; p.trace = nullptr;
   p.rms_eps = 0.f; p.w_dynamic = 0;
   p.x_full = nullptr; p.ag_flags = nullptr; p.copy_rows = 0;
   p.rope_cs = nullptr; p.rope_pos = nullptr; p.rope_slots = nullptr; p.k_cache = nullptr; p.v_cache = nullptr;
@@ -477,7 +477,7 @@ static int fi_awq_gemm_impl(const void* X, const void* qw, const void* scales, c
     if (comm->world > kMaxRanks || comm->ag_world > kMaxRanks) return -15;
     if (comm->mode != 0 && dual_rows > 0) return -16;   // a gated epilogue needs the full K sum
     p.comm_mode = comm->mode; p.world = comm->world; p.rank = comm->rank;
-    p.rows_per_rank = comm->rows_per_rank; p.xfer_16bit = comm->xfer_16bit;
+    p.rows_per_rank = comm->rows_per_rank; p.xfer_16bit = comm->xfer_16bit; p.comm_phases = comm->phases;
     p.ag_world = comm->ag_world > 1 ? comm->ag_world : 1; p.ag_rows_per_rank = comm->ag_rows_per_rank;
     p.slab_elems = comm->slab_elems;
     p.epoch = reinterpret_cast<unsigned int*>(comm->epoch);
@@ -488,6 +488,8 @@ static int fi_awq_gemm_impl(const void* X, const void* qw, const void* scales, c
     const long tiles = static_cast<long>((N + BM - 1) / BM) * ((T + bn - 1) / bn);
     if (comm->mode != 0 && tiles > kMaxCommTiles) return -18;
     if (comm->mode != 0 && (N % 8) != 0) return -19;
+    // the two-hop all-reduce sends 16-bit results and owns chunks inside a 128-row tile
+    if (comm->xfer_16bit == kXferTwoShot && (comm->mode != kCommAllReduce || out_fp32 || (ldc % 4) != 0)) return -24;
   }
   if (grp != nullptr) {
     if (comm != nullptr && comm->mode != 0) return -20;

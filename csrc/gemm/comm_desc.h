@@ -7,10 +7,12 @@ struct FiComm {
   int world;
   int rank;
   int rows_per_rank;     // reduce-scatter: rows of the output shard (multiple of the token tile)
-  int xfer_16bit;        // 0: fp32 + flags, 1: 16-bit values + flags, 2: fp32 with inline epoch flags (8 B per value)
+  int xfer_16bit;        // 0: fp32 + flags, 1: 16-bit values + flags, 2: fp32 with inline epoch flags (8 B per value),
+                         // 3: two-hop all-reduce (partials to the chunk owner, 16-bit result back), inline epochs
   int ag_world;          // > 1: the token operand is the concatenation of every rank's shard
   int ag_rows_per_rank;  // rows of one token shard
-  int reserved;
+  int phases;            // 0 = whole collective in this launch; else a bit mask (1 push, 2 reduce, 4 collect) for the
+                         // phase-by-phase emulation of several ranks on one GPU
   long slab_elems;       // elements of one (parity, source rank) receive slab
   unsigned long long recv[8];     // receive area of rank d, as mapped into this process
   unsigned long long flags[8];    // flag words of rank d

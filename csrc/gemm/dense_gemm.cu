@@ -380,7 +380,7 @@ static int fi_dense_gemm_impl(const void* X, const void* W, void* C, const void*
   p.dual_rows = dual_rows; p.act = act; p.out_fp32 = out_fp32; p.is_fp16 = dtype == 1;
   p.splits = splits; p.status = status;
   p.tile_expert = nullptr; p.tile_row0 = nullptr; p.tile_rows = nullptr; p.n_tiles = nullptr; p.expert_rows = 0; p.grid_tiles = 0;
-  p.comm_mode = 0; p.world = 1; p.rank = 0; p.rows_per_rank = 0; p.xfer_16bit = 0; p.trace = nullptr;
+  p.comm_mode = 0; p.world = 1; p.rank = 0; p.rows_per_rank = 0; p.xfer_16bit = 0; p.comm_phases = 0; p.trace = nullptr;
   p.rms_eps = rms_eps; p.w_dynamic = w_dynamic;
   p.x_full = nullptr; p.ag_flags = nullptr; p.copy_rows = 0;
   for (int d = 0; d < kMaxRanks; ++d) p.x_peers[d] = 0;
@@ -401,7 +401,7 @@ static int fi_dense_gemm_impl(const void* X, const void* W, void* C, const void*
     if (comm->world > kMaxRanks || comm->ag_world > kMaxRanks) return -15;
     if (comm->mode != 0 && dual_rows > 0) return -16;   // a gated epilogue needs the full K sum
     p.comm_mode = comm->mode; p.world = comm->world; p.rank = comm->rank;
-    p.rows_per_rank = comm->rows_per_rank; p.xfer_16bit = comm->xfer_16bit;
+    p.rows_per_rank = comm->rows_per_rank; p.xfer_16bit = comm->xfer_16bit; p.comm_phases = comm->phases;
     p.ag_world = comm->ag_world > 1 ? comm->ag_world : 1; p.ag_rows_per_rank = comm->ag_rows_per_rank;
     p.slab_elems = comm->slab_elems;
     p.epoch = reinterpret_cast<unsigned int*>(comm->epoch);
@@ -417,6 +417,8 @@ static int fi_dense_gemm_impl(const void* X, const void* W, void* C, const void*
     const long tiles = static_cast<long>((N + BM - 1) / BM) * ((T + bn - 1) / bn);
     if (comm->mode != 0 && tiles > kMaxCommTiles) return -18;
     if (comm->mode != 0 && (N % 8) != 0) return -19;
+    // the two-hop all-reduce sends 16-bit results and owns chunks inside a 128-row tile
+    if (comm->xfer_16bit == kXferTwoShot && (comm->mode != kCommAllReduce || out_fp32 || (ldc % 4) != 0)) return -24;
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (dual_rows > 0) return dispatch<true>(bn, tw, tx, p, s);

@@ -27,6 +27,11 @@ constexpr int kThreads = 192;
 constexpr int kMaxRanks = 8;
 constexpr int kFlagParts = 8;       // flag words per (tile, source rank): one per cluster part
 constexpr int kXferInlineFlags = 2;  // GemmParams::xfer_16bit value: fp32 values with the epoch in every 8-byte word
+constexpr int kXferTwoShot = 3;      // all-reduce in two hops: partials go to the chunk's owner, the owner sends the result
+// Phases of a fused collective (GemmParams::comm_phases, 0 = all).  A real call runs all of them in one
+// launch; a single-GPU emulation of several ranks launches phase by phase, all ranks per phase, because
+// launches on one GPU cannot wait for one another.
+constexpr int kPhasePush = 1, kPhaseReduce = 2, kPhaseCollect = 4;
 constexpr int kMaxCommTiles = 8192; // tiles per call that the flag area can describe
 
 enum Act : int { kActNone = 0, kActSilu = 1, kActGeluTanh = 2 };
@@ -58,7 +63,9 @@ struct GemmParams {
   int comm_mode;
   int world, rank;
   int rows_per_rank;     // reduce-scatter: token t belongs to rank t / rows_per_rank
-  int xfer_16bit;        // 0: fp32 + flags, 1: 16-bit values + flags, 2: fp32 with inline epoch flags (8 B per value)
+  int xfer_16bit;        // 0: fp32 + flags, 1: 16-bit values + flags, 2: fp32 with inline epoch flags (8 B per value),
+                         // 3: two-hop all-reduce with inline epochs (see epilogue_two_shot)
+  int comm_phases;       // bit mask of kPhase*; 0 = every phase in this launch
   int ag_world;          // > 1: token tile t0 is read from rank t0 / ag_rows_per_rank
   int ag_rows_per_rank;
   long slab_elems;       // elements of one (parity, source) receive slab
@@ -208,6 +215,131 @@ __device__ __forceinline__ void finalize_store8(const GemmParams& p, float* g, i
   }
 }
 
+// Re-read one (value, epoch, value, epoch) word until both epochs match the running call.  Bounded:
+// gives up after the cycle budget (or shortly after any other wait of the process has failed), records
+// the status and raises the CTA's abort flag.
+__device__ __forceinline__ bool poll_epoch_word(const uint4* src, unsigned int epoch_now, uint4& w,
+                                                volatile int* aborted, int* status, long long t0) {
+  while (w.y != epoch_now || w.w != epoch_now) {
+    if (*aborted || clock64() - t0 > FI_WAIT_CYCLES ||
+        (status != nullptr && clock64() - t0 > (FI_WAIT_CYCLES >> 10) &&
+         *reinterpret_cast<const volatile int*>(status) != 0)) {
+      set_status(status, kStatusTimeoutPeer);
+      *aborted = 1;
+      return false;
+    }
+    w = ld_volatile_v4(src);
+  }
+  return true;
+}
+
+// Two-hop all-reduce of a decode-sized tile (xfer_16bit == kXferTwoShot, 16-bit output).
+//
+// The 16 eight-value chunks of a tile row are dealt to the ranks round robin (chunk c belongs to rank
+// c % world).  Hop 1 (done by the caller's first pass): every rank stores its fp32 partial of a chunk
+// into the OWNER's receive slab, each 8-byte word carrying the call's epoch.  Hop 2 (here): the owner
+// sums the world partials in rank order, finishes the epilogue (activation, bias, residual), stores
+// the 16-bit result locally and sends it to every peer, again with inline epochs; the peers copy it
+// into their output.  Per rank and tile this moves 2 * (world - 1) / world of the tile instead of
+// (world - 1) tiles, and a thread polls a handful of independent words instead of a chain of
+// world - 1 dependent ones.  The result words reuse slots of the sender's slab that hop 1 never writes
+// (a rank does not send its own chunks to anybody), so the slab layout is that of the one-hop form.
+template <int BN>
+__device__ __forceinline__ void epilogue_two_shot(const GemmParams& p, const float* stage_f32, volatile int* aborted,
+                                                  int n0, int t0, unsigned int epoch_now, int t_end, int S,
+                                                  int crank, int rows_mine, int phases, int act_after_sum) {
+  const int W = p.world, me = p.rank;
+  const int parity = static_cast<int>(epoch_now & 1u);
+  const int own_per_row = (BM / 8 - me + W - 1) / W;
+  if (!*aborted && (phases & kPhaseReduce)) {
+    const int items = rows_mine * own_per_row * 2;       // (row, owned chunk, half chunk of 4 values)
+    for (int idx = threadIdx.x; idx < items; idx += blockDim.x) {
+      const int half = idx & 1;
+      const int j = (idx >> 1) % own_per_row;
+      const int tl = crank + ((idx >> 1) / own_per_row) * S;
+      const int nl = (me + j * W) * 8 + half * 4;
+      const int t = t0 + tl, n = n0 + nl;
+      if (t >= t_end || n >= p.N) continue;
+      const long pos = static_cast<long>(t) * p.N + n;
+      uint4 w[kMaxRanks][2];
+      const long long w0 = clock64();
+#pragma unroll
+      for (int s = 0; s < kMaxRanks; ++s) {
+        if (s < W && s != me) {
+          const uint4* src = reinterpret_cast<const uint4*>(p.recv[me]) +
+                             (((static_cast<long>(parity) * W + s) * p.slab_elems + pos) >> 1);
+          w[s][0] = ld_volatile_v4(src);
+          w[s][1] = ld_volatile_v4(src + 1);
+        }
+      }
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      bool ok = true;
+#pragma unroll
+      for (int s = 0; s < kMaxRanks; ++s) {
+        if (s >= W) continue;
+        if (s == me) {
+          const float4 a = *reinterpret_cast<const float4*>(stage_f32 + tl * BM + nl);
+          acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+        } else {
+          const uint4* src = reinterpret_cast<const uint4*>(p.recv[me]) +
+                             (((static_cast<long>(parity) * W + s) * p.slab_elems + pos) >> 1);
+          ok = ok && poll_epoch_word(src, epoch_now, w[s][0], aborted, p.status, w0) &&
+               poll_epoch_word(src + 1, epoch_now, w[s][1], aborted, p.status, w0);
+          acc[0] += __uint_as_float(w[s][0].x); acc[1] += __uint_as_float(w[s][0].z);
+          acc[2] += __uint_as_float(w[s][1].x); acc[3] += __uint_as_float(w[s][1].z);
+        }
+      }
+      if (!ok) break;
+      if (act_after_sum) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[q] = apply_act(acc[q], p.act);
+      }
+      const size_t coff = static_cast<size_t>(t) * p.ldc + n;
+      if (p.bias != nullptr) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[q] += ld16_as_float(p.bias, n + q, p.is_fp16);
+      }
+      if (p.residual != nullptr) {
+        const uint2 r2 = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p.residual) + coff);
+        float r[8];
+        unpack8(make_uint4(r2.x, r2.y, 0u, 0u), p.is_fp16, r);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[q] += r[q];
+      }
+      float g8[8] = {acc[0], acc[1], acc[2], acc[3], 0.f, 0.f, 0.f, 0.f};
+      uint32_t pk[4];
+      pack8(g8, p.is_fp16, pk);
+      *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.C) + coff) = make_uint2(pk[0], pk[1]);
+      const long roff = ((static_cast<long>(parity) * W + me) * p.slab_elems + pos) >> 1;
+      const uint4 word = make_uint4(pk[0], epoch_now, pk[1], epoch_now);
+#pragma unroll
+      for (int d = 0; d < kMaxRanks; ++d)
+        if (d < W && d != me) st_volatile_v4(reinterpret_cast<uint4*>(p.recv[d]) + roff, word);
+    }
+  }
+  if (!*aborted && (phases & kPhaseCollect)) {
+    const int items = rows_mine * (BM / 8);
+    for (int idx = threadIdx.x; idx < items; idx += blockDim.x) {
+      const int c = idx % (BM / 8);
+      const int owner = c % W;
+      if (owner == me) continue;
+      const int tl = crank + (idx / (BM / 8)) * S;
+      const int t = t0 + tl, n = n0 + c * 8;
+      if (t >= t_end || n >= p.N) continue;
+      const long pos = static_cast<long>(t) * p.N + n;
+      const uint4* src = reinterpret_cast<const uint4*>(p.recv[me]) +
+                         (((static_cast<long>(parity) * W + owner) * p.slab_elems + pos) >> 1);
+      const long long w0 = clock64();
+      uint4 a = ld_volatile_v4(src), b = ld_volatile_v4(src + 2);
+      if (!poll_epoch_word(src, epoch_now, a, aborted, p.status, w0) ||
+          !poll_epoch_word(src + 2, epoch_now, b, aborted, p.status, w0))
+        break;
+      *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.C) + static_cast<size_t>(t) * p.ldc + n) =
+          make_uint4(a.x, a.z, b.x, b.z);
+    }
+  }
+}
+
 // Part 1: warps 2..5.  Returns false when the accumulator never arrived.
 template <int BN, bool DUAL>
 __device__ __forceinline__ void epilogue_tmem_to_smem(const GemmParams& p, uint64_t* accum_bar,
@@ -281,6 +413,8 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
   const int rank = (S > 1) ? static_cast<int>(blockIdx.z) : 0;   // rank inside the split-K cluster
   if (S > 1) cluster.sync();
   const bool comm = p.comm_mode != kCommNone;
+  const int phases = p.comm_phases != 0 ? p.comm_phases : (kPhasePush | kPhaseReduce | kPhaseCollect);
+  const bool two_shot = comm && p.xfer_16bit == kXferTwoShot;
   const int rows_mine = (BN - rank + S - 1) / S;
   const int owner = p.comm_mode == kCommReduceScatter ? t0 / p.rows_per_rank : -1;
   const int parity = static_cast<int>(epoch_now & 1u);
@@ -351,6 +485,18 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
       }
       const long trow = (p.comm_mode == kCommReduceScatter) ? (t - owner * p.rows_per_rank) : t;
       const long off = (static_cast<long>(parity) * p.world + p.rank) * p.slab_elems + trow * p.N + n;
+      if (!(phases & kPhasePush)) continue;
+      if (two_shot) {   // hop 1: the partial of this chunk goes to the chunk's owner only
+        const int own = (nl >> 3) % p.world;
+        if (own != p.rank) {
+          uint4* dst = reinterpret_cast<uint4*>(p.recv[own]) + (off >> 1);
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            st_volatile_v4(dst + q, make_uint4(__float_as_uint(g[2 * q]), epoch_now,
+                                               __float_as_uint(g[2 * q + 1]), epoch_now));
+        }
+        continue;
+      }
       for (int d = 0; d < p.world; ++d) {
         if (d == p.rank || (owner >= 0 && d != owner)) continue;
         if (p.xfer_16bit == kXferInlineFlags) {
@@ -420,18 +566,18 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
   trace_mark(p.trace, epoch_now, 2);
   if (comm) {
     const unsigned int tile = static_cast<unsigned int>(t0 / BN) * gridDim.x + blockIdx.x;
-    const bool inline_flags = p.xfer_16bit == kXferInlineFlags;
+    const bool inline_flags = p.xfer_16bit == kXferInlineFlags || two_shot;
     if (!inline_flags && pushes) __threadfence_system();
     __syncthreads();
     const bool i_own = i_own_tile;
     if (!inline_flags && !*aborted && threadIdx.x < p.world && static_cast<int>(threadIdx.x) != p.rank) {
       const int d = threadIdx.x;
-      if (owner < 0 || d == owner) {
+      if ((owner < 0 || d == owner) && (phases & kPhasePush)) {
         unsigned int* f = reinterpret_cast<unsigned int*>(p.flags[d]) +
                           (static_cast<size_t>(tile) * p.world + p.rank) * kFlagParts + rank;
         st_release_sys(f, epoch_now);
       }
-      if (i_own) {
+      if (i_own && (phases & kPhaseReduce)) {
         const unsigned int* mine = reinterpret_cast<const unsigned int*>(p.flags[p.rank]) +
                                    (static_cast<size_t>(tile) * p.world + d) * kFlagParts + rank;
         if (!wait_flag(mine, epoch_now, p.status)) {
@@ -442,8 +588,11 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
     }
     __syncthreads();
     trace_mark(p.trace, epoch_now, 3);
+    if (two_shot)
+      epilogue_two_shot<BN>(p, stage_f32, aborted, n0, t0, epoch_now, t_end, S, rank, rows_mine, phases,
+                            !DUAL && p.act != kActNone);
     // ---- phase C: sum the partials of all ranks in rank order, finish the epilogue, store
-    if (!*aborted && i_own) {
+    if (!two_shot && !*aborted && i_own && (phases & kPhaseReduce)) {
       for (int idx = threadIdx.x; idx < rows_mine * (BM / 8); idx += blockDim.x) {
         const int tl = rank + (idx / (BM / 8)) * S;
         const int nl = (idx % (BM / 8)) * 8;
@@ -470,21 +619,14 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
             if (inline_flags) {
               const uint4* src = reinterpret_cast<const uint4*>(p.recv[p.rank]) + (off >> 1);
               const long long w0 = clock64();
+              uint4 wv[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) wv[q] = ld_volatile_v4(src + q);   // four independent loads in flight
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                uint4 wv = ld_volatile_v4(src + q);
-                while (wv.y != epoch_now || wv.w != epoch_now) {
-                  if (*aborted || clock64() - w0 > FI_WAIT_CYCLES ||
-                      (p.status != nullptr && clock64() - w0 > (FI_WAIT_CYCLES >> 10) &&
-                       *reinterpret_cast<const volatile int*>(p.status) != 0)) {
-                    set_status(p.status, kStatusTimeoutPeer);
-                    *aborted = 1;
-                    break;
-                  }
-                  wv = ld_volatile_v4(src + q);
-                }
-                v[2 * q] = __uint_as_float(wv.x);
-                v[2 * q + 1] = __uint_as_float(wv.z);
+                poll_epoch_word(src + q, epoch_now, wv[q], aborted, p.status, w0);
+                v[2 * q] = __uint_as_float(wv[q].x);
+                v[2 * q + 1] = __uint_as_float(wv[q].z);
               }
             } else if (p.xfer_16bit) {
               unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.recv[p.rank]) + off),
@@ -507,8 +649,9 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
       }
     }
   }
-  if (comm || p.ag_world > 1) {
-    // the last CTA of the call publishes the new epoch for the next fused call
+  if ((comm || p.ag_world > 1) && (!comm || (phases & (two_shot ? kPhaseCollect : kPhaseReduce)))) {
+    // the last CTA of the call publishes the new epoch for the next fused call (in a phase-by-phase
+    // emulation only the launch that runs the call's last phase does)
     __syncthreads();
     trace_mark(p.trace, epoch_now, 4);
     if (threadIdx.x == 0) {

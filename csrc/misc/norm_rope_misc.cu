@@ -387,6 +387,21 @@ __global__ void slot_mapping_kernel(const int* __restrict__ positions,
   slots[t] = blk <= 0 ? -1 : blk * bs + pos % bs;
 }
 
+// ------------------------------------------------------------------ row gather of an int32 table
+// out[r, :] = table[idx[r], :]: the block-table rows of the sequences of a decode batch (one launch
+// inside the captured step instead of a library index_select plus an index-widening copy).
+__global__ void gather_rows_i32_kernel(const int* __restrict__ table, const int* __restrict__ idx,
+                                       int* __restrict__ out, int cols, int n_table_rows) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  const int r = blockIdx.x;
+  int src = idx[r];
+  src = src < 0 ? 0 : (src >= n_table_rows ? n_table_rows - 1 : src);
+  const int* from = table + static_cast<long>(src) * cols;
+  int* to = out + static_cast<long>(r) * cols;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) to[c] = from[c];
+}
+
 // ------------------------------------------------------------------ greedy arg-max
 // One block per row; ties resolve to the lowest index (matches torch.argmax on CPU).
 template <typename T>
@@ -566,6 +581,15 @@ extern "C" int fi_slot_mapping(const int* positions, const int* token_seq, const
   if (T <= 0) return 0;
   fi::launch_kernel(slot_mapping_kernel, dim3((T + 255) / 256), dim3(256), 0, FI_STREAM(stream), 0, 
       positions, token_seq, block_tables, max_blocks, bs, slots, T);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fi_gather_rows_i32(const int* table, const int* idx, int* out, int rows, int cols,
+                                  int n_table_rows, void* stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (n_table_rows <= 0) return -10;
+  fi::launch_kernel(gather_rows_i32_kernel, dim3(rows), dim3(cols >= 256 ? 256 : 64), 0, FI_STREAM(stream), 0,
+                    table, idx, out, cols, n_table_rows);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -218,6 +218,7 @@ struct CombineComm {
   unsigned int* epoch;              // local: completed fused calls
   unsigned int* done;               // local: finished CTAs of this call
   int* status;
+  int phases;
 };
 
 template <typename T>
@@ -232,6 +233,7 @@ __global__ void moe_combine_allreduce_kernel(const T* __restrict__ y_sorted, con
   const unsigned int epoch_now = *c.epoch + 1u;
   const long parity = epoch_now & 1u;
   const int t = blockIdx.x;
+  const int phases = c.phases != 0 ? c.phases : 3;   // 1 = push partials, 2 = sum + store (split only when one GPU emulates several ranks)
   for (int ch = threadIdx.x; ch < H / 8; ch += blockDim.x) {
     float acc[8];
 #pragma unroll
@@ -248,13 +250,14 @@ __global__ void moe_combine_allreduce_kernel(const T* __restrict__ y_sorted, con
     const long elem = static_cast<long>(t) * H + ch * 8;
     const long my_off = (parity * c.world + c.rank) * c.slab_elems + elem;
     for (int d = 0; d < c.world; ++d) {
-      if (d == c.rank) continue;
+      if (d == c.rank || !(phases & 1)) continue;
       uint4* dst = reinterpret_cast<uint4*>(c.recv[d]) + (my_off >> 1);
 #pragma unroll
       for (int q = 0; q < 4; ++q)
         fi::st_volatile_v4(dst + q, make_uint4(__float_as_uint(acc[2 * q]), epoch_now,
                                                __float_as_uint(acc[2 * q + 1]), epoch_now));
     }
+    if (!(phases & 2)) continue;
     float sum[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) sum[j] = 0.f;
@@ -267,19 +270,21 @@ __global__ void moe_combine_allreduce_kernel(const T* __restrict__ y_sorted, con
         const long off = (parity * c.world + s) * c.slab_elems + elem;
         const uint4* src = reinterpret_cast<const uint4*>(c.recv[c.rank]) + (off >> 1);
         const long long w0 = clock64();
+        uint4 wv[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) wv[q] = fi::ld_volatile_v4(src + q);   // four independent loads in flight
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          uint4 wv = fi::ld_volatile_v4(src + q);
-          while (wv.y != epoch_now || wv.w != epoch_now) {
+          while (wv[q].y != epoch_now || wv[q].w != epoch_now) {
             if (aborted || clock64() - w0 > FI_WAIT_CYCLES) {
               fi::set_status(c.status, fi::kStatusTimeoutPeer);
               aborted = 1;
               break;
             }
-            wv = fi::ld_volatile_v4(src + q);
+            wv[q] = fi::ld_volatile_v4(src + q);
           }
-          v[2 * q] = __uint_as_float(wv.x);
-          v[2 * q + 1] = __uint_as_float(wv.z);
+          v[2 * q] = __uint_as_float(wv[q].x);
+          v[2 * q + 1] = __uint_as_float(wv[q].z);
         }
       }
 #pragma unroll
@@ -300,6 +305,7 @@ __global__ void moe_combine_allreduce_kernel(const T* __restrict__ y_sorted, con
     }
   }
   // the last CTA of the call publishes the new epoch for the next fused call
+  if (!(phases & 2)) return;
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
@@ -323,7 +329,7 @@ extern "C" int fi_moe_combine_allreduce(const void* y_sorted, const int* slot_of
   if (H % 8 != 0 || comm == nullptr || comm->world < 2 || comm->world > 8) return -10;
   if (static_cast<long>(T) * H > comm->slab_elems) return -11;
   CombineComm c;
-  c.world = comm->world; c.rank = comm->rank; c.slab_elems = comm->slab_elems;
+  c.world = comm->world; c.rank = comm->rank; c.slab_elems = comm->slab_elems; c.phases = comm->phases;
   for (int d = 0; d < 8; ++d) c.recv[d] = comm->recv[d];
   c.epoch = reinterpret_cast<unsigned int*>(comm->epoch);
   c.done = reinterpret_cast<unsigned int*>(comm->done);

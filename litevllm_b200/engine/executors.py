@@ -71,16 +71,24 @@ class DecodeExecutor:
     def _run(self, batch: ForwardBatch) -> torch.Tensor:
         return self.model(batch, self.kv_cache)
 
-    def _step_body(self, batch: ForwardBatch) -> torch.Tensor:
+    def _step_body(self, batch: ForwardBatch, greedy_only: bool = False) -> torch.Tensor:
         """What one captured decode step consists of: gather the block-table rows of the batch's
         slots, run the model, and leave the greedy token of every row in the input-id buffer (the
         next pipelined step reads its ids from there; other callers overwrite the buffer anyway).
         Keeping all three inside the graph leaves one host-to-device and one device-to-host copy
-        per step outside it."""
+        per step outside it.  ``greedy_only``: nobody will look at the logits, so a model whose
+        lm_head is sharded over the vocabulary may write the tokens itself from its local slice
+        (vocabulary-parallel arg-max) instead of gathering full logits."""
         d = self.builder._decode_buffers(batch.num_seqs)
-        torch.index_select(self.builder.kv.block_tables, 0, d["meta"][3].long(), out=d["block_tables"])
+        ops.gather_rows_i32(self.builder.kv.block_tables, d["meta"][3], d["block_tables"])
+        batch.extras.pop("greedy_done", None)
+        if greedy_only:
+            batch.extras["greedy_out"] = d["ids"]
+        else:
+            batch.extras.pop("greedy_out", None)
         logits = self._run(batch)
-        ops.argmax(logits, out=d["ids"])
+        if not batch.extras.pop("greedy_done", False):
+            ops.argmax(logits, out=d["ids"])
         return logits
 
     @torch.inference_mode()
@@ -98,23 +106,23 @@ class DecodeExecutor:
             if stateful:
                 self.model.finish_batch(batch, states or {r.request_id: r for r in reqs})
             return LogitsResult(logits, batch.request_ids)
-        bucket = batch.num_seqs
-        entry = self._graphs.get(bucket)
+        key = (batch.num_seqs, False)
+        entry = self._graphs.get(key)
         if entry is None:
             entry = self._capture(batch)
-            self._graphs[bucket] = entry
+            self._graphs[key] = entry
         graph, out, max_kv_cap = entry
         if batch.max_kv_len > max_kv_cap:
             # attention split count was chosen for a shorter context: recapture
             entry = self._capture(batch)
-            self._graphs[bucket] = entry
+            self._graphs[key] = entry
             graph, out, max_kv_cap = entry
         with span("decode_graph_replay"):
             graph.replay()
         self.graph_replays += 1
         return LogitsResult(out, batch.request_ids)
 
-    def _capture(self, batch: ForwardBatch):
+    def _capture(self, batch: ForwardBatch, greedy_only: bool = False):
         # graphs are captured for the full context so one graph serves the whole request lifetime
         full_ctx = self.builder.kv.blocks_per_seq * self.builder.kv.block_size
         saved = batch.max_kv_len
@@ -125,14 +133,14 @@ class DecodeExecutor:
         ids_saved = batch.input_ids.clone()
         with torch.cuda.stream(side):
             for _ in range(2):
-                self._step_body(batch)
+                self._step_body(batch, greedy_only)
                 batch.input_ids.copy_(ids_saved)      # the body leaves the greedy tokens in the id buffer
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         n0 = ops.launch_count()
         with torch.cuda.graph(graph, pool=self._pool):
-            out = self._step_body(batch)
+            out = self._step_body(batch, greedy_only)
         self.launches_per_graph[batch.num_seqs] = ops.launch_count() - n0
         if self._pool is None:
             self._pool = graph.pool()
@@ -143,7 +151,8 @@ class DecodeExecutor:
     @torch.inference_mode()
     def replay_or_capture(self, bucket: int, reqs: list[RequestState], max_kv_len: int) -> torch.Tensor:
         """Run the decode forward on the persistent bucket buffers (already filled by the caller)
-        and return the logits tensor ``[bucket, vocab]``."""
+        and return the logits tensor (the pipelined decode only uses the greedy tokens the step left in
+        the id buffer; under a vocabulary-sharded lm_head the logits are this rank's slice)."""
         d = self.builder._decode_buffers(bucket)
         batch = ForwardBatch(
             input_ids=d["ids"], positions=d["meta"][0], slot_mapping=d["meta"][1], block_tables=d["block_tables"],
@@ -152,11 +161,12 @@ class DecodeExecutor:
             request_ids=[st.request_id for st in reqs], extras={"num_real": len(reqs), "bucket": bucket})
         if not self.use_cuda_graph:
             self.eager_steps += 1
-            return self._step_body(batch)
-        entry = self._graphs.get(bucket)
+            return self._step_body(batch, greedy_only=True)
+        key = (bucket, True)
+        entry = self._graphs.get(key)
         if entry is None:
-            entry = self._capture(batch)
-            self._graphs[bucket] = entry
+            entry = self._capture(batch, greedy_only=True)
+            self._graphs[key] = entry
         with span("decode_graph_replay"):
             entry[0].replay()
         self.graph_replays += 1

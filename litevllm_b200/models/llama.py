@@ -277,6 +277,16 @@ class LlamaForCausalLM(nn.Module):
         else:
             logits = self.lm_head(x, out_dtype=torch.float32)
             if self.lm_head.tp > 1:
+                greedy_out = batch.extras.get("greedy_out") if batch.extras else None
+                st = pstate.get_state()
+                if (greedy_out is not None and logits.is_cuda and st.comm_backend == "fused" and st.symm is not None
+                        and st.argmax_ok and logits.shape[0] <= 1024):
+                    # only the greedy tokens are wanted: agree on them from the vocabulary slices (one kernel,
+                    # 16 bytes per row and peer) instead of gathering [rows, vocab] logits
+                    from ..parallel import fused_ops
+                    fused_ops.argmax_vocab_parallel(logits, pstate.tp_rank() * logits.shape[1], out=greedy_out)
+                    batch.extras["greedy_done"] = True
+                    return logits
                 logits = pstate.all_gather_last_dim(logits)
         return logits
 

@@ -430,6 +430,21 @@ def slot_mapping(positions, token_seq, block_tables, block_size, out=None):
     return out
 
 
+def gather_rows_i32(table, idx, out):
+    """``out[r] = table[idx[r]]`` for int32 ``table`` [n, cols], int32 ``idx`` [rows] (out-of-range
+    indices are clamped): the block-table rows of a decode batch."""
+    if not table.is_cuda:
+        out.copy_(table.index_select(0, idx.long().clamp_(0, table.shape[0] - 1)))
+        return out
+    assert table.dtype == torch.int32 and idx.dtype == torch.int32 and out.dtype == torch.int32
+    assert table.is_contiguous() and out.is_contiguous() and idx.is_contiguous()
+    rc = _lib.kernels().fi_gather_rows_i32(_p(table), _p(idx), _p(out), idx.shape[0], table.shape[1], table.shape[0],
+                                           _stream())
+    _lib.check(rc, "fi_gather_rows_i32")
+    _count()
+    return out
+
+
 def argmax(logits, out=None):
     if not logits.is_cuda:
         r = reference.argmax(logits)

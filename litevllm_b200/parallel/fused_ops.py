@@ -20,7 +20,19 @@ from .. import ops
 from ..ops import _lib
 from . import state as pstate
 
+import os
+
 _parity = [0]
+# decode-sized all-reduces switch from the one-hop push (every rank stores its whole partial tile into
+# every peer) to the two-hop form (partials to the chunk owner, 16-bit result back) at this world size
+_TWO_SHOT_MIN_WORLD = int(os.environ.get("FI_TWO_SHOT_MIN_WORLD", "4"))
+
+
+def decode_allreduce_format(world: int, out_dtype: torch.dtype) -> int:
+    """Transfer format of a decode-sized fused all-reduce: 2 = one hop, 3 = two hops."""
+    if world >= _TWO_SHOT_MIN_WORLD and out_dtype in (torch.bfloat16, torch.float16):
+        return 3
+    return 2
 
 
 def _fused_available(x: torch.Tensor) -> bool:
@@ -35,7 +47,8 @@ def row_parallel_linear(layer, x: torch.Tensor, residual: torch.Tensor | None, o
     if _fused_available(x):
         heap = st.symm
         if T > 0 and T <= 256 and heap.fits_low_latency(T, N):
-            return _fused_gemm_allreduce(layer, x, residual, out, heap, 2)     # decode: one NVLink crossing
+            fmt = decode_allreduce_format(heap.world, x.dtype if out is None else out.dtype)
+            return _fused_gemm_allreduce(layer, x, residual, out, heap, fmt)   # decode: inline epochs, no flags
         xfer16 = T > 256
         elem = 2 if xfer16 else 4
         if heap.fits_recv(T, N, elem) and T > 0:
@@ -51,15 +64,15 @@ def row_parallel_linear(layer, x: torch.Tensor, residual: torch.Tensor | None, o
     return partial
 
 
-def _fused_gemm_allreduce(layer, x, residual, out, heap, xfer16: bool | int):
+def _fused_gemm_allreduce(layer, x, residual, out, heap, xfer16: bool | int, phases: int = 0):
     T, K = x.shape
     N = layer.out_features
     if out is None:
         out = torch.empty(T, N, dtype=x.dtype, device=x.device)
-    comm = heap.comm_desc(mode=1, T=T, N=N, xfer_16bit=xfer16)
+    comm = heap.comm_desc(mode=1, T=T, N=N, xfer_16bit=xfer16, phases=phases)
     lib = _lib.kernels()
     dt = ops._DT[x.dtype]
-    bias = layer.bias if pstate.tp_rank() == 0 else None
+    bias = layer.bias      # added after the cross-rank sum by whichever rank finishes an element, so every rank passes it
     if layer.quant_method is None:
         w = layer.weight
         rc = lib.fi_dense_gemm_comm(ops._p(x), ops._p(w), ops._p(out), ops._p(bias), ops._p(residual), T, N, K,
@@ -82,16 +95,16 @@ def _fused_gemm_allreduce(layer, x, residual, out, heap, xfer16: bool | int):
 # --------------------------------------------------------------------------- sequence-parallel forms
 def gemm_reduce_scatter(x: torch.Tensor, w: torch.Tensor, residual_shard: torch.Tensor | None,
                         rows_per_rank: int, out_shard: torch.Tensor | None = None,
-                        xfer_16bit: bool = True) -> torch.Tensor:
+                        xfer_16bit: bool = True, heap=None, phases: int = 0) -> torch.Tensor:
     """``(x @ w.T)`` summed over ranks, each rank keeping token rows
     ``[rank*rows_per_rank, (rank+1)*rows_per_rank)`` (+ its residual shard).  One fused kernel."""
-    st = pstate.get_state()
-    heap = st.symm
+    if heap is None:
+        heap = pstate.get_state().symm
     T, K = x.shape
     N = w.shape[0]
     if out_shard is None:
         out_shard = torch.empty(rows_per_rank, N, dtype=x.dtype, device=x.device)
-    comm = heap.comm_desc(mode=2, T=T, N=N, xfer_16bit=xfer_16bit, rows_per_rank=rows_per_rank)
+    comm = heap.comm_desc(mode=2, T=T, N=N, xfer_16bit=xfer_16bit, rows_per_rank=rows_per_rank, phases=phases)
     rc = _lib.kernels().fi_dense_gemm_comm(
         ops._p(x), ops._p(w), ops._p(out_shard), None, ops._p(residual_shard), T, N, K, x.stride(0), w.stride(0),
         out_shard.stride(0), 0, 0, 0, ops._DT[x.dtype], 0, 0, ops._p(ops.status_word(x.device)), ops._stream(),
@@ -132,6 +145,26 @@ def allgather_gemm(x_shard: torch.Tensor, w: torch.Tensor, T_total: int, rows_pe
         ops._ACT[gated_act] if gated_act else 0, inter, 0, ops._DT[x_shard.dtype], 0, 0,
         ops._p(ops.status_word(x_shard.device)), ops._stream(), ctypes.byref(comm))
     _lib.check(rc, "fi_dense_gemm_comm(all_gather)")
+    ops._count()
+    return out
+
+
+def argmax_vocab_parallel(logits_local: torch.Tensor, vocab_offset: int, out: torch.Tensor | None = None,
+                          heap=None, phases: int = 0) -> torch.Tensor:
+    """Greedy token of every row from vocabulary-sharded fp32 logits ``[rows, V_local]`` in one kernel:
+    local arg-max, one 16-byte word per row to every peer, pick the best of ``world`` candidates (ties
+    to the lowest global index).  Every rank returns the same ids."""
+    if heap is None:
+        heap = pstate.get_state().symm
+    rows, V = logits_local.shape
+    assert logits_local.dtype == torch.float32 and logits_local.stride(1) == 1
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int64, device=logits_local.device)
+    comm = heap.argmax_desc(phases)
+    rc = _lib.kernels().fi_argmax_tp(ops._p(logits_local), logits_local.stride(0), rows, V, int(vocab_offset),
+                                     ops._p(out), ops._p(ops.status_word(logits_local.device)), ops._stream(),
+                                     ctypes.byref(comm))
+    _lib.check(rc, "fi_argmax_tp")
     ops._count()
     return out
 

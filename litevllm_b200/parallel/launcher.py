@@ -135,26 +135,57 @@ def _self_test_fused(st) -> None:
 
     g = torch.Generator(device=dev).manual_seed(1234 + st.rank)
     ok_ar = ok_sp = True
-    try:
-        T, N, K = 32, 512, 256
-        x = (torch.randn(T, K, generator=g, device=dev) * 0.5).bfloat16()
-        wt = (torch.randn(N, K, generator=g, device=dev) * 0.05).bfloat16()
-        layer = _Layer()
-        layer.weight, layer.out_features = wt, N
-        want = x.float() @ wt.float().t()
-        dist.all_reduce(want, group=st.group)
-        for _ in range(2):      # twice: both slab parities
-            got = fused_ops._fused_gemm_allreduce(layer, x, None, None, st.symm, 2)
-        torch.cuda.synchronize(dev)
-        ok_ar = status_ok() and close(got, want)
-    except Exception as e:  # pragma: no cover - platform dependent
-        logger.warning("fused all-reduce self-test raised %r", e)
-        ok_ar = False
-    if not agree(ok_ar):
+    verdicts: dict = {}
+    st.self_test = verdicts
+
+    def run_allreduce(fmt: int) -> bool:
+        try:
+            T, N, K = 32, 512, 256
+            x = (torch.randn(T, K, generator=g, device=dev) * 0.5).bfloat16()
+            wt = (torch.randn(N, K, generator=g, device=dev) * 0.05).bfloat16()
+            res = torch.randn(T, N, generator=g, device=dev).bfloat16()
+            dist.broadcast(res, src=0, group=st.group)
+            layer = _Layer()
+            layer.weight, layer.out_features = wt, N
+            want = x.float() @ wt.float().t()
+            dist.all_reduce(want, group=st.group)
+            want = want + res.float()
+            for _ in range(2):      # twice: both slab parities
+                got = fused_ops._fused_gemm_allreduce(layer, x, res, None, st.symm, fmt)
+            torch.cuda.synchronize(dev)
+            return status_ok() and close(got, want)
+        except Exception as e:  # pragma: no cover - platform dependent
+            logger.warning("fused all-reduce (format %d) self-test raised %r", fmt, e)
+            return False
+
+    ok_ar = agree(run_allreduce(2))
+    verdicts["allreduce_one_hop"] = ok_ar
+    if ok_ar and fused_ops.decode_allreduce_format(w, torch.bfloat16) == 3:
+        ok_two = agree(run_allreduce(3))
+        verdicts["allreduce_two_hop"] = ok_two
+        if not ok_two:
+            logger.warning("rank %d: the two-hop all-reduce failed its start-up check; using the one-hop form", st.rank)
+            fused_ops._TWO_SHOT_MIN_WORLD = 1 << 30
+    if not ok_ar:
         logger.warning("rank %d: fused collectives failed their start-up check; using NCCL collectives", st.rank)
         st.symm = None
         st.comm_backend = "nccl"
         return
+    try:
+        rows, V = 8, 1024
+        lg = torch.randn(rows, V, generator=g, device=dev)
+        gathered = [torch.empty_like(lg) for _ in range(w)]
+        dist.all_gather(gathered, lg, group=st.group)
+        want_ids = torch.cat(gathered, dim=1).argmax(-1)
+        for _ in range(2):
+            got_ids = fused_ops.argmax_vocab_parallel(lg, st.rank * V)
+        torch.cuda.synchronize(dev)
+        ok_am = status_ok() and bool(torch.equal(got_ids, want_ids))
+    except Exception as e:  # pragma: no cover - platform dependent
+        logger.warning("vocabulary-parallel arg-max self-test raised %r", e)
+        ok_am = False
+    st.argmax_ok = agree(ok_am)
+    verdicts["argmax_vocab_parallel"] = st.argmax_ok
     try:
         rpr, K, N = 128, 256, 256
         x = (torch.randn(rpr * w, K, generator=g, device=dev) * 0.5).bfloat16()
@@ -180,6 +211,7 @@ def _self_test_fused(st) -> None:
         logger.warning("sequence-parallel self-test raised %r", e)
         ok_sp = False
     st.sequence_parallel_ok = agree(ok_sp)
+    verdicts["sequence_parallel"] = st.sequence_parallel_ok
     if not st.sequence_parallel_ok:
         logger.warning("rank %d: fused reduce-scatter / all-gather failed their start-up check; "
                        "sequence-parallel prefill is off", st.rank)

@@ -26,6 +26,8 @@ class ParallelState:
     group: object | None = None
     symm: object | None = None      # SymmetricHeap when the fused backend is up
     sequence_parallel_ok: bool = True   # cleared when the fused reduce-scatter / all-gather start-up check fails
+    argmax_ok: bool = True              # cleared when the vocabulary-parallel arg-max start-up check fails
+    self_test: dict | None = None       # verdicts of the start-up checks of the fused collectives, per form
 
     @property
     def tp_rank(self) -> int:
