@@ -60,6 +60,87 @@ def write_checkpoint(out: Path, cfg: dict, seed: int = 0) -> None:
         {"eos_token": "<e>", "bos_token": "<b>", "unk_token": "<u>", "pad_token": "<u>"}))
 
 
+class CopyCounter:
+    """Counts the bytes that cross the host/device boundary while ONE untimed engine step runs, by
+    wrapping the torch entry points a Python engine can move data with (tensor construction on a CUDA
+    device from host data, ``.to`` / ``.cuda`` / ``.cpu`` / ``copy_`` across devices, ``.item`` /
+    ``.tolist`` / ``.numpy`` on CUDA tensors).  The reference's code is not touched; the wrappers are
+    installed after the timed region and removed again."""
+
+    def __init__(self, torch):
+        self.torch = torch
+        self.h2d = 0
+        self.d2h = 0
+        self._saved = []
+
+    @staticmethod
+    def _nbytes(t):
+        return int(t.numel() * t.element_size())
+
+    def _patch(self, owner, name, make):
+        orig = getattr(owner, name)
+        self._saved.append((owner, name, orig))
+        setattr(owner, name, make(orig))
+
+    def __enter__(self):
+        torch, me = self.torch, self
+        T = torch.Tensor
+
+        def is_cuda_dev(d):
+            return d is not None and str(d).startswith("cuda")
+
+        def ctor(orig):
+            def f(data, *a, **k):
+                out = orig(data, *a, **k)
+                if isinstance(out, T) and out.is_cuda and not (isinstance(data, T) and data.is_cuda):
+                    me.h2d += me._nbytes(out)
+                return out
+            return f
+
+        def mover(orig):
+            def f(self_, *a, **k):
+                out = orig(self_, *a, **k)
+                if isinstance(out, T) and out is not self_:
+                    if out.is_cuda and not self_.is_cuda:
+                        me.h2d += me._nbytes(out)
+                    elif self_.is_cuda and not out.is_cuda:
+                        me.d2h += me._nbytes(self_)
+                return out
+            return f
+
+        def copy_(orig):
+            def f(self_, src, *a, **k):
+                if isinstance(src, T):
+                    if self_.is_cuda and not src.is_cuda:
+                        me.h2d += me._nbytes(self_)
+                    elif src.is_cuda and not self_.is_cuda:
+                        me.d2h += me._nbytes(self_)
+                return orig(self_, src, *a, **k)
+            return f
+
+        def reader(orig):
+            def f(self_, *a, **k):
+                if self_.is_cuda:
+                    me.d2h += me._nbytes(self_)
+                return orig(self_, *a, **k)
+            return f
+
+        for name in ("tensor", "as_tensor"):
+            self._patch(torch, name, ctor)
+        for name in ("to", "cuda", "cpu"):
+            self._patch(T, name, mover)
+        self._patch(T, "copy_", copy_)
+        for name in ("item", "tolist", "numpy", "__int__", "__float__", "__bool__", "__index__"):
+            self._patch(T, name, reader)
+        return self
+
+    def __exit__(self, *exc):
+        for owner, name, orig in reversed(self._saved):
+            setattr(owner, name, orig)
+        self._saved = []
+        return False
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref-dir", required=True)
@@ -128,10 +209,23 @@ def main():
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
+    # one more, untimed, step with the copy counter installed: bytes in and out per step of the stock loop
+    h2d_bytes = d2h_bytes = None
+    try:
+        with CopyCounter(torch) as cc:
+            eng.step()
+            torch.cuda.synchronize()
+        h2d_bytes, d2h_bytes = cc.h2d, cc.d2h
+    except Exception as e:   # the count is a label, never a reason to lose the measurement
+        print(f"copy counter failed: {e!r}", file=sys.stderr)
     res = {"impl": "reference", "value": round(n_tok / (ms / 1e3), 1), "unit": "tok/s", "n_gpus": 1, "steps": K,
            "warmup": W, "ms_per_step": round(ms / K, 4), "tokens_in_timed_region": n_tok,
            "active_requests_cap": cap, "ttft_p50_ms": round(statistics.median(ttft.values()) * 1e3, 2) if ttft else None,
            "dtype": "bf16", "data": "synthetic",
+           "e2e": {"value": round(n_tok / (ms / 1e3), 1), "unit": "tok/s", "ms_per_step": round(ms / K, 4),
+                   "api": "reference LiteEngine.add_request + LiteEngine.step (host token lists in, sampled ids out)",
+                   "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+                   "bytes_counted_by": "torch entry points wrapped during one extra untimed step"},
            "config": {"model": "tinyllama-1.1b (random init N(0,0.02))", "global_batch": B, "prompt_len": P,
                       "seq_len": P + 1 + W + K, "parallelism": "single GPU (the reference has no distributed layer)",
                       "profile": "throughput", "kv_type": "fp16",

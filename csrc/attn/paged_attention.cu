@@ -19,6 +19,7 @@
 #include "../common/launch.cuh"
 #include "paged_attention_noalloc.h"
 #include <atomic>
+#include <cooperative_groups.h>
 #include <math_constants.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -103,6 +104,10 @@ struct AttnParams {
   // optional [B * gridDim.y] zero-initialised tickets: the split CTA that arrives last merges the
   // partials itself (and resets the ticket), so no separate merge launch is needed
   unsigned int* merge_tickets;
+  // > 0: the split CTAs of one (sequence, KV head group) form a thread-block cluster and merge their
+  // partials through distributed shared memory at this byte offset of the dynamic shared memory
+  // ([16][HD] sums + [16][2] max/denominator per CTA): no global scratch, no tickets, no second launch
+  int cluster_off;
 };
 
 // Load `rows` KV tokens starting at token tok0 of sequence b / kv head kvh into a swizzled tile.
@@ -541,13 +546,51 @@ __global__ void __launch_bounds__(128) paged_decode_v2_kernel(const AttnParams p
     if (p.splits == 1) {
       const float v = l > 0.f ? acc / l * (fp8 ? p.v_scale : 1.f) : 0.f;
       reinterpret_cast<T*>(p.out)[(static_cast<long>(b) * p.nh + head) * HD + d] = MmaT<T>::from_f(v);
+    } else if (p.cluster_off > 0) {
+      float* cO = reinterpret_cast<float*>(smem_raw + p.cluster_off);
+      cO[i] = acc;
+      if (d == 0) { cO[16 * HD + r * 2] = m; cO[16 * HD + r * 2 + 1] = l; }
     } else {
       const long base = (static_cast<long>(b) * p.nh + head) * p.splits + split;
       p.ws_o[base * HD + d] = acc;
       if (d == 0) { p.ws_ml[base * 2] = m; p.ws_ml[base * 2 + 1] = l; }
     }
   }
-  if (p.splits > 1 && p.merge_tickets != nullptr) {
+  if (p.splits > 1 && p.cluster_off > 0) {
+    // the cluster's CTAs hold one partial each in their shared memory; every CTA finishes its share of
+    // the (head, channel) outputs from all of them and nobody leaves before the peers have read
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    float* cO = reinterpret_cast<float*>(smem_raw + p.cluster_off);
+    const int E = heads_here * HD;
+    const int per = (E + p.splits - 1) / p.splits;
+    const int i_end = min(E, (split + 1) * per);
+    for (int i = split * per + threadIdx.x; i < i_end; i += 128) {
+      const int r = i / HD;
+      float ms[8], m = -CUDART_INF_F;
+#pragma unroll
+      for (int sidx = 0; sidx < 8; ++sidx) {
+        if (sidx < p.splits) {
+          ms[sidx] = cluster.map_shared_rank(cO, sidx)[16 * HD + r * 2];
+          m = fmaxf(m, ms[sidx]);
+        }
+      }
+      float acc = 0.f, l = 0.f;
+#pragma unroll
+      for (int sidx = 0; sidx < 8; ++sidx) {
+        if (sidx < p.splits) {
+          const float* peer = cluster.map_shared_rank(cO, sidx);
+          const float f = ms[sidx] == -CUDART_INF_F ? 0.f : exp2f((ms[sidx] - m) * kLog2e);
+          acc += f * peer[i];
+          l += f * peer[16 * HD + r * 2 + 1];
+        }
+      }
+      const float v = l > 0.f ? acc / l * (fp8 ? p.v_scale : 1.f) : 0.f;
+      reinterpret_cast<T*>(p.out)[(static_cast<long>(b) * p.nh + head0) * HD + i] = MmaT<T>::from_f(v);
+    }
+    cluster.sync();
+  } else if (p.splits > 1 && p.merge_tickets != nullptr) {
     // last split CTA of this (sequence, head group) merges: every CTA publishes its partials, takes
     // a ticket, and the one that draws the last ticket reads all of them back (L2) and finishes
     __shared__ int is_last;
@@ -774,11 +817,21 @@ int launch_decode(const AttnParams& p, int B, cudaStream_t s) {
     const int raw = p.kv_fp8 ? tile : tile * 2;
     const int pipe_bytes = 4 * (NST * 2 * raw + (p.kv_fp8 ? 2 * tile * 2 : 0));
     const int merge_bytes = (4 * 16 * HD + 4 * 16 * 2) * 4;
-    const int smem = 16 * HD * 2 + (pipe_bytes > merge_bytes ? pipe_bytes : merge_bytes);
+    int smem = 16 * HD * 2 + (pipe_bytes > merge_bytes ? pipe_bytes : merge_bytes);
+    AttnParams pc = p;
+    pc.cluster_off = 0;
+    if (p.cluster_off != 0 && p.splits > 1 && p.splits <= 8) {   // cluster of the split CTAs merges through DSMEM
+      pc.cluster_off = (smem + 127) & ~127;
+      smem = pc.cluster_off + (16 * HD + 32) * 4;
+    }
     auto kern = paged_decode_v2_kernel<T, HD, NST>;
     cudaError_t ce = fi::ensure_dynamic_smem(kern, smem);
     if (ce != cudaSuccess) return static_cast<int>(ce);
-    fi::launch_kernel(kern, dim3(p.splits, p.nkv * groups, B), dim3(128), smem, s, 0, p);
+    if (pc.cluster_off > 0) {
+      ce = fi::launch_kernel_cluster(kern, dim3(p.splits, p.nkv * groups, B), dim3(128), smem, s, dim3(p.splits, 1, 1), pc);
+      return static_cast<int>(ce != cudaSuccess ? ce : cudaGetLastError());
+    }
+    fi::launch_kernel(kern, dim3(p.splits, p.nkv * groups, B), dim3(128), smem, s, 0, pc);
   } else {
     const int kv_bytes = (16 * HD + 4 * 64 * HD) * 2;
     const int merge_bytes = (4 * 16 * HD + 4 * 16 * 2) * 4 + 16 * HD * 2;
@@ -788,7 +841,7 @@ int launch_decode(const AttnParams& p, int B, cudaStream_t s) {
     if (ce != cudaSuccess) return static_cast<int>(ce);
     fi::launch_kernel(kern, dim3(p.splits, p.nkv * groups, B), dim3(128), smem, s, 0, p);
   }
-  const bool merged_in_kernel = p.merge_tickets != nullptr && p.block_size % 16 == 0;
+  const bool merged_in_kernel = (p.merge_tickets != nullptr || (p.cluster_off != 0 && p.splits <= 8)) && p.block_size % 16 == 0;
   if (p.splits > 1 && !merged_in_kernel)
     fi::launch_kernel(decode_merge_kernel<T, HD>, dim3(p.nh, B), dim3(HD >= 128 ? 128 : 64), 0, s, 0, p);
   return static_cast<int>(cudaGetLastError());
@@ -853,6 +906,38 @@ extern "C" int fi_paged_decode_merged(const void* q, long q_stride, const void* 
   p.ws_ml = ws_ml; p.max_blocks = max_blocks; p.block_size = block_size; p.nh = nh; p.nkv = nkv;
   p.window = window; p.sm_scale = sm_scale; p.softcap = softcap; p.k_scale = k_scale;
   p.v_scale = v_scale; p.kv_fp8 = kv_fp8; p.splits = splits; p.merge_tickets = tickets;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+#define FI_DEC(TT, HD) return launch_decode<TT, HD>(p, B, s)
+  if (dtype == 0) {
+    if (hd == 64) FI_DEC(__nv_bfloat16, 64);
+    if (hd == 128) FI_DEC(__nv_bfloat16, 128);
+    if (hd == 256) FI_DEC(__nv_bfloat16, 256);
+  } else if (dtype == 1) {
+    if (hd == 64) FI_DEC(__half, 64);
+    if (hd == 128) FI_DEC(__half, 128);
+    if (hd == 256) FI_DEC(__half, 256);
+  }
+#undef FI_DEC
+  return -11;
+}
+
+// Same as fi_paged_decode for 2 <= splits <= 8 with the split CTAs of a (sequence, KV head group)
+// launched as one thread-block cluster that merges its partials through distributed shared memory:
+// one launch, no scratch buffers, no atomics.  Needs block_size % 16 == 0.
+extern "C" int fi_paged_decode_cluster(const void* q, long q_stride, const void* k_cache,
+                               const void* v_cache, void* out, const int* block_tables,
+                               const int* seq_lens, int B, int nh,
+                               int nkv, int hd, int max_blocks, int block_size, int window,
+                               float sm_scale, float softcap, int kv_fp8, float k_scale,
+                               float v_scale, int splits, int dtype, void* stream) {
+  if (B <= 0) return 0;
+  if (nkv <= 0 || nh <= 0 || nh % nkv != 0 || splits < 1 || splits > 8 || block_size % 16 != 0) return -10;
+  AttnParams p = {};
+  p.q = q; p.q_stride = q_stride; p.k_cache = k_cache; p.v_cache = v_cache; p.out = out;
+  p.block_tables = block_tables; p.seq_lens = seq_lens; p.cu_q = nullptr; p.ws_o = nullptr;
+  p.ws_ml = nullptr; p.max_blocks = max_blocks; p.block_size = block_size; p.nh = nh; p.nkv = nkv;
+  p.window = window; p.sm_scale = sm_scale; p.softcap = softcap; p.k_scale = k_scale;
+  p.v_scale = v_scale; p.kv_fp8 = kv_fp8; p.splits = splits; p.cluster_off = 1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 #define FI_DEC(TT, HD) return launch_decode<TT, HD>(p, B, s)
   if (dtype == 0) {

@@ -289,7 +289,15 @@ def _merge_tickets(device: torch.device) -> torch.Tensor:
     return t
 
 
+# how split-KV partials are merged: "cluster" (the split CTAs form a thread-block cluster and merge through
+# distributed shared memory: one launch, no scratch), "kernel" (separate merge launch), "ticket" (last CTA merges)
+_DECODE_MERGE = os.environ.get("FI_DECODE_MERGE", "cluster")
+_DECODE_SPLITS = int(os.environ.get("FI_DECODE_SPLITS", "0"))
+
+
 def pick_decode_splits(B: int, nkv: int, max_kv_len: int, sm_count: int = 148) -> int:
+    if _DECODE_SPLITS > 0:
+        return _DECODE_SPLITS
     chunks = max(1, (max_kv_len + 63) // 64)
     ctas = max(1, B * nkv)
     want = max(1, (2 * sm_count + ctas - 1) // ctas)
@@ -316,6 +324,14 @@ def paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, nh, nkv,
             max_kv_len = block_tables.shape[1] * k_cache.shape[2]
         eff = min(max_kv_len, window) if window and window > 0 else max_kv_len
         splits = pick_decode_splits(B, nkv, eff)
+    if 1 < splits <= 8 and _DECODE_MERGE == "cluster" and k_cache.shape[2] % 16 == 0:
+        rc = _lib.kernels().fi_paged_decode_cluster(
+            _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(block_tables), _p(seq_lens), B, nh, nkv, hd,
+            block_tables.shape[1], k_cache.shape[2], int(window or 0), sm_scale, float(softcap or 0.0),
+            1 if k_cache.dtype == torch.float8_e4m3fn else 0, k_scale, v_scale, splits, _DT[q.dtype], _stream())
+        _lib.check(rc, "fi_paged_decode_cluster")
+        _count()
+        return out
     ws_o = ws_ml = None
     if splits > 1:
         n_o = B * nh * splits * hd
@@ -324,7 +340,8 @@ def paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, nh, nkv,
         ws_o, ws_ml = ws[:n_o], ws[n_o:]
     groups = nkv * ((nh // nkv + 15) // 16)
     kv_per_split = (max_kv_len if max_kv_len is not None else block_tables.shape[1] * k_cache.shape[2]) // splits
-    if splits > 1 and kv_per_split >= 1024 and k_cache.shape[2] % 16 == 0 and B * groups <= _MERGE_TICKETS:
+    if splits > 1 and (kv_per_split >= 1024 or _DECODE_MERGE == "ticket") and _DECODE_MERGE != "kernel" \
+            and k_cache.shape[2] % 16 == 0 and B * groups <= _MERGE_TICKETS:
         # long splits: the last split CTA merges (one launch instead of two).  Short splits keep the
         # separate merge kernel: its launch overlaps the attention kernel's tail under programmatic
         # dependent launch, while the ticket (fence + atomic) would sit on every CTA's critical path

@@ -158,11 +158,36 @@ def test_paged_decode(nh, nkv, hd, fp8, window, softcap, splits):
     _close(y, yr, 2e-2, 2e-2, f"decode nh{nh} nkv{nkv} hd{hd}")
 
 
+@pytest.mark.parametrize("merge", ["cluster", "kernel", "ticket"])
+@pytest.mark.parametrize("nh,nkv,hd,fp8,splits", [(32, 4, 64, False, 2), (32, 4, 64, False, 4), (32, 8, 128, True, 8),
+                                                  (16, 8, 256, False, 3), (40, 2, 128, False, 5)])
+def test_paged_decode_merge_variants(monkeypatch, merge, nh, nkv, hd, fp8, splits):
+    """The three ways of merging split-KV partials (thread-block cluster over distributed shared memory,
+    separate merge launch, last-CTA ticket) against the fp32 oracle, including splits with no tokens."""
+    monkeypatch.setattr(ops, "_DECODE_MERGE", merge)
+    torch.manual_seed(7)
+    lens = [1, 40, 300, 129, 1000, 64, 17]
+    B, bs = len(lens), 16
+    kc, vc, bt = _fill_paged(B, lens, nkv, hd, bs, fp8)
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    ks = vs = 0.5 if fp8 else 1.0
+    cu = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    for rep in range(2):
+        q = torch.randn(B, nh * hd, device=DEV).bfloat16()
+        y = ops.paged_attention_decode(q, kc, vc, bt, sl, nh, nkv, hd, scale, 0, 0.0, ks, vs, splits=splits,
+                                       max_kv_len=max(lens))
+        yr = ref.paged_attention(q, kc, vc, bt, sl, cu, nh, nkv, hd, scale, 0, 0.0, ks, vs, out_dtype=torch.float32)
+        _close(y, yr, 2e-2, 2e-2, f"{merge} merge rep {rep} nh{nh} nkv{nkv} hd{hd} splits {splits}")
+
+
 @pytest.mark.parametrize("nh,nkv,hd,fp8", [(8, 2, 64, False), (32, 8, 128, False), (8, 2, 128, True)])
 def test_paged_decode_long_context_merges_in_kernel(nh, nkv, hd, fp8):
     """Long splits (>= 1024 tokens each): the last split CTA merges the partials itself; run twice so the
     second call sees the tickets the first one left (they must be zero again)."""
     torch.manual_seed(11)
+    import litevllm_b200.ops as O
+    saved, O._DECODE_MERGE = O._DECODE_MERGE, "ticket"
     lens = [4096, 2100, 3000, 1]
     B, bs = len(lens), 16
     kc, vc, bt = _fill_paged(B, lens, nkv, hd, bs, fp8)
@@ -176,6 +201,7 @@ def test_paged_decode_long_context_merges_in_kernel(nh, nkv, hd, fp8):
                                        max_kv_len=max(lens))
         yr = ref.paged_attention(q, kc, vc, bt, sl, cu, nh, nkv, hd, scale, 0, 0.0, ks, vs, out_dtype=torch.float32)
         _close(y, yr, 2e-2, 2e-2, f"merged decode rep {rep} nh{nh} nkv{nkv} hd{hd}")
+    O._DECODE_MERGE = saved
     assert int(ops._merge_tickets(torch.device(DEV, 0)).abs().sum().item()) == 0
 
 
