@@ -22,8 +22,12 @@ using namespace fi;
 
 namespace {
 
+// Debug aid: device array of 8 x uint64 that CTA (0,0,0) of every plain GEMM launch fills with cycle
+// counts of its phases (see cycle_mark); null = off.  Set with fi_dense_gemm_set_trace.
+unsigned long long* g_plain_trace = nullptr;
 
-template <int BN, int STAGES, bool DUAL>
+
+template <int BN, int STAGES, bool DUAL, bool RED = (BN <= 64 || (BN == 128 && !DUAL))>
 __global__ void __launch_bounds__(kThreads)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                   const __grid_constant__ TokenMaps tmaps_x, const GemmParams p) {
@@ -45,6 +49,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
   volatile int* aborted = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* row_ss = reinterpret_cast<float*>(tmem_slot + 2);   // [BN] floats after the control words: sum of squares per token
+  // split-K exchange area (never aliases the ring: peers store into it while this CTA may still be in its main loop)
+  float* red = RED ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(row_ss) + ((BN * 4 + 15) & ~15)) : nullptr;
   const bool rms = p.rms_eps > 0.f;
   // fp32 staging of the accumulator tile(s); aliases the pipeline ring once the main loop is done.
   float* stage_f32 = reinterpret_cast<float*>(smem);
@@ -52,6 +58,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BM;
+  if (threadIdx.x == 0) cycle_mark(p.trace, p.comm_mode != kCommNone, 0);
   if (p.copy_rows > 0 && static_cast<int>(blockIdx.y) < p.copy_rows) {   // staged all-gather: copier CTA
     ag_copier<BN>(p);
     return;
@@ -81,13 +88,15 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) cycle_mark(p.trace, p.comm_mode != kCommNone, 1);
   if (threadIdx.x == 0) pdl_launch_dependents();
   // the producer waits later, after prefetching weight tiles (a fused collective reads its epoch
   // word below, which the previous call writes, so there every warp waits first)
   const bool fused_call = p.comm_mode != kCommNone || p.ag_world > 1;
   if (warp != 0 || fused_call) pdl_wait();
+  if (threadIdx.x == 64) cycle_mark(p.trace, p.comm_mode != kCommNone, 2);
   const unsigned int epoch_now = (p.comm_mode != kCommNone || p.ag_world > 1) ? *p.epoch + 1u : 0u;
-  trace_mark(p.trace, epoch_now, 0);
+  if (fused_call) trace_mark(p.trace, epoch_now, 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -225,9 +234,9 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     asm volatile("bar.sync 1, 128;" ::: "memory");   // the four warps: row_ss complete before it is used
   }
   // ---------------------------------------------------------------- epilogue (epilogue.cuh)
-  if (warp >= 2) epilogue_tmem_to_smem<BN, DUAL>(p, accum_bar, tmem_base, stage_f32, aborted, warp, lane, row_ss);
+  if (warp >= 2) epilogue_tmem_to_smem<BN, DUAL>(p, accum_bar, tmem_base, stage_f32, aborted, warp, lane, row_ss, red);
   __syncthreads();
-  epilogue_reduce_store<BN, DUAL>(p, stage_f32, aborted, n0, t0, epoch_now, p.T, row_ss);
+  epilogue_reduce_store<BN, DUAL>(p, stage_f32, aborted, n0, t0, epoch_now, p.T, row_ss, red);
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
@@ -237,7 +246,9 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
 
 template <int BN, int STAGES, bool DUAL>
 constexpr int smem_bytes() {
-  return STAGES * (BM * 128 * (DUAL ? 2 : 1) + BN * 128) + (2 * STAGES + 1) * 8 + 16 + BN * 4 + 1024;
+  constexpr bool red = BN <= 64 || (BN == 128 && !DUAL);   // tile shapes that may run split-K carry the exchange area
+  return STAGES * (BM * 128 * (DUAL ? 2 : 1) + BN * 128) + (2 * STAGES + 1) * 8 + 16 + BN * 4 + 16 + 1024 +
+         (red ? ((DUAL ? 2 : 1) * red_tile_floats<BN>() + 2 * (BN + 8)) * 4 : 0);
 }
 
 // Split-K choice.  A cluster of S CTAs must be co-scheduled inside one GPC, so the number of
@@ -310,7 +321,7 @@ int dispatch(int bn, const CUtensorMap& tw, const TokenMaps& tx, const GemmParam
   switch (bn) {
     case 16: return launch<16, DUAL ? 5 : 8, DUAL>(tw, tx, p, s);
     case 32: return launch<32, DUAL ? 5 : 8, DUAL>(tw, tx, p, s);
-    case 64: return launch<64, DUAL ? 4 : 6, DUAL>(tw, tx, p, s);
+    case 64: return launch<64, DUAL ? 3 : 6, DUAL>(tw, tx, p, s);
     case 128: return launch<128, DUAL ? 2 : 3, DUAL>(tw, tx, p, s);
     default: return launch<256, DUAL ? 3 : 4, DUAL>(tw, tx, p, s);
   }
@@ -380,7 +391,7 @@ static int fi_dense_gemm_impl(const void* X, const void* W, void* C, const void*
   p.dual_rows = dual_rows; p.act = act; p.out_fp32 = out_fp32; p.is_fp16 = dtype == 1;
   p.splits = splits; p.status = status;
   p.tile_expert = nullptr; p.tile_row0 = nullptr; p.tile_rows = nullptr; p.n_tiles = nullptr; p.expert_rows = 0; p.grid_tiles = 0;
-  p.comm_mode = 0; p.world = 1; p.rank = 0; p.rows_per_rank = 0; p.xfer_16bit = 0; p.comm_phases = 0; p.trace = nullptr;
+  p.comm_mode = 0; p.world = 1; p.rank = 0; p.rows_per_rank = 0; p.xfer_16bit = 0; p.comm_phases = 0; p.trace = g_plain_trace;
   p.rms_eps = rms_eps; p.w_dynamic = w_dynamic;
   p.x_full = nullptr; p.ag_flags = nullptr; p.copy_rows = 0;
   for (int d = 0; d < kMaxRanks; ++d) p.x_peers[d] = 0;
@@ -423,6 +434,13 @@ static int fi_dense_gemm_impl(const void* X, const void* W, void* C, const void*
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (dual_rows > 0) return dispatch<true>(bn, tw, tx, p, s);
   return dispatch<false>(bn, tw, tx, p, s);
+}
+
+// Phase trace of plain GEMM launches (per-stage profile spans of the hot GEMM): `trace` is a device array of
+// 8 unsigned 64-bit words, or null to switch the trace off.  Every later launch overwrites it.
+extern "C" int fi_dense_gemm_set_trace(void* trace) {
+  g_plain_trace = reinterpret_cast<unsigned long long*>(trace);
+  return 0;
 }
 
 extern "C" int fi_dense_gemm(const void* X, const void* W, void* C, const void* bias,
