@@ -28,6 +28,9 @@ def main():
     ap.add_argument("--tp", type=int, default=1, help="shard the shapes as tensor parallelism of this size would")
     ap.add_argument("--sweep", action="store_true")
     ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--chains", type=int, default=0,
+                    help="> 0: run whole layers (qkv, o_proj, gate|up, down in order) as this many independent "
+                         "token-slice chains on as many streams inside one graph and print the time per layer")
     ap.add_argument("--trace", action="store_true",
                     help="also print the phase trace of the last launch's first CTA (cycles between marks)")
     args = ap.parse_args()
@@ -45,6 +48,56 @@ def main():
 
     shapes = {"qkv(+rmsnorm)": ("plain_norm", Q, H), "o_proj(+residual)": ("residual", H, H // tp),
               "gate|up(+rmsnorm, silu*up)": ("gated_norm", I, H), "down(+residual)": ("residual", H, I)}
+    if args.chains > 0:
+        C = args.chains
+        Tc = T // C
+        layers = []
+        for _ in range(L):
+            layers.append({n: rnd((2 * N) if k.startswith("gated") else N, K) for n, (k, N, K) in shapes.items()})
+        xs = [{n: rnd(Tc, K, scale=0.5) for n, (k, N, K) in shapes.items()} for _ in range(C)]
+        rs = [{n: rnd(Tc, N, scale=0.5) for n, (k, N, K) in shapes.items()} for _ in range(C)]
+        os_ = [{n: torch.empty(Tc, N, dtype=bf, device=dev) for n, (k, N, K) in shapes.items()} for _ in range(C)]
+        streams = [torch.cuda.Stream() for _ in range(C)]
+
+        def chain(c):
+            for lw in layers:
+                for n, (kind, N, K) in shapes.items():
+                    if kind == "plain_norm":
+                        ops.linear(xs[c][n], lw[n], out=os_[c][n], rms_eps=1e-5)
+                    elif kind == "residual":
+                        ops.linear(xs[c][n], lw[n], residual=rs[c][n], out=os_[c][n])
+                    else:
+                        ops.gated_linear(xs[c][n], lw[n], "silu", out=os_[c][n], rms_eps=1e-5)
+
+        def all_chains():
+            cur = torch.cuda.current_stream()
+            for c, st in enumerate(streams):
+                st.wait_stream(cur)
+                with torch.cuda.stream(st):
+                    chain(c)
+            for st in streams:
+                cur.wait_stream(st)
+
+        all_chains()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            all_chains()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ops.check_status(dev)
+        us = e0.elapsed_time(e1) * 1e3 / (args.reps * L)
+        wbytes = sum(w.numel() * 2 for w in layers[0].values())
+        print(json.dumps({"chains": C, "tokens_per_chain": Tc, "layers": L, "us_per_layer_all_chains": round(us, 2),
+                          "weights_mb_per_layer": round(wbytes / 1e6, 1),
+                          "roofline_us_weights_once": round(wbytes / 6536e3, 2)}))
+        return
     results = {}
     for name, (kind, N, K) in shapes.items():
         ws = [rnd((2 * N) if kind.startswith("gated") else N, K) for _ in range(L)]
