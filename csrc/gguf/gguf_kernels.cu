@@ -1,4 +1,4 @@
-// GGUF block-format kernels for sm_100a (Q8_0, Q2_K, IQ2_XXS): dense dequantisation, a
+// GGUF block-format kernels for sm_100a (Q8_0, Q2_K, IQ2_XXS, Q4_0, Q4_K, Q6_K): dense dequantisation, a
 // weight-streaming GEMV for up to 8 activation rows, and the routed-expert variants (gate|up with
 // the clamped SiLU gate, down projection) that read the raw expert payloads in place.
 //
@@ -79,6 +79,35 @@ __device__ __forceinline__ void decode8(const uint8_t* blk, int v0, float* out, 
     const uint8_t* q = blk + 16 + n * 32 + l;
 #pragma unroll
     for (int j = 0; j < 8; ++j) out[j] = dl * static_cast<float>((q[j] >> (2 * s)) & 3) - ml;
+  } else if (TYPE == 2) {   // Q4_0: values 0..15 are the low nibbles of the 16 bytes, 16..31 the high nibbles
+    const float d = h2f(blk);
+    const uint8_t* q = blk + 2 + (v0 & 15);
+    const int sh = (v0 >> 4) * 4;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[j] = d * static_cast<float>(static_cast<int>((q[j] >> sh) & 0x0F) - 8);
+  } else if (TYPE == 12) {   // Q4_K: chunk c = v/64 shares 32 bytes, half h = (v%64)/32 picks the nibble, sub-block 2c+h
+    const int c = v0 >> 6, h = (v0 & 63) >> 5, l = v0 & 31, sb = 2 * c + h;
+    const uint8_t* s12 = blk + 4;
+    int sc, mn;
+    if (sb < 4) { sc = s12[sb] & 63; mn = s12[sb + 4] & 63; }
+    else { sc = (s12[sb + 4] & 0x0F) | ((s12[sb - 4] >> 6) << 4); mn = (s12[sb + 4] >> 4) | ((s12[sb] >> 6) << 4); }
+    const float dl = h2f(blk) * static_cast<float>(sc);
+    const float ml = h2f(blk + 2) * static_cast<float>(mn);
+    const uint8_t* q = blk + 16 + c * 32 + l;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[j] = dl * static_cast<float>((q[j] >> (4 * h)) & 0x0F) - ml;
+  } else if (TYPE == 14) {   // Q6_K: half n = v/128, quarter qt = (v%128)/32, l = v%32
+    const int n = v0 >> 7, qt = (v0 & 127) >> 5, l = v0 & 31;
+    const uint8_t* ql = blk + 64 * n + l + ((qt & 1) ? 32 : 0);
+    const uint8_t* qh = blk + 128 + 32 * n + l;
+    const int8_t sc = reinterpret_cast<const int8_t*>(blk + 192)[8 * n + (l >> 4) + 2 * qt];
+    const float dl = h2f(blk + 208) * static_cast<float>(sc);
+    const int lsh = (qt >> 1) * 4, hsh = 2 * qt;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int q = static_cast<int>((ql[j] >> lsh) & 0x0F) | (static_cast<int>((qh[j] >> hsh) & 3) << 4);
+      out[j] = dl * static_cast<float>(q - 32);
+    }
   } else {   // IQ2_XXS: group ib = v/32, row l = (v%32)/8
     const int ib = v0 >> 5, l = (v0 & 31) >> 3;
     const uint8_t* q = blk + 2 + ib * 8;
@@ -98,6 +127,9 @@ template <int TYPE> struct Blk;
 template <> struct Blk<8> { static constexpr int kVals = 32, kBytes = 34; };
 template <> struct Blk<10> { static constexpr int kVals = 256, kBytes = 84; };
 template <> struct Blk<16> { static constexpr int kVals = 256, kBytes = 66; };
+template <> struct Blk<2> { static constexpr int kVals = 32, kBytes = 18; };
+template <> struct Blk<12> { static constexpr int kVals = 256, kBytes = 144; };
+template <> struct Blk<14> { static constexpr int kVals = 256, kBytes = 210; };
 
 template <int TYPE, typename T>
 __global__ void dequant_kernel(const uint8_t* __restrict__ raw, long row_stride, int K, T* __restrict__ out) {
@@ -176,7 +208,7 @@ __global__ void gemv_kernel(const T* __restrict__ x, long ldx, const uint8_t* __
 // chunk go through plain loads), so the 34/66/84-byte blocks are fetched with full-width
 // transactions and decoded from shared memory.
 template <int TYPE> struct Chunk {
-  static constexpr int kVals = TYPE == 8 ? 1024 : 4096;                       // values per chunk
+  static constexpr int kVals = Blk<TYPE>::kVals == 32 ? 1024 : (Blk<TYPE>::kBytes > 100 ? 2048 : 4096);   // values per chunk
   static constexpr int kBytes = kVals / Blk<TYPE>::kVals * Blk<TYPE>::kBytes;
   static constexpr int kBuf = (kBytes + 16 + 15) / 16 * 16;                   // + room to keep the 16-byte phase
 };
@@ -306,8 +338,12 @@ __device__ __forceinline__ const uint8_t* stage_row(const uint8_t* g, int K, uin
   cp_async_commit();
   return d;
 }
+__host__ __device__ constexpr int blk_vals(int type) { return (type == 8 || type == 2) ? 32 : 256; }
+__host__ __device__ constexpr int blk_bytes(int type) {
+  return type == 8 ? 34 : type == 2 ? 18 : type == 10 ? 84 : type == 12 ? 144 : type == 14 ? 210 : 66;
+}
 __host__ __device__ constexpr int row_buf_bytes(int type, int K) {
-  return ((K / (type == 8 ? 32 : 256)) * (type == 8 ? 34 : type == 10 ? 84 : 66) + 16 + 15) / 16 * 16;
+  return ((K / blk_vals(type)) * blk_bytes(type) + 16 + 15) / 16 * 16;
 }
 
 template <int TG, int TU, typename T>
@@ -388,13 +424,16 @@ __global__ void moe_down_kernel(const T* __restrict__ a, const uint8_t* __restri
     case 8: { constexpr int TY = 8; __VA_ARGS__; break; }   \
     case 10: { constexpr int TY = 10; __VA_ARGS__; break; } \
     case 16: { constexpr int TY = 16; __VA_ARGS__; break; } \
+    case 2: { constexpr int TY = 2; __VA_ARGS__; break; }   \
+    case 12: { constexpr int TY = 12; __VA_ARGS__; break; } \
+    case 14: { constexpr int TY = 14; __VA_ARGS__; break; } \
     default: return -11;                                \
   }
 
 extern "C" int fi_gguf_dequant(const void* raw, int type, int rows, int K, long row_stride, void* out, int dtype,
                                void* stream) {
   if (rows <= 0) return 0;
-  if (K % 256 != 0 && !(type == 8 && K % 32 == 0)) return -10;
+  if (K % 256 != 0 && !((type == 8 || type == 2) && K % 32 == 0)) return -10;
   if (int rc = ensure_tables()) return rc;
   const uint8_t* r = static_cast<const uint8_t*>(raw);
   FI_TYPE_SWITCH(type, {

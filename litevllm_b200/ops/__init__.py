@@ -22,6 +22,45 @@ _status_words: dict[int, torch.Tensor] = {}
 _launches = [0]
 
 
+# FI_BOUNDS_CHECK=1: every op that follows an index tensor (block tables, cache slots, token ids, row
+# indices) first validates it against the extent of the buffer it indexes and raises an IndexError that
+# names the operand, the offending value and its position.  The checks read the tensors back (one
+# synchronisation per op), so this is a debugging mode: it finds the bad table entry that a memory
+# checker would report as an out-of-bounds access, before the kernel is launched.
+_BOUNDS_CHECK = os.environ.get("FI_BOUNDS_CHECK", "0") == "1"
+
+
+def set_bounds_check(on: bool) -> None:
+    global _BOUNDS_CHECK
+    _BOUNDS_CHECK = bool(on)
+
+
+def _check_index(name: str, idx: torch.Tensor, lo: int, hi: int, what: str) -> None:
+    """Raise unless every element of ``idx`` lies in ``[lo, hi)``."""
+    if idx is None or idx.numel() == 0:
+        return
+    bad = (idx < lo) | (idx >= hi)
+    if bool(bad.any()):
+        pos = torch.nonzero(bad)[0].tolist()
+        val = int(idx[tuple(pos)])
+        raise IndexError(f"{name}: value {val} at position {pos} is outside [{lo}, {hi}) ({what})")
+
+
+def _check_paged(name: str, block_tables, seq_lens, k_cache, cu_q=None) -> None:
+    num_blocks, bs = k_cache.shape[0], k_cache.shape[2]
+    cap = block_tables.shape[1] * bs
+    _check_index(name + ".seq_lens", seq_lens, 0, cap + 1, f"block table holds {cap} tokens per sequence")
+    # only the entries a sequence's length reaches are followed by the kernels
+    need = (seq_lens.to(torch.int64) + bs - 1) // bs
+    cols = torch.arange(block_tables.shape[1], device=block_tables.device)
+    used = cols[None, :] < need[:, None]
+    ids = torch.where(used, block_tables.to(torch.int64), torch.zeros_like(block_tables, dtype=torch.int64))
+    _check_index(name + ".block_tables", ids, 0, num_blocks, f"KV pool has {num_blocks} blocks")
+    if cu_q is not None:
+        d = cu_q[1:] - cu_q[:-1]
+        _check_index(name + ".cu_q (differences)", d, 0, 1 << 30, "query offsets must not decrease")
+
+
 def launch_count() -> int:
     """Number of native kernel launches issued by this process through the op layer (launches
     recorded while a CUDA graph is being captured count once; replays are counted by the caller)."""
@@ -248,6 +287,10 @@ def rope_and_cache(qkv, positions, cos_sin, slot_mapping, k_cache, v_cache, nh, 
         return reference.rope_and_cache(qkv, positions, cos_sin, slot_mapping, k_cache, v_cache, nh,
                                         nkv, hd, rot_dim, freq_stream, q_norm_w, k_norm_w,
                                         qk_norm_mode, v_norm, eps, k_scale, v_scale)
+    if _BOUNDS_CHECK:
+        _check_index("rope_and_cache.slot_mapping", slot_mapping, -(1 << 31), k_cache.shape[0] * k_cache.shape[2],
+                     "flat slots of the KV pool; negative = skip")
+        _check_index("rope_and_cache.positions", positions, 0, cos_sin.shape[0], "rows of the cos/sin table")
     T = qkv.shape[0]
     assert qkv.is_contiguous() and positions.dtype == torch.int32
     assert slot_mapping.dtype == torch.int32
@@ -262,6 +305,9 @@ def rope_and_cache(qkv, positions, cos_sin, slot_mapping, k_cache, v_cache, nh, 
 
 def reshape_and_cache(k, v, slot_mapping, k_cache, v_cache, k_scale=1.0, v_scale=1.0):
     """k, v: [T, nkv, hd] (last two dims contiguous)."""
+    if _BOUNDS_CHECK:
+        _check_index("reshape_and_cache.slot_mapping", slot_mapping, -(1 << 31), k_cache.shape[0] * k_cache.shape[2],
+                     "flat slots of the KV pool; negative = skip")
     if not k.is_cuda:
         return reference.reshape_and_cache(k, v, slot_mapping, k_cache, v_cache, k_scale, v_scale)
     T, nkv, hd = k.shape
@@ -309,6 +355,8 @@ def paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, nh, nkv,
                            max_kv_len=None, cu_q=None):
     """One query token per sequence.  q: [B, >= nh*hd] with row stride q.stride(0)."""
     B = seq_lens.shape[0]
+    if _BOUNDS_CHECK:
+        _check_paged("paged_attention_decode", block_tables, seq_lens, k_cache)
     if not q.is_cuda:
         cu = torch.arange(B + 1, dtype=torch.int32)
         y = reference.paged_attention(q, k_cache, v_cache, block_tables, seq_lens, cu, nh, nkv, hd,
@@ -367,6 +415,8 @@ def paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, nh, nkv,
 def paged_attention_prefill(q, k_cache, v_cache, block_tables, seq_lens, cu_q, max_q_len, nh, nkv,
                             hd, sm_scale, window=0, softcap=0.0, k_scale=1.0, v_scale=1.0, out=None):
     """Varlen causal attention of new tokens against the paged cache (which already holds them)."""
+    if _BOUNDS_CHECK:
+        _check_paged("paged_attention_prefill", block_tables, seq_lens, k_cache, cu_q)
     if not q.is_cuda:
         y = reference.paged_attention(q, k_cache, v_cache, block_tables, seq_lens, cu_q, nh, nkv, hd,
                                       sm_scale, window, softcap, k_scale, v_scale)
@@ -390,6 +440,8 @@ def paged_attention_prefill(q, k_cache, v_cache, block_tables, seq_lens, cu_q, m
 
 # ---------------------------------------------------------------------------- small ops
 def embedding(ids, table, scale=1.0, vocab_start=0, vocab_end=None, out=None):
+    if _BOUNDS_CHECK and vocab_start == 0 and vocab_end is None:
+        _check_index("embedding.ids", ids, 0, table.shape[0], "rows of the embedding table")
     if not table.is_cuda:
         y = reference.embedding(ids, table, scale, vocab_start, vocab_end)
         if out is not None:
@@ -450,6 +502,8 @@ def slot_mapping(positions, token_seq, block_tables, block_size, out=None):
 def gather_rows_i32(table, idx, out):
     """``out[r] = table[idx[r]]`` for int32 ``table`` [n, cols], int32 ``idx`` [rows] (out-of-range
     indices are clamped): the block-table rows of a decode batch."""
+    if _BOUNDS_CHECK:
+        _check_index("gather_rows_i32.idx", idx, 0, table.shape[0], "rows of the table")
     if not table.is_cuda:
         out.copy_(table.index_select(0, idx.long().clamp_(0, table.shape[0] - 1)))
         return out

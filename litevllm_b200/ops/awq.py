@@ -87,7 +87,16 @@ class Int4Weight:
             self.nib, self.scales, self.zeros = nib, scales, zeros
 
     def dense(self) -> torch.Tensor:
-        return dequantize(self.nib, self.scales, self.zeros, self.group)
+        """float32 [N, K]; rebuilt from the runtime layout when the loading-time tensors were dropped."""
+        if self.nib is not None:
+            return dequantize(self.nib, self.scales, self.zeros, self.group)
+        w = self.qw.to(torch.int64) & 0xFFFFFFFF
+        cols = []
+        for i in range(4):                       # word = sum_i col[2i] << 4i | col[2i+1] << (16 + 4i)
+            cols += [(w >> (4 * i)) & 0xF, (w >> (16 + 4 * i)) & 0xF]
+        nib = torch.stack(cols, dim=-1).reshape(self.N, self.K).to(torch.uint8)
+        zeros = self.zeros_t.t().contiguous() if self.zeros_t is not None else None
+        return dequantize(nib, self.scales_t.t().contiguous(), zeros, self.group)
 
 
 def int4_linear(x: torch.Tensor, w: Int4Weight, bias=None, residual=None, act=None, gated_act=None,

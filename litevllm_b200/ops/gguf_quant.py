@@ -7,8 +7,16 @@ points (csrc/gguf/gguf_kernels.cu).
   IQ2_XXS 66 B / 256 values: fp16 d, 8 groups of 32 values: 4 grid-row bytes + a 32-bit word holding
                              4 x 7-bit sign indices and a 4-bit scale;
                              value = d * (0.5 + scale) * 0.25 * grid[row][j] * sign
+  Q4_0    18 B / 32 values : fp16 d, 16 bytes: value j = low nibble of byte j, value j+16 = high
+                             nibble;  value = d * (q - 8)
+  Q4_K    144 B / 256 values: fp16 d, fp16 dmin, 12 bytes of 6-bit (scale, min) pairs for 8 sub-blocks
+                             of 32, 128 bytes of nibbles (64 values share 32 bytes: low nibbles first);
+                             value = d * sc * q - dmin * m
+  Q6_K    210 B / 256 values: 128 bytes of low nibbles, 64 bytes of 2-bit high parts, 16 int8 scales,
+                             fp16 d;  value = d * sc * (q - 32)
 The block layouts are GGML's (reference decoders: vllm/model_executor/models/deepseek_v4_flash/
-quant.py:61-453).  Activations are kept in 16/32-bit floats (no Q8_K activation round trip).
+quant.py:61-453 and vllm/model_executor/layers/quantization/tensor.py:782-833).  Activations are kept
+in 16/32-bit floats (no Q8_K activation round trip).
 """
 from __future__ import annotations
 
@@ -17,9 +25,11 @@ import torch
 
 from . import _DT, _count, _lib, _p, _stream
 
-GGML_TYPES = {"F32": 0, "F16": 1, "Q8_0": 8, "Q2_K": 10, "IQ2_XXS": 16, "I32": 26, "BF16": 30}
+GGML_TYPES = {"F32": 0, "F16": 1, "Q4_0": 2, "Q8_0": 8, "Q2_K": 10, "Q4_K": 12, "Q6_K": 14, "IQ2_XXS": 16, "I32": 26,
+              "BF16": 30}
 TYPE_NAMES = {v: k for k, v in GGML_TYPES.items()}
-BLOCK = {8: (32, 34), 10: (256, 84), 16: (256, 66)}     # type -> (values per block, bytes per block)
+# type -> (values per block, bytes per block)
+BLOCK = {2: (32, 18), 8: (32, 34), 10: (256, 84), 12: (256, 144), 14: (256, 210), 16: (256, 66)}
 
 _KSIGNS = None
 _GRID = None
@@ -69,6 +79,35 @@ def dequantize(raw: torch.Tensor, ggml_type: int, K: int) -> torch.Tensor:
         sh = torch.tensor([0, 2, 4, 6], device=raw.device, dtype=torch.uint8).view(1, 1, 1, 4, 1)
         codes = ((qs.reshape(rows, -1, 2, 1, 32) >> sh) & 3).reshape(rows, -1, 16, 16).float()
         return (dl[..., None] * codes - ml[..., None]).reshape(rows, K)
+    if ggml_type == 2:
+        d = _f16(blk[..., 0:2])
+        qs = blk[..., 2:]
+        q = torch.cat([qs & 0x0F, qs >> 4], dim=-1).float() - 8.0
+        return (d[..., None] * q).reshape(rows, K)
+    if ggml_type == 12:
+        d, dmin = _f16(blk[..., 0:2]), _f16(blk[..., 2:4])
+        sb = blk[..., 4:16].long()                                      # 12 bytes -> 8 x (6-bit scale, 6-bit min)
+        sc_lo, mn_lo = sb[..., 0:4] & 63, sb[..., 4:8] & 63
+        sc_hi = (sb[..., 8:12] & 0x0F) | ((sb[..., 0:4] >> 6) << 4)
+        mn_hi = (sb[..., 8:12] >> 4) | ((sb[..., 4:8] >> 6) << 4)
+        sc = torch.cat([sc_lo, sc_hi], dim=-1).float()                  # [.., 8]
+        mn = torch.cat([mn_lo, mn_hi], dim=-1).float()
+        qs = blk[..., 16:].reshape(rows, -1, 4, 32)                     # 4 chunks of 64 values share 32 bytes each
+        q = torch.stack([qs & 0x0F, qs >> 4], dim=-2).reshape(rows, -1, 8, 32).float()   # sub-block = 2 * chunk + half
+        y = d[..., None, None] * sc[..., None] * q - dmin[..., None, None] * mn[..., None]
+        return y.reshape(rows, K)
+    if ggml_type == 14:
+        ql = blk[..., 0:128].reshape(rows, -1, 2, 64)                   # two halves of 128 values
+        qh = blk[..., 128:192].reshape(rows, -1, 2, 32)
+        sc = blk[..., 192:208].contiguous().view(torch.int8).float().reshape(rows, -1, 2, 8)
+        d = _f16(blk[..., 208:210])
+        lo = torch.stack([ql[..., 0:32] & 0x0F, ql[..., 32:64] & 0x0F, ql[..., 0:32] >> 4, ql[..., 32:64] >> 4], dim=-2)
+        hi = torch.stack([(qh >> s_) & 3 for s_ in (0, 2, 4, 6)], dim=-2)
+        q = (lo | (hi << 4)).float() - 32.0                              # [.., half, quarter, 32]
+        # scale of value l in quarter qt: sc[l // 16 + 2 * qt]
+        scq = sc.reshape(rows, -1, 2, 4, 2)                              # [.., half, quarter, l // 16]
+        scv = scq[..., None].expand(*scq.shape, 16).reshape(rows, -1, 2, 4, 32)
+        return (d[..., None, None, None] * scv * q).reshape(rows, K)
     if ggml_type == 16:
         ksigns, grid = _tables()
         ksigns, grid = ksigns.to(raw.device), grid.to(raw.device)
@@ -107,8 +146,13 @@ def random_blocks(ggml_type: int, rows: int, K: int, seed: int, scale: float = 0
     raw = torch.randint(0, 256, (rows, nblk, nb), generator=g, device=device, dtype=torch.int16).to(torch.uint8)
     d = (torch.rand(rows, nblk, generator=g, device=device) * scale + scale * 0.1).to(torch.float16)
     dbytes = d.view(torch.uint8).reshape(rows, nblk, 2)
-    if ggml_type == 8:
+    if ggml_type in (2, 8):
         raw[..., 0:2] = dbytes
+    elif ggml_type == 12:
+        raw[..., 0:2] = (d * 0.05).to(torch.float16).view(torch.uint8).reshape(rows, nblk, 2)
+        raw[..., 2:4] = (d * 0.1).to(torch.float16).view(torch.uint8).reshape(rows, nblk, 2)
+    elif ggml_type == 14:
+        raw[..., 208:210] = (d * 0.02).to(torch.float16).view(torch.uint8).reshape(rows, nblk, 2)
     elif ggml_type == 10:
         raw[..., 80:82] = dbytes
         raw[..., 82:84] = (d * 0.5).to(torch.float16).view(torch.uint8).reshape(rows, nblk, 2)

@@ -313,3 +313,26 @@ def test_tokenizer_helpers_and_incremental_detokenizer():
                                      "text_config": {"hidden_size": 8, "model_type": "gemma4_text"},
                                      "vision_config": {"patch_size": 16}})
     assert flat["hidden_size"] == 8 and flat["vision_config"]["patch_size"] == 16 and is_gguf_path("a/b.GGUF")
+
+
+def test_bounds_check_mode_names_the_bad_index():
+    """FI_BOUNDS_CHECK mode: index tensors are validated against the buffers they index before an op runs."""
+    from litevllm_b200 import ops
+    ops.set_bounds_check(True)
+    try:
+        kc = torch.zeros(9, 2, 16, 8)
+        vc = torch.zeros_like(kc)
+        q = torch.randn(2, 4 * 8)
+        bt = torch.tensor([[1, 2, 0], [3, 99, 0]], dtype=torch.int32)
+        with pytest.raises(IndexError, match=r"block_tables: value 99 at position \[1, 1\]"):
+            ops.paged_attention_decode(q, kc, vc, bt, torch.tensor([20, 17], dtype=torch.int32), 4, 2, 8, 0.3)
+        # the same table is fine while the second sequence stays inside its first block
+        ops.paged_attention_decode(q, kc, vc, bt, torch.tensor([20, 16], dtype=torch.int32), 4, 2, 8, 0.3)
+        with pytest.raises(IndexError, match="seq_lens"):
+            ops.paged_attention_decode(q, kc, vc, bt, torch.tensor([20, 49], dtype=torch.int32), 4, 2, 8, 0.3)
+        with pytest.raises(IndexError, match="embedding.ids"):
+            ops.embedding(torch.tensor([0, 7, 12]), torch.zeros(12, 4))
+        with pytest.raises(IndexError, match="slot_mapping"):
+            ops.reshape_and_cache(torch.zeros(1, 2, 8), torch.zeros(1, 2, 8), torch.tensor([9 * 16], dtype=torch.int32), kc, vc)
+    finally:
+        ops.set_bounds_check(False)

@@ -127,3 +127,59 @@ def test_deepseek_gguf_file_end_to_end(tmp_path):
     from_file = [o.outputs[0].token_ids for o in LLM(str(f), **kw).generate(prompts, sp)]
     in_memory = [o.outputs[0].token_ids for o in LLM("synthetic:tiny-deepseek-test", **kw).generate(prompts, sp)]
     assert from_file == in_memory
+
+
+# ----------------------------------------------------------------------------- block decoders, weights, policy
+@pytest.mark.parametrize("name", ["Q4_0", "Q4_K", "Q6_K", "Q8_0", "Q2_K", "IQ2_XXS"])
+def test_block_decoders_match_the_gguf_package(name):
+    """The PyTorch reference decoder of every supported block type against the ``gguf`` package's own
+    numpy decoder (bit-exact: both are straight transcriptions of the block layouts)."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    ty = gq.GGML_TYPES[name]
+    raw = gq.random_blocks(ty, 7, 768, seed=11)
+    mine = gq.dequantize(raw, ty, 768)
+    want = torch.from_numpy(quants.dequantize(raw.numpy(), getattr(gguf.GGMLQuantizationType, name)))
+    assert torch.equal(mine, want)
+
+
+def test_gguf_weight_policy_and_audit_cpu():
+    from litevllm_b200.layers.quantization import tensor as qt
+    K, N = 256, 24
+    raw = gq.random_blocks(gq.GGML_TYPES["Q4_K"], N, K, seed=2)
+    w = qt.GGUFWeight(raw, "Q4_K", K, prefix="model.layers.0.mlp.down_proj")
+    x = torch.randn(5, K)
+    want = x @ gq.dequantize(raw, 12, K).t()
+    qt.reset_runtime_stats()
+    qt.enable_audit(True)
+    try:
+        pol_all = qt.resolve_execution_policy(scope="all")
+        pol_attn = qt.resolve_execution_policy(scope="attention_only")
+        pol_hf = qt.resolve_execution_policy(scope="all", high_fidelity_prefixes=("down_proj",))
+        assert qt.should_use_native_path(w.prefix, pol_all) == (True, "scope all")
+        assert qt.should_use_native_path(w.prefix, pol_attn)[0] is False
+        assert qt.should_use_native_path("model.layers.0.self_attn.qkv_proj", pol_attn)[0] is True
+        assert qt.should_use_native_path(w.prefix, pol_hf) == (False, "high-fidelity prefix 'down_proj'")
+        with pytest.raises(ValueError):
+            qt.resolve_execution_policy(scope="sometimes")
+        for pol in (pol_all, pol_attn, pol_attn, pol_hf):
+            y = w.matmul(x, policy=pol)
+            assert torch.allclose(y, want, atol=1e-4, rtol=1e-4)
+        summ = qt.audit_summary()
+        assert summ["counters"]["gguf.native"] == 1 and summ["counters"]["gguf.dense"] == 1
+        assert summ["counters"]["gguf.dense_cached"] == 2          # the dense copy was reused twice
+        row = summ["prefixes"][w.prefix]
+        assert row["calls"] == 4 and row["tokens"] == 20 and row["native"] == 1 and row["dense"] == 3
+        assert summ["recent_events"][-1]["reason"].startswith("high-fidelity")
+        assert summ["dense_cache"]["entries"] >= 1
+    finally:
+        qt.enable_audit(False)
+        qt.clear_global_weight_cache()
+    with pytest.raises(ValueError):
+        qt.GGUFWeight(raw[:, :-1], "Q4_K", K)
+    # byte-bounded LRU
+    c = qt.LRUWeightCache(max_size=8, max_bytes=4 * 100 * 4)
+    for i in range(6):
+        c.put(i, torch.zeros(100))
+    assert c.get_memory_stats()["entries"] == 4 and c.get(0) is None and c.get(5) is not None
+    assert c.put(99, torch.zeros(10000)) is False

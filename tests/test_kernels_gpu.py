@@ -358,7 +358,7 @@ def test_fused_experts_int4(T, E, K, H, I, e_lo, e_n):
     ops.check_status(x.device)
 
 
-@pytest.mark.parametrize("tname", ["Q8_0", "Q2_K", "IQ2_XXS"])
+@pytest.mark.parametrize("tname", ["Q8_0", "Q2_K", "IQ2_XXS", "Q4_0", "Q4_K", "Q6_K"])
 def test_gguf_dequant_and_gemv(tname):
     from litevllm_b200.ops import gguf_quant as gq
     ty = gq.GGML_TYPES[tname]
@@ -371,6 +371,16 @@ def test_gguf_dequant_and_gemv(tname):
         x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
         y = gq.gguf_linear(x, raw, ty, K, out_dtype=torch.float32)
         _close(y.cpu(), x.float().cpu() @ want.t(), 3e-2, 3e-2 * float(want.abs().max()) * 8, f"gemv {tname} M{M}")
+    # the same bytes behind the weight interface: native path and (high-fidelity prefix) dense path
+    from litevllm_b200.layers.quantization import tensor as qt
+    w = qt.GGUFWeight(raw, tname, K, prefix="model.layers.0.mlp.down_proj")
+    x = (torch.randn(6, K, device=DEV) * 0.5).bfloat16()
+    ref_y = x.float().cpu() @ want.t()
+    tol = 3e-2 * float(want.abs().max()) * 8
+    _close(w.matmul(x, out_dtype=torch.float32).cpu(), ref_y, 3e-2, tol, f"GGUFWeight native {tname}")
+    hf = qt.resolve_execution_policy(scope="all", high_fidelity_prefixes=("down_proj",))
+    _close(w.matmul(x, policy=hf).float().cpu(), ref_y, 3e-2, tol, f"GGUFWeight dense {tname}")
+    qt.clear_global_weight_cache()
 
 
 def test_q8_0_quantize_roundtrip():
