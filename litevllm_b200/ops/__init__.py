@@ -155,6 +155,14 @@ def linear(x, w, bias=None, residual=None, act=None, out=None, out_dtype=None, s
     if T == 0:
         return out
     assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    if residual is not None and residual.data_ptr() != out.data_ptr() and residual.stride(0) != out.stride(0):
+        # the kernels index the residual with the output's row pitch
+        if out.is_contiguous():
+            residual = residual.contiguous()
+        else:
+            tmp = torch.empty_strided(out.shape, out.stride(), dtype=residual.dtype, device=out.device)
+            tmp.copy_(residual)
+            residual = tmp
     if rms_eps > 0:
         rc = _lib.kernels().fi_dense_gemm_rmsnorm(
             _p(x), _p(w), _p(out), _p(bias), _p(residual), T, N, K, x.stride(0), w.stride(0),
@@ -367,6 +375,12 @@ def paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, nh, nkv,
         return y
     if out is None:
         out = torch.empty(B, nh * hd, dtype=q.dtype, device=q.device)
+    elif not out.is_contiguous():
+        # the kernels write rows of nh * hd values back to back
+        tmp = paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, nh, nkv, hd, sm_scale, window,
+                                     softcap, k_scale, v_scale, None, splits, max_kv_len, cu_q)
+        out.copy_(tmp)
+        return out
     if splits <= 0:
         if max_kv_len is None:
             max_kv_len = block_tables.shape[1] * k_cache.shape[2]
@@ -428,6 +442,11 @@ def paged_attention_prefill(q, k_cache, v_cache, block_tables, seq_lens, cu_q, m
     B = seq_lens.shape[0]
     if out is None:
         out = torch.empty(T, nh * hd, dtype=q.dtype, device=q.device)
+    elif not out.is_contiguous():
+        tmp = paged_attention_prefill(q, k_cache, v_cache, block_tables, seq_lens, cu_q, max_q_len, nh, nkv, hd,
+                                      sm_scale, window, softcap, k_scale, v_scale, None)
+        out.copy_(tmp)
+        return out
     rc = _lib.kernels().fi_paged_prefill(
         _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(block_tables), _p(seq_lens),
         _p(cu_q), B, int(max_q_len), nh, nkv, hd, block_tables.shape[1], k_cache.shape[2],

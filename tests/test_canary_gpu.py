@@ -12,7 +12,7 @@ from litevllm_b200.ops import reference as ref
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
-SENTINEL = -1234.0
+SENTINEL = -1024.0      # exactly representable in bf16 and fp16
 
 
 class Guarded:
@@ -133,7 +133,7 @@ def test_attention_and_cache_writes_stay_inside():
     cs = ref.build_cos_sin(hd, 256, 10000.0).to(DEV)
     ops.rope_and_cache(qkv, pos, cs, slots, kc, vc, nh, nkv, hd, hd)
     for splits in (1, 2, 3):
-        out = Guarded(B, nh * hd, torch.bfloat16)
+        out = Guarded(B, nh * hd, torch.bfloat16, pad_cols=0)      # contiguous rows: guard rows above and below
         ops.paged_attention_decode(qkv[:B], kc, vc, bt, sl, nh, nkv, hd, scale, out=out.view, splits=splits,
                                    max_kv_len=max(lens))
         torch.cuda.synchronize()
