@@ -158,7 +158,8 @@ class DecodeExecutor:
             input_ids=d["ids"], positions=d["meta"][0], slot_mapping=d["meta"][1], block_tables=d["block_tables"],
             seq_lens=d["meta"][2], cu_q=None, logits_indices=None, num_seqs=bucket, num_tokens=bucket, max_q_len=1,
             max_kv_len=max_kv_len, is_decode=True, config=self.builder.cfg,
-            request_ids=[st.request_id for st in reqs], extras={"num_real": len(reqs), "bucket": bucket})
+            request_ids=[st.request_id for st in reqs],
+            extras={"num_real": len(reqs), "bucket": bucket, "slot_ids": d["meta"][3]})
         if not self.use_cuda_graph:
             self.eager_steps += 1
             return self._step_body(batch, greedy_only=True)

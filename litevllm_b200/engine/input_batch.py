@@ -125,7 +125,8 @@ class InputBatchBuilder:
             block_tables=block_tables, seq_lens=dm[base + B + 1:base + 2 * B + 1], cu_q=cu,
             logits_indices=(cu[1:] - 1).long(), num_seqs=B, num_tokens=T, max_q_len=max(q_lens),
             max_kv_len=max(kv_lens), is_decode=False, config=self.cfg,
-            request_ids=[it.request_id for it in items], seq_lens_cpu=kv_lens, q_lens_cpu=q_lens)
+            request_ids=[it.request_id for it in items], seq_lens_cpu=kv_lens, q_lens_cpu=q_lens,
+            extras={"slot_ids": slot_ids})
 
     # ------------------------------------------------------------------ decode
     def _decode_buffers(self, bucket: int) -> dict:
@@ -178,4 +179,4 @@ class InputBatchBuilder:
             block_tables=d["block_tables"], seq_lens=d["meta"][2], cu_q=None, logits_indices=None,
             num_seqs=bucket, num_tokens=bucket, max_q_len=1, max_kv_len=max(kv_lens) if kv_lens else 1,
             is_decode=True, config=self.cfg, request_ids=[st.request_id for st in reqs],
-            seq_lens_cpu=kv_lens, q_lens_cpu=[1] * n, extras={"num_real": n, "bucket": bucket})
+            seq_lens_cpu=kv_lens, q_lens_cpu=[1] * n, extras={"num_real": n, "bucket": bucket, "slot_ids": d["meta"][3]})

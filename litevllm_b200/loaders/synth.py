@@ -201,7 +201,21 @@ def iter_qwen35_weights(arch: ModelArch, seed: int = 0, dtype=torch.float32, dev
             yield p + "self_attn.k_proj.weight", w(p + "k", arch.num_kv_heads * hd, H)
             yield p + "self_attn.v_proj.weight", w(p + "v", arch.num_kv_heads * hd, H)
             yield p + "self_attn.o_proj.weight", w(p + "o", H, arch.num_heads * hd)
-        yield p + "mlp.gate_proj.weight", w(p + "g", I, H)
-        yield p + "mlp.up_proj.weight", w(p + "u", I, H)
-        yield p + "mlp.down_proj.weight", w(p + "d", H, I)
+        if arch.moe.num_experts > 0:
+            EI = arch.moe.expert_intermediate
+            yield p + "mlp.gate.weight", w(p + "router", arch.moe.num_experts, H, std=0.5)
+            for ex in range(arch.moe.num_experts):
+                yield p + f"mlp.experts.{ex}.gate_proj.weight", w(p + f"eg{ex}", EI, H)
+                yield p + f"mlp.experts.{ex}.up_proj.weight", w(p + f"eu{ex}", EI, H)
+                yield p + f"mlp.experts.{ex}.down_proj.weight", w(p + f"ed{ex}", H, EI)
+            if arch.moe.shared_intermediate > 0:
+                SI = arch.moe.shared_intermediate
+                yield p + "mlp.shared_expert.gate_proj.weight", w(p + "sg", SI, H)
+                yield p + "mlp.shared_expert.up_proj.weight", w(p + "su", SI, H)
+                yield p + "mlp.shared_expert.down_proj.weight", w(p + "sd", H, SI)
+                yield p + "mlp.shared_expert_gate.weight", w(p + "sgate", 1, H, std=0.5)
+        else:
+            yield p + "mlp.gate_proj.weight", w(p + "g", I, H)
+            yield p + "mlp.up_proj.weight", w(p + "u", I, H)
+            yield p + "mlp.down_proj.weight", w(p + "d", H, I)
     yield "lm_head.weight", w("lm_head", V, H)

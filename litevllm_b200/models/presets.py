@@ -86,6 +86,9 @@ PRESETS["tiny-qwen35-test"] = {
     "full_attention_interval": 4, "linear_num_key_heads": 2, "linear_num_value_heads": 4, "linear_key_head_dim": 32,
     "linear_value_head_dim": 32, "linear_conv_kernel_dim": 4, "attn_output_gate": True, "eos_token_id": 1,
 }
+PRESETS["tiny-qwen35-moe-test"] = dict(PRESETS["tiny-qwen35-test"], architectures=["Qwen3_5MoeForCausalLM"],
+                                      num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128,
+                                      shared_expert_intermediate_size=128, norm_topk_prob=True)
 PRESETS["tiny-qwen3-test"] = dict(PRESETS["tiny-llama-test"], architectures=["Qwen3ForCausalLM"], model_type="qwen3",
                                   head_dim=64)
 PRESETS["tiny-qwen2vl-test"] = dict(PRESETS["tiny-llama-test"], architectures=["Qwen2VLForConditionalGeneration"],
