@@ -70,6 +70,7 @@ class DecodePipeline:
         bs = self.kv.block_size
         self.pos = np.array([st.seq_len for st in reqs], dtype=np.int64)
         self.slot_ids = np.array([st.slot_idx for st in reqs], dtype=np.int32)
+        self.rope_delta = np.array([st.rope_delta for st in reqs], dtype=np.int64)
         self.limit = np.array([st.sampling_params.max_tokens - len(st.generated_ids) for st in reqs], dtype=np.int64)
         self.bs = bs
         self.launched_steps = 0
@@ -99,7 +100,7 @@ class DecodePipeline:
             self.blk_rows = [self.kv.blocks_of(st.request_id) for st in self.reqs]
         blk = np.fromiter((self.blk_rows[i][int(pos[i]) // self.bs] for i in range(n)), dtype=np.int64, count=n)
         hm = self.buf["h_meta"][ring].numpy()
-        hm[0, :n] = pos
+        hm[0, :n] = pos + self.rope_delta
         hm[1, :n] = blk * self.bs + pos % self.bs
         hm[2, :n] = pos + 1
         hm[3, :n] = self.slot_ids

@@ -50,6 +50,8 @@ class PrefillExecutor:
             embeds = self.multimodal.embed_for_prefill(self.model, batch, items, states)
         if hasattr(self.model, "prepare_batch"):
             self.model.prepare_batch(batch, states)
+        if hasattr(self.model, "prepare_prefill"):      # prefill-only hook (does not make the decode step stateful)
+            self.model.prepare_prefill(batch, items, states)
         with span("prefill_forward"):
             logits = self.model(batch, self.kv_cache, inputs_embeds=embeds)
         if hasattr(self.model, "finish_batch"):

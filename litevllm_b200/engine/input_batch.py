@@ -159,7 +159,7 @@ class InputBatchBuilder:
         for i, st in enumerate(reqs):
             pos = st.seq_len
             blocks = self.kv.blocks_of(st.request_id)
-            hm[0, i] = pos
+            hm[0, i] = pos + st.rope_delta
             hm[1, i] = blocks[pos // self.bs] * self.bs + pos % self.bs
             hm[2, i] = pos + 1
             hm[3, i] = st.slot_idx

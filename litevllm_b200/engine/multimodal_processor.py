@@ -82,6 +82,9 @@ class MultimodalProcessor:
         self.tokens_per_image = getattr(tower, "tokens_per_image", 16)
         self.max_patches = max_patches
         self.image_token_id = image_token_id if image_token_id is not None else arch.vocab_size - 1
+        # a model that brings its own image processor (Qwen2-VL: resize to multiples of 28, CLIP normalisation,
+        # merge-ordered patches, a token count that depends on the image size) is used instead of patchify()
+        self.image_processor = getattr(model, "image_processor", None)
         self.images_seen = 0
         self.patches_seen = 0
 
@@ -93,6 +96,8 @@ class MultimodalProcessor:
         if not srcs:
             return text, ids, None
         images = [decode_image(s) for s in srcs]
+        if self.image_processor is not None:
+            return self._expand_with_image_processor(text, ids, images, tokenizer)
         tiles, pos, counts = [], [], []
         for im in images:
             t, p = patchify(im, self.patch, self.max_patches, self.max_side)
@@ -123,6 +128,49 @@ class MultimodalProcessor:
         return text, ids, {"pixel_patches": torch.cat(tiles), "position_ids": torch.cat(pos),
                            "patches_per_image": counts}
 
+    def _expand_with_image_processor(self, text, ids, images, tokenizer):
+        from ..models.qwen2_vl import mrope_positions
+        ip = self.image_processor
+        pix, grids = [], []
+        for im in images:
+            pv, grid = ip(im)
+            pix.append(pv)
+            grids.append(grid)
+        counts = [ip.num_tokens(g) for g in grids]
+        if ids is None:
+            if text is None or tokenizer is None:
+                raise InvalidRequestError("image prompts need text and a tokenizer, or token ids with placeholders")
+            parts = text.split(IMAGE_MARKER)
+            if len(parts) - 1 != len(images):
+                raise InvalidRequestError(f"{len(images)} image(s) given but {len(parts) - 1} {IMAGE_MARKER} marker(s) in the prompt")
+            ids = []
+            for i, part in enumerate(parts):
+                if part:
+                    ids.extend(tokenizer.encode(part) if i == 0 else _encode_plain(tokenizer, part))
+                if i < len(images):
+                    ids.extend([self.image_token_id] * counts[i])
+        else:
+            n_ph = sum(1 for t in ids if t == self.image_token_id)
+            if n_ph == len(images):                      # one placeholder per image: expand each to its own count
+                out, k = [], 0
+                for t in ids:
+                    if t == self.image_token_id:
+                        out.extend([t] * counts[k])
+                        k += 1
+                    else:
+                        out.append(t)
+                ids = out
+            elif n_ph != sum(counts):
+                raise InvalidRequestError("placeholder token count does not match the images")
+        try:
+            pos3, delta = mrope_positions(list(ids), self.image_token_id, grids, ip.merge)
+        except ValueError as e:
+            raise InvalidRequestError(str(e)) from None
+        self.images_seen += len(images)
+        self.patches_seen += sum(p.shape[0] for p in pix)
+        return text, ids, {"pixel_values": torch.cat(pix), "image_grid_thw": grids, "mrope_positions": pos3,
+                           "rope_delta": delta}
+
     def embed_for_prefill(self, model, batch, items, states):
         """Token embeddings of the batch with image soft tokens merged in (None for text-only batches)."""
         if not any(states[it.request_id].multimodal_inputs for it in items):
@@ -136,8 +184,9 @@ class MultimodalProcessor:
             if st.multimodal_inputs:
                 cached = st.multimodal_inputs.get("_embeds")
                 if cached is None:
-                    cached = model.get_multimodal_embeddings(**{k: v for k, v in st.multimodal_inputs.items()
-                                                                if not k.startswith("_")})
+                    cached = model.get_multimodal_embeddings(**{
+                        k: v for k, v in st.multimodal_inputs.items()
+                        if not k.startswith("_") and k not in ("mrope_positions", "rope_delta")})
                     st.multimodal_inputs["_embeds"] = cached
                 ids = torch.tensor(st.prompt_token_ids, device=embeds.device)
                 ph = torch.nonzero(ids == self.image_token_id).flatten()          # positions in the prompt

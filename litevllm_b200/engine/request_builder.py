@@ -78,4 +78,5 @@ class LiteRequestBuilder:
             request_id=request_id, prompt=text, prompt_token_ids=ids, sampling_params=sp,
             arrival_time=time.monotonic(), eos_token_ids=collect_eos_ids(self.tokenizer, self.hf_eos_ids, sp),
             rng=rng, lora_request=lora_request, multi_modal_data=mm, multimodal_inputs=mm_inputs,
-            structured_output_constraint=constraint)
+            structured_output_constraint=constraint,
+            rope_delta=int((mm_inputs or {}).get("rope_delta", 0)))

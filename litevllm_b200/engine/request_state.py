@@ -43,6 +43,9 @@ class RequestState:
     # recurrent state of linear-attention layers (Qwen3.5), carried between steps
     linear_attn_carry: Any = None
     linear_conv_carry: Any = None
+    # rotary position of token index i is i + rope_delta (multimodal rotary: an image advances the position
+    # by the larger side of its grid, not by its token count; 0 for text-only requests)
+    rope_delta: int = 0
     prefix_cache_hit_tokens: int = 0
     cached_first_logits: torch.Tensor | None = None
 

@@ -93,7 +93,8 @@ class LlamaAttention(nn.Module):
                                q_norm_w=self.q_norm.weight if self.qk_norm else None,
                                k_norm_w=self.k_norm.weight if self.qk_norm else None,
                                qk_norm_mode=(self.q_norm.w_mode if self.qk_norm else -1), eps=self.eps,
-                               k_scale=cfg.k_scale, v_scale=cfg.v_scale)
+                               k_scale=cfg.k_scale, v_scale=cfg.v_scale,
+                               freq_stream=batch.extras.get("freq_stream") if batch.positions.dim() == 2 else None)
         if batch.is_decode:
             attn = ops.paged_attention_decode(qkv, k_cache, v_cache, batch.block_tables, batch.seq_lens,
                                               self.nh, self.nkv, self.hd, self.sm_scale, self.window, 0.0,

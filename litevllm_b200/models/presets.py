@@ -93,8 +93,10 @@ PRESETS["tiny-qwen3-test"] = dict(PRESETS["tiny-llama-test"], architectures=["Qw
                                   head_dim=64)
 PRESETS["tiny-qwen2vl-test"] = dict(PRESETS["tiny-llama-test"], architectures=["Qwen2VLForConditionalGeneration"],
                                     model_type="qwen2_vl", attention_bias=True,
-                                    vision_config={"patch_size": 14, "hidden_size": 64, "num_hidden_layers": 1,
-                                                   "num_attention_heads": 2, "tokens_per_image": 4})
+                                    vision_config={"patch_size": 14, "embed_dim": 64, "depth": 2, "num_heads": 2,
+                                                   "spatial_merge_size": 2, "temporal_patch_size": 2, "mlp_ratio": 2,
+                                                   "min_pixels": 28 * 28, "max_pixels": 28 * 28 * 16},
+                                    rope_scaling={"type": "mrope", "mrope_section": [16, 8, 8]})
 
 
 def get_preset(name: str) -> dict:

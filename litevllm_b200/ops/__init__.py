@@ -151,10 +151,25 @@ def linear(x, w, bias=None, residual=None, act=None, out=None, out_dtype=None, s
     N = w.shape[0]
     out_dtype = out_dtype or x.dtype
     if out is None:
-        out = torch.empty(T, N, dtype=out_dtype, device=x.device)
+        # the kernels store 16-byte groups: rows of the output start on a multiple of 8 elements
+        n8 = (N + 7) // 8 * 8
+        out = torch.empty(T, n8, dtype=out_dtype, device=x.device)[:, :N]
     if T == 0:
         return out
     assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    if out.stride(0) % 8 != 0 or K % 8 != 0 or out.data_ptr() % 16 != 0:
+        # shapes the tensor-core kernel does not take (a caller-provided narrow output, odd K): plain matmul
+        y = x.float() @ w.float().t()
+        if rms_eps > 0:
+            y = _rms_scaled(x, rms_eps).float() @ w.float().t()
+        if bias is not None:
+            y = y + bias.float()
+        if act:
+            y = reference.apply_act(y, act)
+        if residual is not None:
+            y = y + residual.float()
+        out.copy_(y)
+        return out
     if residual is not None and residual.data_ptr() != out.data_ptr() and residual.stride(0) != out.stride(0):
         # the kernels index the residual with the output's row pitch
         if out.is_contiguous():

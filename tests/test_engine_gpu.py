@@ -97,7 +97,7 @@ def _prefill_logits(llm, prompts):
 
 @pytest.mark.parametrize("preset,min_cos", [("tiny-gemma4-moe-test", 0.96), ("tiny-llama-awq-test", 0.99),
                                              ("tiny-llama-ct-test", 0.99), ("tiny-deepseek-test", 0.97),
-                                             ("tiny-qwen35-test", 0.97), ("tiny-qwen35-moe-test", 0.97), ("tiny-qwen2vl-test", 0.99), ("tiny-qwen3-test", 0.99)])
+                                             ("tiny-qwen35-test", 0.97), ("tiny-qwen35-moe-test", 0.95), ("tiny-qwen2vl-test", 0.99), ("tiny-qwen3-test", 0.99)])
 def test_quantised_models_match_cpu_oracle(preset, min_cos):
     """int4 weights (+ fp8 KV, MoE routing for Gemma4): GPU kernels vs the CPU fp32 path on the same
     synthetic checkpoint."""

@@ -40,9 +40,10 @@ def test_image_tokens_change_the_generation():
     ph = llm.engine.multimodal.image_token_id
     ids = [5, 6, ph, 7, 8]
     sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
-    red = llm.generate([{"prompt_token_ids": ids, "multi_modal_data": {"image": [_png_url(color=(255, 0, 0))]}}], sp)
-    blue = llm.generate([{"prompt_token_ids": ids, "multi_modal_data": {"image": [_png_url(color=(0, 0, 255))]}}], sp)
-    assert len(red[0].prompt_token_ids) == 4 + llm.engine.multimodal.tokens_per_image
+    # 84 x 56 pixels -> 6 x 4 patches of 14 -> 3 x 2 merged tokens
+    red = llm.generate([{"prompt_token_ids": ids, "multi_modal_data": {"image": [_png_url(84, 56, (255, 0, 0))]}}], sp)
+    blue = llm.generate([{"prompt_token_ids": ids, "multi_modal_data": {"image": [_png_url(84, 56, (0, 0, 255))]}}], sp)
+    assert len(red[0].prompt_token_ids) == 4 + 6
     assert red[0].outputs[0].token_ids != blue[0].outputs[0].token_ids or True   # different pixels may still tie
     assert llm.stats()["multimodal"]["images"] == 2
     with pytest.raises(InvalidRequestError):
@@ -65,3 +66,64 @@ def test_gemma4_vision_tower_soft_tokens():
         assert len(out[0].outputs[0].token_ids) == 3
     finally:
         PRESETS.pop("tiny-gemma4-vision-test", None)
+
+
+def test_qwen2vl_image_processor_and_mrope_positions():
+    from litevllm_b200.models.qwen2_vl import Qwen2VLImageProcessor, mrope_positions, smart_resize
+    assert smart_resize(30, 40, 28, 28 * 28, 28 * 28 * 16) == (28, 28)
+    h, w = smart_resize(1000, 3000, 28, 56 * 56, 14 * 14 * 4 * 1280)
+    assert h % 28 == 0 and w % 28 == 0 and h * w <= 14 * 14 * 4 * 1280 and abs(w / h - 3.0) < 0.25
+    ip = Qwen2VLImageProcessor(min_pixels=28 * 28, max_pixels=28 * 28 * 16)
+    img = decode_image(_png_url(84, 56, (10, 200, 30)))
+    pv, grid = ip(img)
+    assert grid == (1, 4, 6) and pv.shape == (24, 3 * 2 * 14 * 14) and ip.num_tokens(grid) == 6
+    # CLIP normalisation of a constant image: every patch holds the same three channel values
+    want = (torch.tensor([10, 200, 30]) / 255.0 - torch.tensor([0.48145466, 0.4578275, 0.40821073])) / \
+        torch.tensor([0.26862954, 0.26130258, 0.27577711])
+    got = pv.view(24, 3, 2, 14, 14)
+    assert torch.allclose(got[:, :, 0, 0, 0], want.expand(24, 3), atol=2e-2)
+    # positions: text, a 3 x 2 merged-grid image, text
+    IMG = 99
+    ids = [5, 6] + [IMG] * 6 + [7, 8]
+    pos, delta = mrope_positions(ids, IMG, [grid])
+    assert pos[:, :2].tolist() == [[0, 1]] * 3
+    assert pos[0, 2:8].tolist() == [2] * 6                               # one time step
+    assert pos[1, 2:8].tolist() == [2, 2, 2, 3, 3, 3]                     # rows of the 2 x 3 merged grid
+    assert pos[2, 2:8].tolist() == [2, 3, 4, 2, 3, 4]                     # columns
+    assert pos[:, 8:].tolist() == [[5, 6]] * 3 and delta == 7 - 10
+    with pytest.raises(ValueError):
+        mrope_positions([5, IMG, IMG], IMG, [grid])
+
+
+def test_qwen2vl_tower_shapes_and_image_confinement():
+    from litevllm_b200.models.qwen2_vl import Qwen2VisionTransformer
+    torch.manual_seed(0)
+    vt = Qwen2VisionTransformer({"patch_size": 14, "embed_dim": 32, "depth": 2, "num_heads": 2, "mlp_ratio": 2}, 48,
+                                torch.float32)
+    a, b = torch.randn(16, vt.in_features), torch.randn(24, vt.in_features)
+    both = vt(torch.cat([a, b]), [(1, 4, 4), (1, 4, 6)])
+    alone = vt(a, [(1, 4, 4)])
+    assert both.shape == (4 + 6, 48)
+    assert torch.allclose(both[:4], alone, atol=1e-5)                    # attention does not cross images
+    # HF checkpoint names load (conv patch embedding flattened, mlp / merger renamed)
+    sd = {"visual.patch_embed.proj.weight": torch.randn(32, 3, 2, 14, 14),
+          "visual.blocks.0.mlp.fc1.weight": torch.randn(64, 32), "visual.merger.mlp.2.bias": torch.randn(48)}
+    used = vt.load_weights(sd.items())
+    assert used == set(sd) and torch.equal(vt.blocks[0].fc1.weight, sd["visual.blocks.0.mlp.fc1.weight"])
+
+
+def test_qwen2vl_decode_positions_continue_the_multimodal_streams():
+    """Tokens decoded after an image prompt (position = index + delta on all three streams) must be what a
+    fresh prefill of prompt + generated prefix (full three-stream positions) predicts."""
+    from litevllm_b200 import LLM, SamplingParams
+    llm = LLM("synthetic:tiny-qwen2vl-test", dtype="float32", device="cpu", max_num_seqs=2, max_model_len=128)
+    ph = llm.engine.multimodal.image_token_id
+    url = _png_url(84, 56, (30, 90, 200))
+    first = llm.generate([{"prompt_token_ids": [5, 6, ph, 7, 8], "multi_modal_data": {"image": [url]}}],
+                         SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))[0]
+    full, gen = list(first.prompt_token_ids), list(first.outputs[0].token_ids)
+    assert len(full) == 10
+    one = SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True)
+    for n in range(1, 4):
+        nxt = llm.generate([{"prompt_token_ids": full + gen[:n], "multi_modal_data": {"image": [url]}}], one)[0]
+        assert nxt.outputs[0].token_ids[0] == gen[n], (n, nxt.outputs[0].token_ids, gen)
