@@ -14,7 +14,10 @@ from .errors import BackgroundLoopError
 
 class AsyncDriver:
     def __init__(self, engine, lock: threading.RLock, min_step_interval_s: float = 0.001,
-                 idle_timeout_s: float = 1.0, sleep_fn=time.sleep):
+                 idle_timeout_s: float = 1.0, sleep_fn=time.sleep, coordinator=None):
+        # coordinator (multi-rank serving, rank 0 only): told before every step which requests were admitted or
+        # aborted since the last one, so that the worker ranks can mirror this engine step by step
+        self.coordinator = coordinator
         self.engine = engine
         self.lock = lock
         self.min_step_interval_s = min_step_interval_s
@@ -45,7 +48,10 @@ class AsyncDriver:
         while self._running:
             try:
                 with self.lock:
-                    busy = self.engine.has_unfinished_requests()
+                    if self.coordinator is not None:
+                        busy = self.coordinator.before_step(self.engine)
+                    else:
+                        busy = self.engine.has_unfinished_requests()
                     if busy:
                         self.engine.step()
                         self.steps += 1
@@ -67,7 +73,9 @@ class AsyncDriver:
                     self._wake.get(timeout=self.idle_timeout_s)
                     self.idle_wakeups += 1
                 except queue.Empty:
-                    pass
+                    if self.coordinator is not None:      # a quiet server still tells its workers that it is alive
+                        with self.lock:
+                            self.coordinator.keepalive()
                 # drain extra wake tokens
                 while True:
                     try:
@@ -80,6 +88,9 @@ class AsyncDriver:
         return self._running and self._thread is not None and self._thread.is_alive()
 
     def shutdown(self, timeout: float = 5.0) -> None:
+        if self.coordinator is not None:
+            with self.lock:
+                self.coordinator.shutdown()
         self._running = False
         self._wake.put(0)
         t = self._thread

@@ -19,14 +19,29 @@ from .protocol import EngineClient
 class AsyncLLM(EngineClient):
     def __init__(self, vllm_config, engine: LiteEngine | None = None, tokenizer=None, start_driver: bool = True):
         self.vllm_config = vllm_config
+        # several ranks: join the job first (process group, symmetric heap), then build this rank's engine;
+        # rank 0 gets a coordinator that mirrors its request stream to the workers (parallel/serving.py)
+        self._parallel = None
+        self.coordinator = None
+        self.channel = None
+        if engine is None and vllm_config.parallel_config.is_distributed:
+            from ..parallel.launcher import init_distributed_engine
+            from ..parallel.serving import ServingCoordinator, make_channel
+            self._parallel = init_distributed_engine(vllm_config)
+            self.channel = make_channel(self._parallel.state)
+            if self._parallel.state.rank == 0:
+                self.coordinator = ServingCoordinator(self.channel)
         self.engine = engine or LiteEngine(vllm_config)
+        if self._parallel is not None:
+            self._parallel.attach(self.engine)
         self.engine_lock = self.engine.lock
         mc = vllm_config.model_config
         self.tokenizer = tokenizer or get_tokenizer(mc.tokenizer, mc.trust_remote_code, mc.revision,
                                                     vocab_size=mc.arch.vocab_size)
         self.engine.set_tokenizer(self.tokenizer)
         self.driver = AsyncDriver(self.engine, self.engine_lock,
-                                  vllm_config.runtime_config.async_driver_min_step_interval_s)
+                                  vllm_config.runtime_config.async_driver_min_step_interval_s,
+                                  coordinator=self.coordinator)
         self._start_driver = start_driver
         self._closed = False
 
@@ -38,10 +53,24 @@ class AsyncLLM(EngineClient):
         return self.vllm_config.model_config
 
     # ------------------------------------------------------------------ request path
+    @property
+    def is_worker_rank(self) -> bool:
+        return self._parallel is not None and self._parallel.state.rank != 0
+
+    def serve_as_worker(self, on_step=None) -> int:
+        """Worker ranks of a multi-rank server: mirror rank 0 until it shuts down."""
+        from ..parallel.serving import worker_serve_loop
+        return worker_serve_loop(self.engine, self.channel, on_step)
+
     def _submit_sync(self, request_id, prompt, sampling_params, lora_request, multi_modal_data, loop):
+        if self.coordinator is not None:
+            self.coordinator.check_supported(lora_request, multi_modal_data)
+            sampling_params = self.coordinator.prepare_params(sampling_params)
         with self.engine_lock:
-            self.engine.add_request(request_id, prompt, sampling_params, lora_request=lora_request,
-                                    multi_modal_data=multi_modal_data, loop=loop)
+            st = self.engine.add_request(request_id, prompt, sampling_params, lora_request=lora_request,
+                                         multi_modal_data=multi_modal_data, loop=loop)
+            if self.coordinator is not None:
+                self.coordinator.record_request(st)
 
     async def submit(self, prompt, sampling_params, request_id: str, lora_request=None, multi_modal_data=None) -> None:
         if self._closed:
@@ -79,7 +108,8 @@ class AsyncLLM(EngineClient):
         def _do():
             with self.engine_lock:
                 for rid in ids:
-                    self.engine.abort_request(rid)
+                    if self.engine.abort_request(rid) and self.coordinator is not None:
+                        self.coordinator.record_abort(rid)
         await asyncio.to_thread(_do)
 
     # ------------------------------------------------------------------ admin
@@ -108,3 +138,5 @@ class AsyncLLM(EngineClient):
         self._closed = True
         self.driver.shutdown()
         self.engine.shutdown()
+        if self._parallel is not None:
+            self._parallel.shutdown()

@@ -314,6 +314,11 @@ def main(argv: list[str] | None = None) -> None:
     engine = build_engine(args.model, **kw)
     served_model = args.model
     debug_endpoints_enabled = args.enable_debug_endpoints
+    if getattr(engine, "is_worker_rank", False):
+        # launched with one process per GPU (torchrun): only rank 0 listens; the others mirror its engine
+        engine.serve_as_worker()
+        engine.shutdown()
+        return
     import uvicorn
     uvicorn.run(app, host=args.host, port=args.port, log_level="info")
 
