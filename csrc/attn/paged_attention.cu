@@ -100,7 +100,13 @@ struct AttnParams {
   float* ws_ml;             // decode partials [B, nh, splits, 2]
   int max_blocks, block_size, nh, nkv, window;  // window <= 0: none
   float sm_scale, softcap, k_scale, v_scale;
+  // kv_fp8 is the cache format: 0 = 16-bit, 1 = e4m3 with one scale per tensor (k_scale / v_scale),
+  // 2 = e4m3 with one scale per (token, kv head) row, 3 = packed int4 (low nibbles = first half of the
+  // channels, high nibbles = second half, two's complement in [-7, 7]) with one scale per row.
+  // Formats 2 and 3 read their fp32 row scales from k_scales / v_scales [num_blocks, nkv, block_size].
   int kv_fp8, splits;
+  const float* k_scales;
+  const float* v_scales;
   // optional [B * gridDim.y] zero-initialised tickets: the split CTA that arrives last merges the
   // partials itself (and resets the ticket), so no separate merge launch is needed
   unsigned int* merge_tickets;
@@ -115,8 +121,38 @@ struct AttnParams {
 template <typename T, int HD, int ROWS, int THREADS>
 __device__ __forceinline__ void load_kv_tile(T* tile, const void* cache, const int* bt,
                                              int block_size, int nkv, int kvh, int tok0, int lo,
-                                             int hi, bool fp8) {
+                                             int hi, int fp8, const float* scales = nullptr) {
   constexpr int CPR = HD / 8;  // 16-byte chunks (of 16-bit elements) per row
+  if (fp8 == 3) {
+    // packed int4 with a scale per row: 16 bytes hold channels [16c, 16c+16) in their low nibbles and
+    // channels [HD/2 + 16c, HD/2 + 16c + 16) in their high nibbles
+    constexpr int CPR4 = HD / 32;
+    for (int i = threadIdx.x; i < ROWS * CPR4; i += THREADS) {
+      const int r = i / CPR4, c = i % CPR4;
+      const int tok = tok0 + r;
+      const bool valid = tok >= lo && tok < hi;
+      uint4 raw = make_uint4(0, 0, 0, 0);
+      float sc = 0.f;
+      if (valid) {
+        const int blk = bt[tok / block_size];
+        const long rowi = (static_cast<long>(blk) * nkv + kvh) * block_size + tok % block_size;
+        raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(cache) + rowi * (HD / 2) + c * 16);
+        sc = scales[rowi];
+      }
+      const uint8_t* b = reinterpret_cast<const uint8_t*>(&raw);
+      T lo16[16], hi16[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        lo16[j] = MmaT<T>::from_f(static_cast<float>(static_cast<int>((b[j] & 0x0F) ^ 8) - 8) * sc);
+        hi16[j] = MmaT<T>::from_f(static_cast<float>(static_cast<int>((b[j] >> 4) ^ 8) - 8) * sc);
+      }
+      *reinterpret_cast<uint4*>(tile + tile_off<HD>(r, 2 * c)) = *reinterpret_cast<uint4*>(&lo16[0]);
+      *reinterpret_cast<uint4*>(tile + tile_off<HD>(r, 2 * c + 1)) = *reinterpret_cast<uint4*>(&lo16[8]);
+      *reinterpret_cast<uint4*>(tile + tile_off<HD>(r, HD / 16 + 2 * c)) = *reinterpret_cast<uint4*>(&hi16[0]);
+      *reinterpret_cast<uint4*>(tile + tile_off<HD>(r, HD / 16 + 2 * c + 1)) = *reinterpret_cast<uint4*>(&hi16[8]);
+    }
+    return;
+  }
   if (!fp8) {
     for (int i = threadIdx.x; i < ROWS * CPR; i += THREADS) {
       const int r = i / CPR, c = i % CPR;
@@ -137,17 +173,18 @@ __device__ __forceinline__ void load_kv_tile(T* tile, const void* cache, const i
       const int tok = tok0 + r;
       const bool valid = tok >= lo && tok < hi;
       uint4 raw = make_uint4(0, 0, 0, 0);
+      float sc = 1.f;
       if (valid) {
         const int blk = bt[tok / block_size];
-        const uint8_t* src = reinterpret_cast<const uint8_t*>(cache) +
-                             ((static_cast<long>(blk) * nkv + kvh) * block_size + tok % block_size) * HD +
-                             c * 16;
+        const long rowi = (static_cast<long>(blk) * nkv + kvh) * block_size + tok % block_size;
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(cache) + rowi * HD + c * 16;
         raw = *reinterpret_cast<const uint4*>(src);
+        if (fp8 == 2) sc = scales[rowi];      // row-scaled e4m3: the true value is stored value x row scale
       }
       const __nv_fp8_e4m3* f8 = reinterpret_cast<const __nv_fp8_e4m3*>(&raw);
       T tmp[16];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) tmp[j] = MmaT<T>::from_f(static_cast<float>(f8[j]));
+      for (int j = 0; j < 16; ++j) tmp[j] = MmaT<T>::from_f(static_cast<float>(f8[j]) * sc);
       *reinterpret_cast<uint4*>(tile + tile_off<HD>(r, 2 * c)) = *reinterpret_cast<uint4*>(&tmp[0]);
       *reinterpret_cast<uint4*>(tile + tile_off<HD>(r, 2 * c + 1)) = *reinterpret_cast<uint4*>(&tmp[8]);
     }
@@ -202,18 +239,18 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const AttnParams p) {
 #pragma unroll
   for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
   float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
-  const float scale = p.sm_scale * (p.kv_fp8 ? p.k_scale : 1.f);
+  const float scale = p.sm_scale * (p.kv_fp8 == 1 ? p.k_scale : 1.f);
 
   if (c_begin < c_end) {
-    load_kv_tile<T, HD, CH, 128>(sK, p.k_cache, bt, p.block_size, p.nkv, kvh, c_begin * CH, lo, seq_len, p.kv_fp8);
-    load_kv_tile<T, HD, CH, 128>(sV, p.v_cache, bt, p.block_size, p.nkv, kvh, c_begin * CH, lo, seq_len, p.kv_fp8);
+    load_kv_tile<T, HD, CH, 128>(sK, p.k_cache, bt, p.block_size, p.nkv, kvh, c_begin * CH, lo, seq_len, p.kv_fp8, p.k_scales);
+    load_kv_tile<T, HD, CH, 128>(sV, p.v_cache, bt, p.block_size, p.nkv, kvh, c_begin * CH, lo, seq_len, p.kv_fp8, p.v_scales);
   }
   cp_async_commit();
   for (int c = c_begin; c < c_end; ++c) {
     const int buf = (c - c_begin) & 1;
     if (c + 1 < c_end) {
-      load_kv_tile<T, HD, CH, 128>(sK + (buf ^ 1) * CH * HD, p.k_cache, bt, p.block_size, p.nkv, kvh, (c + 1) * CH, lo, seq_len, p.kv_fp8);
-      load_kv_tile<T, HD, CH, 128>(sV + (buf ^ 1) * CH * HD, p.v_cache, bt, p.block_size, p.nkv, kvh, (c + 1) * CH, lo, seq_len, p.kv_fp8);
+      load_kv_tile<T, HD, CH, 128>(sK + (buf ^ 1) * CH * HD, p.k_cache, bt, p.block_size, p.nkv, kvh, (c + 1) * CH, lo, seq_len, p.kv_fp8, p.k_scales);
+      load_kv_tile<T, HD, CH, 128>(sV + (buf ^ 1) * CH * HD, p.v_cache, bt, p.block_size, p.nkv, kvh, (c + 1) * CH, lo, seq_len, p.kv_fp8, p.v_scales);
     }
     cp_async_commit();
     cp_async_wait<1>();
@@ -316,7 +353,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const AttnParams p) {
     }
     const int head = head0 + r;
     if (p.splits == 1) {
-      const float v = l > 0.f ? acc / l * (p.kv_fp8 ? p.v_scale : 1.f) : 0.f;
+      const float v = l > 0.f ? acc / l * (p.kv_fp8 == 1 ? p.v_scale : 1.f) : 0.f;
       reinterpret_cast<T*>(p.out)[(static_cast<long>(b) * p.nh + head) * HD + d] = MmaT<T>::from_f(v);
     } else {
       const long base = (static_cast<long>(b) * p.nh + head) * p.splits + split;
@@ -339,7 +376,7 @@ __global__ void __launch_bounds__(128) paged_decode_v2_kernel(const AttnParams p
   constexpr int TILE = 16 * HD;                      // elements of one 16-token tile
   T* sQ = reinterpret_cast<T*>(smem_raw);            // [16][HD]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool fp8 = p.kv_fp8 != 0;
+  const bool fp8 = p.kv_fp8 == 1;     // row-scaled caches (formats 2, 3) take the other decode kernel
   // per-warp regions: raw K/V stages (+ conversion tiles when the cache is fp8)
   const int raw_tile_bytes = fp8 ? TILE : TILE * 2;
   const int warp_bytes = NST * 2 * raw_tile_bytes + (fp8 ? 2 * TILE * 2 : 0);
@@ -640,7 +677,7 @@ __global__ void decode_merge_kernel(const AttnParams p) {
       acc += f * p.ws_o[(base + s) * HD + d];
       l += f * p.ws_ml[(base + s) * 2 + 1];
     }
-    const float v = l > 0.f ? acc / l * (p.kv_fp8 ? p.v_scale : 1.f) : 0.f;
+    const float v = l > 0.f ? acc / l * (p.kv_fp8 == 1 ? p.v_scale : 1.f) : 0.f;
     reinterpret_cast<T*>(p.out)[(static_cast<long>(b) * p.nh + head) * HD + d] = MmaT<T>::from_f(v);
   }
 }
@@ -680,7 +717,7 @@ __global__ void __launch_bounds__(128) paged_prefill_kernel(const AttnParams p) 
   const int lo_tile = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
   const int c_begin = lo_tile / CH;
   const int c_end = last_pos / CH + 1;
-  const float scale = p.sm_scale * (p.kv_fp8 ? p.k_scale : 1.f);
+  const float scale = p.sm_scale * (p.kv_fp8 == 1 ? p.k_scale : 1.f);
   const int row0 = qt0 + warp * 16 + (lane >> 2);  // query index (within the sequence's new tokens)
   const int posr0 = pos0 + row0, posr1 = posr0 + 8;
 
@@ -689,8 +726,8 @@ __global__ void __launch_bounds__(128) paged_prefill_kernel(const AttnParams p) 
   for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
   float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
 
-  load_kv_tile<T, HD, CH, 128>(sK, p.k_cache, bt, p.block_size, p.nkv, kvh, c_begin * CH, 0, seq_len, p.kv_fp8);
-  load_kv_tile<T, HD, CH, 128>(sV, p.v_cache, bt, p.block_size, p.nkv, kvh, c_begin * CH, 0, seq_len, p.kv_fp8);
+  load_kv_tile<T, HD, CH, 128>(sK, p.k_cache, bt, p.block_size, p.nkv, kvh, c_begin * CH, 0, seq_len, p.kv_fp8, p.k_scales);
+  load_kv_tile<T, HD, CH, 128>(sV, p.v_cache, bt, p.block_size, p.nkv, kvh, c_begin * CH, 0, seq_len, p.kv_fp8, p.v_scales);
   cp_async_commit();
   // the warp's 16 query rows stay in registers for the whole KV sweep
   __syncthreads();   // sQ was staged with plain stores by all threads
@@ -701,8 +738,8 @@ __global__ void __launch_bounds__(128) paged_prefill_kernel(const AttnParams p) 
   for (int c = c_begin; c < c_end; ++c) {
     const int buf = (c - c_begin) & 1;
     if (c + 1 < c_end) {
-      load_kv_tile<T, HD, CH, 128>(sK + (buf ^ 1) * CH * HD, p.k_cache, bt, p.block_size, p.nkv, kvh, (c + 1) * CH, 0, seq_len, p.kv_fp8);
-      load_kv_tile<T, HD, CH, 128>(sV + (buf ^ 1) * CH * HD, p.v_cache, bt, p.block_size, p.nkv, kvh, (c + 1) * CH, 0, seq_len, p.kv_fp8);
+      load_kv_tile<T, HD, CH, 128>(sK + (buf ^ 1) * CH * HD, p.k_cache, bt, p.block_size, p.nkv, kvh, (c + 1) * CH, 0, seq_len, p.kv_fp8, p.k_scales);
+      load_kv_tile<T, HD, CH, 128>(sV + (buf ^ 1) * CH * HD, p.v_cache, bt, p.block_size, p.nkv, kvh, (c + 1) * CH, 0, seq_len, p.kv_fp8, p.v_scales);
     }
     cp_async_commit();
     cp_async_wait<1>();
@@ -790,7 +827,7 @@ __global__ void __launch_bounds__(128) paged_prefill_kernel(const AttnParams p) 
   cp_async_wait<0>();
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  const float vs = p.kv_fp8 ? p.v_scale : 1.f;
+  const float vs = p.kv_fp8 == 1 ? p.v_scale : 1.f;
   const float i0 = l0 > 0.f ? vs / l0 : 0.f, i1 = l1 > 0.f ? vs / l1 : 0.f;
   T* out = reinterpret_cast<T*>(p.out);
 #pragma unroll
@@ -811,7 +848,7 @@ template <typename T, int HD>
 int launch_decode(const AttnParams& p, int B, cudaStream_t s) {
   const int G = p.nh / p.nkv;
   const int groups = (G + 15) / 16;
-  if (p.block_size % 16 == 0) {
+  if (p.block_size % 16 == 0 && p.kv_fp8 <= 1) {
     constexpr int NST = HD <= 64 ? 4 : HD <= 128 ? 3 : 2;
     const int tile = 16 * HD;
     const int raw = p.kv_fp8 ? tile : tile * 2;
@@ -841,7 +878,8 @@ int launch_decode(const AttnParams& p, int B, cudaStream_t s) {
     if (ce != cudaSuccess) return static_cast<int>(ce);
     fi::launch_kernel(kern, dim3(p.splits, p.nkv * groups, B), dim3(128), smem, s, 0, p);
   }
-  const bool merged_in_kernel = (p.merge_tickets != nullptr || (p.cluster_off != 0 && p.splits <= 8)) && p.block_size % 16 == 0;
+  const bool merged_in_kernel = (p.merge_tickets != nullptr || (p.cluster_off != 0 && p.splits <= 8)) &&
+                                p.block_size % 16 == 0 && p.kv_fp8 <= 1;
   if (p.splits > 1 && !merged_in_kernel)
     fi::launch_kernel(decode_merge_kernel<T, HD>, dim3(p.nh, B), dim3(HD >= 128 ? 128 : 64), 0, s, 0, p);
   return static_cast<int>(cudaGetLastError());
@@ -918,6 +956,67 @@ extern "C" int fi_paged_decode_merged(const void* q, long q_stride, const void* 
     if (hd == 256) FI_DEC(__half, 256);
   }
 #undef FI_DEC
+  return -11;
+}
+
+// Decode / prefill attention over a ROW-SCALED cache: kv_mode 2 = e4m3 values with one fp32 scale per
+// (token, kv head) row ("block-scaled" fp8), kv_mode 3 = packed int4 rows [.., hd / 2] bytes with one
+// scale per row.  k_scales / v_scales: fp32 [num_blocks, nkv, block_size].  The tiles are dequantised to
+// 16-bit while they are staged, the attention math is that of the 16-bit path.  Decode scratch as in
+// fi_paged_decode (ws_o / ws_ml for splits > 1).
+extern "C" int fi_paged_decode_rowscaled(const void* q, long q_stride, const void* k_cache, const void* v_cache,
+                               const float* k_scales, const float* v_scales, void* out, const int* block_tables,
+                               const int* seq_lens, float* ws_o, float* ws_ml, int B, int nh, int nkv, int hd,
+                               int max_blocks, int block_size, int window, float sm_scale, float softcap,
+                               int kv_mode, int splits, int dtype, void* stream) {
+  if (B <= 0) return 0;
+  if (nkv <= 0 || nh <= 0 || nh % nkv != 0 || splits < 1 || (kv_mode != 2 && kv_mode != 3) || hd % 32 != 0) return -10;
+  if (k_scales == nullptr || v_scales == nullptr || (splits > 1 && (ws_o == nullptr || ws_ml == nullptr))) return -12;
+  AttnParams p = {};
+  p.q = q; p.q_stride = q_stride; p.k_cache = k_cache; p.v_cache = v_cache; p.out = out;
+  p.block_tables = block_tables; p.seq_lens = seq_lens; p.cu_q = nullptr; p.ws_o = ws_o;
+  p.ws_ml = ws_ml; p.max_blocks = max_blocks; p.block_size = block_size; p.nh = nh; p.nkv = nkv;
+  p.window = window; p.sm_scale = sm_scale; p.softcap = softcap; p.k_scale = 1.f;
+  p.v_scale = 1.f; p.kv_fp8 = kv_mode; p.splits = splits; p.k_scales = k_scales; p.v_scales = v_scales;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+#define FI_DEC(TT, HD) return launch_decode<TT, HD>(p, B, s)
+  if (dtype == 0) {
+    if (hd == 64) FI_DEC(__nv_bfloat16, 64);
+    if (hd == 128) FI_DEC(__nv_bfloat16, 128);
+    if (hd == 256) FI_DEC(__nv_bfloat16, 256);
+  } else if (dtype == 1) {
+    if (hd == 64) FI_DEC(__half, 64);
+    if (hd == 128) FI_DEC(__half, 128);
+    if (hd == 256) FI_DEC(__half, 256);
+  }
+#undef FI_DEC
+  return -11;
+}
+
+extern "C" int fi_paged_prefill_rowscaled(const void* q, long q_stride, const void* k_cache, const void* v_cache,
+                                const float* k_scales, const float* v_scales, void* out, const int* block_tables,
+                                const int* seq_lens, const int* cu_q, int B, int max_q_len, int nh,
+                                int nkv, int hd, int max_blocks, int block_size, int window,
+                                float sm_scale, float softcap, int kv_mode, int dtype, void* stream) {
+  if (B <= 0 || max_q_len <= 0) return 0;
+  if (nkv <= 0 || nh <= 0 || nh % nkv != 0 || (kv_mode != 2 && kv_mode != 3) || hd % 32 != 0) return -10;
+  if (k_scales == nullptr || v_scales == nullptr) return -12;
+  AttnParams p = {};
+  p.q = q; p.q_stride = q_stride; p.k_cache = k_cache; p.v_cache = v_cache; p.out = out;
+  p.block_tables = block_tables; p.seq_lens = seq_lens; p.cu_q = cu_q; p.max_blocks = max_blocks;
+  p.block_size = block_size; p.nh = nh; p.nkv = nkv; p.window = window; p.sm_scale = sm_scale;
+  p.softcap = softcap; p.k_scale = 1.f; p.v_scale = 1.f; p.kv_fp8 = kv_mode; p.splits = 1;
+  p.k_scales = k_scales; p.v_scales = v_scales;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == 0) {
+    if (hd == 64) return launch_prefill<__nv_bfloat16, 64, 64>(p, B, max_q_len, s);
+    if (hd == 128) return launch_prefill<__nv_bfloat16, 128, 64>(p, B, max_q_len, s);
+    if (hd == 256) return launch_prefill<__nv_bfloat16, 256, 32>(p, B, max_q_len, s);
+  } else if (dtype == 1) {
+    if (hd == 64) return launch_prefill<__half, 64, 64>(p, B, max_q_len, s);
+    if (hd == 128) return launch_prefill<__half, 128, 64>(p, B, max_q_len, s);
+    if (hd == 256) return launch_prefill<__half, 256, 32>(p, B, max_q_len, s);
+  }
   return -11;
 }
 

@@ -306,6 +306,54 @@ __global__ void reshape_and_cache_kernel(const T* __restrict__ k, const T* __res
   }
 }
 
+// Row-scaled cache write: every (token, kv head) row gets its own fp32 scale.
+//   mode 2: e4m3 of value / scale with scale = max|row| / 448           ("block-scaled" fp8 KV)
+//   mode 3: packed int4, q = clamp(round(value / scale), -7, 7) with scale = max(max|row| / 7, 1e-4); byte d holds
+//           channel d in its low nibble and channel d + hd/2 in its high nibble (two's complement)
+// k, v: rows [T, nkv, hd] with pitches ldk / ldv (already rotated / normalised); caches [blocks, nkv, bs, hd or hd/2];
+// scales fp32 [blocks, nkv, bs].  One warp per (token, head).  The int4 rule is the reference's
+// (vllm/kernels/triton/reshape_and_cache.py:186-262: dynamic row-wise scale, divisor 7).
+template <typename T>
+__global__ void kv_quant_rows_kernel(const T* __restrict__ k, const T* __restrict__ v, long ldk, long ldv,
+                                     const int* __restrict__ slot_mapping, uint8_t* __restrict__ k_cache,
+                                     uint8_t* __restrict__ v_cache, float* __restrict__ k_scales,
+                                     float* __restrict__ v_scales, int nkv, int hd, int block_size, int mode) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  const int t = blockIdx.x;
+  const int slot = slot_mapping[t];
+  if (slot < 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int blk = slot / block_size, off = slot % block_size;
+  for (int item = warp; item < 2 * nkv; item += nwarps) {
+    const bool is_v = item >= nkv;
+    const int h = is_v ? item - nkv : item;
+    const T* src = (is_v ? v + static_cast<long>(t) * ldv : k + static_cast<long>(t) * ldk) + static_cast<long>(h) * hd;
+    const long rowi = (static_cast<long>(blk) * nkv + h) * block_size + off;
+    float amax = 0.f;
+    for (int i = lane; i < hd; i += 32) amax = fmaxf(amax, fabsf(Cvt<T>::to_f(src[i])));
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    uint8_t* dst = is_v ? v_cache : k_cache;
+    float* sdst = is_v ? v_scales : k_scales;
+    if (mode == 3) {
+      const float sc = fmaxf(amax / 7.f, 1e-4f);
+      const int half = hd >> 1;
+      for (int i = lane; i < half; i += 32) {
+        const int lo = static_cast<int>(fminf(fmaxf(floorf(Cvt<T>::to_f(src[i]) / sc + 0.5f), -7.f), 7.f));
+        const int hi = static_cast<int>(fminf(fmaxf(floorf(Cvt<T>::to_f(src[i + half]) / sc + 0.5f), -7.f), 7.f));
+        dst[rowi * half + i] = static_cast<uint8_t>((lo & 0x0F) | ((hi & 0x0F) << 4));
+      }
+      if (lane == 0) sdst[rowi] = sc;
+    } else {
+      const float sc = fmaxf(amax / 448.f, 1e-12f);
+      const float inv = 1.f / sc;
+      for (int i = lane; i < hd; i += 32)
+        reinterpret_cast<__nv_fp8_e4m3*>(dst)[rowi * hd + i] = __nv_fp8_e4m3(Cvt<T>::to_f(src[i]) * inv);
+      if (lane == 0) sdst[rowi] = sc;
+    }
+  }
+}
+
 // ------------------------------------------------------------------ embedding gather
 template <typename T>
 __global__ void embedding_kernel(const long* __restrict__ ids, const T* __restrict__ table,
@@ -541,6 +589,26 @@ extern "C" int fi_reshape_and_cache(const void* k, const void* v, const int* slo
         kv_fp8, k_scale, v_scale);
     return static_cast<int>(cudaGetLastError());
   });
+}
+
+// Row-scaled cache write (modes 2 and 3, see kv_quant_rows_kernel).  dtype: 0 bf16, 1 fp16 (k, v).
+extern "C" int fi_kv_quant_rows(const void* k, const void* v, long ldk, long ldv, const int* slot_mapping,
+                                void* k_cache, void* v_cache, float* k_scales, float* v_scales, int T, int nkv,
+                                int hd, int block_size, int mode, int dtype, void* stream) {
+  if (T <= 0) return 0;
+  if ((mode != 2 && mode != 3) || hd % 2 != 0 || nkv <= 0 || k_scales == nullptr || v_scales == nullptr) return -10;
+  const int threads = 2 * nkv >= 8 ? 256 : 128;
+  if (dtype == 0)
+    fi::launch_kernel(kv_quant_rows_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, FI_STREAM(stream), 0,
+                      (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, ldk, ldv, slot_mapping, (uint8_t*)k_cache,
+                      (uint8_t*)v_cache, k_scales, v_scales, nkv, hd, block_size, mode);
+  else if (dtype == 1)
+    fi::launch_kernel(kv_quant_rows_kernel<__half>, dim3(T), dim3(threads), 0, FI_STREAM(stream), 0, (const __half*)k,
+                      (const __half*)v, ldk, ldv, slot_mapping, (uint8_t*)k_cache, (uint8_t*)v_cache, k_scales, v_scales,
+                      nkv, hd, block_size, mode);
+  else
+    return -11;
+  return static_cast<int>(cudaGetLastError());
 }
 
 extern "C" int fi_embedding(const long* ids, const void* table, void* out, int T, int H,

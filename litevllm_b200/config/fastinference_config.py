@@ -4,7 +4,7 @@ Schema (unknown keys are errors; contract: vllm/engine/fastinference_config.py:1
 reference, extended with a ``[parallel]`` table for multi-GPU serving)::
 
     profile  = "auto" | "balanced" | "latency" | "throughput" | "accuracy" | "benchmark"
-    kv_type  = "auto" | "fp16" | "fp8" | "turbo_int4"
+    kv_type  = "auto" | "fp16" | "fp8" | "fp8_block" | "turbo_int4"
     debug    = false
     log_level = "info"
     [benchmark]      profile = "default"
@@ -25,7 +25,7 @@ from typing import Any
 from .env_registry import is_usable_tuning_key
 
 PROFILES = ("auto", "balanced", "latency", "throughput", "accuracy", "benchmark")
-KV_TYPES = ("auto", "fp16", "fp8", "turbo_int4")
+KV_TYPES = ("auto", "fp16", "fp8", "fp8_block", "turbo_int4")
 COMM_BACKENDS = ("fused", "nccl")
 
 

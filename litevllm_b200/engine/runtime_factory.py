@@ -45,7 +45,8 @@ class LiteRuntimeFactory:
     @staticmethod
     def build(ctx: RuntimeAssemblyContext) -> RuntimeComponents:
         plan, rc, custom = ctx.plan, ctx.runtime_config, ctx.custom
-        kv_cache = FlatKVCache(ctx.kv_specs, plan.num_total_blocks, plan.block_size, ctx.kv_plan.dtype, ctx.device)
+        kv_cache = FlatKVCache(ctx.kv_specs, plan.num_total_blocks, plan.block_size, ctx.kv_plan.dtype, ctx.device,
+                               fmt=getattr(ctx.kv_plan, "fmt", 0))
         allocator = BlockAllocator(plan.num_total_blocks)
         kv_manager = KVBlockManager(allocator, plan.block_size, plan.max_active_requests, plan.num_blocks_per_seq,
                                     ctx.device, kv_cache)

@@ -14,7 +14,7 @@ from dataclasses import dataclass
 import torch
 
 from ..utils.misc import cdiv, round_up
-from .kv_cache import KVLayerSpec, bytes_per_block, kv_torch_dtype
+from .kv_cache import KVLayerSpec, bytes_per_block, kv_format, kv_torch_dtype
 
 DEFAULT_CONTEXT_CAP = 4096
 
@@ -38,6 +38,7 @@ class KVCachePlan:
     k_scale: float
     v_scale: float
     bytes_total: int
+    fmt: int = 0          # 0 16-bit, 1 fp8 per-tensor scale, 2 fp8 row scales, 3 packed int4 row scales
 
 
 class RuntimePlanner:
@@ -76,6 +77,9 @@ class RuntimePlanner:
                             forced_dtype: str | None = None) -> KVCachePlan:
         name = forced_dtype or self.rc.kv_cache_dtype
         dt = kv_torch_dtype(name, model_dtype)
-        total = bytes_per_block(specs, plan.block_size, dt) * plan.num_total_blocks
+        fmt = kv_format(name)
+        if fmt == 3 and any(s.head_dim % 32 or s.v_dim % 32 for s in specs if s.num_kv_heads > 0):
+            name, dt, fmt = "fp8", kv_torch_dtype("fp8", model_dtype), 1      # odd head widths cannot be nibble-packed
+        total = bytes_per_block(specs, plan.block_size, dt, fmt) * plan.num_total_blocks
         return KVCachePlan(dtype=dt, dtype_name=name, k_scale=self.rc.k_scale, v_scale=self.rc.v_scale,
-                           bytes_total=total)
+                           bytes_total=total, fmt=fmt)

@@ -317,12 +317,35 @@ def rope_and_cache(qkv, positions, cos_sin, slot_mapping, k_cache, v_cache, nh, 
     T = qkv.shape[0]
     assert qkv.is_contiguous() and positions.dtype == torch.int32
     assert slot_mapping.dtype == torch.int32
+    mode = reference.kv_mode(k_cache)
+    if mode >= 2:
+        # row-scaled cache: rotate / normalise in place without a cache write, then quantise the k and v rows
+        rc = _lib.kernels().fi_rope_cache(
+            _p(qkv), _p(positions), _p(cos_sin), _p(freq_stream), None, _p(k_cache), _p(v_cache), _p(q_norm_w),
+            _p(k_norm_w), T, nh, nkv, hd, rot_dim, k_cache.shape[2], 0, 1.0, 1.0, eps, qk_norm_mode,
+            1 if v_norm else 0, _DT[qkv.dtype], _stream())
+        _lib.check(rc, "fi_rope_cache")
+        _count()
+        kv = qkv.view(T, nh + 2 * nkv, hd)
+        _kv_quant_rows(kv[:, nh:nh + nkv], kv[:, nh + nkv:], slot_mapping, k_cache, v_cache, mode)
+        return
     rc = _lib.kernels().fi_rope_cache(
         _p(qkv), _p(positions), _p(cos_sin), _p(freq_stream), _p(slot_mapping), _p(k_cache),
         _p(v_cache), _p(q_norm_w), _p(k_norm_w), T, nh, nkv, hd, rot_dim, k_cache.shape[2],
         1 if k_cache.dtype == torch.float8_e4m3fn else 0, k_scale, v_scale, eps, qk_norm_mode,
         1 if v_norm else 0, _DT[qkv.dtype], _stream())
     _lib.check(rc, "fi_rope_cache")
+    _count()
+
+
+def _kv_quant_rows(k, v, slot_mapping, k_cache, v_cache, mode: int) -> None:
+    """k, v: [T, nkv, hd] views (last two dims contiguous) -> row-scaled cache (formats 2 and 3)."""
+    T, nkv, hd = k.shape
+    assert k.stride(2) == 1 and k.stride(1) == hd and v.stride(2) == 1 and v.stride(1) == hd
+    rc = _lib.kernels().fi_kv_quant_rows(_p(k), _p(v), k.stride(0), v.stride(0), _p(slot_mapping), _p(k_cache),
+                                         _p(v_cache), _p(k_cache.fi_scales), _p(v_cache.fi_scales), T, nkv, hd,
+                                         k_cache.shape[2], mode, _DT[k.dtype], _stream())
+    _lib.check(rc, "fi_kv_quant_rows")
     _count()
 
 
@@ -334,6 +357,10 @@ def reshape_and_cache(k, v, slot_mapping, k_cache, v_cache, k_scale=1.0, v_scale
     if not k.is_cuda:
         return reference.reshape_and_cache(k, v, slot_mapping, k_cache, v_cache, k_scale, v_scale)
     T, nkv, hd = k.shape
+    mode = reference.kv_mode(k_cache)
+    if mode >= 2:
+        _kv_quant_rows(k, v, slot_mapping, k_cache, v_cache, mode)
+        return
     rc = _lib.kernels().fi_reshape_and_cache(
         _p(k), _p(v), _p(slot_mapping), _p(k_cache), _p(v_cache), T, k.stride(0), v.stride(0), nkv,
         hd, k_cache.shape[2], 1 if k_cache.dtype == torch.float8_e4m3fn else 0, k_scale, v_scale,
@@ -401,6 +428,20 @@ def paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, nh, nkv,
             max_kv_len = block_tables.shape[1] * k_cache.shape[2]
         eff = min(max_kv_len, window) if window and window > 0 else max_kv_len
         splits = pick_decode_splits(B, nkv, eff)
+    mode = reference.kv_mode(k_cache)
+    if mode >= 2:
+        ws_o = ws_ml = None
+        if splits > 1:
+            n_o = B * nh * splits * hd
+            ws = scratch("decode_ws", (n_o + B * nh * splits * 2) * 4, q.device).view(torch.float32)
+            ws_o, ws_ml = ws[:n_o], ws[n_o:]
+        rc = _lib.kernels().fi_paged_decode_rowscaled(
+            _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(k_cache.fi_scales), _p(v_cache.fi_scales), _p(out),
+            _p(block_tables), _p(seq_lens), _p(ws_o), _p(ws_ml), B, nh, nkv, hd, block_tables.shape[1],
+            k_cache.shape[2], int(window or 0), sm_scale, float(softcap or 0.0), mode, splits, _DT[q.dtype], _stream())
+        _lib.check(rc, "fi_paged_decode_rowscaled")
+        _count(2 if splits > 1 else 1)
+        return out
     if 1 < splits <= 8 and _DECODE_MERGE == "cluster" and k_cache.shape[2] % 16 == 0:
         rc = _lib.kernels().fi_paged_decode_cluster(
             _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(block_tables), _p(seq_lens), B, nh, nkv, hd,
@@ -461,6 +502,15 @@ def paged_attention_prefill(q, k_cache, v_cache, block_tables, seq_lens, cu_q, m
         tmp = paged_attention_prefill(q, k_cache, v_cache, block_tables, seq_lens, cu_q, max_q_len, nh, nkv, hd,
                                       sm_scale, window, softcap, k_scale, v_scale, None)
         out.copy_(tmp)
+        return out
+    mode = reference.kv_mode(k_cache)
+    if mode >= 2:
+        rc = _lib.kernels().fi_paged_prefill_rowscaled(
+            _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(k_cache.fi_scales), _p(v_cache.fi_scales), _p(out),
+            _p(block_tables), _p(seq_lens), _p(cu_q), B, int(max_q_len), nh, nkv, hd, block_tables.shape[1],
+            k_cache.shape[2], int(window or 0), sm_scale, float(softcap or 0.0), mode, _DT[q.dtype], _stream())
+        _lib.check(rc, "fi_paged_prefill_rowscaled")
+        _count()
         return out
     rc = _lib.kernels().fi_paged_prefill(
         _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(block_tables), _p(seq_lens),

@@ -117,6 +117,41 @@ def rope_and_cache(qkv, positions, cos_sin, slot_mapping, k_cache, v_cache, nh, 
     reshape_and_cache(k, v, slot_mapping, k_cache, v_cache, k_scale, v_scale)
 
 
+# ---- row-scaled cache formats: one fp32 scale per (token, kv head) row, kept in ``cache.fi_scales``
+# [num_blocks, nkv, block_size]; ``cache.fi_mode`` = 2 (e4m3 rows, "block-scaled" fp8) or 3 (packed int4)
+def kv_mode(cache) -> int:
+    m = getattr(cache, "fi_mode", None)
+    if m is not None:
+        return int(m)
+    return 1 if cache.dtype == torch.float8_e4m3fn else 0
+
+
+def quant_rows(x: torch.Tensor, mode: int):
+    """x [..., hd] -> (stored rows, fp32 scales [...]).  mode 3: packed int4 uint8 [..., hd/2] (byte d = channel d
+    in the low nibble, channel d + hd/2 in the high nibble, q = clamp(floor(x / s + 0.5), -7, 7), s = max(amax / 7,
+    1e-4)); mode 2: e4m3 of x / s with s = amax / 448."""
+    xf = x.float()
+    amax = xf.abs().amax(-1)
+    if mode == 3:
+        sc = (amax / 7.0).clamp_min(1e-4)
+        q = torch.floor(xf / sc[..., None] + 0.5).clamp(-7, 7).to(torch.int16)
+        half = x.shape[-1] // 2
+        packed = (q[..., :half] & 0x0F) | ((q[..., half:] & 0x0F) << 4)
+        return packed.to(torch.uint8), sc
+    sc = (amax / 448.0).clamp_min(1e-12)
+    return (xf / sc[..., None]).to(torch.float8_e4m3fn), sc
+
+
+def dequant_rows(stored: torch.Tensor, scales: torch.Tensor, mode: int) -> torch.Tensor:
+    """Inverse of :func:`quant_rows` -> float32 [..., hd]."""
+    if mode == 3:
+        b = stored.to(torch.int16)
+        lo = ((b & 0x0F) ^ 8) - 8
+        hi = ((b >> 4) ^ 8) - 8
+        return torch.cat([lo, hi], dim=-1).float() * scales[..., None]
+    return stored.float() * scales[..., None]
+
+
 def reshape_and_cache(k, v, slot_mapping, k_cache, v_cache, k_scale=1.0, v_scale=1.0):
     """k, v: [T, nkv, hd] -> paged cache at slot_mapping (negative slot = skip)."""
     bs = k_cache.shape[2]
@@ -126,6 +161,13 @@ def reshape_and_cache(k, v, slot_mapping, k_cache, v_cache, k_scale=1.0, v_scale
     slots = slot_mapping[valid].long()
     blk, off = slots // bs, slots % bs
     kk, vv = k[valid], v[valid]
+    mode = kv_mode(k_cache)
+    if mode >= 2:
+        for cache, rows in ((k_cache, kk), (v_cache, vv)):
+            stored, sc = quant_rows(rows, mode)
+            cache[blk, :, off] = stored
+            cache.fi_scales[blk, :, off] = sc
+        return
     if k_cache.dtype == torch.float8_e4m3fn:
         k_cache[blk, :, off] = fp8_quant(kk, k_scale)
         v_cache[blk, :, off] = fp8_quant(vv, v_scale)
@@ -137,6 +179,11 @@ def reshape_and_cache(k, v, slot_mapping, k_cache, v_cache, k_scale=1.0, v_scale
 def _gather_kv(cache, block_table, n_tokens, scale):
     bs = cache.shape[2]
     nb = (n_tokens + bs - 1) // bs
+    mode = kv_mode(cache)
+    if mode >= 2:
+        idx = block_table[:nb].long()
+        blocks = dequant_rows(cache[idx], cache.fi_scales[idx], mode)       # [nb, nkv, bs, hd]
+        return blocks.permute(1, 0, 2, 3).reshape(cache.shape[1], nb * bs, blocks.shape[3])[:, :n_tokens]
     blocks = cache[block_table[:nb].long()]  # [nb, nkv, bs, hd]
     x = blocks.permute(1, 0, 2, 3).reshape(cache.shape[1], nb * bs, cache.shape[3])[:, :n_tokens]
     x = x.float()
