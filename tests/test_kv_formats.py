@@ -101,7 +101,7 @@ def test_row_scaled_cache_write_and_attention_gpu(mode, nh, nkv, hd):
         # nibbles may differ by one step where bf16 rounding of value / scale sits on a boundary
         diff = (ref.dequant_rows(kc.cpu(), kc.fi_scales.cpu(), 3) - ref.dequant_rows(kr, kr.fi_scales, 3)).abs()
         assert float((diff / kr.fi_scales[..., None].clamp_min(1e-4)).max()) <= 1.001
-        assert float((diff > 0).float().mean()) < 0.01
+        assert float((kc.cpu() != kr).float().mean()) < 0.01      # bytes differ only at exact .5 boundaries
     else:
         assert float((kc.cpu().float() - kr.float()).abs().max()) <= 32.0          # one e4m3 step at the top of the range
     assert torch.allclose(kc.fi_scales.cpu(), kr.fi_scales, rtol=1e-5, atol=1e-7)
