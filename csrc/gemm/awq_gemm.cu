@@ -73,7 +73,7 @@ __device__ __forceinline__ int raw_swizzle_chunk(int row, int c) {
 constexpr int kDequantWarps = 8;
 constexpr int kAwqThreads = 64 + kDequantWarps * 32;
 
-template <typename T, int BN, int RST, int AST, bool DUAL>
+template <typename T, int BN, int RST, int AST, bool DUAL, bool ROW = false>
 __global__ void __launch_bounds__(kAwqThreads)
 awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 const __grid_constant__ TokenMaps tmaps_x, const GemmParams p) {
@@ -90,6 +90,11 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                             : TMEM_COLS_NEED <= 256 ? 256 : 512;
   constexpr int STAGES = RST;  // name used by the shared epilogue text
   (void)STAGES;
+  // Row-per-thread dequantisation (template flag ROW; decode-sized token tiles with SUBS == 4 k-blocks per raw stage):
+  // a thread owns one weight row and two whole k-blocks (128 values = one AWQ group) of every raw stage, so it
+  // waits for the raw stage once, fetches one scale / zero point per 64..128 values and touches a barrier once
+  // per 64 values: about half the per-value overhead of the half-k-block scheme used for larger token tiles.
+  constexpr bool kRowScheme = ROW && (SUBS == 4);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -129,7 +134,9 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       mbar_init(&raw_empty[s], 1 + kDequantWarps);   // MMA commit (token tile) + one arrival per dequant warp
     }
     for (int s = 0; s < AST; ++s) {
-      mbar_init(&a_full[s], kDequantWarps);   // one arrival per dequant warp
+      // one arrival per dequant warp that writes the stage: all eight in the half-k-block scheme, the four
+      // that own the k-block in the row-per-thread scheme (SUBS == 4)
+      mbar_init(&a_full[s], kRowScheme ? kDequantWarps / 2 : kDequantWarps);
       mbar_init(&a_empty[s], 1);
     }
     mbar_init(accum_bar, 1);
@@ -238,6 +245,121 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const int dw = warp - 2;
     const int row = (dw & 3) * 32 + lane;
     const int half = dw >> 2;
+    if constexpr (kRowScheme) {
+      const bool pow2 = (p.group & (p.group - 1)) == 0;
+      const int gshift = 31 - __clz(p.group);
+      const bool two_scales = p.group < 64;          // group 32: the two halves of a k-block have their own scale
+      const uint16_t* scales16 = reinterpret_cast<const uint16_t*>(p.scales);
+      uint32_t st_off[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) st_off[c] = sw128_offset(row, c);
+      uint32_t ld_off[2][2];                         // [my k-block u][16-byte half h] inside the packed tile
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          ld_off[u][h] = SUBS * B_BYTES + row * QROW + raw_swizzle_chunk<SUBS>(row, (half * 2 + u) * 2 + h) * 16;
+      size_t srow[NA];
+      bool rvalid[NA];
+#pragma unroll
+      for (int a = 0; a < NA; ++a) {
+        const int grow = w_row0 + (a == 0 ? n0 : p.dual_rows + n0) + row;
+        rvalid[a] = grow < p.n_rows_total;
+        srow[a] = rvalid[a] ? grow : 0;
+      }
+      // (scale, zero) words of my two k-blocks of a raw stage, loaded one stage ahead
+      uint16_t s_raw[NA][2][2];
+      uint8_t z_raw[NA][2][2];
+      auto fetch = [&](int rs) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int kb = kb_begin + rs * SUBS + half * 2 + u;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int k = kb * BK + h * 32;
+            const size_t g = static_cast<size_t>(pow2 ? (k >> gshift) : (k / p.group)) * p.n_rows_total;
+#pragma unroll
+            for (int a = 0; a < NA; ++a) {
+              s_raw[a][u][h] = 0;
+              z_raw[a][u][h] = 8;
+              if (rvalid[a] && kb < kb_end && (h == 0 || two_scales)) {
+                s_raw[a][u][h] = scales16[g + srow[a]];
+                if (p.zeros != nullptr) z_raw[a][u][h] = p.zeros[g + srow[a]];
+              }
+            }
+          }
+        }
+      };
+      const int n_rs = (kb_end - kb_begin + SUBS - 1) / SUBS;
+      if (n_rs > 0) fetch(0);
+      bool ok = true;
+      int s = 0;
+      uint32_t raw_ph = 0;
+      for (int rs = 0; rs < n_rs && ok; ++rs) {
+        uint32_t s2[NA][2][2], z2[NA][2][2];
+#pragma unroll
+        for (int a = 0; a < NA; ++a)
+#pragma unroll
+          for (int u = 0; u < 2; ++u)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              // static indices only: a run-time index would push the arrays into local memory
+              const uint16_t sr = (h == 1 && two_scales) ? s_raw[a][u][1] : s_raw[a][u][0];
+              const uint8_t zr = (h == 1 && two_scales) ? z_raw[a][u][1] : z_raw[a][u][0];
+              s2[a][u][h] = static_cast<uint32_t>(sr) * 0x00010001u;
+              z2[a][u][h] = Pack<T>::kMagic2 + static_cast<uint32_t>(zr) * 0x00010001u;
+            }
+        if (rs + 1 < n_rs) fetch(rs + 1);
+        if (!mbar_wait(&raw_full[s], raw_ph)) {
+          set_status(p.status, kStatusTimeoutFull);
+          *aborted = 1;
+          ok = false;
+          break;
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int sub = half * 2 + u;
+          const int kb = kb_begin + rs * SUBS + sub;
+          if (kb >= kb_end) break;                                       // ragged last raw stage (uniform per warp)
+          const int it = rs * SUBS + sub;                                // k-blocks use the A stages round robin
+          const int j = it % AST;
+          const uint32_t a_ph = ((static_cast<uint32_t>(it / AST)) & 1u) ^ 1u;
+          if (!mbar_wait(&a_empty[j], a_ph)) {
+            set_status(p.status, kStatusTimeoutFull);
+            *aborted = 1;
+            ok = false;
+            break;
+          }
+#pragma unroll
+          for (int a = 0; a < NA; ++a) {
+            uint8_t* dst = a_ring + (j * NA + a) * A_BYTES;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const uint4 w4 = *reinterpret_cast<const uint4*>(raw_ring + s * RAW_BYTES + a * Q_BYTES + ld_off[u][h]);
+              const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
+              const typename Pack<T>::v2 sv = *reinterpret_cast<const typename Pack<T>::v2*>(&s2[a][u][h]);
+              const typename Pack<T>::v2 zv = *reinterpret_cast<const typename Pack<T>::v2*>(&z2[a][u][h]);
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                uint32_t o[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const uint32_t v = ((words[c] >> (4 * i)) & 0x000F000Fu) | Pack<T>::kMagic2;
+                  o[i] = Pack<T>::sub_mul(v, zv, sv);
+                }
+                *reinterpret_cast<uint4*>(dst + st_off[h * 4 + c]) = make_uint4(o[0], o[1], o[2], o[3]);
+              }
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&a_full[j]);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&raw_empty[s]);
+        if (++s == RST) { s = 0; raw_ph ^= 1; }
+      }
+    } else {
     uint32_t st_off[4], ld_off[SUBS];
 #pragma unroll
     for (int c = 0; c < 4; ++c) st_off[c] = sw128_offset(row, half * 4 + c);
@@ -323,6 +445,7 @@ awq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
         if (++s == RST) { s = 0; raw_ph ^= 1; }
       }
     }
+    }   // half-k-block scheme
   }
   // ---------------------------------------------------------------- epilogue (epilogue.cuh)
   if (warp >= 2 && warp < 6) epilogue_tmem_to_smem<BN, DUAL>(p, accum_bar, tmem_base, stage_f32, aborted, warp, lane);
@@ -344,9 +467,9 @@ constexpr int smem_bytes() {
   return ring_bytes<BN, RST, AST, DUAL>() + (2 * RST + 2 * AST + 1) * 8 + 16 + 1024;
 }
 
-template <typename T, int BN, int RST, int AST, bool DUAL>
+template <typename T, int BN, int RST, int AST, bool DUAL, bool ROW = false>
 int launch(const CUtensorMap& tw, const TokenMaps& tx, GemmParams p, cudaStream_t stream) {
-  auto kern = awq_gemm_kernel<T, BN, RST, AST, DUAL>;
+  auto kern = awq_gemm_kernel<T, BN, RST, AST, DUAL, ROW>;
   constexpr int smem = smem_bytes<BN, RST, AST, DUAL>();
   constexpr int ring = ring_bytes<BN, RST, AST, DUAL>();
   static_assert(BN * BM * 4 <= ring, "fp32 staging tile must fit inside the rings");
@@ -392,12 +515,21 @@ int launch(const CUtensorMap& tw, const TokenMaps& tx, GemmParams p, cudaStream_
                                         dim3(kAwqThreads), smem, stream, p.splits, tw, tx, p));
 }
 
+inline bool row_scheme() {
+  static const bool on = [] {
+    const char* v = getenv("FI_AWQ_ROW_SCHEME");
+    return v == nullptr || v[0] != '0';
+  }();
+  return on;
+}
+
 template <typename T, bool DUAL>
 int dispatch(int bn, const CUtensorMap& tw, const TokenMaps& tx, const GemmParams& p, cudaStream_t s) {
   switch (bn) {
     // raw stages hold raw_subs(BN) k-blocks each; sizes keep two CTAs per SM where possible
-    case 16: return launch<T, 16, 2, DUAL ? 2 : 3, DUAL>(tw, tx, p, s);
-    case 32: return launch<T, 32, 2, DUAL ? 2 : 3, DUAL>(tw, tx, p, s);
+    // decode-sized tiles: row-per-thread dequantisers (FI_AWQ_ROW_SCHEME=0: the older half-k-block dequantisers)
+    case 16: return row_scheme() ? launch<T, 16, 2, DUAL ? 2 : 3, DUAL, true>(tw, tx, p, s) : launch<T, 16, 2, DUAL ? 2 : 3, DUAL>(tw, tx, p, s);
+    case 32: return row_scheme() ? launch<T, 32, 2, DUAL ? 2 : 3, DUAL, true>(tw, tx, p, s) : launch<T, 32, 2, DUAL ? 2 : 3, DUAL>(tw, tx, p, s);
     case 64: return launch<T, 64, 2, DUAL ? 2 : 3, DUAL>(tw, tx, p, s);
     default: return launch<T, 128, 3, DUAL ? 2 : 3, DUAL>(tw, tx, p, s);
   }
