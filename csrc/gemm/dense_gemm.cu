@@ -27,7 +27,7 @@ namespace {
 unsigned long long* g_plain_trace = nullptr;
 
 
-template <int BN, int STAGES, bool DUAL, bool RED = (BN <= 64 || (BN == 128 && !DUAL))>
+template <int BN, int STAGES, bool DUAL>
 __global__ void __launch_bounds__(kThreads)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                   const __grid_constant__ TokenMaps tmaps_x, const GemmParams p) {
@@ -49,8 +49,6 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
   volatile int* aborted = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* row_ss = reinterpret_cast<float*>(tmem_slot + 2);   // [BN] floats after the control words: sum of squares per token
-  // split-K exchange area (never aliases the ring: peers store into it while this CTA may still be in its main loop)
-  float* red = RED ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(row_ss) + ((BN * 4 + 15) & ~15)) : nullptr;
   const bool rms = p.rms_eps > 0.f;
   // fp32 staging of the accumulator tile(s); aliases the pipeline ring once the main loop is done.
   float* stage_f32 = reinterpret_cast<float*>(smem);
@@ -234,9 +232,9 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     asm volatile("bar.sync 1, 128;" ::: "memory");   // the four warps: row_ss complete before it is used
   }
   // ---------------------------------------------------------------- epilogue (epilogue.cuh)
-  if (warp >= 2) epilogue_tmem_to_smem<BN, DUAL>(p, accum_bar, tmem_base, stage_f32, aborted, warp, lane, row_ss, red);
+  if (warp >= 2) epilogue_tmem_to_smem<BN, DUAL>(p, accum_bar, tmem_base, stage_f32, aborted, warp, lane, row_ss);
   __syncthreads();
-  epilogue_reduce_store<BN, DUAL>(p, stage_f32, aborted, n0, t0, epoch_now, p.T, row_ss, red);
+  epilogue_reduce_store<BN, DUAL>(p, stage_f32, aborted, n0, t0, epoch_now, p.T, row_ss);
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
@@ -246,9 +244,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
 
 template <int BN, int STAGES, bool DUAL>
 constexpr int smem_bytes() {
-  constexpr bool red = BN <= 64 || (BN == 128 && !DUAL);   // tile shapes that may run split-K carry the exchange area
-  return STAGES * (BM * 128 * (DUAL ? 2 : 1) + BN * 128) + (2 * STAGES + 1) * 8 + 16 + BN * 4 + 16 + 1024 +
-         (red ? ((DUAL ? 2 : 1) * red_tile_floats<BN>() + 2 * (BN + 8)) * 4 : 0);
+  return STAGES * (BM * 128 * (DUAL ? 2 : 1) + BN * 128) + (2 * STAGES + 1) * 8 + 16 + BN * 4 + 1024;
 }
 
 // Split-K choice.  A cluster of S CTAs must be co-scheduled inside one GPC, so the number of
@@ -321,7 +317,7 @@ int dispatch(int bn, const CUtensorMap& tw, const TokenMaps& tx, const GemmParam
   switch (bn) {
     case 16: return launch<16, DUAL ? 5 : 8, DUAL>(tw, tx, p, s);
     case 32: return launch<32, DUAL ? 5 : 8, DUAL>(tw, tx, p, s);
-    case 64: return launch<64, DUAL ? 3 : 6, DUAL>(tw, tx, p, s);
+    case 64: return launch<64, DUAL ? 4 : 6, DUAL>(tw, tx, p, s);
     case 128: return launch<128, DUAL ? 2 : 3, DUAL>(tw, tx, p, s);
     default: return launch<256, DUAL ? 3 : 4, DUAL>(tw, tx, p, s);
   }

@@ -350,21 +350,11 @@ __device__ __forceinline__ void epilogue_two_shot(const GemmParams& p, const flo
 }
 
 // Part 1: warps 2..5.  Returns false when the accumulator never arrived.
-// Rows of one (source CTA) slab of the split-K exchange area: token rows are dealt to the cluster's
-// CTAs round robin (row tl belongs to CTA tl % S and is its local row tl / S), at most BN/S + 1 rows each.
-template <int BN>
-__host__ __device__ constexpr int red_tile_floats() { return (BN + 8) * BM; }
-
-// `red` (optional): split-K exchange area of (DUAL ? 2 : 1) * red_tile_floats<BN>() floats (+ 2 * (BN + 8)
-// floats for the RMSNorm sums) that does NOT alias the pipeline ring.  With it, a CTA of a split-K
-// cluster stores each accumulator row straight into the shared memory of the CTA that owns the row
-// (distributed shared memory), so the owners later sum local memory only and nobody has to stay
-// resident for its peers; without it the partial tile is parked locally and pulled by the owners.
 template <int BN, bool DUAL>
 __device__ __forceinline__ void epilogue_tmem_to_smem(const GemmParams& p, uint64_t* accum_bar,
                                                       uint32_t tmem_base, float* stage_f32,
                                                       volatile int* aborted, int warp, int lane,
-                                                      const float* row_ss = nullptr, float* red = nullptr) {
+                                                      const float* row_ss = nullptr) {
   bool ok = mbar_wait(accum_bar, 0);
   if (!ok) {
     set_status(p.status, kStatusTimeoutAccum);
@@ -375,31 +365,7 @@ __device__ __forceinline__ void epilogue_tmem_to_smem(const GemmParams& p, uint6
   const int q = warp & 3;  // TMEM lane quarter this warp may read
   const int n_local = q * 32 + lane;
   const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-  if (ok && red != nullptr && p.splits > 1) {
-    // push form: row tl of this CTA's partial goes to slab `my rank` of CTA tl % S
-    namespace cg = cooperative_groups;
-    cg::cluster_group cluster = cg::this_cluster();
-    const int S = p.splits, me = static_cast<int>(blockIdx.z), RM = (BN + S - 1) / S;
-#pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 16) {
-      uint32_t r[16], u[16];
-      tmem_ld_x16(taddr + c0, r);
-      if (DUAL) tmem_ld_x16(taddr + BN + c0, u);
-      tmem_ld_wait();
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const int tl = c0 + j;
-        float* dst = cluster.map_shared_rank(red, tl % S) + (me * RM + tl / S) * BM + n_local;
-        dst[0] = __uint_as_float(r[j]);
-        if (DUAL) dst[red_tile_floats<BN>()] = __uint_as_float(u[j]);
-      }
-    }
-    if (p.rms_eps > 0.f && q == 0) {   // the per-token sums of squares of this CTA's K slice travel the same way
-      float* ss_base = red + (DUAL ? 2 : 1) * red_tile_floats<BN>();
-      for (int tl = lane; tl < BN; tl += 32)
-        cluster.map_shared_rank(ss_base, tl % S)[me * RM + tl / S] = row_ss[tl];
-    }
-  } else if (ok) {
+  if (ok) {
     const bool fuse_act_now = DUAL && (p.splits == 1);
     const bool norm_now = p.rms_eps > 0.f && p.splits == 1;   // with split-K the scale is applied after the sum
     const float inv_k = 1.f / static_cast<float>(p.K);
@@ -450,7 +416,7 @@ template <int BN, bool DUAL>
 __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float* stage_f32,
                                                       volatile int* aborted, int n0, int t0,
                                                       unsigned int epoch_now, int t_end,
-                                                      float* row_ss = nullptr, float* red = nullptr) {
+                                                      float* row_ss = nullptr) {
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   const int S = p.splits;
@@ -472,8 +438,6 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
   // an owned tile without split-K has nothing to do before the final sum: its partial already sits
   // in the staging tile and nobody else wants it
   const bool skip_first_pass = comm && S == 1 && !pushes;
-  const bool pushed = red != nullptr && S > 1;   // the peers stored their rows into my exchange area
-  const int RM = (BN + S - 1) / S;
 
   if (!*aborted && !skip_first_pass) {
     for (int idx = threadIdx.x; idx < rows_mine * (BM / 8); idx += blockDim.x) {
@@ -485,36 +449,7 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
       float g[8], u[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) { g[j] = 0.f; u[j] = 0.f; }
-      if (pushed) {
-        const int jl = idx / (BM / 8);
-#pragma unroll
-        for (int pr = 0; pr < 8; ++pr) {
-          if (pr < S) {
-            const float* src = red + (pr * RM + jl) * BM + nl;
-            const float4 a = *reinterpret_cast<const float4*>(src);
-            const float4 b = *reinterpret_cast<const float4*>(src + 4);
-            g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
-            g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
-            if (DUAL) {
-              const float4 c = *reinterpret_cast<const float4*>(src + red_tile_floats<BN>());
-              const float4 d = *reinterpret_cast<const float4*>(src + red_tile_floats<BN>() + 4);
-              u[0] += c.x; u[1] += c.y; u[2] += c.z; u[3] += c.w;
-              u[4] += d.x; u[5] += d.y; u[6] += d.z; u[7] += d.w;
-            }
-          }
-        }
-        if (p.rms_eps > 0.f) {
-          const float* ss_base = red + (DUAL ? 2 : 1) * red_tile_floats<BN>();
-          float ss = 0.f;
-#pragma unroll
-          for (int pr = 0; pr < 8; ++pr)
-            if (pr < S) ss += ss_base[pr * RM + jl];
-          const float rstd = rsqrtf(ss / static_cast<float>(p.K) + p.rms_eps);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) { g[j] *= rstd; u[j] *= rstd; }
-        }
-      }
-      for (int pr = 0; pr < (pushed ? 0 : S); ++pr) {
+      for (int pr = 0; pr < S; ++pr) {
         const float* src = (S > 1) ? cluster.map_shared_rank(stage_f32, pr) : stage_f32;
         const float4 a = *reinterpret_cast<const float4*>(src + tl * BM + nl);
         const float4 b = *reinterpret_cast<const float4*>(src + tl * BM + nl + 4);
@@ -527,7 +462,7 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
           u[4] += d.x; u[5] += d.y; u[6] += d.z; u[7] += d.w;
         }
       }
-      if (p.rms_eps > 0.f && S > 1 && !pushed) {
+      if (p.rms_eps > 0.f && S > 1) {
         float ss = 0.f;
         for (int pr = 0; pr < S; ++pr) ss += cluster.map_shared_rank(row_ss, pr)[tl];
         const float rstd = rsqrtf(ss / static_cast<float>(p.K) + p.rms_eps);
@@ -742,7 +677,7 @@ __device__ __forceinline__ void epilogue_reduce_store(const GemmParams& p, float
       }
     }
   }
-  if (S > 1 && !pushed) cluster.sync();  // pull form: nobody leaves while a peer may still read its staging tile
+  if (S > 1) cluster.sync();  // nobody leaves while a peer may still read its staging tile
   if (comm) trace_mark(p.trace, epoch_now, 5);
   if (threadIdx.x == 0) cycle_mark(p.trace, comm, 7);
 }
