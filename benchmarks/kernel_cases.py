@@ -128,6 +128,20 @@ def main():
             (B * L * (nh + 2 * nkv) * hd + B * L * nh * hd) * 2, 4.0 * B * nh * L * L * hd / 2, \
             f"B={B} L={L} causal {nh}q/{nkv}kv hd={hd}"
 
+    @case("prefill_attention_hd64")
+    def _():
+        B, L, nh, nkv, hd, bs = 8, 1024, 32, 4, 64, 16     # one TinyLlama prefill micro-batch
+        blocks_per = L // bs
+        nb = B * blocks_per + 1
+        kc, vc = rnd(nb, nkv, bs, hd), rnd(nb, nkv, bs, hd)
+        bt = (torch.arange(B * blocks_per, device=dev, dtype=torch.int32) + 1).view(B, blocks_per)
+        sl = torch.full((B,), L, dtype=torch.int32, device=dev)
+        cu = (torch.arange(B + 1, device=dev, dtype=torch.int32) * L)
+        qkv = rnd(B * L, (nh + 2 * nkv) * hd)
+        return (lambda: ops.paged_attention_prefill(qkv, kc, vc, bt, sl, cu, L, nh, nkv, hd, hd ** -0.5)), \
+            (B * L * (nh + 2 * nkv) * hd + B * L * nh * hd) * 2, 4.0 * B * nh * L * L * hd / 2, \
+            f"B={B} L={L} causal {nh}q/{nkv}kv hd={hd}"
+
     @case("rmsnorm")
     def _():
         T, H = 65536, 4096                                # 537 MB in + out

@@ -1,0 +1,423 @@
+// Chunked-prefill attention on the tcgen05 tensor cores: varlen causal attention of the new tokens
+// of every sequence against the paged 16-bit KV cache (which already holds them).
+//
+// One CTA owns 128 query rows of one (sequence, query head) and walks the KV range it can see in
+// tiles of 128 keys:
+//
+//   warp 0   TMA producer: the Q tile once, then K and V tiles page by page (a page of 16 tokens is
+//            one box per 64 channels) into a ring of STAGES tiles, 128-byte swizzle
+//   warp 1   UMMA issuer:  S = Q K^T  (128 x 128, fp32 in TMEM, two S buffers so the product of the
+//            next tile runs under the softmax of this one) and  PV = P V  (128 x HD, its own TMEM
+//            columns; V is read MN-major, exactly as the cache stores it)
+//   warps 2-5  one query row per thread: read S from TMEM, online softmax in the exp2 domain, write
+//            P in the operand layout to shared memory, then fold PV into the row's fp32 output
+//            registers (o = o * alpha + PV) so TMEM never has to be rescaled
+//
+// Masks (causal edge, sliding window, end of sequence) are applied only in tiles that touch an edge.
+// Every wait is bounded; a wait that runs out sets the status word and the CTA leaves through the
+// common teardown (TMEM freed).
+//
+// The reference computes the same thing with its Triton context-attention kernel
+// (vllm/attention/ops/triton_prefix_prefill.py in the reference tree).
+#include <math_constants.h>
+
+#include "../common/launch.cuh"
+#include "../common/ptx.cuh"
+#include "../common/tensormap.h"
+
+namespace {
+using namespace fi;
+
+struct TcParams {
+  void* out;                 // [T, nh * HD]
+  const int* block_tables;   // [B, max_blocks]
+  const int* seq_lens;       // [B]
+  const int* cu_q;           // [B + 1]
+  int* status;
+  int max_blocks, block_size, nh, nkv, window;
+  float sm_scale, softcap;
+  int is_fp16;
+};
+
+constexpr int kTile = 128;            // query rows per CTA and keys per KV tile
+constexpr int kAtomBytes = 128 * 128; // 128 rows of 128 bytes: 64 channels (or keys) of one tile
+constexpr int kTcThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int HD, int STAGES>
+struct TcSmem {
+  static constexpr int kQ = HD * 256;
+  static constexpr int kP = 2 * kAtomBytes;
+  static constexpr int kKV = HD * 256;
+  static constexpr int kBars = 256;
+  static constexpr int kBytes = kQ + kP + 2 * STAGES * kKV + kBars + 1024;
+};
+
+__device__ __forceinline__ uint32_t pack2(float a, float b, int is_fp16) {
+  if (is_fp16) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int HD, int STAGES>
+__global__ void __launch_bounds__(kTcThreads, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                  const __grid_constant__ CUtensorMap v_map, const TcParams p) {
+  using L = TcSmem<HD, STAGES>;
+  constexpr int kAtoms = HD / 64;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kPvCol = 256;
+
+  // This kernel takes all 512 TMEM columns of its SM.  It therefore waits for the preceding kernel
+  // BEFORE it allocates (a predecessor CTA that has not allocated yet must never find the columns held
+  // by a CTA that is waiting for it), and lets its successors start only after every CTA of this grid
+  // holds its columns.
+  pdl_wait();
+  // a kernel of this stream already reported a failed wait: do not add seconds of waiting per CTA
+  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) return;
+  const int b = blockIdx.z, head = blockIdx.y;
+  const int q_begin = p.cu_q[b];
+  const int q_len = p.cu_q[b + 1] - q_begin;
+  // the tiles with the longest KV range are scheduled first
+  const int qt0 = (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) * kTile;
+  if (qt0 >= q_len) return;
+  const int seq_len = p.seq_lens[b];
+  const int pos0 = seq_len - q_len;
+  const int rows = min(kTile, q_len - qt0);
+  const int first_pos = pos0 + qt0, last_pos = first_pos + rows - 1;
+  const int kv_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+  const int tile_begin = kv_lo / kTile;
+  const int n_tiles = last_pos / kTile + 1 - tile_begin;
+  const int kvh = head / (p.nh / p.nkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = base;
+  uint8_t* sP = sQ + L::kQ;
+  uint8_t* sK = sP + L::kP;
+  uint8_t* sV = sK + STAGES * L::kKV;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + STAGES * L::kKV);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;
+  uint64_t* v_full = k_full + STAGES;
+  uint64_t* kv_empty = v_full + STAGES;
+  uint64_t* s_full = kv_empty + STAGES;      // [2]
+  uint64_t* s_empty = s_full + 2;            // [2]
+  uint64_t* p_full = s_empty + 2;
+  uint64_t* pv_full = p_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_full + 1);
+  volatile int* aborted = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 128);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(pv_full, 1);
+    *aborted = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      tma_prefetch_desc(&q_map);
+      tma_prefetch_desc(&k_map);
+      tma_prefetch_desc(&v_map);
+      mbar_expect_tx(q_full, L::kQ);
+#pragma unroll
+      for (int a = 0; a < kAtoms; ++a)
+        tma_load_2d(sQ + a * kAtomBytes, &q_map, q_full, head * HD + a * 64, q_begin + qt0);
+      const int* bt = p.block_tables + static_cast<long>(b) * p.max_blocks;
+      int issued = 0;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j % STAGES;
+        const uint32_t ph = (j / STAGES) & 1;
+        if (!mbar_wait(&kv_empty[st], ph ^ 1)) {
+          set_status(p.status, kStatusTimeoutEmpty);
+          *aborted = 1;
+          break;
+        }
+        const int tok0 = (tile_begin + j) * kTile;
+        mbar_expect_tx(&k_full[st], L::kKV);
+        mbar_expect_tx(&v_full[st], L::kKV);
+        int rowi[8];
+#pragma unroll
+        for (int pg = 0; pg < 8; ++pg) {
+          const int tok = tok0 + pg * 16;
+          const int blk = tok < seq_len ? bt[tok / p.block_size] : 0;   // past the end: the null block
+          rowi[pg] = (blk * p.nkv + kvh) * p.block_size + tok % p.block_size;
+        }
+#pragma unroll
+        for (int pg = 0; pg < 8; ++pg)
+#pragma unroll
+          for (int a = 0; a < kAtoms; ++a)
+            tma_load_2d(sK + st * L::kKV + a * kAtomBytes + pg * 2048, &k_map, &k_full[st], a * 64, rowi[pg]);
+#pragma unroll
+        for (int pg = 0; pg < 8; ++pg)
+#pragma unroll
+          for (int a = 0; a < kAtoms; ++a)
+            tma_load_2d(sV + st * L::kKV + a * kAtomBytes + pg * 2048, &v_map, &v_full[st], a * 64, rowi[pg]);
+        issued = j + 1;
+      }
+      // own copies in flight: the last tiles issued must have landed before the CTA may leave
+      for (int j = max(0, issued - STAGES); j < issued; ++j) {
+        const int st = j % STAGES;
+        const uint32_t ph = (j / STAGES) & 1;
+        if (!mbar_wait(&k_full[st], ph) || !mbar_wait(&v_full[st], ph)) {
+          set_status(p.status, kStatusTimeoutFull);
+          break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ UMMA issuer
+    if (elect_one()) {
+      const uint32_t fmt = p.is_fp16 ? 0 : 1;
+      const uint32_t idesc_qk = umma_idesc_f16(fmt, kTile, kTile);
+      const uint32_t idesc_pv = umma_idesc_f16(fmt, kTile, HD) | kUmmaBMnMajor;
+      bool ok = mbar_wait(q_full, 0);
+      if (!ok) set_status(p.status, kStatusTimeoutFull);
+      auto issue_qk = [&](int j) -> bool {
+        const int st = j % STAGES, sb = j & 1;
+        if (!mbar_wait(&k_full[st], (j / STAGES) & 1)) return false;
+        if (!mbar_wait(&s_empty[sb], ((j >> 1) & 1) ^ 1)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int a = 0; a < kAtoms; ++a) {
+          const uint64_t dq = umma_desc_sw128_kmajor(smem_u32(sQ + a * kAtomBytes));
+          const uint64_t dk = umma_desc_sw128_kmajor(smem_u32(sK + st * L::kKV + a * kAtomBytes));
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_f16(tmem_base + sb * kTile, dq + 2 * k, dk + 2 * k, idesc_qk, (a | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[sb]);
+        return true;
+      };
+      ok = ok && issue_qk(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) ok = issue_qk(j + 1);
+        const int st = j % STAGES;
+        ok = ok && mbar_wait(p_full, j & 1) && mbar_wait(&v_full[st], (j / STAGES) & 1);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          // P: keys [16k, 16k + 16) = 32 bytes inside the 64-key block k / 4
+          const uint64_t dp = umma_desc_sw128_kmajor(smem_u32(sP + (k >> 2) * kAtomBytes)) + 2 * (k & 3);
+          // V: 16 keys = 16 rows of 128 bytes; the second 64 channels follow one 128-row block later
+          const uint64_t dv = umma_desc_sw128_mnmajor(smem_u32(sV + st * L::kKV + k * 2048), kAtomBytes);
+          umma_f16(tmem_base + kPvCol, dp, dv, idesc_pv, k != 0 ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[st]);
+        umma_commit(pv_full);
+      }
+      if (!ok) {
+        set_status(p.status, kStatusTimeoutFull);
+        *aborted = 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + output rows
+    const int quad = warp & 3;                       // TMEM lanes this warp may read: [32 quad, 32 quad + 32)
+    const int row = quad * 32 + lane;
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+    const int qpos = first_pos + row;
+    const float sl2 = p.sm_scale * kLog2e;
+    const bool capped = p.softcap > 0.f;
+    const float cap_in = capped ? p.sm_scale / p.softcap : 0.f, cap_out = p.softcap * kLog2e;
+    float o[HD];
+#pragma unroll
+    for (int d = 0; d < HD; ++d) o[d] = 0.f;
+    float m = -CUDART_INF_F, l = 0.f, alpha_prev = 1.f;
+    bool ok = true;
+
+    auto fold_pv = [&](float alpha) {
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_x32(t_lane + kPvCol + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[c * 32 + e] = fmaf(o[c * 32 + e], alpha, __uint_as_float(r[e]));
+      }
+    };
+
+    for (int j = 0; j < n_tiles; ++j) {
+      const int sb = j & 1;
+      if (!mbar_wait(&s_full[sb], (j >> 1) & 1)) { ok = false; break; }
+      tc_fence_after();
+      const int k0 = (tile_begin + j) * kTile;
+      // keys of this tile a row may see: [vis_lo, vis_hi)
+      const bool edge = (k0 + kTile - 1 > first_pos) || (p.window > 0 && k0 <= last_pos - p.window);
+      const int vis_hi = min(kTile, qpos - k0 + 1);
+      const int vis_lo = p.window > 0 ? max(0, qpos - p.window + 1 - k0) : 0;
+      const uint32_t t_s = t_lane + sb * kTile;
+
+      // pass 1: the row maximum (in the exp2 domain)
+      float mt = -CUDART_INF_F;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_x32(t_s + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          float v = __uint_as_float(r[e]);
+          if (capped) v = fast_tanh(v * cap_in);
+          if (edge) {
+            const int kk = c * 32 + e;
+            if (kk < vis_lo || kk >= vis_hi) v = -CUDART_INF_F;
+          }
+          mt = fmaxf(mt, v);
+        }
+      }
+      mt *= capped ? cap_out : sl2;                  // both factors are positive
+      const float m_new = fmaxf(m, mt);
+      const float m_use = m_new == -CUDART_INF_F ? 0.f : m_new;
+      const float alpha = fast_exp2(m - m_use);
+
+      if (j > 0) {
+        if (!mbar_wait(pv_full, (j - 1) & 1)) { ok = false; break; }
+        tc_fence_after();
+        fold_pv(alpha_prev);
+      }
+
+      // pass 2: probabilities, written as the A operand of P V (K-major, 128-byte swizzle)
+      float rs = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_x32(t_s + c * 32, r);
+        tmem_ld_wait();
+        uint32_t w[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float v0 = __uint_as_float(r[e]), v1 = __uint_as_float(r[e + 1]);
+          if (capped) {
+            v0 = fast_tanh(v0 * cap_in) * cap_out;
+            v1 = fast_tanh(v1 * cap_in) * cap_out;
+          } else {
+            v0 *= sl2;
+            v1 *= sl2;
+          }
+          float p0 = fast_exp2(v0 - m_use), p1 = fast_exp2(v1 - m_use);
+          if (edge) {
+            const int kk = c * 32 + e;
+            if (kk < vis_lo || kk >= vis_hi) p0 = 0.f;
+            if (kk + 1 < vis_lo || kk + 1 >= vis_hi) p1 = 0.f;
+          }
+          rs += p0 + p1;
+          w[e >> 1] = pack2(p0, p1, p.is_fp16);
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = c * 4 + q4;              // 16-byte chunk (8 keys) of the row's 256 bytes
+          *reinterpret_cast<uint4*>(sP + (chunk >> 3) * kAtomBytes + sw128_offset(row, chunk & 7)) =
+              make_uint4(w[q4 * 4], w[q4 * 4 + 1], w[q4 * 4 + 2], w[q4 * 4 + 3]);
+        }
+      }
+      l = l * alpha + rs;
+      m = m_new;
+      alpha_prev = alpha;
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(p_full);
+      mbar_arrive(&s_empty[sb]);
+    }
+    if (ok) ok = mbar_wait(pv_full, (n_tiles - 1) & 1);
+    if (ok) {
+      tc_fence_after();
+      fold_pv(alpha_prev);
+      if (row < rows) {
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        uint16_t* dst = reinterpret_cast<uint16_t*>(p.out) +
+                        (static_cast<long>(q_begin + qt0 + row) * p.nh + head) * HD;
+#pragma unroll
+        for (int c = 0; c < HD / 8; ++c) {
+          uint4 v;
+          v.x = pack2(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv, p.is_fp16);
+          v.y = pack2(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv, p.is_fp16);
+          v.z = pack2(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv, p.is_fp16);
+          v.w = pack2(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv, p.is_fp16);
+          *reinterpret_cast<uint4*>(dst + c * 8) = v;
+        }
+      }
+    } else {
+      set_status(p.status, kStatusTimeoutAccum);
+      *aborted = 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int HD, int STAGES>
+int launch_tc(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const TcParams& p, int B,
+              int max_q_len, cudaStream_t s) {
+  auto kern = prefill_tc_kernel<HD, STAGES>;
+  constexpr int smem = TcSmem<HD, STAGES>::kBytes;
+  cudaError_t ce = fi::ensure_dynamic_smem(kern, smem);
+  if (ce != cudaSuccess) return static_cast<int>(ce);
+  ce = fi::launch_kernel(kern, dim3((max_q_len + kTile - 1) / kTile, p.nh, B), dim3(kTcThreads), smem, s, 0, qm, km,
+                         vm, p);
+  return static_cast<int>(ce != cudaSuccess ? ce : cudaGetLastError());
+}
+
+}  // namespace
+
+// Tensor-core prefill attention for 16-bit caches with head size 64 or 128 and pages of a multiple of
+// 16 tokens.  Returns -12 when the arguments are outside what this kernel covers (the caller then uses
+// the general kernel), other negative values for malformed arguments.
+//   q: token t, head h at q + (t * q_stride + h * hd) elements, T_total rows; caches [num_blocks, nkv,
+//   block_size, hd]; out [T_total, nh * hd].
+extern "C" int fi_paged_prefill_tc(const void* q, long q_stride, const void* k_cache, const void* v_cache, void* out,
+                                   const int* block_tables, const int* seq_lens, const int* cu_q, int B,
+                                   int T_total, int max_q_len, int nh, int nkv, int hd, long num_blocks,
+                                   int max_blocks, int block_size, int window, float sm_scale, float softcap,
+                                   int dtype, int* status, void* stream) {
+  if (B <= 0 || max_q_len <= 0 || T_total <= 0) return 0;
+  if (nkv <= 0 || nh <= 0 || nh % nkv != 0) return -10;
+  if ((hd != 64 && hd != 128) || block_size % 16 != 0 || (dtype != 0 && dtype != 1)) return -12;
+  if ((reinterpret_cast<uintptr_t>(q) & 15) != 0 || (q_stride * 2) % 16 != 0 ||
+      (reinterpret_cast<uintptr_t>(out) & 15) != 0)
+    return -12;
+  CUtensorMap qm, km, vm;
+  const uint64_t kv_rows = static_cast<uint64_t>(num_blocks) * nkv * block_size;
+  if (fi::make_tmap_2d_16bit_sw128(&qm, q, T_total, static_cast<uint64_t>(nh) * hd, q_stride, kTile) != 0 ||
+      fi::make_tmap_2d_16bit_sw128(&km, k_cache, kv_rows, hd, hd, 16) != 0 ||
+      fi::make_tmap_2d_16bit_sw128(&vm, v_cache, kv_rows, hd, hd, 16) != 0)
+    return -12;
+  TcParams p = {};
+  p.out = out; p.block_tables = block_tables; p.seq_lens = seq_lens; p.cu_q = cu_q; p.status = status;
+  p.max_blocks = max_blocks; p.block_size = block_size; p.nh = nh; p.nkv = nkv; p.window = window;
+  p.sm_scale = sm_scale; p.softcap = softcap; p.is_fp16 = dtype == 1;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (hd == 64) return launch_tc<64, 4>(qm, km, vm, p, B, max_q_len, s);
+  return launch_tc<128, 2>(qm, km, vm, p, B, max_q_len, s);
+}

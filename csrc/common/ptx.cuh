@@ -152,6 +152,24 @@ __device__ __forceinline__ uint64_t umma_desc_sw128_kmajor(uint32_t smem_addr) {
   return d;
 }
 
+// Shared-memory operand descriptor for an MN-major tile with the 128-byte swizzle: every 128-byte
+// row holds 64 consecutive M (or N) elements of ONE k index, eight consecutive k rows form a
+// 1024-byte group (again what a TMA box of 64 x 16-bit elements with SWIZZLE_128B produces, read with
+// the roles of the two axes exchanged).  `mn_atom_bytes` is the distance between two 64-element
+// blocks along M/N (leading byte offset), the 8-row k groups follow one another at 1024 bytes
+// (stride byte offset).
+__device__ __forceinline__ uint64_t umma_desc_sw128_mnmajor(uint32_t smem_addr, uint32_t mn_atom_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>((mn_atom_bytes & 0x3FFFF) >> 4) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+// Bit of the kind::f16 instruction descriptor that marks operand B as MN-major (bit 15 is operand A's).
+constexpr uint32_t kUmmaBMnMajor = 1u << 16;
+
 // Instruction descriptor for kind::f16 with fp32 accumulation, both operands K-major.
 //   ab_fmt: 0 = f16, 1 = bf16.  M in {64,128}, N multiple of 8 (16 when M == 128), N <= 256.
 __host__ __device__ constexpr uint32_t umma_idesc_f16(int ab_fmt, int M, int N) {
@@ -199,6 +217,19 @@ __device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t* r) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -218,6 +249,16 @@ __device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
 }
 
 // ---------------------------------------------------------------- misc
+__device__ __forceinline__ float fast_exp2(float x) {   // 2^x on the special-function unit; 2^-inf = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void set_status(int* status, int code) {
   if (status != nullptr) atomicCAS(status, 0, code);
 }

@@ -389,6 +389,10 @@ def _merge_tickets(device: torch.device) -> torch.Tensor:
 # distributed shared memory: one launch, no scratch), "kernel" (separate merge launch), "ticket" (last CTA merges)
 _DECODE_MERGE = os.environ.get("FI_DECODE_MERGE", "cluster")
 _DECODE_SPLITS = int(os.environ.get("FI_DECODE_SPLITS", "0"))
+# Prefill attention kernel: "auto" = the tcgen05 kernel (128 query rows per CTA) when the longest new
+# chunk has at least _PREFILL_TC_MIN_Q tokens, else the 64-row mma.sync kernel; "on" / "off" force one.
+_PREFILL_TC = os.environ.get("FI_PREFILL_TC", "auto")
+_PREFILL_TC_MIN_Q = int(os.environ.get("FI_PREFILL_TC_MIN_Q", "64"))
 
 
 def pick_decode_splits(B: int, nkv: int, max_kv_len: int, sm_count: int = 148) -> int:
@@ -512,6 +516,17 @@ def paged_attention_prefill(q, k_cache, v_cache, block_tables, seq_lens, cu_q, m
         _lib.check(rc, "fi_paged_prefill_rowscaled")
         _count()
         return out
+    if (_PREFILL_TC != "off" and hd in (64, 128) and k_cache.dtype == q.dtype and k_cache.shape[2] % 16 == 0
+            and k_cache.is_contiguous() and v_cache.is_contiguous()
+            and (_PREFILL_TC == "on" or int(max_q_len) >= _PREFILL_TC_MIN_Q)):
+        rc = _lib.kernels().fi_paged_prefill_tc(
+            _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(block_tables), _p(seq_lens), _p(cu_q), B, T,
+            int(max_q_len), nh, nkv, hd, k_cache.shape[0], block_tables.shape[1], k_cache.shape[2], int(window or 0),
+            sm_scale, float(softcap or 0.0), _DT[q.dtype], _p(status_word(q.device)), _stream())
+        if rc != -12:       # -12: outside what the tensor-core kernel covers, take the general one
+            _lib.check(rc, "fi_paged_prefill_tc")
+            _count()
+            return out
     rc = _lib.kernels().fi_paged_prefill(
         _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(block_tables), _p(seq_lens),
         _p(cu_q), B, int(max_q_len), nh, nkv, hd, block_tables.shape[1], k_cache.shape[2],

@@ -228,6 +228,42 @@ def test_paged_prefill(nh, nkv, hd, fp8, window, softcap):
     _close(y, yr, 2e-2, 2e-2, f"prefill nh{nh} nkv{nkv} hd{hd}")
 
 
+@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 64), (4, 2, 128), (2, 2, 64)])
+@pytest.mark.parametrize("window,softcap,dtype", [(0, 0.0, torch.bfloat16), (300, 0.0, torch.bfloat16),
+                                                  (0, 30.0, torch.float16), (128, 20.0, torch.bfloat16)])
+def test_paged_prefill_tensor_core(nh, nkv, hd, window, softcap, dtype):
+    """The tcgen05 prefill kernel against the fp32 oracle, and against the mma.sync kernel's own result:
+    several 128-row query tiles and 128-key tiles per sequence, chunks that continue a cached prefix,
+    ragged lengths on both axes, sliding window and soft cap."""
+    import litevllm_b200.ops as O
+    torch.manual_seed(16)
+    cases = [(700, 700), (1, 1), (130, 1500), (128, 128), (257, 900), (5, 1000), (384, 385)]
+    B, bs = len(cases), 16
+    lens = [c[1] for c in cases]
+    kc, vc, bt = _fill_paged(B, lens, nkv, hd, bs, False, dtype)
+    T = sum(c[0] for c in cases)
+    width = (nh + 2 * nkv) * hd
+    qkv = torch.randn(T, width, device=DEV).to(dtype)
+    cu = torch.tensor([0] + list(torch.tensor([c[0] for c in cases]).cumsum(0)), dtype=torch.int32, device=DEV)
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    outs = {}
+    saved = O._PREFILL_TC
+    try:
+        for mode in ("on", "off"):
+            O._PREFILL_TC = mode
+            outs[mode] = ops.paged_attention_prefill(qkv, kc, vc, bt, sl, cu, max(c[0] for c in cases), nh, nkv, hd,
+                                                     scale, window, softcap)
+    finally:
+        O._PREFILL_TC = saved
+    torch.cuda.synchronize()
+    ops.check_status(torch.device(DEV, 0))
+    yr = ref.paged_attention(qkv, kc, vc, bt, sl, cu, nh, nkv, hd, scale, window, softcap, 1.0, 1.0,
+                             out_dtype=torch.float32)
+    _close(outs["on"], yr, 2e-2, 2e-2, f"tc prefill nh{nh} nkv{nkv} hd{hd} w{window} cap{softcap}")
+    _close(outs["on"], outs["off"].float(), 2e-2, 2e-2, "tc prefill vs mma.sync prefill")
+
+
 def test_small_ops():
     torch.manual_seed(7)
     table = torch.randn(1000, 256, device=DEV).bfloat16()
