@@ -9,9 +9,11 @@
 //   warp 1   UMMA issuer:  S = Q K^T  (128 x 128, fp32 in TMEM, two S buffers so the product of the
 //            next tile runs under the softmax of this one) and  PV = P V  (128 x HD, its own TMEM
 //            columns; V is read MN-major, exactly as the cache stores it)
-//   warps 2-5  one query row per thread: read S from TMEM, online softmax in the exp2 domain, write
-//            P in the operand layout to shared memory, then fold PV into the row's fp32 output
-//            registers (o = o * alpha + PV) so TMEM never has to be rescaled
+//   warps 2-9  two threads per query row (warps 2-5 own keys 0-63 of a tile and the first half of the
+//            output channels, warps 6-9 keys 64-127 and the second half): read S from TMEM, online
+//            softmax in the exp2 domain (the two halves exchange their row maximum through shared
+//            memory once per tile), write P in the operand layout to shared memory, then fold PV into
+//            the row's fp32 output registers (o = o * alpha + PV) so TMEM never has to be rescaled
 //
 // Masks (causal edge, sliding window, end of sequence) are applied only in tiles that touch an edge.
 // Every wait is bounded; a wait that runs out sets the status word and the CTA leaves through the
@@ -20,6 +22,8 @@
 // The reference computes the same thing with its Triton context-attention kernel
 // (vllm/attention/ops/triton_prefix_prefill.py in the reference tree).
 #include <math_constants.h>
+
+#include <type_traits>
 
 #include "../common/launch.cuh"
 #include "../common/ptx.cuh"
@@ -41,7 +45,7 @@ struct TcParams {
 
 constexpr int kTile = 128;            // query rows per CTA and keys per KV tile
 constexpr int kAtomBytes = 128 * 128; // 128 rows of 128 bytes: 64 channels (or keys) of one tile
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 320;      // TMA warp, UMMA warp, 8 softmax warps
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <int HD, int STAGES>
@@ -49,7 +53,7 @@ struct TcSmem {
   static constexpr int kQ = HD * 256;
   static constexpr int kP = 2 * kAtomBytes;
   static constexpr int kKV = HD * 256;
-  static constexpr int kBars = 256;
+  static constexpr int kBars = 256 + 3 * 2 * 128 * 4;   // barriers + row maxima [2 parities][2 halves][128] + sums
   static constexpr int kBytes = kQ + kP + 2 * STAGES * kKV + kBars + 1024;
 };
 
@@ -109,8 +113,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
   uint64_t* s_empty = s_full + 2;            // [2]
   uint64_t* p_full = s_empty + 2;
   uint64_t* pv_full = p_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_full + 1);
+  uint64_t* pair_bar = pv_full + 1;          // [4]: the two warps of a TMEM quadrant
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_bar + 4);
   volatile int* aborted = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* half_max = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);   // [2][2][128]
+  float* half_sum = half_max + 2 * 2 * 128;                                             // [2][128]
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -121,10 +128,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 128);
+      mbar_init(&s_empty[i], 256);
     }
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 256);
     mbar_init(pv_full, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 64);
     *aborted = 0;
     mbar_fence_init();
   }
@@ -239,60 +247,116 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------------ softmax + output rows
+    constexpr int HH = HD / 2;                       // output channels per thread
     const int quad = warp & 3;                       // TMEM lanes this warp may read: [32 quad, 32 quad + 32)
+    const int half = (warp - 2) >> 2;                // 0: keys 0-63 / channels 0-HH-1, 1: the other halves
     const int row = quad * 32 + lane;
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
     const int qpos = first_pos + row;
     const float sl2 = p.sm_scale * kLog2e;
     const bool capped = p.softcap > 0.f;
     const float cap_in = capped ? p.sm_scale / p.softcap : 0.f, cap_out = p.softcap * kLog2e;
-    float o[HD];
+    float o[HH];
 #pragma unroll
-    for (int d = 0; d < HD; ++d) o[d] = 0.f;
+    for (int d = 0; d < HH; ++d) o[d] = 0.f;
     float m = -CUDART_INF_F, l = 0.f, alpha_prev = 1.f;
     bool ok = true;
+    // the two warps that share a TMEM quadrant (same rows, different halves) meet on a barrier of their
+    // own; an mbarrier, so that the wait is bounded like every other one
+    uint32_t pair_n = 0;
+    auto pair_sync = [&]() -> bool {
+      mbar_arrive(&pair_bar[quad]);
+      return mbar_wait(&pair_bar[quad], (pair_n++) & 1);
+    };
 
     auto fold_pv = [&](float alpha) {
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = 0; c < HH / 32; ++c) {
         uint32_t r[32];
-        tmem_ld_x32(t_lane + kPvCol + c * 32, r);
+        tmem_ld_x32(t_lane + kPvCol + half * HH + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 32; ++e) o[c * 32 + e] = fmaf(o[c * 32 + e], alpha, __uint_as_float(r[e]));
       }
     };
 
-    for (int j = 0; j < n_tiles; ++j) {
-      const int sb = j & 1;
-      if (!mbar_wait(&s_full[sb], (j >> 1) & 1)) { ok = false; break; }
-      tc_fence_after();
-      const int k0 = (tile_begin + j) * kTile;
-      // keys of this tile a row may see: [vis_lo, vis_hi)
-      const bool edge = (k0 + kTile - 1 > first_pos) || (p.window > 0 && k0 <= last_pos - p.window);
-      const int vis_hi = min(kTile, qpos - k0 + 1);
-      const int vis_lo = p.window > 0 ? max(0, qpos - p.window + 1 - k0) : 0;
-      const uint32_t t_s = t_lane + sb * kTile;
-
-      // pass 1: the row maximum (in the exp2 domain)
+    // The two passes over a half row of S, compiled once per (touches a mask edge, soft cap) so that the
+    // common tile carries neither the comparisons nor the tanh.
+    constexpr std::integral_constant<bool, true> kTrue{};
+    constexpr std::integral_constant<bool, false> kFalse{};
+    auto pass1 = [&](auto edge_c, auto cap_c, uint32_t t_s, int vis_lo, int vis_hi) -> float {
       float mt = -CUDART_INF_F;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
         tmem_ld_x32(t_s + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
           float v = __uint_as_float(r[e]);
-          if (capped) v = fast_tanh(v * cap_in);
-          if (edge) {
+          if (decltype(cap_c)::value) v = fast_tanh(v * cap_in);
+          if (decltype(edge_c)::value) {
             const int kk = c * 32 + e;
             if (kk < vis_lo || kk >= vis_hi) v = -CUDART_INF_F;
           }
           mt = fmaxf(mt, v);
         }
       }
+      return mt;
+    };
+    auto pass2 = [&](auto edge_c, auto cap_c, uint32_t t_s, int vis_lo, int vis_hi, float m_use) -> float {
+      float rs = 0.f;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+        tmem_ld_x32(t_s + c * 32, r);
+        tmem_ld_wait();
+        uint32_t w[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float v0 = __uint_as_float(r[e]), v1 = __uint_as_float(r[e + 1]);
+          float p0, p1;
+          if (decltype(cap_c)::value) {
+            p0 = fast_exp2(fmaf(fast_tanh(v0 * cap_in), cap_out, -m_use));
+            p1 = fast_exp2(fmaf(fast_tanh(v1 * cap_in), cap_out, -m_use));
+          } else {
+            p0 = fast_exp2(fmaf(v0, sl2, -m_use));
+            p1 = fast_exp2(fmaf(v1, sl2, -m_use));
+          }
+          if (decltype(edge_c)::value) {
+            const int kk = c * 32 + e;
+            if (kk < vis_lo || kk >= vis_hi) p0 = 0.f;
+            if (kk + 1 < vis_lo || kk + 1 >= vis_hi) p1 = 0.f;
+          }
+          rs += p0 + p1;
+          w[e >> 1] = pack2(p0, p1, p.is_fp16);
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4)
+          *reinterpret_cast<uint4*>(sP + half * kAtomBytes + sw128_offset(row, c * 4 + q4)) =
+              make_uint4(w[q4 * 4], w[q4 * 4 + 1], w[q4 * 4 + 2], w[q4 * 4 + 3]);
+      }
+      return rs;
+    };
+
+    for (int j = 0; j < n_tiles; ++j) {
+      const int sb = j & 1;
+      if (!mbar_wait(&s_full[sb], (j >> 1) & 1)) { ok = false; break; }
+      tc_fence_after();
+      const int k0 = (tile_begin + j) * kTile + half * 64;   // first key of this thread's 64
+      // keys of this half-tile the row may see: [vis_lo, vis_hi)
+      const bool edge = (k0 + 63 > first_pos) || (p.window > 0 && k0 <= last_pos - p.window);
+      const int vis_hi = min(64, qpos - k0 + 1);
+      const int vis_lo = p.window > 0 ? max(0, qpos - p.window + 1 - k0) : 0;
+      const uint32_t t_s = t_lane + sb * kTile + half * 64;
+
+      // pass 1: the maximum of this half of the row (in the exp2 domain), then the other half's
+      float mt = capped ? (edge ? pass1(kTrue, kTrue, t_s, vis_lo, vis_hi) : pass1(kFalse, kTrue, t_s, 0, 64))
+                        : (edge ? pass1(kTrue, kFalse, t_s, vis_lo, vis_hi) : pass1(kFalse, kFalse, t_s, 0, 64));
       mt *= capped ? cap_out : sl2;                  // both factors are positive
+      half_max[(sb * 2 + half) * 128 + row] = mt;
+      if (!pair_sync()) { ok = false; break; }
+      mt = fmaxf(mt, half_max[(sb * 2 + (half ^ 1)) * 128 + row]);
       const float m_new = fmaxf(m, mt);
       const float m_use = m_new == -CUDART_INF_F ? 0.f : m_new;
       const float alpha = fast_exp2(m - m_use);
@@ -303,41 +367,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         fold_pv(alpha_prev);
       }
 
-      // pass 2: probabilities, written as the A operand of P V (K-major, 128-byte swizzle)
-      float rs = 0.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_x32(t_s + c * 32, r);
-        tmem_ld_wait();
-        uint32_t w[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float v0 = __uint_as_float(r[e]), v1 = __uint_as_float(r[e + 1]);
-          if (capped) {
-            v0 = fast_tanh(v0 * cap_in) * cap_out;
-            v1 = fast_tanh(v1 * cap_in) * cap_out;
-          } else {
-            v0 *= sl2;
-            v1 *= sl2;
-          }
-          float p0 = fast_exp2(v0 - m_use), p1 = fast_exp2(v1 - m_use);
-          if (edge) {
-            const int kk = c * 32 + e;
-            if (kk < vis_lo || kk >= vis_hi) p0 = 0.f;
-            if (kk + 1 < vis_lo || kk + 1 >= vis_hi) p1 = 0.f;
-          }
-          rs += p0 + p1;
-          w[e >> 1] = pack2(p0, p1, p.is_fp16);
-        }
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = c * 4 + q4;              // 16-byte chunk (8 keys) of the row's 256 bytes
-          *reinterpret_cast<uint4*>(sP + (chunk >> 3) * kAtomBytes + sw128_offset(row, chunk & 7)) =
-              make_uint4(w[q4 * 4], w[q4 * 4 + 1], w[q4 * 4 + 2], w[q4 * 4 + 3]);
-        }
-      }
-      l = l * alpha + rs;
+      // pass 2: probabilities, written as the A operand of P V (K-major, 128-byte swizzle; the 64 keys
+      // of this half are exactly one 128-byte row of the half's own block)
+      const float rs =
+          capped ? (edge ? pass2(kTrue, kTrue, t_s, vis_lo, vis_hi, m_use) : pass2(kFalse, kTrue, t_s, 0, 64, m_use))
+                 : (edge ? pass2(kTrue, kFalse, t_s, vis_lo, vis_hi, m_use) : pass2(kFalse, kFalse, t_s, 0, 64, m_use));
+      l = l * alpha + rs;                            // this half's share of the denominator
       m = m_new;
       alpha_prev = alpha;
       tc_fence_before();
@@ -349,12 +384,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     if (ok) {
       tc_fence_after();
       fold_pv(alpha_prev);
-      if (row < rows) {
+      half_sum[half * 128 + row] = l;
+      ok = pair_sync();
+      l += half_sum[(half ^ 1) * 128 + row];
+      if (row < rows && ok) {
         const float inv = l > 0.f ? 1.f / l : 0.f;
         uint16_t* dst = reinterpret_cast<uint16_t*>(p.out) +
-                        (static_cast<long>(q_begin + qt0 + row) * p.nh + head) * HD;
+                        (static_cast<long>(q_begin + qt0 + row) * p.nh + head) * HD + half * HH;
 #pragma unroll
-        for (int c = 0; c < HD / 8; ++c) {
+        for (int c = 0; c < HH / 8; ++c) {
           uint4 v;
           v.x = pack2(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv, p.is_fp16);
           v.y = pack2(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv, p.is_fp16);
@@ -363,7 +401,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
           *reinterpret_cast<uint4*>(dst + c * 8) = v;
         }
       }
-    } else {
+    }
+    if (!ok) {
       set_status(p.status, kStatusTimeoutAccum);
       *aborted = 1;
     }
