@@ -38,6 +38,9 @@ struct TcParams {
   const int* seq_lens;       // [B]
   const int* cu_q;           // [B + 1]
   int* status;
+  // optional device array of 256 cycle counts: the CTA (0, 0, 0) records when its softmax thread 0,
+  // its UMMA thread and its TMA thread pass the points of the first 16 tiles (see mark())
+  unsigned long long* trace;
   int max_blocks, block_size, nh, nkv, window;
   float sm_scale, softcap;
   int is_fp16;
@@ -56,6 +59,11 @@ struct TcSmem {
   static constexpr int kBars = 256 + 3 * 2 * 128 * 4;   // barriers + row maxima [2 parities][2 halves][128] + sums
   static constexpr int kBytes = kQ + kP + 2 * STAGES * kKV + kBars + 1024;
 };
+
+__device__ __forceinline__ void mark(unsigned long long* trace, int slot) {
+  if (trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && slot < 256)
+    trace[slot] = static_cast<unsigned long long>(clock64());
+}
 
 __device__ __forceinline__ uint32_t pack2(float a, float b, int is_fp16) {
   if (is_fp16) {
@@ -166,6 +174,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
           *aborted = 1;
           break;
         }
+        if (j < 16) mark(p.trace, 192 + j * 2);
         const int tok0 = (tile_begin + j) * kTile;
         mbar_expect_tx(&k_full[st], L::kKV);
         mbar_expect_tx(&v_full[st], L::kKV);
@@ -187,6 +196,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
           for (int a = 0; a < kAtoms; ++a)
             tma_load_2d(sV + st * L::kKV + a * kAtomBytes + pg * 2048, &v_map, &v_full[st], a * 64, rowi[pg]);
         issued = j + 1;
+        if (j < 16) mark(p.trace, 193 + j * 2);
       }
       // own copies in flight: the last tiles issued must have landed before the CTA may leave
       for (int j = max(0, issued - STAGES); j < issued; ++j) {
@@ -225,9 +235,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
       ok = ok && issue_qk(0);
       for (int j = 0; j < n_tiles && ok; ++j) {
         if (j + 1 < n_tiles) ok = issue_qk(j + 1);
+        if (j < 16) mark(p.trace, 128 + j * 4);
         const int st = j % STAGES;
-        ok = ok && mbar_wait(p_full, j & 1) && mbar_wait(&v_full[st], (j / STAGES) & 1);
+        ok = ok && mbar_wait(p_full, j & 1);
+        if (j < 16) mark(p.trace, 129 + j * 4);
+        ok = ok && mbar_wait(&v_full[st], (j / STAGES) & 1);
         if (!ok) break;
+        if (j < 16) mark(p.trace, 130 + j * 4);
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
@@ -235,10 +249,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
           const uint64_t dp = umma_desc_sw128_kmajor(smem_u32(sP + (k >> 2) * kAtomBytes)) + 2 * (k & 3);
           // V: 16 keys = 16 rows of 128 bytes; the second 64 channels follow one 128-row block later
           const uint64_t dv = umma_desc_sw128_mnmajor(smem_u32(sV + st * L::kKV + k * 2048), kAtomBytes);
-          umma_f16(tmem_base + kPvCol, dp, dv, idesc_pv, k != 0 ? 1u : 0u);
+          umma_f16(tmem_base + kPvCol + (j & 1) * HD, dp, dv, idesc_pv, k != 0 ? 1u : 0u);
         }
         umma_commit(&kv_empty[st]);
         umma_commit(pv_full);
+        if (j < 16) mark(p.trace, 131 + j * 4);
       }
       if (!ok) {
         set_status(p.status, kStatusTimeoutFull);
@@ -269,121 +284,97 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
       return mbar_wait(&pair_bar[quad], (pair_n++) & 1);
     };
 
-    auto fold_pv = [&](float alpha) {
+    auto fold_pv = [&](int buf, float alpha) {
 #pragma unroll
       for (int c = 0; c < HH / 32; ++c) {
         uint32_t r[32];
-        tmem_ld_x32(t_lane + kPvCol + half * HH + c * 32, r);
+        tmem_ld_x32(t_lane + kPvCol + buf * HD + half * HH + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 32; ++e) o[c * 32 + e] = fmaf(o[c * 32 + e], alpha, __uint_as_float(r[e]));
       }
     };
+    const float to_log2 = capped ? cap_out : sl2;    // raw (or tanh'ed) score -> exponent of 2
 
-    // The two passes over a half row of S, compiled once per (touches a mask edge, soft cap) so that the
-    // common tile carries neither the comparisons nor the tanh.
-    constexpr std::integral_constant<bool, true> kTrue{};
-    constexpr std::integral_constant<bool, false> kFalse{};
-    auto pass1 = [&](auto edge_c, auto cap_c, uint32_t t_s, int vis_lo, int vis_hi) -> float {
-      float mt = -CUDART_INF_F;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld_x32(t_s + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float v = __uint_as_float(r[e]);
-          if (decltype(cap_c)::value) v = fast_tanh(v * cap_in);
-          if (decltype(edge_c)::value) {
-            const int kk = c * 32 + e;
-            if (kk < vis_lo || kk >= vis_hi) v = -CUDART_INF_F;
-          }
-          mt = fmaxf(mt, v);
-        }
-      }
-      return mt;
-    };
-    auto pass2 = [&](auto edge_c, auto cap_c, uint32_t t_s, int vis_lo, int vis_hi, float m_use) -> float {
-      float rs = 0.f;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld_x32(t_s + c * 32, r);
-        tmem_ld_wait();
-        uint32_t w[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float v0 = __uint_as_float(r[e]), v1 = __uint_as_float(r[e + 1]);
-          float p0, p1;
-          if (decltype(cap_c)::value) {
-            p0 = fast_exp2(fmaf(fast_tanh(v0 * cap_in), cap_out, -m_use));
-            p1 = fast_exp2(fmaf(fast_tanh(v1 * cap_in), cap_out, -m_use));
-          } else {
-            p0 = fast_exp2(fmaf(v0, sl2, -m_use));
-            p1 = fast_exp2(fmaf(v1, sl2, -m_use));
-          }
-          if (decltype(edge_c)::value) {
-            const int kk = c * 32 + e;
-            if (kk < vis_lo || kk >= vis_hi) p0 = 0.f;
-            if (kk + 1 < vis_lo || kk + 1 >= vis_hi) p1 = 0.f;
-          }
-          rs += p0 + p1;
-          w[e >> 1] = pack2(p0, p1, p.is_fp16);
-        }
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4)
-          *reinterpret_cast<uint4*>(sP + half * kAtomBytes + sw128_offset(row, c * 4 + q4)) =
-              make_uint4(w[q4 * 4], w[q4 * 4 + 1], w[q4 * 4 + 2], w[q4 * 4 + 3]);
-      }
-      return rs;
-    };
-
+    unsigned long long* tr = (threadIdx.x == 64) ? p.trace : nullptr;
     for (int j = 0; j < n_tiles; ++j) {
       const int sb = j & 1;
       if (!mbar_wait(&s_full[sb], (j >> 1) & 1)) { ok = false; break; }
+      if (j < 16) mark(tr, j * 8);
       tc_fence_after();
-      const int k0 = (tile_begin + j) * kTile + half * 64;   // first key of this thread's 64
-      // keys of this half-tile the row may see: [vis_lo, vis_hi)
-      const bool edge = (k0 + 63 > first_pos) || (p.window > 0 && k0 <= last_pos - p.window);
-      const int vis_hi = min(64, qpos - k0 + 1);
-      const int vis_lo = p.window > 0 ? max(0, qpos - p.window + 1 - k0) : 0;
-      const uint32_t t_s = t_lane + sb * kTile + half * 64;
+      // this thread's 64 scores: read once, kept in registers, and the S buffer handed back at once
+      uint32_t sr[64];
+      tmem_ld_x32(t_lane + sb * kTile + half * 64, sr);
+      tmem_ld_x32(t_lane + sb * kTile + half * 64 + 32, sr + 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&s_empty[sb]);
+      if (j < 16) mark(tr, j * 8 + 1);
 
-      // pass 1: the maximum of this half of the row (in the exp2 domain), then the other half's
-      float mt = capped ? (edge ? pass1(kTrue, kTrue, t_s, vis_lo, vis_hi) : pass1(kFalse, kTrue, t_s, 0, 64))
-                        : (edge ? pass1(kTrue, kFalse, t_s, vis_lo, vis_hi) : pass1(kFalse, kFalse, t_s, 0, 64));
-      mt *= capped ? cap_out : sl2;                  // both factors are positive
+      const int k0 = (tile_begin + j) * kTile + half * 64;   // first key of this thread's 64
+      // keys of this half-tile the row may see: [vis_lo, vis_hi); only tiles on an edge look at them
+      const bool edge = (k0 + 63 > first_pos) || (p.window > 0 && k0 <= last_pos - p.window);
+      if (capped) {
+#pragma unroll
+        for (int e = 0; e < 64; ++e) sr[e] = __float_as_uint(fast_tanh(__uint_as_float(sr[e]) * cap_in));
+      }
+      if (edge) {
+        const int vis_hi = qpos - k0 + 1;
+        const int vis_lo = p.window > 0 ? qpos - p.window + 1 - k0 : 0;
+#pragma unroll
+        for (int e = 0; e < 64; ++e)
+          if (e < vis_lo || e >= vis_hi) sr[e] = 0xff800000u;   // -inf: probability 0
+      }
+      float mt = -CUDART_INF_F;
+#pragma unroll
+      for (int e = 0; e < 64; ++e) mt = fmaxf(mt, __uint_as_float(sr[e]));
+      mt *= to_log2;                                 // the factor is positive
       half_max[(sb * 2 + half) * 128 + row] = mt;
+      if (j < 16) mark(tr, j * 8 + 2);
       if (!pair_sync()) { ok = false; break; }
+      if (j < 16) mark(tr, j * 8 + 3);
       mt = fmaxf(mt, half_max[(sb * 2 + (half ^ 1)) * 128 + row]);
       const float m_new = fmaxf(m, mt);
       const float m_use = m_new == -CUDART_INF_F ? 0.f : m_new;
       const float alpha = fast_exp2(m - m_use);
 
-      if (j > 0) {
-        if (!mbar_wait(pv_full, (j - 1) & 1)) { ok = false; break; }
-        tc_fence_after();
-        fold_pv(alpha_prev);
+      // probabilities, packed in place (two per register)
+      float rs = 0.f;
+#pragma unroll
+      for (int e = 0; e < 64; e += 2) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(sr[e]), to_log2, -m_use));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(sr[e + 1]), to_log2, -m_use));
+        rs += p0 + p1;
+        sr[e >> 1] = pack2(p0, p1, p.is_fp16);
       }
-
-      // pass 2: probabilities, written as the A operand of P V (K-major, 128-byte swizzle; the 64 keys
-      // of this half are exactly one 128-byte row of the half's own block)
-      const float rs =
-          capped ? (edge ? pass2(kTrue, kTrue, t_s, vis_lo, vis_hi, m_use) : pass2(kFalse, kTrue, t_s, 0, 64, m_use))
-                 : (edge ? pass2(kTrue, kFalse, t_s, vis_lo, vis_hi, m_use) : pass2(kFalse, kFalse, t_s, 0, 64, m_use));
       l = l * alpha + rs;                            // this half's share of the denominator
       m = m_new;
-      alpha_prev = alpha;
-      tc_fence_before();
+
+      // P is the A operand of P V (K-major, 128-byte swizzle; the 64 keys of this half are exactly one
+      // 128-byte row of the half's own block).  The previous product must have finished reading it.
+      if (j < 16) mark(tr, j * 8 + 4);
+      if (j > 0 && !mbar_wait(pv_full, (j - 1) & 1)) { ok = false; break; }
+      if (j < 16) mark(tr, j * 8 + 5);
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        *reinterpret_cast<uint4*>(sP + half * kAtomBytes + sw128_offset(row, q)) =
+            make_uint4(sr[q * 4], sr[q * 4 + 1], sr[q * 4 + 2], sr[q * 4 + 3]);
       fence_proxy_async_smem();
       mbar_arrive(p_full);
-      mbar_arrive(&s_empty[sb]);
+      if (j < 16) mark(tr, j * 8 + 6);
+      // fold the previous tile's product while the tensor core works on this one
+      if (j > 0) {
+        tc_fence_after();
+        fold_pv((j - 1) & 1, alpha_prev);
+        tc_fence_before();
+      }
+      if (j < 16) mark(tr, j * 8 + 7);
+      alpha_prev = alpha;
     }
     if (ok) ok = mbar_wait(pv_full, (n_tiles - 1) & 1);
     if (ok) {
       tc_fence_after();
-      fold_pv(alpha_prev);
+      fold_pv((n_tiles - 1) & 1, alpha_prev);
       half_sum[half * 128 + row] = l;
       ok = pair_sync();
       l += half_sum[(half ^ 1) * 128 + row];
@@ -428,7 +419,16 @@ int launch_tc(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& v
   return static_cast<int>(ce != cudaSuccess ? ce : cudaGetLastError());
 }
 
+unsigned long long* g_tc_trace = nullptr;
+
 }  // namespace
+
+// Development aid: a device array of 256 cycle counts (or null) that the next launches fill, see
+// TcParams::trace.
+extern "C" int fi_paged_prefill_tc_set_trace(void* trace) {
+  g_tc_trace = reinterpret_cast<unsigned long long*>(trace);
+  return 0;
+}
 
 // Tensor-core prefill attention for 16-bit caches with head size 64 or 128 and pages of a multiple of
 // 16 tokens.  Returns -12 when the arguments are outside what this kernel covers (the caller then uses
@@ -454,6 +454,7 @@ extern "C" int fi_paged_prefill_tc(const void* q, long q_stride, const void* k_c
     return -12;
   TcParams p = {};
   p.out = out; p.block_tables = block_tables; p.seq_lens = seq_lens; p.cu_q = cu_q; p.status = status;
+  p.trace = g_tc_trace;
   p.max_blocks = max_blocks; p.block_size = block_size; p.nh = nh; p.nkv = nkv; p.window = window;
   p.sm_scale = sm_scale; p.softcap = softcap; p.is_fp16 = dtype == 1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
