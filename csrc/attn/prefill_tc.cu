@@ -5,15 +5,17 @@
 // tiles of 128 keys:
 //
 //   warp 0   TMA producer: the Q tile once, then K and V tiles page by page (a page of 16 tokens is
-//            one box per 64 channels) into a ring of STAGES tiles, 128-byte swizzle
+//            one box per 64 channels, one lane per box) into rings of STAGES tiles, 128-byte swizzle
 //   warp 1   UMMA issuer:  S = Q K^T  (128 x 128, fp32 in TMEM, two S buffers so the product of the
-//            next tile runs under the softmax of this one) and  PV = P V  (128 x HD, its own TMEM
-//            columns; V is read MN-major, exactly as the cache stores it)
+//            next tile runs under the softmax of this one) and  PV = P V  (128 x HD, two buffers of
+//            their own; P is read from TMEM, V MN-major from shared memory, exactly as the cache
+//            stores it)
 //   warps 2-9  two threads per query row (warps 2-5 own keys 0-63 of a tile and the first half of the
 //            output channels, warps 6-9 keys 64-127 and the second half): read S from TMEM, online
 //            softmax in the exp2 domain (the two halves exchange their row maximum through shared
-//            memory once per tile), write P in the operand layout to shared memory, then fold PV into
-//            the row's fp32 output registers (o = o * alpha + PV) so TMEM never has to be rescaled
+//            memory once per tile), write P as 16-bit pairs over the first 64 columns of the S buffer,
+//            then fold PV of the previous tile into the row's fp32 output registers
+//            (o = o * alpha + PV) so TMEM never has to be rescaled
 //
 // Masks (causal edge, sliding window, end of sequence) are applied only in tiles that touch an edge.
 // Every wait is bounded; a wait that runs out sets the status word and the CTA leaves through the
@@ -22,8 +24,6 @@
 // The reference computes the same thing with its Triton context-attention kernel
 // (vllm/attention/ops/triton_prefix_prefill.py in the reference tree).
 #include <math_constants.h>
-
-#include <type_traits>
 
 #include "../common/launch.cuh"
 #include "../common/ptx.cuh"
@@ -54,10 +54,9 @@ constexpr float kLog2e = 1.4426950408889634f;
 template <int HD, int STAGES>
 struct TcSmem {
   static constexpr int kQ = HD * 256;
-  static constexpr int kP = 2 * kAtomBytes;
   static constexpr int kKV = HD * 256;
-  static constexpr int kBars = 256 + 3 * 2 * 128 * 4;   // barriers + row maxima [2 parities][2 halves][128] + sums
-  static constexpr int kBytes = kQ + kP + 2 * STAGES * kKV + kBars + 1024;
+  static constexpr int kHead = 3072;   // barriers (512 B) + row maxima [2 parities][2 halves][128], padded to 1024
+  static constexpr int kBytes = kHead + kQ + 2 * STAGES * kKV;
 };
 
 __device__ __forceinline__ void mark(unsigned long long* trace, int slot) {
@@ -80,6 +79,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                   const __grid_constant__ CUtensorMap v_map, const TcParams p) {
   using L = TcSmem<HD, STAGES>;
   constexpr int kAtoms = HD / 64;
+  constexpr int kBoxes = 8 * kAtoms;            // TMA boxes (one page x 64 channels) per K or V tile
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kPvCol = 256;
 
@@ -106,38 +106,42 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
   const int kvh = head / (p.nh / p.nkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = base;
-  uint8_t* sP = sQ + L::kQ;
-  uint8_t* sK = sP + L::kP;
+  // The swizzled tiles need 1024-byte alignment and the largest configuration uses the whole 227 KB, so
+  // there is no slack to round up with: the block starts aligned or the CTA refuses to run.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if ((smem_u32(smem_raw) & 1023u) != 0) {
+    if (threadIdx.x == 0) set_status(p.status, kStatusBadArg);
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw);
+  uint8_t* sQ = smem_raw + L::kHead;
+  uint8_t* sK = sQ + L::kQ;
   uint8_t* sV = sK + STAGES * L::kKV;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + STAGES * L::kKV);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;
   uint64_t* v_full = k_full + STAGES;
-  uint64_t* kv_empty = v_full + STAGES;
-  uint64_t* s_full = kv_empty + STAGES;      // [2]
-  uint64_t* s_empty = s_full + 2;            // [2]
-  uint64_t* p_full = s_empty + 2;
+  uint64_t* k_empty = v_full + STAGES;
+  uint64_t* v_empty = k_empty + STAGES;
+  uint64_t* s_full = v_empty + STAGES;       // [2]
+  uint64_t* p_full = s_full + 2;
   uint64_t* pv_full = p_full + 1;
   uint64_t* pair_bar = pv_full + 1;          // [4]: the two warps of a TMEM quadrant
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_bar + 4);
   volatile int* aborted = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* half_max = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);   // [2][2][128]
-  float* half_sum = half_max + 2 * 2 * 128;                                             // [2][128]
+  float* half_max = reinterpret_cast<float*>(smem_raw + 512);   // [2 parities][2 halves][128]
+  // the denominators meet in the parity buffer that the last tile did not use
+  float* half_sum = half_max + (n_tiles & 1) * 2 * 128;        // [2 halves][128]
+  static_assert((1 + 4 * STAGES + 2 + 1 + 1 + 4) * 8 + 8 <= 512, "barrier block");
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < STAGES; ++i) {
-      mbar_init(&k_full[i], 1);
-      mbar_init(&v_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+      mbar_init(&k_full[i], kBoxes);          // every producer lane announces its own box
+      mbar_init(&v_full[i], kBoxes);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 256);
-    }
+    for (int i = 0; i < 2; ++i) mbar_init(&s_full[i], 1);
     mbar_init(p_full, 256);
     mbar_init(pv_full, 1);
     for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 64);
@@ -156,53 +160,51 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (elect_one()) {
+    // One lane per box: lanes [0, kBoxes) fetch the K tile, lanes [kBoxes, 2 kBoxes) the V tile; lane
+    // l's box is page (l / kAtoms) % 8, channels 64 (l % kAtoms).  The K slot of a stage is free as soon
+    // as Q K^T of its tile has run, the V slot after P V, so the two halves wait separately.
+    if (lane == 0) {
       tma_prefetch_desc(&q_map);
-      tma_prefetch_desc(&k_map);
-      tma_prefetch_desc(&v_map);
       mbar_expect_tx(q_full, L::kQ);
 #pragma unroll
       for (int a = 0; a < kAtoms; ++a)
         tma_load_2d(sQ + a * kAtomBytes, &q_map, q_full, head * HD + a * 64, q_begin + qt0);
+    }
+    if (lane < 2 * kBoxes) {
+      const bool is_v = lane >= kBoxes;
+      const int pg = ((lane % kBoxes) / kAtoms), a = lane % kAtoms;
+      const CUtensorMap* map = is_v ? &v_map : &k_map;
+      uint8_t* tile0 = (is_v ? sV : sK) + a * kAtomBytes + pg * 2048;
+      uint64_t* full = is_v ? v_full : k_full;
+      uint64_t* empty = is_v ? v_empty : k_empty;
+      tma_prefetch_desc(map);
       const int* bt = p.block_tables + static_cast<long>(b) * p.max_blocks;
+      auto row_of = [&](int j) -> int {
+        const int tok = (tile_begin + j) * kTile + pg * 16;
+        const int blk = tok < seq_len ? bt[tok / p.block_size] : 0;     // past the end: the null block
+        return (blk * p.nkv + kvh) * p.block_size + tok % p.block_size;
+      };
+      int row_next = row_of(0);
       int issued = 0;
       for (int j = 0; j < n_tiles; ++j) {
         const int st = j % STAGES;
         const uint32_t ph = (j / STAGES) & 1;
-        if (!mbar_wait(&kv_empty[st], ph ^ 1)) {
+        const int row = row_next;
+        if (j + 1 < n_tiles) row_next = row_of(j + 1);   // the page id of the next tile is in flight during the wait
+        if (!mbar_wait(&empty[st], ph ^ 1)) {
           set_status(p.status, kStatusTimeoutEmpty);
           *aborted = 1;
           break;
         }
-        if (j < 16) mark(p.trace, 192 + j * 2);
-        const int tok0 = (tile_begin + j) * kTile;
-        mbar_expect_tx(&k_full[st], L::kKV);
-        mbar_expect_tx(&v_full[st], L::kKV);
-        int rowi[8];
-#pragma unroll
-        for (int pg = 0; pg < 8; ++pg) {
-          const int tok = tok0 + pg * 16;
-          const int blk = tok < seq_len ? bt[tok / p.block_size] : 0;   // past the end: the null block
-          rowi[pg] = (blk * p.nkv + kvh) * p.block_size + tok % p.block_size;
-        }
-#pragma unroll
-        for (int pg = 0; pg < 8; ++pg)
-#pragma unroll
-          for (int a = 0; a < kAtoms; ++a)
-            tma_load_2d(sK + st * L::kKV + a * kAtomBytes + pg * 2048, &k_map, &k_full[st], a * 64, rowi[pg]);
-#pragma unroll
-        for (int pg = 0; pg < 8; ++pg)
-#pragma unroll
-          for (int a = 0; a < kAtoms; ++a)
-            tma_load_2d(sV + st * L::kKV + a * kAtomBytes + pg * 2048, &v_map, &v_full[st], a * 64, rowi[pg]);
+        if (lane == 0 && j < 16) mark(p.trace, 192 + j * 2);
+        mbar_expect_tx(&full[st], 2048);
+        tma_load_2d(tile0 + st * L::kKV, map, &full[st], a * 64, row);
         issued = j + 1;
-        if (j < 16) mark(p.trace, 193 + j * 2);
+        if (lane == 0 && j < 16) mark(p.trace, 193 + j * 2);
       }
       // own copies in flight: the last tiles issued must have landed before the CTA may leave
       for (int j = max(0, issued - STAGES); j < issued; ++j) {
-        const int st = j % STAGES;
-        const uint32_t ph = (j / STAGES) & 1;
-        if (!mbar_wait(&k_full[st], ph) || !mbar_wait(&v_full[st], ph)) {
+        if (!mbar_wait(&full[j % STAGES], (j / STAGES) & 1)) {
           set_status(p.status, kStatusTimeoutFull);
           break;
         }
@@ -210,6 +212,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ UMMA issuer
+    // The tensor pipe runs the products in the order they are issued, which is what keeps the aliases
+    // apart: Q K^T of tile j+2 (same S buffer as tile j, which also holds P of tile j) is issued after
+    // P V of tile j, and P V of tile j is issued only after all 256 softmax threads have read S_j and
+    // written P_j.
     if (elect_one()) {
       const uint32_t fmt = p.is_fp16 ? 0 : 1;
       const uint32_t idesc_qk = umma_idesc_f16(fmt, kTile, kTile);
@@ -219,7 +225,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
       auto issue_qk = [&](int j) -> bool {
         const int st = j % STAGES, sb = j & 1;
         if (!mbar_wait(&k_full[st], (j / STAGES) & 1)) return false;
-        if (!mbar_wait(&s_empty[sb], ((j >> 1) & 1) ^ 1)) return false;
         tc_fence_after();
 #pragma unroll
         for (int a = 0; a < kAtoms; ++a) {
@@ -230,6 +235,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             umma_f16(tmem_base + sb * kTile, dq + 2 * k, dk + 2 * k, idesc_qk, (a | k) != 0 ? 1u : 0u);
         }
         umma_commit(&s_full[sb]);
+        umma_commit(&k_empty[st]);
         return true;
       };
       ok = ok && issue_qk(0);
@@ -245,13 +251,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          // P: keys [16k, 16k + 16) = 32 bytes inside the 64-key block k / 4
-          const uint64_t dp = umma_desc_sw128_kmajor(smem_u32(sP + (k >> 2) * kAtomBytes)) + 2 * (k & 3);
+          // P: rows in lanes, keys [16k, 16k + 16) in 8 columns of the tile's S buffer
+          const uint32_t tp = tmem_base + (j & 1) * kTile + k * 8;
           // V: 16 keys = 16 rows of 128 bytes; the second 64 channels follow one 128-row block later
           const uint64_t dv = umma_desc_sw128_mnmajor(smem_u32(sV + st * L::kKV + k * 2048), kAtomBytes);
-          umma_f16(tmem_base + kPvCol + (j & 1) * HD, dp, dv, idesc_pv, k != 0 ? 1u : 0u);
+          umma_f16_a_tmem(tmem_base + kPvCol + (j & 1) * HD, tp, dv, idesc_pv, k != 0 ? 1u : 0u);
         }
-        umma_commit(&kv_empty[st]);
+        umma_commit(&v_empty[st]);
         umma_commit(pv_full);
         if (j < 16) mark(p.trace, 131 + j * 4);
       }
@@ -302,13 +308,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
       if (!mbar_wait(&s_full[sb], (j >> 1) & 1)) { ok = false; break; }
       if (j < 16) mark(tr, j * 8);
       tc_fence_after();
-      // this thread's 64 scores: read once, kept in registers, and the S buffer handed back at once
+      // this thread's 64 scores: read once, kept in registers
       uint32_t sr[64];
       tmem_ld_x32(t_lane + sb * kTile + half * 64, sr);
       tmem_ld_x32(t_lane + sb * kTile + half * 64 + 32, sr + 32);
       tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(&s_empty[sb]);
       if (j < 16) mark(tr, j * 8 + 1);
 
       const int k0 = (tile_begin + j) * kTile + half * 64;   // first key of this thread's 64
@@ -325,12 +329,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         for (int e = 0; e < 64; ++e)
           if (e < vis_lo || e >= vis_hi) sr[e] = 0xff800000u;   // -inf: probability 0
       }
-      float mt = -CUDART_INF_F;
+      float mt4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-      for (int e = 0; e < 64; ++e) mt = fmaxf(mt, __uint_as_float(sr[e]));
-      mt *= to_log2;                                 // the factor is positive
+      for (int e = 0; e < 64; ++e) mt4[e & 3] = fmaxf(mt4[e & 3], __uint_as_float(sr[e]));
+      float mt = fmaxf(fmaxf(mt4[0], mt4[1]), fmaxf(mt4[2], mt4[3])) * to_log2;   // the factor is positive
       half_max[(sb * 2 + half) * 128 + row] = mt;
       if (j < 16) mark(tr, j * 8 + 2);
+      // after this meeting both halves hold their scores in registers: the buffer may take P
       if (!pair_sync()) { ok = false; break; }
       if (j < 16) mark(tr, j * 8 + 3);
       mt = fmaxf(mt, half_max[(sb * 2 + (half ^ 1)) * 128 + row]);
@@ -338,32 +343,29 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
       const float m_use = m_new == -CUDART_INF_F ? 0.f : m_new;
       const float alpha = fast_exp2(m - m_use);
 
-      // probabilities, packed in place (two per register)
-      float rs = 0.f;
+      // probabilities, packed in place (two per register) and written over the first 64 columns of the
+      // S buffer: the A operand of P V, read from tensor memory
+      float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
       for (int e = 0; e < 64; e += 2) {
         const float p0 = fast_exp2(fmaf(__uint_as_float(sr[e]), to_log2, -m_use));
         const float p1 = fast_exp2(fmaf(__uint_as_float(sr[e + 1]), to_log2, -m_use));
-        rs += p0 + p1;
+        rs0 += p0;
+        rs1 += p1;
         sr[e >> 1] = pack2(p0, p1, p.is_fp16);
       }
-      l = l * alpha + rs;                            // this half's share of the denominator
+      l = l * alpha + (rs0 + rs1);                   // this half's share of the denominator
       m = m_new;
-
-      // P is the A operand of P V (K-major, 128-byte swizzle; the 64 keys of this half are exactly one
-      // 128-byte row of the half's own block).  The previous product must have finished reading it.
       if (j < 16) mark(tr, j * 8 + 4);
-      if (j > 0 && !mbar_wait(pv_full, (j - 1) & 1)) { ok = false; break; }
-      if (j < 16) mark(tr, j * 8 + 5);
-#pragma unroll
-      for (int q = 0; q < 8; ++q)
-        *reinterpret_cast<uint4*>(sP + half * kAtomBytes + sw128_offset(row, q)) =
-            make_uint4(sr[q * 4], sr[q * 4 + 1], sr[q * 4 + 2], sr[q * 4 + 3]);
-      fence_proxy_async_smem();
+      tmem_st_x32(t_lane + sb * kTile + half * 32, sr);
+      tmem_st_wait();
+      tc_fence_before();
       mbar_arrive(p_full);
-      if (j < 16) mark(tr, j * 8 + 6);
+      if (j < 16) mark(tr, j * 8 + 5);
       // fold the previous tile's product while the tensor core works on this one
       if (j > 0) {
+        if (!mbar_wait(pv_full, (j - 1) & 1)) { ok = false; break; }
+        if (j < 16) mark(tr, j * 8 + 6);
         tc_fence_after();
         fold_pv((j - 1) & 1, alpha_prev);
         tc_fence_before();
@@ -458,6 +460,6 @@ extern "C" int fi_paged_prefill_tc(const void* q, long q_stride, const void* k_c
   p.max_blocks = max_blocks; p.block_size = block_size; p.nh = nh; p.nkv = nkv; p.window = window;
   p.sm_scale = sm_scale; p.softcap = softcap; p.is_fp16 = dtype == 1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (hd == 64) return launch_tc<64, 4>(qm, km, vm, p, B, max_q_len, s);
-  return launch_tc<128, 2>(qm, km, vm, p, B, max_q_len, s);
+  if (hd == 64) return launch_tc<64, 6>(qm, km, vm, p, B, max_q_len, s);
+  return launch_tc<128, 3>(qm, km, vm, p, B, max_q_len, s);
 }
