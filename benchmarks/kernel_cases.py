@@ -35,6 +35,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--json", default=None)
     ap.add_argument("--list", action="store_true")
+    ap.add_argument("--kv-block", type=int, default=16, help="tokens per KV page in the prefill attention cases")
     args = ap.parse_args()
 
     import torch
@@ -116,7 +117,7 @@ def main():
 
     @case("prefill_attention")
     def _():
-        B, L, nh, nkv, hd, bs = 8, 2048, 32, 8, 128, 16
+        B, L, nh, nkv, hd, bs = 8, 2048, 32, 8, 128, args.kv_block
         blocks_per = L // bs
         nb = B * blocks_per + 1
         kc, vc = rnd(nb, nkv, bs, hd), rnd(nb, nkv, bs, hd)
@@ -126,11 +127,11 @@ def main():
         qkv = rnd(B * L, (nh + 2 * nkv) * hd)
         return (lambda: ops.paged_attention_prefill(qkv, kc, vc, bt, sl, cu, L, nh, nkv, hd, hd ** -0.5)), \
             (B * L * (nh + 2 * nkv) * hd + B * L * nh * hd) * 2, 4.0 * B * nh * L * L * hd / 2, \
-            f"B={B} L={L} causal {nh}q/{nkv}kv hd={hd}"
+            f"B={B} L={L} causal {nh}q/{nkv}kv hd={hd} page {bs}"
 
     @case("prefill_attention_hd64")
     def _():
-        B, L, nh, nkv, hd, bs = 8, 1024, 32, 4, 64, 16     # one TinyLlama prefill micro-batch
+        B, L, nh, nkv, hd, bs = 8, 1024, 32, 4, 64, args.kv_block     # one TinyLlama prefill micro-batch
         blocks_per = L // bs
         nb = B * blocks_per + 1
         kc, vc = rnd(nb, nkv, bs, hd), rnd(nb, nkv, bs, hd)
@@ -140,7 +141,7 @@ def main():
         qkv = rnd(B * L, (nh + 2 * nkv) * hd)
         return (lambda: ops.paged_attention_prefill(qkv, kc, vc, bt, sl, cu, L, nh, nkv, hd, hd ** -0.5)), \
             (B * L * (nh + 2 * nkv) * hd + B * L * nh * hd) * 2, 4.0 * B * nh * L * L * hd / 2, \
-            f"B={B} L={L} causal {nh}q/{nkv}kv hd={hd}"
+            f"B={B} L={L} causal {nh}q/{nkv}kv hd={hd} page {bs}"
 
     @case("rmsnorm")
     def _():

@@ -79,7 +79,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                   const __grid_constant__ CUtensorMap v_map, const TcParams p) {
   using L = TcSmem<HD, STAGES>;
   constexpr int kAtoms = HD / 64;
-  constexpr int kBoxes = 8 * kAtoms;            // TMA boxes (one page x 64 channels) per K or V tile
+  // TMA boxes per K or V tile: one per (run of box_rows tokens inside a page, 64 channels); 16-token
+  // pages give 8 runs per 128-key tile, pages of 128 tokens one
+  const int box_rows = min(p.block_size, kTile);
+  const int n_boxes = (kTile / box_rows) * kAtoms;
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kPvCol = 256;
 
@@ -136,8 +139,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < STAGES; ++i) {
-      mbar_init(&k_full[i], kBoxes);          // every producer lane announces its own box
-      mbar_init(&v_full[i], kBoxes);
+      mbar_init(&k_full[i], n_boxes);         // every producer lane announces its own box
+      mbar_init(&v_full[i], n_boxes);
       mbar_init(&k_empty[i], 1);
       mbar_init(&v_empty[i], 1);
     }
@@ -160,8 +163,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    // One lane per box: lanes [0, kBoxes) fetch the K tile, lanes [kBoxes, 2 kBoxes) the V tile; lane
-    // l's box is page (l / kAtoms) % 8, channels 64 (l % kAtoms).  The K slot of a stage is free as soon
+    // One lane per box: lanes [0, n_boxes) fetch the K tile, lanes [n_boxes, 2 n_boxes) the V tile;
+    // lane l's box is token run (l % n_boxes) / kAtoms, channels 64 (l % kAtoms).  The K slot of a stage is free as soon
     // as Q K^T of its tile has run, the V slot after P V, so the two halves wait separately.
     if (lane == 0) {
       tma_prefetch_desc(&q_map);
@@ -170,17 +173,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
       for (int a = 0; a < kAtoms; ++a)
         tma_load_2d(sQ + a * kAtomBytes, &q_map, q_full, head * HD + a * 64, q_begin + qt0);
     }
-    if (lane < 2 * kBoxes) {
-      const bool is_v = lane >= kBoxes;
-      const int pg = ((lane % kBoxes) / kAtoms), a = lane % kAtoms;
+    if (lane < 2 * n_boxes) {
+      const bool is_v = lane >= n_boxes;
+      const int pg = ((lane % n_boxes) / kAtoms), a = lane % kAtoms;
+      const uint32_t box_bytes = static_cast<uint32_t>(box_rows) * 128u;
       const CUtensorMap* map = is_v ? &v_map : &k_map;
-      uint8_t* tile0 = (is_v ? sV : sK) + a * kAtomBytes + pg * 2048;
+      uint8_t* tile0 = (is_v ? sV : sK) + a * kAtomBytes + pg * box_bytes;
       uint64_t* full = is_v ? v_full : k_full;
       uint64_t* empty = is_v ? v_empty : k_empty;
       tma_prefetch_desc(map);
       const int* bt = p.block_tables + static_cast<long>(b) * p.max_blocks;
       auto row_of = [&](int j) -> int {
-        const int tok = (tile_begin + j) * kTile + pg * 16;
+        const int tok = (tile_begin + j) * kTile + pg * box_rows;
         const int blk = tok < seq_len ? bt[tok / p.block_size] : 0;     // past the end: the null block
         return (blk * p.nkv + kvh) * p.block_size + tok % p.block_size;
       };
@@ -197,7 +201,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
           break;
         }
         if (lane == 0 && j < 16) mark(p.trace, 192 + j * 2);
-        mbar_expect_tx(&full[st], 2048);
+        mbar_expect_tx(&full[st], box_bytes);
         tma_load_2d(tile0 + st * L::kKV, map, &full[st], a * 64, row);
         issued = j + 1;
         if (lane == 0 && j < 16) mark(p.trace, 193 + j * 2);
@@ -432,8 +436,8 @@ extern "C" int fi_paged_prefill_tc_set_trace(void* trace) {
   return 0;
 }
 
-// Tensor-core prefill attention for 16-bit caches with head size 64 or 128 and pages of a multiple of
-// 16 tokens.  Returns -12 when the arguments are outside what this kernel covers (the caller then uses
+// Tensor-core prefill attention for 16-bit caches with head size 64 or 128 and pages of 16, 32, 64 or
+// a multiple of 128 tokens (larger pages mean fewer, larger TMA boxes per tile).  Returns -12 when the arguments are outside what this kernel covers (the caller then uses
 // the general kernel), other negative values for malformed arguments.
 //   q: token t, head h at q + (t * q_stride + h * hd) elements, T_total rows; caches [num_blocks, nkv,
 //   block_size, hd]; out [T_total, nh * hd].
@@ -444,15 +448,16 @@ extern "C" int fi_paged_prefill_tc(const void* q, long q_stride, const void* k_c
                                    int dtype, int* status, void* stream) {
   if (B <= 0 || max_q_len <= 0 || T_total <= 0) return 0;
   if (nkv <= 0 || nh <= 0 || nh % nkv != 0) return -10;
-  if ((hd != 64 && hd != 128) || block_size % 16 != 0 || (dtype != 0 && dtype != 1)) return -12;
+  if ((hd != 64 && hd != 128) || (dtype != 0 && dtype != 1)) return -12;
+  if (block_size != 16 && block_size != 32 && block_size != 64 && block_size % 128 != 0) return -12;
   if ((reinterpret_cast<uintptr_t>(q) & 15) != 0 || (q_stride * 2) % 16 != 0 ||
       (reinterpret_cast<uintptr_t>(out) & 15) != 0)
     return -12;
   CUtensorMap qm, km, vm;
   const uint64_t kv_rows = static_cast<uint64_t>(num_blocks) * nkv * block_size;
   if (fi::make_tmap_2d_16bit_sw128(&qm, q, T_total, static_cast<uint64_t>(nh) * hd, q_stride, kTile) != 0 ||
-      fi::make_tmap_2d_16bit_sw128(&km, k_cache, kv_rows, hd, hd, 16) != 0 ||
-      fi::make_tmap_2d_16bit_sw128(&vm, v_cache, kv_rows, hd, hd, 16) != 0)
+      fi::make_tmap_2d_16bit_sw128(&km, k_cache, kv_rows, hd, hd, block_size < kTile ? block_size : kTile) != 0 ||
+      fi::make_tmap_2d_16bit_sw128(&vm, v_cache, kv_rows, hd, hd, block_size < kTile ? block_size : kTile) != 0)
     return -12;
   TcParams p = {};
   p.out = out; p.block_tables = block_tables; p.seq_lens = seq_lens; p.cu_q = cu_q; p.status = status;

@@ -516,7 +516,7 @@ def paged_attention_prefill(q, k_cache, v_cache, block_tables, seq_lens, cu_q, m
         _lib.check(rc, "fi_paged_prefill_rowscaled")
         _count()
         return out
-    if (_PREFILL_TC != "off" and hd in (64, 128) and k_cache.dtype == q.dtype and k_cache.shape[2] % 16 == 0
+    if (_PREFILL_TC != "off" and hd in (64, 128) and k_cache.dtype == q.dtype and (k_cache.shape[2] in (16, 32, 64) or k_cache.shape[2] % 128 == 0)
             and k_cache.is_contiguous() and v_cache.is_contiguous()
             and (_PREFILL_TC == "on" or int(max_q_len) >= _PREFILL_TC_MIN_Q)):
         rc = _lib.kernels().fi_paged_prefill_tc(

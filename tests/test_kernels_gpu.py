@@ -229,16 +229,16 @@ def test_paged_prefill(nh, nkv, hd, fp8, window, softcap):
 
 
 @pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 64), (4, 2, 128), (2, 2, 64)])
-@pytest.mark.parametrize("window,softcap,dtype", [(0, 0.0, torch.bfloat16), (300, 0.0, torch.bfloat16),
-                                                  (0, 30.0, torch.float16), (128, 20.0, torch.bfloat16)])
-def test_paged_prefill_tensor_core(nh, nkv, hd, window, softcap, dtype):
+@pytest.mark.parametrize("window,softcap,dtype,bs", [(0, 0.0, torch.bfloat16, 16), (300, 0.0, torch.bfloat16, 32),
+                                                     (0, 30.0, torch.float16, 64), (128, 20.0, torch.bfloat16, 128)])
+def test_paged_prefill_tensor_core(nh, nkv, hd, window, softcap, dtype, bs):
     """The tcgen05 prefill kernel against the fp32 oracle, and against the mma.sync kernel's own result:
     several 128-row query tiles and 128-key tiles per sequence, chunks that continue a cached prefix,
     ragged lengths on both axes, sliding window and soft cap."""
     import litevllm_b200.ops as O
     torch.manual_seed(16)
     cases = [(700, 700), (1, 1), (130, 1500), (128, 128), (257, 900), (5, 1000), (384, 385)]
-    B, bs = len(cases), 16
+    B = len(cases)
     lens = [c[1] for c in cases]
     kc, vc, bt = _fill_paged(B, lens, nkv, hd, bs, False, dtype)
     T = sum(c[0] for c in cases)
