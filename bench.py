@@ -46,8 +46,11 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--comm-backend", default="fused", choices=["fused", "nccl"])
-    ap.add_argument("--parallel", default="tp", choices=["tp", "ep"],
-                    help="how N GPUs are used: tensor parallel (dense models) or expert parallel (MoE models)")
+    ap.add_argument("--parallel", default="auto", choices=["auto", "dp", "tp", "ep"],
+                    help="how N GPUs are used: dp = N whole-engine replicas with the batch sharded over them, tp = "
+                         "tensor parallel with the fused collectives, ep = expert parallel (MoE models); auto = dp "
+                         "for the headline model when N divides the batch (a 1.1B model at batch 32 is bound by "
+                         "per-kernel latency, so replicas beat sharding), else tp")
     ap.add_argument("--profile-json", default=None, help="write per-phase timings here")
     ap.add_argument("--ctx-points", type=int, nargs="*", default=[1536, 2040],
                     help="contexts at which the K decode steps are timed again (headline model only)")
@@ -134,7 +137,7 @@ def _token_hash(rows) -> str:
 
 
 def _build_llm(args, world: int, local_rank: int, tp: int, ep: int, max_len: int, model: str | None = None,
-               batch: int | None = None, prompt_len: int | None = None, extra_cfg: dict | None = None):
+               batch: int | None = None, prompt_len: int | None = None, extra_cfg: dict | None = None, dp: int = 1):
     from litevllm_b200 import LLM
     B = batch or args.batch
     P = prompt_len or args.prompt_len
@@ -146,7 +149,7 @@ def _build_llm(args, world: int, local_rank: int, tp: int, ep: int, max_len: int
         cfg.update(extra_cfg)
     return LLM(f"synthetic:{model or args.model}", dtype="bfloat16", max_num_seqs=B, max_model_len=max_len,
                max_num_batched_tokens=max(8192, B * P), tensor_parallel_size=tp, expert_parallel_size=ep,
-               comm_backend=args.comm_backend, fastinference_config=cfg, device=f"cuda:{local_rank}")
+               data_parallel_size=dp, comm_backend=args.comm_backend, fastinference_config=cfg, device=f"cuda:{local_rank}")
 
 
 def _greedy_tokens(eng, prompts, n_new: int, tag: str, first_logits: dict | None = None):
@@ -251,7 +254,15 @@ def run_ours(args) -> dict:
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     B, P, K, W = args.batch, args.prompt_len, args.steps, args.warmup
-    slack = (B + 7) // 8 + 2          # decode steps early finishers of the prefill run ahead
+    mode = args.parallel
+    if mode == "auto":
+        mode = "dp" if (world > 1 and args.model == "tinyllama-1.1b" and B % world == 0) else "tp"
+    if mode == "dp" and B % world != 0:
+        raise SystemExit(f"--parallel dp shards the batch: {B} requests do not divide over {world} replicas")
+    # requests this rank serves itself: all of them, or its share when the ranks are replicas
+    mine = list(range(rank, B, world)) if mode == "dp" else list(range(B))
+    Bl = len(mine)
+    slack = (Bl + 7) // 8 + 2         # decode steps early finishers of the prefill run ahead
     ctx_points = [c for c in args.ctx_points if c > P + 8] if args.model == "tinyllama-1.1b" else []
     max_len = max([P + 1 + W + K + slack + 16] + [c + W + K + slack + 8 for c in ctx_points])
     max_len = (max_len + 15) // 16 * 16
@@ -283,14 +294,14 @@ def run_ours(args) -> dict:
     if args.profile_json:
         from litevllm_b200.utils.profiling import PROFILER
         PROFILER.configure(True, nvtx=True)      # event pairs are resolved after the timed regions
-    tp = world if args.parallel == "tp" else 1
-    ep = world if args.parallel == "ep" else 1
-    llm = _build_llm(args, world, local_rank, tp, ep, max_len)
+    tp = world if mode == "tp" else 1
+    ep = world if mode == "ep" else 1
+    llm = _build_llm(args, world, local_rank, tp, ep, max_len, batch=Bl, dp=world if mode == "dp" else 1)
     eng = llm.engine
     vocab = eng.arch.vocab_size
     # prompts live in pinned host memory; the engine's batch builder copies them to the device
     prompt_ids = torch.randint(0, vocab, (B, P), generator=g, dtype=torch.int64).pin_memory()
-    prompts = [row.tolist() for row in prompt_ids]
+    prompts = [prompt_ids[i].tolist() for i in mine]
     sp = SamplingParams(temperature=0.0, max_tokens=1 + W + K + slack, ignore_eos=True)
 
     def barrier():
@@ -315,15 +326,17 @@ def run_ours(args) -> dict:
     tokens_match = None
     tokens_check = None
     if tp1_tokens is not None and rank == 0:
+        tp1_tokens = [tp1_tokens[i] for i in mine]
+        tp1_logits = {k: tp1_logits[i] for k, i in enumerate(mine) if i in tp1_logits}
         # 16 greedy tokens per prompt, strictly; and, because random-init logits are nearly flat and the
         # parallel run sums in another order, the first token again with near-ties set aside: a prompt
         # counts as a near-tie when the one-GPU run's top-2 margin is below four times the largest
         # logit difference seen between the two runs
         tokens_match = _token_hash(tp1_tokens) == _token_hash(first_tokens)
         first_equal = [int(a[0] == b[0]) for a, b in zip(tp1_tokens, first_tokens)]
-        tokens_check = {"prompts": B, "tokens_per_prompt": N_CHECK, "first_token_equal": sum(first_equal),
+        tokens_check = {"prompts": Bl, "tokens_per_prompt": N_CHECK, "first_token_equal": sum(first_equal),
                         "hash_tp1": _token_hash(tp1_tokens), "hash_this_run": _token_hash(first_tokens)}
-        common = [i for i in range(B) if i in tp1_logits and i in run_logits
+        common = [i for i in range(Bl) if i in tp1_logits and i in run_logits
                   and tp1_logits[i].shape == run_logits[i].shape]
         if common:
             diff = max(float((tp1_logits[i] - run_logits[i]).abs().max()) for i in common)
@@ -340,10 +353,10 @@ def run_ours(args) -> dict:
     # ------------------------------------------------------------------ e2e: public API, H2D + D2H each step
     def submit_and_first_tokens(tag: str, params) -> list[float]:
         t_submit = time.perf_counter()
-        for i in range(B):
+        for i in range(Bl):
             eng.add_request(f"{tag}-{i}", prompts[i], params)
         seen = {}
-        while len(seen) < B:
+        while len(seen) < Bl:
             outs = eng.step()
             now = time.perf_counter()
             for o in outs:
@@ -377,27 +390,28 @@ def run_ours(args) -> dict:
     barrier()
     e2e_ms = max_over_ranks(ev0.elapsed_time(ev1))
     e2e_window = (wall0, wall1)
-    assert n_tokens == B * K, f"expected {B * K} tokens in the timed region, got {n_tokens}"
+    assert n_tokens == Bl * K, f"expected {Bl * K} tokens in the timed region, got {n_tokens}"
     while eng.has_unfinished_requests():
         eng.step()
     ttft_runs = [max_over_ranks(statistics.median(t) * 1e3) for t in (ttft_a, ttft_b)]
     ttft_p50_ms = max_over_ranks(statistics.median(ttft_a + ttft_b) * 1e3)
-    bucket = eng.builder.bucket_for(B)
-    h2d_per_step = 4 * bucket * 4                       # 4 x int32 metadata rows (positions, slots, lengths, slot ids); token ids stay on the device
-    d2h_per_step = B * 8                                 # sampled token ids (int64)
+    bucket = eng.builder.bucket_for(Bl)
+    copies = world if mode == "dp" else 1               # every replica copies its own metadata and token ids
+    h2d_per_step = 4 * bucket * 4 * copies              # 4 x int32 metadata rows (positions, slots, lengths, slot ids); token ids stay on the device
+    d2h_per_step = Bl * 8 * copies                       # sampled token ids (int64)
 
     # ------------------------------------------------------------------ device-only: decode steps back to back
     # Same engine, same captured graph: the decode pipeline is driven directly, sampled tokens are fed
     # back on the device and nothing is read back or post-processed on the host inside the timed region.
     sp_long = SamplingParams(temperature=0.0, max_tokens=max_len - P - 2, ignore_eos=True)
-    for i in range(B):
+    for i in range(Bl):
         eng.add_request(f"dev-{i}", prompts[i], sp_long)
-    while any(eng.scheduler.requests[f"dev-{i}"].is_prefill for i in range(B)):
+    while any(eng.scheduler.requests[f"dev-{i}"].is_prefill for i in range(Bl)):
         eng.step()
     for _ in range(W):
         eng.step()
     pipe = eng.backend.pipeline
-    assert pipe is not None and pipe.active and len(pipe.reqs) == B, "decode pipeline not active"
+    assert pipe is not None and pipe.active and len(pipe.reqs) == Bl, "decode pipeline not active"
     while pipe.inflight:           # settle the step launched by the warm-up
         pipe.collect_oldest()
 
@@ -461,7 +475,7 @@ def run_ours(args) -> dict:
     while pipe.inflight:
         pipe.collect_oldest()
     pipe.stop()
-    for i in range(B):
+    for i in range(Bl):
         eng.abort_request(f"dev-{i}")
     ops.check_status(dev)
     per_graph = getattr(eng.decode_executor, "launches_per_graph", {}).get(bucket, 0)
@@ -470,7 +484,9 @@ def run_ours(args) -> dict:
     from litevllm_b200.parallel import state as pstate
     pst = pstate.get_state()
     effective_backend = "none (one GPU)" if world == 1 else pst.comm_backend
-    if world > 1 and pst.comm_backend == "fused":
+    if mode == "dp" and world > 1:
+        effective_backend = "none (replicas: no collective inside a step)"
+    elif world > 1 and pst.comm_backend == "fused":
         from litevllm_b200.parallel import fused_ops
         effective_backend = "fused (" + ("two-hop" if fused_ops.decode_allreduce_format(world, torch.bfloat16) == 3
                                         else "one-hop") + " all-reduce in the GEMM epilogue" + \
@@ -486,7 +502,9 @@ def run_ours(args) -> dict:
         "vs_baseline": round(value / PUBLISHED_TPS.get(args.model, BASELINE_TPS), 2), "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
         "config": {"model": f"{args.model} (random init N(0,0.02))", "global_batch": B, "seq_len": P + 1 + W + K,
-                   "prompt_len": P, "parallelism": f"{args.parallel}{world}",
+                   "prompt_len": P,
+                   "parallelism": (f"dp{world} ({world} replicas of the whole engine, {Bl} requests each)"
+                                   if mode == "dp" and world > 1 else f"{mode}{world}"),
                    "comm_backend_requested": args.comm_backend, "comm_backend": effective_backend,
                    "self_test": pst.self_test,
                    "l2_policy": "inputs larger than L2 (%.1f GB of weights + KV streamed every step)"
@@ -502,9 +520,9 @@ def run_ours(args) -> dict:
                 "wall_ms_per_step": round(e2e_wall_ms / K, 4), "wall_value": round(B * K / (e2e_wall_ms / 1e3), 1),
                 "h2d_bytes_per_step": h2d_per_step, "d2h_bytes_per_step": d2h_per_step,
                 "api": "LiteEngine.add_request + LiteEngine.step (the loop inside LLM.generate)"},
-        "gpu_launches": int(dev_replays * per_graph + dev_eager),
-        "gpu_launches_detail": {"graph_replays": dev_replays, "kernels_per_graph": per_graph,
-                                "eager_native_launches": dev_eager},
+        "gpu_launches": int(dev_replays * per_graph + dev_eager) * world,
+        "gpu_launches_detail": {"ranks": world, "graph_replays_per_rank": dev_replays, "kernels_per_graph": per_graph,
+                                "eager_native_launches_per_rank": dev_eager},
         "clocks": clocks, "clocks_e2e": sampler.summary(*e2e_window),
         "diag": {"graph_replay_only_ms_per_step": round(graph_only_ms, 4) if graph_only_ms else None,
                  "pdl": os.environ.get("FI_USE_PDL", "1") != "0"},

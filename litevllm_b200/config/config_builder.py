@@ -26,7 +26,7 @@ _KNOWN_KW = {
     "fastinference_config", "fastinference_config_path", "trust_remote_code", "revision",
     "max_model_len", "gpu_memory_utilization", "max_num_seqs", "concurrent_reqs",
     "max_num_batched_tokens", "tokenizer", "dtype", "cache_block_size", "policy_mode",
-    "tensor_parallel_size", "expert_parallel_size", "comm_backend", "seed", "hf_overrides",
+    "tensor_parallel_size", "expert_parallel_size", "data_parallel_size", "comm_backend", "seed", "hf_overrides",
     "load_format", "device", "quantization", "enforce_eager",
 }
 
@@ -97,6 +97,7 @@ def build_vllm_config(model: str, **kwargs: Any) -> VllmConfig:
     parallel = ParallelConfig.from_env(
         tp=int(kwargs.get("tensor_parallel_size") or fi.parallel.tensor_parallel_size),
         ep=int(kwargs.get("expert_parallel_size") or fi.parallel.expert_parallel_size),
+        dp=int(kwargs.get("data_parallel_size") or 1),
         comm_backend=str(kwargs.get("comm_backend") or fi.parallel.comm_backend))
 
     cfg = VllmConfig(

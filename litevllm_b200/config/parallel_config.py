@@ -3,7 +3,8 @@
 The reference is single-GPU (vllm/engine/lite_engine.py:146 pins ``cuda:0``); tensor and expert
 parallelism are additions of this engine.  One process drives one GPU; ``world_size`` is
 ``tensor_parallel_size`` for dense models and ``max(tp, ep)`` for MoE models (experts are sharded
-over the same ranks that hold the attention shards).
+over the same ranks that hold the attention shards).  ``data_parallel_size`` > 1 instead runs that many
+whole single-GPU engines and shards the requests (parallel/data_parallel.py).
 """
 from __future__ import annotations
 
@@ -15,6 +16,7 @@ from dataclasses import dataclass
 class ParallelConfig:
     tensor_parallel_size: int = 1
     expert_parallel_size: int = 1
+    data_parallel_size: int = 1   # whole-engine replicas; requests are sharded over them
     comm_backend: str = "fused"   # "fused": in-kernel NVLink collectives; "nccl": library collectives
     rank: int = 0
     local_rank: int = 0
@@ -30,8 +32,11 @@ class ParallelConfig:
         return self.world_size > 1
 
     @classmethod
-    def from_env(cls, tp: int = 1, ep: int = 1, comm_backend: str = "fused") -> "ParallelConfig":
-        return cls(tensor_parallel_size=tp, expert_parallel_size=ep, comm_backend=comm_backend,
+    def from_env(cls, tp: int = 1, ep: int = 1, comm_backend: str = "fused", dp: int = 1) -> "ParallelConfig":
+        if dp > 1 and max(tp, ep) > 1:
+            raise NotImplementedError("data_parallel_size > 1 runs replicas of single-GPU engines; "
+                                      "replicas of tensor/expert-parallel groups are separate torchrun jobs")
+        return cls(tensor_parallel_size=tp, expert_parallel_size=ep, data_parallel_size=dp, comm_backend=comm_backend,
                    rank=int(os.environ.get("RANK", "0")),
                    local_rank=int(os.environ.get("LOCAL_RANK", "0")),
                    master_addr=os.environ.get("MASTER_ADDR", "127.0.0.1"),

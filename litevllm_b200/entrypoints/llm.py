@@ -26,6 +26,14 @@ class LLM:
         tokenizer = kwargs.pop("tokenizer_object", None)
         self.vllm_config = build_vllm_config(model, **kwargs)
         self._parallel = None
+        self._dp = None
+        pc = self.vllm_config.parallel_config
+        if pc.data_parallel_size > 1:
+            # replicas: this process owns one whole engine on its own GPU and a share of every call's prompts
+            from ..parallel.data_parallel import DataParallelGroup
+            self._dp = DataParallelGroup(pc.data_parallel_size)
+            if torch.cuda.is_available() and self.vllm_config.device in ("auto", "cuda"):
+                self.vllm_config.device = f"cuda:{self._dp.local_rank}"
         if self.vllm_config.parallel_config.is_distributed:
             from ..parallel.launcher import init_distributed_engine
             self._parallel = init_distributed_engine(self.vllm_config)
@@ -58,6 +66,15 @@ class LLM:
             params = sampling_params
         else:
             params = [sampling_params or SamplingParams()] * len(prompts)
+        if self._dp is not None:
+            # every replica is called with the same arguments and serves prompts rank, rank + N, ...
+            n_all = len(prompts)
+            mine = self._dp.my_indices(n_all)
+            local = self._generate_local([prompts[i] for i in mine], [params[i] for i in mine], lora_request)
+            return self.output_processor.process_outputs(self._dp.gather_in_order(local, n_all))
+        return self.output_processor.process_outputs(self._generate_local(prompts, params, lora_request))
+
+    def _generate_local(self, prompts: list, params: list, lora_request=None) -> list[RequestOutput]:
         results: dict[str, RequestOutput] = {}
         order: list[str] = []
         group = self.engine.max_active_requests
@@ -83,7 +100,7 @@ class LLM:
                     raise RuntimeError("engine went idle with unfinished requests")
             for rid in ids:
                 self.engine.scheduler.pop_sync_outputs(rid)
-        return self.output_processor.process_outputs([results[r] for r in order])
+        return [results[r] for r in order]
 
     def stats(self) -> dict:
         return self.engine.stats()
@@ -101,3 +118,5 @@ class LLM:
         self.engine.shutdown()
         if self._parallel is not None:
             self._parallel.shutdown()
+        if self._dp is not None:
+            self._dp.shutdown()

@@ -33,6 +33,16 @@ class CompletionOutput:
     def finished(self) -> bool:
         return self.finish_reason is not None
 
+    # An output that leaves its process (data-parallel replicas hand theirs to the caller's rank) carries
+    # its text, not the tokenizer closure that would have produced it.
+    def __getstate__(self):
+        return {"index": self.index, "token_ids": self.token_ids, "cumulative_logprob": self.cumulative_logprob,
+                "finish_reason": self.finish_reason, "_text": self.text, "_decode": None}
+
+    def __setstate__(self, state):
+        for k, v in state.items():
+            setattr(self, k, v)
+
     def __repr__(self) -> str:
         return (f"CompletionOutput(index={self.index}, n_tokens={len(self.token_ids)}, "
                 f"finish_reason={self.finish_reason!r})")
