@@ -101,8 +101,12 @@ def main():
         out = torch.empty(T, N, device=dev, dtype=torch.bfloat16)
         layer = Layer()
         layer.weight, layer.out_features = w, N
-        xfer16 = 1 if T > 256 else 2       # decode shapes use the inline-epoch low-latency format
-        elem = 2 if T > 256 else 8
+        # decode shapes use an inline-epoch low-latency format: one hop (every rank sends its partial to
+        # every peer) or, from four ranks on, two hops (partials to the owner of a column chunk, 16-bit
+        # sums broadcast back); both are timed, "fused_us" is the one the engine picks for this world size
+        decode = T <= 256
+        xfer16 = 1 if not decode else fused_ops.decode_allreduce_format(world, torch.bfloat16)
+        elem = 2 if not decode else 8
         iters = args.iters if T <= 256 else 4
         flops = 2.0 * T * N * K
         t_compute = flops / (tflops * 1e12) * 1e6
@@ -121,12 +125,21 @@ def main():
 
         t_local = timed(local_only, iters)
         t_f, t_n = timed(fused_ar, iters), timed(nccl_ar, iters)
-        link = (world - 1) * T * N * elem / (NVLINK_GBS * 1e9) * 1e6
+        per_format = {}
+        if decode:
+            for name, fmt in (("one_hop_us", 2), ("two_hop_us", 3)):
+                per_format[name] = round(timed(lambda: fused_ops._fused_gemm_allreduce(layer, x, res, out, st.symm, fmt),
+                                               iters), 2)
+        if decode and xfer16 == 3:
+            # per GPU: (world - 1) / world of the tile out as fp32 words with their epochs, the same share back as 16-bit sums
+            link = (world - 1) / world * T * N * (8 + 4) / (NVLINK_GBS * 1e9) * 1e6
+        else:
+            link = (world - 1) * T * N * elem / (NVLINK_GBS * 1e9) * 1e6
         roof = max(t_compute, link, t_hbm)
         rows.append({"op": "gemm+all_reduce", "shape": label, "T": T, "N": N, "K_per_rank": K, "fused_us": round(t_f, 2),
                      "nccl_us": round(t_n, 2), "local_gemm_us": round(t_local, 2), "roofline_us": round(roof, 2),
                      "bound": "compute" if roof == t_compute else ("nvlink" if roof == link else "hbm"),
-                     "frac_of_roofline": round(roof / t_f, 3), "speedup_vs_nccl": round(t_n / t_f, 2)})
+                     "frac_of_roofline": round(roof / t_f, 3), "speedup_vs_nccl": round(t_n / t_f, 2), **per_format})
         if T >= world * 128:
             rpr = T // world
             res_s = torch.zeros(rpr, N, device=dev, dtype=torch.bfloat16)

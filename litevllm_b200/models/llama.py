@@ -214,7 +214,9 @@ class LlamaForCausalLM(nn.Module):
         if batch.is_decode or not h.is_cuda or batch.lora_mapping is not None:
             return False
         st = pstate.get_state()
-        if st.tp_size <= 1 or st.comm_backend != "fused" or st.symm is None or not st.sequence_parallel_ok:
+        from ..parallel.fused_ops import fused_prefill_ok
+        if (st.tp_size <= 1 or st.comm_backend != "fused" or st.symm is None or not st.sequence_parallel_ok
+                or not fused_prefill_ok(st.tp_size)):
             return False
         if h.shape[0] < self.sp_min_tokens:
             return False
