@@ -222,7 +222,12 @@ class LlamaForCausalLM(nn.Module):
             return False
         l0 = self.layers[0]
         lin = (l0.self_attn.qkv_proj, l0.self_attn.o_proj, l0.mlp.gate_up_proj, l0.mlp.down_proj)
-        if any(m.quant_method is not None or m.bias is not None for m in lin):
+        if any(m.bias is not None for m in lin):
+            return False
+        # 16-bit layers or int4 layers (the int4 GEMM carries the same all-gather producer and
+        # reduce-scatter epilogue); other quantised formats keep the replicated-activation prefill
+        from ..layers.quantization.awq import Int4LinearMethod
+        if any(m.quant_method is not None and not isinstance(m.quant_method, Int4LinearMethod) for m in lin):
             return False
         w = st.tp_size
         rpr = (h.shape[0] + w * 128 - 1) // (w * 128) * 128
@@ -255,7 +260,7 @@ class LlamaForCausalLM(nn.Module):
         for i, layer in enumerate(self.layers):
             at, mlp = layer.self_attn, layer.mlp
             x = layer.input_layernorm(h)
-            qkv = fused_ops.allgather_gemm(x, at.qkv_proj.weight, Tpad, rpr)[:T]
+            qkv = fused_ops.allgather_gemm(x, at.qkv_proj, Tpad, rpr)[:T]
             k_cache, v_cache = kv_caches[i]
             ops.rope_and_cache(qkv, batch.positions, cs, batch.slot_mapping, k_cache, v_cache, at.nh, at.nkv, at.hd,
                                at.rot_dim, q_norm_w=at.q_norm.weight if at.qk_norm else None,
@@ -265,10 +270,10 @@ class LlamaForCausalLM(nn.Module):
             ops.paged_attention_prefill(qkv, k_cache, v_cache, batch.block_tables, batch.seq_lens, batch.cu_q,
                                         batch.max_q_len, at.nh, at.nkv, at.hd, at.sm_scale, at.window, 0.0,
                                         cfg.k_scale, cfg.v_scale, out=attn[:T])
-            fused_ops.gemm_reduce_scatter(attn, at.o_proj.weight, h, rpr, out_shard=h)
+            fused_ops.gemm_reduce_scatter(attn, at.o_proj, h, rpr, out_shard=h)
             x = layer.post_attention_layernorm(h)
-            a = fused_ops.allgather_gemm(x, mlp.gate_up_proj.weight, Tpad, rpr, gated_act=mlp.gate_up_proj.gated_act)
-            fused_ops.gemm_reduce_scatter(a, mlp.down_proj.weight, h, rpr, out_shard=h)
+            a = fused_ops.allgather_gemm(x, mlp.gate_up_proj, Tpad, rpr, gated_act=mlp.gate_up_proj.gated_act)
+            fused_ops.gemm_reduce_scatter(a, mlp.down_proj, h, rpr, out_shard=h)
         full = pstate.all_gather_rows(h)[:T]
         return self.compute_logits(full, batch)
 

@@ -104,18 +104,45 @@ def _fused_gemm_allreduce(layer, x, residual, out, heap, xfer16: bool | int, pha
 
 
 # --------------------------------------------------------------------------- sequence-parallel forms
-def gemm_reduce_scatter(x: torch.Tensor, w: torch.Tensor, residual_shard: torch.Tensor | None,
+def _int4_of(w):
+    """``w`` is a weight matrix or a linear layer; returns the layer's runtime int4 weight or None."""
+    if isinstance(w, torch.Tensor):
+        return None
+    if w.quant_method is None:
+        return None
+    if w.int4 is None:
+        w.quant_method.process_weights_after_loading(w)
+    return w.int4
+
+
+def _dense_of(w) -> torch.Tensor:
+    return w if isinstance(w, torch.Tensor) else w.weight
+
+
+def gemm_reduce_scatter(x: torch.Tensor, w, residual_shard: torch.Tensor | None,
                         rows_per_rank: int, out_shard: torch.Tensor | None = None,
                         xfer_16bit: bool = True, heap=None, phases: int = 0) -> torch.Tensor:
     """``(x @ w.T)`` summed over ranks, each rank keeping token rows
-    ``[rank*rows_per_rank, (rank+1)*rows_per_rank)`` (+ its residual shard).  One fused kernel."""
+    ``[rank*rows_per_rank, (rank+1)*rows_per_rank)`` (+ its residual shard).  One fused kernel.
+    ``w`` is a 16-bit weight matrix or a linear layer (16-bit or int4: the int4 GEMM has the same
+    collective epilogue)."""
     if heap is None:
         heap = pstate.get_state().symm
     T, K = x.shape
-    N = w.shape[0]
+    q = _int4_of(w)
+    N = q.N if q is not None else _dense_of(w).shape[0]
     if out_shard is None:
         out_shard = torch.empty(rows_per_rank, N, dtype=x.dtype, device=x.device)
     comm = heap.comm_desc(mode=2, T=T, N=N, xfer_16bit=xfer_16bit, rows_per_rank=rows_per_rank, phases=phases)
+    if q is not None:
+        rc = _lib.kernels().fi_awq_gemm_comm(
+            ops._p(x), ops._p(q.qw), ops._p(q.scales_t), ops._p(q.zeros_t), ops._p(out_shard), None,
+            ops._p(residual_shard), T, N, K, q.group, x.stride(0), out_shard.stride(0), 0, 0, 0, ops._DT[x.dtype], 0, 0,
+            ops._p(ops.status_word(x.device)), ops._stream(), ctypes.byref(comm))
+        _lib.check(rc, "fi_awq_gemm_comm(reduce_scatter)")
+        ops._count()
+        return out_shard
+    w = _dense_of(w)
     rc = _lib.kernels().fi_dense_gemm_comm(
         ops._p(x), ops._p(w), ops._p(out_shard), None, ops._p(residual_shard), T, N, K, x.stride(0), w.stride(0),
         out_shard.stride(0), 0, 0, 0, ops._DT[x.dtype], 0, 0, ops._p(ops.status_word(x.device)), ops._stream(),
@@ -125,7 +152,7 @@ def gemm_reduce_scatter(x: torch.Tensor, w: torch.Tensor, residual_shard: torch.
     return out_shard
 
 
-def allgather_gemm(x_shard: torch.Tensor, w: torch.Tensor, T_total: int, rows_per_rank: int,
+def allgather_gemm(x_shard: torch.Tensor, w, T_total: int, rows_per_rank: int,
                    out: torch.Tensor | None = None, gated_act: str | None = None,
                    staged: bool | None = None) -> torch.Tensor:
     """``concat_over_ranks(x_shard) @ w.T`` in one kernel: every rank parks its shard in the
@@ -135,7 +162,8 @@ def allgather_gemm(x_shard: torch.Tensor, w: torch.Tensor, T_total: int, rows_pe
     (``staged=True``, the default when the token count is ``world * rows_per_rank``).  With
     ``staged=False`` every CTA's TMA producer reads its token tiles straight from the owner's
     memory instead (plain, non-multicast TMA loads over NVLink): simpler, but a remote tile is
-    re-read once per weight tile."""
+    re-read once per weight tile.  ``w`` is a 16-bit weight matrix or a linear layer; an int4 layer
+    runs the int4 GEMM, whose producer pulls the token tiles from the owners (the unstaged form)."""
     st = pstate.get_state()
     heap = st.symm
     K = x_shard.shape[1]
@@ -143,10 +171,23 @@ def allgather_gemm(x_shard: torch.Tensor, w: torch.Tensor, T_total: int, rows_pe
     _parity[0] += 1
     buf = heap.xbuf(parity, rows_per_rank, K, x_shard.dtype)
     buf[: x_shard.shape[0]].copy_(x_shard)
-    inter = w.shape[0] // 2 if gated_act else 0
-    N = inter if gated_act else w.shape[0]
+    q = _int4_of(w)
+    rows_w = q.N if q is not None else _dense_of(w).shape[0]
+    inter = rows_w // 2 if gated_act else 0
+    N = inter if gated_act else rows_w
     if out is None:
         out = torch.empty(T_total, N, dtype=x_shard.dtype, device=x_shard.device)
+    if q is not None:
+        comm = heap.comm_desc(mode=0, T=T_total, N=N, xfer_16bit=False, ag_world=st.world_size,
+                              ag_rows_per_rank=rows_per_rank, x_parity=parity, staged=False)
+        rc = _lib.kernels().fi_awq_gemm_comm(
+            ops._p(buf), ops._p(q.qw), ops._p(q.scales_t), ops._p(q.zeros_t), ops._p(out), None, None, T_total, N, K,
+            q.group, buf.stride(0), out.stride(0), ops._ACT[gated_act] if gated_act else 0, inter, 0,
+            ops._DT[x_shard.dtype], 0, 0, ops._p(ops.status_word(x_shard.device)), ops._stream(), ctypes.byref(comm))
+        _lib.check(rc, "fi_awq_gemm_comm(all_gather)")
+        ops._count()
+        return out
+    w = _dense_of(w)
     if staged is None:
         staged = T_total == st.world_size * rows_per_rank
     comm = heap.comm_desc(mode=0, T=T_total, N=N, xfer_16bit=False, ag_world=st.world_size,

@@ -226,6 +226,22 @@ def _worker(rank: int, world: int, port: int, fn, args):
     fn(rank, world, *args)
 
 
+def _usable_port(port: int) -> int:
+    """``port`` if it can be bound on the loopback interface right now, else a free one."""
+    import socket
+    for candidate in (port, 0):
+        with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+            s.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+            try:
+                s.bind(("127.0.0.1", candidate))
+                return s.getsockname()[1]
+            except OSError:
+                continue
+    return port
+
+
 def spawn(fn, world: int, args: tuple = (), port: int = 29531, join: bool = True):
-    """Run ``fn(rank, world, *args)`` in ``world`` local processes."""
+    """Run ``fn(rank, world, *args)`` in ``world`` local processes (rendezvous on 127.0.0.1; a busy
+    ``port`` is replaced by a free one)."""
+    port = _usable_port(port)
     return mp.spawn(_worker, args=(world, port, fn, args), nprocs=world, join=join)

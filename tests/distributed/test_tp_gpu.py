@@ -129,17 +129,22 @@ def test_fused_collective_gemms_match_nccl():
     assert reps[0]["epoch"] == reps[1]["epoch"] > 0
 
 
-def _e2e_worker(rank, world, out_dir, backend):
+def _e2e_worker(rank, world, out_dir, backend, preset="tiny-llama-test"):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     os.environ["FI_SP_MIN_TOKENS"] = "64"      # the 142-token prefill batch runs the sequence-parallel path
-    from litevllm_b200 import LLM, SamplingParams
+    from litevllm_b200 import LLM, SamplingParams, ops
     g = torch.Generator().manual_seed(5)
     prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (9, 40, 23, 70)]
-    llm = LLM("synthetic:tiny-llama-test", dtype="bfloat16", max_num_seqs=4, max_model_len=128,
+    llm = LLM(f"synthetic:{preset}", dtype="bfloat16", max_num_seqs=4, max_model_len=128,
               tensor_parallel_size=world, comm_backend=backend)
+    sp_calls = []
+    model = llm.engine.model
+    orig = model._forward_sequence_parallel
+    model._forward_sequence_parallel = lambda *a, **k: (sp_calls.append(1), orig(*a, **k))[1]
     outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    ops.check_status(torch.device("cuda", rank))
     with open(os.path.join(out_dir, f"{backend}{rank}.json"), "w") as f:
-        json.dump([o.outputs[0].token_ids for o in outs], f)
+        json.dump({"tokens": [o.outputs[0].token_ids for o in outs], "sp_calls": len(sp_calls)}, f)
     llm.shutdown()
 
 
@@ -150,13 +155,31 @@ def test_tp2_generation(backend):
     prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (9, 40, 23, 70)]
     with tempfile.TemporaryDirectory() as d:
         spawn(_e2e_worker, 2, args=(d, backend), port=29552 if backend == "nccl" else 29553)
-        got = [json.load(open(os.path.join(d, f"{backend}{r}.json"))) for r in range(2)]
+        got = [json.load(open(os.path.join(d, f"{backend}{r}.json")))["tokens"] for r in range(2)]
     assert got[0] == got[1], "ranks diverged"
     ref = LLM("synthetic:tiny-llama-test", dtype="bfloat16", device="cuda:0", max_num_seqs=4, max_model_len=128)
     want = [o.outputs[0].token_ids for o in
             ref.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))]
     first_ok = sum(int(a[0] == b[0]) for a, b in zip(got[0], want))
     assert first_ok >= 3, (got[0], want)
+
+
+def test_tp2_int4_prefill_runs_sequence_parallel():
+    """Int4 (AWQ) layers under tensor parallelism: the prefill must take the sequence-parallel path
+    (all-gather->int4 GEMM, int4 GEMM->reduce-scatter) and produce the tokens of the one-GPU run."""
+    from litevllm_b200 import LLM, SamplingParams
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (9, 40, 23, 70)]
+    with tempfile.TemporaryDirectory() as d:
+        spawn(_e2e_worker, 2, args=(d, "fused", "tiny-llama-awq-test"), port=29556)
+        got = [json.load(open(os.path.join(d, f"fused{r}.json"))) for r in range(2)]
+    assert got[0]["tokens"] == got[1]["tokens"], "ranks diverged"
+    assert got[0]["sp_calls"] >= 1, "the int4 prefill did not take the sequence-parallel path"
+    ref = LLM("synthetic:tiny-llama-awq-test", dtype="bfloat16", device="cuda:0", max_num_seqs=4, max_model_len=128)
+    want = [o.outputs[0].token_ids for o in
+            ref.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))]
+    first_ok = sum(int(a[0] == b[0]) for a, b in zip(got[0]["tokens"], want))
+    assert first_ok >= 3, (got[0]["tokens"], want)
 
 
 def _ep_worker(rank, world, out_dir, preset):
