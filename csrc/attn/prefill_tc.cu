@@ -126,15 +126,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
   uint64_t* k_empty = v_full + STAGES;
   uint64_t* v_empty = k_empty + STAGES;
   uint64_t* s_full = v_empty + STAGES;       // [2]
-  uint64_t* p_full = s_full + 2;
-  uint64_t* pv_full = p_full + 1;
-  uint64_t* pair_bar = pv_full + 1;          // [4]: the two warps of a TMEM quadrant
+  // One barrier per buffer parity for every hand-over: a waiter that is late by a whole tile then still
+  // finds "its" phase (a single barrier would already be one phase further and the parity test would
+  // read as "not yet", for ever).
+  uint64_t* p_full = s_full + 2;             // [2]
+  uint64_t* pv_full = p_full + 2;            // [2]
+  uint64_t* pair_bar = pv_full + 2;          // [4]: the two warps of a TMEM quadrant
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_bar + 4);
   volatile int* aborted = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* half_max = reinterpret_cast<float*>(smem_raw + 512);   // [2 parities][2 halves][128]
   // the denominators meet in the parity buffer that the last tile did not use
   float* half_sum = half_max + (n_tiles & 1) * 2 * 128;        // [2 halves][128]
-  static_assert((1 + 4 * STAGES + 2 + 1 + 1 + 4) * 8 + 8 <= 512, "barrier block");
+  static_assert((1 + 4 * STAGES + 2 + 2 + 2 + 4) * 8 + 8 <= 512, "barrier block");
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -144,9 +147,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
       mbar_init(&k_empty[i], 1);
       mbar_init(&v_empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) mbar_init(&s_full[i], 1);
-    mbar_init(p_full, 256);
-    mbar_init(pv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 256);
+      mbar_init(&pv_full[i], 1);
+    }
     for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 64);
     *aborted = 0;
     mbar_fence_init();
@@ -247,7 +252,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         if (j + 1 < n_tiles) ok = issue_qk(j + 1);
         if (j < 16) mark(p.trace, 128 + j * 4);
         const int st = j % STAGES;
-        ok = ok && mbar_wait(p_full, j & 1);
+        ok = ok && mbar_wait(&p_full[j & 1], (j >> 1) & 1);
         if (j < 16) mark(p.trace, 129 + j * 4);
         ok = ok && mbar_wait(&v_full[st], (j / STAGES) & 1);
         if (!ok) break;
@@ -262,7 +267,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
           umma_f16_a_tmem(tmem_base + kPvCol + (j & 1) * HD, tp, dv, idesc_pv, k != 0 ? 1u : 0u);
         }
         umma_commit(&v_empty[st]);
-        umma_commit(pv_full);
+        umma_commit(&pv_full[j & 1]);
         if (j < 16) mark(p.trace, 131 + j * 4);
       }
       if (!ok) {
@@ -364,11 +369,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
       tmem_st_x32(t_lane + sb * kTile + half * 32, sr);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(&p_full[sb]);
       if (j < 16) mark(tr, j * 8 + 5);
       // fold the previous tile's product while the tensor core works on this one
       if (j > 0) {
-        if (!mbar_wait(pv_full, (j - 1) & 1)) { ok = false; break; }
+        if (!mbar_wait(&pv_full[(j - 1) & 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
         if (j < 16) mark(tr, j * 8 + 6);
         tc_fence_after();
         fold_pv((j - 1) & 1, alpha_prev);
@@ -377,7 +382,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
       if (j < 16) mark(tr, j * 8 + 7);
       alpha_prev = alpha;
     }
-    if (ok) ok = mbar_wait(pv_full, (n_tiles - 1) & 1);
+    if (ok) ok = mbar_wait(&pv_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
     if (ok) {
       tc_fence_after();
       fold_pv((n_tiles - 1) & 1, alpha_prev);

@@ -132,6 +132,7 @@ def test_fused_collective_gemms_match_nccl():
 def _e2e_worker(rank, world, out_dir, backend, preset="tiny-llama-test"):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     os.environ["FI_SP_MIN_TOKENS"] = "64"      # the 142-token prefill batch runs the sequence-parallel path
+    os.environ["FI_SP_INT4"] = "1"             # int4 layers take that path only on request
     from litevllm_b200 import LLM, SamplingParams, ops
     g = torch.Generator().manual_seed(5)
     prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (9, 40, 23, 70)]

@@ -264,6 +264,29 @@ def test_paged_prefill_tensor_core(nh, nkv, hd, window, softcap, dtype, bs):
     _close(outs["on"], outs["off"].float(), 2e-2, 2e-2, "tc prefill vs mma.sync prefill")
 
 
+def test_paged_prefill_tensor_core_repeated():
+    """Many back-to-back launches over long sequences (hundreds of KV tiles per CTA in flight on every SM):
+    no bounded wait may run out and every launch must give the same result."""
+    import litevllm_b200.ops as O
+    torch.manual_seed(17)
+    nh, nkv, hd, bs, B, L = 16, 4, 128, 16, 6, 2048
+    kc, vc, bt = _fill_paged(B, [L] * B, nkv, hd, bs, False)
+    qkv = torch.randn(B * L, (nh + 2 * nkv) * hd, device=DEV).bfloat16()
+    cu = torch.arange(B + 1, dtype=torch.int32, device=DEV) * L
+    sl = torch.full((B,), L, dtype=torch.int32, device=DEV)
+    saved = O._PREFILL_TC
+    O._PREFILL_TC = "on"
+    try:
+        first = ops.paged_attention_prefill(qkv, kc, vc, bt, sl, cu, L, nh, nkv, hd, hd ** -0.5).clone()
+        for _ in range(40):
+            y = ops.paged_attention_prefill(qkv, kc, vc, bt, sl, cu, L, nh, nkv, hd, hd ** -0.5)
+        torch.cuda.synchronize()
+    finally:
+        O._PREFILL_TC = saved
+    ops.check_status(torch.device(DEV, 0))
+    assert torch.equal(y, first)
+
+
 def test_small_ops():
     torch.manual_seed(7)
     table = torch.randn(1000, 256, device=DEV).bfloat16()
