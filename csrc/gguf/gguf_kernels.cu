@@ -416,6 +416,156 @@ __global__ void moe_down_kernel(const T* __restrict__ a, const uint8_t* __restri
   }
 }
 
+// ------------------------------------------------------------------------------ grouped routed experts
+// The routes are sorted by expert (fi_moe_align) and cut into tiles of at most kGrpM routes of one
+// expert.  One CTA column (blockIdx.y) is one tile: the tile's activation rows sit in shared memory as
+// 16-bit values, every weight row of the expert is fetched and decoded ONCE per tile and dotted with all
+// of the tile's rows, so an expert that serves m routes is streamed ceil(m / kGrpM) times instead of m
+// times.  A warp owns kMoeRows weight rows and fetches row r + 1 while it works on row r.
+// Inputs and outputs are in sorted-slot order (slot = position in sorted_route).
+constexpr int kGrpM = 8;
+
+template <int TYPE, typename T>
+__device__ __forceinline__ void row_dot16(const uint8_t* r, int K, const T* xs, int M, int lane, float* acc,
+                                          const Iq2Tables& tab) {
+  for (int v0 = lane * 8; v0 < K; v0 += 32 * 8) {
+    float w[8];
+    decode8<TYPE>(r + (v0 / Blk<TYPE>::kVals) * Blk<TYPE>::kBytes, v0 % Blk<TYPE>::kVals, w, tab);
+#pragma unroll
+    for (int m = 0; m < kGrpM; ++m) {
+      if (m < M) {
+        float a[8];
+        unpack8_16bit<T>(*reinterpret_cast<const uint4*>(xs + static_cast<size_t>(m) * K + v0), a);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[m] += w[j] * a[j];
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < kGrpM; ++m)
+    for (int o = 16; o > 0; o >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], o);
+}
+
+template <int TG, int TU, typename T>
+__global__ void moe_gate_up_grouped_kernel(const T* __restrict__ x, long ldx, const uint8_t* __restrict__ gate,
+                                           const uint8_t* __restrict__ up, long expert_stride_g, long expert_stride_u,
+                                           long row_stride_g, long row_stride_u, const int* __restrict__ sorted_route,
+                                           const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                                           const int* __restrict__ tile_rows, const int* __restrict__ n_tiles, int top_k,
+                                           int I, int K, float clamp, T* __restrict__ a_sorted) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  extern __shared__ __align__(16) uint8_t gsm[];
+  const Iq2Tables tab = load_iq2_tables<TG == 16 || TU == 16>();
+  const int t = blockIdx.y;
+  if (t >= *n_tiles) return;
+  const int e = tile_expert[t], r0 = tile_row0[t], M = tile_rows[t];
+  T* xs = reinterpret_cast<T*>(gsm);                                  // [M][K]
+  for (int i = threadIdx.x; i < M * (K / 8); i += blockDim.x) {
+    const int m = i / (K / 8), c = i % (K / 8);
+    const int tok = sorted_route[r0 + m] / top_k;
+    reinterpret_cast<uint4*>(xs + static_cast<size_t>(m) * K)[c] =
+        reinterpret_cast<const uint4*>(x + static_cast<long>(tok) * ldx)[c];
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bg = row_buf_bytes(TG, K), bu = row_buf_bytes(TU, K);
+  uint8_t* wb = gsm + ((static_cast<size_t>(kGrpM) * K * sizeof(T) + 15) & ~static_cast<size_t>(15)) +
+                static_cast<size_t>(warp) * 2 * (bg + bu);
+  const uint8_t* ge = gate + static_cast<long>(e) * expert_stride_g;
+  const uint8_t* ue = up + static_cast<long>(e) * expert_stride_u;
+  auto row_of = [&](int rr) { return (blockIdx.x * kMoeRows + rr) * kMoeWarps + warp; };
+  const uint8_t* gd[2];
+  const uint8_t* ud[2];
+  auto fetch = [&](int rr) {
+    const int row = row_of(rr);
+    if (row < I) {
+      uint8_t* b = wb + (rr & 1) * (bg + bu);
+      gd[rr & 1] = stage_chunk(ge + static_cast<long>(row) * row_stride_g, K / Blk<TG>::kVals * Blk<TG>::kBytes, b, lane);
+      ud[rr & 1] = stage_chunk(ue + static_cast<long>(row) * row_stride_u, K / Blk<TU>::kVals * Blk<TU>::kBytes, b + bg, lane);
+    }
+    cp_async_commit();
+  };
+  fetch(0);
+  for (int rr = 0; rr < kMoeRows; ++rr) {
+    const int row = row_of(rr);
+    if (row >= I) break;
+    if (rr + 1 < kMoeRows) fetch(rr + 1);
+    else cp_async_commit();
+    cp_async_wait<1>();
+    __syncwarp();
+    float g[kGrpM], u[kGrpM];
+#pragma unroll
+    for (int m = 0; m < kGrpM; ++m) g[m] = u[m] = 0.f;
+    row_dot16<TG, T>(gd[rr & 1], K, xs, M, lane, g, tab);
+    row_dot16<TU, T>(ud[rr & 1], K, xs, M, lane, u, tab);
+    __syncwarp();
+    if (lane == 0) {
+#pragma unroll
+      for (int m = 0; m < kGrpM; ++m) {
+        if (m < M) {
+          float gv = g[m], uv = u[m];
+          if (clamp > 0.f) { gv = fminf(gv, clamp); uv = fminf(fmaxf(uv, -clamp), clamp); }
+          a_sorted[static_cast<long>(r0 + m) * I + row] = static_cast<T>(gv / (1.f + __expf(-gv)) * uv);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+}
+
+template <int TD, typename T>
+__global__ void moe_down_grouped_kernel(const T* __restrict__ a_sorted, const uint8_t* __restrict__ down,
+                                        long expert_stride, long row_stride, const int* __restrict__ tile_expert,
+                                        const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
+                                        const int* __restrict__ n_tiles, int H, int I, T* __restrict__ y_sorted) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  extern __shared__ __align__(16) uint8_t gsm[];
+  const Iq2Tables tab = load_iq2_tables<TD == 16>();
+  const int t = blockIdx.y;
+  if (t >= *n_tiles) return;
+  const int e = tile_expert[t], r0 = tile_row0[t], M = tile_rows[t];
+  T* xs = reinterpret_cast<T*>(gsm);                                  // [M][I]
+  for (int i = threadIdx.x; i < M * (I / 8); i += blockDim.x)
+    reinterpret_cast<uint4*>(xs)[i] = reinterpret_cast<const uint4*>(a_sorted + static_cast<long>(r0) * I)[i];
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bd = row_buf_bytes(TD, I);
+  uint8_t* wb = gsm + ((static_cast<size_t>(kGrpM) * I * sizeof(T) + 15) & ~static_cast<size_t>(15)) +
+                static_cast<size_t>(warp) * 2 * bd;
+  const uint8_t* de = down + static_cast<long>(e) * expert_stride;
+  auto row_of = [&](int rr) { return (blockIdx.x * kMoeRows + rr) * kMoeWarps + warp; };
+  const uint8_t* dd[2];
+  auto fetch = [&](int rr) {
+    const int row = row_of(rr);
+    if (row < H)
+      dd[rr & 1] = stage_chunk(de + static_cast<long>(row) * row_stride, I / Blk<TD>::kVals * Blk<TD>::kBytes,
+                               wb + (rr & 1) * bd, lane);
+    cp_async_commit();
+  };
+  fetch(0);
+  for (int rr = 0; rr < kMoeRows; ++rr) {
+    const int row = row_of(rr);
+    if (row >= H) break;
+    if (rr + 1 < kMoeRows) fetch(rr + 1);
+    else cp_async_commit();
+    cp_async_wait<1>();
+    __syncwarp();
+    float acc[kGrpM];
+#pragma unroll
+    for (int m = 0; m < kGrpM; ++m) acc[m] = 0.f;
+    row_dot16<TD, T>(dd[rr & 1], I, xs, M, lane, acc, tab);
+    __syncwarp();
+    if (lane == 0) {
+#pragma unroll
+      for (int m = 0; m < kGrpM; ++m)
+        if (m < M) y_sorted[static_cast<long>(r0 + m) * H + row] = static_cast<T>(acc[m]);
+    }
+  }
+  cp_async_wait<0>();
+}
+
 }  // namespace
 
 #define FI_STREAM(s) reinterpret_cast<cudaStream_t>(s)
@@ -532,6 +682,61 @@ extern "C" int fi_gguf_moe_down(const void* a, const void* down, int type_d, lon
     fi::ensure_dynamic_smem(moe_down_kernel<TY, __nv_bfloat16>, 200 * 1024);
     fi::launch_kernel(moe_down_kernel<TY, __nv_bfloat16>, grid, dim3(wpb * 32), smem, FI_STREAM(stream), 0,
                       (const __nv_bfloat16*)a, d, sd, row_stride, ids, e_lo, e_hi, H, I, (__nv_bfloat16*)y);
+  });
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Grouped forms of the routed-expert kernels: routes sorted by expert and cut into tiles of at most
+// 8 routes (fi_moe_align with bn = 8); every tile streams its expert once.  a_sorted / y_sorted are
+// indexed by sorted slot; x is indexed by token.  bf16 activations.
+extern "C" int fi_gguf_moe_gate_up_grouped(const void* x, long ldx, const void* gate, const void* up, int type_g,
+                                           int type_u, long row_stride_g, long row_stride_u, const int* sorted_route,
+                                           const int* tile_expert, const int* tile_row0, const int* tile_rows,
+                                           const int* n_tiles, int max_tiles, int top_k, int I, int K, float clamp,
+                                           void* a_sorted, void* stream) {
+  if (max_tiles <= 0) return 0;
+  if (int rc = ensure_tables()) return rc;
+  if (K % 256 != 0) return -10;
+  const size_t smem = ((static_cast<size_t>(kGrpM) * K * 2 + 15) & ~static_cast<size_t>(15)) +
+                      static_cast<size_t>(kMoeWarps) * 2 * (row_buf_bytes(type_g, K) + row_buf_bytes(type_u, K));
+  if (smem > 200 * 1024) return -12;
+  const int rows_per_cta = kMoeWarps * kMoeRows;
+  const dim3 grid((I + rows_per_cta - 1) / rows_per_cta, max_tiles);
+  const uint8_t* g = static_cast<const uint8_t*>(gate);
+  const uint8_t* u = static_cast<const uint8_t*>(up);
+  const long sg = row_stride_g * I, su = row_stride_u * I;
+#define FI_GUG(TG, TU)                                                                                              \
+  fi::ensure_dynamic_smem(moe_gate_up_grouped_kernel<TG, TU, __nv_bfloat16>, 200 * 1024);                            \
+  fi::launch_kernel(moe_gate_up_grouped_kernel<TG, TU, __nv_bfloat16>, grid, dim3(kMoeWarps * 32), smem,            \
+                    FI_STREAM(stream), 0, (const __nv_bfloat16*)x, ldx, g, u, sg, su, row_stride_g, row_stride_u,   \
+                    sorted_route, tile_expert, tile_row0, tile_rows, n_tiles, top_k, I, K, clamp,                   \
+                    (__nv_bfloat16*)a_sorted)
+  if (type_g == 16 && type_u == 16) { FI_GUG(16, 16); }
+  else if (type_g == 10 && type_u == 10) { FI_GUG(10, 10); }
+  else if (type_g == 8 && type_u == 8) { FI_GUG(8, 8); }
+  else return -11;
+#undef FI_GUG
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fi_gguf_moe_down_grouped(const void* a_sorted, const void* down, int type_d, long row_stride,
+                                        const int* tile_expert, const int* tile_row0, const int* tile_rows,
+                                        const int* n_tiles, int max_tiles, int H, int I, void* y_sorted, void* stream) {
+  if (max_tiles <= 0) return 0;
+  if (int rc = ensure_tables()) return rc;
+  if (I % 256 != 0) return -10;
+  const size_t smem = ((static_cast<size_t>(kGrpM) * I * 2 + 15) & ~static_cast<size_t>(15)) +
+                      static_cast<size_t>(kMoeWarps) * 2 * row_buf_bytes(type_d, I);
+  if (smem > 200 * 1024) return -12;
+  const int rows_per_cta = kMoeWarps * kMoeRows;
+  const dim3 grid((H + rows_per_cta - 1) / rows_per_cta, max_tiles);
+  const uint8_t* d = static_cast<const uint8_t*>(down);
+  const long sd = row_stride * H;
+  FI_TYPE_SWITCH(type_d, {
+    fi::ensure_dynamic_smem(moe_down_grouped_kernel<TY, __nv_bfloat16>, 200 * 1024);
+    fi::launch_kernel(moe_down_grouped_kernel<TY, __nv_bfloat16>, grid, dim3(kMoeWarps * 32), smem, FI_STREAM(stream), 0,
+                      (const __nv_bfloat16*)a_sorted, d, sd, row_stride, tile_expert, tile_row0, tile_rows, n_tiles, H,
+                      I, (__nv_bfloat16*)y_sorted);
   });
   return static_cast<int>(cudaGetLastError());
 }

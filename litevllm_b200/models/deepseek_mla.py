@@ -15,6 +15,8 @@ deepseek_v4_flash/*); its MoE numerics (sigmoid/softplus scoring, shared expert,
 """
 from __future__ import annotations
 
+import os
+
 import torch
 from torch import nn
 
@@ -27,6 +29,10 @@ from ..ops import _lib, _p, _stream, _count, scratch
 from ..parallel import state as pstate
 from .arch import ModelArch
 from .llama import RMSNormWeight
+
+# Routed experts from GGUF blocks: "auto" sorts the routes by expert and runs the grouped kernels when a
+# step has at least as many routes as local experts, "on" / "off" force one form.
+_GROUPED = os.environ.get("FI_GGUF_MOE_GROUPED", "auto")
 
 PAD_HD = 256
 
@@ -166,14 +172,44 @@ class RoutedExperts(nn.Module):
             y = buf[n * self.I * esz: n * (self.I + H) * esz].view(x.dtype).view(n, H)
             e_hi = self.e_lo + self.e_local
             ids_flat = ids.reshape(-1)
-            rc = lib.fi_gguf_moe_gate_up(_p(x), x.stride(0), _p(self.raw["gate"]), _p(self.raw["up"]),
-                                         self.types["gate"], self.types["up"], self.raw["gate"].shape[-1],
-                                         self.raw["up"].shape[-1], _p(ids_flat), n, K, self.e_lo, e_hi, self.I, H,
-                                         self.clamp, _p(a), _stream())
-            _lib.check(rc, "fi_gguf_moe_gate_up")
-            rc = lib.fi_gguf_moe_down(_p(a), _p(self.raw["down"]), self.types["down"], self.raw["down"].shape[-1],
-                                      _p(ids_flat), n, self.e_lo, e_hi, H, self.I, _p(y), _stream())
-            _lib.check(rc, "fi_gguf_moe_down")
+            slot_of = None
+            grouped = (_GROUPED == "on" or (_GROUPED == "auto" and n >= self.e_local)) and x.dtype == torch.bfloat16 \
+                and self.types["gate"] == self.types["up"] and self.types["gate"] in (8, 10, 16)
+            if grouped:
+                # many routes per expert (prefill, large decode batches): sort the routes by expert and let every
+                # tile of up to 8 routes stream its expert once
+                max_tiles = n // 8 + self.e_local
+                ints = scratch("ds_moe_ints", (2 * n + self.e_local + 1 + 3 * max_tiles + 8) * 4, x.device).view(torch.int32)
+                o = 0
+                sorted_route = ints[o:o + n]; o += n
+                slot_of = ints[o:o + n]; o += n
+                offsets = ints[o:o + self.e_local + 1]; o += self.e_local + 1
+                tile_expert = ints[o:o + max_tiles]; o += max_tiles
+                tile_row0 = ints[o:o + max_tiles]; o += max_tiles
+                tile_rows = ints[o:o + max_tiles]; o += max_tiles
+                n_tiles = ints[o:o + 1]
+                rc = lib.fi_moe_align(_p(ids_flat), n, self.e_lo, e_hi, 8, _p(sorted_route), _p(slot_of), _p(offsets),
+                                      _p(tile_expert), _p(tile_row0), _p(tile_rows), _p(n_tiles), _stream())
+                _lib.check(rc, "fi_moe_align")
+                rc = lib.fi_gguf_moe_gate_up_grouped(
+                    _p(x), x.stride(0), _p(self.raw["gate"]), _p(self.raw["up"]), self.types["gate"], self.types["up"],
+                    self.raw["gate"].shape[-1], self.raw["up"].shape[-1], _p(sorted_route), _p(tile_expert),
+                    _p(tile_row0), _p(tile_rows), _p(n_tiles), max_tiles, K, self.I, H, self.clamp, _p(a), _stream())
+                _lib.check(rc, "fi_gguf_moe_gate_up_grouped")
+                rc = lib.fi_gguf_moe_down_grouped(_p(a), _p(self.raw["down"]), self.types["down"],
+                                                  self.raw["down"].shape[-1], _p(tile_expert), _p(tile_row0),
+                                                  _p(tile_rows), _p(n_tiles), max_tiles, H, self.I, _p(y), _stream())
+                _lib.check(rc, "fi_gguf_moe_down_grouped")
+                _count(1)
+            else:
+                rc = lib.fi_gguf_moe_gate_up(_p(x), x.stride(0), _p(self.raw["gate"]), _p(self.raw["up"]),
+                                             self.types["gate"], self.types["up"], self.raw["gate"].shape[-1],
+                                             self.raw["up"].shape[-1], _p(ids_flat), n, K, self.e_lo, e_hi, self.I, H,
+                                             self.clamp, _p(a), _stream())
+                _lib.check(rc, "fi_gguf_moe_gate_up")
+                rc = lib.fi_gguf_moe_down(_p(a), _p(self.raw["down"]), self.types["down"], self.raw["down"].shape[-1],
+                                          _p(ids_flat), n, self.e_lo, e_hi, H, self.I, _p(y), _stream())
+                _lib.check(rc, "fi_gguf_moe_down")
             out = torch.empty(T, H, dtype=x.dtype, device=x.device)
             heap = None
             if pstate.ep_size() > 1:
@@ -183,12 +219,12 @@ class RoutedExperts(nn.Module):
                 # expert parallel: combine + sum over ranks in one kernel (routes of other ranks are zero rows)
                 import ctypes
                 comm = heap.comm_desc(mode=1, T=T, N=H, xfer_16bit=2)
-                rc = lib.fi_moe_combine_allreduce(_p(y), None, _p(weights), None, _p(out), T, K, H, ops._DT[x.dtype],
+                rc = lib.fi_moe_combine_allreduce(_p(y), _p(slot_of), _p(weights), None, _p(out), T, K, H, ops._DT[x.dtype],
                                                   _p(ops.status_word(x.device)), _stream(), ctypes.byref(comm))
                 _lib.check(rc, "fi_moe_combine_allreduce")
                 _count(3)
                 return out
-            rc = lib.fi_moe_combine(_p(y), None, _p(weights), None, _p(out), T, K, H, ops._DT[x.dtype], _stream())
+            rc = lib.fi_moe_combine(_p(y), _p(slot_of), _p(weights), None, _p(out), T, K, H, ops._DT[x.dtype], _stream())
             _lib.check(rc, "fi_moe_combine")
             _count(3)
         if pstate.ep_size() > 1:

@@ -645,3 +645,72 @@ def test_fused_collective_epilogue_loopback_world1():
             heap.close()
         if created:
             dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("tg,td", [("IQ2_XXS", "Q2_K"), ("Q8_0", "Q8_0"), ("Q2_K", "IQ2_XXS")])
+@pytest.mark.parametrize("T", [3, 40])
+def test_gguf_routed_experts_grouped_and_per_route(tg, td, T):
+    """Routed experts stored as GGUF blocks: the per-route kernels and the expert-grouped kernels (routes
+    sorted by expert, every tile of up to 8 routes streams its expert once) against the dequantise-and-matmul
+    oracle, for few routes (every expert hit at most once or twice) and many (ragged tiles, several per expert)."""
+    import litevllm_b200.models.deepseek_mla as dm
+    from litevllm_b200.loaders.gguf import GGUFTensor
+    from litevllm_b200.models.arch import arch_from_hf_config
+    from litevllm_b200.models.presets import get_preset
+    from litevllm_b200.ops import gguf_quant as gq
+    arch = arch_from_hf_config(get_preset("tiny-deepseek-test"))
+    E, I, H, K = arch.moe.num_experts, arch.moe.expert_intermediate, arch.hidden_size, arch.moe.top_k
+    dev = torch.device(DEV, 0)
+    with torch.device(dev):
+        ex = dm.RoutedExperts(arch, torch.bfloat16)
+    ex.device = dev
+    tyg, tyd = gq.GGML_TYPES[tg], gq.GGML_TYPES[td]
+    ex.load("gate", GGUFTensor(gq.random_blocks(tyg, E * I, H, seed=21, scale=0.05).view(E, I, -1), tyg, (E, I, H)))
+    ex.load("up", GGUFTensor(gq.random_blocks(tyg, E * I, H, seed=22, scale=0.05).view(E, I, -1), tyg, (E, I, H)))
+    ex.load("down", GGUFTensor(gq.random_blocks(tyd, E * H, I, seed=23, scale=0.05).view(E, H, -1), tyd, (E, H, I)))
+    g = torch.Generator(device=dev).manual_seed(T)
+    x = torch.randn(T, H, generator=g, device=dev).bfloat16()
+    ids = torch.stack([torch.randperm(E, generator=g, device=dev)[:K] for _ in range(T)]).to(torch.int32)
+    w = torch.rand(T, K, generator=g, device=dev)
+    outs = {}
+    saved = dm._GROUPED
+    try:
+        for mode in ("off", "on"):
+            dm._GROUPED = mode
+            outs[mode] = ex(x, ids, w).float()
+    finally:
+        dm._GROUPED = saved
+    torch.cuda.synchronize()
+    cpu = dm.RoutedExperts.__new__(dm.RoutedExperts)
+    cpu.__dict__.update(ex.__dict__)
+    cpu.raw = {k: v.cpu() for k, v in ex.raw.items()}
+    want = dm.RoutedExperts.forward(cpu, x.cpu(), ids.cpu().long(), w.cpu()).float()
+    for mode, got in outs.items():
+        err = (got.cpu() - want).abs().max().item()
+        assert err < 0.03 * max(1.0, want.abs().max().item()), (mode, err, want.abs().max().item())
+    assert (outs["on"] - outs["off"]).abs().max().item() < 0.02 * max(1.0, want.abs().max().item())
+
+
+def test_gguf_dense_layer_resident_copy_budget(monkeypatch):
+    """A GGUF linear layer keeps its blocks when the budget for 16-bit copies is zero and swaps them for a
+    dense weight (same results within rounding) when there is room."""
+    from litevllm_b200.layers.linear import LiteLinear
+    from litevllm_b200.layers.quantization import gguf as gl
+    from litevllm_b200.loaders.gguf import GGUFTensor
+    from litevllm_b200.ops import gguf_quant as gq
+    dev = torch.device(DEV, 0)
+    N, K = 384, 512
+    raw = gq.random_blocks(gq.GGML_TYPES["Q8_0"], N, K, seed=5, scale=0.05)
+    x = torch.randn(5, K, device=dev).bfloat16()
+    outs = {}
+    for budget in ("0", "1"):
+        monkeypatch.setenv("FI_GGUF_DENSE_RESIDENT_GB", budget)
+        monkeypatch.setattr(gl, "_resident_used", [0])
+        with torch.device(dev):
+            layer = LiteLinear(K, N, dtype=torch.bfloat16, quant_config=gl.GGUFConfig(), prefix="blk.0.attn_q")
+        layer.quant_method.load_piece(layer, 0, "weight", GGUFTensor(raw, gq.GGML_TYPES["Q8_0"], (N, K)), (0, N))
+        outs[budget] = layer(x).float()
+        assert (layer.g_raw is None) == (budget == "1") and (layer.weight is not None) == (budget == "1")
+    want = x.float().cpu() @ gq.dequantize(raw, gq.GGML_TYPES["Q8_0"], K).t()
+    for k, got in outs.items():
+        assert (got.cpu() - want).abs().max().item() < 0.03 * max(1.0, want.abs().max().item()), k
