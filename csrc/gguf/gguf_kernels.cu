@@ -566,6 +566,243 @@ __global__ void moe_down_grouped_kernel(const T* __restrict__ a_sorted, const ui
   cp_async_wait<0>();
 }
 
+// ------------------------------------------------------------------------------ int8 activations
+// Q2_K and IQ2_XXS weights are small integers times a block scale, so with the activations quantised to
+// int8 (one fp32 scale per 32 values, as llama.cpp's Q8 activation blocks) a group of 32 weights is eight
+// dp4a instructions instead of 32 conversions and 32 FMAs: the routed-expert kernels above spend about ten
+// instructions per weight on decoding, these about one and a half.
+//   IQ2_XXS: codebook magnitudes (8 / 25 / 43) get their signs with (m ^ mask) - mask on packed bytes.
+//   Q2_K:    2-bit codes are masked out four at a time; the block minimum uses the integer sum of the
+//            16 activations it covers.
+__device__ __forceinline__ uint32_t sign_mask4(uint32_t s4) {   // bit j of s4 -> byte j = 0xFF
+  return ((s4 * 0x00204081u) & 0x01010101u) * 0xFFu;
+}
+
+// One activation row: int8 codes q[K], scales d[K / 32], integer sums of every 16 codes s16[K / 16].
+template <typename T>
+__device__ __forceinline__ void stage_act_q8(const T* __restrict__ x, int K, int8_t* q, float* d, int* s16) {
+  for (int b = threadIdx.x; b < K / 32; b += blockDim.x) {
+    float v[32];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) unpack8_16bit<T>(reinterpret_cast<const uint4*>(x + b * 32)[c], v + c * 8);
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    const float inv = amax > 0.f ? 127.f / amax : 0.f;
+    uint32_t w[8];
+    int sum0 = 0, sum1 = 0;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      int c[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) c[k] = __float2int_rn(v[j + k] * inv);
+      if (j < 16) sum0 += c[0] + c[1] + c[2] + c[3];
+      else sum1 += c[0] + c[1] + c[2] + c[3];
+      w[j >> 2] = (c[0] & 0xFF) | ((c[1] & 0xFF) << 8) | ((c[2] & 0xFF) << 16) | (static_cast<uint32_t>(c[3] & 0xFF) << 24);
+    }
+    reinterpret_cast<uint4*>(q + b * 32)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    reinterpret_cast<uint4*>(q + b * 32)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    d[b] = amax / 127.f;
+    s16[2 * b] = sum0;
+    s16[2 * b + 1] = sum1;
+  }
+}
+
+template <int MAXM> struct ActQ8 {
+  // shared-memory footprint of MAXM activation rows of K values
+  __host__ __device__ static constexpr size_t bytes(int K) {
+    return static_cast<size_t>(MAXM) * (K + (K / 32) * 4 + (K / 16) * 4);
+  }
+};
+
+// Dot products of one weight row (types 10 and 16; the row is 4-byte aligned for type 10, 2-byte for 16)
+// with M int8 activation rows.
+template <int TYPE, int MAXM>
+__device__ __forceinline__ void row_dot_q8(const uint8_t* r, int K, const int8_t* xq, const float* xd, const int* xs16,
+                                           int M, int lane, float* acc, const Iq2Tables& tab) {
+  static_assert(TYPE == 10 || TYPE == 16, "int8-activation path: Q2_K and IQ2_XXS");
+  for (int g = lane; g < K / 32; g += 32) {
+    const int v0 = g * 32;
+    const uint8_t* blk = r + (v0 >> 8) * Blk<TYPE>::kBytes;
+    const int o = v0 & 255;
+    uint32_t w[8];
+    if (TYPE == 16) {
+      const uint16_t* q16 = reinterpret_cast<const uint16_t*>(blk + 2 + (o >> 5) * 8);
+      const uint32_t idx = q16[0] | (static_cast<uint32_t>(q16[1]) << 16);
+      const uint32_t word = q16[2] | (static_cast<uint32_t>(q16[3]) << 16);
+      const float db = h2f(blk) * (0.5f + static_cast<float>(word >> 28)) * 0.25f;
+#pragma unroll
+      for (int l = 0; l < 4; ++l) {
+        const uint64_t g64 = tab.grid[(idx >> (8 * l)) & 255];
+        const uint32_t sg = tab.signs[(word >> (7 * l)) & 127];
+        const uint32_t m0 = sign_mask4(sg & 15), m1 = sign_mask4(sg >> 4);
+        w[2 * l] = __vsub4(static_cast<uint32_t>(g64) ^ m0, m0);
+        w[2 * l + 1] = __vsub4(static_cast<uint32_t>(g64 >> 32) ^ m1, m1);
+      }
+#pragma unroll
+      for (int m = 0; m < MAXM; ++m) {
+        if (m < M) {
+          const int* xw = reinterpret_cast<const int*>(xq + static_cast<size_t>(m) * K + v0);
+          int sacc = 0;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sacc = __dp4a(static_cast<int>(w[i]), xw[i], sacc);
+          acc[m] += db * xd[m * (K / 32) + g] * static_cast<float>(sacc);
+        }
+      }
+    } else {
+      const int n = o >> 7, sh = ((o & 127) >> 5) * 2, sub = n * 8 + ((o & 127) >> 5) * 2;
+      const uint32_t sc0 = blk[sub], sc1 = blk[sub + 1];
+      const float d = h2f(blk + 80), dmin = h2f(blk + 82);
+      const uint32_t* qw = reinterpret_cast<const uint32_t*>(blk + 16 + n * 32);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) w[i] = (qw[i] >> sh) & 0x03030303u;
+      const float a0 = d * static_cast<float>(sc0 & 15), a1 = d * static_cast<float>(sc1 & 15);
+      const float b0 = dmin * static_cast<float>(sc0 >> 4), b1 = dmin * static_cast<float>(sc1 >> 4);
+#pragma unroll
+      for (int m = 0; m < MAXM; ++m) {
+        if (m < M) {
+          const int* xw = reinterpret_cast<const int*>(xq + static_cast<size_t>(m) * K + v0);
+          int s0 = 0, s1 = 0;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) s0 = __dp4a(static_cast<int>(w[i]), xw[i], s0);
+#pragma unroll
+          for (int i = 4; i < 8; ++i) s1 = __dp4a(static_cast<int>(w[i]), xw[i], s1);
+          const int* ss = xs16 + m * (K / 16) + 2 * g;
+          acc[m] += xd[m * (K / 32) + g] * (a0 * static_cast<float>(s0) + a1 * static_cast<float>(s1) -
+                                            b0 * static_cast<float>(ss[0]) - b1 * static_cast<float>(ss[1]));
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MAXM; ++m)
+    for (int o = 16; o > 0; o >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], o);
+}
+
+// Grouped gate|up and down with int8 activations (same tiling as the kernels above; MAXM = 1 serves decode
+// steps whose routes all hit different experts: fi_moe_align with tiles of one route).
+template <int TG, int TU, int MAXM, typename T>
+__global__ void moe_gate_up_q8_kernel(const T* __restrict__ x, long ldx, const uint8_t* __restrict__ gate,
+                                      const uint8_t* __restrict__ up, long expert_stride_g, long expert_stride_u,
+                                      long row_stride_g, long row_stride_u, const int* __restrict__ sorted_route,
+                                      const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                                      const int* __restrict__ tile_rows, const int* __restrict__ n_tiles, int top_k,
+                                      int I, int K, float clamp, T* __restrict__ a_sorted) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  extern __shared__ __align__(16) uint8_t gsm[];
+  const Iq2Tables tab = load_iq2_tables<TG == 16 || TU == 16>();
+  const int t = blockIdx.y;
+  if (t >= *n_tiles) return;
+  const int e = tile_expert[t], r0 = tile_row0[t], M = tile_rows[t];
+  int8_t* xq = reinterpret_cast<int8_t*>(gsm);
+  float* xd = reinterpret_cast<float*>(gsm + static_cast<size_t>(MAXM) * K);
+  int* xs16 = reinterpret_cast<int*>(xd + MAXM * (K / 32));
+  for (int m = 0; m < M; ++m) {
+    const int tok = sorted_route[r0 + m] / top_k;
+    stage_act_q8<T>(x + static_cast<long>(tok) * ldx, K, xq + static_cast<size_t>(m) * K, xd + m * (K / 32),
+                    xs16 + m * (K / 16));
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bg = row_buf_bytes(TG, K), bu = row_buf_bytes(TU, K);
+  uint8_t* wb = gsm + ((ActQ8<MAXM>::bytes(K) + 15) & ~static_cast<size_t>(15)) + static_cast<size_t>(warp) * 2 * (bg + bu);
+  const uint8_t* ge = gate + static_cast<long>(e) * expert_stride_g;
+  const uint8_t* ue = up + static_cast<long>(e) * expert_stride_u;
+  auto row_of = [&](int rr) { return (blockIdx.x * kMoeRows + rr) * kMoeWarps + warp; };
+  const uint8_t* gd[2];
+  const uint8_t* ud[2];
+  auto fetch = [&](int rr) {
+    const int row = row_of(rr);
+    if (row < I) {
+      uint8_t* b = wb + (rr & 1) * (bg + bu);
+      gd[rr & 1] = stage_chunk(ge + static_cast<long>(row) * row_stride_g, K / Blk<TG>::kVals * Blk<TG>::kBytes, b, lane);
+      ud[rr & 1] = stage_chunk(ue + static_cast<long>(row) * row_stride_u, K / Blk<TU>::kVals * Blk<TU>::kBytes, b + bg, lane);
+    }
+    cp_async_commit();
+  };
+  fetch(0);
+  for (int rr = 0; rr < kMoeRows; ++rr) {
+    const int row = row_of(rr);
+    if (row >= I) break;
+    if (rr + 1 < kMoeRows) fetch(rr + 1);
+    else cp_async_commit();
+    cp_async_wait<1>();
+    __syncwarp();
+    float g[MAXM], u[MAXM];
+#pragma unroll
+    for (int m = 0; m < MAXM; ++m) g[m] = u[m] = 0.f;
+    row_dot_q8<TG, MAXM>(gd[rr & 1], K, xq, xd, xs16, M, lane, g, tab);
+    row_dot_q8<TU, MAXM>(ud[rr & 1], K, xq, xd, xs16, M, lane, u, tab);
+    __syncwarp();
+    if (lane == 0) {
+#pragma unroll
+      for (int m = 0; m < MAXM; ++m) {
+        if (m < M) {
+          float gv = g[m], uv = u[m];
+          if (clamp > 0.f) { gv = fminf(gv, clamp); uv = fminf(fmaxf(uv, -clamp), clamp); }
+          a_sorted[static_cast<long>(r0 + m) * I + row] = static_cast<T>(gv / (1.f + __expf(-gv)) * uv);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+}
+
+template <int TD, int MAXM, typename T>
+__global__ void moe_down_q8_kernel(const T* __restrict__ a_sorted, const uint8_t* __restrict__ down,
+                                   long expert_stride, long row_stride, const int* __restrict__ tile_expert,
+                                   const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
+                                   const int* __restrict__ n_tiles, int H, int I, T* __restrict__ y_sorted) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  extern __shared__ __align__(16) uint8_t gsm[];
+  const Iq2Tables tab = load_iq2_tables<TD == 16>();
+  const int t = blockIdx.y;
+  if (t >= *n_tiles) return;
+  const int e = tile_expert[t], r0 = tile_row0[t], M = tile_rows[t];
+  int8_t* xq = reinterpret_cast<int8_t*>(gsm);
+  float* xd = reinterpret_cast<float*>(gsm + static_cast<size_t>(MAXM) * I);
+  int* xs16 = reinterpret_cast<int*>(xd + MAXM * (I / 32));
+  for (int m = 0; m < M; ++m)
+    stage_act_q8<T>(a_sorted + static_cast<long>(r0 + m) * I, I, xq + static_cast<size_t>(m) * I, xd + m * (I / 32),
+                    xs16 + m * (I / 16));
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bd = row_buf_bytes(TD, I);
+  uint8_t* wb = gsm + ((ActQ8<MAXM>::bytes(I) + 15) & ~static_cast<size_t>(15)) + static_cast<size_t>(warp) * 2 * bd;
+  const uint8_t* de = down + static_cast<long>(e) * expert_stride;
+  auto row_of = [&](int rr) { return (blockIdx.x * kMoeRows + rr) * kMoeWarps + warp; };
+  const uint8_t* dd[2];
+  auto fetch = [&](int rr) {
+    const int row = row_of(rr);
+    if (row < H)
+      dd[rr & 1] = stage_chunk(de + static_cast<long>(row) * row_stride, I / Blk<TD>::kVals * Blk<TD>::kBytes,
+                               wb + (rr & 1) * bd, lane);
+    cp_async_commit();
+  };
+  fetch(0);
+  for (int rr = 0; rr < kMoeRows; ++rr) {
+    const int row = row_of(rr);
+    if (row >= H) break;
+    if (rr + 1 < kMoeRows) fetch(rr + 1);
+    else cp_async_commit();
+    cp_async_wait<1>();
+    __syncwarp();
+    float acc[MAXM];
+#pragma unroll
+    for (int m = 0; m < MAXM; ++m) acc[m] = 0.f;
+    row_dot_q8<TD, MAXM>(dd[rr & 1], I, xq, xd, xs16, M, lane, acc, tab);
+    __syncwarp();
+    if (lane == 0) {
+#pragma unroll
+      for (int m = 0; m < MAXM; ++m)
+        if (m < M) y_sorted[static_cast<long>(r0 + m) * H + row] = static_cast<T>(acc[m]);
+    }
+  }
+  cp_async_wait<0>();
+}
+
 }  // namespace
 
 #define FI_STREAM(s) reinterpret_cast<cudaStream_t>(s)
@@ -738,5 +975,69 @@ extern "C" int fi_gguf_moe_down_grouped(const void* a_sorted, const void* down, 
                       (const __nv_bfloat16*)a_sorted, d, sd, row_stride, tile_expert, tile_row0, tile_rows, n_tiles, H,
                       I, (__nv_bfloat16*)y_sorted);
   });
+  return static_cast<int>(cudaGetLastError());
+}
+
+// The same two steps with int8 activations (Q2_K / IQ2_XXS experts only; tile_m = 1 or 8 must match the
+// bn given to fi_moe_align).  Returns -11 for other formats: the caller then uses the float kernels.
+extern "C" int fi_gguf_moe_gate_up_q8(const void* x, long ldx, const void* gate, const void* up, int type_g,
+                                      int type_u, long row_stride_g, long row_stride_u, const int* sorted_route,
+                                      const int* tile_expert, const int* tile_row0, const int* tile_rows,
+                                      const int* n_tiles, int max_tiles, int tile_m, int top_k, int I, int K,
+                                      float clamp, void* a_sorted, void* stream) {
+  if (max_tiles <= 0) return 0;
+  if (int rc = ensure_tables()) return rc;
+  if (K % 256 != 0 || (ldx % 8) != 0 || (tile_m != 1 && tile_m != 8)) return -10;
+  if (type_g != type_u || (type_g != 10 && type_g != 16)) return -11;
+  if ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up)) & 3) return -11;
+  const size_t act = tile_m == 1 ? ActQ8<1>::bytes(K) : ActQ8<8>::bytes(K);
+  const size_t smem = ((act + 15) & ~static_cast<size_t>(15)) +
+                      static_cast<size_t>(kMoeWarps) * 2 * (row_buf_bytes(type_g, K) + row_buf_bytes(type_u, K));
+  if (smem > 200 * 1024) return -12;
+  const int rows_per_cta = kMoeWarps * kMoeRows;
+  const dim3 grid((I + rows_per_cta - 1) / rows_per_cta, max_tiles);
+  const uint8_t* g = static_cast<const uint8_t*>(gate);
+  const uint8_t* u = static_cast<const uint8_t*>(up);
+  const long sg = row_stride_g * I, su = row_stride_u * I;
+#define FI_GUQ(TY, MM)                                                                                              \
+  fi::ensure_dynamic_smem(moe_gate_up_q8_kernel<TY, TY, MM, __nv_bfloat16>, 200 * 1024);                             \
+  fi::launch_kernel(moe_gate_up_q8_kernel<TY, TY, MM, __nv_bfloat16>, grid, dim3(kMoeWarps * 32), smem,             \
+                    FI_STREAM(stream), 0, (const __nv_bfloat16*)x, ldx, g, u, sg, su, row_stride_g, row_stride_u,   \
+                    sorted_route, tile_expert, tile_row0, tile_rows, n_tiles, top_k, I, K, clamp,                   \
+                    (__nv_bfloat16*)a_sorted)
+  if (type_g == 16 && tile_m == 1) { FI_GUQ(16, 1); }
+  else if (type_g == 16) { FI_GUQ(16, 8); }
+  else if (tile_m == 1) { FI_GUQ(10, 1); }
+  else { FI_GUQ(10, 8); }
+#undef FI_GUQ
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fi_gguf_moe_down_q8(const void* a_sorted, const void* down, int type_d, long row_stride,
+                                   const int* tile_expert, const int* tile_row0, const int* tile_rows,
+                                   const int* n_tiles, int max_tiles, int tile_m, int H, int I, void* y_sorted,
+                                   void* stream) {
+  if (max_tiles <= 0) return 0;
+  if (int rc = ensure_tables()) return rc;
+  if (I % 256 != 0 || (tile_m != 1 && tile_m != 8)) return -10;
+  if (type_d != 10 && type_d != 16) return -11;
+  if (reinterpret_cast<uintptr_t>(down) & 3) return -11;
+  const size_t act = tile_m == 1 ? ActQ8<1>::bytes(I) : ActQ8<8>::bytes(I);
+  const size_t smem = ((act + 15) & ~static_cast<size_t>(15)) + static_cast<size_t>(kMoeWarps) * 2 * row_buf_bytes(type_d, I);
+  if (smem > 200 * 1024) return -12;
+  const int rows_per_cta = kMoeWarps * kMoeRows;
+  const dim3 grid((H + rows_per_cta - 1) / rows_per_cta, max_tiles);
+  const uint8_t* d = static_cast<const uint8_t*>(down);
+  const long sd = row_stride * H;
+#define FI_DQ(TY, MM)                                                                                          \
+  fi::ensure_dynamic_smem(moe_down_q8_kernel<TY, MM, __nv_bfloat16>, 200 * 1024);                               \
+  fi::launch_kernel(moe_down_q8_kernel<TY, MM, __nv_bfloat16>, grid, dim3(kMoeWarps * 32), smem,               \
+                    FI_STREAM(stream), 0, (const __nv_bfloat16*)a_sorted, d, sd, row_stride, tile_expert,     \
+                    tile_row0, tile_rows, n_tiles, H, I, (__nv_bfloat16*)y_sorted)
+  if (type_d == 16 && tile_m == 1) { FI_DQ(16, 1); }
+  else if (type_d == 16) { FI_DQ(16, 8); }
+  else if (tile_m == 1) { FI_DQ(10, 1); }
+  else { FI_DQ(10, 8); }
+#undef FI_DQ
   return static_cast<int>(cudaGetLastError());
 }

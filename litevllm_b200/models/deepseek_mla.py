@@ -33,6 +33,9 @@ from .llama import RMSNormWeight
 # Routed experts from GGUF blocks: "auto" sorts the routes by expert and runs the grouped kernels when a
 # step has at least as many routes as local experts, "on" / "off" force one form.
 _GROUPED = os.environ.get("FI_GGUF_MOE_GROUPED", "auto")
+# Q2_K / IQ2_XXS experts: quantise the activations to int8 (a scale per 32 values) and use integer dot products
+# (FI_GGUF_MOE_Q8=0 keeps 16-bit activations and float arithmetic).
+_Q8 = os.environ.get("FI_GGUF_MOE_Q8", "1") != "0"
 
 PAD_HD = 256
 
@@ -173,12 +176,17 @@ class RoutedExperts(nn.Module):
             e_hi = self.e_lo + self.e_local
             ids_flat = ids.reshape(-1)
             slot_of = None
-            grouped = (_GROUPED == "on" or (_GROUPED == "auto" and n >= self.e_local)) and x.dtype == torch.bfloat16 \
-                and self.types["gate"] == self.types["up"] and self.types["gate"] in (8, 10, 16)
+            same_gu = self.types["gate"] == self.types["up"]
+            # int8 activations + dp4a for the 2-bit formats; 16-bit activations for the others
+            q8 = _Q8 and x.dtype == torch.bfloat16 and same_gu and self.types["gate"] in (10, 16) \
+                and self.types["down"] in (10, 16)
+            grouped = q8 or ((_GROUPED == "on" or (_GROUPED == "auto" and n >= self.e_local))
+                             and x.dtype == torch.bfloat16 and same_gu and self.types["gate"] in (8, 10, 16))
             if grouped:
-                # many routes per expert (prefill, large decode batches): sort the routes by expert and let every
-                # tile of up to 8 routes stream its expert once
-                max_tiles = n // 8 + self.e_local
+                # routes sorted by expert; a tile of up to 8 routes of one expert streams that expert once.  Steps
+                # with fewer routes than experts (small decode batches) use tiles of one route.
+                tile_m = 8 if (not q8 or n >= self.e_local) else 1
+                max_tiles = n if tile_m == 1 else n // 8 + self.e_local
                 ints = scratch("ds_moe_ints", (2 * n + self.e_local + 1 + 3 * max_tiles + 8) * 4, x.device).view(torch.int32)
                 o = 0
                 sorted_route = ints[o:o + n]; o += n
@@ -188,18 +196,32 @@ class RoutedExperts(nn.Module):
                 tile_row0 = ints[o:o + max_tiles]; o += max_tiles
                 tile_rows = ints[o:o + max_tiles]; o += max_tiles
                 n_tiles = ints[o:o + 1]
-                rc = lib.fi_moe_align(_p(ids_flat), n, self.e_lo, e_hi, 8, _p(sorted_route), _p(slot_of), _p(offsets),
+                rc = lib.fi_moe_align(_p(ids_flat), n, self.e_lo, e_hi, tile_m, _p(sorted_route), _p(slot_of), _p(offsets),
                                       _p(tile_expert), _p(tile_row0), _p(tile_rows), _p(n_tiles), _stream())
                 _lib.check(rc, "fi_moe_align")
-                rc = lib.fi_gguf_moe_gate_up_grouped(
-                    _p(x), x.stride(0), _p(self.raw["gate"]), _p(self.raw["up"]), self.types["gate"], self.types["up"],
-                    self.raw["gate"].shape[-1], self.raw["up"].shape[-1], _p(sorted_route), _p(tile_expert),
-                    _p(tile_row0), _p(tile_rows), _p(n_tiles), max_tiles, K, self.I, H, self.clamp, _p(a), _stream())
-                _lib.check(rc, "fi_gguf_moe_gate_up_grouped")
-                rc = lib.fi_gguf_moe_down_grouped(_p(a), _p(self.raw["down"]), self.types["down"],
-                                                  self.raw["down"].shape[-1], _p(tile_expert), _p(tile_row0),
-                                                  _p(tile_rows), _p(n_tiles), max_tiles, H, self.I, _p(y), _stream())
-                _lib.check(rc, "fi_gguf_moe_down_grouped")
+                if q8:
+                    rc = lib.fi_gguf_moe_gate_up_q8(
+                        _p(x), x.stride(0), _p(self.raw["gate"]), _p(self.raw["up"]), self.types["gate"],
+                        self.types["up"], self.raw["gate"].shape[-1], self.raw["up"].shape[-1], _p(sorted_route),
+                        _p(tile_expert), _p(tile_row0), _p(tile_rows), _p(n_tiles), max_tiles, tile_m, K, self.I, H,
+                        self.clamp, _p(a), _stream())
+                    _lib.check(rc, "fi_gguf_moe_gate_up_q8")
+                    rc = lib.fi_gguf_moe_down_q8(_p(a), _p(self.raw["down"]), self.types["down"],
+                                                 self.raw["down"].shape[-1], _p(tile_expert), _p(tile_row0),
+                                                 _p(tile_rows), _p(n_tiles), max_tiles, tile_m, H, self.I, _p(y),
+                                                 _stream())
+                    _lib.check(rc, "fi_gguf_moe_down_q8")
+                else:
+                    rc = lib.fi_gguf_moe_gate_up_grouped(
+                        _p(x), x.stride(0), _p(self.raw["gate"]), _p(self.raw["up"]), self.types["gate"],
+                        self.types["up"], self.raw["gate"].shape[-1], self.raw["up"].shape[-1], _p(sorted_route),
+                        _p(tile_expert), _p(tile_row0), _p(tile_rows), _p(n_tiles), max_tiles, K, self.I, H, self.clamp,
+                        _p(a), _stream())
+                    _lib.check(rc, "fi_gguf_moe_gate_up_grouped")
+                    rc = lib.fi_gguf_moe_down_grouped(_p(a), _p(self.raw["down"]), self.types["down"],
+                                                      self.raw["down"].shape[-1], _p(tile_expert), _p(tile_row0),
+                                                      _p(tile_rows), _p(n_tiles), max_tiles, H, self.I, _p(y), _stream())
+                    _lib.check(rc, "fi_gguf_moe_down_grouped")
                 _count(1)
             else:
                 rc = lib.fi_gguf_moe_gate_up(_p(x), x.stride(0), _p(self.raw["gate"]), _p(self.raw["up"]),

@@ -673,13 +673,16 @@ def test_gguf_routed_experts_grouped_and_per_route(tg, td, T):
     ids = torch.stack([torch.randperm(E, generator=g, device=dev)[:K] for _ in range(T)]).to(torch.int32)
     w = torch.rand(T, K, generator=g, device=dev)
     outs = {}
-    saved = dm._GROUPED
+    saved = dm._GROUPED, dm._Q8
     try:
+        dm._Q8 = False
         for mode in ("off", "on"):
             dm._GROUPED = mode
             outs[mode] = ex(x, ids, w).float()
+        dm._Q8, dm._GROUPED = True, "auto"
+        outs["q8"] = ex(x, ids, w).float()       # int8 activations (the 2-bit formats; Q8_0 keeps the float path)
     finally:
-        dm._GROUPED = saved
+        dm._GROUPED, dm._Q8 = saved
     torch.cuda.synchronize()
     cpu = dm.RoutedExperts.__new__(dm.RoutedExperts)
     cpu.__dict__.update(ex.__dict__)
