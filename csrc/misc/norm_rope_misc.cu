@@ -154,7 +154,9 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ p
   T* row = qkv + static_cast<long>(t) * total_heads * hd;
   const int slot = slot_mapping ? slot_mapping[t] : -1;
   const int half = rot_dim >> 1;
-  for (int h = warp; h < total_heads; h += nwarps) {
+  // the heads of a token are spread over gridDim.y CTAs (few tokens with many heads would otherwise
+  // keep a handful of SMs busy)
+  for (int h = blockIdx.y * nwarps + warp; h < total_heads; h += nwarps * gridDim.y) {
     T* x = row + static_cast<long>(h) * hd;
     const bool is_q = h < nh;
     const bool is_k = !is_q && h < nh + nkv;
@@ -550,6 +552,55 @@ extern "C" int fi_rmsnorm(const void* x, void* residual, const void* w, void* ou
   });
 }
 
+// Multi-head latent attention, materialised form: builds the [q | k | v] row of a token with padded heads
+// in one pass.  q head = [rope part | no-position part | 0], k head = [shared rope key | no-position key | 0],
+// v head = [value | 0]; q is [T, nh, nope + rope] (no-position part first), k_rope [T, rope] with row pitch
+// ldk, kvb [T, nh, nope + vd].  All section widths are multiples of 8 (16-byte moves).
+template <typename T>
+__global__ void mla_assemble_kernel(const T* __restrict__ q, const T* __restrict__ k_rope, long ldk,
+                                    const T* __restrict__ kvb, T* __restrict__ buf, int nh, int nope, int rope,
+                                    int vd, int pad) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y * (blockDim.x >> 5) + warp;
+  if (head >= 3 * nh) return;
+  const int kind = head / nh, h = head % nh;
+  uint4* dst = reinterpret_cast<uint4*>(buf + (static_cast<long>(t) * 3 * nh + head) * pad);
+  const T* qh = q + (static_cast<long>(t) * nh + h) * (nope + rope);
+  const T* kh = kvb + (static_cast<long>(t) * nh + h) * (nope + vd);
+  for (int c = lane; c < pad / 8; c += 32) {
+    const int i = c * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (kind == 0) {
+      if (i < rope) v = *reinterpret_cast<const uint4*>(qh + nope + i);
+      else if (i < rope + nope) v = *reinterpret_cast<const uint4*>(qh + i - rope);
+    } else if (kind == 1) {
+      if (i < rope) v = *reinterpret_cast<const uint4*>(k_rope + static_cast<long>(t) * ldk + i);
+      else if (i < rope + nope) v = *reinterpret_cast<const uint4*>(kh + i - rope);
+    } else {
+      if (i < vd) v = *reinterpret_cast<const uint4*>(kh + nope + i);
+    }
+    dst[c] = v;
+  }
+}
+
+extern "C" int fi_mla_assemble(const void* q, const void* k_rope, long ldk, const void* kvb, void* buf, int T, int nh,
+                               int nope, int rope, int vd, int pad, int dtype, void* stream) {
+  if (T <= 0) return 0;
+  if ((nope | rope | vd | pad) % 8 != 0 || ldk % 8 != 0 || rope + nope > pad || vd > pad) return -10;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_rope) | reinterpret_cast<uintptr_t>(kvb) |
+       reinterpret_cast<uintptr_t>(buf)) & 15)
+    return -10;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using Tt = std::remove_pointer_t<decltype(tag)>;
+    fi::launch_kernel(mla_assemble_kernel<Tt>, dim3(T, (3 * nh + 7) / 8), dim3(256), 0, FI_STREAM(stream), 0,
+                      (const Tt*)q, (const Tt*)k_rope, ldk, (const Tt*)kvb, (Tt*)buf, nh, nope, rope, vd, pad);
+    return static_cast<int>(cudaGetLastError());
+  });
+}
+
 extern "C" int fi_rope_cache(void* qkv, const int* positions, const float* cos_sin,
                              const int* freq_stream, const int* slot_mapping, void* k_cache,
                              void* v_cache, const void* qw, const void* kw, int T, int nh, int nkv,
@@ -569,7 +620,12 @@ extern "C" int fi_rope_cache(void* qkv, const int* positions, const float* cos_s
     }
     int warps = nh + 2 * nkv;
     if (warps > 16) warps = 16;
-    fi::launch_kernel(rope_cache_kernel<Tt>, dim3(T), dim3(warps * 32), 0, FI_STREAM(stream), 0, 
+    // head groups per token: enough CTAs for about two waves when the token count alone does not give them
+    int groups = (nh + 2 * nkv + warps - 1) / warps;
+    const int want = (2 * 148 + T - 1) / T;
+    if (groups > want) groups = want;
+    if (groups < 1) groups = 1;
+    fi::launch_kernel(rope_cache_kernel<Tt>, dim3(T, groups), dim3(warps * 32), 0, FI_STREAM(stream), 0, 
         (Tt*)qkv, positions, cos_sin, freq_stream, slot_mapping, k_cache, v_cache, (const Tt*)qw,
         (const Tt*)kw, T, nh, nkv, hd, rot_dim, block_size, kv_fp8, k_scale, v_scale, eps,
         qk_norm_mode, v_norm);

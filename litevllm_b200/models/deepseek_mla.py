@@ -86,12 +86,19 @@ class MLAAttention(nn.Module):
         k_rope = kva[:, self.kv_lora:]
         kvb = self.kv_b_proj(latent).view(T, self.nh, self.nope + self.vd)
         # assemble [q | k | v] with padded heads laid out [rope | nope | 0]
-        buf = torch.zeros(T, 3 * self.nh, PAD_HD, dtype=x.dtype, device=x.device)
-        buf[:, : self.nh, : self.rope] = q[..., self.nope:]
-        buf[:, : self.nh, self.rope:self.qk] = q[..., : self.nope]
-        buf[:, self.nh:2 * self.nh, : self.rope] = k_rope[:, None, :]
-        buf[:, self.nh:2 * self.nh, self.rope:self.qk] = kvb[..., : self.nope]
-        buf[:, 2 * self.nh:, : self.vd] = kvb[..., self.nope:]
+        if x.is_cuda and q.is_contiguous() and kvb.is_contiguous() and x.dtype in (torch.bfloat16, torch.float16):
+            buf = torch.empty(T, 3 * self.nh, PAD_HD, dtype=x.dtype, device=x.device)
+            rc = _lib.kernels().fi_mla_assemble(_p(q), _p(k_rope), k_rope.stride(0), _p(kvb), _p(buf), T, self.nh,
+                                                self.nope, self.rope, self.vd, PAD_HD, ops._DT[x.dtype], _stream())
+            _lib.check(rc, "fi_mla_assemble")
+            _count()
+        else:
+            buf = torch.zeros(T, 3 * self.nh, PAD_HD, dtype=x.dtype, device=x.device)
+            buf[:, : self.nh, : self.rope] = q[..., self.nope:]
+            buf[:, : self.nh, self.rope:self.qk] = q[..., : self.nope]
+            buf[:, self.nh:2 * self.nh, : self.rope] = k_rope[:, None, :]
+            buf[:, self.nh:2 * self.nh, self.rope:self.qk] = kvb[..., : self.nope]
+            buf[:, 2 * self.nh:, : self.vd] = kvb[..., self.nope:]
         qkv = buf.view(T, 3 * self.nh * PAD_HD)
         k_cache, v_cache = kv
         cfg = batch.config
