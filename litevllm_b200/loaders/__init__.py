@@ -75,7 +75,22 @@ def get_model(vllm_config, device: str | torch.device = "auto") -> torch.nn.Modu
         weights = iter_gguf_weights(mc.model, mc.arch)
     else:
         weights = iter_safetensors(mc.model)
+    # repacked int4 layouts from an earlier start of the same checkpoint on the same rank layout
+    cache_path = None
+    if not mc.synthetic and not mc.is_gguf and dev.type == "cuda":
+        from . import repack_cache
+        from ..parallel import state as pstate
+        st = pstate.get_state()
+        cache_path = repack_cache.cache_file(mc.model, st.rank, max(st.world_size, 1), mc.dtype)
+        if cache_path is not None and repack_cache.attach(model, cache_path, dev):
+            logger.info("int4 layouts attached from %s; packed tensors of the checkpoint are not read", cache_path)
+            weights = repack_cache.lazy_safetensors_without_packed(mc.model)
+            cache_path = None
     consumed = model.load_weights(weights)
+    if cache_path is not None:
+        n = repack_cache.save(model, cache_path)
+        if n:
+            logger.info("wrote the repacked layouts of %d int4 layers to %s", n, cache_path)
     logger.info("loaded %d tensors into %s on %s", len(consumed), cls.__name__, dev)
     model.eval()
     return model

@@ -27,6 +27,7 @@ from ..ops import gguf_quant as gq
 from ..ops import moe as moe_ops
 from ..ops import _lib, _p, _stream, _count, scratch
 from ..parallel import state as pstate
+from ..utils.profiling import stage
 from .arch import ModelArch
 from .llama import RMSNormWeight
 
@@ -297,11 +298,13 @@ class DeepseekDecoderLayer(nn.Module):
             self.mlp = GatedMLP(arch.hidden_size, arch.intermediate_size, dtype, qc, p + ".mlp")
 
     def forward(self, h, batch, kv, max_pos):
-        h = self.self_attn(self.input_layernorm(h), h, batch, kv, max_pos)
+        with stage("layer.attention"):
+            h = self.self_attn(self.input_layernorm(h), h, batch, kv, max_pos)
         x = self.post_attention_layernorm(h)
-        if self.is_moe:
-            return self.mlp(x, h)
-        return self.mlp(x, residual=h)
+        with stage("layer.moe" if self.is_moe else "layer.mlp"):
+            if self.is_moe:
+                return self.mlp(x, h)
+            return self.mlp(x, residual=h)
 
 
 class DeepseekMLAForCausalLM(nn.Module):

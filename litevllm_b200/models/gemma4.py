@@ -22,6 +22,7 @@ from ..layers.rope import get_cos_sin
 from ..ops import moe as moe_ops
 from ..ops.awq import Int4Weight, unpack_nibbles
 from ..parallel import state as pstate
+from ..utils.profiling import stage
 from .arch import ModelArch
 from .llama import RMSNormWeight
 
@@ -182,17 +183,22 @@ class Gemma4DecoderLayer(nn.Module):
             self.mlp = Gemma4MLP(arch, arch.intermediate_size, dtype, qc, p + ".mlp")
 
     def forward(self, h, batch, kv, max_pos):
-        a = self.self_attn(self.input_layernorm(h), batch, kv, max_pos)
-        h = ops.rmsnorm(a, self.post_attention_layernorm.weight, self.post_attention_layernorm.eps, addend=h)
+        with stage("layer.attention"):
+            a = self.self_attn(self.input_layernorm(h), batch, kv, max_pos)
+            h = ops.rmsnorm(a, self.post_attention_layernorm.weight, self.post_attention_layernorm.eps, addend=h)
         x = self.pre_feedforward_layernorm(h)
         if self.use_moe:
-            dense = self.post_feedforward_layernorm_1(self.shared_mlp(x, batch))
-            ids, w = self.router(h)
-            sparse = self.experts(self.pre_feedforward_layernorm_2(h), ids, w)
+            with stage("layer.moe.shared"):
+                dense = self.post_feedforward_layernorm_1(self.shared_mlp(x, batch))
+            with stage("layer.moe.router"):
+                ids, w = self.router(h)
+            with stage("layer.moe.experts"):
+                sparse = self.experts(self.pre_feedforward_layernorm_2(h), ids, w)
             y = ops.rmsnorm(sparse, self.post_feedforward_layernorm_2.weight, self.post_feedforward_layernorm_2.eps,
                             addend=dense)
         else:
-            y = self.mlp(x, batch)
+            with stage("layer.mlp"):
+                y = self.mlp(x, batch)
         h = ops.rmsnorm(y, self.post_feedforward_layernorm.weight, self.post_feedforward_layernorm.eps, addend=h)
         if self._scalar != 1.0:
             h = h * self._scalar

@@ -17,6 +17,7 @@ from .. import ops
 from ..layers.linear import LiteLinear
 from ..layers.rope import get_cos_sin
 from ..parallel import state as pstate
+from ..utils.profiling import stage
 from .arch import ModelArch
 
 
@@ -151,10 +152,12 @@ class LlamaDecoderLayer(nn.Module):
             h = self.self_attn(h, h, batch, kv, cos_sin, norm_eps=self.input_layernorm.eps)
             return self.mlp(h, h, batch, norm_eps=self.post_attention_layernorm.eps)
         lora = batch.lora_mapping is not None and self.fused_norm
-        x = self.input_layernorm(h)
-        h = self.self_attn(x, h, batch, kv, cos_sin, lora_x=self.input_layernorm.weighted(h) if lora else None)
-        x = self.post_attention_layernorm(h)
-        return self.mlp(x, h, batch, lora_x=self.post_attention_layernorm.weighted(h) if lora else None)
+        with stage("layer.attention"):
+            x = self.input_layernorm(h)
+            h = self.self_attn(x, h, batch, kv, cos_sin, lora_x=self.input_layernorm.weighted(h) if lora else None)
+        with stage("layer.mlp"):
+            x = self.post_attention_layernorm(h)
+            return self.mlp(x, h, batch, lora_x=self.post_attention_layernorm.weighted(h) if lora else None)
 
 
 class LlamaForCausalLM(nn.Module):

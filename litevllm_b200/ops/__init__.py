@@ -486,6 +486,44 @@ def paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, nh, nkv,
     return out
 
 
+def paged_metadata_snapshot(q, k_cache, block_tables, seq_lens, cu_q=None, scope: str = "") -> dict:
+    """Synchronising description of one paged-attention call's addressing, for diagnostics: shapes and strides,
+    the blocks every sequence needs against the width of its block-table row, the range of block ids in use and
+    which rows or ids fall outside the cache.  Raises ``IndexError`` when any do.  Small batches list every row,
+    large ones only ranges.  Reference: vllm/kernels/triton/paged_attention.py:223-289."""
+    if q.is_cuda:
+        torch.cuda.synchronize(q.device)
+    bs = int(k_cache.shape[2])
+    lens = [int(v) for v in seq_lens.detach().cpu().tolist()]
+    table = block_tables.detach().cpu()
+    need = [(n + bs - 1) // bs for n in lens]
+    width = int(table.shape[1])
+    short_rows = [r for r, n in enumerate(need) if n > width]
+    ids = [int(b) for r, n in enumerate(need) for b in table[r, :min(n, width)].tolist()]
+    bad_ids = sorted({b for b in ids if b < 0 or b >= int(k_cache.shape[0])})
+    few = len(lens) <= 8
+    snap = {
+        "scope": scope, "query_shape": list(q.shape), "query_strides": list(q.stride()),
+        "cache_shape": list(k_cache.shape), "cache_strides": list(k_cache.stride()), "cache_dtype": str(k_cache.dtype),
+        "block_size": bs, "block_table_shape": list(table.shape),
+        "seq_lens": lens if few else {"count": len(lens), "min": min(lens, default=None), "max": max(lens, default=None)},
+        "blocks_needed": need if few else {"min": min(need, default=None), "max": max(need, default=None)},
+        "block_ids": [table[r, :min(n, width)].tolist() for r, n in enumerate(need)] if few else "omitted (more than 8 rows)",
+        "block_id_range": [min(ids), max(ids)] if ids else None,
+        "rows_longer_than_table": short_rows, "block_ids_outside_cache": bad_ids[:8],
+    }
+    if cu_q is not None:
+        cu = [int(v) for v in cu_q.detach().cpu().tolist()]
+        snap["new_tokens"] = [b - a for a, b in zip(cu, cu[1:])] if few else {"total": cu[-1] if cu else 0}
+        over = [r for r, (a, b) in enumerate(zip(cu, cu[1:])) if b - a > lens[r]] if len(cu) == len(lens) + 1 else []
+        snap["rows_with_more_new_tokens_than_length"] = over
+        if over:
+            short_rows = short_rows or over
+    if short_rows or bad_ids:
+        raise IndexError(f"paged attention metadata out of range: {snap}")
+    return snap
+
+
 def paged_attention_prefill(q, k_cache, v_cache, block_tables, seq_lens, cu_q, max_q_len, nh, nkv,
                             hd, sm_scale, window=0, softcap=0.0, k_scale=1.0, v_scale=1.0, out=None):
     """Varlen causal attention of new tokens against the paged cache (which already holds them)."""

@@ -86,6 +86,15 @@ class Int4Weight:
             self.qw = self.scales_t = self.zeros_t = None
             self.nib, self.scales, self.zeros = nib, scales, zeros
 
+    @classmethod
+    def from_runtime(cls, qw, scales_t, zeros_t, N: int, K: int, group: int) -> "Int4Weight":
+        """Wrap tensors that already are in the kernel's layout (the on-disk repack cache)."""
+        w = cls.__new__(cls)
+        w.N, w.K, w.group = int(N), int(K), int(group)
+        w.qw, w.scales_t, w.zeros_t = qw, scales_t, zeros_t
+        w.nib = w.scales = w.zeros = None
+        return w
+
     def dense(self) -> torch.Tensor:
         """float32 [N, K]; rebuilt from the runtime layout when the loading-time tensors were dropped."""
         if self.nib is not None:

@@ -99,3 +99,20 @@ class SpanProfiler:
 
 PROFILER = SpanProfiler()
 span = PROFILER.span
+
+# Per-stage spans inside a model's forward (attention / dense MLP / router / routed experts / shared expert of
+# every layer, final norm + lm_head).  They are a second switch on top of the profiler itself because they
+# only measure eager forwards (prefill, or decode with CUDA graphs off): under graph capture or replay no
+# Python runs per stage.  ``FASTINFERENCE_PROFILE_STAGES=1`` (environment) or ``PROFILER.stages = True``.
+# Reference: vllm/model_executor/models/gemma4/profiling.py:57-97 (per-stage wall-clock spans).
+import os as _os
+
+PROFILER.stages = _os.environ.get("FASTINFERENCE_PROFILE_STAGES", "0") == "1"
+_NO_SPAN = contextlib.nullcontext()
+
+
+def stage(scope: str):
+    """``with stage("layer.attn"): ...`` - a profiler span when stage profiling is on, else a shared no-op."""
+    if PROFILER.stages and (PROFILER.enabled or PROFILER.nvtx):
+        return PROFILER.span(scope)
+    return _NO_SPAN

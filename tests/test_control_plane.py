@@ -336,3 +336,38 @@ def test_bounds_check_mode_names_the_bad_index():
             ops.reshape_and_cache(torch.zeros(1, 2, 8), torch.zeros(1, 2, 8), torch.tensor([9 * 16], dtype=torch.int32), kc, vc)
     finally:
         ops.set_bounds_check(False)
+
+
+def test_stage_spans_and_attention_metadata_snapshot():
+    """Per-stage profile spans of an eager forward, and the paged-attention metadata snapshot: a consistent call
+    is described, a block id outside the cache or a sequence longer than its block-table row is refused."""
+    import pytest
+    import torch
+    from litevllm_b200 import LLM, SamplingParams, ops
+    from litevllm_b200.utils.profiling import PROFILER
+    PROFILER.reset()
+    PROFILER.configure(True)
+    saved = PROFILER.stages
+    PROFILER.stages = True
+    try:
+        llm = LLM("synthetic:tiny-llama-test", dtype="float32", device="cpu", max_num_seqs=2, max_model_len=64)
+        llm.generate([[1, 2, 3, 4, 5]], SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))
+        summ = PROFILER.summary()
+        llm.shutdown()
+    finally:
+        PROFILER.stages = saved
+        PROFILER.configure(False)
+    assert summ["layer.attention"]["count"] >= 2 and summ["layer.mlp"]["count"] >= 2
+    PROFILER.reset()
+
+    kc = torch.zeros(6, 2, 16, 8)
+    q = torch.zeros(3, 4 * 8)
+    bt = torch.tensor([[1, 2, 0], [3, 0, 0]], dtype=torch.int32)
+    snap = ops.paged_metadata_snapshot(q, kc, bt, torch.tensor([20, 5], dtype=torch.int32),
+                                       torch.tensor([0, 2, 3], dtype=torch.int32), scope="layer0")
+    assert snap["blocks_needed"] == [2, 1] and snap["block_id_range"] == [1, 3] and snap["new_tokens"] == [2, 1]
+    with pytest.raises(IndexError):
+        ops.paged_metadata_snapshot(q, kc, torch.tensor([[1, 9, 0], [3, 0, 0]], dtype=torch.int32),
+                                    torch.tensor([20, 5], dtype=torch.int32))
+    with pytest.raises(IndexError):
+        ops.paged_metadata_snapshot(q, kc, bt, torch.tensor([70, 5], dtype=torch.int32))

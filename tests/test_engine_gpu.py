@@ -111,3 +111,46 @@ def test_quantised_models_match_cpu_oracle(preset, min_cos):
     outs = gpu.generate(_prompts(512, (9, 33)), SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
     assert all(len(o.outputs[0].token_ids) == 8 for o in outs)
     ops.check_status(torch.device("cuda:0"))
+
+
+def test_int4_repack_cache_round_trip(tmp_path, monkeypatch):
+    """An AWQ checkpoint directory loaded twice with FASTINFERENCE_REPACK_CACHE_DIR set: the first start
+    writes the repacked layouts, the second attaches them (no packed tensor is read) and generates the same
+    tokens; a touched checkpoint file changes the fingerprint and the cache is not used."""
+    import json
+    import os
+
+    from safetensors.torch import save_file
+
+    from litevllm_b200 import LLM, SamplingParams
+    from litevllm_b200.loaders import repack_cache, synth
+    from litevllm_b200.models.arch import arch_from_hf_config
+    from litevllm_b200.models.presets import get_preset
+    preset = get_preset("tiny-llama-awq-test")
+    ckpt = tmp_path / "ckpt"
+    ckpt.mkdir()
+    (ckpt / "config.json").write_text(json.dumps(preset))
+    arch = arch_from_hf_config(preset)
+    tensors = {n: t.contiguous().cpu() for n, t in synth.iter_llama_weights(arch, 0, torch.float32, "cpu")}
+    save_file(tensors, str(ckpt / "model.safetensors"))
+    monkeypatch.setenv("FASTINFERENCE_REPACK_CACHE_DIR", str(tmp_path / "cache"))
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    prompts = [[3, 9, 27, 81], [5, 6, 7]]
+
+    def run():
+        llm = LLM(str(ckpt), dtype="bfloat16", device="cuda:0", max_num_seqs=2, max_model_len=64)
+        cached = [getattr(m, "_repack_cached", False) for m in llm.engine.model.modules() if hasattr(m, "int4")]
+        toks = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+        llm.shutdown()
+        return toks, cached
+
+    first, cached1 = run()
+    files = list((tmp_path / "cache").glob("*.pt"))
+    assert len(files) == 1 and not any(cached1)
+    second, cached2 = run()
+    assert cached2 and all(cached2) and second == first
+    st = os.stat(ckpt / "model.safetensors")
+    os.utime(ckpt / "model.safetensors", ns=(st.st_atime_ns, st.st_mtime_ns + 10 ** 9))
+    assert repack_cache.fingerprint(ckpt) not in files[0].name
+    third, cached3 = run()
+    assert not any(cached3) and third == first
