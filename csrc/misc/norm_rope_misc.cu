@@ -452,6 +452,34 @@ __global__ void gather_rows_i32_kernel(const int* __restrict__ table, const int*
   for (int c = threadIdx.x; c < cols; c += blockDim.x) to[c] = from[c];
 }
 
+// ------------------------------------------------------------------ selective KV blocks
+// Sparse decode attention over a subset of a sequence's KV blocks: block i of n is kept when
+// i % stride == 0, or i < min_blocks, or i == n - 1.  The kept block ids are written densely into
+// out_table[r, :] and out_len[r] is the token count of the compacted sequence (every kept block full except
+// the last one of the sequence, which stays last), so the ordinary paged decode kernel runs unchanged on
+// the compact table.  One warp per sequence.
+__global__ void select_blocks_kernel(const int* __restrict__ table, const int* __restrict__ seq_lens,
+                                     int* __restrict__ out_table, int* __restrict__ out_len, int cols,
+                                     int block_size, int stride, int min_blocks) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  const int r = blockIdx.x, lane = threadIdx.x;
+  const int len = seq_lens[r];
+  const int n = len > 0 ? min((len + block_size - 1) / block_size, cols) : 0;
+  const int* from = table + static_cast<long>(r) * cols;
+  int* to = out_table + static_cast<long>(r) * cols;
+  int kept = 0;
+  for (int base = 0; base < n; base += 32) {
+    const int i = base + lane;
+    const bool keep = i < n && (i % stride == 0 || i < min_blocks || i == n - 1);
+    const unsigned m = __ballot_sync(0xffffffffu, keep);
+    if (keep) to[kept + __popc(m & ((1u << lane) - 1u))] = from[i];
+    kept += __popc(m);
+  }
+  for (int c = kept + lane; c < cols; c += 32) to[c] = 0;      // the null block
+  if (lane == 0) out_len[r] = n > 0 ? (kept - 1) * block_size + (len - (n - 1) * block_size) : 0;
+}
+
 // ------------------------------------------------------------------ greedy arg-max
 // One block per row; ties resolve to the lowest index (matches torch.argmax on CPU).
 template <typename T>
@@ -714,6 +742,15 @@ extern "C" int fi_gather_rows_i32(const int* table, const int* idx, int* out, in
   if (n_table_rows <= 0) return -10;
   fi::launch_kernel(gather_rows_i32_kernel, dim3(rows), dim3(cols >= 256 ? 256 : 64), 0, FI_STREAM(stream), 0,
                     table, idx, out, cols, n_table_rows);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fi_select_blocks(const int* table, const int* seq_lens, int* out_table, int* out_len, int rows,
+                                int cols, int block_size, int stride, int min_blocks, void* stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (block_size <= 0 || stride <= 0 || min_blocks < 0) return -10;
+  fi::launch_kernel(select_blocks_kernel, dim3(rows), dim3(32), 0, FI_STREAM(stream), 0, table, seq_lens, out_table,
+                    out_len, cols, block_size, stride, min_blocks);
   return static_cast<int>(cudaGetLastError());
 }
 

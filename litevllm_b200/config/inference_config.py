@@ -17,6 +17,10 @@ class LiteInferenceConfig:
     kernel_policy: dict[str, Any] = field(default_factory=dict)
     profile_spans: bool = False
     nvtx: bool = False
+    # selective (sparse) decode attention: fraction of a sequence's KV blocks that global-attention layers
+    # read (0 = all of them), and how many leading blocks are always kept
+    kv_select_ratio: float = 0.0
+    kv_select_min_blocks: int = 4
 
     def model_value(self, key: str, default: Any = None) -> Any:
         return self.model_policy.get(key, default)

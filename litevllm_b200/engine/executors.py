@@ -71,6 +71,7 @@ class DecodeExecutor:
         self.launches_per_graph: dict[int, int] = {}
 
     def _run(self, batch: ForwardBatch) -> torch.Tensor:
+        batch.extras.pop("_selected_blocks", None)      # per-step product of the selective-attention kernel
         return self.model(batch, self.kv_cache)
 
     def _step_body(self, batch: ForwardBatch, greedy_only: bool = False) -> torch.Tensor:

@@ -42,6 +42,21 @@ class ForwardBatch:
     q_lens_cpu: list[int] = field(default_factory=list)
     extras: dict = field(default_factory=dict)   # model-specific carries (linear-attention state, ...)
 
+    def attention_tables(self, window: int = 0):
+        """``(block_tables, seq_lens)`` an attention layer should read.  With selective attention on
+        (``kv_select_ratio`` > 0) a decode step's global-attention layers (no sliding window) get the compact
+        tables of the kept blocks; they are built once per step, by one kernel, the first time a layer asks."""
+        cfg = self.config
+        if not self.is_decode or window or getattr(cfg, "kv_select_ratio", 0.0) <= 0.0:
+            return self.block_tables, self.seq_lens
+        sel = self.extras.get("_selected_blocks")
+        if sel is None:
+            from .. import ops
+            stride = max(1, int(1.0 / cfg.kv_select_ratio))
+            sel = ops.select_blocks(self.block_tables, self.seq_lens, cfg.block_size, stride, cfg.kv_select_min_blocks)
+            self.extras["_selected_blocks"] = sel
+        return sel
+
 
 def decode_buckets(max_active: int) -> list[int]:
     out, b = [], 1

@@ -54,7 +54,9 @@ class LiteEngine:
             kv_cache_dtype=self.model_policy.force_kv_cache_dtype or self.rc.kv_cache_dtype,
             k_scale=self.rc.k_scale, v_scale=self.rc.v_scale, block_size=self.rc.block_size,
             fusion_level=self.rc.fusion_level, nvtx=self.rc.profile_nvtx,
-            profile_spans=self.rc.profile_step_events)
+            profile_spans=self.rc.profile_step_events,
+            kv_select_ratio=max(0.0, min(1.0, float(self.rc.kv_select_ratio))),
+            kv_select_min_blocks=max(1, int(self.rc.kv_select_min_blocks)))
         self.adapter.install_tuning_config(self.rc, self.inf_config)
         if self.inf_config.profile_spans or self.inf_config.nvtx:
             from ..utils.profiling import PROFILER

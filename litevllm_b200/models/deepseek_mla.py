@@ -106,7 +106,7 @@ class MLAAttention(nn.Module):
         ops.rope_and_cache(qkv, batch.positions, self.cos_sin(x.device, max_pos), batch.slot_mapping, k_cache, v_cache,
                            self.nh, self.nh, PAD_HD, self.rope, k_scale=cfg.k_scale, v_scale=cfg.v_scale)
         if batch.is_decode:
-            attn = ops.paged_attention_decode(qkv, k_cache, v_cache, batch.block_tables, batch.seq_lens, self.nh,
+            attn = ops.paged_attention_decode(qkv, k_cache, v_cache, *batch.attention_tables(0), self.nh,
                                               self.nh, PAD_HD, self.sm_scale, 0, 0.0, cfg.k_scale, cfg.v_scale,
                                               max_kv_len=batch.max_kv_len)
         else:

@@ -74,7 +74,7 @@ class Gemma4Attention(nn.Module):
                            k_norm_w=self.k_norm.weight, qk_norm_mode=0, v_norm=True, eps=self.eps,
                            k_scale=cfg.k_scale, v_scale=cfg.v_scale)
         if batch.is_decode:
-            attn = ops.paged_attention_decode(qkv, k_cache, v_cache, batch.block_tables, batch.seq_lens, self.nh,
+            attn = ops.paged_attention_decode(qkv, k_cache, v_cache, *batch.attention_tables(self.window), self.nh,
                                               self.nkv, self.hd, 1.0, self.window, self.softcap, cfg.k_scale,
                                               cfg.v_scale, max_kv_len=batch.max_kv_len)
         else:

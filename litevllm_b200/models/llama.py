@@ -97,7 +97,7 @@ class LlamaAttention(nn.Module):
                                k_scale=cfg.k_scale, v_scale=cfg.v_scale,
                                freq_stream=batch.extras.get("freq_stream") if batch.positions.dim() == 2 else None)
         if batch.is_decode:
-            attn = ops.paged_attention_decode(qkv, k_cache, v_cache, batch.block_tables, batch.seq_lens,
+            attn = ops.paged_attention_decode(qkv, k_cache, v_cache, *batch.attention_tables(self.window),
                                               self.nh, self.nkv, self.hd, self.sm_scale, self.window, 0.0,
                                               cfg.k_scale, cfg.v_scale, max_kv_len=batch.max_kv_len)
         else:

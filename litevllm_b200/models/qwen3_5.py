@@ -183,7 +183,7 @@ class GatedFullAttention(nn.Module):
                            self.hd, self.rot_dim, q_norm_w=self.q_norm.weight, k_norm_w=self.k_norm.weight,
                            qk_norm_mode=1, eps=self.eps, k_scale=cfg.k_scale, v_scale=cfg.v_scale)
         if batch.is_decode:
-            attn = ops.paged_attention_decode(qkv, k_cache, v_cache, batch.block_tables, batch.seq_lens, self.nh,
+            attn = ops.paged_attention_decode(qkv, k_cache, v_cache, *batch.attention_tables(0), self.nh,
                                               self.nkv, self.hd, self.hd ** -0.5, 0, 0.0, cfg.k_scale, cfg.v_scale,
                                               max_kv_len=batch.max_kv_len)
         else:

@@ -653,6 +653,36 @@ def gather_rows_i32(table, idx, out):
     return out
 
 
+def select_blocks(block_tables, seq_lens, block_size: int, stride: int, min_blocks: int, out_table=None, out_len=None):
+    """Compact block tables for selective (sparse) decode attention: of a sequence's ``n`` KV blocks keep
+    block ``i`` when ``i % stride == 0``, ``i < min_blocks`` or ``i == n - 1``.  Returns ``(table, lens)`` of
+    the input shapes: the kept ids packed to the left (rest: the null block) and the token count of the
+    compacted sequence.  The paged decode kernel then runs unchanged on them.
+    Reference: vllm/kernels/triton/paged_attention.py:94-120 (active-block index lists)."""
+    if out_table is None:
+        out_table = torch.empty_like(block_tables)
+    if out_len is None:
+        out_len = torch.empty_like(seq_lens)
+    if not block_tables.is_cuda:
+        out_table.zero_()
+        for r in range(block_tables.shape[0]):
+            ln = int(seq_lens[r])
+            n = min((ln + block_size - 1) // block_size, block_tables.shape[1]) if ln > 0 else 0
+            keep = [i for i in range(n) if i % stride == 0 or i < min_blocks or i == n - 1]
+            if keep:
+                out_table[r, :len(keep)] = block_tables[r, keep]
+            out_len[r] = (len(keep) - 1) * block_size + (ln - (n - 1) * block_size) if n > 0 else 0
+        return out_table, out_len
+    assert block_tables.dtype == torch.int32 and seq_lens.dtype == torch.int32
+    assert block_tables.is_contiguous() and out_table.is_contiguous()
+    rc = _lib.kernels().fi_select_blocks(_p(block_tables), _p(seq_lens), _p(out_table), _p(out_len),
+                                         block_tables.shape[0], block_tables.shape[1], int(block_size), int(stride),
+                                         int(min_blocks), _stream())
+    _lib.check(rc, "fi_select_blocks")
+    _count()
+    return out_table, out_len
+
+
 def argmax(logits, out=None):
     if not logits.is_cuda:
         r = reference.argmax(logits)

@@ -371,3 +371,29 @@ def test_stage_spans_and_attention_metadata_snapshot():
                                     torch.tensor([20, 5], dtype=torch.int32))
     with pytest.raises(IndexError):
         ops.paged_metadata_snapshot(q, kc, bt, torch.tensor([70, 5], dtype=torch.int32))
+
+
+def test_selective_block_tables_and_engine_cpu():
+    """Selective decode attention: the compact table keeps every stride-th block, the leading blocks and the
+    last one; with a ratio of 1 the engine generates exactly what it generates without the feature, with a
+    small ratio it still runs to completion on a context of many blocks."""
+    import torch
+    from litevllm_b200 import LLM, SamplingParams, ops
+    bt = torch.arange(1, 25, dtype=torch.int32).view(2, 12)
+    sl = torch.tensor([16 * 9 + 5, 7], dtype=torch.int32)          # 10 blocks (last partial), 1 block
+    tab, lens = ops.select_blocks(bt, sl, 16, 4, 2)
+    assert tab[0, :5].tolist() == [1, 2, 5, 9, 10] and tab[0, 5:].tolist() == [0] * 7    # blocks 0,1 | 4 | 8 | 9
+    assert lens.tolist() == [4 * 16 + 5, 7] and tab[1, 0].item() == 13
+    prompt = [(7 * i) % 500 + 1 for i in range(100)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+
+    def run(ratio):
+        cfg = {"tuning_keyvals": {"FASTINFERENCE_KV_SELECT_RATIO": str(ratio), "FASTINFERENCE_KV_SELECT_MIN_BLOCKS": "1"}}
+        llm = LLM("synthetic:tiny-llama-test", dtype="float32", device="cpu", max_num_seqs=2, max_model_len=160,
+                  fastinference_config=cfg if ratio else None)
+        out = llm.generate([prompt], sp)[0].outputs[0].token_ids
+        llm.shutdown()
+        return out
+    base = run(0)
+    assert run(1.0) == base
+    assert len(run(0.25)) == 6

@@ -717,3 +717,25 @@ def test_gguf_dense_layer_resident_copy_budget(monkeypatch):
     want = x.float().cpu() @ gq.dequantize(raw, gq.GGML_TYPES["Q8_0"], K).t()
     for k, got in outs.items():
         assert (got.cpu() - want).abs().max().item() < 0.03 * max(1.0, want.abs().max().item()), k
+
+
+def test_select_blocks_kernel_and_sparse_decode():
+    """The block-selection kernel against its CPU form, and decode attention over the compact table against
+    the fp32 oracle evaluated on exactly the kept tokens."""
+    torch.manual_seed(31)
+    nh, nkv, hd, bs = 8, 2, 64, 16
+    lens = [16 * 9 + 5, 7, 16 * 40, 33]
+    B = len(lens)
+    kc, vc, bt = _fill_paged(B, lens, nkv, hd, bs, False)
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    tab, sel_len = ops.select_blocks(bt, sl, bs, 4, 2)
+    tab_c, len_c = ops.select_blocks(bt.cpu(), sl.cpu(), bs, 4, 2)
+    assert torch.equal(tab.cpu(), tab_c) and torch.equal(sel_len.cpu(), len_c)
+    q = torch.randn(B, nh * hd, device=DEV).bfloat16()
+    scale = 1.0 / math.sqrt(hd)
+    y = ops.paged_attention_decode(q, kc, vc, tab, sel_len, nh, nkv, hd, scale, 0, 0.0, 1.0, 1.0,
+                                   max_kv_len=max(lens))
+    cu = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    yr = ref.paged_attention(q, kc, vc, tab, sel_len, cu, nh, nkv, hd, scale, 0, 0.0, 1.0, 1.0, out_dtype=torch.float32)
+    _close(y, yr, 2e-2, 2e-2, "sparse decode over the compact table")
+    assert sel_len.tolist()[2] < lens[2] // 2
