@@ -46,9 +46,10 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--comm-backend", default="fused", choices=["fused", "nccl"])
-    ap.add_argument("--parallel", default="auto", choices=["auto", "dp", "tp", "ep"],
+    ap.add_argument("--parallel", default="auto", choices=["auto", "dp", "tp", "ep", "tpep"],
                     help="how N GPUs are used: dp = N whole-engine replicas with the batch sharded over them, tp = "
-                         "tensor parallel with the fused collectives, ep = expert parallel (MoE models); auto = dp "
+                         "tensor parallel with the fused collectives, ep = expert parallel (MoE models: experts sharded, "
+                         "attention replicated), tpep = experts sharded and attention / dense layers tensor parallel; auto = dp "
                          "for the headline model when N divides the batch (a 1.1B model at batch 32 is bound by "
                          "per-kernel latency, so replicas beat sharding), else tp")
     ap.add_argument("--profile-json", default=None, help="write per-phase timings here")
@@ -294,8 +295,8 @@ def run_ours(args) -> dict:
     if args.profile_json:
         from litevllm_b200.utils.profiling import PROFILER
         PROFILER.configure(True, nvtx=True)      # event pairs are resolved after the timed regions
-    tp = world if mode == "tp" else 1
-    ep = world if mode == "ep" else 1
+    tp = world if mode in ("tp", "tpep") else 1
+    ep = world if mode in ("ep", "tpep") else 1
     llm = _build_llm(args, world, local_rank, tp, ep, max_len, batch=Bl, dp=world if mode == "dp" else 1)
     eng = llm.engine
     vocab = eng.arch.vocab_size

@@ -55,7 +55,9 @@ def row_parallel_linear(layer, x: torch.Tensor, residual: torch.Tensor | None, o
     st = pstate.get_state()
     T = x.shape[0]
     N = layer.out_features
-    if _fused_available(x):
+    # shapes the tcgen05 kernels take: K in whole 64-element blocks (int4) / 8-element chunks (16-bit)
+    k_ok = x.shape[1] % (64 if layer.quant_method is not None else 8) == 0 and N % 8 == 0
+    if _fused_available(x) and k_ok:
         heap = st.symm
         if T > 0 and T <= 256 and heap.fits_low_latency(T, N):
             fmt = decode_allreduce_format(heap.world, x.dtype if out is None else out.dtype)
