@@ -37,6 +37,9 @@ _GROUPED = os.environ.get("FI_GGUF_MOE_GROUPED", "auto")
 # Q2_K / IQ2_XXS experts: quantise the activations to int8 (a scale per 32 values) and use integer dot products
 # (FI_GGUF_MOE_Q8=0 keeps 16-bit activations and float arithmetic).
 _Q8 = os.environ.get("FI_GGUF_MOE_Q8", "1") != "0"
+# Multi-head latent attention in absorbed form (one 576-value cache row per token instead of per-head K and V):
+# on when the kv_b projections are dense 16-bit matrices on a GPU; FI_MLA_ABSORBED=0 keeps the materialised form.
+_ABSORBED = os.environ.get("FI_MLA_ABSORBED", "1") != "0"
 
 PAD_HD = 256
 
@@ -69,6 +72,66 @@ class MLAAttention(nn.Module):
         self.sm_scale = self.qk ** -0.5
         self.rope_theta, self.rope_scaling = arch.rope_theta, arch.rope_scaling
         self._cos_sin = None
+        self.absorbed = False      # set by the model once the weights are in (see kv_cache_specs)
+
+    def can_absorb(self) -> bool:
+        """The absorbed form needs the kv_b projection as a dense 16-bit matrix on a GPU (its two halves are
+        applied per head, before and after the attention) and the cache-row geometry the kernel is built for."""
+        w = getattr(self.kv_b_proj, "weight", None)
+        return (w is not None and w.is_cuda and w.dtype in (torch.bfloat16, torch.float16)
+                and self.kv_lora == 512 and self.rope == 64 and self.kv_b_proj.bias is None)
+
+    def _forward_absorbed(self, x, h, batch, kv, max_pos):
+        """Attention over one shared cache row per token ([normed latent | rotary key], 576 values):
+        q_nope goes through W_UK first (a batched product per head), the kernel returns sums of latent rows,
+        W_UV is applied to them afterwards.  Prefill rows are flattened: every new token is a row with its own
+        visible length."""
+        T = x.shape[0]
+        nh, nope, vd = self.nh, self.nope, self.vd
+        if self.q_lora:
+            q = self.q_b_proj(self.q_a_layernorm(self.q_a_proj(x)))
+        else:
+            q = self.q_proj(x)
+        q = q.view(T, nh, self.qk)
+        kva = self.kv_a_proj_with_mqa(x)
+        cache = kv[0]
+        if cache.dtype != x.dtype or cache.shape[-1] != self.kv_lora + self.rope:
+            raise RuntimeError("absorbed multi-head latent attention needs a 16-bit cache of 576-value rows; "
+                               "set FI_MLA_ABSORBED=0 for quantised KV caches")
+        w = self.kv_b_proj.weight.view(nh, nope + vd, self.kv_lora)
+        q_lat = torch.bmm(q[..., :nope].transpose(0, 1), w[:, :nope, :])          # [nh, T, 512]
+        q_cat = torch.empty(T, nh, self.kv_lora + self.rope, dtype=x.dtype, device=x.device)
+        lib = _lib.kernels()
+        dt = ops._DT[x.dtype]
+        rc = lib.fi_mla_prepare(_p(kva), kva.stride(0), _p(self.kv_a_layernorm.weight), self.kv_a_layernorm.eps, _p(q),
+                                nope, _p(q_lat), q_lat.stride(0), q_lat.stride(1), _p(batch.positions),
+                                _p(self.cos_sin(x.device, max_pos)), _p(batch.slot_mapping), _p(cache), _p(q_cat), T, nh,
+                                dt, _stream())
+        _lib.check(rc, "fi_mla_prepare")
+        if batch.is_decode:
+            rows, row_lens, seq_of_row = T, batch.seq_lens, None
+        else:
+            rows = T
+            row_lens = (batch.positions + 1).to(torch.int32)
+            ar = torch.arange(T, device=x.device, dtype=batch.cu_q.dtype)
+            seq_of_row = torch.searchsorted(batch.cu_q[1:].contiguous(), ar, right=True).to(torch.int32)
+        bs = cache.shape[2]
+        chunks = max(1, (int(batch.max_kv_len) + 63) // 64)
+        ctas = max(1, rows * ((nh + 15) // 16))
+        splits = int(max(1, min((2 * 148 + ctas - 1) // ctas, chunks, 16)))
+        ws_o = ws_ml = None
+        if splits > 1:
+            n_o = rows * nh * splits * self.kv_lora
+            ws = scratch("mla_ws", (n_o + rows * nh * splits * 2) * 4, x.device).view(torch.float32)
+            ws_o, ws_ml = ws[:n_o], ws[n_o:]
+        out_lat = torch.empty(nh, T, self.kv_lora, dtype=x.dtype, device=x.device)
+        rc = lib.fi_mla_decode(_p(q_cat), _p(cache), _p(out_lat), out_lat.stride(0), out_lat.stride(1),
+                               _p(batch.block_tables), _p(row_lens), _p(seq_of_row), _p(ws_o), _p(ws_ml), rows, nh,
+                               batch.block_tables.shape[1], bs, splits, self.sm_scale, dt, _stream())
+        _lib.check(rc, "fi_mla_decode")
+        _count(3 if splits > 1 else 2)
+        o = torch.bmm(out_lat, w[:, nope:, :].transpose(1, 2))                      # [nh, T, vd]
+        return self.o_proj(o.transpose(0, 1).reshape(T, nh * vd), residual=h, out=h)
 
     def cos_sin(self, device, max_pos):
         if self._cos_sin is None or self._cos_sin.device != device:
@@ -76,6 +139,8 @@ class MLAAttention(nn.Module):
         return self._cos_sin
 
     def forward(self, x, h, batch, kv, max_pos):
+        if self.absorbed and x.is_cuda:
+            return self._forward_absorbed(x, h, batch, kv, max_pos)
         T = x.shape[0]
         if self.q_lora:
             q = self.q_b_proj(self.q_a_layernorm(self.q_a_proj(x)))
@@ -325,6 +390,20 @@ class DeepseekMLAForCausalLM(nn.Module):
         self.max_pos = max(mc.max_model_len, 16)
 
     def kv_cache_specs(self):
+        """Called once the weights are in.  With dense 16-bit kv_b projections on a GPU the attention runs in
+        absorbed form on one shared [latent | rotary key] row per token (576 values, no V pool); otherwise
+        per-head K and V rows padded to 256 channels."""
+        from ..engine.kv_cache import KVLayerSpec
+        for l in self.layers:
+            qm = getattr(l.self_attn.kv_b_proj, "quant_method", None)
+            if qm is not None and hasattr(qm, "process_weights_after_loading"):
+                qm.process_weights_after_loading(l.self_attn.kv_b_proj)
+        absorb = _ABSORBED and all(l.self_attn.can_absorb() for l in self.layers)
+        for l in self.layers:
+            l.self_attn.absorbed = absorb
+        if absorb:
+            a = self.layers[0].self_attn
+            return [KVLayerSpec(1, a.kv_lora + a.rope, 0) for _ in self.layers]
         return [(l.self_attn.nh, PAD_HD) for l in self.layers]
 
     def forward(self, batch, kv_caches, inputs_embeds=None):

@@ -79,6 +79,9 @@ PRESETS["tiny-deepseek-test"] = dict(PRESETS["deepseek-mla-moe"], hidden_size=25
                                      qk_rope_head_dim=64, qk_nope_head_dim=64, v_head_dim=64, intermediate_size=256,
                                      moe_intermediate_size=256, n_routed_experts=8, num_experts_per_tok=2,
                                      vocab_size=512, max_position_embeddings=512)
+# the latent geometry of the full-size model (512 + 64) with 20 heads: exercises the absorbed attention kernel
+PRESETS["tiny-deepseek-mla512-test"] = dict(PRESETS["tiny-deepseek-test"], num_attention_heads=20, num_key_value_heads=20,
+                                            kv_lora_rank=512, qk_nope_head_dim=128, v_head_dim=128)
 PRESETS["tiny-qwen35-test"] = {
     "architectures": ["Qwen3_5ForCausalLM"], "model_type": "qwen3_5", "hidden_size": 256, "num_hidden_layers": 4,
     "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 256, "vocab_size": 512,

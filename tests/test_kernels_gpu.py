@@ -739,3 +739,41 @@ def test_select_blocks_kernel_and_sparse_decode():
     yr = ref.paged_attention(q, kc, vc, tab, sel_len, cu, nh, nkv, hd, scale, 0, 0.0, 1.0, 1.0, out_dtype=torch.float32)
     _close(y, yr, 2e-2, 2e-2, "sparse decode over the compact table")
     assert sel_len.tolist()[2] < lens[2] // 2
+
+
+@pytest.mark.parametrize("nh,splits", [(20, 1), (64, 1), (16, 3), (40, 5)])
+def test_mla_absorbed_decode_kernel(nh, splits):
+    """The latent-space attention kernel (576-value cache rows shared by all heads, the first 512 values are
+    also the value) against fp32 PyTorch: several 64-row chunks, ragged lengths, head counts that do not fill
+    a 16-row tile, one launch and split launches with the merge, rows that share a block table."""
+    from litevllm_b200.ops import _lib, _p, _stream
+    torch.manual_seed(nh + splits)
+    dev = torch.device(DEV, 0)
+    bs, nb, KD, VD = 16, 100, 576, 512
+    lens = [1, 70, 300, 129, 64]
+    seq_of_row = [0, 1, 2, 2, 3]                 # rows 2 and 3 read the same sequence with different lengths
+    max_blocks = 20
+    cache = (torch.randn(nb, 1, bs, KD, device=dev) * 0.5).bfloat16()
+    bt = torch.zeros(4, max_blocks, dtype=torch.int32, device=dev)
+    perm = torch.randperm(nb - 1, device=dev)[: 4 * max_blocks].view(4, max_blocks) + 1
+    bt.copy_(perm.to(torch.int32))
+    rows = len(lens)
+    q = (torch.randn(rows, nh, KD, device=dev) * 0.3).bfloat16()
+    row_lens = torch.tensor(lens, dtype=torch.int32, device=dev)
+    sor = torch.tensor(seq_of_row, dtype=torch.int32, device=dev)
+    out = torch.zeros(nh, rows, VD, dtype=torch.bfloat16, device=dev)
+    ws_o = torch.empty(rows * nh * splits * VD, dtype=torch.float32, device=dev) if splits > 1 else None
+    ws_ml = torch.empty(rows * nh * splits * 2, dtype=torch.float32, device=dev) if splits > 1 else None
+    scale = 192 ** -0.5
+    rc = _lib.kernels().fi_mla_decode(_p(q), _p(cache), _p(out), out.stride(0), out.stride(1), _p(bt), _p(row_lens),
+                                      _p(sor), _p(ws_o), _p(ws_ml), rows, nh, max_blocks, bs, splits, scale, 0, _stream())
+    assert rc == 0
+    torch.cuda.synchronize()
+    flat = cache.view(nb * bs, KD).float()
+    for r in range(rows):
+        idx = torch.tensor([int(bt[seq_of_row[r], t // bs]) * bs + t % bs for t in range(lens[r])], device=dev)
+        k = flat[idx]
+        p = torch.softmax(q[r].float() @ k.t() * scale, dim=-1)
+        want = p @ k[:, :VD]
+        got = out[:, r].float()
+        assert (got - want).abs().max().item() < 0.02 * max(1.0, want.abs().max().item()), (r, nh, splits)
