@@ -16,9 +16,11 @@
 //                       through ldmatrix.trans, as V for the output (each warp 128 of the 512 latent
 //                       channels over all 64 tokens; P goes through shared memory once per chunk).
 //   mla_merge_kernel    combines the split partials.
-// A "row" is a (sequence, query token): decode batches have one row per sequence; prefill rows carry their
-// own visible length and point at their sequence's block table (seq_of_row), the same flattening the
-// reference uses for its prefill (vllm/engine/lite_engine.py:53-104).
+//   mla_ctx_to_pool_kernel  prefill: up-projected context rows -> padded per-head K/V rows of a temporary pool
+// A "row" is a (sequence, query token): decode batches have one row per sequence; rows may also carry their
+// own visible length and point at their sequence's block table (seq_of_row), the flattening the reference
+// uses for its prefill (vllm/engine/lite_engine.py:53-104).  The model itself prefills in the per-head form
+// on a temporary pool (many query rows per sequence amortise a K/V tile there).
 // The reference keeps per-head K/V for this model family; the absorbed form follows the DeepSeek-V2 paper.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -346,9 +348,61 @@ __global__ void mla_prepare_kernel(const T* __restrict__ kva, long ldkva, const 
   }
 }
 
+// Prefill runs in the per-head form on a temporary paged K/V pool: row i of the batch's context (prefix +
+// new tokens, gathered from the latent cache) becomes, for every head, the key [rotary key | no-position
+// key | 0] and the value [value | 0], padded to `pad` channels, at slot slots[i] of pools shaped
+// [blocks, nh, block_size, pad].  ctx: [Tc, 576] latent rows; kvb: [Tc, nh, nope + vd] up-projected rows.
+template <typename T>
+__global__ void mla_ctx_to_pool_kernel(const T* __restrict__ ctx, const T* __restrict__ kvb,
+                                       const int* __restrict__ slots, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                       int nh, int nope, int vd, int pad, int block_size) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y * (blockDim.x >> 5) + warp;
+  if (h >= nh) return;
+  const int slot = slots[t];
+  if (slot < 0) return;
+  const long row = (static_cast<long>(slot / block_size) * nh + h) * block_size + slot % block_size;
+  uint4* kd = reinterpret_cast<uint4*>(k_pool + row * pad);
+  uint4* vdst = reinterpret_cast<uint4*>(v_pool + row * pad);
+  const T* kr = ctx + static_cast<long>(t) * KD + VD;
+  const T* kh = kvb + (static_cast<long>(t) * nh + h) * (nope + vd);
+  for (int c = lane; c < pad / 8; c += 32) {
+    const int i = c * 8;
+    uint4 kv4 = make_uint4(0, 0, 0, 0), vv4 = make_uint4(0, 0, 0, 0);
+    if (i < ROT) kv4 = *reinterpret_cast<const uint4*>(kr + i);
+    else if (i < ROT + nope) kv4 = *reinterpret_cast<const uint4*>(kh + i - ROT);
+    if (i < vd) vv4 = *reinterpret_cast<const uint4*>(kh + nope + i);
+    kd[c] = kv4;
+    vdst[c] = vv4;
+  }
+}
+
 }  // namespace
 
 #define FI_STREAM(s) reinterpret_cast<cudaStream_t>(s)
+
+extern "C" int fi_mla_ctx_to_pool(const void* ctx, const void* kvb, const int* slots, void* k_pool, void* v_pool,
+                                  int Tc, int nh, int nope, int vd, int pad, int block_size, int dtype, void* stream) {
+  if (Tc <= 0) return 0;
+  if ((nope | vd | pad) % 8 != 0 || ROT + nope > pad || vd > pad || block_size <= 0) return -10;
+  if ((reinterpret_cast<uintptr_t>(ctx) | reinterpret_cast<uintptr_t>(kvb) | reinterpret_cast<uintptr_t>(k_pool) |
+       reinterpret_cast<uintptr_t>(v_pool)) & 15)
+    return -10;
+  const dim3 grid(Tc, (nh + 7) / 8);
+  if (dtype == 0)
+    fi::launch_kernel(mla_ctx_to_pool_kernel<__nv_bfloat16>, grid, dim3(256), 0, FI_STREAM(stream), 0,
+                      (const __nv_bfloat16*)ctx, (const __nv_bfloat16*)kvb, slots, (__nv_bfloat16*)k_pool,
+                      (__nv_bfloat16*)v_pool, nh, nope, vd, pad, block_size);
+  else if (dtype == 1)
+    fi::launch_kernel(mla_ctx_to_pool_kernel<__half>, grid, dim3(256), 0, FI_STREAM(stream), 0, (const __half*)ctx,
+                      (const __half*)kvb, slots, (__half*)k_pool, (__half*)v_pool, nh, nope, vd, pad, block_size);
+  else
+    return -11;
+  return static_cast<int>(cudaGetLastError());
+}
 
 // dtype: 0 bf16, 1 fp16.  The rotary width is 64 and the latent width 512 (the cache row is 576 values).
 extern "C" int fi_mla_prepare(const void* kva, long ldkva, const void* norm_w, float eps, const void* q, int nope,

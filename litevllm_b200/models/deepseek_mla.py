@@ -40,6 +40,7 @@ _Q8 = os.environ.get("FI_GGUF_MOE_Q8", "1") != "0"
 # Multi-head latent attention in absorbed form (one 576-value cache row per token instead of per-head K and V):
 # on when the kv_b projections are dense 16-bit matrices on a GPU; FI_MLA_ABSORBED=0 keeps the materialised form.
 _ABSORBED = os.environ.get("FI_MLA_ABSORBED", "1") != "0"
+_MATERIALISED_MAX_TOKENS = 8192
 
 PAD_HD = 256
 
@@ -108,13 +109,9 @@ class MLAAttention(nn.Module):
                                 _p(self.cos_sin(x.device, max_pos)), _p(batch.slot_mapping), _p(cache), _p(q_cat), T, nh,
                                 dt, _stream())
         _lib.check(rc, "fi_mla_prepare")
-        if batch.is_decode:
-            rows, row_lens, seq_of_row = T, batch.seq_lens, None
-        else:
-            rows = T
-            row_lens = (batch.positions + 1).to(torch.int32)
-            ar = torch.arange(T, device=x.device, dtype=batch.cu_q.dtype)
-            seq_of_row = torch.searchsorted(batch.cu_q[1:].contiguous(), ar, right=True).to(torch.int32)
+        if not batch.is_decode:
+            return self._prefill_from_latent(x, h, batch, q, q_cat, cache)
+        rows, row_lens, seq_of_row = T, batch.seq_lens, None
         bs = cache.shape[2]
         chunks = max(1, (int(batch.max_kv_len) + 63) // 64)
         ctas = max(1, rows * ((nh + 15) // 16))
@@ -133,6 +130,48 @@ class MLAAttention(nn.Module):
         o = torch.bmm(out_lat, w[:, nope:, :].transpose(1, 2))                      # [nh, T, vd]
         return self.o_proj(o.transpose(0, 1).reshape(T, nh * vd), residual=h, out=h)
 
+    def _prefill_from_latent(self, x, h, batch, q, q_cat, cache):
+        """Prefill of the absorbed form: many query rows per sequence make the per-head form the efficient
+        one, so the context of every sequence of the batch (cached prefix + the rows just written) is gathered
+        from the latent cache, up-projected through kv_b, laid out as padded per-head K/V rows in a temporary
+        paged pool with consecutive blocks, and the ordinary varlen prefill kernel runs on that pool."""
+        T = x.shape[0]
+        nh, nope, vd, rope = self.nh, self.nope, self.vd, self.rope
+        dev, dt = x.device, x.dtype
+        B = batch.seq_lens.shape[0]
+        bs = cache.shape[2]
+        lens = batch.seq_lens.to(torch.int64)
+        blocks_per = (lens + bs - 1) // bs
+        blk0 = torch.cumsum(blocks_per, 0) - blocks_per                       # first temporary block of every sequence
+        cu = torch.cumsum(lens, 0)
+        Tc = int(sum(batch.seq_lens_cpu)) if batch.seq_lens_cpu else int(cu[-1].item())
+        n_tmp = int(sum((n + bs - 1) // bs for n in batch.seq_lens_cpu)) if batch.seq_lens_cpu else int(blocks_per.sum().item())
+        idx = torch.arange(Tc, device=dev)
+        seq = torch.searchsorted(cu, idx, right=True)
+        pos = idx - (cu - lens)[seq]
+        src_blk = batch.block_tables.to(torch.int64)[seq, pos // bs]
+        ctx = cache.view(-1, self.kv_lora + rope)[src_blk * bs + pos % bs]     # [Tc, 576]: normed latent | rotated key
+        kvb = self.kv_b_proj(ctx[:, : self.kv_lora].contiguous())              # [Tc, nh * (nope + vd)]
+        tmp_slots = ((blk0[seq] + pos // bs) * bs + pos % bs).to(torch.int32)
+        pools = scratch("mla_tmp_pool", 2 * n_tmp * nh * bs * PAD_HD * x.element_size() + 512, dev)
+        half = n_tmp * nh * bs * PAD_HD * x.element_size()
+        k_pool = pools[:half].view(dt).view(n_tmp, nh, bs, PAD_HD)
+        v_pool = pools[half:2 * half].view(dt).view(n_tmp, nh, bs, PAD_HD)
+        lib = _lib.kernels()
+        rc = lib.fi_mla_ctx_to_pool(_p(ctx), _p(kvb), _p(tmp_slots), _p(k_pool), _p(v_pool), Tc, nh, nope, vd, PAD_HD, bs,
+                                    ops._DT[dt], _stream())
+        _lib.check(rc, "fi_mla_ctx_to_pool")
+        _count()
+        max_b = int(max((n + bs - 1) // bs for n in batch.seq_lens_cpu)) if batch.seq_lens_cpu else int(blocks_per.max().item())
+        tmp_bt = (blk0[:, None] + torch.arange(max_b, device=dev)[None, :]).clamp_(max=max(n_tmp - 1, 0)).to(torch.int32)
+        q_pad = torch.zeros(T, nh, PAD_HD, dtype=dt, device=dev)
+        q_pad[..., :rope] = q_cat[..., self.kv_lora:]
+        q_pad[..., rope:rope + nope] = q[..., :nope]
+        attn = ops.paged_attention_prefill(q_pad.view(T, nh * PAD_HD), k_pool, v_pool, tmp_bt, batch.seq_lens, batch.cu_q,
+                                           batch.max_q_len, nh, nh, PAD_HD, self.sm_scale, 0, 0.0, 1.0, 1.0)
+        o_in = attn.view(T, nh, PAD_HD)[..., :vd].reshape(T, nh * vd)
+        return self.o_proj(o_in, residual=h, out=h)
+
     def cos_sin(self, device, max_pos):
         if self._cos_sin is None or self._cos_sin.device != device:
             self._cos_sin = get_cos_sin(self.rope, max_pos, self.rope_theta, None, device)
@@ -142,6 +181,11 @@ class MLAAttention(nn.Module):
         if self.absorbed and x.is_cuda:
             return self._forward_absorbed(x, h, batch, kv, max_pos)
         T = x.shape[0]
+        if x.is_cuda and T > _MATERIALISED_MAX_TOKENS:
+            # one prefill step of 16,000 tokens in this form ended in an illegal-address report on a B200 and the
+            # cause has not been found; steps of up to 3,072 tokens are covered by tests
+            raise RuntimeError(f"the materialised attention form takes at most {_MATERIALISED_MAX_TOKENS} tokens per "
+                               f"step (got {T}): lower max_num_batched_tokens or use the absorbed form")
         if self.q_lora:
             q = self.q_b_proj(self.q_a_layernorm(self.q_a_proj(x)))
         else:
