@@ -41,6 +41,9 @@ _Q8 = os.environ.get("FI_GGUF_MOE_Q8", "1") != "0"
 # on when the kv_b projections are dense 16-bit matrices on a GPU; FI_MLA_ABSORBED=0 keeps the materialised form.
 _ABSORBED = os.environ.get("FI_MLA_ABSORBED", "1") != "0"
 _MATERIALISED_MAX_TOKENS = 8192
+# Routed experts: from this many routes per local expert (on average) a step dequantises every expert with work
+# once and applies it with the tensor-core GEMM instead of streaming its blocks once per group of 8 routes.
+_DENSE_EXPERT_ROUTES = int(os.environ.get("FI_GGUF_MOE_DENSE_ROUTES", "64"))
 
 PAD_HD = 256
 
@@ -293,6 +296,8 @@ class RoutedExperts(nn.Module):
             e_hi = self.e_lo + self.e_local
             ids_flat = ids.reshape(-1)
             slot_of = None
+            if n >= _DENSE_EXPERT_ROUTES * self.e_local and self.clamp <= 0 and x.dtype in (torch.bfloat16, torch.float16):
+                return self._forward_tensor_core(x, ids_flat, weights, a, y, T, K, H)
             same_gu = self.types["gate"] == self.types["up"]
             # int8 activations + dp4a for the 2-bit formats; 16-bit activations for the others
             q8 = _Q8 and x.dtype == torch.bfloat16 and same_gu and self.types["gate"] in (10, 16) \
@@ -366,6 +371,57 @@ class RoutedExperts(nn.Module):
             rc = lib.fi_moe_combine(_p(y), _p(slot_of), _p(weights), None, _p(out), T, K, H, ops._DT[x.dtype], _stream())
             _lib.check(rc, "fi_moe_combine")
             _count(3)
+        if pstate.ep_size() > 1:
+            from ..parallel import fused_ops
+            out = fused_ops.all_reduce_activations(out)
+        return out
+
+
+    def _forward_tensor_core(self, x, ids_flat, weights, a, y, T, K, H):
+        """Large prefill steps (on average dozens of routes per expert): the routes are sorted by expert, the
+        activation rows gathered in that order, and every expert with work is dequantised into a 16-bit scratch
+        matrix and applied with the tcgen05 GEMM (gate|up, SiLU * up, down).  Streaming the 2-bit blocks once per
+        group of 8 routes (the GEMV-style kernels) costs a pass over the expert per group; here an expert is
+        decoded once per step.  One host read of the per-expert route counts per layer."""
+        lib = _lib.kernels()
+        n = T * K
+        dev, dt = x.device, x.dtype
+        ints = scratch("ds_moe_ints", (2 * n + self.e_local + 1 + 3 * (n // 128 + self.e_local) + 8) * 4, dev).view(torch.int32)
+        mt = n // 128 + self.e_local
+        o = 0
+        sorted_route = ints[o:o + n]; o += n
+        slot_of = ints[o:o + n]; o += n
+        offsets = ints[o:o + self.e_local + 1]; o += self.e_local + 1
+        tile_expert = ints[o:o + mt]; o += mt
+        tile_row0 = ints[o:o + mt]; o += mt
+        tile_rows = ints[o:o + mt]; o += mt
+        n_tiles = ints[o:o + 1]
+        rc = lib.fi_moe_align(_p(ids_flat), n, self.e_lo, self.e_lo + self.e_local, 128, _p(sorted_route), _p(slot_of),
+                              _p(offsets), _p(tile_expert), _p(tile_row0), _p(tile_rows), _p(n_tiles), _stream())
+        _lib.check(rc, "fi_moe_align")
+        xs = scratch("ds_moe_xs", n * H * x.element_size() + 256, dev)[: n * H * x.element_size()].view(dt).view(n, H)
+        rc = lib.fi_moe_gather(_p(x), _p(sorted_route), _p(offsets), self.e_local, n, K, H, _p(xs), ops._DT[dt], _stream())
+        _lib.check(rc, "fi_moe_gather")
+        off = offsets.tolist()
+        I = self.I
+        wgu = scratch("ds_moe_wgu", 2 * I * H * 2 + 256, dev)[: 2 * I * H * 2].view(dt).view(2 * I, H)
+        wd = scratch("ds_moe_wd", H * I * 2 + 256, dev)[: H * I * 2].view(dt).view(H, I)
+        gu = scratch("ds_moe_gu", max(off[e + 1] - off[e] for e in range(self.e_local)) * 2 * I * 2 + 256, dev)
+        for e in range(self.e_local):
+            r0, r1 = off[e], off[e + 1]
+            if r1 <= r0:
+                continue
+            gq.dequantize_cuda(self.raw["gate"][e], self.types["gate"], H, dt, out=wgu[:I])
+            gq.dequantize_cuda(self.raw["up"][e], self.types["up"], H, dt, out=wgu[I:])
+            g = gu[: (r1 - r0) * 2 * I * 2].view(dt).view(r1 - r0, 2 * I)
+            ops.linear(xs[r0:r1], wgu, out=g, static_weight=False)
+            ops.act_mul(g, "silu", out=a[r0:r1])
+            gq.dequantize_cuda(self.raw["down"][e], self.types["down"], I, dt, out=wd)
+            ops.linear(a[r0:r1], wd, out=y[r0:r1], static_weight=False)
+        out = torch.empty(T, H, dtype=dt, device=dev)
+        rc = lib.fi_moe_combine(_p(y), _p(slot_of), _p(weights), None, _p(out), T, K, H, ops._DT[dt], _stream())
+        _lib.check(rc, "fi_moe_combine")
+        _count(3)
         if pstate.ep_size() > 1:
             from ..parallel import fused_ops
             out = fused_ops.all_reduce_activations(out)

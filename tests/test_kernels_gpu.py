@@ -681,6 +681,11 @@ def test_gguf_routed_experts_grouped_and_per_route(tg, td, T):
             outs[mode] = ex(x, ids, w).float()
         dm._Q8, dm._GROUPED = True, "auto"
         outs["q8"] = ex(x, ids, w).float()       # int8 activations (the 2-bit formats; Q8_0 keeps the float path)
+        dense_saved, dm._DENSE_EXPERT_ROUTES = dm._DENSE_EXPERT_ROUTES, 1
+        try:
+            outs["tensor_core"] = ex(x, ids, w).float()     # every expert dequantised once, tcgen05 GEMMs
+        finally:
+            dm._DENSE_EXPERT_ROUTES = dense_saved
     finally:
         dm._GROUPED, dm._Q8 = saved
     torch.cuda.synchronize()
