@@ -298,7 +298,7 @@ __global__ void mla_merge_kernel(const MlaParams p) {
   }
 }
 
-// One CTA per token.  kva: [T, 576] = [latent | shared rotary key] with row pitch ldkva; q: [T, nh, nope +
+// One CTA per token, or several that split the token's heads when there are few tokens.  kva: [T, 576] = [latent | shared rotary key] with row pitch ldkva; q: [T, nh, nope +
 // 64] (rotary part last) ; q_lat element (t, h, d) at q_lat + h * ql_head_stride + t * ql_row_stride + d.
 // cos_sin: fp32 [max_pos, 64] = [cos(32) | sin(32)], rotation pairs (i, i + 32).
 template <typename T>
@@ -316,27 +316,29 @@ __global__ void mla_prepare_kernel(const T* __restrict__ kva, long ldkva, const 
   const float* cs = cos_sin + static_cast<long>(pos) * ROT;
   const int slot = slot_mapping ? slot_mapping[t] : -1;
   const T* row = kva + static_cast<long>(t) * ldkva;
-  // RMSNorm of the latent
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < VD; i += blockDim.x) { const float f = Mma<T>::to_f(row[i]); ss += f * f; }
-  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  if (lane == 0) red[warp] = ss;
-  __syncthreads();
-  float tot = 0.f;
-  for (int w = 0; w < nwarps; ++w) tot += red[w];
-  const float inv = rsqrtf(tot / static_cast<float>(VD) + eps);
-  if (slot >= 0) {
-    T* dst = cache + static_cast<long>(slot) * KD;
-    for (int i = threadIdx.x; i < VD; i += blockDim.x)
-      dst[i] = Mma<T>::from_f(Mma<T>::to_f(Mma<T>::from_f(Mma<T>::to_f(row[i]) * inv)) * Mma<T>::to_f(norm_w[i]));
-    for (int i = threadIdx.x; i < ROT / 2; i += blockDim.x) {
-      const float a = Mma<T>::to_f(row[VD + i]), b = Mma<T>::to_f(row[VD + i + ROT / 2]);
-      dst[VD + i] = Mma<T>::from_f(a * cs[i] - b * cs[ROT / 2 + i]);
-      dst[VD + i + ROT / 2] = Mma<T>::from_f(b * cs[i] + a * cs[ROT / 2 + i]);
+  if (blockIdx.y == 0) {
+    // RMSNorm of the latent + rotary of the shared key -> cache row (the first CTA of the token)
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < VD; i += blockDim.x) { const float f = Mma<T>::to_f(row[i]); ss += f * f; }
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int w = 0; w < nwarps; ++w) tot += red[w];
+    const float inv = rsqrtf(tot / static_cast<float>(VD) + eps);
+    if (slot >= 0) {
+      T* dst = cache + static_cast<long>(slot) * KD;
+      for (int i = threadIdx.x; i < VD; i += blockDim.x)
+        dst[i] = Mma<T>::from_f(Mma<T>::to_f(Mma<T>::from_f(Mma<T>::to_f(row[i]) * inv)) * Mma<T>::to_f(norm_w[i]));
+      for (int i = threadIdx.x; i < ROT / 2; i += blockDim.x) {
+        const float a = Mma<T>::to_f(row[VD + i]), b = Mma<T>::to_f(row[VD + i + ROT / 2]);
+        dst[VD + i] = Mma<T>::from_f(a * cs[i] - b * cs[ROT / 2 + i]);
+        dst[VD + i + ROT / 2] = Mma<T>::from_f(b * cs[i] + a * cs[ROT / 2 + i]);
+      }
     }
   }
-  // q_cat rows of this token: one warp per head
-  for (int h = warp; h < nh; h += nwarps) {
+  // q_cat rows of this token: one warp per head, the heads spread over gridDim.y CTAs
+  for (int h = blockIdx.y * nwarps + warp; h < nh; h += nwarps * gridDim.y) {
     T* dq = q_cat + (static_cast<long>(t) * nh + h) * KD;
     const T* ql = q_lat + h * ql_head_stride + t * ql_row_stride;
     for (int c = lane; c < VD / 8; c += 32)
@@ -412,13 +414,15 @@ extern "C" int fi_mla_prepare(const void* kva, long ldkva, const void* norm_w, f
   if (T <= 0) return 0;
   if (ldkva % 8 != 0 || ql_head_stride % 8 != 0 || ql_row_stride % 8 != 0 || nope < 0) return -10;
   if ((reinterpret_cast<uintptr_t>(q_lat) | reinterpret_cast<uintptr_t>(q_cat)) & 15) return -10;
+  // few tokens (decode): spread a token's heads over several CTAs
+  const dim3 grid(T, T >= 128 ? 1 : (nh + 7) / 8);
   if (dtype == 0)
-    fi::launch_kernel(mla_prepare_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, FI_STREAM(stream), 0,
+    fi::launch_kernel(mla_prepare_kernel<__nv_bfloat16>, grid, dim3(256), 0, FI_STREAM(stream), 0,
                       (const __nv_bfloat16*)kva, ldkva, (const __nv_bfloat16*)norm_w, eps, (const __nv_bfloat16*)q, nope,
                       (const __nv_bfloat16*)q_lat, ql_head_stride, ql_row_stride, positions, cos_sin, slot_mapping,
                       (__nv_bfloat16*)cache, (__nv_bfloat16*)q_cat, nh);
   else if (dtype == 1)
-    fi::launch_kernel(mla_prepare_kernel<__half>, dim3(T), dim3(256), 0, FI_STREAM(stream), 0, (const __half*)kva,
+    fi::launch_kernel(mla_prepare_kernel<__half>, grid, dim3(256), 0, FI_STREAM(stream), 0, (const __half*)kva,
                       ldkva, (const __half*)norm_w, eps, (const __half*)q, nope, (const __half*)q_lat, ql_head_stride,
                       ql_row_stride, positions, cos_sin, slot_mapping, (__half*)cache, (__half*)q_cat, nh);
   else

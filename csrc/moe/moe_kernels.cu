@@ -128,9 +128,20 @@ __global__ void moe_align_kernel(const int* __restrict__ topk_ids, int n_routes,
     if (e >= e_lo && e < e_hi) atomicAdd(&counts[e - e_lo], 1);
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int acc = 0, nt = 0;
-    for (int e = 0; e < EL; ++e) {
+  if (threadIdx.x < 32) {
+    // one warp: every lane owns a contiguous range of experts, the ranges are chained by a warp prefix sum
+    const int lane = threadIdx.x;
+    const int per = (EL + 31) / 32;
+    const int e0 = min(EL, lane * per), e1 = min(EL, e0 + per);
+    int rows = 0, tiles = 0;
+    for (int e = e0; e < e1; ++e) { rows += counts[e]; tiles += (counts[e] + bn - 1) / bn; }
+    int row_pre = rows, tile_pre = tiles;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int r = __shfl_up_sync(0xffffffffu, row_pre, o), t = __shfl_up_sync(0xffffffffu, tile_pre, o);
+      if (lane >= o) { row_pre += r; tile_pre += t; }
+    }
+    int acc = row_pre - rows, nt = tile_pre - tiles;
+    for (int e = e0; e < e1; ++e) {
       offs[e] = acc;
       for (int r = 0; r < counts[e]; r += bn) {
         tile_expert[nt] = e;
@@ -140,8 +151,10 @@ __global__ void moe_align_kernel(const int* __restrict__ topk_ids, int n_routes,
       }
       acc += counts[e];
     }
-    offs[EL] = acc;
-    *n_tiles = nt;
+    if (lane == 31) {
+      offs[EL] = row_pre;
+      *n_tiles = tile_pre;
+    }
   }
   __syncthreads();
   for (int i = threadIdx.x; i <= EL; i += blockDim.x) expert_offsets[i] = offs[i];
@@ -178,7 +191,7 @@ __global__ void moe_combine_kernel(const T* __restrict__ y_sorted, const int* __
   fi::pdl_launch_dependents();
   fi::pdl_wait();
   const int t = blockIdx.x;
-  for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < H / 8; c += blockDim.x * gridDim.y) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
@@ -386,11 +399,11 @@ extern "C" int fi_moe_combine(const void* y_sorted, const int* slot_of, const fl
   if (T <= 0) return 0;
   if (H % 8 != 0) return -10;
   if (dtype == 0)
-    fi::launch_kernel(moe_combine_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, FI_STREAM(stream), 0,
+    fi::launch_kernel(moe_combine_kernel<__nv_bfloat16>, dim3(T, T < 128 ? (H / 8 + 127) / 128 : 1), dim3(128), 0, FI_STREAM(stream), 0,
                       (const __nv_bfloat16*)y_sorted, slot_of, topk_w, (const __nv_bfloat16*)residual,
                       (__nv_bfloat16*)out, K, H);
   else
-    fi::launch_kernel(moe_combine_kernel<__half>, dim3(T), dim3(128), 0, FI_STREAM(stream), 0,
+    fi::launch_kernel(moe_combine_kernel<__half>, dim3(T, T < 128 ? (H / 8 + 127) / 128 : 1), dim3(128), 0, FI_STREAM(stream), 0,
                       (const __half*)y_sorted, slot_of, topk_w, (const __half*)residual, (__half*)out, K, H);
   return static_cast<int>(cudaGetLastError());
 }
