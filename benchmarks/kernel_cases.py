@@ -143,6 +143,31 @@ def main():
             (B * L * (nh + 2 * nkv) * hd + B * L * nh * hd) * 2, 4.0 * B * nh * L * L * hd / 2, \
             f"B={B} L={L} causal {nh}q/{nkv}kv hd={hd} page {bs}"
 
+    @case("gguf_moe_decode")
+    def _():
+        # routed experts of one DeepSeek-shaped layer at decode size: 8 tokens x top-6 over 256 experts,
+        # IQ2_XXS gate / up, Q2_K down (1.8 GB of expert blocks on the device; ~48 experts are touched per call)
+        import litevllm_b200.models.deepseek_mla as dm
+        from litevllm_b200.loaders.gguf import GGUFTensor
+        from litevllm_b200.models.arch import arch_from_hf_config
+        from litevllm_b200.models.presets import get_preset
+        arch = arch_from_hf_config(get_preset("deepseek-mla-moe"))
+        E, I, H, K = arch.moe.num_experts, arch.moe.expert_intermediate, arch.hidden_size, arch.moe.top_k
+        with torch.device(dev):
+            ex = dm.RoutedExperts(arch, bf)
+        ex.device = dev
+        for which, ty, rows, cols, seed in (("gate", 16, I, H, 1), ("up", 16, I, H, 2), ("down", 10, H, I, 3)):
+            raw = gq.random_blocks(ty, 8 * rows, cols, seed=seed, scale=0.05).to(dev)
+            raw = raw.repeat(E // 8, 1).view(E, rows, -1).contiguous()          # 8 distinct experts, tiled to 256
+            ex.raw[which], ex.types[which] = raw, ty
+        T = 8
+        x = rnd(T, H)
+        ids = torch.stack([torch.randperm(E, generator=g, device=dev)[:K] for _ in range(T)]).to(torch.int32)
+        w = torch.rand(T, K, generator=g, device=dev)
+        nbytes = T * K * (2 * I * H * 66 // 256 + H * I * 84 // 256)
+        return (lambda: ex(x, ids, w)), nbytes, 2.0 * T * K * 3 * I * H, \
+            f"T={T} top-{K} of {E} experts, H={H} I={I}, IQ2_XXS gate/up + Q2_K down, int8 activations (align + 2 kernels + combine)"
+
     @case("rmsnorm")
     def _():
         T, H = 65536, 4096                                # 537 MB in + out

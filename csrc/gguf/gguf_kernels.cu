@@ -23,8 +23,10 @@ __device__ __forceinline__ float h2f(const uint8_t* p) {
   return __half2float(__ushort_as_half(static_cast<unsigned short>(p[0] | (p[1] << 8))));
 }
 
-__constant__ uint64_t c_grid[256];
-__constant__ uint8_t c_signs[128];
+// The tables live in global memory: every CTA copies them into shared memory with one coalesced load per
+// thread (constant memory would serialise the 256 different addresses of that copy).
+__device__ uint64_t c_grid[256];
+__device__ uint8_t c_signs[128];
 bool g_tables_ready[64] = {false};
 
 int ensure_tables() {
@@ -634,7 +636,10 @@ __device__ __forceinline__ void row_dot_q8(const uint8_t* r, int K, const int8_t
 #pragma unroll
       for (int l = 0; l < 4; ++l) {
         const uint64_t g64 = tab.grid[(idx >> (8 * l)) & 255];
-        const uint32_t sg = tab.signs[(word >> (7 * l)) & 127];
+        // the sign table entry of a 7-bit index is the index itself plus its parity as bit 7 (an even number of
+        // minus signs per group of 8): two ALU instructions instead of a shared-memory lookup
+        const uint32_t s7 = (word >> (7 * l)) & 127u;
+        const uint32_t sg = s7 | ((__popc(s7) & 1u) << 7);
         const uint32_t m0 = sign_mask4(sg & 15), m1 = sign_mask4(sg >> 4);
         w[2 * l] = __vsub4(static_cast<uint32_t>(g64) ^ m0, m0);
         w[2 * l + 1] = __vsub4(static_cast<uint32_t>(g64 >> 32) ^ m1, m1);
@@ -642,7 +647,9 @@ __device__ __forceinline__ void row_dot_q8(const uint8_t* r, int K, const int8_t
 #pragma unroll
       for (int m = 0; m < MAXM; ++m) {
         if (m < M) {
-          const int* xw = reinterpret_cast<const int*>(xq + static_cast<size_t>(m) * K + v0);
+          const int4* xv = reinterpret_cast<const int4*>(xq + static_cast<size_t>(m) * K + v0);   // 32-byte aligned
+          const int4 x0 = xv[0], x1 = xv[1];
+          const int xw[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
           int sacc = 0;
 #pragma unroll
           for (int i = 0; i < 8; ++i) sacc = __dp4a(static_cast<int>(w[i]), xw[i], sacc);
@@ -661,7 +668,9 @@ __device__ __forceinline__ void row_dot_q8(const uint8_t* r, int K, const int8_t
 #pragma unroll
       for (int m = 0; m < MAXM; ++m) {
         if (m < M) {
-          const int* xw = reinterpret_cast<const int*>(xq + static_cast<size_t>(m) * K + v0);
+          const int4* xv = reinterpret_cast<const int4*>(xq + static_cast<size_t>(m) * K + v0);
+          const int4 x0 = xv[0], x1 = xv[1];
+          const int xw[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
           int s0 = 0, s1 = 0;
 #pragma unroll
           for (int i = 0; i < 4; ++i) s0 = __dp4a(static_cast<int>(w[i]), xw[i], s0);
@@ -681,6 +690,10 @@ __device__ __forceinline__ void row_dot_q8(const uint8_t* r, int K, const int8_t
 
 // Grouped gate|up and down with int8 activations (same tiling as the kernels above; MAXM = 1 serves decode
 // steps whose routes all hit different experts: fi_moe_align with tiles of one route).
+// rows per warp of the int8-activation kernels: twice the float kernels' count halves the CTAs and with them the
+// per-CTA set-up (activation quantisation, codebook copy)
+constexpr int kQ8Rows = 8;
+
 template <int TG, int TU, int MAXM, typename T>
 __global__ void moe_gate_up_q8_kernel(const T* __restrict__ x, long ldx, const uint8_t* __restrict__ gate,
                                       const uint8_t* __restrict__ up, long expert_stride_g, long expert_stride_u,
@@ -709,7 +722,7 @@ __global__ void moe_gate_up_q8_kernel(const T* __restrict__ x, long ldx, const u
   uint8_t* wb = gsm + ((ActQ8<MAXM>::bytes(K) + 15) & ~static_cast<size_t>(15)) + static_cast<size_t>(warp) * 2 * (bg + bu);
   const uint8_t* ge = gate + static_cast<long>(e) * expert_stride_g;
   const uint8_t* ue = up + static_cast<long>(e) * expert_stride_u;
-  auto row_of = [&](int rr) { return (blockIdx.x * kMoeRows + rr) * kMoeWarps + warp; };
+  auto row_of = [&](int rr) { return (blockIdx.x * kQ8Rows + rr) * kMoeWarps + warp; };
   const uint8_t* gd[2];
   const uint8_t* ud[2];
   auto fetch = [&](int rr) {
@@ -722,10 +735,10 @@ __global__ void moe_gate_up_q8_kernel(const T* __restrict__ x, long ldx, const u
     cp_async_commit();
   };
   fetch(0);
-  for (int rr = 0; rr < kMoeRows; ++rr) {
+  for (int rr = 0; rr < kQ8Rows; ++rr) {
     const int row = row_of(rr);
     if (row >= I) break;
-    if (rr + 1 < kMoeRows) fetch(rr + 1);
+    if (rr + 1 < kQ8Rows) fetch(rr + 1);
     else cp_async_commit();
     cp_async_wait<1>();
     __syncwarp();
@@ -772,7 +785,7 @@ __global__ void moe_down_q8_kernel(const T* __restrict__ a_sorted, const uint8_t
   const int bd = row_buf_bytes(TD, I);
   uint8_t* wb = gsm + ((ActQ8<MAXM>::bytes(I) + 15) & ~static_cast<size_t>(15)) + static_cast<size_t>(warp) * 2 * bd;
   const uint8_t* de = down + static_cast<long>(e) * expert_stride;
-  auto row_of = [&](int rr) { return (blockIdx.x * kMoeRows + rr) * kMoeWarps + warp; };
+  auto row_of = [&](int rr) { return (blockIdx.x * kQ8Rows + rr) * kMoeWarps + warp; };
   const uint8_t* dd[2];
   auto fetch = [&](int rr) {
     const int row = row_of(rr);
@@ -782,10 +795,10 @@ __global__ void moe_down_q8_kernel(const T* __restrict__ a_sorted, const uint8_t
     cp_async_commit();
   };
   fetch(0);
-  for (int rr = 0; rr < kMoeRows; ++rr) {
+  for (int rr = 0; rr < kQ8Rows; ++rr) {
     const int row = row_of(rr);
     if (row >= H) break;
-    if (rr + 1 < kMoeRows) fetch(rr + 1);
+    if (rr + 1 < kQ8Rows) fetch(rr + 1);
     else cp_async_commit();
     cp_async_wait<1>();
     __syncwarp();
@@ -994,7 +1007,7 @@ extern "C" int fi_gguf_moe_gate_up_q8(const void* x, long ldx, const void* gate,
   const size_t smem = ((act + 15) & ~static_cast<size_t>(15)) +
                       static_cast<size_t>(kMoeWarps) * 2 * (row_buf_bytes(type_g, K) + row_buf_bytes(type_u, K));
   if (smem > 200 * 1024) return -12;
-  const int rows_per_cta = kMoeWarps * kMoeRows;
+  const int rows_per_cta = kMoeWarps * kQ8Rows;
   const dim3 grid((I + rows_per_cta - 1) / rows_per_cta, max_tiles);
   const uint8_t* g = static_cast<const uint8_t*>(gate);
   const uint8_t* u = static_cast<const uint8_t*>(up);
@@ -1025,7 +1038,7 @@ extern "C" int fi_gguf_moe_down_q8(const void* a_sorted, const void* down, int t
   const size_t act = tile_m == 1 ? ActQ8<1>::bytes(I) : ActQ8<8>::bytes(I);
   const size_t smem = ((act + 15) & ~static_cast<size_t>(15)) + static_cast<size_t>(kMoeWarps) * 2 * row_buf_bytes(type_d, I);
   if (smem > 200 * 1024) return -12;
-  const int rows_per_cta = kMoeWarps * kMoeRows;
+  const int rows_per_cta = kMoeWarps * kQ8Rows;
   const dim3 grid((H + rows_per_cta - 1) / rows_per_cta, max_tiles);
   const uint8_t* d = static_cast<const uint8_t*>(down);
   const long sd = row_stride * H;
