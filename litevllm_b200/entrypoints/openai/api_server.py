@@ -108,8 +108,16 @@ def _render_chat_prompt(tokenizer, messages: list[dict]) -> str:
             return tmpl(messages, tokenize=False, add_generation_prompt=True)
         except Exception:
             pass
-    from ...transformers_utils.chat_templates import render_fallback
-    return render_fallback(messages)
+    # no usable template on the tokenizer: the registered fallback of the model type, then of the model family
+    from ...transformers_utils.chat_templates import get_chat_template_fallback, render_fallback, template_for_family
+    name = "plain"
+    try:
+        mc = engine.engine.vllm_config.model_config
+        path = get_chat_template_fallback(str((mc.hf_config or {}).get("model_type", "")), str(mc.tokenizer))
+        name = str(path) if path is not None else template_for_family(mc.arch.family)
+    except Exception:
+        pass
+    return render_fallback(messages, name)
 
 
 def _parse_structured(body: dict) -> StructuredOutputsParams | None:

@@ -164,3 +164,24 @@ def test_package_uses_no_foreign_kernel_backends():
     for f in (root / "litevllm_b200").rglob("*.py"):
         text = f.read_text()
         assert "import triton" not in text and "torch.compile(" not in text, f
+
+
+def test_chat_template_registry_and_jinja_fallbacks(tmp_path):
+    """Built-in jinja fallbacks (list-of-blocks content, generation prompt on and off), the model-type registry
+    with a callable choice, a registered custom template, and the sandbox refusing attribute tricks."""
+    import pytest
+    from litevllm_b200.transformers_utils import chat_templates as ct
+    msgs = [{"role": "user", "content": [{"type": "text", "text": "see "}, {"type": "image_url", "image_url": {"url": "u"}}]},
+            {"role": "assistant", "content": "ok"}]
+    assert ct.render_fallback(msgs, "chatml") == ("<|im_start|>user\nsee <image><|im_end|>\n<|im_start|>assistant\nok<|im_end|>\n"
+                                                   "<|im_start|>assistant\n")
+    assert ct.render_fallback(msgs, "gemma", add_generation_prompt=False).endswith("<start_of_turn>model\nok<end_of_turn>\n")
+    assert ct.get_chat_template_fallback("qwen", "Qwen-7B-Chat").name == "chatml.jinja"
+    assert ct.get_chat_template_fallback("qwen", "Qwen-7B").name == "plain.jinja"
+    assert ct.get_chat_template_fallback("unknown-type") is None
+    custom = tmp_path / "mine.jinja"
+    custom.write_text("{% for m in messages %}<{{ m['role'] }}>{{ m['content'] | text }}{% endfor %}")
+    ct.register_chat_template_fallback("my-model", custom)
+    assert ct.render_fallback(msgs, str(ct.get_chat_template_fallback("my-model"))) == "<user>see <image><assistant>ok"
+    with pytest.raises(Exception):
+        ct.render_template("{{ messages.__class__.__mro__ }}", msgs)
