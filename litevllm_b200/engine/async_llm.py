@@ -24,6 +24,23 @@ class AsyncLLM(EngineClient):
         self._parallel = None
         self.coordinator = None
         self.channel = None
+        self.dp_router = None         # rank 0 of a server with data-parallel replicas
+        self._dp_link = None          # this replica's mailbox (ranks other than 0)
+        self._dp = None
+        if engine is None and vllm_config.parallel_config.data_parallel_size > 1:
+            # replicas: every rank a whole engine on its own GPU; the process group only provides the store
+            import torch
+            import torch.distributed as dist
+            from ..parallel.data_parallel import DataParallelGroup
+            from ..parallel.dp_serving import DataParallelRouter, ReplicaLink
+            self._dp = DataParallelGroup(vllm_config.parallel_config.data_parallel_size)
+            if torch.cuda.is_available() and vllm_config.device in ("auto", "cuda"):
+                vllm_config.device = f"cuda:{self._dp.local_rank}"
+            store = dist.distributed_c10d._get_default_store()
+            if self._dp.rank == 0:
+                self.dp_router = DataParallelRouter(store, self._dp.size)
+            else:
+                self._dp_link = ReplicaLink(store, self._dp.rank)
         if engine is None and vllm_config.parallel_config.is_distributed:
             from ..parallel.launcher import init_distributed_engine
             from ..parallel.serving import ServingCoordinator, make_channel
@@ -55,14 +72,37 @@ class AsyncLLM(EngineClient):
     # ------------------------------------------------------------------ request path
     @property
     def is_worker_rank(self) -> bool:
+        if self._dp is not None:
+            return self._dp.rank != 0
         return self._parallel is not None and self._parallel.state.rank != 0
 
     def serve_as_worker(self, on_step=None) -> int:
-        """Worker ranks of a multi-rank server: mirror rank 0 until it shuts down."""
+        """Ranks other than 0 of a multi-rank server.  Tensor / expert parallel: mirror rank 0 step by step
+        until it shuts down.  Data parallel: serve the requests rank 0 routes to this replica."""
+        if self._dp_link is not None:
+            from ..parallel.dp_serving import replica_serve_loop
+            return replica_serve_loop(self.engine, self._dp_link, on_step=on_step)
         from ..parallel.serving import worker_serve_loop
         return worker_serve_loop(self.engine, self.channel, on_step)
 
     def _submit_sync(self, request_id, prompt, sampling_params, lora_request, multi_modal_data, loop):
+        if self.dp_router is not None:
+            replica = self.dp_router.choose()
+            if replica != 0:
+                if lora_request is not None or multi_modal_data:
+                    replica = 0       # adapters and images stay on the rank that received them
+                else:
+                    # validate and tokenise here, run there
+                    with self.engine_lock:
+                        self.engine._build_lazy()
+                        st = self.engine.request_builder.build(request_id, prompt, sampling_params, None, None)
+                        self.engine.adapter.validate_request(st.sampling_params, st.prompt_len, None, None)
+                    from ..parallel.serving import ServingCoordinator, sampling_params_to_wire
+                    sp = ServingCoordinator.prepare_params(st.sampling_params)
+                    self.dp_router.submit_remote(replica, request_id, list(st.prompt_token_ids),
+                                                 sampling_params_to_wire(sp), loop)
+                    return
+            self.dp_router.note_local(request_id)
         if self.coordinator is not None:
             self.coordinator.check_supported(lora_request, multi_modal_data)
             sampling_params = self.coordinator.prepare_params(sampling_params)
@@ -83,8 +123,10 @@ class AsyncLLM(EngineClient):
 
     async def stream(self, request_id: str):
         finished = False
+        remote = self.dp_router is not None and self.dp_router.is_remote(request_id)
+        source = self.dp_router.stream(request_id) if remote else self.engine.get_request_stream(request_id)
         try:
-            async for out in self.engine.get_request_stream(request_id):
+            async for out in source:
                 if getattr(out, "finished", False):
                     finished = True
                 yield out
@@ -92,6 +134,8 @@ class AsyncLLM(EngineClient):
             finished = True   # the stream already delivered its terminal item (an exception)
             raise
         finally:
+            if self.dp_router is not None and not remote:
+                self.dp_router.finish_local(request_id)
             if not finished:
                 await self.abort(request_id)
 
@@ -108,6 +152,8 @@ class AsyncLLM(EngineClient):
         def _do():
             with self.engine_lock:
                 for rid in ids:
+                    if self.dp_router is not None and self.dp_router.abort(rid):
+                        continue
                     if self.engine.abort_request(rid) and self.coordinator is not None:
                         self.coordinator.record_abort(rid)
         await asyncio.to_thread(_do)
@@ -120,6 +166,8 @@ class AsyncLLM(EngineClient):
         with self.engine_lock:
             s = self.engine.stats()
         s["async_driver"] = self.driver.stats()
+        if self.dp_router is not None:
+            s["data_parallel"] = self.dp_router.stats()
         return s
 
     def reset_stats(self, clear_prefix_cache: bool = False) -> None:
@@ -136,6 +184,8 @@ class AsyncLLM(EngineClient):
 
     def shutdown(self) -> None:
         self._closed = True
+        if self.dp_router is not None:
+            self.dp_router.shutdown()
         self.driver.shutdown()
         self.engine.shutdown()
         if self._parallel is not None:

@@ -313,17 +313,22 @@ def main(argv: list[str] | None = None) -> None:
     ap.add_argument("--dtype", default=None)
     ap.add_argument("--tensor-parallel-size", type=int, default=None)
     ap.add_argument("--expert-parallel-size", type=int, default=None)
+    ap.add_argument("--data-parallel-size", type=int, default=None,
+                    help="whole-engine replicas (one process per GPU under torchrun): rank 0 serves HTTP and routes "
+                         "every request to the replica with the fewest requests in flight")
     args = ap.parse_args(argv)
     kw = {k: v for k, v in dict(trust_remote_code=args.trust_remote_code, revision=args.revision,
                                 policy_mode=args.policy_mode, max_model_len=args.max_model_len,
                                 max_num_seqs=args.max_num_seqs, dtype=args.dtype,
                                 tensor_parallel_size=args.tensor_parallel_size,
-                                expert_parallel_size=args.expert_parallel_size).items() if v}
+                                expert_parallel_size=args.expert_parallel_size,
+                                data_parallel_size=args.data_parallel_size).items() if v}
     engine = build_engine(args.model, **kw)
     served_model = args.model
     debug_endpoints_enabled = args.enable_debug_endpoints
     if getattr(engine, "is_worker_rank", False):
         # launched with one process per GPU (torchrun): only rank 0 listens; the others mirror its engine
+        # (tensor / expert parallel) or serve the requests it routes to them (data parallel)
         engine.serve_as_worker()
         engine.shutdown()
         return
