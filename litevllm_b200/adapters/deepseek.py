@@ -1,7 +1,6 @@
-"""DeepSeek adapter (MLA + MoE, GGUF).  The reference's adapter for its V4-Flash data plane is
-greedy-only, batch 1, no LoRA, no multimodal and caps admission by a byte budget
-(vllm/adapters/deepseek_v4_flash.py:24-193); the generic MLA model here runs through the ordinary
-executors, so only the LoRA/multimodal restrictions remain."""
+"""DeepSeek adapter (MLA + MoE, GGUF): the generic MLA model runs through the ordinary executors, so only the
+LoRA / multimodal restrictions apply.  The V4-Flash checkpoint family, whose model owns its data plane, has
+its own adapter (``adapters/deepseek_v4_flash.py``)."""
 from ..engine.errors import InvalidRequestError
 from .base import ModelAdapter, ModelCapabilities, RuntimeModelPolicy
 

@@ -1,10 +1,10 @@
-"""Adapter selection, most specific first: DeepSeek -> Gemma4 -> Qwen2-VL -> Qwen3.5 -> Llama, else
+"""Adapter selection, most specific first: DeepSeek-V4-Flash -> DeepSeek -> Gemma4 -> Qwen2-VL -> Qwen3.5 -> Llama, else
 an error (reference: vllm/adapters/registry.py:123-140)."""
 from __future__ import annotations
 
 import importlib
 
-_ORDER = [("deepseek", "DeepSeekAdapter"), ("gemma4", "Gemma4Adapter"), ("qwen2_vl", "Qwen2VLAdapter"),
+_ORDER = [("deepseek_v4_flash", "DeepSeekV4FlashAdapter"), ("deepseek", "DeepSeekAdapter"), ("gemma4", "Gemma4Adapter"), ("qwen2_vl", "Qwen2VLAdapter"),
           ("qwen3_5", "Qwen35Adapter"), ("llama", "LlamaAdapter")]
 
 

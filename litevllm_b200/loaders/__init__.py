@@ -59,6 +59,8 @@ def synthetic_weights(vllm_config, device) -> Iterator[tuple[str, torch.Tensor]]
         return synth.iter_deepseek_weights(mc.arch, mc.seed, mc.dtype, gen_dev)
     if fam == "qwen3_5":
         return synth.iter_qwen35_weights(mc.arch, mc.seed, mc.dtype, gen_dev)
+    if fam == "deepseek_v4_flash":
+        return iter(())             # the model draws its own seeded weights when no tensor arrives
     raise ValueError(f"no synthetic weight stream for family {fam}")
 
 

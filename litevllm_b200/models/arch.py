@@ -131,6 +131,8 @@ def arch_from_hf_config(cfg: dict) -> ModelArch:
     model_type = str(text.get("model_type", cfg.get("model_type", ""))).lower()
     if "gemma4" in name or "gemma4" in model_type or "gemma3n" in name:
         family = "gemma4"
+    elif "deepseekv4" in name.replace("_", "") or "deepseek_v4" in model_type:
+        family = "deepseek_v4_flash"
     elif "deepseek" in name or "deepseek" in model_type:
         family = "deepseek_mla"
     elif "qwen3_5" in model_type or "qwen3_5" in name or "qwen3next" in name or "qwen3_next" in model_type:
@@ -202,6 +204,10 @@ def arch_from_hf_config(cfg: dict) -> ModelArch:
                            renormalize=bool(text.get("norm_topk_prob", True)),
                            routed_scaling=float(text.get("routed_scaling_factor", 1.0)),
                            first_dense_layers=int(text.get("first_k_dense_replace", 0)))
+    if family == "deepseek_v4_flash":
+        arch.extra["v4_rows"] = {k: text[k] for k in ("num_hidden_layers", "head_dim", "sliding_window",
+                                                      "compress_ratio_coarse", "layer_compress_ratios")
+                                 if text.get(k) is not None}
     if family == "qwen3_5":
         lt = text.get("layer_types") or []
         interval = int(text.get("full_attention_interval", 4))

@@ -1,0 +1,434 @@
+"""DeepSeek-V4-Flash: the model-owned data plane built from the blocks of this package.
+
+Unlike the other model families this one does not run through the paged KV cache and the batched
+executors: every request owns its latent rows (a sliding window per layer, plus compressed rows and indexer
+rows on the compressed layers) and the model returns token ids, not logits.  A prefill chunk or a decode
+batch goes through the layers as one group: projections, hyper-connections, router and experts are batched
+over the group's tokens; only the row appends, the compressor state machine and the attention walk the
+tokens in order.  One token through one layer:
+
+    hyper-connection pre (Sinkhorn-mixed streams -> layer input) -> RMSNorm -> q (low rank) and the shared
+    latent row (K = V) -> per-head RMS norm of q, rotary on the tail channels, fp8 round trip of the latent
+    -> append to the window -> shared-latent attention with sinks over [window rows | compressed rows emitted
+    by earlier tokens (fine layers: the indexer's top-k of them)] -> feed the compressor (and the indexer's
+    compressor), which emit one normed, rotated row every ``ratio`` tokens -> inverse rotary on the output tail -> grouped low-rank output projection -> hyper-connection
+    post -> RMSNorm -> router (token-id hash table on the first layers, sqrt-softplus top-k elsewhere) ->
+    routed experts (+ shared expert) on the Q8_K round-tripped input -> hyper-connection post
+
+and after the last layer: sigmoid-gated sum of the streams -> RMSNorm -> lm_head -> arg-max.
+
+Weights are dense tensors (fp32 on the CPU, the model dtype on a GPU); synthetic checkpoints draw them from
+a seeded generator.  The GGUF weight store, the expert staging LRU and the decode-graph experiments of the
+reference's data plane are not part of this model.
+Reference: vllm/model_executor/models/deepseek_v4_flash/model.py:249-304, 537-607, 933-1130
+(prefill_request / decode_tokens_batch / token steps), gpu_layers.py:684-926, 1247-1610 (layer forwards),
+compressed_kv.py:289-455 (row pools), kv_lifecycle.py (release).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+from torch import nn
+
+from .attention import CompressorState, compressor_step, indexer_scores, indexer_topk, shared_kv_attention
+from .hyper_connection import hyper_connection_post, hyper_connection_pre
+from .moe import hash_routed_expert_ids, sqrt_softplus_router
+from ...utils.profiling import stage
+from .ops import fp8_kv_qat, indexer_qat, q8_k_roundtrip
+
+
+@dataclass
+class V4Config:
+    hidden: int
+    layers: int
+    heads: int
+    head_dim: int            # width of a latent row (keys = values)
+    rotary_dim: int
+    q_lora: int
+    window: int
+    ratios: tuple            # per layer: 0 = sliding window only, 4 = compressor + indexer top-k, other = compressor
+    indexer_heads: int
+    indexer_topk: int
+    hc: int                  # hyper-connection streams
+    o_groups: int
+    o_lora: int
+    experts: int
+    top_k: int
+    expert_inter: int
+    shared_inter: int
+    hash_layers: int         # the first layers route by token id
+    routed_scale: float
+    vocab: int
+    eps: float
+    rope_theta: float
+    swiglu_clamp: float
+
+    @classmethod
+    def from_hf(cls, cfg: dict) -> "V4Config":
+        g = cfg.get
+        return cls(hidden=int(cfg["hidden_size"]), layers=int(cfg["num_hidden_layers"]),
+                   heads=int(cfg["num_attention_heads"]), head_dim=int(g("head_dim", 512)),
+                   rotary_dim=int(g("qk_rope_head_dim", 64)), q_lora=int(g("q_lora_rank", 1024)),
+                   window=int(g("sliding_window", 128)),
+                   ratios=tuple(int(r) for r in (g("layer_compress_ratios") or cls.default_ratios(
+                       int(cfg["num_hidden_layers"]), int(g("compress_ratio_coarse", 128))))),
+                   indexer_heads=int(g("index_n_heads", 4)), indexer_topk=int(g("index_topk", 512)),
+                   hc=int(g("hc_mult", 4)), o_groups=int(g("o_groups", 4)), o_lora=int(g("o_lora_rank", 256)),
+                   experts=int(g("n_routed_experts", 8)), top_k=int(g("num_experts_per_tok", 2)),
+                   expert_inter=int(g("moe_intermediate_size", 256)), shared_inter=int(g("shared_intermediate_size", g("moe_intermediate_size", 256))),
+                   hash_layers=int(g("num_hash_layers", 1)), routed_scale=float(g("routed_scaling_factor", 1.5)),
+                   vocab=int(cfg["vocab_size"]), eps=float(g("rms_norm_eps", 1e-6)),
+                   rope_theta=float(g("rope_theta", 10000.0)), swiglu_clamp=float(g("swiglu_limit", 0.0)))
+
+    @staticmethod
+    def default_ratios(layers: int, coarse: int = 128) -> list:
+        """The checkpoint family's pattern: the first two layers see the window only, then fine (ratio 4,
+        indexer-selected) and coarse (all rows) compressed layers alternate."""
+        return [0 if i < 2 else (4 if i % 2 == 0 else coarse) for i in range(layers)]
+
+
+@dataclass
+class LayerRows:
+    """One request's rows of one layer."""
+    window: torch.Tensor                       # [window, head_dim] ring buffer
+    count: int = 0                             # tokens seen
+    compressed: list = field(default_factory=list)        # emitted rows [head_dim]
+    index_rows: list = field(default_factory=list)        # emitted indexer rows [128]
+    comp_state: CompressorState | None = None
+    index_state: CompressorState | None = None
+    ratio: int = 0
+
+
+@dataclass
+class RequestRows:
+    layers: list
+    pos: int = 0
+
+    def bytes(self) -> int:
+        n = 0
+        for lr in self.layers:
+            n += lr.window.numel() * lr.window.element_size()
+            n += sum(r.numel() * 4 for r in lr.compressed) + sum(r.numel() * 4 for r in lr.index_rows)
+        return n
+
+
+def _rms(x: torch.Tensor, w: torch.Tensor | None, eps: float) -> torch.Tensor:
+    y = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + eps)
+    return y if w is None else y * w.float()
+
+
+def _lin(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x @ w.T`` in the weight's dtype (tensor cores for 16-bit weights on a GPU), fp32 result."""
+    return torch.nn.functional.linear(x.to(w.dtype), w).float()
+
+
+def _rotate_tail(x: torch.Tensor, pos: torch.Tensor, rot: int, theta: float, inverse: bool = False) -> torch.Tensor:
+    """Rotary embedding on the last ``rot`` channels (pairs (i, i + rot/2)) of ``[T, ..., D]`` at positions
+    ``pos`` ``[T]``; ``inverse`` rotates back."""
+    if rot == 0:
+        return x
+    half = rot // 2
+    inv_freq = theta ** (-torch.arange(half, dtype=torch.float32, device=x.device) / half)
+    ang = (-pos if inverse else pos).float().reshape(-1, *([1] * (x.dim() - 1))) * inv_freq
+    c, s = torch.cos(ang), torch.sin(ang)
+    head, tail = x[..., :-rot], x[..., -rot:]
+    a, b = tail[..., :half], tail[..., half:]
+    return torch.cat([head, a * c - b * s, b * c + a * s], dim=-1)
+
+
+class V4Layer(nn.Module):
+    def __init__(self, c: V4Config, i: int, dtype):
+        super().__init__()
+        H, D, hc = c.hidden, c.head_dim, c.hc
+        n_mix = 2 * hc + hc * hc
+        P = lambda *s: nn.Parameter(torch.empty(*s, dtype=dtype), requires_grad=False)
+        self.ratio = r = c.ratios[i]
+        self.compressed, self.indexed = r > 0, r == 4
+        self.hash_routed = i < c.hash_layers
+        # hyper-connections (attention and feed-forward halves)
+        self.hc_attn_fn, self.hc_attn_base, self.hc_attn_scale = P(hc * H, n_mix), P(n_mix), P(3)
+        self.hc_ffn_fn, self.hc_ffn_base, self.hc_ffn_scale = P(hc * H, n_mix), P(n_mix), P(3)
+        self.attn_norm, self.ffn_norm = P(H), P(H)
+        self.q_a, self.q_a_norm, self.q_b = P(c.q_lora, H), P(c.q_lora), P(c.heads * D, c.q_lora)
+        self.kv_proj, self.kv_norm = P(D, H), P(D)
+        self.sinks = P(c.heads)
+        gh = c.heads // c.o_groups
+        self.o_a = P(c.o_groups, c.o_lora, gh * D)
+        self.o_b = P(H, c.o_groups * c.o_lora)
+        if self.compressed:
+            width = (2 if r == 4 else 1) * D
+            self.comp_kv, self.comp_gate, self.comp_ape, self.comp_norm = P(width, H), P(width, H), P(r, width), P(D)
+        if self.indexed:
+            self.idx_q = P(c.indexer_heads * 128, c.q_lora)          # from the normed low-rank query
+            self.idx_w = P(c.indexer_heads, H)
+            self.idx_kv, self.idx_gate, self.idx_ape, self.idx_norm = P(256, H), P(256, H), P(4, 256), P(128)
+        self.router = P(c.experts, H)
+        self.router_bias = nn.Parameter(torch.zeros(c.experts, dtype=torch.float32), requires_grad=False)
+        if self.hash_routed:
+            self.register_buffer("hash_table", torch.zeros(c.top_k, c.vocab, dtype=torch.int32))
+        self.w_gate, self.w_up = P(c.experts, c.expert_inter, H), P(c.experts, c.expert_inter, H)
+        self.w_down = P(c.experts, H, c.expert_inter)
+        self.s_gate, self.s_up, self.s_down = P(c.shared_inter, H), P(c.shared_inter, H), P(H, c.shared_inter)
+
+
+class DeepseekV4FlashForCausalLM(nn.Module):
+    supports_lora = False
+    supports_multimodal = False
+    supports_cuda_graph = False
+    model_owned_data_plane = True
+
+    def __init__(self, vllm_config):
+        super().__init__()
+        mc = vllm_config.model_config
+        self.cfg = c = V4Config.from_hf(mc.hf_config or {})
+        self.dtype = mc.dtype
+        self.seed = int(getattr(mc, "seed", 0) or 0)
+        self.synthetic = bool(getattr(mc, "synthetic", False))
+        self.embed = nn.Parameter(torch.empty(c.vocab, c.hidden, dtype=mc.dtype), requires_grad=False)
+        self.layers = nn.ModuleList([V4Layer(c, i, mc.dtype) for i in range(c.layers)])
+        self.final_norm = nn.Parameter(torch.empty(c.hidden, dtype=mc.dtype), requires_grad=False)
+        self.out_hc_fn = nn.Parameter(torch.empty(c.hc, c.hc * c.hidden, dtype=mc.dtype), requires_grad=False)
+        self.out_hc_base = nn.Parameter(torch.empty(c.hc, dtype=mc.dtype), requires_grad=False)
+        self.out_hc_scale = nn.Parameter(torch.empty(1, dtype=mc.dtype), requires_grad=False)
+        self.lm_head = nn.Parameter(torch.empty(c.vocab, c.hidden, dtype=mc.dtype), requires_grad=False)
+        self.requests: dict[str, RequestRows] = {}
+        self.max_model_len = int(mc.max_model_len)
+
+    # ------------------------------------------------------------------ weights
+    def kv_cache_specs(self):
+        # the generic paged pool is not used by this model: one minimal layer keeps the stock allocator happy
+        return [(1, 16)]
+
+    # GGUF tensor names of the checkpoint family -> parameter names of this module
+    _GGUF_TOP = {"token_embd.weight": "embed", "output_norm.weight": "final_norm", "output.weight": "lm_head",
+                 "output_hc_fn.weight": "out_hc_fn", "output_hc_base.weight": "out_hc_base",
+                 "output_hc_scale.weight": "out_hc_scale"}
+    _GGUF_LAYER = {
+        "attn_norm.weight": "attn_norm", "attn_sinks.weight": "sinks", "attn_q_a.weight": "q_a",
+        "attn_q_a_norm.weight": "q_a_norm", "attn_q_b.weight": "q_b", "attn_kv.weight": "kv_proj",
+        "attn_kv_a_norm.weight": "kv_norm", "attn_output_a.weight": "o_a", "attn_output_b.weight": "o_b",
+        "attn_compressor_kv.weight": "comp_kv", "attn_compressor_gate.weight": "comp_gate",
+        "attn_compressor_ape.weight": "comp_ape", "attn_compressor_norm.weight": "comp_norm",
+        "indexer.attn_q_b.weight": "idx_q", "indexer.proj.weight": "idx_w",
+        "indexer_compressor_kv.weight": "idx_kv", "indexer_compressor_gate.weight": "idx_gate",
+        "indexer_compressor_ape.weight": "idx_ape", "indexer_compressor_norm.weight": "idx_norm",
+        "ffn_norm.weight": "ffn_norm", "ffn_gate_inp.weight": "router", "exp_probs_b.bias": "router_bias",
+        "ffn_gate_tid2eid.weight": "hash_table", "ffn_gate_exps.weight": "w_gate", "ffn_up_exps.weight": "w_up",
+        "ffn_down_exps.weight": "w_down", "ffn_gate_shexp.weight": "s_gate", "ffn_up_shexp.weight": "s_up",
+        "ffn_down_shexp.weight": "s_down",
+        "hc_attn_fn.weight": "hc_attn_fn", "hc_attn_base.weight": "hc_attn_base", "hc_attn_scale.weight": "hc_attn_scale",
+        "hc_ffn_fn.weight": "hc_ffn_fn", "hc_ffn_base.weight": "hc_ffn_base", "hc_ffn_scale.weight": "hc_ffn_scale",
+    }
+
+    @classmethod
+    def param_name(cls, name: str) -> str:
+        """Checkpoint tensor name -> parameter name (names that are already parameter names pass through)."""
+        if name in cls._GGUF_TOP:
+            return cls._GGUF_TOP[name]
+        if name.startswith("blk."):
+            _, idx, suffix = name.split(".", 2)
+            if suffix in cls._GGUF_LAYER:
+                return f"layers.{idx}.{cls._GGUF_LAYER[suffix]}"
+        return name
+
+    def load_weights(self, weights):
+        """Named dense tensors (parameter names, or the checkpoint family's GGUF names) are copied into the
+        parameters; a tensor with the right element count but another layout of the same matrix (transposed
+        position table, flattened groups) is reshaped.  A synthetic checkpoint has no tensors and gets seeded
+        random weights (norm gains 1, hyper-connection scales small, a random hash table)."""
+        named = dict(self.named_parameters())
+        named.update(dict(self.named_buffers()))
+        consumed = set()
+        for name, t in weights:
+            target = named.get(self.param_name(name))
+            if target is None:
+                continue
+            if t.shape != target.shape:
+                if t.numel() != target.numel():
+                    raise ValueError(f"{name}: {tuple(t.shape)} does not fit {tuple(target.shape)}")
+                t = t.t() if t.dim() == 2 and t.shape == target.shape[::-1] else t.reshape(target.shape)
+            target.data.copy_(t.to(target.dtype))
+            consumed.add(name)
+        if not consumed:
+            self._init_synthetic()
+        return consumed
+
+    def _init_synthetic(self) -> None:
+        g = torch.Generator().manual_seed(1000 + self.seed)
+        c = self.cfg
+        for name, p in self.named_parameters():
+            if name.endswith("norm"):
+                p.data.fill_(1.0)
+            elif name.endswith("_scale"):
+                p.data.fill_(0.1)
+            elif name.endswith(("_base", "router_bias", "sinks")):
+                p.data.copy_((torch.randn(p.shape, generator=g) * 0.1).to(p.dtype))
+            else:
+                fan_in = max(p.shape) if name.endswith("_fn") else p.shape[-1]
+                p.data.copy_((torch.randn(p.shape, generator=g) / math.sqrt(fan_in)).to(p.dtype))
+        for layer in self.layers:
+            if layer.hash_routed:
+                tab = torch.stack([torch.randperm(c.experts, generator=g)[: c.top_k] for _ in range(c.vocab)], dim=1)
+                layer.hash_table.copy_(tab.to(torch.int32))
+
+    # ------------------------------------------------------------------ request state
+    def _new_request(self, device) -> RequestRows:
+        c = self.cfg
+        layers = []
+        for i in range(c.layers):
+            r = c.ratios[i]
+            lr = LayerRows(window=torch.zeros(c.window, c.head_dim, dtype=torch.float32, device=device), ratio=r)
+            if r > 0:
+                lr.comp_state = CompressorState.empty(c.head_dim, r, device)
+            if r == 4:
+                lr.index_state = CompressorState.empty(128, 4, device)
+            layers.append(lr)
+        return RequestRows(layers)
+
+    def release_request(self, request_id: str) -> bool:
+        return self.requests.pop(request_id, None) is not None
+
+    def request_bytes(self) -> int:
+        return sum(r.bytes() for r in self.requests.values())
+
+    # ------------------------------------------------------------------ a group of tokens, layer by layer
+    def _attention(self, layer: V4Layer, rows_of: list, h: torch.Tensor, pos: torch.Tensor, li: int) -> torch.Tensor:
+        """``h`` ``[T, H]``: the projections run once for the whole group; the row appends, compressor steps
+        and the attention itself walk the tokens in order (token t of a request sees the rows of tokens <= t)."""
+        c = self.cfg
+        T, D, rot = h.shape[0], c.head_dim, c.rotary_dim
+        x = _rms(h, layer.attn_norm, c.eps)
+        q_low = _rms(_lin(x, layer.q_a), layer.q_a_norm, c.eps)
+        q = _lin(q_low, layer.q_b).view(T, c.heads, D)
+        q = _rotate_tail(_rms(q, None, c.eps), pos, rot, c.rope_theta)
+        kv = _rotate_tail(_rms(_lin(x, layer.kv_proj), layer.kv_norm, c.eps), pos, rot, c.rope_theta)
+        kv = fp8_kv_qat(kv, D, rot)
+        if layer.compressed:
+            ckv, cgate, comp_ape = _lin(x, layer.comp_kv), _lin(x, layer.comp_gate), layer.comp_ape.float()
+        if layer.indexed:
+            ikv, igate, idx_ape = _lin(x, layer.idx_kv), _lin(x, layer.idx_gate), layer.idx_ape.float()
+            iq = _lin(q_low, layer.idx_q).view(T, c.indexer_heads, 128)
+            iq = indexer_qat(_rotate_tail(iq, pos, min(rot, 128), c.rope_theta))
+            iw = _lin(x, layer.idx_w)
+        sinks = layer.sinks.float()
+        scale = 1.0 / math.sqrt(D)
+        out = torch.empty(T, c.heads, D, dtype=torch.float32, device=h.device)
+        positions = pos.tolist()
+        r = layer.ratio
+        for t in range(T):
+            lr: LayerRows = rows_of[t].layers[li]
+            p = positions[t]
+            lr.window[lr.count % c.window] = kv[t]
+            lr.count += 1
+            rows = lr.window[:min(lr.count, c.window)]
+            if lr.compressed:
+                # rows emitted by earlier tokens; the fine layers keep the indexer's top-k of them
+                comp = torch.stack(lr.compressed)
+                if layer.indexed:
+                    scores = indexer_scores(iq[t], iw[t], torch.stack(lr.index_rows))
+                    comp = comp[indexer_topk(scores, c.indexer_topk)]
+                rows = torch.cat([rows, comp], 0)
+            out[t] = shared_kv_attention(q[t], rows.contiguous(), sinks, softmax_scale=scale)
+            if layer.compressed:
+                lr.comp_state, emitted = compressor_step(lr.comp_state, ckv[t], cgate[t], comp_ape, p, D, r)
+                if layer.indexed:
+                    lr.index_state, idx_row = compressor_step(lr.index_state, ikv[t], igate[t], idx_ape, p, 128, 4)
+                if emitted is not None:
+                    at = torch.tensor([p + 1 - r], device=h.device)
+                    emitted = _rotate_tail(_rms(emitted, layer.comp_norm, c.eps).unsqueeze(0), at, rot, c.rope_theta)[0]
+                    lr.compressed.append(emitted)
+                    if layer.indexed:
+                        lr.index_rows.append(_rms(idx_row, layer.idx_norm, c.eps))
+        out = _rotate_tail(out, pos, rot, c.rope_theta, inverse=True)
+        gh = c.heads // c.o_groups
+        low = torch.einsum("grk,tgk->tgr", layer.o_a.float(), out.view(T, c.o_groups, gh * D))
+        return _lin(low.reshape(T, -1), layer.o_b)
+
+    def _ffn(self, layer: V4Layer, h: torch.Tensor, token_ids: torch.Tensor) -> torch.Tensor:
+        c = self.cfg
+        x = _rms(h, layer.ffn_norm, c.eps)
+        if layer.hash_routed:
+            scores = torch.sqrt(torch.nn.functional.softplus(x @ layer.router.float().t()))
+            ids = hash_routed_expert_ids(layer.hash_table, token_ids).long()
+            w = scores.gather(1, ids)
+            w = w / w.sum(-1, keepdim=True).clamp_min(1e-20) * c.routed_scale
+        else:
+            ids, w = sqrt_softplus_router(x, layer.router, c.top_k, layer.router_bias, c.routed_scale)
+            ids = ids.long()
+        xq = q8_k_roundtrip(x) if x.shape[-1] % 256 == 0 else x
+
+        def mlp(g_w, u_w, d_w, inp):
+            g, u = _lin(inp, g_w), _lin(inp, u_w)
+            if c.swiglu_clamp > 0:
+                g, u = g.clamp(max=c.swiglu_clamp), u.clamp(-c.swiglu_clamp, c.swiglu_clamp)
+            return _lin(torch.nn.functional.silu(g) * u, d_w)
+
+        y = mlp(layer.s_gate, layer.s_up, layer.s_down, x)
+        for e in torch.unique(ids).tolist():
+            tok, slot = torch.nonzero(ids == e, as_tuple=True)
+            y.index_add_(0, tok, w[tok, slot].unsqueeze(-1) * mlp(layer.w_gate[e], layer.w_up[e], layer.w_down[e], xq[tok]))
+        return y
+
+    @torch.inference_mode()
+    def forward_tokens(self, entries: list) -> torch.Tensor:
+        """``entries``: (request rows, token id) pairs; the tokens of one request appear in prompt order.  Runs
+        them through every layer and returns the final hidden vectors ``[T, H]`` (fp32)."""
+        c = self.cfg
+        dev = self.embed.device
+        seen: dict[int, int] = {}
+        positions = []
+        for rows, _ in entries:
+            k = seen.get(id(rows), 0)
+            positions.append(rows.pos + k)
+            seen[id(rows)] = k + 1
+        rows_of = [r for r, _ in entries]
+        ids = torch.tensor([int(t) for _, t in entries], dtype=torch.long, device=dev)
+        pos = torch.tensor(positions, dtype=torch.long, device=dev)
+        streams = self.embed[ids].float().unsqueeze(1).repeat(1, c.hc, 1)          # [T, hc, H]
+        for li, layer in enumerate(self.layers):
+            with stage("v4_attention"):
+                st = hyper_connection_pre(streams, layer.hc_attn_fn, layer.hc_attn_base, layer.hc_attn_scale, eps=c.eps)
+                streams = hyper_connection_post(self._attention(layer, rows_of, st.mixed, pos, li), streams, st)
+            with stage("v4_experts"):
+                st = hyper_connection_pre(streams, layer.hc_ffn_fn, layer.hc_ffn_base, layer.hc_ffn_scale, eps=c.eps)
+                streams = hyper_connection_post(self._ffn(layer, st.mixed, ids), streams, st)
+        done = set()
+        for rows, _ in entries:
+            if id(rows) not in done:
+                rows.pos += seen[id(rows)]
+                done.add(id(rows))
+        # collapse the streams: sigmoid gains from the normalised flattened streams, then the final norm
+        flat = streams.reshape(streams.shape[0], -1)
+        flat = flat * torch.rsqrt(flat.pow(2).mean(-1, keepdim=True) + c.eps)
+        gains = torch.sigmoid(_lin(flat, self.out_hc_fn) * self.out_hc_scale.float()[0] + self.out_hc_base.float()) + 1e-6
+        return _rms((gains.unsqueeze(-1) * streams).sum(1), self.final_norm, c.eps)
+
+    def _next_tokens(self, hidden: torch.Tensor) -> list[int]:
+        return torch.argmax(_lin(hidden, self.lm_head), dim=-1).tolist()
+
+    # ------------------------------------------------------------------ request API (token ids in, token ids out)
+    @torch.inference_mode()
+    def prefill_request(self, request_id: str, token_ids: list[int], start: int = 0, final: bool = True) -> int | None:
+        """Feed ``token_ids`` (the chunk beginning at prompt position ``start``) token by token; with ``final``
+        return the first generated token."""
+        dev = self.embed.device
+        if start == 0 or request_id not in self.requests:
+            self.requests[request_id] = self._new_request(dev)
+        rows = self.requests[request_id]
+        if rows.pos != start:
+            raise RuntimeError(f"request {request_id}: chunk starts at {start} but {rows.pos} tokens were processed")
+        if not token_ids:
+            return None
+        hidden = self.forward_tokens([(rows, int(t)) for t in token_ids])
+        return self._next_tokens(hidden[-1:])[0] if final else None
+
+    @torch.inference_mode()
+    def decode_tokens_batch(self, request_ids: list[str], last_tokens: list[int]) -> list[int]:
+        """One token for each request; the projections and experts of the whole batch run together."""
+        hidden = self.forward_tokens([(self.requests[r], int(t)) for r, t in zip(request_ids, last_tokens)])
+        return self._next_tokens(hidden)
+
+    def forward(self, batch, kv_caches, inputs_embeds=None):
+        raise RuntimeError("DeepSeek-V4-Flash runs through its own executors (token ids in, token ids out)")

@@ -82,6 +82,18 @@ PRESETS["tiny-deepseek-test"] = dict(PRESETS["deepseek-mla-moe"], hidden_size=25
 # the latent geometry of the full-size model (512 + 64) with 20 heads: exercises the absorbed attention kernel
 PRESETS["tiny-deepseek-mla512-test"] = dict(PRESETS["tiny-deepseek-test"], num_attention_heads=20, num_key_value_heads=20,
                                             kv_lora_rank=512, qk_nope_head_dim=128, v_head_dim=128)
+# DeepSeek-V4-Flash geometry in miniature: 512-wide shared latent rows, a window shorter than the test prompts,
+# two window-only layers, then a fine (ratio 4, indexer top-k smaller than the emitted rows) and a coarse
+# (ratio 8, all rows) compressed layer
+PRESETS["tiny-deepseek-v4-flash-test"] = {
+    "architectures": ["DeepseekV4FlashForCausalLM"], "model_type": "deepseek_v4_flash", "hidden_size": 256,
+    "num_hidden_layers": 4, "num_attention_heads": 4, "num_key_value_heads": 1, "head_dim": 512,
+    "qk_rope_head_dim": 64, "q_lora_rank": 64, "sliding_window": 8, "compress_ratio_coarse": 8, "index_n_heads": 2,
+    "index_topk": 3, "hc_mult": 4, "o_groups": 2, "o_lora_rank": 32, "n_routed_experts": 8,
+    "num_experts_per_tok": 2, "moe_intermediate_size": 128, "num_hash_layers": 1, "routed_scaling_factor": 1.5,
+    "vocab_size": 512, "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "max_position_embeddings": 512,
+    "intermediate_size": 128, "eos_token_id": 1,
+}
 PRESETS["tiny-qwen35-test"] = {
     "architectures": ["Qwen3_5ForCausalLM"], "model_type": "qwen3_5", "hidden_size": 256, "num_hidden_layers": 4,
     "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 256, "vocab_size": 512,

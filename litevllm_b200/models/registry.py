@@ -25,7 +25,7 @@ _MODELS = {
 _FAMILY_DEFAULT = {
     "llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM", "qwen3_5": "Qwen3_5ForCausalLM",
     "qwen2_vl": "Qwen2VLForConditionalGeneration", "gemma4": "Gemma4ForCausalLM",
-    "deepseek_mla": "DeepseekV3ForCausalLM",
+    "deepseek_mla": "DeepseekV3ForCausalLM", "deepseek_v4_flash": "DeepseekV4FlashForCausalLM",
 }
 
 
