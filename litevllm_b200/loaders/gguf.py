@@ -186,12 +186,60 @@ def hf_config_from_gguf(path: str | Path) -> dict:
             "scoring_func": "sigmoid" if int(g.get("expert_gating_func", 2)) == 2 else "softmax",
         })
     elif a == "deepseek4":
-        cfg.update({"architectures": ["DeepseekV4FlashForCausalLM"], "model_type": "deepseek_v4_flash"})
+        cfg.update(_deepseek4_config(g))
     elif a.startswith("qwen2"):
         cfg.update({"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2"})
     else:
         cfg.update({"architectures": ["LlamaForCausalLM"], "model_type": "llama"})
     return cfg
+
+
+def _deepseek4_config(g: "GGUFFile") -> dict:
+    """DeepSeek-V4-Flash: head counts, window, indexer and expert counts come from the ``deepseek4.*`` metadata;
+    the low-rank widths, the group count, the expert width and the number of hash-routed layers are read off the
+    tensor shapes; the rest defaults to the checkpoint family's constants.  Reference (fixed shape validated
+    against the metadata): vllm/model_executor/models/deepseek_v4_flash/gguf_reader.py:100-111, config.py:41-67."""
+    def shape(name, default=None):
+        t = g.tensors.get(name)
+        return t["shape"] if t is not None else default
+
+    layers = int(g.get("block_count"))
+    head_dim = int(g.get("attention.key_length", 512))
+    heads = int(g.get("attention.head_count", 64))
+    q_a = shape("blk.0.attn_q_a.weight", (1024, 0))
+    o_a = shape("blk.0.attn_output_a.weight")          # [groups * rank, heads/groups * head_dim] (or 3-D)
+    o_b = shape("blk.0.attn_output_b.weight")          # [hidden, groups * rank]
+    groups = int(g.get("attention.output_group_count", 0))
+    if not groups and o_a is not None:
+        groups = o_a[0] if len(o_a) == 3 else max(1, heads * head_dim // o_a[-1])
+    groups = groups or 8
+    experts = shape("blk.0.ffn_gate_exps.weight", (0, 2048, 0))
+    shared = shape("blk.0.ffn_gate_shexp.weight", (experts[1], 0))
+    hc_fn = shape("output_hc_fn.weight")
+    out = {
+        "architectures": ["DeepseekV4FlashForCausalLM"], "model_type": "deepseek_v4_flash", "head_dim": head_dim,
+        "qk_rope_head_dim": int(g.get("rope.dimension_count", 64)), "q_lora_rank": int(q_a[0]),
+        "sliding_window": int(g.get("attention.sliding_window", 128)),
+        "index_n_heads": int(g.get("attention.indexer.head_count", 64)),
+        "index_topk": int(g.get("attention.indexer.top_k", 512)),
+        "hc_mult": int(min(hc_fn)) if hc_fn is not None else 4, "o_groups": int(groups),
+        "o_lora_rank": int(o_b[1] // groups) if o_b is not None else 1024,
+        "n_routed_experts": int(g.get("expert_count", experts[0])),
+        "num_experts_per_tok": int(g.get("expert_used_count", 6)),
+        "moe_intermediate_size": int(g.get("expert_feed_forward_length", experts[1])),
+        "shared_intermediate_size": int(shared[0]),
+        "num_hash_layers": sum(1 for i in range(layers) if f"blk.{i}.ffn_gate_tid2eid.weight" in g.tensors),
+        "routed_scaling_factor": float(g.get("expert_weights_scale", 1.5)),
+        "swiglu_limit": float(g.get("swiglu_clamp", 10.0)),
+        "compress_ratio_coarse": int(g.get("attention.compress_ratio_coarse", 128)),
+        "compressed_rope_theta": float(g.get("rope.compressed_freq_base", 160000.0)),
+        "rope_scaling_factor": float(g.get("rope.scaling.factor", 16.0)),
+        "rope_original_context": int(g.get("rope.scaling.original_context_length", 65536)),
+        "rope_beta_fast": float(g.get("rope.scaling.yarn_beta_fast", 32.0)),
+        "rope_beta_slow": float(g.get("rope.scaling.yarn_beta_slow", 1.0)),
+        "tie_word_embeddings": False,
+    }
+    return out
 
 
 # GGUF tensor name -> HF-style module path used by the model classes
@@ -235,6 +283,10 @@ def iter_gguf_weights(path: str | Path, arch=None):
     if p.is_dir():
         p = sorted(p.glob("*.gguf"))[0]
     g = GGUFFile(p)
+    if g.arch() == "deepseek4":          # the model binds the checkpoint's own tensor names
+        for name in g.tensors:
+            yield name, g.load(name)
+        return
     for name in g.tensors:
         hf = gguf_to_hf_name(name)
         if hf is None:

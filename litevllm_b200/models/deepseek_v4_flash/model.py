@@ -36,6 +36,7 @@ from .attention import CompressorState, compressor_step, indexer_scores, indexer
 from .hyper_connection import hyper_connection_post, hyper_connection_pre
 from .moe import hash_routed_expert_ids, sqrt_softplus_router
 from ...utils.profiling import stage
+from ...ops import gguf_quant as gq
 from .ops import fp8_kv_qat, indexer_qat, q8_k_roundtrip
 
 
@@ -64,6 +65,11 @@ class V4Config:
     eps: float
     rope_theta: float
     swiglu_clamp: float
+    rope_theta_compressed: float = 160000.0   # compressed layers: long-context base with YaRN interpolation
+    rope_factor: float = 16.0
+    rope_original_context: int = 65536
+    rope_beta_fast: float = 32.0
+    rope_beta_slow: float = 1.0
 
     @classmethod
     def from_hf(cls, cfg: dict) -> "V4Config":
@@ -80,7 +86,30 @@ class V4Config:
                    expert_inter=int(g("moe_intermediate_size", 256)), shared_inter=int(g("shared_intermediate_size", g("moe_intermediate_size", 256))),
                    hash_layers=int(g("num_hash_layers", 1)), routed_scale=float(g("routed_scaling_factor", 1.5)),
                    vocab=int(cfg["vocab_size"]), eps=float(g("rms_norm_eps", 1e-6)),
-                   rope_theta=float(g("rope_theta", 10000.0)), swiglu_clamp=float(g("swiglu_limit", 0.0)))
+                   rope_theta=float(g("rope_theta", 10000.0)), swiglu_clamp=float(g("swiglu_limit", 0.0)),
+                   rope_theta_compressed=float(g("compressed_rope_theta", 160000.0)),
+                   rope_factor=float(g("rope_scaling_factor", 16.0)),
+                   rope_original_context=int(g("rope_original_context", 65536)),
+                   rope_beta_fast=float(g("rope_beta_fast", 32.0)), rope_beta_slow=float(g("rope_beta_slow", 1.0)))
+
+    def rope_inv_freq(self, compressed: bool) -> torch.Tensor:
+        """Angle per position for each rotary pair.  Window-only layers: ``theta^(-2i/rot)``.  Compressed layers:
+        the long-context base, each pair blended between its interpolated (``/ factor``) and its extrapolated
+        frequency by the YaRN ramp over the correction range of (beta_fast, beta_slow) rotations."""
+        rot = self.rotary_dim
+        i = torch.arange(rot // 2, dtype=torch.float32)
+        if not compressed:
+            return self.rope_theta ** (-2.0 * i / rot)
+        base = self.rope_theta_compressed
+        extrap = base ** (-2.0 * i / rot)
+
+        def corr(n_rot: float) -> float:
+            return rot * math.log(self.rope_original_context / (n_rot * 2.0 * math.pi)) / (2.0 * math.log(base))
+
+        low = max(0.0, float(math.floor(corr(self.rope_beta_fast))))
+        high = min(float(rot - 1), float(math.ceil(corr(self.rope_beta_slow))))
+        ramp = 1.0 - ((i - low) / max(0.001, high - low)).clamp(0.0, 1.0)
+        return extrap * (ramp + (1.0 - ramp) / self.rope_factor)
 
     @staticmethod
     def default_ratios(layers: int, coarse: int = 128) -> list:
@@ -119,23 +148,50 @@ def _rms(x: torch.Tensor, w: torch.Tensor | None, eps: float) -> torch.Tensor:
     return y if w is None else y * w.float()
 
 
-def _lin(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """``x @ w.T`` in the weight's dtype (tensor cores for 16-bit weights on a GPU), fp32 result."""
+class BlockMatrix:
+    """A ``[N, K]`` matrix kept in its GGUF block format (Q8_0, Q4_K, ...): decode-sized products stream the
+    blocks through the GEMV kernel, larger ones dequantise into scratch in front of the tensor-core GEMM."""
+
+    def __init__(self, raw: torch.Tensor, ggml_type: int, K: int, device):
+        self.raw = raw.reshape(-1, raw.shape[-1]).contiguous().to(device)
+        self.ggml_type, self.K, self.N = int(ggml_type), int(K), self.raw.shape[0]
+        self._dense = None
+
+    def dense(self) -> torch.Tensor:
+        if self._dense is None:
+            self._dense = gq.dequantize(self.raw.cpu(), self.ggml_type, self.K).to(self.raw.device)
+        return self._dense
+
+    def linear(self, x: torch.Tensor) -> torch.Tensor:
+        if x.is_cuda:
+            return gq.gguf_linear(x.to(torch.bfloat16).contiguous(), self.raw, self.ggml_type, self.K,
+                                  out_dtype=torch.float32)
+        return x.float() @ self.dense().t()
+
+    def nbytes(self) -> int:
+        return self.raw.numel()
+
+
+def _lin(x: torch.Tensor, w) -> torch.Tensor:
+    """``x @ w.T`` with an fp32 result: block-format matrices through their kernels, dense ones in the weight's
+    dtype (tensor cores for 16-bit weights on a GPU)."""
+    if isinstance(w, BlockMatrix):
+        return w.linear(x)
     return torch.nn.functional.linear(x.to(w.dtype), w).float()
 
 
-def _rotate_tail(x: torch.Tensor, pos: torch.Tensor, rot: int, theta: float, inverse: bool = False) -> torch.Tensor:
-    """Rotary embedding on the last ``rot`` channels (pairs (i, i + rot/2)) of ``[T, ..., D]`` at positions
-    ``pos`` ``[T]``; ``inverse`` rotates back."""
+def _rotate_tail(x: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, inverse: bool = False) -> torch.Tensor:
+    """Rotary embedding on the last ``2 * len(inv_freq)`` channels of ``[T, ..., D]`` at positions ``pos`` ``[T]``;
+    adjacent channels (2i, 2i+1) form a pair.  ``inverse`` rotates back."""
+    rot = 2 * inv_freq.numel()
     if rot == 0:
         return x
-    half = rot // 2
-    inv_freq = theta ** (-torch.arange(half, dtype=torch.float32, device=x.device) / half)
     ang = (-pos if inverse else pos).float().reshape(-1, *([1] * (x.dim() - 1))) * inv_freq
     c, s = torch.cos(ang), torch.sin(ang)
-    head, tail = x[..., :-rot], x[..., -rot:]
-    a, b = tail[..., :half], tail[..., half:]
-    return torch.cat([head, a * c - b * s, b * c + a * s], dim=-1)
+    pairs = x[..., -rot:].unflatten(-1, (rot // 2, 2))
+    a, b = pairs[..., 0], pairs[..., 1]
+    tail = torch.stack((a * c - b * s, a * s + b * c), dim=-1).flatten(-2)
+    return torch.cat([x[..., :-rot], tail], dim=-1)
 
 
 class V4Layer(nn.Module):
@@ -171,6 +227,7 @@ class V4Layer(nn.Module):
         self.w_gate, self.w_up = P(c.experts, c.expert_inter, H), P(c.experts, c.expert_inter, H)
         self.w_down = P(c.experts, H, c.expert_inter)
         self.s_gate, self.s_up, self.s_down = P(c.shared_inter, H), P(c.shared_inter, H), P(H, c.shared_inter)
+        self.routed = None          # RoutedExperts over raw GGUF blocks, once a checkpoint delivers block tensors
 
 
 class DeepseekV4FlashForCausalLM(nn.Module):
@@ -194,6 +251,8 @@ class DeepseekV4FlashForCausalLM(nn.Module):
         self.out_hc_scale = nn.Parameter(torch.empty(1, dtype=mc.dtype), requires_grad=False)
         self.lm_head = nn.Parameter(torch.empty(c.vocab, c.hidden, dtype=mc.dtype), requires_grad=False)
         self.requests: dict[str, RequestRows] = {}
+        self.register_buffer("inv_freq_window", c.rope_inv_freq(False).to(self.embed.device), persistent=False)
+        self.register_buffer("inv_freq_compressed", c.rope_inv_freq(True).to(self.embed.device), persistent=False)
         self.max_model_len = int(mc.max_model_len)
 
     # ------------------------------------------------------------------ weights
@@ -233,18 +292,63 @@ class DeepseekV4FlashForCausalLM(nn.Module):
                 return f"layers.{idx}.{cls._GGUF_LAYER[suffix]}"
         return name
 
+    # matrices that are only ever the weight of ``x @ W.T``: these may stay in their block format
+    _LINEAR = {"q_a", "q_b", "kv_proj", "o_b", "comp_kv", "comp_gate", "idx_q", "idx_w", "idx_kv", "idx_gate",
+               "s_gate", "s_up", "s_down", "lm_head"}
+    _EXPERTS = {"w_gate": "gate", "w_up": "up", "w_down": "down"}
+
+    def _owner(self, pname: str):
+        if pname.startswith("layers."):
+            _, idx, attr = pname.split(".", 2)
+            return (self.layers[int(idx)] if int(idx) < len(self.layers) else None), attr
+        return self, pname
+
+    def _routed_experts(self, layer: V4Layer):
+        if layer.routed is None:
+            from types import SimpleNamespace
+            from ..deepseek_mla import RoutedExperts
+            c = self.cfg
+            shim = SimpleNamespace(hidden_size=c.hidden, extra={"swiglu_clamp": c.swiglu_clamp},
+                                   moe=SimpleNamespace(num_experts=c.experts, expert_intermediate=c.expert_inter,
+                                                       top_k=c.top_k))
+            layer.routed = RoutedExperts(shim, torch.bfloat16)
+            layer.routed.device = self.embed.device
+        return layer.routed
+
     def load_weights(self, weights):
-        """Named dense tensors (parameter names, or the checkpoint family's GGUF names) are copied into the
-        parameters; a tensor with the right element count but another layout of the same matrix (transposed
-        position table, flattened groups) is reshaped.  A synthetic checkpoint has no tensors and gets seeded
-        random weights (norm gains 1, hyper-connection scales small, a random hash table)."""
-        named = dict(self.named_parameters())
-        named.update(dict(self.named_buffers()))
+        """Named tensors (parameter names, or the checkpoint family's GGUF names) go into the parameters.  Dense
+        tensors are copied; one with the right element count but another layout of the same matrix (transposed
+        position table, flattened groups) is reshaped.  Block-quantised tensors stay in HBM as they are where
+        the model only multiplies by them (projections -> ``BlockMatrix``, routed experts -> the expert-grouped
+        GGUF kernels) and are dequantised once otherwise (embedding, tables, grouped output factor).  A synthetic
+        checkpoint has no tensors and gets seeded random weights (norm gains 1, hyper-connection scales small,
+        a random hash table)."""
+        from ...loaders.gguf import GGUFTensor
         consumed = set()
         for name, t in weights:
-            target = named.get(self.param_name(name))
-            if target is None:
+            owner, attr = self._owner(self.param_name(name))
+            target = getattr(owner, attr, None) if owner is not None else None
+            if not isinstance(target, (torch.Tensor, BlockMatrix)) and not (
+                    attr in self._EXPERTS and isinstance(owner, V4Layer) and isinstance(t, GGUFTensor)):
                 continue
+            if isinstance(t, GGUFTensor):
+                if attr in self._EXPERTS and isinstance(owner, V4Layer):
+                    self._routed_experts(owner).load(self._EXPERTS[attr], t)
+                    owner._parameters.pop(attr, None)
+                    setattr(owner, attr, None)
+                    consumed.add(name)
+                    continue
+                rows = t.raw.reshape(-1, t.raw.shape[-1])
+                if attr in self._LINEAR and isinstance(target, torch.Tensor) and target.dim() == 2:
+                    if (rows.shape[0], t.K) != tuple(target.shape):
+                        raise ValueError(f"{name}: {tuple(t.shape)} does not fit {tuple(target.shape)}")
+                    owner._parameters.pop(attr, None)
+                    setattr(owner, attr, BlockMatrix(rows, t.ggml_type, t.K, self.embed.device))
+                    consumed.add(name)
+                    continue
+                t = gq.dequantize(rows, t.ggml_type, t.K).reshape(t.shape)
+            if isinstance(target, BlockMatrix):
+                raise ValueError(f"{name}: already loaded in block format")
             if t.shape != target.shape:
                 if t.numel() != target.numel():
                     raise ValueError(f"{name}: {tuple(t.shape)} does not fit {tuple(target.shape)}")
@@ -302,15 +406,16 @@ class DeepseekV4FlashForCausalLM(nn.Module):
         x = _rms(h, layer.attn_norm, c.eps)
         q_low = _rms(_lin(x, layer.q_a), layer.q_a_norm, c.eps)
         q = _lin(q_low, layer.q_b).view(T, c.heads, D)
-        q = _rotate_tail(_rms(q, None, c.eps), pos, rot, c.rope_theta)
-        kv = _rotate_tail(_rms(_lin(x, layer.kv_proj), layer.kv_norm, c.eps), pos, rot, c.rope_theta)
+        freq = self.inv_freq_compressed if layer.compressed else self.inv_freq_window
+        q = _rotate_tail(_rms(q, None, c.eps), pos, freq)
+        kv = _rotate_tail(_rms(_lin(x, layer.kv_proj), layer.kv_norm, c.eps), pos, freq)
         kv = fp8_kv_qat(kv, D, rot)
         if layer.compressed:
             ckv, cgate, comp_ape = _lin(x, layer.comp_kv), _lin(x, layer.comp_gate), layer.comp_ape.float()
         if layer.indexed:
             ikv, igate, idx_ape = _lin(x, layer.idx_kv), _lin(x, layer.idx_gate), layer.idx_ape.float()
             iq = _lin(q_low, layer.idx_q).view(T, c.indexer_heads, 128)
-            iq = indexer_qat(_rotate_tail(iq, pos, min(rot, 128), c.rope_theta))
+            iq = indexer_qat(_rotate_tail(iq, pos, freq))
             iw = _lin(x, layer.idx_w)
         sinks = layer.sinks.float()
         scale = 1.0 / math.sqrt(D)
@@ -337,11 +442,11 @@ class DeepseekV4FlashForCausalLM(nn.Module):
                     lr.index_state, idx_row = compressor_step(lr.index_state, ikv[t], igate[t], idx_ape, p, 128, 4)
                 if emitted is not None:
                     at = torch.tensor([p + 1 - r], device=h.device)
-                    emitted = _rotate_tail(_rms(emitted, layer.comp_norm, c.eps).unsqueeze(0), at, rot, c.rope_theta)[0]
+                    emitted = _rotate_tail(_rms(emitted, layer.comp_norm, c.eps).unsqueeze(0), at, freq)[0]
                     lr.compressed.append(emitted)
                     if layer.indexed:
                         lr.index_rows.append(_rms(idx_row, layer.idx_norm, c.eps))
-        out = _rotate_tail(out, pos, rot, c.rope_theta, inverse=True)
+        out = _rotate_tail(out, pos, freq, inverse=True)
         gh = c.heads // c.o_groups
         low = torch.einsum("grk,tgk->tgr", layer.o_a.float(), out.view(T, c.o_groups, gh * D))
         return _lin(low.reshape(T, -1), layer.o_b)
@@ -366,6 +471,9 @@ class DeepseekV4FlashForCausalLM(nn.Module):
             return _lin(torch.nn.functional.silu(g) * u, d_w)
 
         y = mlp(layer.s_gate, layer.s_up, layer.s_down, x)
+        if layer.routed is not None:
+            act = torch.bfloat16 if x.is_cuda else torch.float32
+            return y + layer.routed(xq.to(act).contiguous(), ids.to(torch.int32).contiguous(), w.float().contiguous()).float()
         for e in torch.unique(ids).tolist():
             tok, slot = torch.nonzero(ids == e, as_tuple=True)
             y.index_add_(0, tok, w[tok, slot].unsqueeze(-1) * mlp(layer.w_gate[e], layer.w_up[e], layer.w_down[e], xq[tok]))

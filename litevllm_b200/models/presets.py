@@ -90,9 +90,9 @@ PRESETS["tiny-deepseek-v4-flash-test"] = {
     "num_hidden_layers": 4, "num_attention_heads": 4, "num_key_value_heads": 1, "head_dim": 512,
     "qk_rope_head_dim": 64, "q_lora_rank": 64, "sliding_window": 8, "compress_ratio_coarse": 8, "index_n_heads": 2,
     "index_topk": 3, "hc_mult": 4, "o_groups": 2, "o_lora_rank": 32, "n_routed_experts": 8,
-    "num_experts_per_tok": 2, "moe_intermediate_size": 128, "num_hash_layers": 1, "routed_scaling_factor": 1.5,
+    "num_experts_per_tok": 2, "moe_intermediate_size": 256, "num_hash_layers": 1, "routed_scaling_factor": 1.5,
     "vocab_size": 512, "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "max_position_embeddings": 512,
-    "intermediate_size": 128, "eos_token_id": 1,
+    "intermediate_size": 256, "eos_token_id": 1,
 }
 PRESETS["tiny-qwen35-test"] = {
     "architectures": ["Qwen3_5ForCausalLM"], "model_type": "qwen3_5", "hidden_size": 256, "num_hidden_layers": 4,
