@@ -224,13 +224,13 @@ def _worker(rank: int, world: int, port: int, fn, args):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     fn(rank, world, *args)
-    if torch.cuda.is_available() and torch.cuda.is_initialized():
-        # leave without running interpreter teardown: destructors of the process group, of captured graphs and of
-        # the CUDA context race at exit (seen as "double free or corruption" from a finished, successful rank)
-        import sys
-        sys.stdout.flush()
-        sys.stderr.flush()
-        os._exit(0)
+    # leave without running interpreter teardown: destructors of the process group (gloo's threads as well as
+    # NCCL's), of captured graphs and of the CUDA context race at exit (seen as "double free or corruption" from a
+    # finished, successful rank)
+    import sys
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 def _usable_port(port: int) -> int:
