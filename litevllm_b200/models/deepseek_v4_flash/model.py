@@ -33,11 +33,11 @@ import torch
 from torch import nn
 
 from .attention import CompressorState, compressor_step, indexer_scores, indexer_topk, shared_kv_attention
-from .hyper_connection import hyper_connection_post, hyper_connection_pre
+from . import native as nv
 from .moe import hash_routed_expert_ids, sqrt_softplus_router
 from ...utils.profiling import stage
 from ...ops import gguf_quant as gq
-from .ops import fp8_kv_qat, indexer_qat, q8_k_roundtrip
+from .ops import indexer_qat
 
 
 @dataclass
@@ -70,6 +70,7 @@ class V4Config:
     rope_original_context: int = 65536
     rope_beta_fast: float = 32.0
     rope_beta_slow: float = 1.0
+    block_experts: bool = False      # routed experts only ever exist as GGUF blocks (no dense expert parameters)
 
     @classmethod
     def from_hf(cls, cfg: dict) -> "V4Config":
@@ -90,7 +91,9 @@ class V4Config:
                    rope_theta_compressed=float(g("compressed_rope_theta", 160000.0)),
                    rope_factor=float(g("rope_scaling_factor", 16.0)),
                    rope_original_context=int(g("rope_original_context", 65536)),
-                   rope_beta_fast=float(g("rope_beta_fast", 32.0)), rope_beta_slow=float(g("rope_beta_slow", 1.0)))
+                   rope_beta_fast=float(g("rope_beta_fast", 32.0)), rope_beta_slow=float(g("rope_beta_slow", 1.0)),
+                   block_experts=bool(g("synthetic_block_weights", False)) or
+                   (g("quantization_config") or {}).get("quant_method") == "gguf")
 
     def rope_inv_freq(self, compressed: bool) -> torch.Tensor:
         """Angle per position for each rotary pair.  Window-only layers: ``theta^(-2i/rot)``.  Compressed layers:
@@ -120,14 +123,44 @@ class V4Config:
 
 @dataclass
 class LayerRows:
-    """One request's rows of one layer."""
-    window: torch.Tensor                       # [window, head_dim] ring buffer
+    """One request's rows of one layer: ``pool`` holds the sliding-window ring in its first ``window`` rows and the
+    compressed rows after them (so a full window plus all compressed rows is one contiguous range); ``index_pool``
+    the indexer row of every compressed row.  Both grow by doubling."""
+    pool: torch.Tensor                         # [window + capacity, head_dim]
+    window: int
     count: int = 0                             # tokens seen
-    compressed: list = field(default_factory=list)        # emitted rows [head_dim]
-    index_rows: list = field(default_factory=list)        # emitted indexer rows [128]
+    n_comp: int = 0                            # compressed rows emitted
+    index_pool: torch.Tensor | None = None     # [capacity, 128]
     comp_state: CompressorState | None = None
     index_state: CompressorState | None = None
     ratio: int = 0
+
+    def append_compressed(self, row: torch.Tensor, index_row: torch.Tensor | None) -> None:
+        cap = self.pool.shape[0] - self.window
+        if self.n_comp == cap:
+            grown = torch.zeros(self.window + max(16, 2 * cap), self.pool.shape[1], dtype=self.pool.dtype, device=self.pool.device)
+            grown[: self.pool.shape[0]] = self.pool
+            self.pool = grown
+            if self.index_pool is not None:
+                gi = torch.zeros(max(16, 2 * cap), 128, dtype=torch.float32, device=self.pool.device)
+                gi[:cap] = self.index_pool
+                self.index_pool = gi
+        self.pool[self.window + self.n_comp] = row
+        if index_row is not None:
+            self.index_pool[self.n_comp] = index_row
+        self.n_comp += 1
+
+    @property
+    def compressed(self) -> torch.Tensor:
+        return self.pool[self.window: self.window + self.n_comp]
+
+    @property
+    def index_rows(self) -> torch.Tensor:
+        return self.index_pool[: self.n_comp] if self.index_pool is not None else self.pool.new_zeros(0, 128)
+
+    def bytes(self) -> int:
+        n = self.pool.numel() * self.pool.element_size()
+        return n + (self.index_pool.numel() * 4 if self.index_pool is not None else 0)
 
 
 @dataclass
@@ -136,16 +169,7 @@ class RequestRows:
     pos: int = 0
 
     def bytes(self) -> int:
-        n = 0
-        for lr in self.layers:
-            n += lr.window.numel() * lr.window.element_size()
-            n += sum(r.numel() * 4 for r in lr.compressed) + sum(r.numel() * 4 for r in lr.index_rows)
-        return n
-
-
-def _rms(x: torch.Tensor, w: torch.Tensor | None, eps: float) -> torch.Tensor:
-    y = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + eps)
-    return y if w is None else y * w.float()
+        return sum(lr.bytes() for lr in self.layers)
 
 
 class BlockMatrix:
@@ -180,20 +204,6 @@ def _lin(x: torch.Tensor, w) -> torch.Tensor:
     return torch.nn.functional.linear(x.to(w.dtype), w).float()
 
 
-def _rotate_tail(x: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, inverse: bool = False) -> torch.Tensor:
-    """Rotary embedding on the last ``2 * len(inv_freq)`` channels of ``[T, ..., D]`` at positions ``pos`` ``[T]``;
-    adjacent channels (2i, 2i+1) form a pair.  ``inverse`` rotates back."""
-    rot = 2 * inv_freq.numel()
-    if rot == 0:
-        return x
-    ang = (-pos if inverse else pos).float().reshape(-1, *([1] * (x.dim() - 1))) * inv_freq
-    c, s = torch.cos(ang), torch.sin(ang)
-    pairs = x[..., -rot:].unflatten(-1, (rot // 2, 2))
-    a, b = pairs[..., 0], pairs[..., 1]
-    tail = torch.stack((a * c - b * s, a * s + b * c), dim=-1).flatten(-2)
-    return torch.cat([x[..., :-rot], tail], dim=-1)
-
-
 class V4Layer(nn.Module):
     def __init__(self, c: V4Config, i: int, dtype):
         super().__init__()
@@ -224,8 +234,11 @@ class V4Layer(nn.Module):
         self.router_bias = nn.Parameter(torch.zeros(c.experts, dtype=torch.float32), requires_grad=False)
         if self.hash_routed:
             self.register_buffer("hash_table", torch.zeros(c.top_k, c.vocab, dtype=torch.int32))
-        self.w_gate, self.w_up = P(c.experts, c.expert_inter, H), P(c.experts, c.expert_inter, H)
-        self.w_down = P(c.experts, H, c.expert_inter)
+        if c.block_experts:       # a full-size model's experts do not fit as dense tensors: blocks only
+            self.w_gate = self.w_up = self.w_down = None
+        else:
+            self.w_gate, self.w_up = P(c.experts, c.expert_inter, H), P(c.experts, c.expert_inter, H)
+            self.w_down = P(c.experts, H, c.expert_inter)
         self.s_gate, self.s_up, self.s_down = P(c.shared_inter, H), P(c.shared_inter, H), P(H, c.shared_inter)
         self.routed = None          # RoutedExperts over raw GGUF blocks, once a checkpoint delivers block tensors
 
@@ -251,6 +264,8 @@ class DeepseekV4FlashForCausalLM(nn.Module):
         self.out_hc_scale = nn.Parameter(torch.empty(1, dtype=mc.dtype), requires_grad=False)
         self.lm_head = nn.Parameter(torch.empty(c.vocab, c.hidden, dtype=mc.dtype), requires_grad=False)
         self.requests: dict[str, RequestRows] = {}
+        self._f32_cache: dict = {}
+        self._ar = None
         self.register_buffer("inv_freq_window", c.rope_inv_freq(False).to(self.embed.device), persistent=False)
         self.register_buffer("inv_freq_compressed", c.rope_inv_freq(True).to(self.embed.device), persistent=False)
         self.max_model_len = int(mc.max_model_len)
@@ -328,11 +343,12 @@ class DeepseekV4FlashForCausalLM(nn.Module):
         for name, t in weights:
             owner, attr = self._owner(self.param_name(name))
             target = getattr(owner, attr, None) if owner is not None else None
+            expert = attr in self._EXPERTS and isinstance(owner, V4Layer)
             if not isinstance(target, (torch.Tensor, BlockMatrix)) and not (
-                    attr in self._EXPERTS and isinstance(owner, V4Layer) and isinstance(t, GGUFTensor)):
+                    expert and (isinstance(t, GGUFTensor) or self.cfg.block_experts)):
                 continue
-            if isinstance(t, GGUFTensor):
-                if attr in self._EXPERTS and isinstance(owner, V4Layer):
+            if isinstance(t, GGUFTensor) or (expert and target is None):
+                if expert:
                     self._routed_experts(owner).load(self._EXPERTS[attr], t)
                     owner._parameters.pop(attr, None)
                     setattr(owner, attr, None)
@@ -357,11 +373,32 @@ class DeepseekV4FlashForCausalLM(nn.Module):
             consumed.add(name)
         if not consumed:
             self._init_synthetic()
+        self._f32_cache.clear()
+        for layer in self.layers:
+            if layer.hash_routed and bool(((layer.hash_table < 0) | (layer.hash_table >= self.cfg.experts)).any()):
+                raise ValueError("token-id routing table names an expert that does not exist")
         return consumed
 
     def _init_synthetic(self) -> None:
         g = torch.Generator().manual_seed(1000 + self.seed)
         c = self.cfg
+        dev = self.embed.device
+        if c.block_experts:
+            # the checkpoint family's formats, drawn on the device: IQ2_XXS gate / up, Q2_K down, Q8_0 projections
+            from ...loaders.gguf import GGUFTensor
+            for li, layer in enumerate(self.layers):
+                routed = self._routed_experts(layer)
+                for which, ty, rows, K in (("gate", 16, c.expert_inter, c.hidden), ("up", 16, c.expert_inter, c.hidden),
+                                           ("down", 10, c.hidden, c.expert_inter)):
+                    raw = gq.random_blocks(ty, c.experts * rows, K, 7919 * li + ty + len(which) + self.seed, 0.02, str(dev))
+                    routed.load(which, GGUFTensor(raw.view(c.experts, rows, -1), ty, (c.experts, rows, K)))
+                for attr in sorted(self._LINEAR - {"lm_head"}):
+                    p = getattr(layer, attr, None)
+                    if isinstance(p, torch.Tensor) and p.shape[1] % 32 == 0 and p.numel() >= 1 << 20:
+                        N, K = p.shape
+                        raw = gq.random_blocks(8, N, K, 104729 * li + len(attr) + N, 0.5 / math.sqrt(K) / 64, str(dev))
+                        layer._parameters.pop(attr, None)
+                        setattr(layer, attr, BlockMatrix(raw, 8, K, dev))
         for name, p in self.named_parameters():
             if name.endswith("norm"):
                 p.data.fill_(1.0)
@@ -383,11 +420,14 @@ class DeepseekV4FlashForCausalLM(nn.Module):
         layers = []
         for i in range(c.layers):
             r = c.ratios[i]
-            lr = LayerRows(window=torch.zeros(c.window, c.head_dim, dtype=torch.float32, device=device), ratio=r)
+            cap = 0 if r == 0 else 16
+            lr = LayerRows(pool=torch.zeros(c.window + cap, c.head_dim, dtype=torch.float32, device=device),
+                           window=c.window, ratio=r)
             if r > 0:
                 lr.comp_state = CompressorState.empty(c.head_dim, r, device)
             if r == 4:
                 lr.index_state = CompressorState.empty(128, 4, device)
+                lr.index_pool = torch.zeros(cap, 128, dtype=torch.float32, device=device)
             layers.append(lr)
         return RequestRows(layers)
 
@@ -398,26 +438,35 @@ class DeepseekV4FlashForCausalLM(nn.Module):
         return sum(r.bytes() for r in self.requests.values())
 
     # ------------------------------------------------------------------ a group of tokens, layer by layer
+    def _f32(self, owner, attr: str) -> torch.Tensor:
+        """fp32 copy of a small parameter (norm gains, hyper-connection tables, sinks, position biases), made once."""
+        key = (id(owner), attr)
+        t = self._f32_cache.get(key)
+        if t is None:
+            t = self._f32_cache[key] = getattr(owner, attr).detach().float().contiguous()
+        return t
+
+    def _arange(self, n: int) -> torch.Tensor:
+        if self._ar is None or self._ar.numel() < n:
+            self._ar = torch.arange(max(1024, 2 * n), dtype=torch.int32, device=self.embed.device)
+        return self._ar[:n]
+
     def _attention(self, layer: V4Layer, rows_of: list, h: torch.Tensor, pos: torch.Tensor, li: int) -> torch.Tensor:
         """``h`` ``[T, H]``: the projections run once for the whole group; the row appends, compressor steps
         and the attention itself walk the tokens in order (token t of a request sees the rows of tokens <= t)."""
-        c = self.cfg
-        T, D, rot = h.shape[0], c.head_dim, c.rotary_dim
-        x = _rms(h, layer.attn_norm, c.eps)
-        q_low = _rms(_lin(x, layer.q_a), layer.q_a_norm, c.eps)
-        q = _lin(q_low, layer.q_b).view(T, c.heads, D)
+        c, f = self.cfg, self._f32
+        T, D, W = h.shape[0], c.head_dim, c.window
         freq = self.inv_freq_compressed if layer.compressed else self.inv_freq_window
-        q = _rotate_tail(_rms(q, None, c.eps), pos, freq)
-        kv = _rotate_tail(_rms(_lin(x, layer.kv_proj), layer.kv_norm, c.eps), pos, freq)
-        kv = fp8_kv_qat(kv, D, rot)
+        x = nv.norm_rope(h, f(layer, "attn_norm"), None, None, c.eps)
+        q_low = nv.norm_rope(_lin(x, layer.q_a), f(layer, "q_a_norm"), None, None, c.eps)
+        q = nv.norm_rope(_lin(q_low, layer.q_b).view(T, c.heads, D), None, freq, pos, c.eps)
+        kv = nv.norm_rope(_lin(x, layer.kv_proj), f(layer, "kv_norm"), freq, pos, c.eps, fp8=True)
         if layer.compressed:
-            ckv, cgate, comp_ape = _lin(x, layer.comp_kv), _lin(x, layer.comp_gate), layer.comp_ape.float()
+            ckv, cgate, comp_ape = _lin(x, layer.comp_kv), _lin(x, layer.comp_gate), f(layer, "comp_ape")
         if layer.indexed:
-            ikv, igate, idx_ape = _lin(x, layer.idx_kv), _lin(x, layer.idx_gate), layer.idx_ape.float()
-            iq = _lin(q_low, layer.idx_q).view(T, c.indexer_heads, 128)
-            iq = indexer_qat(_rotate_tail(iq, pos, freq))
-            iw = _lin(x, layer.idx_w)
-        sinks = layer.sinks.float()
+            ikv, igate, idx_ape = _lin(x, layer.idx_kv), _lin(x, layer.idx_gate), f(layer, "idx_ape")
+            iq = iw = None                      # only needed once a request has more rows than the indexer keeps
+        sinks = f(layer, "sinks")
         scale = 1.0 / math.sqrt(D)
         out = torch.empty(T, c.heads, D, dtype=torch.float32, device=h.device)
         positions = pos.tolist()
@@ -425,44 +474,51 @@ class DeepseekV4FlashForCausalLM(nn.Module):
         for t in range(T):
             lr: LayerRows = rows_of[t].layers[li]
             p = positions[t]
-            lr.window[lr.count % c.window] = kv[t]
+            lr.pool[lr.count % W] = kv[t]
             lr.count += 1
-            rows = lr.window[:min(lr.count, c.window)]
-            if lr.compressed:
-                # rows emitted by earlier tokens; the fine layers keep the indexer's top-k of them
-                comp = torch.stack(lr.compressed)
-                if layer.indexed:
-                    scores = indexer_scores(iq[t], iw[t], torch.stack(lr.index_rows))
-                    comp = comp[indexer_topk(scores, c.indexer_topk)]
-                rows = torch.cat([rows, comp], 0)
-            out[t] = shared_kv_attention(q[t], rows.contiguous(), sinks, softmax_scale=scale)
+            n_win, n_comp = min(lr.count, W), lr.n_comp
+            index = None
+            if n_comp and layer.indexed and n_comp > c.indexer_topk:
+                # the fine layers keep the indexer's top-k of the rows emitted by earlier tokens
+                if iq is None:
+                    iq = indexer_qat(nv.norm_rope(_lin(q_low, layer.idx_q).view(T, c.indexer_heads, 128), None, freq, pos,
+                                                  c.eps, norm=False))
+                    iw = _lin(x, layer.idx_w)
+                keep = indexer_topk(indexer_scores(iq[t], iw[t], lr.index_rows), c.indexer_topk)
+                index = torch.cat([self._arange(n_win), keep.to(torch.int32) + W])
+            elif n_comp and n_win < W:
+                index = torch.cat([self._arange(n_win), self._arange(W + n_comp)[W:]])
+            if index is not None:
+                out[t] = shared_kv_attention(q[t], lr.pool, sinks, softmax_scale=scale, row_index=index)
+            else:
+                out[t] = shared_kv_attention(q[t], lr.pool[: n_win + n_comp], sinks, softmax_scale=scale)
             if layer.compressed:
-                lr.comp_state, emitted = compressor_step(lr.comp_state, ckv[t], cgate[t], comp_ape, p, D, r)
-                if layer.indexed:
-                    lr.index_state, idx_row = compressor_step(lr.index_state, ikv[t], igate[t], idx_ape, p, 128, 4)
+                emitted = nv.compressor_step_(lr.comp_state, ckv[t], cgate[t], comp_ape, p, D, r)
+                idx_row = nv.compressor_step_(lr.index_state, ikv[t], igate[t], idx_ape, p, 128, 4) if layer.indexed else None
                 if emitted is not None:
-                    at = torch.tensor([p + 1 - r], device=h.device)
-                    emitted = _rotate_tail(_rms(emitted, layer.comp_norm, c.eps).unsqueeze(0), at, freq)[0]
-                    lr.compressed.append(emitted)
-                    if layer.indexed:
-                        lr.index_rows.append(_rms(idx_row, layer.idx_norm, c.eps))
-        out = _rotate_tail(out, pos, freq, inverse=True)
+                    at = pos[t: t + 1] + (1 - r)
+                    emitted = nv.norm_rope(emitted.unsqueeze(0), f(layer, "comp_norm"), freq, at, c.eps, fp8=True)[0]
+                    if idx_row is not None:
+                        idx_row = indexer_qat(nv.norm_rope(idx_row.unsqueeze(0), f(layer, "idx_norm"), freq, at, c.eps))[0]
+                    lr.append_compressed(emitted, idx_row)
+        out = nv.norm_rope(out, None, freq, pos, c.eps, norm=False, inverse=True)
         gh = c.heads // c.o_groups
-        low = torch.einsum("grk,tgk->tgr", layer.o_a.float(), out.view(T, c.o_groups, gh * D))
+        og = out.view(T, c.o_groups, gh * D).to(layer.o_a.dtype)
+        low = torch.einsum("grk,tgk->tgr", layer.o_a, og).float()
         return _lin(low.reshape(T, -1), layer.o_b)
 
     def _ffn(self, layer: V4Layer, h: torch.Tensor, token_ids: torch.Tensor) -> torch.Tensor:
-        c = self.cfg
-        x = _rms(h, layer.ffn_norm, c.eps)
+        c, f = self.cfg, self._f32
+        x = nv.norm_rope(h, f(layer, "ffn_norm"), None, None, c.eps)
         if layer.hash_routed:
-            scores = torch.sqrt(torch.nn.functional.softplus(x @ layer.router.float().t()))
-            ids = hash_routed_expert_ids(layer.hash_table, token_ids).long()
+            scores = torch.sqrt(torch.nn.functional.softplus(x @ f(layer, "router").t()))
+            ids = layer.hash_table[:, token_ids].t().long()          # the table was validated when it was loaded
             w = scores.gather(1, ids)
             w = w / w.sum(-1, keepdim=True).clamp_min(1e-20) * c.routed_scale
         else:
-            ids, w = sqrt_softplus_router(x, layer.router, c.top_k, layer.router_bias, c.routed_scale)
+            ids, w = sqrt_softplus_router(x, f(layer, "router"), c.top_k, layer.router_bias, c.routed_scale)
             ids = ids.long()
-        xq = q8_k_roundtrip(x) if x.shape[-1] % 256 == 0 else x
+        xq = nv.q8k(x) if x.shape[-1] % 256 == 0 else x
 
         def mlp(g_w, u_w, d_w, inp):
             g, u = _lin(inp, g_w), _lin(inp, u_w)
@@ -483,7 +539,7 @@ class DeepseekV4FlashForCausalLM(nn.Module):
     def forward_tokens(self, entries: list) -> torch.Tensor:
         """``entries``: (request rows, token id) pairs; the tokens of one request appear in prompt order.  Runs
         them through every layer and returns the final hidden vectors ``[T, H]`` (fp32)."""
-        c = self.cfg
+        c, f = self.cfg, self._f32
         dev = self.embed.device
         seen: dict[int, int] = {}
         positions = []
@@ -497,21 +553,19 @@ class DeepseekV4FlashForCausalLM(nn.Module):
         streams = self.embed[ids].float().unsqueeze(1).repeat(1, c.hc, 1)          # [T, hc, H]
         for li, layer in enumerate(self.layers):
             with stage("v4_attention"):
-                st = hyper_connection_pre(streams, layer.hc_attn_fn, layer.hc_attn_base, layer.hc_attn_scale, eps=c.eps)
-                streams = hyper_connection_post(self._attention(layer, rows_of, st.mixed, pos, li), streams, st)
+                st = nv.hc_pre(streams, f(layer, "hc_attn_fn"), f(layer, "hc_attn_base"), f(layer, "hc_attn_scale"), c.eps)
+                streams = nv.hc_post(self._attention(layer, rows_of, st.mixed, pos, li), streams, st)
             with stage("v4_experts"):
-                st = hyper_connection_pre(streams, layer.hc_ffn_fn, layer.hc_ffn_base, layer.hc_ffn_scale, eps=c.eps)
-                streams = hyper_connection_post(self._ffn(layer, st.mixed, ids), streams, st)
+                st = nv.hc_pre(streams, f(layer, "hc_ffn_fn"), f(layer, "hc_ffn_base"), f(layer, "hc_ffn_scale"), c.eps)
+                streams = nv.hc_post(self._ffn(layer, st.mixed, ids), streams, st)
         done = set()
         for rows, _ in entries:
             if id(rows) not in done:
                 rows.pos += seen[id(rows)]
                 done.add(id(rows))
-        # collapse the streams: sigmoid gains from the normalised flattened streams, then the final norm
-        flat = streams.reshape(streams.shape[0], -1)
-        flat = flat * torch.rsqrt(flat.pow(2).mean(-1, keepdim=True) + c.eps)
-        gains = torch.sigmoid(_lin(flat, self.out_hc_fn) * self.out_hc_scale.float()[0] + self.out_hc_base.float()) + 1e-6
-        return _rms((gains.unsqueeze(-1) * streams).sum(1), self.final_norm, c.eps)
+        # collapse the streams (sigmoid gains from the normalised flattened streams), then the final norm
+        hidden = nv.hc_collapse(streams, f(self, "out_hc_fn"), f(self, "out_hc_base"), f(self, "out_hc_scale"), c.eps)
+        return nv.norm_rope(hidden, f(self, "final_norm"), None, None, c.eps)
 
     def _next_tokens(self, hidden: torch.Tensor) -> list[int]:
         return torch.argmax(_lin(hidden, self.lm_head), dim=-1).tolist()

@@ -59,19 +59,19 @@ def test_chunked_prefill_equals_one_chunk(llm):
     two = model.prefill_request("b", PROMPTS[0][13:], 13, True)
     assert one == two
     ra, rb = model.requests["a"], model.requests["b"]
-    assert (ra.layers[0].window - rb.layers[0].window).abs().gt(1e-4).float().mean() < 0.002
+    assert (ra.layers[0].pool - rb.layers[0].pool).abs().gt(1e-4).float().mean() < 0.002
     assert ra.pos == rb.pos == len(PROMPTS[0])
     for la, lb in zip(ra.layers, rb.layers):
         # the fp8 round trip may flip a rounding step where the two GEMM shapes differ in the last bit, and a
         # flipped step moves the later layers by a little
-        assert (la.window - lb.window).abs().mean() < 5e-3
-        assert len(la.compressed) == len(lb.compressed)
+        assert (la.pool[: la.window] - lb.pool[: lb.window]).abs().mean() < 5e-3
+        assert la.n_comp == lb.n_comp
     # compressed layers emitted one row per `ratio` tokens, more than the indexer keeps
     cfg = model.cfg
     assert cfg.ratios == (0, 0, 4, 8)
-    assert len(ra.layers[2].compressed) == len(ra.layers[2].index_rows) == len(PROMPTS[0]) // 4 > cfg.indexer_topk
-    assert len(ra.layers[3].compressed) == len(PROMPTS[0]) // 8 and not ra.layers[3].index_rows
-    assert not ra.layers[0].compressed and not ra.layers[1].compressed
+    assert ra.layers[2].n_comp == len(ra.layers[2].index_rows) == len(PROMPTS[0]) // 4 > cfg.indexer_topk
+    assert ra.layers[3].n_comp == len(PROMPTS[0]) // 8 and ra.layers[3].index_pool is None
+    assert ra.layers[0].n_comp == ra.layers[1].n_comp == 0
     with pytest.raises(RuntimeError):
         model.prefill_request("b", [5, 6], 3, True)   # a chunk that does not continue where the rows end
     assert model.release_request("a") and model.release_request("b") and not model.release_request("a")
@@ -229,3 +229,73 @@ def test_gguf_checkpoint_on_gpu_matches_cpu(llm, tmp_path):
     want, got = _tokens(cpu, PROMPTS, 6), _tokens(gpu, PROMPTS, 6)
     agree = sum(a == b for w, g in zip(want, got) for a, b in zip(w, g)) / sum(len(w) for w in want)
     assert got[0][0] == want[0][0] and agree >= 0.5, (want, got)
+
+
+@pytest.mark.gpu
+def test_fused_token_kernels_match_their_pytorch_forms():
+    """Every fused per-token kernel against the PyTorch formulation it replaces (fp32 on the CPU)."""
+    from litevllm_b200.models.deepseek_v4_flash import native as nv
+    from litevllm_b200.models.deepseek_v4_flash.attention import CompressorState
+    from litevllm_b200.models.deepseek_v4_flash.model import V4Config
+    from litevllm_b200.models.presets import PRESETS
+    g = torch.Generator().manual_seed(11)
+    T, hc, H = 5, 4, 512
+    n_mix = 2 * hc + hc * hc
+
+    def both(fn, *args):
+        cpu = fn(*args)
+        gpu = fn(*[a.cuda() if isinstance(a, torch.Tensor) else a for a in args])
+        return cpu, gpu
+
+    def close(a, b, tol=2e-4, what=""):
+        torch.testing.assert_close(b.cpu(), a, rtol=tol, atol=tol, msg=lambda m: f"{what}: {m}")
+
+    streams = torch.randn(T, hc, H, generator=g)
+    fn_w = torch.randn(hc * H, n_mix, generator=g) / 30
+    base, scale = torch.randn(n_mix, generator=g) * 0.3, torch.tensor([0.7, 1.3, 0.9])
+    s_cpu, s_gpu = both(lambda *a: nv.hc_pre(*a, 1e-6), streams, fn_w, base, scale)
+    close(s_cpu.mixed, s_gpu.mixed, what="hc_pre mixed")
+    close(s_cpu.post, s_gpu.post, what="hc_pre post")
+    close(s_cpu.combine, s_gpu.combine, what="hc_pre combine")
+    assert (s_gpu.combine.sum(-1) - 1).abs().max() < 1e-3 and (s_gpu.combine.sum(-2) - 1).abs().max() < 1e-3
+    out = torch.randn(T, H, generator=g)
+    n_cpu = nv.hc_post(out, streams, s_cpu)
+    n_gpu = nv.hc_post(out.cuda(), streams.cuda(), s_gpu)
+    close(n_cpu, n_gpu, what="hc_post")
+    ofn, obase, oscale = torch.randn(hc, hc * H, generator=g) / 30, torch.randn(hc, generator=g), torch.tensor([0.8])
+    c_cpu, c_gpu = both(lambda *a: nv.hc_collapse(*a, 1e-6), streams, ofn, obase, oscale)
+    close(c_cpu, c_gpu, what="hc_collapse")
+
+    cfg = V4Config.from_hf(PRESETS["tiny-deepseek-v4-flash-test"])
+    pos = torch.tensor([0, 3, 17, 200, 4001])
+    for compressed in (False, True):
+        freq = cfg.rope_inv_freq(compressed)
+        x = torch.randn(T, 3, 512, generator=g) * 2
+        w = torch.rand(512, generator=g) + 0.5
+        for kw in (dict(norm=True), dict(norm=False, inverse=True), dict(norm=True, fp8=True)):
+            wt = None if kw.get("inverse") else w
+            a, b = both(lambda xx, ww, ff, pp: nv.norm_rope(xx, ww, ff, pp, 1e-6, **kw), x, wt, freq, pos)
+            if kw.get("fp8"):       # a rounding step may flip where the two sides differ in the last bit
+                assert ((a - b.cpu()).abs() > 1e-3 * a.abs().clamp_min(1e-2)).float().mean() < 0.002
+            else:
+                close(a, b, tol=2e-3, what=f"norm_rope {kw} compressed={compressed}")   # fp32 angles on the CPU side
+    a, b = both(lambda xx, ww: nv.norm_rope(xx, ww, None, None, 1e-6), torch.randn(7, 256, generator=g), torch.rand(256, generator=g))
+    close(a, b, what="plain norm")
+
+    for ratio, D in ((4, 512), (8, 512), (4, 128)):
+        width = (2 if ratio == 4 else 1) * D
+        ape = torch.randn(ratio, width, generator=g)
+        st_c, st_g = CompressorState.empty(D, ratio, "cpu"), CompressorState.empty(D, ratio, "cuda")
+        for tok in range(3 * ratio + 1):
+            kv, sc = torch.randn(width, generator=g), torch.randn(width, generator=g)
+            e_c = nv.compressor_step_(st_c, kv, sc, ape, tok, D, ratio)
+            e_g = nv.compressor_step_(st_g, kv.cuda(), sc.cuda(), ape.cuda(), tok, D, ratio)
+            assert (e_c is None) == (e_g is None) == ((tok + 1) % ratio != 0)
+            if e_c is not None:
+                close(e_c, e_g, what=f"compressor ratio {ratio} token {tok}")
+        close(st_c.kv, st_g.kv, what="compressor state")
+
+    x = torch.randn(6, 512, generator=g)
+    x[2, :256] = 0
+    a, b = both(nv.q8k, x)
+    close(a, b, tol=1e-6, what="q8k")
