@@ -25,6 +25,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=16)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--vocab", type=int, default=32768)
+    ap.add_argument("--host-profile", action="store_true", help="print the host-side profile of extra decode steps")
     a = ap.parse_args()
     from litevllm_b200 import LLM
     from litevllm_b200.models.deepseek_v4_flash.model import BlockMatrix
@@ -73,10 +74,20 @@ def main() -> None:
 
     t_decode, last = timed(decode_steps)
     ms_step = t_decode / a.steps
+    if a.host_profile:
+        import cProfile
+        import pstats
+        prof = cProfile.Profile()
+        prof.enable()
+        decode_steps()
+        torch.cuda.synchronize(dev)
+        prof.disable()
+        pstats.Stats(prof, stream=sys.stderr).sort_stats("tottime").print_stats(28)
     weights = sum(p.numel() * p.element_size() for p in model.parameters())
     for layer in model.layers:
         weights += sum(v.numel() for v in layer.routed.raw.values()) if layer.routed is not None else 0
         weights += sum(getattr(layer, n).nbytes() for n in model._LINEAR if isinstance(getattr(layer, n, None), BlockMatrix))
+    weights += sum(m.nbytes() for m, _ in model._merged.values() if isinstance(m, BlockMatrix))
     print(json.dumps({
         "case": "v4_flash_shaped_step", "layers": a.layers, "batch": a.batch, "prompt_len": a.prompt_len,
         "prefill_ms_per_token": round(t_prefill / (a.batch * a.prompt_len), 3),

@@ -15,6 +15,9 @@ from dataclasses import dataclass
 
 import torch
 
+from ... import ops
+from ...ops import _lib
+
 
 def _native(*tensors) -> bool:
     return all(t is None or (t.is_cuda and t.dtype in (torch.float32, torch.int32)) for t in tensors)
@@ -22,22 +25,27 @@ def _native(*tensors) -> bool:
 
 def shared_kv_attention(queries: torch.Tensor, rows: torch.Tensor, sinks: torch.Tensor | None = None,
                         softmax_scale: float | None = None, row_index: torch.Tensor | None = None,
-                        page_table: torch.Tensor | None = None, page_rows: int = 0) -> torch.Tensor:
+                        page_table: torch.Tensor | None = None, page_rows: int = 0,
+                        out: torch.Tensor | None = None) -> torch.Tensor:
     """queries ``[heads, D]``; ``rows`` ``[n, D]`` (or the whole pool when ``row_index`` / ``page_table``
-    address it); returns ``[heads, D]`` fp32."""
+    address it); returns ``[heads, D]`` fp32 (written into ``out`` when given)."""
     heads, D = queries.shape
     scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
     n_rows = int(row_index.shape[0]) if row_index is not None else (
         rows.shape[0] if page_table is None else page_rows * int(page_table.shape[0]))
     if _native(queries, rows, sinks, row_index, page_table) and D % 128 == 0 and D <= 512:
-        from ... import ops
-        from ...ops import _lib
-        out = torch.empty(heads, D, dtype=torch.float32, device=queries.device)
+        if out is None or not out.is_contiguous():
+            dst = torch.empty(heads, D, dtype=torch.float32, device=queries.device)
+        else:
+            dst = out
         rc = _lib.kernels().fi_dsv4_shared_kv_attention(
             ops._p(queries.contiguous()), ops._p(rows), ops._p(row_index), ops._p(page_table), page_rows,
-            ops._p(sinks), heads, n_rows, D, scale, ops._p(out), ops._stream())
+            ops._p(sinks), heads, n_rows, D, scale, ops._p(dst), ops._stream())
         _lib.check(rc, "fi_dsv4_shared_kv_attention")
-        return out
+        if out is not None and dst is not out:
+            out.copy_(dst)
+            return out
+        return dst
     logical = row_index.long() if row_index is not None else torch.arange(n_rows, device=rows.device)
     if page_table is not None:
         logical = page_table.long()[logical // page_rows] * page_rows + logical % page_rows
@@ -46,7 +54,11 @@ def shared_kv_attention(queries: torch.Tensor, rows: torch.Tensor, sinks: torch.
     if sinks is not None:
         logits = torch.cat([logits, sinks.float().reshape(-1, 1)], dim=-1)
     probs = torch.softmax(logits, dim=-1)
-    return probs[:, :kv.shape[0]] @ kv
+    res = probs[:, :kv.shape[0]] @ kv
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
 
 
 def compressed_row_attention(queries, compressed_rows, selected: torch.Tensor, sinks=None, softmax_scale=None):
@@ -58,8 +70,6 @@ def update_latent_cache(pool: torch.Tensor, rows: torch.Tensor, positions: torch
                         page_table: torch.Tensor | None = None, page_rows: int = 0) -> None:
     """Write latent rows at logical positions through the page table."""
     if _native(pool, rows, positions, page_table):
-        from ... import ops
-        from ...ops import _lib
         rc = _lib.kernels().fi_dsv4_cache_update(ops._p(rows.contiguous()), ops._p(positions), ops._p(page_table),
                                                  page_rows, rows.shape[0], rows.shape[1], ops._p(pool), ops._stream())
         _lib.check(rc, "fi_dsv4_cache_update")
@@ -76,8 +86,6 @@ def indexer_scores(indexer_query: torch.Tensor, indexer_weights: torch.Tensor, c
     H, d = indexer_query.shape
     s = float(scale) if scale is not None else 1.0 / math.sqrt(H * d)
     if _native(indexer_query, indexer_weights, compressed_rows) and d == 128 and compressed_rows.shape[0] > 0:
-        from ... import ops
-        from ...ops import _lib
         out = torch.empty(compressed_rows.shape[0], dtype=torch.float32, device=indexer_query.device)
         rc = _lib.kernels().fi_dsv4_indexer_scores(ops._p(indexer_query.contiguous()), ops._p(indexer_weights),
                                                    ops._p(compressed_rows.contiguous()), compressed_rows.shape[0], H, s,

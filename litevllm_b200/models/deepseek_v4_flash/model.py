@@ -193,7 +193,7 @@ class BlockMatrix:
         return x.float() @ self.dense().t()
 
     def nbytes(self) -> int:
-        return self.raw.numel()
+        return 0 if self.raw is None else self.raw.numel()
 
 
 def _lin(x: torch.Tensor, w) -> torch.Tensor:
@@ -265,6 +265,7 @@ class DeepseekV4FlashForCausalLM(nn.Module):
         self.lm_head = nn.Parameter(torch.empty(c.vocab, c.hidden, dtype=mc.dtype), requires_grad=False)
         self.requests: dict[str, RequestRows] = {}
         self._f32_cache: dict = {}
+        self._merged: dict = {}
         self._ar = None
         self.register_buffer("inv_freq_window", c.rope_inv_freq(False).to(self.embed.device), persistent=False)
         self.register_buffer("inv_freq_compressed", c.rope_inv_freq(True).to(self.embed.device), persistent=False)
@@ -374,6 +375,7 @@ class DeepseekV4FlashForCausalLM(nn.Module):
         if not consumed:
             self._init_synthetic()
         self._f32_cache.clear()
+        self._merged.clear()
         for layer in self.layers:
             if layer.hash_routed and bool(((layer.hash_table < 0) | (layer.hash_table >= self.cfg.experts)).any()):
                 raise ValueError("token-id routing table names an expert that does not exist")
@@ -446,30 +448,57 @@ class DeepseekV4FlashForCausalLM(nn.Module):
             t = self._f32_cache[key] = getattr(owner, attr).detach().float().contiguous()
         return t
 
+    def _project(self, layer: V4Layer, names: tuple, x: torch.Tensor) -> list:
+        """Several projections of the same input as one product: the weights (all dense, or all blocks of one
+        format) are stacked row-wise once per layer, the result is split into views."""
+        key = (id(layer), names)
+        merged = self._merged.get(key)
+        if merged is None:
+            ws = [getattr(layer, n) for n in names]
+            sizes = [w.N if isinstance(w, BlockMatrix) else w.shape[0] for w in ws]
+            if all(isinstance(w, BlockMatrix) for w in ws) and len({(w.ggml_type, w.K) for w in ws}) == 1:
+                stacked = BlockMatrix(torch.cat([w.raw for w in ws]), ws[0].ggml_type, ws[0].K, ws[0].raw.device)
+            elif all(isinstance(w, torch.Tensor) for w in ws) and x.is_cuda:
+                stacked = torch.cat([w.detach() for w in ws])
+            else:
+                stacked = False
+            merged = self._merged[key] = (stacked, sizes)
+            if stacked is not False and x.is_cuda:       # the single matrices are not used again on this device
+                for n, w in zip(names, ws):
+                    if isinstance(w, BlockMatrix):
+                        w.raw = None
+        stacked, sizes = merged
+        if stacked is False:
+            return [_lin(x, getattr(layer, n)) for n in names]
+        return list(_lin(x, stacked).split(sizes, dim=-1))
+
     def _arange(self, n: int) -> torch.Tensor:
         if self._ar is None or self._ar.numel() < n:
             self._ar = torch.arange(max(1024, 2 * n), dtype=torch.int32, device=self.embed.device)
         return self._ar[:n]
 
-    def _attention(self, layer: V4Layer, rows_of: list, h: torch.Tensor, pos: torch.Tensor, li: int) -> torch.Tensor:
+    def _attention(self, layer: V4Layer, rows_of: list, h: torch.Tensor, pos: torch.Tensor, positions: list,
+                   li: int) -> torch.Tensor:
         """``h`` ``[T, H]``: the projections run once for the whole group; the row appends, compressor steps
         and the attention itself walk the tokens in order (token t of a request sees the rows of tokens <= t)."""
         c, f = self.cfg, self._f32
         T, D, W = h.shape[0], c.head_dim, c.window
         freq = self.inv_freq_compressed if layer.compressed else self.inv_freq_window
         x = nv.norm_rope(h, f(layer, "attn_norm"), None, None, c.eps)
-        q_low = nv.norm_rope(_lin(x, layer.q_a), f(layer, "q_a_norm"), None, None, c.eps)
+        names = ("q_a", "kv_proj") + (("comp_kv", "comp_gate") if layer.compressed else ()) + \
+            (("idx_kv", "idx_gate", "idx_w") if layer.indexed else ())
+        proj = self._project(layer, names, x)           # everything that reads the normed layer input
+        q_low = nv.norm_rope(proj[0], f(layer, "q_a_norm"), None, None, c.eps)
         q = nv.norm_rope(_lin(q_low, layer.q_b).view(T, c.heads, D), None, freq, pos, c.eps)
-        kv = nv.norm_rope(_lin(x, layer.kv_proj), f(layer, "kv_norm"), freq, pos, c.eps, fp8=True)
+        kv = nv.norm_rope(proj[1], f(layer, "kv_norm"), freq, pos, c.eps, fp8=True)
         if layer.compressed:
-            ckv, cgate, comp_ape = _lin(x, layer.comp_kv), _lin(x, layer.comp_gate), f(layer, "comp_ape")
+            ckv, cgate, comp_ape = proj[2], proj[3], f(layer, "comp_ape")
         if layer.indexed:
-            ikv, igate, idx_ape = _lin(x, layer.idx_kv), _lin(x, layer.idx_gate), f(layer, "idx_ape")
-            iq = iw = None                      # only needed once a request has more rows than the indexer keeps
+            ikv, igate, iw, idx_ape = proj[4], proj[5], proj[6], f(layer, "idx_ape")
+            iq = None                           # only needed once a request has more rows than the indexer keeps
         sinks = f(layer, "sinks")
         scale = 1.0 / math.sqrt(D)
         out = torch.empty(T, c.heads, D, dtype=torch.float32, device=h.device)
-        positions = pos.tolist()
         r = layer.ratio
         for t in range(T):
             lr: LayerRows = rows_of[t].layers[li]
@@ -483,15 +512,14 @@ class DeepseekV4FlashForCausalLM(nn.Module):
                 if iq is None:
                     iq = indexer_qat(nv.norm_rope(_lin(q_low, layer.idx_q).view(T, c.indexer_heads, 128), None, freq, pos,
                                                   c.eps, norm=False))
-                    iw = _lin(x, layer.idx_w)
                 keep = indexer_topk(indexer_scores(iq[t], iw[t], lr.index_rows), c.indexer_topk)
                 index = torch.cat([self._arange(n_win), keep.to(torch.int32) + W])
             elif n_comp and n_win < W:
                 index = torch.cat([self._arange(n_win), self._arange(W + n_comp)[W:]])
             if index is not None:
-                out[t] = shared_kv_attention(q[t], lr.pool, sinks, softmax_scale=scale, row_index=index)
+                shared_kv_attention(q[t], lr.pool, sinks, softmax_scale=scale, row_index=index, out=out[t])
             else:
-                out[t] = shared_kv_attention(q[t], lr.pool[: n_win + n_comp], sinks, softmax_scale=scale)
+                shared_kv_attention(q[t], lr.pool[: n_win + n_comp], sinks, softmax_scale=scale, out=out[t])
             if layer.compressed:
                 emitted = nv.compressor_step_(lr.comp_state, ckv[t], cgate[t], comp_ape, p, D, r)
                 idx_row = nv.compressor_step_(lr.index_state, ikv[t], igate[t], idx_ape, p, 128, 4) if layer.indexed else None
@@ -512,9 +540,12 @@ class DeepseekV4FlashForCausalLM(nn.Module):
         x = nv.norm_rope(h, f(layer, "ffn_norm"), None, None, c.eps)
         if layer.hash_routed:
             scores = torch.sqrt(torch.nn.functional.softplus(x @ f(layer, "router").t()))
-            ids = layer.hash_table[:, token_ids].t().long()          # the table was validated when it was loaded
-            w = scores.gather(1, ids)
-            w = w / w.sum(-1, keepdim=True).clamp_min(1e-20) * c.routed_scale
+            key = (id(layer), "hash_rows")
+            table = self._f32_cache.get(key)                          # [vocab, top_k] int64, validated at load
+            if table is None:
+                table = self._f32_cache[key] = layer.hash_table.t().long().contiguous()
+            ids = table[token_ids]
+            w = torch.nn.functional.normalize(scores.gather(1, ids), p=1.0, dim=-1, eps=1e-20) * c.routed_scale
         else:
             ids, w = sqrt_softplus_router(x, f(layer, "router"), c.top_k, layer.router_bias, c.routed_scale)
             ids = ids.long()
@@ -526,7 +557,10 @@ class DeepseekV4FlashForCausalLM(nn.Module):
                 g, u = g.clamp(max=c.swiglu_clamp), u.clamp(-c.swiglu_clamp, c.swiglu_clamp)
             return _lin(torch.nn.functional.silu(g) * u, d_w)
 
-        y = mlp(layer.s_gate, layer.s_up, layer.s_down, x)
+        g, u = self._project(layer, ("s_gate", "s_up"), x)
+        if c.swiglu_clamp > 0:
+            g, u = g.clamp(max=c.swiglu_clamp), u.clamp(-c.swiglu_clamp, c.swiglu_clamp)
+        y = _lin(torch.nn.functional.silu(g) * u, layer.s_down)
         if layer.routed is not None:
             act = torch.bfloat16 if x.is_cuda else torch.float32
             return y + layer.routed(xq.to(act).contiguous(), ids.to(torch.int32).contiguous(), w.float().contiguous()).float()
@@ -554,7 +588,7 @@ class DeepseekV4FlashForCausalLM(nn.Module):
         for li, layer in enumerate(self.layers):
             with stage("v4_attention"):
                 st = nv.hc_pre(streams, f(layer, "hc_attn_fn"), f(layer, "hc_attn_base"), f(layer, "hc_attn_scale"), c.eps)
-                streams = nv.hc_post(self._attention(layer, rows_of, st.mixed, pos, li), streams, st)
+                streams = nv.hc_post(self._attention(layer, rows_of, st.mixed, pos, positions, li), streams, st)
             with stage("v4_experts"):
                 st = nv.hc_pre(streams, f(layer, "hc_ffn_fn"), f(layer, "hc_ffn_base"), f(layer, "hc_ffn_scale"), c.eps)
                 streams = nv.hc_post(self._ffn(layer, st.mixed, ids), streams, st)

@@ -6,35 +6,41 @@ from __future__ import annotations
 
 import torch
 
+from ... import ops
+from ...ops import _lib
 from .attention import CompressorState, compressor_step
 from .hyper_connection import HyperConnectionState, hyper_connection_post, hyper_connection_pre
 from .ops import fp8_kv_qat, q8_k_roundtrip
 
 
 def _gpu(*ts) -> bool:
-    return all(t is None or (t.is_cuda and t.dtype == torch.float32) for t in ts)
+    for t in ts:
+        if t is not None and not (t.is_cuda and t.dtype == torch.float32):
+            return False
+    return True
+
+
+_lib_handle = None
 
 
 def _k():
-    from ...ops import _lib
-    return _lib.kernels()
+    global _lib_handle
+    if _lib_handle is None:
+        _lib_handle = _lib.kernels()
+    return _lib_handle
 
 
 def _call(rc: int, what: str) -> None:
-    from ... import ops
-    from ...ops import _lib
-    _lib.check(rc, what)
-    ops._count()
+    if rc != 0:
+        _lib.check(rc, what)
+    ops._launches[0] += 1
 
 
 def _p(t):
-    from ... import ops
-    return ops._p(t)
+    return None if t is None else t.data_ptr()
 
 
-def _s():
-    from ... import ops
-    return ops._stream()
+_s = ops._stream
 
 
 def rms(x: torch.Tensor, w: torch.Tensor | None, eps: float) -> torch.Tensor:

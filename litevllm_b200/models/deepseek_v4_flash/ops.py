@@ -4,6 +4,9 @@ from __future__ import annotations
 
 import torch
 
+from ... import ops
+from ...ops import _lib
+
 _E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
 
 
@@ -46,8 +49,6 @@ def indexer_qat(rows: torch.Tensor) -> torch.Tensor:
     """Hadamard-128 then the FP4 round trip (block 32) for indexer rows ``[..., 128]``; a CUDA fp32
     tensor runs the native kernel."""
     if rows.is_cuda:
-        from ... import ops
-        from ...ops import _lib
         out = rows.float().contiguous().clone().view(-1, 128)
         _lib.check(_lib.kernels().fi_dsv4_indexer_qat(ops._p(out), out.shape[0], ops._stream()), "fi_dsv4_indexer_qat")
         return out.view(rows.shape)

@@ -73,7 +73,15 @@ def _count(n: int = 1) -> None:
 _scratch: dict[tuple, torch.Tensor] = {}
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> int:
+    """Handle of the current CUDA stream of the current device (the raw query: building a ``torch.cuda.Stream``
+    object per native call costs several microseconds of host time)."""
+    if _raw_stream is not None:
+        return _raw_stream(_raw_device() if _raw_device is not None else torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
