@@ -58,10 +58,11 @@ def main() -> None:
     model.prefill_request("warm", prompts[0][:16], 0, True)          # lazy allocations, kernel attributes
     model.release_request("warm")
     rids = [f"r{i}" for i in range(a.batch)]
-    t_prefill, last = 0.0, []
+    t_prefill, last, per_request = 0.0, [], []
     for rid, p in zip(rids, prompts):
         ms, tok = timed(lambda: model.prefill_request(rid, p, 0, True))
         t_prefill += ms
+        per_request.append(round(ms, 1))
         last.append(tok)
     for _ in range(a.warmup):
         last = model.decode_tokens_batch(rids, last)
@@ -90,6 +91,7 @@ def main() -> None:
     weights += sum(m.nbytes() for m, _ in model._merged.values() if isinstance(m, BlockMatrix))
     print(json.dumps({
         "case": "v4_flash_shaped_step", "layers": a.layers, "batch": a.batch, "prompt_len": a.prompt_len,
+        "prefill_ms_per_request": per_request,
         "prefill_ms_per_token": round(t_prefill / (a.batch * a.prompt_len), 3),
         "prefill_ms_per_token_per_layer": round(t_prefill / (a.batch * a.prompt_len * a.layers), 4),
         "decode_ms_per_step": round(ms_step, 3), "decode_ms_per_step_per_layer": round(ms_step / a.layers, 4),

@@ -61,6 +61,34 @@ def shared_kv_attention(queries: torch.Tensor, rows: torch.Tensor, sinks: torch.
     return res
 
 
+def shared_kv_attention_run(queries: torch.Tensor, lin: torch.Tensor, comp: torch.Tensor, spans: torch.Tensor,
+                            sel: torch.Tensor | None = None, sinks: torch.Tensor | None = None,
+                            softmax_scale: float | None = None) -> torch.Tensor:
+    """A run of consecutive tokens of one request at once.  queries ``[T, heads, D]``; token t attends the window
+    rows ``lin[a0:a0 + na]`` and ``nb`` compressed rows of ``comp`` (the first ``nb``, or ``sel[t, :nb]``), where
+    ``(a0, na, nb) = spans[:, t]`` (int32 ``[3, T]``).  Returns ``[T, heads, D]`` fp32."""
+    T, heads, D = queries.shape
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    if _native(queries, lin, comp, spans, sel, sinks) and D % 128 == 0 and D <= 512 and T <= 65535:
+        out = torch.empty(T, heads, D, dtype=torch.float32, device=queries.device)
+        spans = spans.contiguous()
+        rc = _lib.kernels().fi_dsv4_shared_kv_attention_run(
+            ops._p(queries.contiguous()), ops._p(lin), ops._p(comp), spans[0].data_ptr(), spans[1].data_ptr(),
+            spans[2].data_ptr(), ops._p(sel), 0 if sel is None else sel.stride(0), ops._p(sinks), T, heads, D, scale,
+            ops._p(out), ops._stream())
+        _lib.check(rc, "fi_dsv4_shared_kv_attention_run")
+        return out
+    out = torch.empty(T, heads, D, dtype=torch.float32, device=queries.device)
+    host = spans.tolist()
+    for t in range(T):
+        a0, na, nb = host[0][t], host[1][t], host[2][t]
+        rows = lin[a0:a0 + na]
+        if nb:
+            rows = torch.cat([rows, comp[sel[t, :nb].long()] if sel is not None else comp[:nb]], 0)
+        out[t] = shared_kv_attention(queries[t], rows.contiguous(), sinks, softmax_scale=scale)
+    return out
+
+
 def compressed_row_attention(queries, compressed_rows, selected: torch.Tensor, sinks=None, softmax_scale=None):
     """Attention over the selected compressed rows only (indexer top-k)."""
     return shared_kv_attention(queries, compressed_rows, sinks, softmax_scale, row_index=selected.to(torch.int32))

@@ -32,7 +32,8 @@ from dataclasses import dataclass, field
 import torch
 from torch import nn
 
-from .attention import CompressorState, compressor_step, indexer_scores, indexer_topk, shared_kv_attention
+from .attention import (CompressorState, indexer_scores, indexer_topk, shared_kv_attention,
+                        shared_kv_attention_run)
 from . import native as nv
 from .moe import hash_routed_expert_ids, sqrt_softplus_router
 from ...utils.profiling import stage
@@ -149,6 +150,23 @@ class LayerRows:
         if index_row is not None:
             self.index_pool[self.n_comp] = index_row
         self.n_comp += 1
+
+    def append_compressed_many(self, rows: torch.Tensor, index_rows: torch.Tensor | None) -> None:
+        n = rows.shape[0]
+        cap = self.pool.shape[0] - self.window
+        if self.n_comp + n > cap:
+            new_cap = max(16, 2 * cap, self.n_comp + n)
+            grown = torch.zeros(self.window + new_cap, self.pool.shape[1], dtype=self.pool.dtype, device=self.pool.device)
+            grown[: self.pool.shape[0]] = self.pool
+            self.pool = grown
+            if self.index_pool is not None:
+                gi = torch.zeros(new_cap, 128, dtype=torch.float32, device=self.pool.device)
+                gi[:cap] = self.index_pool
+                self.index_pool = gi
+        self.pool[self.window + self.n_comp: self.window + self.n_comp + n] = rows
+        if index_rows is not None:
+            self.index_pool[self.n_comp: self.n_comp + n] = index_rows
+        self.n_comp += n
 
     @property
     def compressed(self) -> torch.Tensor:
@@ -500,8 +518,25 @@ class DeepseekV4FlashForCausalLM(nn.Module):
         scale = 1.0 / math.sqrt(D)
         out = torch.empty(T, c.heads, D, dtype=torch.float32, device=h.device)
         r = layer.ratio
-        for t in range(T):
+        t = 0
+        while t < T:
+            t1 = t + 1
+            while t1 < T and rows_of[t1] is rows_of[t]:
+                t1 += 1
             lr: LayerRows = rows_of[t].layers[li]
+            if t1 - t >= 2:
+                # a run of consecutive tokens of one request (a prefill chunk): compressor windows, row
+                # post-processing, indexer selection and attention each run once for the whole run
+                run = slice(t, t1)
+                if layer.indexed and iq is None and lr.n_comp + (t1 - t + 3) // 4 > c.indexer_topk:
+                    iq = indexer_qat(nv.norm_rope(_lin(q_low, layer.idx_q).view(T, c.indexer_heads, 128), None, freq, pos,
+                                                  c.eps, norm=False))
+                self._attention_run(layer, lr, positions[t], q[run], kv[run],
+                                    (ckv[run], cgate[run], comp_ape) if layer.compressed else None,
+                                    (ikv[run], igate[run], idx_ape, None if iq is None else iq[run], iw[run]) if layer.indexed else None,
+                                    freq, sinks, scale, out[run])
+                t = t1
+                continue
             p = positions[t]
             lr.pool[lr.count % W] = kv[t]
             lr.count += 1
@@ -529,11 +564,73 @@ class DeepseekV4FlashForCausalLM(nn.Module):
                     if idx_row is not None:
                         idx_row = indexer_qat(nv.norm_rope(idx_row.unsqueeze(0), f(layer, "idx_norm"), freq, at, c.eps))[0]
                     lr.append_compressed(emitted, idx_row)
+            t = t1
         out = nv.norm_rope(out, None, freq, pos, c.eps, norm=False, inverse=True)
         gh = c.heads // c.o_groups
         og = out.view(T, c.o_groups, gh * D).to(layer.o_a.dtype)
         low = torch.einsum("grk,tgk->tgr", layer.o_a, og).float()
         return _lin(low.reshape(T, -1), layer.o_b)
+
+    def _attention_run(self, layer: V4Layer, lr: LayerRows, p0: int, q, kv, comp, idx, freq, sinks, scale, out) -> None:
+        """``n >= 2`` consecutive tokens of one request starting at position ``p0``.  Token j sees the window that ends
+        at its own row and the compressed rows emitted by earlier tokens; the rows the run itself emits become
+        visible one token after the token that completes their window."""
+        c, f = self.cfg, self._f32
+        n, D, W, r = q.shape[0], c.head_dim, c.window, layer.ratio
+        dev = q.device
+        count0, n_comp0 = lr.count, lr.n_comp
+        n_prev = min(count0, W - 1)
+        if n_prev:
+            ring = [(count0 - n_prev + i) % W for i in range(n_prev)]
+            lin = torch.cat([lr.pool[torch.tensor(ring, device=dev)], kv])
+        else:
+            lin = kv.contiguous()
+        emit_at: list = []                               # run-relative token index that completes each emitted row
+        if comp is not None:
+            base = p0 - p0 % r
+            ckv, cgate, comp_ape = comp
+            emitted = nv.compressor_run_(lr.comp_state, ckv, cgate, comp_ape, p0, D, r)
+            idx_rows = nv.compressor_run_(lr.index_state, idx[0], idx[1], idx[2], p0, 128, 4) if idx is not None else None
+            if emitted.shape[0]:
+                starts = [base + k * r for k in range(emitted.shape[0])]
+                emit_at = [s0 + r - 1 - p0 for s0 in starts]
+                at = torch.tensor(starts, dtype=torch.long, device=dev)
+                emitted = nv.norm_rope(emitted, f(layer, "comp_norm"), freq, at, c.eps, fp8=True)
+                if idx_rows is not None:
+                    idx_rows = indexer_qat(nv.norm_rope(idx_rows, f(layer, "idx_norm"), freq, at, c.eps))
+                lr.append_compressed_many(emitted, idx_rows)
+        ends = [n_prev + j + 1 for j in range(n)]
+        a0 = [max(0, e - W) for e in ends]
+        na = [e - a for e, a in zip(ends, a0)]
+        nb, k = [], 0
+        for j in range(n):
+            while k < len(emit_at) and emit_at[k] < j:
+                k += 1
+            nb.append(n_comp0 + k)
+        sel = None
+        if idx is not None and nb[-1] > c.indexer_topk:
+            # indexer scores of every token of the run over all rows, rows a token cannot see yet masked out
+            iq, iw = idx[3], idx[4]
+            rows = lr.index_rows
+            n_rows = rows.shape[0]
+            keep = min(c.indexer_topk, n_rows)
+            sel = torch.empty(n, keep, dtype=torch.int32, device=dev)
+            visible = torch.tensor(nb, device=dev)
+            s_scale = 1.0 / math.sqrt(c.indexer_heads * 128)
+            step = max(1, (64 << 20) // max(1, c.indexer_heads * n_rows))
+            for j0 in range(0, n, step):
+                blk = slice(j0, min(n, j0 + step))
+                per_head = torch.einsum("thd,rd->thr", iq[blk], rows).clamp_min_(0.0)
+                scores = (iw[blk].unsqueeze(-1) * per_head).sum(1) * s_scale
+                scores.masked_fill_(torch.arange(n_rows, device=dev)[None] >= visible[blk, None], float("-inf"))
+                sel[blk] = torch.topk(scores, keep, dim=-1, sorted=True).indices.to(torch.int32)
+            nb = [min(v, c.indexer_topk) for v in nb]
+        spans = torch.tensor([a0, na, nb], dtype=torch.int32, device=dev)
+        out.copy_(shared_kv_attention_run(q, lin, lr.pool[W:], spans, sel, sinks, scale))
+        m = min(n, W)
+        ring = [(count0 + n - m + i) % W for i in range(m)]
+        lr.pool[torch.tensor(ring, device=dev)] = kv[n - m:]
+        lr.count += n
 
     def _ffn(self, layer: V4Layer, h: torch.Tensor, token_ids: torch.Tensor) -> torch.Tensor:
         c, f = self.cfg, self._f32

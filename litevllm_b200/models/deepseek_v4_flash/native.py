@@ -148,6 +148,56 @@ def compressor_step_(state: CompressorState, kv_cur: torch.Tensor, score_cur: to
     return emitted
 
 
+def compressor_run_(state: CompressorState, kv_run: torch.Tensor, score_run: torch.Tensor, ape: torch.Tensor,
+                    p0: int, head_dim: int, ratio: int) -> torch.Tensor:
+    """``n`` consecutive tokens starting at position ``p0`` into ``state`` (updated in place); returns the rows of
+    every window the run completes, ``[n_emit, head_dim]``.  An emission only depends on the tokens of its own
+    window (and of the window before it for ratio 4), so all windows of the run are pooled at once from the
+    carried-in rows followed by the run's rows."""
+    n = kv_run.shape[0]
+    coff = 2 if ratio == 4 else 1
+    width = coff * head_dim
+    dev = kv_run.device
+    ape_rows = (ape.t() if ape.shape == (width, ratio) else ape).float()
+    slots = (p0 + torch.arange(n, device=dev)) % ratio
+    sc_run = score_run.float() + ape_rows[slots]
+    kv_run = kv_run.float()
+    part = p0 % ratio                 # tokens already in the current window
+    base = p0 - part                  # position where the current window starts
+    if ratio == 4:                    # rows 0..3: previous window, rows 4..: current window
+        hist_kv = torch.cat([state.kv[:4], state.kv[4:4 + part], kv_run])
+        hist_sc = torch.cat([state.score[:4], state.score[4:4 + part], sc_run])
+        origin = base - 4
+    else:
+        hist_kv = torch.cat([state.kv[:part], kv_run])
+        hist_sc = torch.cat([state.score[:part], sc_run])
+        origin = base
+    end = p0 + n
+    n_emit = (end - base) // ratio
+    emitted = kv_run.new_zeros(0, head_dim)
+    if n_emit > 0:
+        cur = (base - origin + ratio * torch.arange(n_emit, device=dev))[:, None] + torch.arange(ratio, device=dev)[None]
+        if ratio == 4:
+            prev = cur - 4
+            sc = torch.cat([hist_sc[prev][:, :, :head_dim], hist_sc[cur][:, :, head_dim:]], 1)
+            vals = torch.cat([hist_kv[prev][:, :, :head_dim], hist_kv[cur][:, :, head_dim:]], 1)
+        else:
+            sc, vals = hist_sc[cur][:, :, :head_dim], hist_kv[cur][:, :, :head_dim]
+        emitted = (torch.nan_to_num(torch.softmax(sc, dim=1)) * vals).sum(1)
+    new_part = end % ratio
+    i0 = end - new_part - origin
+    if ratio == 4:
+        if end - new_part > base:     # a window was completed: it becomes the previous window
+            state.kv[:4] = hist_kv[i0 - 4:i0]
+            state.score[:4] = hist_sc[i0 - 4:i0]
+        state.kv[4:4 + new_part] = hist_kv[i0:i0 + new_part]
+        state.score[4:4 + new_part] = hist_sc[i0:i0 + new_part]
+    else:
+        state.kv[:new_part] = hist_kv[i0:i0 + new_part]
+        state.score[:new_part] = hist_sc[i0:i0 + new_part]
+    return emitted
+
+
 def q8k(x: torch.Tensor) -> torch.Tensor:
     if _gpu(x) and x.numel() % 256 == 0 and x.shape[-1] % 256 == 0:
         xc = x.contiguous()

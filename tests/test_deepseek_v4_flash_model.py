@@ -299,3 +299,20 @@ def test_fused_token_kernels_match_their_pytorch_forms():
     x[2, :256] = 0
     a, b = both(nv.q8k, x)
     close(a, b, tol=1e-6, what="q8k")
+
+    # a run of tokens in one launch: window spans of a linear buffer plus a prefix / a selection of compressed rows
+    from litevllm_b200.models.deepseek_v4_flash.attention import shared_kv_attention_run
+    n, heads, D = 9, 3, 256
+    q = torch.randn(n, heads, D, generator=g)
+    lin, comp = torch.randn(14, D, generator=g), torch.randn(12, D, generator=g)
+    sinks = torch.randn(heads, generator=g)
+    a0 = [max(0, j + 6 - 8) for j in range(n)]
+    na = [j + 6 - s0 for j, s0 in enumerate(a0)]
+    nb = [min(12, 3 + j) for j in range(n)]
+    spans = torch.tensor([a0, na, nb], dtype=torch.int32)
+    a, b = both(lambda *t: shared_kv_attention_run(t[0], t[1], t[2], t[3], None, t[4], 0.07), q, lin, comp, spans, sinks)
+    close(a, b, what="attention run, prefix rows")
+    sel = torch.stack([torch.randperm(12, generator=g)[:5] for _ in range(n)]).to(torch.int32)
+    spans[2] = torch.tensor([min(5, v) for v in nb], dtype=torch.int32)
+    a, b = both(lambda *t: shared_kv_attention_run(t[0], t[1], t[2], t[3], t[4], t[5], 0.07), q, lin, comp, spans, sel, sinks)
+    close(a, b, what="attention run, selected rows")
