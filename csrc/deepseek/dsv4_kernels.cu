@@ -18,6 +18,8 @@
 //   fi_dsv4_shared_kv_attention_run : the same attention for a run of consecutive tokens of one request (a
 //                              prefill chunk) in one launch: per token a window range of a linear row buffer plus
 //                              a prefix, or a selected list, of the compressed rows.
+//   fi_dsv4_shared_kv_attention_ptrs : the same attention for one token of each request of a decode batch in one
+//                              launch (per-request row pools through a pointer array).
 //   fi_dsv4_cache_update     : write latent rows through a page table.  Reference: .../cache.py:41-65.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -225,6 +227,67 @@ __global__ void __launch_bounds__(128) shared_kv_attention_run_kernel(
   for (int j = 0; j < per; ++j) out[qo + j * 128 + threadIdx.x] = acc[j] * inv;
 }
 
+// One token of each of T requests (a decode batch): CTA (head, token).  pools[t] points to that request's rows:
+// the first n_win[t] rows are its sliding window (ring order is irrelevant to attention), its compressed rows
+// start at row `comp_row0`; token t attends nb[t] of them: the first nb[t], or sel[t * sel_stride + ..] when
+// use_sel[t] is set.
+__global__ void __launch_bounds__(128) shared_kv_attention_ptrs_kernel(
+    const float* __restrict__ q, const float* const* __restrict__ pools, const int* __restrict__ n_win,
+    const int* __restrict__ nb, const int* __restrict__ use_sel, const int* __restrict__ sel, int sel_stride,
+    int comp_row0, const float* __restrict__ sinks, int heads, int D, float scale, float* __restrict__ out) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  __shared__ float qs[512];
+  __shared__ float sc[kChunk];
+  __shared__ const float* rowp[kChunk];
+  const int h = blockIdx.x, t = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long qo = (static_cast<long>(t) * heads + h) * D;
+  for (int i = threadIdx.x; i < D; i += 128) qs[i] = q[qo + i] * scale;
+  const int per = D / 128;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float m = sinks ? sinks[h] : -CUDART_INF_F;
+  float l = sinks ? 1.f : 0.f;
+  const float* pool = pools[t];
+  const int n_a = n_win[t], n_rows = n_a + nb[t];
+  const bool by_sel = sel != nullptr && use_sel[t] != 0;
+  __syncthreads();
+  for (int r0 = 0; r0 < n_rows; r0 += kChunk) {
+    const int n = min(kChunk, n_rows - r0);
+    if (threadIdx.x < n) {
+      const int r = r0 + threadIdx.x;
+      const int row = r < n_a ? r : comp_row0 + (by_sel ? sel[static_cast<long>(t) * sel_stride + (r - n_a)] : (r - n_a));
+      rowp[threadIdx.x] = pool + static_cast<long>(row) * D;
+    }
+    __syncthreads();
+    for (int i = warp; i < n; i += 4) {
+      const float* row = rowp[i];
+      float d = 0.f;
+      for (int c = lane; c < D; c += 32) d += qs[c] * row[c];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+      if (lane == 0) sc[i] = d;
+    }
+    __syncthreads();
+    float cm = m;
+    for (int i = 0; i < n; ++i) cm = fmaxf(cm, sc[i]);
+    const float corr = (m == -CUDART_INF_F) ? 0.f : __expf(m - cm);
+    l *= corr;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] *= corr;
+    for (int i = 0; i < n; ++i) {
+      const float p = __expf(sc[i] - cm);
+      l += p;
+      const float* row = rowp[i];
+      for (int j = 0; j < per; ++j) acc[j] += p * row[j * 128 + threadIdx.x];
+    }
+    m = cm;
+    __syncthreads();
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  for (int j = 0; j < per; ++j) out[qo + j * 128 + threadIdx.x] = acc[j] * inv;
+}
+
 __global__ void cache_update_kernel(const float* __restrict__ rows, const int* __restrict__ positions,
                                     const int* __restrict__ page_table, int page_rows, int D,
                                     float* __restrict__ pool) {
@@ -275,6 +338,19 @@ extern "C" int fi_dsv4_shared_kv_attention_run(const float* q, const float* lin,
   if (D > 512 || D % 128 != 0 || T > 65535 || (sel != nullptr && sel_stride <= 0)) return -10;
   fi::launch_kernel(shared_kv_attention_run_kernel, dim3(heads, T), dim3(128), 0, FI_STREAM(stream), 0, q, lin, comp, a0,
                     na, nb, sel, sel_stride, sinks, heads, D, scale, out);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fi_dsv4_shared_kv_attention_ptrs(const float* q, void* pools, const int* n_win, const int* nb,
+                                                const int* use_sel, const int* sel, int sel_stride, int comp_row0,
+                                                const float* sinks, int T, int heads, int D, float scale, float* out,
+                                                void* stream) {
+  if (heads <= 0 || T <= 0) return 0;
+  if (D > 512 || D % 128 != 0 || T > 65535 || comp_row0 < 0 || (sel != nullptr && (sel_stride <= 0 || use_sel == nullptr)))
+    return -10;
+  fi::launch_kernel(shared_kv_attention_ptrs_kernel, dim3(heads, T), dim3(128), 0, FI_STREAM(stream), 0, q,
+                    static_cast<const float* const*>(pools), n_win, nb, use_sel, sel, sel_stride, comp_row0, sinks, heads, D,
+                    scale, out);
   return static_cast<int>(cudaGetLastError());
 }
 

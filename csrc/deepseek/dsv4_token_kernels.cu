@@ -18,6 +18,9 @@
 //                         attention output.  Reference: .../attention.py:141-197, ops.py (fp8 KV round trip).
 //   fi_dsv4_compressor_step : one token into the rolling compressor window (in place) and, every `ratio`
 //                         tokens, the softmax(score)-weighted row.  Reference: .../attention.py:665-760.
+//   fi_dsv4_compressor_step_batch / fi_dsv4_scatter_rows : the compressor step and the window-row write for one
+//                         token of each request of a decode batch (per-request state and pool addresses come in
+//                         pointer arrays).
 //   fi_dsv4_q8k_roundtrip : Q8_K activation round trip (blocks of 256, scale from the signed extreme value).
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -265,6 +268,68 @@ __global__ void compressor_step_kernel(float* __restrict__ state_kv, float* __re
   }
 }
 
+// The same step for one token of each of `n` requests (a decode batch): CTA i works on the state that
+// state_kv[i] / state_score[i] point to, with kv_cur / score_cur rows of pitch `pitch` floats and pos[i].
+// emitted: [n, head_dim]; row i is written when (pos[i] + 1) % ratio == 0.
+__global__ void compressor_step_batch_kernel(float* const* __restrict__ state_kv, float* const* __restrict__ state_score,
+                                             const float* __restrict__ kv_cur, const float* __restrict__ score_cur,
+                                             long pitch, const float* __restrict__ ape, long ape_stride_pos,
+                                             long ape_stride_c, const long* __restrict__ pos, int ratio, int head_dim,
+                                             float* __restrict__ emitted) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  const int i = blockIdx.x;
+  float* skv = state_kv[i];
+  float* ssc = state_score[i];
+  const float* kc = kv_cur + i * pitch;
+  const float* sc = score_cur + i * pitch;
+  const int p = static_cast<int>(pos[i]);
+  const int coff = ratio == 4 ? 2 : 1;
+  const int width = coff * head_dim;
+  const int slot = p % ratio;
+  const int row = ratio == 4 ? ratio + slot : slot;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    skv[static_cast<long>(row) * width + c] = kc[c];
+    ssc[static_cast<long>(row) * width + c] = sc[c] + ape[slot * ape_stride_pos + c * ape_stride_c];
+  }
+  __syncthreads();
+  if ((p + 1) % ratio != 0) return;
+  const int n_rows = coff * ratio;
+  for (int c = threadIdx.x; c < head_dim; c += blockDim.x) {
+    float mx = -CUDART_INF_F;
+    for (int r = 0; r < n_rows; ++r) {
+      const int col = (ratio == 4 && r >= ratio) ? head_dim + c : c;
+      mx = fmaxf(mx, ssc[static_cast<long>(r) * width + col]);
+    }
+    float den = 0.f, num = 0.f;
+    if (mx > -CUDART_INF_F) {
+      for (int r = 0; r < n_rows; ++r) {
+        const int col = (ratio == 4 && r >= ratio) ? head_dim + c : c;
+        const float e = __expf(ssc[static_cast<long>(r) * width + col] - mx);
+        den += e;
+        num += e * skv[static_cast<long>(r) * width + col];
+      }
+    }
+    emitted[static_cast<long>(i) * head_dim + c] = den > 0.f ? num / den : 0.f;
+  }
+  __syncthreads();
+  if (ratio == 4) {
+    for (int k = threadIdx.x; k < ratio * width; k += blockDim.x) {
+      skv[k] = skv[static_cast<long>(ratio) * width + k];
+      ssc[k] = ssc[static_cast<long>(ratio) * width + k];
+    }
+  }
+}
+
+// rows [n, D] (pitch floats apart) to n unrelated destinations.  grid n, block 128.
+__global__ void scatter_rows_kernel(const float* __restrict__ rows, long pitch, float* const* __restrict__ dst, int D) {
+  fi::pdl_launch_dependents();
+  fi::pdl_wait();
+  const float* src = rows + blockIdx.x * pitch;
+  float* d = dst[blockIdx.x];
+  for (int c = threadIdx.x; c < D; c += blockDim.x) d[c] = src[c];
+}
+
 // grid n_blocks (of 256 values), block 256
 __global__ void q8k_roundtrip_kernel(const float* __restrict__ x, float* __restrict__ y) {
   fi::pdl_launch_dependents();
@@ -336,6 +401,25 @@ extern "C" int fi_dsv4_compressor_step(float* state_kv, float* state_score, cons
   if (ratio <= 0 || head_dim <= 0 || pos < 0) return -10;
   fi::launch_kernel(compressor_step_kernel, dim3(1), dim3(256), 0, FI_STREAM(stream), 0, state_kv, state_score, kv_cur,
                     score_cur, ape, ape_stride_pos, ape_stride_c, pos, ratio, head_dim, emitted);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fi_dsv4_compressor_step_batch(void* state_kv, void* state_score, const float* kv_cur,
+                                             const float* score_cur, long pitch, const float* ape, long ape_stride_pos,
+                                             long ape_stride_c, const long* pos, int n, int ratio, int head_dim,
+                                             float* emitted, void* stream) {
+  if (n <= 0) return 0;
+  if (ratio <= 0 || head_dim <= 0) return -10;
+  fi::launch_kernel(compressor_step_batch_kernel, dim3(n), dim3(256), 0, FI_STREAM(stream), 0,
+                    static_cast<float* const*>(state_kv), static_cast<float* const*>(state_score), kv_cur, score_cur, pitch,
+                    ape, ape_stride_pos, ape_stride_c, pos, ratio, head_dim, emitted);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fi_dsv4_scatter_rows(const float* rows, long pitch, void* dst, int n, int D, void* stream) {
+  if (n <= 0 || D <= 0) return 0;
+  fi::launch_kernel(scatter_rows_kernel, dim3(n), dim3(128), 0, FI_STREAM(stream), 0, rows, pitch,
+                    static_cast<float* const*>(dst), D);
   return static_cast<int>(cudaGetLastError());
 }
 

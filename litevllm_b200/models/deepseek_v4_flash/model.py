@@ -518,12 +518,20 @@ class DeepseekV4FlashForCausalLM(nn.Module):
         scale = 1.0 / math.sqrt(D)
         out = torch.empty(T, c.heads, D, dtype=torch.float32, device=h.device)
         r = layer.ratio
+        singles: list = []                      # tokens that are alone in their request (a decode batch)
+        lone = sum(1 for j in range(T) if (j == 0 or rows_of[j - 1] is not rows_of[j])
+                   and (j == T - 1 or rows_of[j + 1] is not rows_of[j]))
+        batch_singles = h.is_cuda and lone >= 2  # one request alone: the pointer tables cost more than they save
         t = 0
         while t < T:
             t1 = t + 1
             while t1 < T and rows_of[t1] is rows_of[t]:
                 t1 += 1
             lr: LayerRows = rows_of[t].layers[li]
+            if t1 - t == 1 and batch_singles:
+                singles.append(t)
+                t = t1
+                continue
             if t1 - t >= 2:
                 # a run of consecutive tokens of one request (a prefill chunk): compressor windows, row
                 # post-processing, indexer selection and attention each run once for the whole run
@@ -565,11 +573,85 @@ class DeepseekV4FlashForCausalLM(nn.Module):
                         idx_row = indexer_qat(nv.norm_rope(idx_row.unsqueeze(0), f(layer, "idx_norm"), freq, at, c.eps))[0]
                     lr.append_compressed(emitted, idx_row)
             t = t1
+        if singles:
+            if layer.indexed and iq is None and any(rows_of[t].layers[li].n_comp > c.indexer_topk for t in singles):
+                iq = indexer_qat(nv.norm_rope(_lin(q_low, layer.idx_q).view(T, c.indexer_heads, 128), None, freq, pos,
+                                              c.eps, norm=False))
+            self._attention_singles(layer, li, singles, rows_of, positions, pos, q, kv,
+                                    (ckv, cgate, comp_ape) if layer.compressed else None,
+                                    (ikv, igate, idx_ape, iq, iw) if layer.indexed else None, freq, sinks, scale, out)
         out = nv.norm_rope(out, None, freq, pos, c.eps, norm=False, inverse=True)
         gh = c.heads // c.o_groups
         og = out.view(T, c.o_groups, gh * D).to(layer.o_a.dtype)
         low = torch.einsum("grk,tgk->tgr", layer.o_a, og).float()
         return _lin(low.reshape(T, -1), layer.o_b)
+
+    def _attention_singles(self, layer: V4Layer, li: int, ts: list, rows_of: list, positions: list, pos, q, kv, comp, idx,
+                           freq, sinks, scale, out) -> None:
+        """One token of each of several requests (a decode batch) on a GPU: the window-row writes, the attention and
+        the compressor steps of all of them are one launch each; per-request pools and states are addressed
+        through pointer arrays built on the host."""
+        c, f = self.cfg, self._f32
+        n, T, D, W, r = len(ts), q.shape[0], c.head_dim, c.window, layer.ratio
+        dev = q.device
+        lrs = [rows_of[t].layers[li] for t in ts]
+        whole = n == T
+        pick = None if whole else torch.tensor(ts, device=dev)
+        take = (lambda x: x) if whole else (lambda x: x[pick])
+        dst = [lr.pool.data_ptr() + (lr.count % W) * D * 4 for lr in lrs]
+        for lr in lrs:
+            lr.count += 1
+        n_win = [min(lr.count, W) for lr in lrs]
+        nb = [lr.n_comp for lr in lrs]
+        use_sel = [0] * n
+        sel = None
+        if idx is not None and max(nb) > c.indexer_topk:
+            sel = torch.zeros(n, c.indexer_topk, dtype=torch.int32, device=dev)
+            for i, (t, lr) in enumerate(zip(ts, lrs)):
+                if nb[i] > c.indexer_topk:
+                    sel[i] = indexer_topk(indexer_scores(idx[3][t], idx[4][t], lr.index_rows), c.indexer_topk).to(torch.int32)
+                    use_sel[i], nb[i] = 1, c.indexer_topk
+        ptr_rows = [dst, [lr.pool.data_ptr() for lr in lrs]]
+        if comp is not None:
+            ptr_rows += [[lr.comp_state.kv.data_ptr() for lr in lrs], [lr.comp_state.score.data_ptr() for lr in lrs]]
+        if idx is not None:
+            ptr_rows += [[lr.index_state.kv.data_ptr() for lr in lrs], [lr.index_state.score.data_ptr() for lr in lrs]]
+        ptrs = torch.tensor(ptr_rows, dtype=torch.int64, device=dev)
+        meta = torch.tensor([n_win, nb, use_sel], dtype=torch.int32, device=dev)
+        lib, P, S = nv._k(), nv._p, nv._s
+        kv_s, q_s = take(kv).contiguous(), take(q).contiguous()
+        nv._call(lib.fi_dsv4_scatter_rows(P(kv_s), D, ptrs[0].data_ptr(), n, D, S()), "fi_dsv4_scatter_rows")
+        o = out if whole else torch.empty(n, c.heads, D, dtype=torch.float32, device=dev)
+        nv._call(lib.fi_dsv4_shared_kv_attention_ptrs(
+            P(q_s), ptrs[1].data_ptr(), meta[0].data_ptr(), meta[1].data_ptr(), meta[2].data_ptr(), P(sel),
+            0 if sel is None else sel.stride(0), W, P(sinks), n, c.heads, D, scale, P(o), S()),
+            "fi_dsv4_shared_kv_attention_ptrs")
+        if not whole:
+            out[pick] = o
+        if comp is None:
+            return
+        pos_s = take(pos).contiguous()
+        emits = [i for i, t in enumerate(ts) if (positions[t] + 1) % r == 0]
+
+        def step(state_rows: int, cur, gate, ape, head_dim: int, ratio: int) -> torch.Tensor:
+            cur, gate = take(cur), take(gate)
+            width = (2 if ratio == 4 else 1) * head_dim
+            sp, sc = (ape.stride(1), ape.stride(0)) if ape.shape == (width, ratio) else (ape.stride(0), ape.stride(1))
+            em = torch.empty(n, head_dim, dtype=torch.float32, device=dev)
+            nv._call(lib.fi_dsv4_compressor_step_batch(
+                ptrs[state_rows].data_ptr(), ptrs[state_rows + 1].data_ptr(), P(cur), P(gate), cur.stride(0), P(ape), sp, sc,
+                P(pos_s), n, ratio, head_dim, P(em), S()), "fi_dsv4_compressor_step_batch")
+            return em
+
+        emitted = step(2, comp[0], comp[1], comp[2], D, r)
+        idx_rows = step(4, idx[0], idx[1], idx[2], 128, 4) if idx is not None else None
+        if emits:
+            e = torch.tensor(emits, device=dev)
+            at = pos_s[e] + (1 - r)
+            rows = nv.norm_rope(emitted[e], f(layer, "comp_norm"), freq, at, c.eps, fp8=True)
+            irows = indexer_qat(nv.norm_rope(idx_rows[e], f(layer, "idx_norm"), freq, at, c.eps)) if idx_rows is not None else None
+            for k, i in enumerate(emits):
+                lrs[i].append_compressed(rows[k], None if irows is None else irows[k])
 
     def _attention_run(self, layer: V4Layer, lr: LayerRows, p0: int, q, kv, comp, idx, freq, sinks, scale, out) -> None:
         """``n >= 2`` consecutive tokens of one request starting at position ``p0``.  Token j sees the window that ends

@@ -112,6 +112,11 @@ def test_gpu_tokens_match_cpu(llm):
     agree = sum(a == b for w, g in zip(want, got) for a, b in zip(w, g)) / sum(len(w) for w in want)
     assert got[0][0] == want[0][0] and got[1][0] == want[1][0]
     assert agree >= 0.75, (want, got)
+    # the decode batch (one launch per step for all requests) against each request decoded alone
+    alone = [_tokens(gpu, [p], 8)[0] for p in PROMPTS]
+    same = sum(a == b for w, g in zip(alone, got) for a, b in zip(w, g)) / sum(len(w) for w in alone)
+    assert same >= 0.85, (alone, got)
+    assert gpu.engine.model.requests == {}
 
 
 def test_checkpoint_tensor_names_map_to_parameters(llm):
