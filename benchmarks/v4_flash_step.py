@@ -26,6 +26,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--vocab", type=int, default=32768)
     ap.add_argument("--host-profile", action="store_true", help="print the host-side profile of extra decode steps")
+    ap.add_argument("--engine", action="store_true", help="also time LLM.generate of the same prompts (host clock)")
     a = ap.parse_args()
     from litevllm_b200 import LLM
     from litevllm_b200.models.deepseek_v4_flash.model import BlockMatrix
@@ -84,6 +85,21 @@ def main() -> None:
         torch.cuda.synchronize(dev)
         prof.disable()
         pstats.Stats(prof, stream=sys.stderr).sort_stats("tottime").print_stats(28)
+    rows_mb = round(model.request_bytes() / 2 ** 20, 2)
+    engine = {}
+    if a.engine:
+        import time
+        from litevllm_b200 import SamplingParams
+        for rid in rids:
+            model.release_request(rid)
+        sp = SamplingParams(max_tokens=a.steps, temperature=0.0, ignore_eos=True)
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        outs = llm.generate([{"prompt_token_ids": p} for p in prompts], sp)
+        dt = time.perf_counter() - t0
+        n_out = sum(len(o.outputs[0].token_ids) for o in outs)
+        engine = {"engine_generate_s": round(dt, 3), "engine_generated_tokens": n_out,
+                  "engine_tok_s_incl_prefill": round(n_out / dt, 2)}
     weights = sum(p.numel() * p.element_size() for p in model.parameters())
     for layer in model.layers:
         weights += sum(v.numel() for v in layer.routed.raw.values()) if layer.routed is not None else 0
@@ -96,7 +112,7 @@ def main() -> None:
         "prefill_ms_per_token_per_layer": round(t_prefill / (a.batch * a.prompt_len * a.layers), 4),
         "decode_ms_per_step": round(ms_step, 3), "decode_ms_per_step_per_layer": round(ms_step / a.layers, 4),
         "decode_tok_s": round(a.batch * 1000.0 / ms_step, 2), "weights_gb": round(weights / 2 ** 30, 2),
-        "rows_mb": round(model.request_bytes() / 2 ** 20, 2),
+        "rows_mb": rows_mb, **engine,
         "note": "model-owned data plane, eager launches; per-layer figures scale to the 43 layers of the full model"}))
 
 
