@@ -26,6 +26,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--vocab", type=int, default=32768)
     ap.add_argument("--host-profile", action="store_true", help="print the host-side profile of extra decode steps")
+    ap.add_argument("--kernel-table", action="store_true",
+                    help="print the GPU kernels of one more prefill and one decode step by total time (shares only)")
     ap.add_argument("--engine", action="store_true", help="also time LLM.generate of the same prompts (host clock)")
     a = ap.parse_args()
     from litevllm_b200 import LLM
@@ -86,6 +88,15 @@ def main() -> None:
         prof.disable()
         pstats.Stats(prof, stream=sys.stderr).sort_stats("tottime").print_stats(28)
     rows_mb = round(model.request_bytes() / 2 ** 20, 2)
+    if a.kernel_table:
+        from torch.profiler import ProfilerActivity, profile
+        for what, fn in (("prefill", lambda: model.prefill_request("kt", prompts[0], 0, True)), ("decode", decode_steps)):
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                fn()
+                torch.cuda.synchronize(dev)
+            print(f"--- {what}", file=sys.stderr)
+            print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=14, max_name_column_width=60), file=sys.stderr)
+        model.release_request("kt")
     engine = {}
     if a.engine:
         import time

@@ -321,3 +321,14 @@ def test_fused_token_kernels_match_their_pytorch_forms():
     spans[2] = torch.tensor([min(5, v) for v in nb], dtype=torch.int32)
     a, b = both(lambda *t: shared_kv_attention_run(t[0], t[1], t[2], t[3], t[4], t[5], 0.07), q, lin, comp, spans, sel, sinks)
     close(a, b, what="attention run, selected rows")
+
+
+def test_abort_releases_the_rows(llm):
+    eng = llm.engine
+    eng.add_request("abort-me", {"prompt_token_ids": PROMPTS[0]}, _greedy(50))
+    for _ in range(3):
+        eng.step()
+    assert "abort-me" in eng.model.requests and eng.model.request_bytes() > 0
+    assert eng.abort_request("abort-me")
+    assert eng.model.requests == {}
+    assert not eng.has_unfinished_requests()
