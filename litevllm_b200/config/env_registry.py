@@ -80,3 +80,8 @@ def get_public_env(environ: Mapping[str, str], name: str, default: str = "") -> 
     if spec is None or spec.scope is not EnvScope.PUBLIC:
         raise ValueError(f"{name} is not a public environment variable of this engine")
     return environ.get(name, default)
+
+
+def kernel_switches() -> dict[str, str]:
+    """The ``FI_*`` process-environment switches of the kernel layer with what each selects."""
+    return dict(env_names.KERNEL_SWITCHES)

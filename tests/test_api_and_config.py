@@ -185,3 +185,19 @@ def test_chat_template_registry_and_jinja_fallbacks(tmp_path):
     assert ct.render_fallback(msgs, str(ct.get_chat_template_fallback("my-model"))) == "<user>see <image><assistant>ok"
     with pytest.raises(Exception):
         ct.render_template("{{ messages.__class__.__mro__ }}", msgs)
+
+
+def test_every_kernel_switch_read_by_the_package_is_registered():
+    """A ``FI_*`` environment name that some module reads must be listed (with its meaning) in the registry."""
+    import pathlib
+    import re
+    from litevllm_b200.config.env_registry import kernel_switches
+    root = pathlib.Path(__file__).resolve().parent.parent
+    used = set()
+    for path in list((root / "litevllm_b200").rglob("*.py")) + [root / "bench.py"]:
+        if path.name == "env_names.py":
+            continue
+        used |= set(re.findall(r'"(FI_[A-Z0-9_]+)"', path.read_text()))
+    listed = kernel_switches()
+    assert used <= set(listed), sorted(used - set(listed))
+    assert all(listed[n] for n in listed)
