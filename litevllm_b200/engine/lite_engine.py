@@ -219,3 +219,7 @@ class LiteEngine:
         with self.lock:
             for rid in self.scheduler.all_request_ids():
                 self.abort_request(rid)
+        # the engine's objects were parked in the collector's permanent generation at start-up; give them back so
+        # that dropping the last reference (and a collection) frees the weights and the KV pool
+        import gc
+        gc.unfreeze()

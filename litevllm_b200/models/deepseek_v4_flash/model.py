@@ -419,6 +419,7 @@ class DeepseekV4FlashForCausalLM(nn.Module):
                         raw = gq.random_blocks(8, N, K, 104729 * li + len(attr) + N, 0.5 / math.sqrt(K) / 64, str(dev))
                         layer._parameters.pop(attr, None)
                         setattr(layer, attr, BlockMatrix(raw, 8, K, dev))
+        gdev = None
         for name, p in self.named_parameters():
             if name.endswith("norm"):
                 p.data.fill_(1.0)
@@ -428,10 +429,15 @@ class DeepseekV4FlashForCausalLM(nn.Module):
                 p.data.copy_((torch.randn(p.shape, generator=g) * 0.1).to(p.dtype))
             else:
                 fan_in = max(p.shape) if name.endswith("_fn") else p.shape[-1]
-                p.data.copy_((torch.randn(p.shape, generator=g) / math.sqrt(fan_in)).to(p.dtype))
+                if p.is_cuda and p.numel() >= 1 << 24:       # large tensors of full-size models: drawn on the device
+                    if gdev is None:
+                        gdev = torch.Generator(device=p.device).manual_seed(2000 + self.seed)
+                    p.data.copy_((torch.randn(p.shape, generator=gdev, device=p.device) / math.sqrt(fan_in)).to(p.dtype))
+                else:
+                    p.data.copy_((torch.randn(p.shape, generator=g) / math.sqrt(fan_in)).to(p.dtype))
         for layer in self.layers:
-            if layer.hash_routed:
-                tab = torch.stack([torch.randperm(c.experts, generator=g)[: c.top_k] for _ in range(c.vocab)], dim=1)
+            if layer.hash_routed:        # top_k distinct experts per token id: the first columns of a random permutation
+                tab = torch.rand(c.vocab, c.experts, generator=g).argsort(dim=1)[:, : c.top_k].t()
                 layer.hash_table.copy_(tab.to(torch.int32))
 
     # ------------------------------------------------------------------ request state

@@ -94,6 +94,17 @@ PRESETS["tiny-deepseek-v4-flash-test"] = {
     "vocab_size": 512, "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "max_position_embeddings": 512,
     "intermediate_size": 256, "eos_token_id": 1,
 }
+# the full-size geometry of the DeepSeek-V4-Flash checkpoint family; as a synthetic model its weights are random
+# blocks in the checkpoint's formats (IQ2_XXS / Q2_K experts, Q8_0 projections: about 90 GB)
+PRESETS["deepseek-v4-flash"] = {
+    "architectures": ["DeepseekV4FlashForCausalLM"], "model_type": "deepseek_v4_flash", "hidden_size": 4096,
+    "num_hidden_layers": 43, "num_attention_heads": 64, "num_key_value_heads": 1, "head_dim": 512,
+    "qk_rope_head_dim": 64, "q_lora_rank": 1024, "sliding_window": 128, "index_n_heads": 64, "index_topk": 512,
+    "hc_mult": 4, "o_groups": 8, "o_lora_rank": 1024, "n_routed_experts": 256, "num_experts_per_tok": 6,
+    "moe_intermediate_size": 2048, "num_hash_layers": 3, "routed_scaling_factor": 1.5, "swiglu_limit": 10.0,
+    "vocab_size": 129280, "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "max_position_embeddings": 65536,
+    "intermediate_size": 2048, "eos_token_id": 1, "synthetic_block_weights": True,
+}
 PRESETS["tiny-qwen35-test"] = {
     "architectures": ["Qwen3_5ForCausalLM"], "model_type": "qwen3_5", "hidden_size": 256, "num_hidden_layers": 4,
     "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 256, "vocab_size": 512,

@@ -397,3 +397,23 @@ def test_selective_block_tables_and_engine_cpu():
     base = run(0)
     assert run(1.0) == base
     assert len(run(0.25)) == 6
+
+
+def test_engine_and_weights_are_freed_after_shutdown():
+    """The engine parks its objects in the collector's permanent generation while it runs; after ``shutdown`` a
+    dropped engine (model, KV pool) must be collectable again, or a second engine in the same process would find
+    the first one's memory still in use."""
+    import gc
+    import weakref
+    from litevllm_b200 import LLM, SamplingParams
+
+    def build_and_drop():
+        llm = LLM("synthetic:tiny-llama-test", device="cpu", max_model_len=64, dtype="float32")
+        llm.generate([{"prompt_token_ids": [3, 4, 5]}], SamplingParams(max_tokens=2, temperature=0.0, ignore_eos=True))
+        refs = weakref.ref(llm.engine.model), weakref.ref(llm.engine.kv_cache)
+        llm.shutdown()
+        return refs
+
+    model_ref, kv_ref = build_and_drop()
+    gc.collect()
+    assert model_ref() is None and kv_ref() is None
