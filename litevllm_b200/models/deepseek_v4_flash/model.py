@@ -27,6 +27,7 @@ compressed_kv.py:289-455 (row pools), kv_lifecycle.py (release).
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 
 import torch
@@ -39,6 +40,11 @@ from .moe import hash_routed_expert_ids, sqrt_softplus_router
 from ...utils.profiling import stage
 from ...ops import gguf_quant as gq
 from .ops import indexer_qat
+
+
+# decode steps replay CUDA graphs of their static stretches (FI_V4_DECODE_GRAPHS=0: every launch from Python)
+_DECODE_GRAPHS = os.environ.get("FI_V4_DECODE_GRAPHS", "1") != "0"
+_DECODE_GRAPH_MAX_T = 8          # up to the batch the block-format GEMV serves in one pass
 
 
 @dataclass
@@ -284,6 +290,7 @@ class DeepseekV4FlashForCausalLM(nn.Module):
         self.requests: dict[str, RequestRows] = {}
         self._f32_cache: dict = {}
         self._merged: dict = {}
+        self._dgraphs: dict = {}
         self._ar = None
         self.register_buffer("inv_freq_window", c.rope_inv_freq(False).to(self.embed.device), persistent=False)
         self.register_buffer("inv_freq_compressed", c.rope_inv_freq(True).to(self.embed.device), persistent=False)
@@ -394,6 +401,7 @@ class DeepseekV4FlashForCausalLM(nn.Module):
             self._init_synthetic()
         self._f32_cache.clear()
         self._merged.clear()
+        self._dgraphs.clear()
         for layer in self.layers:
             if layer.hash_routed and bool(((layer.hash_table < 0) | (layer.hash_table >= self.cfg.experts)).any()):
                 raise ValueError("token-id routing table names an expert that does not exist")
@@ -505,16 +513,46 @@ class DeepseekV4FlashForCausalLM(nn.Module):
                    li: int) -> torch.Tensor:
         """``h`` ``[T, H]``: the projections run once for the whole group; the row appends, compressor steps
         and the attention itself walk the tokens in order (token t of a request sees the rows of tokens <= t)."""
+        ctx = self._attn_pre(layer, h, pos)
+        out = torch.empty(h.shape[0], self.cfg.heads, self.cfg.head_dim, dtype=torch.float32, device=h.device)
+        self._attn_rows(layer, li, rows_of, positions, pos, ctx, out)
+        return self._attn_post(layer, out, pos)
+
+    def _attn_pre(self, layer: V4Layer, h: torch.Tensor, pos: torch.Tensor) -> dict:
+        """Everything in front of the rows: layer-input norm, the stacked projection of everything that reads it,
+        low-rank query, per-head norm and rotary, the latent row (norm, rotary, fp8 round trip).  A pure function
+        of its inputs with static shapes (the decode path captures it in a CUDA graph)."""
         c, f = self.cfg, self._f32
-        T, D, W = h.shape[0], c.head_dim, c.window
+        T, D = h.shape[0], c.head_dim
         freq = self.inv_freq_compressed if layer.compressed else self.inv_freq_window
         x = nv.norm_rope(h, f(layer, "attn_norm"), None, None, c.eps)
         names = ("q_a", "kv_proj") + (("comp_kv", "comp_gate") if layer.compressed else ()) + \
             (("idx_kv", "idx_gate", "idx_w") if layer.indexed else ())
-        proj = self._project(layer, names, x)           # everything that reads the normed layer input
+        proj = self._project(layer, names, x)
         q_low = nv.norm_rope(proj[0], f(layer, "q_a_norm"), None, None, c.eps)
         q = nv.norm_rope(_lin(q_low, layer.q_b).view(T, c.heads, D), None, freq, pos, c.eps)
         kv = nv.norm_rope(proj[1], f(layer, "kv_norm"), freq, pos, c.eps, fp8=True)
+        return {"q": q, "kv": kv, "q_low": q_low, "proj": proj, "freq": freq}
+
+    def _attn_post(self, layer: V4Layer, out: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        """Inverse rotary of the attention output and the grouped low-rank output projection (static shapes)."""
+        c = self.cfg
+        T, D = out.shape[0], c.head_dim
+        freq = self.inv_freq_compressed if layer.compressed else self.inv_freq_window
+        out = nv.norm_rope(out, None, freq, pos, c.eps, norm=False, inverse=True)
+        gh = c.heads // c.o_groups
+        og = out.view(T, c.o_groups, gh * D).to(layer.o_a.dtype)
+        low = torch.einsum("grk,tgk->tgr", layer.o_a, og).float()
+        return _lin(low.reshape(T, -1), layer.o_b)
+
+    def _attn_rows(self, layer: V4Layer, li: int, rows_of: list, positions: list, pos: torch.Tensor, ctx: dict,
+                   out: torch.Tensor) -> None:
+        """The part that touches per-request state: window-row appends, attention over each request's rows,
+        compressor steps and emitted rows.  Writes ``out`` ``[T, heads, D]``."""
+        c, f = self.cfg, self._f32
+        q, kv, q_low, proj, freq = ctx["q"], ctx["kv"], ctx["q_low"], ctx["proj"], ctx["freq"]
+        T, D, W = q.shape[0], c.head_dim, c.window
+        h = q
         if layer.compressed:
             ckv, cgate, comp_ape = proj[2], proj[3], f(layer, "comp_ape")
         if layer.indexed:
@@ -522,7 +560,6 @@ class DeepseekV4FlashForCausalLM(nn.Module):
             iq = None                           # only needed once a request has more rows than the indexer keeps
         sinks = f(layer, "sinks")
         scale = 1.0 / math.sqrt(D)
-        out = torch.empty(T, c.heads, D, dtype=torch.float32, device=h.device)
         r = layer.ratio
         singles: list = []                      # tokens that are alone in their request (a decode batch)
         lone = sum(1 for j in range(T) if (j == 0 or rows_of[j - 1] is not rows_of[j])
@@ -586,11 +623,6 @@ class DeepseekV4FlashForCausalLM(nn.Module):
             self._attention_singles(layer, li, singles, rows_of, positions, pos, q, kv,
                                     (ckv, cgate, comp_ape) if layer.compressed else None,
                                     (ikv, igate, idx_ape, iq, iw) if layer.indexed else None, freq, sinks, scale, out)
-        out = nv.norm_rope(out, None, freq, pos, c.eps, norm=False, inverse=True)
-        gh = c.heads // c.o_groups
-        og = out.view(T, c.o_groups, gh * D).to(layer.o_a.dtype)
-        low = torch.einsum("grk,tgk->tgr", layer.o_a, og).float()
-        return _lin(low.reshape(T, -1), layer.o_b)
 
     def _attention_singles(self, layer: V4Layer, li: int, ts: list, rows_of: list, positions: list, pos, q, kv, comp, idx,
                            freq, sinks, scale, out) -> None:
@@ -808,8 +840,94 @@ class DeepseekV4FlashForCausalLM(nn.Module):
     @torch.inference_mode()
     def decode_tokens_batch(self, request_ids: list[str], last_tokens: list[int]) -> list[int]:
         """One token for each request; the projections and experts of the whole batch run together."""
-        hidden = self.forward_tokens([(self.requests[r], int(t)) for r, t in zip(request_ids, last_tokens)])
+        rows = [self.requests[r] for r in request_ids]
+        if self._decode_graphs_ok(rows):
+            return self._decode_step_graphs(rows, [int(t) for t in last_tokens])
+        hidden = self.forward_tokens([(r, int(t)) for r, t in zip(rows, last_tokens)])
         return self._next_tokens(hidden)
+
+    # ------------------------------------------------------------------ decode steps through CUDA graphs
+    # A decode step alternates between work with static shapes (everything except the rows) and work on
+    # per-request state whose sizes change from step to step (window appends, attention over a growing row set,
+    # compressor emissions).  The static stretches - from the output of one layer's attention to the input of the
+    # next layer's - are captured once per batch size and replayed: one launch instead of about forty-five.
+    def _decode_graphs_ok(self, rows: list) -> bool:
+        # dense (non-block) experts group their routes with a host read, which a capture cannot contain
+        return (_DECODE_GRAPHS and self.embed.is_cuda and 1 <= len(rows) <= _DECODE_GRAPH_MAX_T
+                and len({id(r) for r in rows}) == len(rows) and all(l.routed is not None for l in self.layers))
+
+    def _layer_tail(self, li: int, out: torch.Tensor, g: dict) -> None:
+        """Static stretch after layer ``li``'s rows: output projection, the feed-forward half, and either the next
+        layer's front or the head of the model.  Reads and writes the tensors kept in ``g``."""
+        c, f = self.cfg, self._f32
+        layer = self.layers[li]
+        streams = nv.hc_post(self._attn_post(layer, out, g["pos"]), g["streams"][li], g["state"][li])
+        st = nv.hc_pre(streams, f(layer, "hc_ffn_fn"), f(layer, "hc_ffn_base"), f(layer, "hc_ffn_scale"), c.eps)
+        streams = nv.hc_post(self._ffn(layer, st.mixed, g["ids"]), streams, st)
+        if li + 1 < len(self.layers):
+            self._layer_front(li + 1, streams, g)
+        else:
+            hidden = nv.hc_collapse(streams, f(self, "out_hc_fn"), f(self, "out_hc_base"), f(self, "out_hc_scale"), c.eps)
+            hidden = nv.norm_rope(hidden, f(self, "final_norm"), None, None, c.eps)
+            g["tokens"] = torch.argmax(_lin(hidden, self.lm_head), dim=-1)
+
+    def _layer_front(self, li: int, streams: torch.Tensor, g: dict) -> None:
+        c, f = self.cfg, self._f32
+        layer = self.layers[li]
+        st = nv.hc_pre(streams, f(layer, "hc_attn_fn"), f(layer, "hc_attn_base"), f(layer, "hc_attn_scale"), c.eps)
+        g["streams"][li], g["state"][li] = streams, st
+        g["ctx"][li] = self._attn_pre(layer, st.mixed, g["pos"])
+
+    def _capture_decode_graphs(self, T: int) -> dict:
+        c = self.cfg
+        dev = self.embed.device
+        L = len(self.layers)
+        g = {"ids": torch.zeros(T, dtype=torch.long, device=dev), "pos": torch.zeros(T, dtype=torch.long, device=dev),
+             "streams": [None] * L, "state": [None] * L, "ctx": [None] * L, "tokens": None,
+             "out": [torch.zeros(T, c.heads, c.head_dim, dtype=torch.float32, device=dev) for _ in range(L)]}
+
+        def front0():
+            streams = self.embed[g["ids"]].float().unsqueeze(1).repeat(1, c.hc, 1)
+            self._layer_front(0, streams, g)
+
+        # once eagerly on a side stream: lazily built caches, stacked projections, scratch buffers, kernel attributes
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            front0()
+            for li in range(L):
+                self._layer_tail(li, g["out"][li], g)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        graphs, pool = [], None
+        for k in range(L + 1):
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, pool=pool):
+                if k == 0:
+                    front0()
+                else:
+                    self._layer_tail(k - 1, g["out"][k - 1], g)
+            pool = pool or gr.pool()
+            graphs.append(gr)
+        g["graphs"] = graphs
+        return g
+
+    def _decode_step_graphs(self, rows: list, tokens: list) -> list[int]:
+        T = len(rows)
+        g = self._dgraphs.get(T)
+        if g is None:
+            g = self._dgraphs[T] = self._capture_decode_graphs(T)
+        positions = [r.pos for r in rows]
+        meta = torch.tensor([tokens, positions], dtype=torch.long, device=self.embed.device)
+        g["ids"].copy_(meta[0])
+        g["pos"].copy_(meta[1])
+        g["graphs"][0].replay()
+        for li, layer in enumerate(self.layers):
+            self._attn_rows(layer, li, rows, positions, g["pos"], g["ctx"][li], g["out"][li])
+            g["graphs"][li + 1].replay()
+        for r in rows:
+            r.pos += 1
+        return g["tokens"].tolist()
 
     def forward(self, batch, kv_caches, inputs_embeds=None):
         raise RuntimeError("DeepSeek-V4-Flash runs through its own executors (token ids in, token ids out)")
