@@ -360,3 +360,29 @@ def test_abort_releases_the_rows(llm):
     assert eng.abort_request("abort-me")
     assert eng.model.requests == {}
     assert not eng.has_unfinished_requests()
+
+
+def test_served_over_http_greedy_only():
+    """The OpenAI server in front of the model-owned data plane: greedy chat completions stream and finish, a
+    sampling temperature is refused with 400, and the rows are gone afterwards."""
+    import json
+    from fastapi.testclient import TestClient
+    from litevllm_b200.entrypoints.openai import api_server as srv
+    client = TestClient(srv.app)
+    saved = (srv.engine, srv.served_model, srv.debug_endpoints_enabled)
+    try:
+        srv.engine = srv.build_engine(PRESET, dtype="float32", device="cpu", max_num_seqs=2, max_model_len=128)
+        srv.served_model, srv.debug_endpoints_enabled = "v4", False
+        body = {"model": "v4", "messages": [{"role": "user", "content": "hello there"}], "max_tokens": 5, "temperature": 0}
+        r = client.post("/v1/chat/completions", json=body)
+        assert r.status_code == 200 and r.json()["usage"]["completion_tokens"] == 5
+        assert client.post("/v1/chat/completions", json=dict(body, temperature=0.7)).status_code == 400
+        with client.stream("POST", "/v1/chat/completions", json=dict(body, stream=True)) as s:
+            lines = [l for l in s.iter_lines() if l.startswith("data:")]
+        assert lines[-1] == "data: [DONE]" and len(lines) >= 3
+        assert json.loads(lines[0][5:])["choices"][0]["delta"] == {"role": "assistant"}
+        assert srv.engine.engine.model.requests == {}
+    finally:
+        if srv.engine is not None:
+            srv.engine.shutdown()
+        srv.engine, srv.served_model, srv.debug_endpoints_enabled = saved
