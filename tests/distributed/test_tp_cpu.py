@@ -59,3 +59,27 @@ def test_ep2_matches_single_rank(preset):
         got = [json.load(open(os.path.join(d, f"rank{r}.json"))) for r in range(2)]
     assert got[0] == got[1], "ranks diverged"
     assert got[0] == want
+
+
+def _tpep_worker(rank, world, out_dir, preset):
+    from litevllm_b200 import LLM, SamplingParams
+    llm = LLM(f"synthetic:{preset}", dtype="float32", device="cpu", max_num_seqs=4, max_model_len=128,
+              tensor_parallel_size=world, expert_parallel_size=world, comm_backend="nccl")
+    outs = llm.generate(_prompts(), SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))
+    with open(os.path.join(out_dir, f"rank{rank}.json"), "w") as f:
+        json.dump([o.outputs[0].token_ids for o in outs], f)
+    llm.shutdown()
+
+
+@pytest.mark.parametrize("preset", ["tiny-gemma4-moe-test", "tiny-deepseek-test"])
+def test_tp2_with_ep2_matches_single_rank(preset):
+    """Both at once on the same two ranks: attention and dense layers tensor parallel, experts sharded."""
+    from litevllm_b200 import LLM, SamplingParams
+    ref = LLM(f"synthetic:{preset}", dtype="float32", device="cpu", max_num_seqs=4, max_model_len=128)
+    want = [o.outputs[0].token_ids for o in
+            ref.generate(_prompts(), SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))]
+    with tempfile.TemporaryDirectory() as d:
+        spawn(_tpep_worker, 2, args=(d, preset), port=29545 if "gemma" in preset else 29546)
+        got = [json.load(open(os.path.join(d, f"rank{r}.json"))) for r in range(2)]
+    assert got[0] == got[1], "ranks diverged"
+    assert got[0] == want
