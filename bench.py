@@ -276,22 +276,25 @@ def run_ours(args) -> dict:
     N_CHECK = 16
 
     # ------------------------------------------------------------------ TP=1 reference tokens (multi-GPU runs)
-    # Rank 0 runs the same prompts through a one-GPU engine on its own GPU before the parallel engine
-    # exists; the parallel run's first tokens are compared with these.
+    # Every rank runs the same prompts through a one-GPU engine on its own GPU before the parallel engine exists;
+    # the parallel run's first tokens are compared with rank 0's.  All ranks do it, not only rank 0: a rank that
+    # skipped this pass would enter the first parallel step with cold kernels (lazy module loads, attribute
+    # set-up) and fall behind the warm rank by more than the one-second budget of the in-kernel peer waits.
     tp1_tokens = None
     if world > 1 and args.check_tokens:
-        if rank == 0:
-            llm1 = _build_llm(args, 1, local_rank, 1, 1, max_len)
-            vocab1 = llm1.engine.arch.vocab_size
-            g1 = torch.Generator().manual_seed(1234)
-            ids1 = torch.randint(0, vocab1, (B, P), generator=g1, dtype=torch.int64)
-            tp1_logits = {}
-            tp1_tokens = _greedy_tokens(llm1.engine, [r.tolist() for r in ids1], N_CHECK, "tp1", tp1_logits)
-            llm1.shutdown()
-            del llm1
-            import gc
-            gc.collect()
-            torch.cuda.empty_cache()
+        llm1 = _build_llm(args, 1, local_rank, 1, 1, max_len)
+        vocab1 = llm1.engine.arch.vocab_size
+        g1 = torch.Generator().manual_seed(1234)
+        ids1 = torch.randint(0, vocab1, (B, P), generator=g1, dtype=torch.int64)
+        tp1_logits = {}
+        tp1_tokens = _greedy_tokens(llm1.engine, [r.tolist() for r in ids1], N_CHECK, "tp1", tp1_logits)
+        if rank != 0:
+            tp1_tokens = None
+        llm1.shutdown()
+        del llm1
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
 
     if args.profile_json:
         from litevllm_b200.utils.profiling import PROFILER

@@ -87,10 +87,14 @@ class Gemma4Attention(nn.Module):
 class Gemma4MLP(nn.Module):
     def __init__(self, arch: ModelArch, inter: int, dtype, qc, prefix: str):
         super().__init__()
-        self.gate_up_proj = LiteLinear(arch.hidden_size, 2 * inter, dtype=dtype, shard="column", quant_config=qc,
-                                       prefix=prefix + ".gate_up_proj", gated_act="gelu_tanh", out_splits=[inter, inter])
-        self.down_proj = LiteLinear(inter, arch.hidden_size, dtype=dtype, shard="row", quant_config=qc,
-                                    prefix=prefix + ".down_proj")
+        # the tcgen05 GEMMs step through K in blocks of 64: an intermediate width whose per-rank share is not a
+        # multiple of that (2112 over two ranks) stays whole on every rank instead of being sharded
+        sharded = inter % (64 * pstate.tp_size()) == 0
+        self.gate_up_proj = LiteLinear(arch.hidden_size, 2 * inter, dtype=dtype, shard="column" if sharded else None,
+                                       quant_config=qc, prefix=prefix + ".gate_up_proj", gated_act="gelu_tanh",
+                                       out_splits=[inter, inter])
+        self.down_proj = LiteLinear(inter, arch.hidden_size, dtype=dtype, shard="row" if sharded else None,
+                                    quant_config=qc, prefix=prefix + ".down_proj")
 
     def forward(self, x, batch):
         return self.down_proj(self.gate_up_proj(x, lora_mapping=batch.lora_mapping), lora_mapping=batch.lora_mapping)
