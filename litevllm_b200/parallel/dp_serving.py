@@ -69,6 +69,10 @@ def replica_serve_loop(engine, link: ReplicaLink, idle_sleep_s: float = 0.001, o
                 break
             kind = msg[0]
             if kind == "shutdown":
+                try:
+                    link.send_up(("bye",))      # rank 0 keeps the store up until every replica has read its shutdown
+                except Exception:
+                    pass
                 return steps
             if kind == "abort":
                 engine.abort_request(msg[1])
@@ -193,14 +197,30 @@ class DataParallelRouter:
             for rid in list(self._streams):
                 self._finish_remote(rid, EngineFatalError(f"data-parallel pump stopped: {e!r}"))
 
-    def shutdown(self) -> None:
-        for link in self.links.values():
-            try:
-                link.send_down(("shutdown",))
-            except Exception:
-                pass
+    def shutdown(self, wait_s: float = 5.0) -> None:
+        """Tell every replica to stop and wait (bounded) for each to acknowledge: rank 0 hosts the mailbox store, so
+        leaving before a replica has read its shutdown message would show up there as a lost store."""
         self._stop.set()
         self._pump.join(timeout=2.0)
+        waiting = set()
+        for r, link in self.links.items():
+            try:
+                link.send_down(("shutdown",))
+                waiting.add(r)
+            except Exception:
+                pass
+        deadline = time.monotonic() + wait_s
+        while waiting and time.monotonic() < deadline:
+            for r in list(waiting):
+                try:
+                    msg = self.links[r].poll_up()
+                except Exception:
+                    waiting.discard(r)
+                    continue
+                if msg is not None and msg[0] == "bye":
+                    waiting.discard(r)
+            if waiting:
+                time.sleep(0.002)
 
     def stats(self) -> dict:
         with self._lock:
