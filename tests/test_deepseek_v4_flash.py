@@ -127,3 +127,77 @@ def test_native_kernels_match_torch_forms():
     iq, iw, crow = torch.randn(64, 128, generator=g), torch.rand(64, generator=g), torch.randn(1000, 128, generator=g)
     assert torch.allclose(v4.indexer_scores(iq.to(dev), iw.to(dev), crow.to(dev)).cpu(), v4.indexer_scores(iq, iw, crow),
                           atol=1e-3, rtol=1e-4)
+
+
+def test_compressor_run_matches_token_by_token():
+    """A run of tokens pooled at once gives the rows, and leaves the state, of feeding them one at a time."""
+    from litevllm_b200.models.deepseek_v4_flash import native as nv
+    from litevllm_b200.models.deepseek_v4_flash.attention import CompressorState, compressor_step
+    g = torch.Generator().manual_seed(0)
+    for ratio, D in ((4, 16), (8, 16), (3, 8)):
+        width = (2 if ratio == 4 else 1) * D
+        ape = torch.randn(ratio, width, generator=g)
+        for p0, n in ((0, 11), (0, 3), (5, 9), (7, 1), (6, 20), (2, 2)):
+            one, run = CompressorState.empty(D, ratio), CompressorState.empty(D, ratio)
+            kvs, scs = torch.randn(p0 + n, width, generator=g), torch.randn(p0 + n, width, generator=g)
+            for t in range(p0):
+                one, _ = compressor_step(one, kvs[t], scs[t], ape, t, D, ratio)
+                run, _ = compressor_step(run, kvs[t], scs[t], ape, t, D, ratio)
+            want = []
+            for t in range(p0, p0 + n):
+                one, e = compressor_step(one, kvs[t], scs[t], ape, t, D, ratio)
+                if e is not None:
+                    want.append(e)
+            got = nv.compressor_run_(run, kvs[p0:], scs[p0:], ape, p0, D, ratio)
+            assert got.shape[0] == len(want)
+            if want:
+                torch.testing.assert_close(got, torch.stack(want))
+            more = torch.randn(2, 2 * ratio, width, generator=g)
+            for i in range(2 * ratio):           # both continue token by token: the next windows agree as well
+                one, ea = compressor_step(one, more[0, i], more[1, i], ape, p0 + n + i, D, ratio)
+                run, eb = compressor_step(run, more[0, i], more[1, i], ape, p0 + n + i, D, ratio)
+                assert (ea is None) == (eb is None)
+                if ea is not None:
+                    torch.testing.assert_close(ea, eb)
+
+
+def test_attention_run_matches_token_by_token():
+    """The run form (window spans of one linear buffer + a prefix or a selection of compressed rows) against
+    one ``shared_kv_attention`` call per token."""
+    from litevllm_b200.models.deepseek_v4_flash.attention import shared_kv_attention, shared_kv_attention_run
+    g = torch.Generator().manual_seed(4)
+    n, heads, D, W = 7, 3, 128, 5
+    q = torch.randn(n, heads, D, generator=g)
+    lin, comp = torch.randn(n + W - 1, D, generator=g), torch.randn(9, D, generator=g)
+    sinks = torch.randn(heads, generator=g)
+    ends = [W - 1 + j + 1 for j in range(n)]
+    a0 = [max(0, e - W) for e in ends]
+    na = [e - a for e, a in zip(ends, a0)]
+    nb = [min(9, 2 + j) for j in range(n)]
+    spans = torch.tensor([a0, na, nb], dtype=torch.int32)
+    got = shared_kv_attention_run(q, lin, comp, spans, None, sinks, 0.11)
+    for j in range(n):
+        rows = torch.cat([lin[a0[j]:a0[j] + na[j]], comp[:nb[j]]])
+        torch.testing.assert_close(got[j], shared_kv_attention(q[j], rows, sinks, 0.11))
+    sel = torch.stack([torch.randperm(9, generator=g)[:4] for _ in range(n)]).to(torch.int32)
+    spans[2] = torch.tensor([min(4, v) for v in nb], dtype=torch.int32)
+    got = shared_kv_attention_run(q, lin, comp, spans, sel, sinks, 0.11)
+    for j in range(n):
+        k = int(spans[2, j])
+        rows = torch.cat([lin[a0[j]:a0[j] + na[j]], comp[sel[j, :k].long()]])
+        torch.testing.assert_close(got[j], shared_kv_attention(q[j], rows, sinks, 0.11))
+
+
+def test_layer_rows_grow_and_keep_their_rows():
+    from litevllm_b200.models.deepseek_v4_flash.model import LayerRows
+    lr = LayerRows(pool=torch.zeros(4 + 2, 8), window=4, index_pool=torch.zeros(2, 128), ratio=4)
+    rows = torch.arange(40 * 8, dtype=torch.float32).reshape(40, 8)
+    idx = torch.arange(40 * 128, dtype=torch.float32).reshape(40, 128)
+    lr.append_compressed(rows[0], idx[0])
+    lr.append_compressed_many(rows[1:30], idx[1:30])
+    for i in range(30, 40):
+        lr.append_compressed(rows[i], idx[i])
+    assert lr.n_comp == 40 and lr.pool.shape[0] >= 44
+    torch.testing.assert_close(lr.compressed, rows)
+    torch.testing.assert_close(lr.index_rows, idx)
+    assert lr.bytes() == lr.pool.numel() * 4 + lr.index_pool.numel() * 4
