@@ -250,7 +250,7 @@ def test_gguf_checkpoint_round_trip(llm, tmp_path):
 
 
 @pytest.mark.gpu
-def test_gguf_checkpoint_on_gpu_matches_cpu(llm, tmp_path):
+def test_gguf_checkpoint_on_gpu_matches_cpu(llm, tmp_path, monkeypatch):
     """The checkpoint formats of the full-size model (Q8_0 projections, IQ2_XXS / Q2_K routed experts) stay in
     block format on the GPU and run through the GGUF GEMV and expert kernels; tokens follow the CPU model that
     dequantises the same file."""
@@ -262,6 +262,12 @@ def test_gguf_checkpoint_on_gpu_matches_cpu(llm, tmp_path):
     want, got = _tokens(cpu, PROMPTS, 6), _tokens(gpu, PROMPTS, 6)
     agree = sum(a == b for w, g in zip(want, got) for a, b in zip(w, g)) / sum(len(w) for w in want)
     assert got[0][0] == want[0][0] and agree >= 0.3, (want, got)
+    # decode steps replay CUDA graphs of their static stretches; the same steps launched one by one walk the same way
+    from litevllm_b200.models.deepseek_v4_flash import model as v4_model
+    assert gpu.engine.model._dgraphs, "the decode graphs were not used"
+    monkeypatch.setattr(v4_model, "_DECODE_GRAPHS", False)
+    eager = _tokens(gpu, PROMPTS, 6)
+    assert all(a[:3] == b[:3] for a, b in zip(eager, got)), (eager, got)
 
 
 @pytest.mark.gpu
