@@ -203,6 +203,12 @@ def _deepseek4_config(g: "GGUFFile") -> dict:
         t = g.tensors.get(name)
         return t["shape"] if t is not None else default
 
+    for key in ("block_count", "embedding_length", "attention.head_count"):
+        if g.get(key) is None:
+            raise ValueError(f"{g.path}: deepseek4 metadata lacks {key!r}")
+    for name in ("token_embd.weight", "blk.0.attn_q_a.weight", "blk.0.attn_output_b.weight", "blk.0.ffn_gate_exps.weight"):
+        if name not in g.tensors:
+            raise ValueError(f"{g.path}: deepseek4 file lacks the tensor {name!r}")
     layers = int(g.get("block_count"))
     head_dim = int(g.get("attention.key_length", 512))
     heads = int(g.get("attention.head_count", 64))

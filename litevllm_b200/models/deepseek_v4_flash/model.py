@@ -356,18 +356,20 @@ class DeepseekV4FlashForCausalLM(nn.Module):
             layer.routed.device = self.embed.device
         return layer.routed
 
-    def load_weights(self, weights):
+    def load_weights(self, weights, strict: bool = True):
         """Named tensors (parameter names, or the checkpoint family's GGUF names) go into the parameters.  Dense
         tensors are copied; one with the right element count but another layout of the same matrix (transposed
         position table, flattened groups) is reshaped.  Block-quantised tensors stay in HBM as they are where
         the model only multiplies by them (projections -> ``BlockMatrix``, routed experts -> the expert-grouped
         GGUF kernels) and are dequantised once otherwise (embedding, tables, grouped output factor).  A synthetic
         checkpoint has no tensors and gets seeded random weights (norm gains 1, hyper-connection scales small,
-        a random hash table)."""
+        a random hash table).  ``strict``: a checkpoint that delivers tensors has to deliver all of them."""
         from ...loaders.gguf import GGUFTensor
         consumed = set()
+        bound = set()                       # parameter names that received a tensor
         for name, t in weights:
-            owner, attr = self._owner(self.param_name(name))
+            pname = self.param_name(name)
+            owner, attr = self._owner(pname)
             target = getattr(owner, attr, None) if owner is not None else None
             expert = attr in self._EXPERTS and isinstance(owner, V4Layer)
             if not isinstance(target, (torch.Tensor, BlockMatrix)) and not (
@@ -379,6 +381,7 @@ class DeepseekV4FlashForCausalLM(nn.Module):
                     owner._parameters.pop(attr, None)
                     setattr(owner, attr, None)
                     consumed.add(name)
+                    bound.add(pname)
                     continue
                 rows = t.raw.reshape(-1, t.raw.shape[-1])
                 if attr in self._LINEAR and isinstance(target, torch.Tensor) and target.dim() == 2:
@@ -387,6 +390,7 @@ class DeepseekV4FlashForCausalLM(nn.Module):
                     owner._parameters.pop(attr, None)
                     setattr(owner, attr, BlockMatrix(rows, t.ggml_type, t.K, self.embed.device))
                     consumed.add(name)
+                    bound.add(pname)
                     continue
                 t = gq.dequantize(rows, t.ggml_type, t.K).reshape(t.shape)
             if isinstance(target, BlockMatrix):
@@ -397,8 +401,19 @@ class DeepseekV4FlashForCausalLM(nn.Module):
                 t = t.t() if t.dim() == 2 and t.shape == target.shape[::-1] else t.reshape(target.shape)
             target.data.copy_(t.to(target.dtype))
             consumed.add(name)
+            bound.add(pname)
         if not consumed:
             self._init_synthetic()
+        elif strict:
+            # a checkpoint binds every tensor of the model or none: a parameter left as allocated would be noise
+            expected = {n for n, _ in self.named_parameters()} | {n for n, _ in self.named_buffers() if "inv_freq" not in n}
+            expected |= {f"layers.{i}.{a}" for i, l in enumerate(self.layers) for a in self._EXPERTS
+                         if l.routed is not None or self.cfg.block_experts}
+            expected -= {f"layers.{i}.router_bias" for i in range(len(self.layers))}     # optional: zeros without it
+            missing = sorted(expected - bound)
+            if missing:
+                raise ValueError(f"checkpoint leaves {len(missing)} tensors of the model unbound: "
+                                 + ", ".join(missing[:8]) + (" ..." if len(missing) > 8 else ""))
         self._f32_cache.clear()
         self._merged.clear()
         self._dgraphs.clear()

@@ -162,11 +162,13 @@ def test_checkpoint_tensor_names_map_to_parameters(llm):
     try:
         new = torch.arange(keep.numel(), dtype=torch.float32).reshape(keep.shape)
         consumed = model.load_weights([("blk.3.attn_compressor_ape.weight", new.t().contiguous()),
-                                       ("blk.9.unknown.weight", torch.zeros(1))])
+                                       ("blk.9.unknown.weight", torch.zeros(1))], strict=False)
         assert consumed == {"blk.3.attn_compressor_ape.weight"}
         torch.testing.assert_close(model.layers[3].comp_ape.float(), new)
         with pytest.raises(ValueError):
-            model.load_weights([("output_norm.weight", torch.zeros(3))])
+            model.load_weights([("output_norm.weight", torch.zeros(3))], strict=False)
+        with pytest.raises(ValueError, match="unbound"):       # a checkpoint delivers every tensor or none
+            model.load_weights([("blk.3.attn_compressor_ape.weight", new)])
     finally:
         model.layers[3].comp_ape.data.copy_(keep)
 
@@ -392,3 +394,16 @@ def test_served_over_http_greedy_only():
         if srv.engine is not None:
             srv.engine.shutdown()
         srv.engine, srv.served_model, srv.debug_endpoints_enabled = saved
+
+
+def test_deepseek4_files_are_validated(tmp_path):
+    from litevllm_b200.loaders.gguf import hf_config_from_gguf, write_gguf
+    f = tmp_path / "bad.gguf"
+    write_gguf(f, {"general.architecture": "deepseek4", "deepseek4.embedding_length": 256},
+               {"token_embd.weight": torch.zeros(8, 256)})
+    with pytest.raises(ValueError, match="block_count"):
+        hf_config_from_gguf(f)
+    write_gguf(f, {"general.architecture": "deepseek4", "deepseek4.embedding_length": 256, "deepseek4.block_count": 2,
+                   "deepseek4.attention.head_count": 4}, {"token_embd.weight": torch.zeros(8, 256)})
+    with pytest.raises(ValueError, match="attn_q_a"):
+        hf_config_from_gguf(f)
