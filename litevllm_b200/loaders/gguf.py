@@ -154,6 +154,9 @@ def write_gguf(path: str | Path, metadata: dict, tensors: dict, alignment: int =
 def hf_config_from_gguf(path: str | Path) -> dict:
     g = GGUFFile(path)
     a = g.arch()
+    for key in ("embedding_length", "block_count"):
+        if g.get(key) is None:
+            raise ValueError(f"{g.path}: GGUF metadata lacks {a}.{key}")
     heads = int(g.get("attention.head_count", 32))
     hidden = int(g.get("embedding_length"))
     cfg = {
