@@ -282,14 +282,19 @@ def run_ours(args) -> dict:
     # set-up) and fall behind the warm rank by more than the one-second budget of the in-kernel peer waits.
     tp1_tokens = None
     if world > 1 and args.check_tokens:
-        llm1 = _build_llm(args, 1, local_rank, 1, 1, max_len)
+        # replicas serve their own share of the prompts at their own batch size: the reference pass does the same,
+        # so that both walk through identical kernels and the tokens can be compared bit for bit
+        shard = mine if mode == "dp" else list(range(B))
+        llm1 = _build_llm(args, 1, local_rank, 1, 1, max_len, batch=len(shard))
         vocab1 = llm1.engine.arch.vocab_size
         g1 = torch.Generator().manual_seed(1234)
         ids1 = torch.randint(0, vocab1, (B, P), generator=g1, dtype=torch.int64)
         tp1_logits = {}
-        tp1_tokens = _greedy_tokens(llm1.engine, [r.tolist() for r in ids1], N_CHECK, "tp1", tp1_logits)
-        if rank != 0:
-            tp1_tokens = None
+        shard_tokens = _greedy_tokens(llm1.engine, [ids1[i].tolist() for i in shard], N_CHECK, "tp1", tp1_logits)
+        tp1_tokens = None
+        if rank == 0:        # indexed by prompt number, like the run that follows
+            tp1_tokens = {i: shard_tokens[k] for k, i in enumerate(shard)}
+            tp1_logits = {i: tp1_logits[k] for k, i in enumerate(shard) if k in tp1_logits}
         llm1.shutdown()
         del llm1
         import gc
