@@ -31,6 +31,9 @@ class RequestScheduler:
         self._running_set: set[str] = set()
         self.free_slots: deque[int] = deque(range(max_active))
         self._streams: dict[str, asyncio.Queue] = {}
+        # streams of requests that were released before their consumer read (or started to read) them: a short
+        # request can finish, or a fatal error can end it, between admission and the consumer's first await
+        self._late_streams: dict[str, asyncio.Queue] = {}
         self._stream_loops: dict[str, asyncio.AbstractEventLoop] = {}
         self._sync_outputs: dict[str, list] = {}
         self._terminal_sent: set[str] = set()
@@ -122,16 +125,19 @@ class RequestScheduler:
                 box.append(item)
 
     async def get_request_stream(self, request_id: str):
-        q = self._streams.get(request_id)
+        q = self._streams.get(request_id) or self._late_streams.get(request_id)
         if q is None:
             raise KeyError(f"no stream for request {request_id!r}")
-        while True:
-            item = await q.get()
-            if item is _DONE:
-                return
-            if isinstance(item, BaseException):
-                raise item
-            yield item
+        try:
+            while True:
+                item = await q.get()
+                if item is _DONE:
+                    return
+                if isinstance(item, BaseException):
+                    raise item
+                yield item
+        finally:
+            self._late_streams.pop(request_id, None)
 
     def pop_sync_outputs(self, request_id: str) -> list:
         return self._sync_outputs.pop(request_id, [])
@@ -155,7 +161,11 @@ class RequestScheduler:
         if st.slot_idx >= 0:
             self.free_slots.append(st.slot_idx)
             st.slot_idx = -1
-        self._streams.pop(request_id, None)
+        q = self._streams.pop(request_id, None)
+        if q is not None:
+            self._late_streams[request_id] = q
+            while len(self._late_streams) > 1024:        # consumers that never came: drop the oldest
+                self._late_streams.pop(next(iter(self._late_streams)))
         self._stream_loops.pop(request_id, None)
         self._terminal_sent.discard(request_id)
         return st

@@ -1,0 +1,142 @@
+"""Behavioural contracts of the runtime seen from the engine's public surface (CPU, tiny synthetic model):
+finish reasons, stop strings, context limit, planner arithmetic, fatal background errors, queue capacity.
+Reference behaviour: vllm/engine/output_pipeline.py:11-122, vllm/engine/runtime_planner.py:61-104,
+vllm/engine/lite_engine.py:858-898, vllm/engine/request_scheduler.py:12-284."""
+import asyncio
+
+import pytest
+import torch
+
+from litevllm_b200 import LLM, SamplingParams
+from litevllm_b200.engine.errors import EngineFatalError, InvalidRequestError, RequestRejectedError
+
+
+@pytest.fixture(scope="module")
+def llm():
+    return LLM("synthetic:tiny-llama-test", device="cpu", dtype="float32", max_num_seqs=4, max_model_len=64)
+
+
+def _ids(n, k=3):
+    return {"prompt_token_ids": [(k * i + 5) % 400 + 2 for i in range(n)]}
+
+
+def test_finish_reasons_length_eos_and_context_limit(llm):
+    out = llm.generate([_ids(8)], SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True))[0]
+    assert out.finished and out.outputs[0].finish_reason == "length" and len(out.outputs[0].token_ids) == 5
+    # the token the model would produce first, declared a stop token: generation ends on it with reason "stop"
+    first = out.outputs[0].token_ids[0]
+    eng = llm.engine
+    saved = eng.arch.eos_token_ids
+    try:
+        eng.arch.eos_token_ids = [first]
+        eng._lazy_built = False
+        stopped = llm.generate([_ids(8)], SamplingParams(max_tokens=5, temperature=0.0))[0]
+        assert stopped.outputs[0].finish_reason == "stop" and stopped.outputs[0].token_ids == [first]
+        kept = llm.generate([_ids(8)], SamplingParams(max_tokens=5, temperature=0.0, min_tokens=3))[0]
+        assert len(kept.outputs[0].token_ids) >= 3           # the stop token is masked until min_tokens
+    finally:
+        eng.arch.eos_token_ids = saved
+        eng._lazy_built = False
+    # prompt + generated tokens never exceed the planned context: the request ends with "length" at the limit
+    limit = eng.plan.max_model_len
+    with pytest.raises((InvalidRequestError, RequestRejectedError)):
+        llm.generate([_ids(limit - 4)], SamplingParams(max_tokens=50, temperature=0.0, ignore_eos=True))
+    near = llm.generate([_ids(limit - 4)], SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True))[0]
+    assert near.finished and len(near.prompt_token_ids) + len(near.outputs[0].token_ids) <= limit
+
+
+def test_stop_strings_cut_the_text(llm):
+    base = llm.generate(["abc"], SamplingParams(max_tokens=12, temperature=0.0, ignore_eos=True))[0].outputs[0]
+    text = base.text
+    if len(text) < 4:
+        pytest.skip("the dummy tokenizer produced too little text to pick a stop string from")
+    stop = text[2:4]
+    cut = llm.generate(["abc"], SamplingParams(max_tokens=12, temperature=0.0, ignore_eos=True, stop=[stop]))[0].outputs[0]
+    assert cut.finish_reason == "stop" and stop not in cut.text and text.startswith(cut.text)
+    kept = llm.generate(["abc"], SamplingParams(max_tokens=12, temperature=0.0, ignore_eos=True, stop=[stop],
+                                                include_stop_str_in_output=True))[0].outputs[0]
+    assert kept.text.endswith(stop)
+
+
+def test_planner_aligns_context_and_counts_blocks(llm):
+    plan = llm.engine.plan
+    assert plan.max_model_len % plan.block_size == 0 and plan.max_model_len <= 64
+    assert plan.num_blocks_per_seq == plan.max_model_len // plan.block_size
+    assert plan.num_total_blocks == 1 + plan.max_active_requests * plan.num_blocks_per_seq     # block 0 is the null block
+    assert plan.max_active_requests <= 4 and plan.step_token_budget >= plan.max_active_requests
+
+
+def test_generate_serves_more_prompts_than_slots_in_groups(llm):
+    prompts = [_ids(6 + i, k=i + 2) for i in range(9)]           # 9 prompts, 4 slots
+    outs = llm.generate(prompts, SamplingParams(max_tokens=3, temperature=0.0, ignore_eos=True))
+    assert [o.prompt_token_ids for o in outs] == [p["prompt_token_ids"] for p in prompts]
+    alone = [llm.generate([p], SamplingParams(max_tokens=3, temperature=0.0, ignore_eos=True))[0] for p in prompts[:3]]
+    assert [o.outputs[0].token_ids for o in outs[:3]] == [o.outputs[0].token_ids for o in alone]
+    assert not llm.engine.has_unfinished_requests()
+
+
+def test_queue_capacity_rejects_and_releases(llm):
+    eng = llm.engine
+    sp = SamplingParams(max_tokens=2, temperature=0.0, ignore_eos=True)
+    accepted = []
+    with pytest.raises(RequestRejectedError):
+        for i in range(200):                                       # capacity = a small multiple of the slots
+            eng.add_request(f"q{i}", _ids(5), sp)
+            accepted.append(f"q{i}")
+    assert len(accepted) >= eng.max_active_requests
+    for rid in accepted:
+        eng.abort_request(rid)
+    assert not eng.has_unfinished_requests()
+    assert eng.kv_manager.allocator.num_free == eng.plan.num_total_blocks - 1       # every block came back
+
+
+def test_fatal_background_error_fails_streams_and_closes_admission():
+    llm = LLM("synthetic:tiny-llama-test", device="cpu", dtype="float32", max_num_seqs=2, max_model_len=64)
+    eng = llm.engine
+    loop = asyncio.new_event_loop()
+    try:
+        eng.add_request("a", _ids(6), SamplingParams(max_tokens=20, temperature=0.0, ignore_eos=True), loop=loop)
+        stream = eng.get_request_stream("a")
+        eng.step()
+        eng.handle_background_error(RuntimeError("device lost"))
+
+        async def drain():
+            got = []
+            try:
+                async for item in stream:
+                    got.append(item)
+            except Exception as e:        # the published error ends the stream
+                got.append(e)
+            return got
+
+        items = loop.run_until_complete(asyncio.wait_for(drain(), 10))
+        assert items and isinstance(items[-1], Exception) and "device lost" in repr(items[-1]), items
+        assert not eng.has_unfinished_requests()
+        with pytest.raises(EngineFatalError):
+            eng.add_request("b", _ids(4), SamplingParams(max_tokens=2))
+        with pytest.raises(EngineFatalError):
+            eng.step()
+    finally:
+        loop.close()
+        llm.shutdown()
+
+
+def test_a_stream_read_after_the_request_finished_still_delivers(llm):
+    """A one-token request can finish inside the step that admitted it, before its consumer awaits the stream
+    for the first time; the outputs must still be there."""
+    eng = llm.engine
+    loop = asyncio.new_event_loop()
+    try:
+        eng.add_request("late", _ids(5), SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True), loop=loop)
+        while eng.has_unfinished_requests():
+            eng.step()
+
+        async def drain():
+            return [item async for item in eng.get_request_stream("late")]
+
+        items = loop.run_until_complete(asyncio.wait_for(drain(), 10))
+        assert items and items[-1].finished and len(items[-1].outputs[0].token_ids) == 1
+        with pytest.raises(KeyError):                       # consumed: the stream is gone
+            loop.run_until_complete(drain())
+    finally:
+        loop.close()
