@@ -140,3 +140,95 @@ def test_a_stream_read_after_the_request_finished_still_delivers(llm):
             loop.run_until_complete(drain())
     finally:
         loop.close()
+
+
+def test_async_engine_concurrency_early_exit_and_fatal_step():
+    """Several clients at once, a client that walks away after the first chunk (its request is aborted and its
+    slot and blocks come back), and a step that raises in the background loop: every open stream ends with the
+    error, the engine reports unhealthy and refuses new work."""
+    from litevllm_b200.config.config_builder import build_vllm_config
+    from litevllm_b200.engine.async_llm import AsyncLLM
+    from litevllm_b200.engine.errors import LiteRuntimeError
+
+    async def run():
+        eng = AsyncLLM(build_vllm_config("synthetic:tiny-llama-test", dtype="float32", device="cpu", max_num_seqs=4,
+                                         max_model_len=64))
+        try:
+            sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+
+            async def client(i):
+                return [o async for o in eng.generate(_ids(5 + i, k=i + 2), sp, f"c{i}")]
+
+            results = await asyncio.gather(*[client(i) for i in range(6)])        # 6 clients, 4 slots
+            assert all(r[-1].finished and len(r[-1].outputs[0].token_ids) == 6 for r in results)
+            # early exit
+            agen = eng.generate(_ids(7), SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True), "walker")
+            first = await agen.__anext__()
+            assert not first.finished
+            await agen.aclose()
+            for _ in range(200):
+                if eng.stats()["scheduler"]["running"] == 0:
+                    break
+                await asyncio.sleep(0.01)
+            st = eng.stats()
+            assert st["scheduler"]["running"] == 0 and st["scheduler"]["queued"] == 0
+            inner = eng.engine
+            assert inner.kv_manager.allocator.num_free == inner.plan.num_total_blocks - 1
+            # a step that raises
+            await eng.submit(_ids(6), SamplingParams(temperature=0.0, max_tokens=30, ignore_eos=True), "doomed")
+            boom = RuntimeError("step exploded")
+
+            def bad_step():
+                raise boom
+            inner.controller.step = bad_step
+            with pytest.raises(Exception) as ei:
+                async for _ in eng.stream("doomed"):
+                    pass
+            assert "step exploded" in repr(ei.value) or "fatal" in repr(ei.value).lower()
+            for _ in range(200):
+                if not eng.is_healthy():
+                    break
+                await asyncio.sleep(0.01)
+            assert not eng.is_healthy()
+            with pytest.raises(LiteRuntimeError):
+                await eng.submit(_ids(4), sp, "after")
+        finally:
+            eng.shutdown()
+
+    asyncio.run(run())
+
+
+def _llm_with(keyvals, **kw):
+    cfg = {"profile": "balanced", "tuning_keyvals": {f"FASTINFERENCE_{k}": str(v) for k, v in keyvals.items()}}
+    return LLM("synthetic:tiny-llama-test", device="cpu", dtype="float32", max_num_seqs=4, max_model_len=128,
+               fastinference_config=cfg, **kw)
+
+
+def test_chunked_prefill_and_prefix_cache_do_not_change_tokens():
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    long_prompt = _ids(70, k=7)
+    shared = [{"prompt_token_ids": long_prompt["prompt_token_ids"][:48] + [9, 8, 7, 6]},
+              {"prompt_token_ids": long_prompt["prompt_token_ids"][:48] + [11, 12, 13]}]
+    plain = _llm_with({})
+    try:
+        want = [o.outputs[0].token_ids for o in plain.generate([long_prompt] + shared, sp)]
+    finally:
+        plain.shutdown()
+    chunked = _llm_with({"LITE_PREFILL_CHUNK": 16, "MIN_PREFILL_CHUNK": 16, "MAX_PREFILL_CHUNK": 16})
+    try:
+        assert chunked.engine.plan.prefill_chunk_size == 16
+        got = [o.outputs[0].token_ids for o in chunked.generate([long_prompt] + shared, sp)]
+        assert got == want
+        assert chunked.engine.stats()["observer"]["counters"]["steps"] >= 5      # 70 tokens in chunks of 16
+    finally:
+        chunked.shutdown()
+    cached = _llm_with({"PREFIX_CACHE_MAX_ENTRIES": 8})
+    try:
+        first = [o.outputs[0].token_ids for o in cached.generate([long_prompt], sp)]
+        again = [o.outputs[0].token_ids for o in cached.generate([long_prompt], sp)]       # exact hit
+        partial = [o.outputs[0].token_ids for o in cached.generate(shared, sp)]             # shared 48-token prefix
+        assert first == again == want[:1] and partial == want[1:]
+        pc = cached.engine.stats()["backend"]["prefix_cache"]
+        assert pc.get("hits", 0) >= 1, pc
+    finally:
+        cached.shutdown()
