@@ -266,7 +266,15 @@ class RoutedExperts(nn.Module):
             self.raw[which] = gq.quantize_q8_0(w.reshape(E * R, K)).view(E, R, -1).to(self.device)
             self.types[which] = 8
 
-    def forward(self, x, ids, weights):
+    def forward(self, x, ids, weights, reduce: bool = True):
+        """``reduce=False``: the caller owns the exchange between the expert-parallel ranks (rows that arrived by
+        all-to-all): only this rank's experts run, nothing is summed over ranks."""
+        from ..parallel import ep_alltoall
+        if reduce and pstate.ep_size() > 1 and ep_alltoall.ENABLED:
+            def run(rows, expert_ids):
+                one = torch.ones(rows.shape[0], 1, dtype=torch.float32, device=rows.device)
+                return self.forward(rows, expert_ids.view(-1, 1).to(ids.dtype), one, reduce=False)
+            return ep_alltoall.sharded_moe(x, ids, weights, self.e_local, run)
         T, H = x.shape
         K = ids.shape[1]
         n = T * K
@@ -296,7 +304,8 @@ class RoutedExperts(nn.Module):
             e_hi = self.e_lo + self.e_local
             ids_flat = ids.reshape(-1)
             slot_of = None
-            if n >= _DENSE_EXPERT_ROUTES * self.e_local and self.clamp <= 0 and x.dtype in (torch.bfloat16, torch.float16):
+            if reduce and n >= _DENSE_EXPERT_ROUTES * self.e_local and self.clamp <= 0 \
+                    and x.dtype in (torch.bfloat16, torch.float16):
                 return self._forward_tensor_core(x, ids_flat, weights, a, y, T, K, H)
             same_gu = self.types["gate"] == self.types["up"]
             # int8 activations + dp4a for the 2-bit formats; 16-bit activations for the others
@@ -356,7 +365,7 @@ class RoutedExperts(nn.Module):
                 _lib.check(rc, "fi_gguf_moe_down")
             out = torch.empty(T, H, dtype=x.dtype, device=x.device)
             heap = None
-            if pstate.ep_size() > 1:
+            if pstate.ep_size() > 1 and reduce:
                 from ..parallel import fused_ops
                 heap = fused_ops.ep_heap(x)
             if heap is not None and heap.fits_low_latency(T, H):
@@ -371,7 +380,7 @@ class RoutedExperts(nn.Module):
             rc = lib.fi_moe_combine(_p(y), _p(slot_of), _p(weights), None, _p(out), T, K, H, ops._DT[x.dtype], _stream())
             _lib.check(rc, "fi_moe_combine")
             _count(3)
-        if pstate.ep_size() > 1:
+        if pstate.ep_size() > 1 and reduce:
             from ..parallel import fused_ops
             out = fused_ops.all_reduce_activations(out)
         return out
@@ -482,6 +491,9 @@ class DeepseekMLAForCausalLM(nn.Module):
         arch: ModelArch = mc.arch
         self.arch, self.dtype = arch, mc.dtype
         qc = vllm_config.quant_config
+        from ..parallel import ep_alltoall
+        if ep_alltoall.ENABLED and pstate.ep_size() > 1:
+            self.supports_cuda_graph = False      # the all-to-all split sizes are read on the host every step
         self.embed_tokens = nn.Parameter(torch.empty(arch.vocab_size, arch.hidden_size, dtype=mc.dtype), requires_grad=False)
         self.layers = nn.ModuleList([DeepseekDecoderLayer(arch, i, mc.dtype, qc) for i in range(arch.num_layers)])
         self.norm = RMSNormWeight(arch.hidden_size, arch.rms_eps, mc.dtype)

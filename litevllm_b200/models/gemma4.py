@@ -153,7 +153,13 @@ class Gemma4Experts(nn.Module):
         self.finalize()
         heap = None
         if pstate.ep_size() > 1:
-            from ..parallel import fused_ops
+            from ..parallel import ep_alltoall, fused_ops
+            if ep_alltoall.ENABLED:        # tokens sharded over the ranks, routes travel by all-to-all
+                def run(rows, expert_ids):
+                    one = torch.ones(rows.shape[0], 1, dtype=torch.float32, device=rows.device)
+                    return moe_ops.fused_experts(rows, self.w_gate_up, self.w_down, expert_ids.view(-1, 1).to(ids.dtype), one,
+                                                 self.e_local, self.e_lo, "gelu_tanh")
+                return ep_alltoall.sharded_moe(x, ids, weights, self.e_local, run)
             heap = fused_ops.ep_heap(x)
         out = moe_ops.fused_experts(x, self.w_gate_up, self.w_down, ids, weights, self.e_local, self.e_lo, "gelu_tanh",
                                     ep_heap=heap)
@@ -219,6 +225,9 @@ class Gemma4ForCausalLM(nn.Module):
         arch: ModelArch = mc.arch
         self.arch, self.dtype = arch, mc.dtype
         qc = vllm_config.quant_config
+        from ..parallel import ep_alltoall
+        if ep_alltoall.ENABLED and pstate.ep_size() > 1:
+            self.supports_cuda_graph = False      # the all-to-all split sizes are read on the host every step
         self.embed_tokens = nn.Parameter(torch.empty(arch.vocab_size, arch.hidden_size, dtype=mc.dtype), requires_grad=False)
         self.layers = nn.ModuleList([Gemma4DecoderLayer(arch, i, mc.dtype, qc) for i in range(arch.num_layers)])
         self.norm = RMSNormWeight(arch.hidden_size, arch.rms_eps, mc.dtype)

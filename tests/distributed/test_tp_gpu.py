@@ -211,3 +211,17 @@ def test_ep2_generation_fused_combine(preset):
     want = [o.outputs[0].token_ids for o in
             ref.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))]
     assert sum(int(a[0] == b[0]) for a, b in zip(got[0], want)) >= 2, (got[0], want)
+
+
+def test_ep2_alltoall_path_on_gpus(monkeypatch):
+    """``FI_EP_ALLTOALL=1`` over NCCL: tokens sharded over the ranks inside the MoE blocks, routes exchanged by
+    all-to-all, decode launched eagerly; ranks agree and the first tokens match the fused-combine run."""
+    with tempfile.TemporaryDirectory() as d:
+        spawn(_ep_worker, 2, args=(d, "tiny-deepseek-test"), port=29556)
+        fused = [json.load(open(os.path.join(d, f"ep{r}.json"))) for r in range(2)]
+    monkeypatch.setenv("FI_EP_ALLTOALL", "1")
+    with tempfile.TemporaryDirectory() as d:
+        spawn(_ep_worker, 2, args=(d, "tiny-deepseek-test"), port=29557)
+        a2a = [json.load(open(os.path.join(d, f"ep{r}.json"))) for r in range(2)]
+    assert a2a[0] == a2a[1], "ranks diverged"
+    assert sum(int(a[0] == b[0]) for a, b in zip(a2a[0], fused[0])) >= 2, (a2a[0], fused[0])
