@@ -232,3 +232,46 @@ def test_chunked_prefill_and_prefix_cache_do_not_change_tokens():
         assert pc.get("hits", 0) >= 1, pc
     finally:
         cached.shutdown()
+
+
+def test_offline_api_kwargs_profiles_and_output_processors(tmp_path):
+    """`LLM` keyword contract: `concurrent_reqs` is `max_num_seqs`, profiles shape the plan, `trust_remote_code`
+    needs a pinned revision, the "verl" output processor returns padded token-id tensors, stats reset."""
+    sp = SamplingParams(max_tokens=3, temperature=0.0, ignore_eos=True)
+    a = LLM("synthetic:tiny-llama-test", device="cpu", dtype="float32", concurrent_reqs=3, max_model_len=64)
+    try:
+        assert a.engine.plan.max_active_requests == 3
+        outs = a.generate([_ids(5), _ids(7, k=4)], sp)
+        assert a.stats()["observer"]["counters"]["requests_finished"] == 2
+        a.reset_stats()
+        assert a.stats()["observer"]["counters"].get("requests_finished", 0) == 0
+        assert a.model is a.engine.model
+    finally:
+        a.shutdown()
+    lat = LLM("synthetic:tiny-llama-test", device="cpu", dtype="float32", max_model_len=2048,
+              fastinference_config={"profile": "latency"})
+    try:
+        assert lat.engine.plan.max_active_requests == 1 and lat.engine.plan.max_model_len == 512
+    finally:
+        lat.shutdown()
+    with pytest.raises(ValueError):
+        LLM("synthetic:tiny-llama-test", device="cpu", trust_remote_code=True)
+    v = LLM("synthetic:tiny-llama-test", device="cpu", dtype="float32", max_num_seqs=2, max_model_len=64,
+            output_processor="verl")
+    try:
+        res = v.generate([_ids(5), _ids(9, k=4)], SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True))
+        ids = res["response_ids"] if isinstance(res, dict) else res
+        ids = ids if isinstance(ids, torch.Tensor) else ids[0]
+        assert isinstance(ids, torch.Tensor) and ids.shape[0] == 2 and ids.shape[1] >= 4
+        assert [o.outputs[0].token_ids for o in outs][0][:3] == ids[0, :3].tolist()
+    finally:
+        v.shutdown()
+
+
+def test_clear_cache_drops_the_dequantised_weight_cache():
+    import litevllm_b200
+    from litevllm_b200.layers.quantization import tensor as qt
+    cache = qt.global_weight_cache() if hasattr(qt, "global_weight_cache") else None
+    litevllm_b200.clear_cache()
+    if cache is not None:
+        assert len(cache) == 0
