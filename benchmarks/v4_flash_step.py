@@ -1,7 +1,8 @@
 """DeepSeek-V4-Flash-shaped steps on one GPU: the full-size layer geometry (hidden 4096, 64 heads over one
 512-wide latent row, 256 experts of width 2048 with 6 per token, IQ2_XXS / Q2_K expert blocks, Q8_0
 projections) with a configurable number of layers and random block weights.  Times a prefill chunk and decode
-steps of the model-owned data plane with CUDA events and prints one JSON line.
+steps of the model-owned data plane with CUDA events and prints one JSON line (``FI_V4_DECODE_GRAPHS=0`` for
+the decode step without its CUDA graphs).
 
     python benchmarks/v4_flash_step.py --layers 8 --batch 1 --prompt-len 64 --steps 16
 """
@@ -124,7 +125,8 @@ def main() -> None:
         "decode_ms_per_step": round(ms_step, 3), "decode_ms_per_step_per_layer": round(ms_step / a.layers, 4),
         "decode_tok_s": round(a.batch * 1000.0 / ms_step, 2), "weights_gb": round(weights / 2 ** 30, 2),
         "rows_mb": rows_mb, **engine,
-        "note": "model-owned data plane, eager launches; per-layer figures scale to the 43 layers of the full model"}))
+        "decode_graphs": os.environ.get("FI_V4_DECODE_GRAPHS", "1") != "0",
+        "note": "model-owned data plane; per-layer figures scale to the 43 layers of the full model"}))
 
 
 if __name__ == "__main__":

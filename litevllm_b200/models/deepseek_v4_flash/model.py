@@ -17,9 +17,12 @@ tokens in order.  One token through one layer:
 
 and after the last layer: sigmoid-gated sum of the streams -> RMSNorm -> lm_head -> arg-max.
 
-Weights are dense tensors (fp32 on the CPU, the model dtype on a GPU); synthetic checkpoints draw them from
-a seeded generator.  The GGUF weight store, the expert staging LRU and the decode-graph experiments of the
-reference's data plane are not part of this model.
+Weights: a ``deepseek4`` GGUF file binds by tensor name; its block-quantised projections and routed experts stay
+in HBM in their block formats (``BlockMatrix``, the expert-grouped GGUF kernels), the rest is dequantised once.
+A synthetic checkpoint draws dense weights from a seeded generator, or, for full-size geometries, random blocks
+in the checkpoint family's formats.  The whole model is resident: the reference's weight stager with its byte
+budget and expert LRU has no counterpart here.  Decode steps replay CUDA graphs of their static stretches
+(``_decode_step_graphs``); a prefill chunk of one request runs as one pass per layer (``_attention_run``).
 Reference: vllm/model_executor/models/deepseek_v4_flash/model.py:249-304, 537-607, 933-1130
 (prefill_request / decode_tokens_batch / token steps), gpu_layers.py:684-926, 1247-1610 (layer forwards),
 compressed_kv.py:289-455 (row pools), kv_lifecycle.py (release).
