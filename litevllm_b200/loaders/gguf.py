@@ -287,6 +287,109 @@ def gguf_to_hf_name(name: str) -> str | None:
     return None
 
 
+# ----------------------------------------------------------------------------- Qwen3.5 (gated delta-net hybrid)
+# GGUF files of this family differ from the HF checkpoint in three ways (the exporter's conventions): value heads
+# of the linear-attention tensors are stored tiled ([per-key-head copy, key head, dim]) instead of grouped
+# ([key head, copy, dim]); every RMSNorm gain except the gated linear-attention norm has 1 added; the depthwise
+# convolution is [kernel, channels].  ``ssm_a`` holds -exp(A_log).
+# Reference: vllm/model_executor/model_loader/__init__.py:74-215 (the same fix-ups, per tensor at load time).
+_QWEN35_LAYER_MAP = {
+    "attn_norm": "input_layernorm", "post_attention_norm": "post_attention_layernorm", "ffn_norm": "post_attention_layernorm",
+    "attn_q": "self_attn.q_proj", "attn_k": "self_attn.k_proj", "attn_v": "self_attn.v_proj",
+    "attn_output": "self_attn.o_proj", "attn_q_norm": "self_attn.q_norm", "attn_k_norm": "self_attn.k_norm",
+    "ffn_gate": "mlp.gate_proj", "ffn_up": "mlp.up_proj", "ffn_down": "mlp.down_proj",
+    "attn_qkv": "linear_attn.in_proj_qkv", "attn_gate": "linear_attn.in_proj_z", "ssm_alpha": "linear_attn.in_proj_a",
+    "ssm_beta": "linear_attn.in_proj_b", "ssm_out": "linear_attn.out_proj", "ssm_conv1d": "linear_attn.conv1d",
+    "ssm_norm": "linear_attn.norm", "ffn_gate_inp": "mlp.gate", "ffn_gate_shexp": "mlp.shared_expert.gate_proj",
+    "ffn_up_shexp": "mlp.shared_expert.up_proj", "ffn_down_shexp": "mlp.shared_expert.down_proj",
+    "ffn_gate_inp_shexp": "mlp.shared_expert_gate",
+}
+_QWEN35_EXPERTS = {"ffn_gate_exps": "gate_proj", "ffn_up_exps": "up_proj", "ffn_down_exps": "down_proj"}
+
+
+def tiled_to_grouped(t: torch.Tensor, dim: int, num_k: int, per_k: int, head_dim: int) -> torch.Tensor:
+    """Value heads along ``dim`` from the file's tiled order to the grouped order of the HF checkpoint."""
+    shape = list(t.shape)
+    dim %= len(shape)
+    u = t.reshape(*shape[:dim], per_k, num_k, head_dim, *shape[dim + 1:])
+    return u.transpose(dim, dim + 1).contiguous().reshape(shape)
+
+
+def grouped_to_tiled(t: torch.Tensor, dim: int, num_k: int, per_k: int, head_dim: int) -> torch.Tensor:
+    """Inverse of :func:`tiled_to_grouped` (what an exporter applies)."""
+    shape = list(t.shape)
+    dim %= len(shape)
+    u = t.reshape(*shape[:dim], num_k, per_k, head_dim, *shape[dim + 1:])
+    return u.transpose(dim, dim + 1).contiguous().reshape(shape)
+
+
+def qwen35_fixup(kind: str, suffix: str, t: torch.Tensor, extra: dict) -> torch.Tensor:
+    """One dense tensor of a Qwen3.5 GGUF file -> the HF layout the model's loader expects."""
+    nk, nv = int(extra.get("linear_num_key_heads", 0) or 0), int(extra.get("linear_num_value_heads", 0) or 0)
+    dk, dv = int(extra.get("linear_key_head_dim", 0) or 0), int(extra.get("linear_value_head_dim", 0) or 0)
+    tiled = nk > 0 and nv > nk and nv % nk == 0 and dk > 0 and dv > 0
+    per = nv // nk if tiled else 1
+    if kind == "ssm_conv1d" and suffix == "weight":
+        if t.dim() == 2 and t.shape[0] < t.shape[1]:
+            t = t.t()                                           # [kernel, channels] -> [channels, kernel]
+        t = t.reshape(t.shape[0], -1)
+        if tiled and t.shape[0] == 2 * nk * dk + nv * dv:
+            qk = 2 * nk * dk
+            t = torch.cat([t[:qk], tiled_to_grouped(t[qk:], 0, nk, per, dv)])
+        return t.unsqueeze(1).contiguous()                      # [channels, 1, kernel]
+    if kind.endswith("norm") and suffix == "weight" and t.dim() == 1 and kind != "ssm_norm":
+        return t.float() - 1.0
+    if not tiled:
+        return t
+    if kind == "attn_qkv" and suffix == "weight" and t.shape[0] == 2 * nk * dk + nv * dv:
+        qk = 2 * nk * dk
+        return torch.cat([t[:qk], tiled_to_grouped(t[qk:], 0, nk, per, dv)])
+    if kind == "attn_gate" and suffix == "weight" and t.shape[0] == nv * dv:
+        return tiled_to_grouped(t, 0, nk, per, dv)
+    if kind == "ssm_out" and suffix == "weight" and t.shape[-1] == nv * dv:
+        return tiled_to_grouped(t, 1, nk, per, dv)
+    if kind in ("ssm_alpha", "ssm_beta") and suffix == "weight" and t.shape[0] == nv:
+        return tiled_to_grouped(t, 0, nk, per, 1)
+    if kind in ("ssm_a", "ssm_dt") and t.dim() == 1 and t.shape[0] == nv:
+        return tiled_to_grouped(t.unsqueeze(-1), 0, nk, per, 1).squeeze(-1)
+    return t
+
+
+def _iter_qwen35(g: "GGUFFile", arch):
+    from ..ops import gguf_quant as gq
+
+    def dense(name):
+        t = g.load(name)
+        if isinstance(t, GGUFTensor):
+            t = gq.dequantize(t.raw.reshape(-1, t.raw.shape[-1]), t.ggml_type, t.K).reshape(t.shape)
+        return t
+
+    extra = getattr(arch, "extra", {}) or {}
+    for name in g.tensors:
+        hf = {"token_embd.weight": "model.embed_tokens.weight", "output_norm.weight": "model.norm.weight",
+              "output.weight": "lm_head.weight"}.get(name)
+        if hf is not None:
+            t = dense(name)
+            yield hf, (t.float() - 1.0 if name == "output_norm.weight" else t)
+            continue
+        parts = name.split(".")
+        if parts[0] != "blk" or len(parts) < 3:
+            continue
+        layer, kind, suffix = parts[1], parts[2], ".".join(parts[3:])
+        prefix = f"model.layers.{layer}."
+        if kind == "ssm_a":                                      # the file stores -exp(A_log)
+            t = qwen35_fixup(kind, suffix, dense(name).float(), extra)
+            yield prefix + "linear_attn.A_log", (torch.log(-t) if bool((t < 0).all()) else t)
+        elif kind == "ssm_dt":
+            yield prefix + "linear_attn.dt_bias", qwen35_fixup(kind, suffix, dense(name).float(), extra)
+        elif kind in _QWEN35_EXPERTS:                            # [E, rows, cols] -> one tensor per expert
+            t = dense(name)
+            for e in range(t.shape[0]):
+                yield prefix + f"mlp.experts.{e}.{_QWEN35_EXPERTS[kind]}.weight", t[e]
+        elif kind in _QWEN35_LAYER_MAP:
+            yield prefix + _QWEN35_LAYER_MAP[kind] + "." + suffix, qwen35_fixup(kind, suffix, dense(name), extra)
+
+
 def iter_gguf_weights(path: str | Path, arch=None):
     p = Path(path)
     if p.is_dir():
@@ -295,6 +398,9 @@ def iter_gguf_weights(path: str | Path, arch=None):
     if g.arch() == "deepseek4":          # the model binds the checkpoint's own tensor names
         for name in g.tensors:
             yield name, g.load(name)
+        return
+    if getattr(arch, "family", "") == "qwen3_5":
+        yield from _iter_qwen35(g, arch)
         return
     for name in g.tensors:
         hf = gguf_to_hf_name(name)

@@ -104,3 +104,95 @@ def test_step_kernels_match_torch_gpu():
     live = slots.cpu() >= 0
     assert float((y.cpu()[live] - yw[live]).abs().max()) < 2e-2
     assert torch.equal(cpool.cpu(), rpool)
+
+
+@pytest.mark.parametrize("preset", ["tiny-qwen35-test", "tiny-qwen35-moe-test"])
+def test_gguf_file_with_the_exporters_conventions_round_trips(tmp_path, preset):
+    """A Qwen3.5 GGUF file stores value heads tiled, RMSNorm gains plus one, the depthwise convolution as
+    [kernel, channels] and -exp(A_log); a directory with `config.json` and such a file loads to the same model as
+    the HF-layout tensors it was exported from."""
+    import json
+    import re
+    import torch
+    from litevllm_b200 import LLM, SamplingParams
+    from litevllm_b200.loaders import synth
+    from litevllm_b200.loaders.gguf import _QWEN35_LAYER_MAP, grouped_to_tiled, tiled_to_grouped, write_gguf
+    from litevllm_b200.models.presets import PRESETS
+
+    x = torch.arange(2 * 3 * 4 * 5, dtype=torch.float32).reshape(2, 3 * 4, 5)
+    assert torch.equal(tiled_to_grouped(grouped_to_tiled(x, 1, 3, 4, 1), 1, 3, 4, 1), x)
+    assert not torch.equal(grouped_to_tiled(x, 1, 3, 4, 1), x)
+
+    cfg = PRESETS[preset]
+    src = LLM(f"synthetic:{preset}", device="cpu", dtype="float32", max_num_seqs=2, max_model_len=96)
+    arch = src.engine.arch
+    nk, nv, dk, dv = (cfg[k] for k in ("linear_num_key_heads", "linear_num_value_heads", "linear_key_head_dim",
+                                       "linear_value_head_dim"))
+    per, qk = nv // nk, 2 * nk * dk
+    back = {v: k for k, v in _QWEN35_LAYER_MAP.items() if k != "ffn_norm"}
+    tensors = {}
+    experts: dict = {}
+    for name, t in synth.iter_qwen35_weights(arch, 0, torch.float32, "cpu"):
+        t = t.float()
+        em = re.match(r"model\.layers\.(\d+)\.mlp\.experts\.(\d+)\.(\w+)\.weight", name)
+        if em:                                   # the file holds one [experts, rows, cols] tensor per projection
+            experts.setdefault((em.group(1), em.group(3)), {})[int(em.group(2))] = t
+            continue
+        if name == "model.embed_tokens.weight":
+            tensors["token_embd.weight"] = t
+        elif name == "model.norm.weight":
+            tensors["output_norm.weight"] = t + 1.0
+        elif name == "lm_head.weight":
+            tensors["output.weight"] = t
+        else:
+            layer, rest = re.match(r"model\.layers\.(\d+)\.(.+)", name).groups()
+            if rest == "linear_attn.A_log":
+                tensors[f"blk.{layer}.ssm_a"] = grouped_to_tiled((-torch.exp(t)).unsqueeze(-1), 0, nk, per, 1).squeeze(-1)
+            elif rest == "linear_attn.dt_bias":
+                tensors[f"blk.{layer}.ssm_dt.bias"] = grouped_to_tiled(t.unsqueeze(-1), 0, nk, per, 1).squeeze(-1)
+            else:
+                mod, suffix = rest.rsplit(".", 1)
+                kind = back[mod]
+                if kind == "ssm_conv1d":
+                    c = t.reshape(t.shape[0], -1)
+                    c = torch.cat([c[:qk], grouped_to_tiled(c[qk:], 0, nk, per, dv)])
+                    t = c.t().contiguous()                                   # [kernel, channels]
+                elif kind.endswith("norm") and kind != "ssm_norm":
+                    t = t + 1.0
+                elif kind == "attn_qkv":
+                    t = torch.cat([t[:qk], grouped_to_tiled(t[qk:], 0, nk, per, dv)])
+                elif kind == "attn_gate":
+                    t = grouped_to_tiled(t, 0, nk, per, dv)
+                elif kind == "ssm_out":
+                    t = grouped_to_tiled(t, 1, nk, per, dv)
+                elif kind in ("ssm_alpha", "ssm_beta"):
+                    t = grouped_to_tiled(t, 0, nk, per, 1)
+                tensors[f"blk.{layer}.{kind}.{suffix}"] = t.contiguous()
+    for (layer, which), per_expert in experts.items():
+        kind = {"gate_proj": "ffn_gate_exps", "up_proj": "ffn_up_exps", "down_proj": "ffn_down_exps"}[which]
+        tensors[f"blk.{layer}.{kind}.weight"] = torch.stack([per_expert[e] for e in sorted(per_expert)])
+    # the synthetic stream carries no norm gains: give the source model random ones and export them shifted
+    gen = torch.Generator().manual_seed(9)
+    for pname, p in src.engine.model.named_parameters():
+        if not pname.endswith("norm.weight"):
+            continue
+        p.data.copy_(torch.randn(p.shape, generator=gen) * 0.1)
+        if pname == "norm.weight":
+            tensors["output_norm.weight"] = p.detach().float() + 1.0
+            continue
+        layer, mod = re.match(r"layers\.(\d+)\.(.+)\.weight", pname).groups()
+        kind = back[mod]
+        tensors[f"blk.{layer}.{kind}.weight"] = p.detach().float() + (0.0 if kind == "ssm_norm" else 1.0)
+    d = tmp_path / "qwen35-gguf"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(cfg))
+    write_gguf(d / "model.gguf", {"general.architecture": "qwen35", "qwen35.block_count": cfg["num_hidden_layers"],
+                                  "qwen35.embedding_length": cfg["hidden_size"]}, tensors)
+    loaded = LLM(str(d), device="cpu", dtype="float32", max_num_seqs=2, max_model_len=96)
+    a, b = dict(src.engine.model.named_parameters()), dict(loaded.engine.model.named_parameters())
+    assert a.keys() == b.keys()
+    for k in a:
+        torch.testing.assert_close(b[k].float(), a[k].float(), rtol=1e-5, atol=1e-5, msg=lambda m, k=k: f"{k}: {m}")
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    prompt = [{"prompt_token_ids": [(5 * i + 3) % 400 + 2 for i in range(20)]}]
+    assert loaded.generate(prompt, sp)[0].outputs[0].token_ids == src.generate(prompt, sp)[0].outputs[0].token_ids
