@@ -65,8 +65,12 @@ class DeepSeekV4FlashAdapter(ModelAdapter):
         stock_release = engine._on_release
 
         def release(st) -> None:
-            model.release_request(st.request_id)
+            if model.release_request(st.request_id):
+                hook = getattr(engine.observer, "on_model_event", None)
+                if callable(hook):
+                    hook("rows_released", request_id=st.request_id, **model.kv_stats())
             stock_release(st)
 
         engine._on_release = release
-        return CustomRuntimeComponents(V4FlashPrefillExecutor(model), V4FlashDecodeExecutor(model), None)
+        return CustomRuntimeComponents(V4FlashPrefillExecutor(model, engine.observer),
+                                       V4FlashDecodeExecutor(model, engine.observer), None)

@@ -20,6 +20,7 @@ class RuntimeObserver:
     def on_background_error(self, exc: BaseException) -> None: ...
     def on_model_surface(self, surface: dict) -> None: ...
     def on_rank_event(self, kind: str, rank: int) -> None: ...
+    def on_model_event(self, event: str, **payload) -> None: ...       # events of a model-owned data plane
     def stats(self) -> dict: return {}
     def reset(self) -> None: ...
 
@@ -39,6 +40,8 @@ class InMemoryRuntimeObserver(RuntimeObserver):
         self.finish_reasons: Counter = Counter()
         self.last_error: str | None = None
         self.model_surface: dict = {}
+        self.model_events: Counter = Counter()
+        self.last_model_event: dict = {}
         self.started = time.monotonic()
 
     def on_request_added(self, request_id, prompt_len):
@@ -100,6 +103,10 @@ class InMemoryRuntimeObserver(RuntimeObserver):
         s = sorted(values)
         return s[min(len(s) - 1, int(q * len(s)))]
 
+    def on_model_event(self, event, **payload):
+        self.model_events[event] += 1
+        self.last_model_event[event] = payload
+
     def stats(self) -> dict:
         dec = list(self.decode_steps)
         dec_time = sum(s for _, s in dec)
@@ -110,5 +117,6 @@ class InMemoryRuntimeObserver(RuntimeObserver):
             "queue_wait_p50_s": self._pct(list(self.queue_wait), 0.5),
             "decode_tokens_per_s": (sum(n for n, _ in dec) / dec_time) if dec_time > 0 else None,
             "last_error": self.last_error, "model_surface": self.model_surface,
+            "model_events": {"counts": dict(self.model_events), "last": dict(self.last_model_event)},
             "uptime_s": time.monotonic() - self.started,
         }

@@ -489,6 +489,13 @@ class DeepseekV4FlashForCausalLM(nn.Module):
     def request_bytes(self) -> int:
         return sum(r.bytes() for r in self.requests.values())
 
+    def kv_stats(self) -> dict:
+        """Gauges of the per-request rows (reported with the model events and the engine statistics)."""
+        self._active_high_water = max(getattr(self, "_active_high_water", 0), len(self.requests))
+        return {"active_requests": len(self.requests), "active_requests_high_water": self._active_high_water,
+                "row_bytes": self.request_bytes(),
+                "compressed_rows": sum(lr.n_comp for r in self.requests.values() for lr in r.layers)}
+
     # ------------------------------------------------------------------ a group of tokens, layer by layer
     def _f32(self, owner, attr: str) -> torch.Tensor:
         """fp32 copy of a small parameter (norm gains, hyper-connection tables, sinks, position biases), made once."""

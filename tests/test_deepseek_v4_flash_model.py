@@ -407,3 +407,14 @@ def test_deepseek4_files_are_validated(tmp_path):
                    "deepseek4.attention.head_count": 4}, {"token_embd.weight": torch.zeros(8, 256)})
     with pytest.raises(ValueError, match="attn_q_a"):
         hf_config_from_gguf(f)
+
+
+def test_model_events_reach_the_observer(llm):
+    eng = llm.engine
+    eng.observer.reset()
+    _tokens(llm, PROMPTS, 4)
+    ev = eng.stats()["observer"]["model_events"]
+    assert ev["counts"]["rows_allocated"] == 2 and ev["counts"]["rows_released"] == 2
+    assert ev["counts"]["decode_batch"] >= 3 and ev["last"]["decode_batch"]["batch_size"] >= 1
+    assert ev["last"]["rows_released"]["active_requests"] == 0
+    assert ev["last"]["rows_allocated"]["active_requests_high_water"] >= 1
