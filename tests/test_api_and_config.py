@@ -201,3 +201,24 @@ def test_every_kernel_switch_read_by_the_package_is_registered():
     listed = kernel_switches()
     assert used <= set(listed), sorted(used - set(listed))
     assert all(listed[n] for n in listed)
+
+
+def test_hot_kernels_are_written_for_the_blackwell_tensor_path():
+    """Structure check on the kernel sources: the GEMM-shaped kernels issue `tcgen05` MMAs through the shared PTX
+    helpers, feed them with TMA tensor copies and read accumulators from tensor memory; the Hopper-only
+    instruction family appears in no kernel."""
+    import pathlib
+    import re
+    csrc = pathlib.Path(__file__).resolve().parent.parent / "csrc"
+    ptx = (csrc / "common" / "ptx.cuh").read_text()
+    for needle in ("tcgen05.mma", "tcgen05.alloc", "tcgen05.ld", "tcgen05.commit", "cp.async.bulk.tensor", "mbarrier"):
+        assert needle in ptx, needle
+    helpers = {"mma": r"umma_f16\w*\(", "tma": r"tma_load_\dd\(", "tmem": r"tmem_ld\w*\("}
+    for rel in ("gemm/dense_gemm.cu", "gemm/dense_gemm_persistent.cu", "gemm/awq_gemm.cu", "attn/prefill_tc.cu"):
+        text = (csrc / rel).read_text() + (csrc / "gemm" / "epilogue.cuh").read_text()
+        for what, pat in helpers.items():
+            assert re.search(pat, text), f"{rel}: no {what} helper call"
+    hopper_only = "wg" + "mma"
+    for path in csrc.rglob("*.cu*"):
+        code = "\n".join(l for l in path.read_text().splitlines() if not l.lstrip().startswith("//"))
+        assert hopper_only not in code, path
