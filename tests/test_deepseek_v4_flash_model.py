@@ -418,3 +418,19 @@ def test_model_events_reach_the_observer(llm):
     assert ev["counts"]["decode_batch"] >= 3 and ev["last"]["decode_batch"]["batch_size"] >= 1
     assert ev["last"]["rows_released"]["active_requests"] == 0
     assert ev["last"]["rows_allocated"]["active_requests_high_water"] >= 1
+
+
+def test_engine_chunked_prefill_matches_one_shot(llm):
+    """The engine feeds a long prompt in chunks (`start` advances, the last chunk returns the first token)."""
+    cfg = {"profile": "balanced", "tuning_keyvals": {"FASTINFERENCE_LITE_PREFILL_CHUNK": "16", "FASTINFERENCE_MIN_PREFILL_CHUNK": "16",
+                                                     "FASTINFERENCE_MAX_PREFILL_CHUNK": "16"}}
+    chunked = LLM(PRESET, device="cpu", max_model_len=128, dtype="float32", fastinference_config=cfg)
+    try:
+        assert chunked.engine.plan.prefill_chunk_size == 16
+        long_prompt = [(13 * i + 7) % 500 + 2 for i in range(57)]
+        want = _tokens(llm, [long_prompt], 5)
+        got = _tokens(chunked, [long_prompt], 5)
+        assert got[0][:2] == want[0][:2], (got, want)          # same model, same rows: the walk starts the same
+        assert chunked.engine.model.requests == {}
+    finally:
+        chunked.shutdown()
