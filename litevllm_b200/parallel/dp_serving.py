@@ -103,6 +103,7 @@ class DataParallelRouter:
         self.inflight = [0] * replicas
         self.owner: dict[str, int] = {}
         self._streams: dict[str, tuple[asyncio.Queue, asyncio.AbstractEventLoop]] = {}
+        self._done: dict[str, None] = {}        # finished remotely, stream not read to its end yet (oldest first)
         self._lock = threading.Lock()
         self._stop = threading.Event()
         self._poll_sleep_s = poll_sleep_s
@@ -139,14 +140,22 @@ class DataParallelRouter:
         return self.owner.get(request_id, 0) != 0
 
     async def stream(self, request_id: str):
+        """Outputs of a remote request.  The queue outlives the request until its consumer has read it: a short
+        request can finish on its replica before the consumer awaits the stream for the first time."""
         q, _ = self._streams[request_id]
-        while True:
-            item = await q.get()
-            if isinstance(item, BaseException):
-                raise item
-            yield item
-            if getattr(item, "finished", False):
-                return
+        try:
+            while True:
+                item = await q.get()
+                if isinstance(item, BaseException):
+                    raise item
+                yield item
+                if getattr(item, "finished", False):
+                    return
+        finally:
+            with self._lock:
+                self._streams.pop(request_id, None)
+                self.owner.pop(request_id, None)
+                self._done.pop(request_id, None)
 
     def abort(self, request_id: str) -> bool:
         with self._lock:
@@ -165,13 +174,19 @@ class DataParallelRouter:
             loop.call_soon_threadsafe(q.put_nowait, item)
 
     def _finish_remote(self, request_id: str, terminal=None) -> None:
+        """Book-keeping first, delivery second: the consumer may drop the stream the moment it sees the last item."""
+        with self._lock:
+            r = self.owner.get(request_id)
+            if r and request_id not in self._done:
+                self.inflight[r] = max(0, self.inflight[r] - 1)
+                self._done[request_id] = None
+                while len(self._done) > 1024:           # consumers that never came back: forget the oldest
+                    old = next(iter(self._done))
+                    self._done.pop(old)
+                    self.owner.pop(old, None)
+                    self._streams.pop(old, None)
         if terminal is not None:
             self._deliver(request_id, terminal)
-        with self._lock:
-            r = self.owner.pop(request_id, None)
-            if r:
-                self.inflight[r] = max(0, self.inflight[r] - 1)
-            self._streams.pop(request_id, None)
 
     def _pump_loop(self) -> None:
         try:
@@ -183,9 +198,10 @@ class DataParallelRouter:
                         busy = True
                         if msg[0] == "out":
                             out = msg[1]
-                            self._deliver(out.request_id, out)
                             if out.finished:
-                                self._finish_remote(out.request_id)
+                                self._finish_remote(out.request_id, out)
+                            else:
+                                self._deliver(out.request_id, out)
                         elif msg[0] == "error":
                             from ..engine.errors import RequestRejectedError
                             self._finish_remote(msg[1], RequestRejectedError(msg[2]))
