@@ -45,7 +45,7 @@ class RuntimeConfig:
     prefill_sla_ttft_ms: float
     default_min_new_tokens: int = 0
     queue_timeout_s: float = 30.0
-    async_driver_min_step_interval_s: float = 0.001
+    async_driver_min_step_interval_s: float = 0.0002
     memory_audit_topn: int = 20
     k_scale: float = 1.0
     v_scale: float = 1.0
