@@ -3,8 +3,9 @@
 The reference is single-GPU (vllm/engine/lite_engine.py:146 pins ``cuda:0``); tensor and expert
 parallelism are additions of this engine.  One process drives one GPU; ``world_size`` is
 ``tensor_parallel_size`` for dense models and ``max(tp, ep)`` for MoE models (experts are sharded
-over the same ranks that hold the attention shards).  ``data_parallel_size`` > 1 instead runs that many
-whole single-GPU engines and shards the requests (parallel/data_parallel.py).
+over the same ranks that hold the attention shards).  ``data_parallel_size`` > 1 runs that many whole engines
+(each a single GPU, or a tensor / expert-parallel group of consecutive ranks) and shards the requests over them
+(parallel/data_parallel.py).
 """
 from __future__ import annotations
 
@@ -33,9 +34,8 @@ class ParallelConfig:
 
     @classmethod
     def from_env(cls, tp: int = 1, ep: int = 1, comm_backend: str = "fused", dp: int = 1) -> "ParallelConfig":
-        if dp > 1 and max(tp, ep) > 1:
-            raise NotImplementedError("data_parallel_size > 1 runs replicas of single-GPU engines; "
-                                      "replicas of tensor/expert-parallel groups are separate torchrun jobs")
+        # dp > 1 with tp / ep > 1: replicas of tensor / expert-parallel groups; WORLD_SIZE = dp * max(tp, ep), ranks
+        # [k * group, (k + 1) * group) form replica k (offline generation; the servers route to single-GPU replicas)
         return cls(tensor_parallel_size=tp, expert_parallel_size=ep, data_parallel_size=dp, comm_backend=comm_backend,
                    rank=int(os.environ.get("RANK", "0")),
                    local_rank=int(os.environ.get("LOCAL_RANK", "0")),

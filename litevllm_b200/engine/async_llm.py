@@ -28,6 +28,9 @@ class AsyncLLM(EngineClient):
         self._dp_link = None          # this replica's mailbox (ranks other than 0)
         self._dp = None
         if engine is None and vllm_config.parallel_config.data_parallel_size > 1:
+            if vllm_config.parallel_config.is_distributed:
+                raise NotImplementedError("the server routes requests to single-GPU replicas; replicas that are tensor / "
+                                          "expert-parallel groups serve offline generation (LLM) only")
             # replicas: every rank a whole engine on its own GPU; the process group only provides the store
             import torch
             import torch.distributed as dist

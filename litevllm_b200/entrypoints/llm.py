@@ -31,7 +31,7 @@ class LLM:
         if pc.data_parallel_size > 1:
             # replicas: this process owns one whole engine on its own GPU and a share of every call's prompts
             from ..parallel.data_parallel import DataParallelGroup
-            self._dp = DataParallelGroup(pc.data_parallel_size)
+            self._dp = DataParallelGroup(pc.data_parallel_size, group_size=pc.world_size)
             if torch.cuda.is_available() and self.vllm_config.device in ("auto", "cuda"):
                 self.vllm_config.device = f"cuda:{self._dp.local_rank}"
         if self.vllm_config.parallel_config.is_distributed:

@@ -38,7 +38,7 @@ class DistributedHandle:
         rc = engine.rc
         store = dist.distributed_c10d._get_default_store()
         self.heartbeat = Heartbeat(store, self.state.rank, self.state.world_size, rc.heartbeat_interval_s,
-                                   rc.heartbeat_timeout_s)
+                                   rc.heartbeat_timeout_s, prefix=f"fi/hb/{self.state.replica}")
         self.heartbeat.start()
         last = [time.monotonic()]
 
@@ -83,8 +83,15 @@ class DistributedHandle:
 
 def init_distributed_engine(vllm_config) -> DistributedHandle:
     pc = vllm_config.parallel_config
-    st = pstate.init_parallel(pc.tensor_parallel_size, pc.expert_parallel_size, pc.comm_backend)
-    if st.world_size > 1 and torch.cuda.is_available() and pc.comm_backend == "fused":
+    st = pstate.init_parallel(pc.tensor_parallel_size, pc.expert_parallel_size, pc.comm_backend,
+                              replicas=max(1, pc.data_parallel_size))
+    if st.replicas > 1 and st.comm_backend == "fused":
+        # the symmetric heap exchanges its handles over the whole job's group: groups of a replicated job use the
+        # library collectives
+        logger.info("rank %d: %d replicas of %d-rank groups: library collectives inside each group",
+                    st.global_rank, st.replicas, st.world_size)
+        st.comm_backend = "nccl"
+    if st.world_size > 1 and torch.cuda.is_available() and st.comm_backend == "fused":
         from .symm import SymmetricHeap
         dev = torch.device("cuda", st.local_rank)
         try:

@@ -28,6 +28,9 @@ class ParallelState:
     sequence_parallel_ok: bool = True   # cleared when the fused reduce-scatter / all-gather start-up check fails
     argmax_ok: bool = True              # cleared when the vocabulary-parallel arg-max start-up check fails
     self_test: dict | None = None       # verdicts of the start-up checks of the fused collectives, per form
+    replica: int = 0                    # which tensor / expert-parallel group of the job this rank belongs to
+    replicas: int = 1
+    global_rank: int = 0                # rank in the whole job (``rank`` is the rank inside the group)
 
     @property
     def tp_rank(self) -> int:
@@ -62,18 +65,22 @@ def ep_rank() -> int:
 
 
 def init_parallel(tp: int = 1, ep: int = 1, comm_backend: str = "fused", backend: str | None = None,
-                  timeout_s: float = 600.0) -> ParallelState:
-    """Join the job described by RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT (torchrun style)."""
+                  timeout_s: float = 600.0, replicas: int = 1) -> ParallelState:
+    """Join the job described by RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT (torchrun style).  With
+    ``replicas`` > 1 the job holds that many tensor / expert-parallel groups of consecutive ranks; the state then
+    describes this rank's own group (rank and size inside it) and every collective of this module runs on it."""
     global _STATE
-    world = max(tp, ep)
-    if world == 1:
+    group_size = max(tp, ep)
+    world = group_size * max(1, replicas)
+    if group_size == 1:
         _STATE = ParallelState(comm_backend=comm_backend)
         return _STATE
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
     env_world = int(os.environ.get("WORLD_SIZE", str(world)))
     if env_world != world:
-        raise RuntimeError(f"WORLD_SIZE={env_world} does not match tp={tp} / ep={ep}")
+        raise RuntimeError(f"WORLD_SIZE={env_world} does not match tp={tp} / ep={ep}"
+                           + (f" x {replicas} replicas" if replicas > 1 else ""))
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29500")
     use_cuda = torch.cuda.is_available()
@@ -87,8 +94,18 @@ def init_parallel(tp: int = 1, ep: int = 1, comm_backend: str = "fused", backend
             kwargs["device_id"] = torch.device("cuda", local_rank)
         dist.init_process_group(backend=backend, rank=rank, world_size=world,
                                 timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
-    _STATE = ParallelState(rank=rank, world_size=world, tp_size=tp, ep_size=ep, local_rank=local_rank,
-                           comm_backend=comm_backend, group=dist.group.WORLD)
+    group, replica = dist.group.WORLD, 0
+    if replicas > 1:
+        replica = rank // group_size
+        # every rank creates every group, in the same order (group creation is a collective of the whole job)
+        for k in range(replicas):
+            g = dist.new_group(list(range(k * group_size, (k + 1) * group_size)), backend=backend,
+                               timeout=datetime.timedelta(seconds=timeout_s))
+            if k == replica:
+                group = g
+    _STATE = ParallelState(rank=rank % group_size, world_size=group_size, tp_size=tp, ep_size=ep, local_rank=local_rank,
+                           comm_backend=comm_backend, group=group)
+    _STATE.replica, _STATE.replicas, _STATE.global_rank = replica, max(1, replicas), rank
     return _STATE
 
 
@@ -148,7 +165,8 @@ def broadcast_object(obj, src: int = 0):
     if _STATE.world_size == 1:
         return obj
     box = [obj]
-    dist.broadcast_object_list(box, src=src, group=_STATE.group)
+    # ``src`` names a rank of this group; the library call wants the rank in the whole job
+    dist.broadcast_object_list(box, src=_STATE.global_rank - _STATE.rank + src, group=_STATE.group)
     return box[0]
 
 
