@@ -46,7 +46,8 @@ def _export(preset, directory, shards=1, prefix="", extra=None):
 
 
 @pytest.mark.parametrize("preset,shards", [("tiny-llama-test", 1), ("tiny-llama-awq-test", 3), ("tiny-llama-ct-test", 2),
-                                           ("tiny-qwen3-test", 2)])
+                                           ("tiny-qwen3-test", 2), ("tiny-gemma4-moe-test", 2), ("tiny-qwen35-test", 1),
+                                           ("tiny-qwen35-moe-test", 2)])
 def test_safetensors_directory_loads_to_the_same_model(tmp_path, preset, shards):
     d = tmp_path / "ckpt"
     want = _export(preset, d, shards=shards)
