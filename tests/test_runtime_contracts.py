@@ -275,3 +275,51 @@ def test_clear_cache_drops_the_dequantised_weight_cache():
     litevllm_b200.clear_cache()
     if cache is not None:
         assert len(cache) == 0
+
+
+def test_http_structured_outputs_choice_errors_and_limits():
+    """OpenAI surface: a `choice` constraint yields one of the options, malformed structured-output requests are
+    400, an oversized body is 413, a full queue is 429, `max_completion_tokens` is honoured."""
+    import json
+    from fastapi.testclient import TestClient
+    from litevllm_b200.entrypoints.openai import api_server as srv
+    client = TestClient(srv.app)
+    saved = (srv.engine, srv.served_model, srv.debug_endpoints_enabled)
+    try:
+        srv.engine = srv.build_engine("synthetic:tiny-llama-test", dtype="float32", device="cpu", max_num_seqs=2,
+                                      max_model_len=128)
+        srv.served_model, srv.debug_endpoints_enabled = "tiny", True
+        body = {"model": "tiny", "messages": [{"role": "user", "content": "pick"}], "temperature": 0, "max_tokens": 8}
+        r = client.post("/v1/chat/completions", json=dict(body, structured_outputs={"choice": ["aa", "bb", "cab"]}))
+        # the stand-in tokenizer of synthetic models writes token ids; its ids are character codes
+        picked = "".join(chr(int(t)) for t in r.json()["choices"][0]["message"]["content"].split())
+        assert r.status_code == 200 and picked in ("aa", "bb", "cab"), r.text
+        assert client.post("/v1/chat/completions", json=dict(body, structured_outputs={"nonsense": 1})).status_code == 400
+        assert client.post("/v1/chat/completions", json=dict(body, response_format={"type": "yaml"})).status_code == 400
+        assert client.post("/v1/chat/completions", json=dict(body, response_format={"type": "json_schema"})).status_code == 400
+        assert client.post("/v1/chat/completions", json=dict(body, response_format={"type": "text"})).status_code == 200
+        r = client.post("/v1/chat/completions", json={"model": "tiny", "messages": body["messages"], "temperature": 0,
+                                                      "max_completion_tokens": 3})
+        assert r.status_code == 200 and r.json()["usage"]["completion_tokens"] == 3
+        assert r.json()["choices"][0]["finish_reason"] in ("length", "stop") and r.json()["id"].startswith("chat")
+        big = {"model": "tiny", "messages": [{"role": "user", "content": "x" * (srv.MAX_REQUEST_BODY_BYTES + 10)}]}
+        assert client.post("/v1/chat/completions", content=json.dumps(big),
+                           headers={"content-type": "application/json"}).status_code == 413
+        assert client.get("/debug/runtime_stats").status_code == 200       # enabled above
+        # a full queue answers 429: fill the slots and the queue with long requests behind the server's back
+        inner = srv.engine.engine
+        sp = SamplingParams(max_tokens=100, temperature=0.0, ignore_eos=True)
+        filled = []
+        try:
+            for i in range(100):
+                inner.add_request(f"fill{i}", _ids(5), sp)
+                filled.append(f"fill{i}")
+        except RequestRejectedError:
+            pass
+        assert client.post("/v1/chat/completions", json=body).status_code == 429
+        for rid in filled:
+            inner.abort_request(rid)
+    finally:
+        if srv.engine is not None:
+            srv.engine.shutdown()
+        srv.engine, srv.served_model, srv.debug_endpoints_enabled = saved
