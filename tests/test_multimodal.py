@@ -127,3 +127,36 @@ def test_qwen2vl_decode_positions_continue_the_multimodal_streams():
     for n in range(1, 4):
         nxt = llm.generate([{"prompt_token_ids": full + gen[:n], "multi_modal_data": {"image": [url]}}], one)[0]
         assert nxt.outputs[0].token_ids[0] == gen[n], (n, nxt.outputs[0].token_ids, gen)
+
+
+def test_chat_request_with_image_blocks_over_http():
+    """OpenAI message content as blocks: `image_url` data URLs reach the engine as images (placeholder expanded),
+    a remote URL and an image for a text-only model are 400."""
+    from fastapi.testclient import TestClient
+    from litevllm_b200.entrypoints.openai import api_server as srv
+    client = TestClient(srv.app)
+    saved = (srv.engine, srv.served_model, srv.debug_endpoints_enabled)
+
+    def body(url, model="vl"):
+        return {"model": model, "temperature": 0, "max_tokens": 3,
+                "messages": [{"role": "user", "content": [{"type": "text", "text": "what is this"},
+                                                          {"type": "image_url", "image_url": {"url": url}}]}]}
+    try:
+        srv.engine = srv.build_engine("synthetic:tiny-qwen2vl-test", dtype="float32", device="cpu", max_num_seqs=2,
+                                      max_model_len=256)
+        srv.served_model = "vl"
+        r = client.post("/v1/chat/completions", json=body(_png_url(84, 56)))
+        assert r.status_code == 200, r.text
+        assert r.json()["usage"]["completion_tokens"] == 3 and r.json()["usage"]["prompt_tokens"] > 6   # 6 image tokens + text
+        assert srv.engine.stats()["multimodal"]["images"] == 1
+        assert client.post("/v1/chat/completions", json=body("http://example.com/cat.png")).status_code == 400
+        assert client.post("/v1/chat/completions", json=body("data:image/gif;base64,AAAA")).status_code == 400
+        srv.engine.shutdown()
+        srv.engine = srv.build_engine("synthetic:tiny-llama-test", dtype="float32", device="cpu", max_num_seqs=2,
+                                      max_model_len=128)
+        srv.served_model = "txt"
+        assert client.post("/v1/chat/completions", json=body(_png_url(), model="txt")).status_code == 400
+    finally:
+        if srv.engine is not None:
+            srv.engine.shutdown()
+        srv.engine, srv.served_model, srv.debug_endpoints_enabled = saved
