@@ -148,7 +148,6 @@ def main():
         # routed experts of one DeepSeek-shaped layer at decode size: 8 tokens x top-6 over 256 experts,
         # IQ2_XXS gate / up, Q2_K down (1.8 GB of expert blocks on the device; ~48 experts are touched per call)
         import litevllm_b200.models.deepseek_mla as dm
-        from litevllm_b200.loaders.gguf import GGUFTensor
         from litevllm_b200.models.arch import arch_from_hf_config
         from litevllm_b200.models.presets import get_preset
         arch = arch_from_hf_config(get_preset("deepseek-mla-moe"))

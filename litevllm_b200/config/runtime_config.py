@@ -10,7 +10,6 @@ from __future__ import annotations
 import os
 from collections.abc import Mapping
 from dataclasses import dataclass, field, replace
-from typing import Any
 
 from .env_registry import collect_legacy_tuning_env, truthy
 from .runtime_policy import BackendRuntimePolicy, SchedulerRuntimePolicy

@@ -14,7 +14,7 @@ import time
 import torch
 
 from .errors import ExecutionStepError
-from .executors import LogitsResult, TokenDecodeResult, TokenPrefillResult
+from .executors import TokenDecodeResult, TokenPrefillResult
 from .request_state import RequestState
 from .sampling_driver import SamplingDriver
 from .step_plan import StepPlan

@@ -19,7 +19,6 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from .. import ops
 from .request_state import RequestState
 
 RING = 4

@@ -4,8 +4,6 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-import torch
-
 from .errors import InvalidRequestError
 
 

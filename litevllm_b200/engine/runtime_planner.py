@@ -13,7 +13,7 @@ from dataclasses import dataclass
 
 import torch
 
-from ..utils.misc import cdiv, round_up
+from ..utils.misc import cdiv
 from .kv_cache import KVLayerSpec, bytes_per_block, kv_format, kv_torch_dtype
 
 DEFAULT_CONTEXT_CAP = 4096

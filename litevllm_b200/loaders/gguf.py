@@ -19,7 +19,7 @@ import numpy as np
 import torch
 
 from ..ops import _lib
-from ..ops.gguf_quant import BLOCK, GGML_TYPES, TYPE_NAMES
+from ..ops.gguf_quant import BLOCK, TYPE_NAMES
 
 _NP = {0: np.float32, 1: np.float16, 26: np.int32}
 

@@ -31,7 +31,7 @@ from __future__ import annotations
 
 import math
 import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import torch
 from torch import nn
@@ -39,7 +39,7 @@ from torch import nn
 from .attention import (CompressorState, indexer_scores, indexer_topk, shared_kv_attention,
                         shared_kv_attention_run)
 from . import native as nv
-from .moe import hash_routed_expert_ids, sqrt_softplus_router
+from .moe import sqrt_softplus_router
 from ...utils.profiling import stage
 from ...ops import gguf_quant as gq
 from .ops import indexer_qat

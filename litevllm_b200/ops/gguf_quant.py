@@ -20,7 +20,6 @@ in 16/32-bit floats (no Q8_K activation round trip).
 """
 from __future__ import annotations
 
-import numpy as np
 import torch
 
 from . import _DT, _count, _lib, _p, _stream
