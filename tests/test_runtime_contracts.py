@@ -323,3 +323,62 @@ def test_http_structured_outputs_choice_errors_and_limits():
         if srv.engine is not None:
             srv.engine.shutdown()
         srv.engine, srv.served_model, srv.debug_endpoints_enabled = saved
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_random_arrivals_and_aborts_keep_every_invariant(seed):
+    """A seeded storm on a small engine: requests of random length arrive while others decode, some are aborted
+    at random moments, prefill runs in small chunks.  Every surviving request generates exactly what it generates
+    alone, every slot and KV block comes back, nothing is left in the scheduler."""
+    import random
+    rng = random.Random(seed)
+    cfg = {"profile": "balanced", "tuning_keyvals": {"FASTINFERENCE_LITE_PREFILL_CHUNK": "16",
+                                                     "FASTINFERENCE_MIN_PREFILL_CHUNK": "16",
+                                                     "FASTINFERENCE_MAX_PREFILL_CHUNK": "16"}}
+    llm = LLM("synthetic:tiny-llama-test", device="cpu", dtype="float32", max_num_seqs=3, max_model_len=96,
+              fastinference_config=cfg)
+    eng = llm.engine
+    try:
+        specs = {}
+        for i in range(14):
+            n = rng.randint(3, 50)
+            specs[f"s{i}"] = ([rng.randint(2, 400) for _ in range(n)], rng.randint(1, 9))
+        alone = {}
+        for rid, (ids, mt) in specs.items():
+            out = llm.generate([{"prompt_token_ids": ids}], SamplingParams(max_tokens=mt, temperature=0.0, ignore_eos=True))[0]
+            alone[rid] = out.outputs[0].token_ids
+        pending = list(specs)
+        rng.shuffle(pending)
+        doomed = set(rng.sample(pending, 4))
+        finished, live = {}, set()
+        steps = 0
+        while pending or eng.has_unfinished_requests():
+            steps += 1
+            assert steps < 2000, "the engine stopped making progress"
+            if pending and rng.random() < 0.5:
+                rid = pending.pop()
+                ids, mt = specs[rid]
+                try:
+                    eng.add_request(rid, {"prompt_token_ids": ids}, SamplingParams(max_tokens=mt, temperature=0.0, ignore_eos=True))
+                    live.add(rid)
+                except RequestRejectedError:
+                    pending.insert(0, rid)                      # queue full right now: try again later
+            for rid in list(live & doomed):
+                if rng.random() < 0.15:
+                    assert eng.abort_request(rid)
+                    live.discard(rid)
+                    doomed.discard(rid)
+            for o in eng.step():
+                if o is not None and o.finished:
+                    finished[o.request_id] = o.outputs[0].token_ids
+                    live.discard(o.request_id)
+        for rid, toks in finished.items():
+            assert toks == alone[rid], rid
+        assert set(finished) | {r for r in specs if r not in finished} == set(specs)
+        assert len(finished) >= len(specs) - 4
+        st = eng.stats()["scheduler"]
+        assert st["running"] == 0 and st["queued"] == 0
+        assert eng.kv_manager.allocator.num_free == eng.plan.num_total_blocks - 1
+        assert len(eng.scheduler.free_slots) == eng.plan.max_active_requests
+    finally:
+        llm.shutdown()
