@@ -325,17 +325,20 @@ def test_http_structured_outputs_choice_errors_and_limits():
         srv.engine, srv.served_model, srv.debug_endpoints_enabled = saved
 
 
-@pytest.mark.parametrize("seed", [1, 2, 3])
-def test_random_arrivals_and_aborts_keep_every_invariant(seed):
+@pytest.mark.parametrize("preset,seed", [("tiny-llama-test", 1), ("tiny-llama-test", 2), ("tiny-llama-test", 3),
+                                         ("tiny-qwen35-test", 4), ("tiny-qwen35-moe-test", 5), ("tiny-gemma4-moe-test", 6),
+                                         ("tiny-deepseek-test", 7), ("tiny-deepseek-v4-flash-test", 8)])
+def test_random_arrivals_and_aborts_keep_every_invariant(preset, seed):
     """A seeded storm on a small engine: requests of random length arrive while others decode, some are aborted
     at random moments, prefill runs in small chunks.  Every surviving request generates exactly what it generates
-    alone, every slot and KV block comes back, nothing is left in the scheduler."""
+    alone (also for the models that keep per-slot or per-request state: recurrent state pools, latent rows), every
+    slot and KV block comes back, nothing is left in the scheduler."""
     import random
     rng = random.Random(seed)
     cfg = {"profile": "balanced", "tuning_keyvals": {"FASTINFERENCE_LITE_PREFILL_CHUNK": "16",
                                                      "FASTINFERENCE_MIN_PREFILL_CHUNK": "16",
                                                      "FASTINFERENCE_MAX_PREFILL_CHUNK": "16"}}
-    llm = LLM("synthetic:tiny-llama-test", device="cpu", dtype="float32", max_num_seqs=3, max_model_len=96,
+    llm = LLM(f"synthetic:{preset}", device="cpu", dtype="float32", max_num_seqs=3, max_model_len=96,
               fastinference_config=cfg)
     eng = llm.engine
     try:
