@@ -142,3 +142,65 @@ def test_ep2_alltoall_path_matches_single_rank(preset, monkeypatch):
         spawn(_ep_alltoall_worker, 2, args=(d, preset), port=29551 if "gemma" in preset else 29552)
         got = [json.load(open(os.path.join(d, f"rank{r}.json"))) for r in range(2)]
     assert got[0] == got[1] == want
+
+
+def _storm(llm, seed, n_requests=9):
+    """Random arrivals and aborts driven through the engine; returns {request id: tokens} of what finished."""
+    import random
+
+    from litevllm_b200 import SamplingParams
+    from litevllm_b200.engine.errors import RequestRejectedError
+    rng = random.Random(seed)
+    eng = llm.engine
+    specs = {f"s{i}": ([rng.randint(2, 400) for _ in range(rng.randint(3, 40))], rng.randint(1, 7)) for i in range(n_requests)}
+    pending = list(specs)
+    rng.shuffle(pending)
+    doomed = set(rng.sample(pending, 2))
+    finished, live, steps = {}, set(), 0
+    while pending or eng.has_unfinished_requests():
+        steps += 1
+        assert steps < 2000
+        if pending and rng.random() < 0.5:
+            rid = pending.pop()
+            ids, mt = specs[rid]
+            try:
+                eng.add_request(rid, {"prompt_token_ids": ids}, SamplingParams(max_tokens=mt, temperature=0.0, ignore_eos=True))
+                live.add(rid)
+            except RequestRejectedError:
+                pending.insert(0, rid)
+        for rid in list(live & doomed):
+            if rng.random() < 0.2:
+                eng.abort_request(rid)
+                live.discard(rid)
+                doomed.discard(rid)
+        for o in eng.step():
+            if o is not None and o.finished:
+                finished[o.request_id] = o.outputs[0].token_ids
+                live.discard(o.request_id)
+    assert eng.kv_manager.allocator.num_free == eng.plan.num_total_blocks - 1
+    return finished
+
+
+def _storm_worker(rank, world, out_dir, preset, mode):
+    from litevllm_b200 import LLM
+    kw = {"tensor_parallel_size": world} if mode == "tp" else {"expert_parallel_size": world}
+    llm = LLM(f"synthetic:{preset}", dtype="float32", device="cpu", max_num_seqs=3, max_model_len=96,
+              comm_backend="nccl", **kw)
+    got = _storm(llm, seed=11)
+    with open(os.path.join(out_dir, f"rank{rank}.json"), "w") as f:
+        json.dump(got, f)
+    llm.shutdown()
+
+
+@pytest.mark.parametrize("preset,mode", [("tiny-llama-test", "tp"), ("tiny-gemma4-moe-test", "ep")])
+def test_ranks_stay_in_step_through_random_arrivals_and_aborts(preset, mode):
+    """Every rank runs the same seeded storm (the control plane is deterministic, so no plan is exchanged): the
+    ranks must finish the same requests with the same tokens as one rank alone."""
+    from litevllm_b200 import LLM
+    ref = LLM(f"synthetic:{preset}", dtype="float32", device="cpu", max_num_seqs=3, max_model_len=96)
+    want = _storm(ref, seed=11)
+    ref.shutdown()
+    with tempfile.TemporaryDirectory() as d:
+        spawn(_storm_worker, 2, args=(d, preset, mode), port=29563 if mode == "tp" else 29564)
+        got = [json.load(open(os.path.join(d, f"rank{r}.json"))) for r in range(2)]
+    assert got[0] == got[1] == want
