@@ -385,3 +385,68 @@ def test_random_arrivals_and_aborts_keep_every_invariant(preset, seed):
         assert len(eng.scheduler.free_slots) == eng.plan.max_active_requests
     finally:
         llm.shutdown()
+
+
+def test_async_clients_that_come_and_go():
+    """Twenty-four clients against the background loop: random lengths, a third of them walk away after a random
+    number of chunks.  Everyone who stays gets exactly their tokens, and the engine ends empty."""
+    import random
+    from litevllm_b200.config.config_builder import build_vllm_config
+    from litevllm_b200.engine.async_llm import AsyncLLM
+    from litevllm_b200.engine.errors import LiteRuntimeError
+    rng = random.Random(21)
+    plans = [(f"u{i}", [rng.randint(2, 400) for _ in range(rng.randint(3, 30))], rng.randint(1, 8),
+              rng.random() < 0.33, rng.randint(0, 3)) for i in range(24)]
+
+    async def run():
+        eng = AsyncLLM(build_vllm_config("synthetic:tiny-llama-test", dtype="float32", device="cpu", max_num_seqs=4,
+                                         max_model_len=64))
+        try:
+            async def client(rid, ids, mt, leaves, after):
+                await asyncio.sleep(rng.random() * 0.02)
+                sp = SamplingParams(temperature=0.0, max_tokens=mt, ignore_eos=True)
+                while True:
+                    try:
+                        await eng.submit({"prompt_token_ids": ids}, sp, rid)
+                        break
+                    except LiteRuntimeError:                  # queue full: a real client would retry on 429
+                        await asyncio.sleep(0.005)
+                seen, last = 0, None
+                agen = eng.stream(rid)
+                try:
+                    async for out in agen:
+                        seen, last = seen + 1, out
+                        if leaves and seen > after and not out.finished:
+                            return rid, None
+                finally:
+                    await agen.aclose()
+                return rid, last.outputs[0].token_ids
+
+            results = dict(await asyncio.gather(*[client(*p) for p in plans]))
+            for _ in range(300):
+                s = eng.stats()["scheduler"]
+                if s["running"] == 0 and s["queued"] == 0:
+                    break
+                await asyncio.sleep(0.01)
+            s = eng.stats()["scheduler"]
+            assert s["running"] == 0 and s["queued"] == 0
+            inner = eng.engine
+            assert inner.kv_manager.allocator.num_free == inner.plan.num_total_blocks - 1
+            assert eng.is_healthy()
+            return results
+        finally:
+            eng.shutdown()
+
+    results = asyncio.run(run())
+    ref = LLM("synthetic:tiny-llama-test", device="cpu", dtype="float32", max_num_seqs=4, max_model_len=64)
+    try:
+        stayed = 0
+        for rid, ids, mt, leaves, after in plans:
+            if results[rid] is None:
+                continue
+            stayed += 1
+            want = ref.generate([{"prompt_token_ids": ids}], SamplingParams(temperature=0.0, max_tokens=mt, ignore_eos=True))
+            assert results[rid] == want[0].outputs[0].token_ids, rid
+        assert stayed >= 12
+    finally:
+        ref.shutdown()
