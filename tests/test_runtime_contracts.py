@@ -450,3 +450,37 @@ def test_async_clients_that_come_and_go():
         assert stayed >= 12
     finally:
         ref.shutdown()
+
+
+def test_prefix_cache_under_a_storm_of_related_prompts():
+    """Prompts that share prefixes of several lengths, a small prefix cache with evictions, chunked prefill, random
+    arrival order: hits and partial hits must never change a token."""
+    import random
+    rng = random.Random(5)
+    base = [rng.randint(2, 400) for _ in range(64)]
+    prompts = []
+    for i in range(16):
+        keep = rng.choice([0, 16, 32, 48, 64])
+        prompts.append(base[:keep] + [rng.randint(2, 400) for _ in range(rng.randint(1, 12))])
+    prompts += [list(base), list(base)]                              # exact repeats
+    sp = SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True)
+    plain = _llm_with({})
+    try:
+        want = [plain.generate([{"prompt_token_ids": p}], sp)[0].outputs[0].token_ids for p in prompts]
+    finally:
+        plain.shutdown()
+    cached = _llm_with({"PREFIX_CACHE_MAX_ENTRIES": 3, "LITE_PREFILL_CHUNK": 16, "MIN_PREFILL_CHUNK": 16, "MAX_PREFILL_CHUNK": 16})
+    try:
+        order = list(range(len(prompts)))
+        rng.shuffle(order)
+        for lo in range(0, len(order), 3):                           # groups of three run together
+            group = order[lo:lo + 3]
+            outs = cached.generate([{"prompt_token_ids": prompts[i]} for i in group], sp)
+            for i, o in zip(group, outs):
+                assert o.outputs[0].token_ids == want[i], i
+        pc = cached.engine.stats()["backend"]["prefix_cache"]
+        assert pc["hits"] >= 3 and pc["entries"] <= 3 and pc["evictions"] >= 1, pc
+        eng = cached.engine
+        assert eng.kv_manager.allocator.num_free == eng.plan.num_total_blocks - 1
+    finally:
+        cached.shutdown()
