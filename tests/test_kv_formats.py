@@ -141,3 +141,25 @@ def test_engine_row_scaled_kv_gpu(kv):
     outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
     assert all(len(o.outputs[0].token_ids) == 8 for o in outs)
     ops.check_status(torch.device("cuda:0"))
+
+
+@pytest.mark.parametrize("kv_type", ["fp8", "fp8_block", "turbo_int4"])
+def test_quantised_caches_keep_batch_invariance_on_the_cpu_path(kv_type):
+    """Rows are quantised one (token, head) at a time, so what a request generates cannot depend on who shares the
+    step with it or on how its prompt was chunked."""
+    import random
+    from litevllm_b200 import LLM, SamplingParams
+    rng = random.Random(7)
+    prompts = [{"prompt_token_ids": [rng.randint(2, 400) for _ in range(rng.randint(5, 45))]} for _ in range(7)]
+    sp = SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True)
+    cfg = {"profile": "balanced", "kv_type": kv_type,
+           "tuning_keyvals": {"FASTINFERENCE_LITE_PREFILL_CHUNK": "16", "FASTINFERENCE_MIN_PREFILL_CHUNK": "16",
+                              "FASTINFERENCE_MAX_PREFILL_CHUNK": "16"}}
+    llm = LLM("synthetic:tiny-llama-test", dtype="float32", device="cpu", max_num_seqs=3, max_model_len=96,
+              fastinference_config=cfg)
+    try:
+        together = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+        alone = [llm.generate([p], sp)[0].outputs[0].token_ids for p in prompts]
+        assert together == alone
+    finally:
+        llm.shutdown()
