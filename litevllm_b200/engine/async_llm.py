@@ -133,6 +133,8 @@ class AsyncLLM(EngineClient):
                 if getattr(out, "finished", False):
                     finished = True
                 yield out
+        except (GeneratorExit, asyncio.CancelledError):
+            raise             # the consumer went away (closed the stream, disconnected): abort below
         except BaseException:
             finished = True   # the stream already delivered its terminal item (an exception)
             raise

@@ -162,10 +162,14 @@ def test_async_engine_concurrency_early_exit_and_fatal_step():
             results = await asyncio.gather(*[client(i) for i in range(6)])        # 6 clients, 4 slots
             assert all(r[-1].finished and len(r[-1].outputs[0].token_ids) == 6 for r in results)
             # early exit
-            agen = eng.generate(_ids(7), SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True), "walker")
+            agen = eng.stream("walker")
+            await eng.submit(_ids(7), SamplingParams(temperature=0.0, max_tokens=50, ignore_eos=True), "walker")
             first = await agen.__anext__()
             assert not first.finished
             await agen.aclose()
+            st = eng.stats()
+            # aborted, not run to its end: the request is gone right away and counted as an abort
+            assert st["scheduler"]["running"] == 0 and st["observer"]["counters"].get("requests_aborted", 0) == 1, st["observer"]
             for _ in range(200):
                 if eng.stats()["scheduler"]["running"] == 0:
                     break
