@@ -434,3 +434,49 @@ def test_engine_chunked_prefill_matches_one_shot(llm):
         assert chunked.engine.model.requests == {}
     finally:
         chunked.shutdown()
+
+
+def test_async_clients_leave_no_rows_behind():
+    """Clients of the background loop that finish or walk away: every request's rows are released either way."""
+    import asyncio
+    import random
+    from litevllm_b200.config.config_builder import build_vllm_config
+    from litevllm_b200.engine.async_llm import AsyncLLM
+    from litevllm_b200.engine.errors import LiteRuntimeError
+    rng = random.Random(3)
+    plans = [(f"c{i}", [rng.randint(2, 500) for _ in range(rng.randint(4, 40))], rng.randint(1, 6), i % 3 == 0) for i in range(9)]
+
+    async def run():
+        eng = AsyncLLM(build_vllm_config(PRESET, dtype="float32", device="cpu", max_num_seqs=3, max_model_len=128))
+        try:
+            async def client(rid, ids, mt, leaves):
+                sp = SamplingParams(temperature=0.0, max_tokens=mt if not leaves else 30, ignore_eos=True)
+                while True:
+                    try:
+                        await eng.submit({"prompt_token_ids": ids}, sp, rid)
+                        break
+                    except LiteRuntimeError:
+                        await asyncio.sleep(0.01)
+                agen = eng.stream(rid)
+                try:
+                    async for out in agen:
+                        if leaves and not out.finished:
+                            return False
+                finally:
+                    await agen.aclose()
+                return True
+
+            done = await asyncio.gather(*[client(*p) for p in plans])
+            for _ in range(300):
+                if eng.stats()["scheduler"]["running"] == 0:
+                    break
+                await asyncio.sleep(0.01)
+            model = eng.engine.model
+            ev = eng.stats()["observer"]["model_events"]["counts"]
+            return done, dict(model.requests), ev
+        finally:
+            eng.shutdown()
+
+    done, left, ev = asyncio.run(run())
+    assert left == {} and sum(done) >= 6
+    assert ev["rows_allocated"] == ev["rows_released"] == 9
