@@ -160,3 +160,45 @@ def test_chat_request_with_image_blocks_over_http():
         if srv.engine is not None:
             srv.engine.shutdown()
         srv.engine, srv.served_model, srv.debug_endpoints_enabled = saved
+
+
+def test_image_and_text_requests_share_steps_without_interfering():
+    """Requests with and without images in the same steps (chunked prefill, one abort): a request's tokens are the
+    ones it generates alone - placeholder expansion, embedding merge and the per-request rotary offset stay with
+    their request."""
+    import random
+    from litevllm_b200 import LLM, SamplingParams
+    cfg = {"profile": "balanced", "tuning_keyvals": {"FASTINFERENCE_LITE_PREFILL_CHUNK": "16", "FASTINFERENCE_MIN_PREFILL_CHUNK": "16",
+                                                     "FASTINFERENCE_MAX_PREFILL_CHUNK": "16"}}
+    llm = LLM("synthetic:tiny-qwen2vl-test", dtype="float32", device="cpu", max_num_seqs=3, max_model_len=160,
+              fastinference_config=cfg)
+    eng = llm.engine
+    try:
+        ph = eng.multimodal.image_token_id
+        rng = random.Random(2)
+        sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+        reqs = {}
+        for i in range(7):
+            ids = [rng.randint(5, 300) for _ in range(rng.randint(3, 12))]
+            if i % 2 == 0:
+                ids.insert(rng.randint(0, len(ids)), ph)
+                color = (rng.randint(0, 255), rng.randint(0, 255), rng.randint(0, 255))
+                reqs[f"m{i}"] = {"prompt_token_ids": ids, "multi_modal_data": {"image": [_png_url(84, 56, color)]}}
+            else:
+                reqs[f"m{i}"] = {"prompt_token_ids": ids}
+        alone = {rid: llm.generate([p], sp)[0].outputs[0].token_ids for rid, p in reqs.items()}
+        pending, finished = list(reqs), {}
+        aborted = False
+        while pending or eng.has_unfinished_requests():
+            if pending and rng.random() < 0.7:
+                rid = pending.pop()
+                eng.add_request(rid, reqs[rid], sp)
+            if not aborted and "m2" not in pending and "m2" not in finished and rng.random() < 0.3:
+                aborted = eng.abort_request("m2")
+            for o in eng.step():
+                if o is not None and o.finished:
+                    finished[o.request_id] = o.outputs[0].token_ids
+        assert len(finished) >= 6 and all(finished[r] == alone[r] for r in finished)
+        assert eng.kv_manager.allocator.num_free == eng.plan.num_total_blocks - 1
+    finally:
+        llm.shutdown()
