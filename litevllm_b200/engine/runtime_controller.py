@@ -33,7 +33,7 @@ class RuntimeController:
     def _reject_expired(self) -> None:
         for st in self.scheduler.expire_queued():
             err = RequestRejectedError(
-                f"request {st.request_id} waited longer than {self.scheduler.queue_timeout_s:.0f}s in the queue",
+                f"request {st.request_id} waited longer than {self.scheduler.queue_timeout_s:g} s in the queue (queue timeout)",
                 "queue_timeout")
             self.scheduler.publish_output(st.request_id, err)
             self.observer.on_request_rejected(st.request_id, "queue_timeout")

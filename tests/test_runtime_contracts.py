@@ -549,3 +549,38 @@ def test_lora_requests_in_a_storm_of_mixed_batches(tmp_path):
         assert llm.unregister_lora_adapter("a1") and llm.unregister_lora_adapter("a2")
     finally:
         llm.shutdown()
+
+
+def test_queued_requests_expire_with_a_rejection():
+    """A request that waits longer than the queue time-out is rejected (HTTP 429 material) while the running ones go
+    on; its stream ends with the error."""
+    import time
+    llm = _llm_with({"LITE_QUEUE_TIMEOUT_SECONDS": 0.05, "KV_MAX_ACTIVE_REQUESTS": 2}, )
+    eng = llm.engine
+    loop = asyncio.new_event_loop()
+    try:
+        sp = SamplingParams(max_tokens=40, temperature=0.0, ignore_eos=True)
+        assert eng.plan.max_active_requests == 2
+        eng.add_request("run1", _ids(5), sp)
+        eng.add_request("run2", _ids(6), sp)
+        eng.add_request("waits", _ids(7), sp, loop=loop)
+        eng.step()
+        time.sleep(0.08)
+        for _ in range(3):
+            eng.step()
+
+        async def drain():
+            try:
+                return [o async for o in eng.get_request_stream("waits")]
+            except Exception as e:
+                return e
+
+        got = loop.run_until_complete(asyncio.wait_for(drain(), 10))
+        assert isinstance(got, RequestRejectedError) and "queue timeout" in str(got) and "0.05 s" in str(got), got
+        assert eng.stats()["observer"]["reject_reasons"], eng.stats()["observer"]
+        assert eng.stats()["scheduler"]["running"] == 2
+        eng.abort_request("run1"), eng.abort_request("run2")
+        assert not eng.has_unfinished_requests()
+    finally:
+        loop.close()
+        llm.shutdown()
