@@ -29,8 +29,14 @@ def main() -> None:
     ap.add_argument("--host-profile", action="store_true", help="print the host-side profile of extra decode steps")
     ap.add_argument("--kernel-table", action="store_true",
                     help="print the GPU kernels of one more prefill and one decode step by total time (shares only)")
+    ap.add_argument("--staging-budget-gb", type=float, default=0.0,
+                    help="device budget for routed experts; the rest stays in pinned host memory behind "
+                         "least-recently-used slots (0: everything resident)")
+    ap.add_argument("--pin-hot", type=int, default=0, help="after warm-up, pin this many most-used experts per block")
     ap.add_argument("--engine", action="store_true", help="also time LLM.generate of the same prompts (host clock)")
     a = ap.parse_args()
+    if a.staging_budget_gb > 0:
+        os.environ["FI_EXPERT_STAGING_GB"] = repr(a.staging_budget_gb)       # read when the model is built
     from litevllm_b200 import LLM
     from litevllm_b200.models.deepseek_v4_flash.model import BlockMatrix
     from litevllm_b200.models.presets import PRESETS
@@ -70,6 +76,9 @@ def main() -> None:
         last.append(tok)
     for _ in range(a.warmup):
         last = model.decode_tokens_batch(rids, last)
+    if a.pin_hot > 0:
+        from litevllm_b200.layers import expert_stager
+        expert_stager.pin_hot_experts(model, a.pin_hot)
 
     def decode_steps():
         toks = last
@@ -115,6 +124,8 @@ def main() -> None:
     weights = sum(p.numel() * p.element_size() for p in model.parameters())
     for layer in model.layers:
         weights += sum(v.numel() for v in layer.routed.raw.values()) if layer.routed is not None else 0
+        if layer.routed is not None and layer.routed.stager is not None:
+            weights += layer.routed.stager.device_bytes
         weights += sum(getattr(layer, n).nbytes() for n in model._LINEAR if isinstance(getattr(layer, n, None), BlockMatrix))
     weights += sum(m.nbytes() for m, _ in model._merged.values() if isinstance(m, BlockMatrix))
     print(json.dumps({
@@ -125,7 +136,8 @@ def main() -> None:
         "decode_ms_per_step": round(ms_step, 3), "decode_ms_per_step_per_layer": round(ms_step / a.layers, 4),
         "decode_tok_s": round(a.batch * 1000.0 / ms_step, 2), "weights_gb": round(weights / 2 ** 30, 2),
         "rows_mb": rows_mb, **engine,
-        "decode_graphs": os.environ.get("FI_V4_DECODE_GRAPHS", "1") != "0",
+        "decode_graphs": os.environ.get("FI_V4_DECODE_GRAPHS", "1") != "0" and a.staging_budget_gb <= 0,
+        "expert_staging": llm.engine.stats()["expert_staging"],
         "note": "model-owned data plane; per-layer figures scale to the 43 layers of the full model"}))
 
 

@@ -15,6 +15,7 @@ import torch
 
 from ..adapters.registry import get_model_adapter
 from ..config.inference_config import LiteInferenceConfig
+from ..layers import expert_stager
 from ..config.loadtime_policy import estimate_param_bytes, select_loadtime_policy
 from ..loaders import get_model, resolve_device
 from ..logger import init_logger
@@ -198,6 +199,7 @@ class LiteEngine:
                  "lora": self.lora_registry.stats() if self.lora_registry else {},
                  "multimodal": self.multimodal.stats() if self.multimodal else {},
                  "memory": self.memory.as_dict(), "profile_spans": self._span_summary(),
+                 "expert_staging": expert_stager.summary(self.model),
                  "parallel": {"tp": self.rc.tensor_parallel_size, "ep": self.rc.expert_parallel_size,
                               "comm_backend": self.rc.comm_backend}}
         return self.controller.stats(extra)

@@ -240,6 +240,19 @@ class GatedMLP(nn.Module):
         return self.down_proj(self.gate_up_proj(x), residual=residual, out=residual)
 
 
+def _block_staging_budget(arch) -> int | None:
+    """Device bytes one MoE block may spend on expert payloads: the model's budget (``expert_staging_gb`` of the
+    architecture's extras, else ``FI_EXPERT_STAGING_GB``) split evenly over its MoE blocks.  None: no staging."""
+    from ..layers import expert_stager
+    total = arch.extra.get("expert_staging_gb")
+    total = int(float(total) * 2 ** 30) if total else expert_stager.budget_bytes_from_env()
+    if total is None:
+        return None
+    blocks = arch.extra.get("moe_blocks") or \
+        max(1, getattr(arch, "num_layers", 1) - getattr(arch.moe, "first_dense_layers", 0))
+    return max(1, total // int(blocks))
+
+
 class RoutedExperts(nn.Module):
     """Routed experts kept as raw GGUF blocks: gate/up ``[E, I, row bytes]``, down ``[E, H, row bytes]``."""
 
@@ -254,17 +267,60 @@ class RoutedExperts(nn.Module):
         self.raw: dict[str, torch.Tensor] = {}
         self.types: dict[str, int] = {}
         self.clamp = float(arch.extra.get("swiglu_clamp", 0.0))
+        # a device budget for expert payloads keeps them in pinned host memory behind a slab of device slots
+        self.stage_budget = _block_staging_budget(arch)
+        self.host: dict[str, torch.Tensor] = {}
+        self.stager = None
 
     def load(self, which: str, t) -> None:
         from ..loaders.gguf import GGUFTensor
         if isinstance(t, GGUFTensor):
-            self.raw[which] = t.raw[self.e_lo:self.e_lo + self.e_local].contiguous().to(self.device)
+            blocks = t.raw[self.e_lo:self.e_lo + self.e_local].contiguous()
             self.types[which] = t.ggml_type
         else:   # float experts: store as Q8_0 blocks so one code path serves them
             w = t[self.e_lo:self.e_lo + self.e_local].float()
             E, R, K = w.shape
-            self.raw[which] = gq.quantize_q8_0(w.reshape(E * R, K)).view(E, R, -1).to(self.device)
+            blocks = gq.quantize_q8_0(w.reshape(E * R, K)).view(E, R, -1)
             self.types[which] = 8
+        if self.stage_budget is None:
+            self.raw[which] = blocks.to(self.device)
+        else:
+            blocks = blocks.cpu()
+            self.host[which] = blocks.pin_memory() if torch.device(self.device).type == "cuda" else blocks
+            self.stager = None
+
+    def _ensure_stager(self):
+        """Built at the first step after the three payloads arrived.  A budget that holds every expert turns
+        staging off: the payloads move to the device for good."""
+        if self.stager is None and len(self.host) == 3:
+            from ..layers.expert_stager import ExpertStager
+            per_expert = sum(int(t[0].numel()) * t.element_size() for t in self.host.values())
+            if self.stage_budget >= per_expert * self.e_local:
+                for k, t in self.host.items():
+                    self.raw[k] = t.to(self.device)
+                self.host, self.stage_budget = {}, None
+                return None
+            self.stager = ExpertStager(self.host, self.device, self.stage_budget, min_slots=min(self.e_local, self.top_k))
+        return self.stager
+
+    def _forward_staged(self, x, ids, weights, reduce: bool):
+        """The step's experts become resident in waves; each wave runs on the slab with its routes renumbered
+        to slots and every other route dropped.  One host read of the routed ids per block."""
+        st = self.stager
+        st.stats["steps"] += 1
+        named = torch.unique(ids).tolist()
+        local = [e - self.e_lo for e in named if self.e_lo <= e < self.e_lo + self.e_local]
+        out = None
+        for wave in st.waves(local):
+            placed = st.stage(wave)
+            part = self._core(x, st.slot_ids(ids, placed, self.e_lo), weights, False, st.slab, 0, st.slots)
+            out = part if out is None else out.add_(part)
+        if out is None:
+            out = torch.zeros(x.shape[0], self.H, dtype=x.dtype, device=x.device)
+        if pstate.ep_size() > 1 and reduce:
+            from ..parallel import fused_ops
+            out = fused_ops.all_reduce_activations(out)
+        return out
 
     def forward(self, x, ids, weights, reduce: bool = True):
         """``reduce=False``: the caller owns the exchange between the expert-parallel ranks (rows that arrived by
@@ -275,17 +331,24 @@ class RoutedExperts(nn.Module):
                 one = torch.ones(rows.shape[0], 1, dtype=torch.float32, device=rows.device)
                 return self.forward(rows, expert_ids.view(-1, 1).to(ids.dtype), one, reduce=False)
             return ep_alltoall.sharded_moe(x, ids, weights, self.e_local, run)
+        if self.stage_budget is not None and self._ensure_stager() is not None:
+            return self._forward_staged(x, ids, weights, reduce)
+        return self._core(x, ids, weights, reduce, self.raw, self.e_lo, self.e_local)
+
+    def _core(self, x, ids, weights, reduce, raw, e_lo, e_local):
+        """The experts ``[e_lo, e_lo + e_local)`` whose payloads are ``raw`` applied to the routes that name them;
+        other routes contribute nothing."""
         T, H = x.shape
         K = ids.shape[1]
         n = T * K
         if not x.is_cuda:
             out = torch.zeros(T, H, dtype=torch.float32)
-            g = gq.dequantize(self.raw["gate"].reshape(-1, self.raw["gate"].shape[-1]), self.types["gate"], H).view(self.e_local, self.I, H)
-            u = gq.dequantize(self.raw["up"].reshape(-1, self.raw["up"].shape[-1]), self.types["up"], H).view(self.e_local, self.I, H)
-            d = gq.dequantize(self.raw["down"].reshape(-1, self.raw["down"].shape[-1]), self.types["down"], self.I).view(self.e_local, H, self.I)
+            g = gq.dequantize(raw["gate"].reshape(-1, raw["gate"].shape[-1]), self.types["gate"], H).view(e_local, self.I, H)
+            u = gq.dequantize(raw["up"].reshape(-1, raw["up"].shape[-1]), self.types["up"], H).view(e_local, self.I, H)
+            d = gq.dequantize(raw["down"].reshape(-1, raw["down"].shape[-1]), self.types["down"], self.I).view(e_local, H, self.I)
             xf = x.float()
-            for e in range(self.e_local):
-                tok, slot = torch.nonzero(ids == e + self.e_lo, as_tuple=True)
+            for e in range(e_local):
+                tok, slot = torch.nonzero(ids == e + e_lo, as_tuple=True)
                 if tok.numel() == 0:
                     continue
                 gv, uv = xf[tok] @ g[e].t(), xf[tok] @ u[e].t()
@@ -301,67 +364,67 @@ class RoutedExperts(nn.Module):
             buf = scratch("ds_moe", n * (self.I + H) * esz + 256, x.device)
             a = buf[: n * self.I * esz].view(x.dtype).view(n, self.I)
             y = buf[n * self.I * esz: n * (self.I + H) * esz].view(x.dtype).view(n, H)
-            e_hi = self.e_lo + self.e_local
+            e_hi = e_lo + e_local
             ids_flat = ids.reshape(-1)
             slot_of = None
-            if reduce and n >= _DENSE_EXPERT_ROUTES * self.e_local and self.clamp <= 0 \
+            if (reduce or raw is not self.raw) and n >= _DENSE_EXPERT_ROUTES * e_local and self.clamp <= 0 \
                     and x.dtype in (torch.bfloat16, torch.float16):
-                return self._forward_tensor_core(x, ids_flat, weights, a, y, T, K, H)
+                return self._forward_tensor_core(x, ids_flat, weights, a, y, T, K, H, raw, e_lo, e_local, reduce)
             same_gu = self.types["gate"] == self.types["up"]
             # int8 activations + dp4a for the 2-bit formats; 16-bit activations for the others
             q8 = _Q8 and x.dtype == torch.bfloat16 and same_gu and self.types["gate"] in (10, 16) \
                 and self.types["down"] in (10, 16)
-            grouped = q8 or ((_GROUPED == "on" or (_GROUPED == "auto" and n >= self.e_local))
+            grouped = q8 or ((_GROUPED == "on" or (_GROUPED == "auto" and n >= e_local))
                              and x.dtype == torch.bfloat16 and same_gu and self.types["gate"] in (8, 10, 16))
             if grouped:
                 # routes sorted by expert; a tile of up to 8 routes of one expert streams that expert once.  Steps
                 # with fewer routes than experts (small decode batches) use tiles of one route.
-                tile_m = 8 if (not q8 or n >= self.e_local) else 1
-                max_tiles = n if tile_m == 1 else n // 8 + self.e_local
-                ints = scratch("ds_moe_ints", (2 * n + self.e_local + 1 + 3 * max_tiles + 8) * 4, x.device).view(torch.int32)
+                tile_m = 8 if (not q8 or n >= e_local) else 1
+                max_tiles = n if tile_m == 1 else n // 8 + e_local
+                ints = scratch("ds_moe_ints", (2 * n + e_local + 1 + 3 * max_tiles + 8) * 4, x.device).view(torch.int32)
                 o = 0
                 sorted_route = ints[o:o + n]; o += n
                 slot_of = ints[o:o + n]; o += n
-                offsets = ints[o:o + self.e_local + 1]; o += self.e_local + 1
+                offsets = ints[o:o + e_local + 1]; o += e_local + 1
                 tile_expert = ints[o:o + max_tiles]; o += max_tiles
                 tile_row0 = ints[o:o + max_tiles]; o += max_tiles
                 tile_rows = ints[o:o + max_tiles]; o += max_tiles
                 n_tiles = ints[o:o + 1]
-                rc = lib.fi_moe_align(_p(ids_flat), n, self.e_lo, e_hi, tile_m, _p(sorted_route), _p(slot_of), _p(offsets),
+                rc = lib.fi_moe_align(_p(ids_flat), n, e_lo, e_hi, tile_m, _p(sorted_route), _p(slot_of), _p(offsets),
                                       _p(tile_expert), _p(tile_row0), _p(tile_rows), _p(n_tiles), _stream())
                 _lib.check(rc, "fi_moe_align")
                 if q8:
                     rc = lib.fi_gguf_moe_gate_up_q8(
-                        _p(x), x.stride(0), _p(self.raw["gate"]), _p(self.raw["up"]), self.types["gate"],
-                        self.types["up"], self.raw["gate"].shape[-1], self.raw["up"].shape[-1], _p(sorted_route),
+                        _p(x), x.stride(0), _p(raw["gate"]), _p(raw["up"]), self.types["gate"],
+                        self.types["up"], raw["gate"].shape[-1], raw["up"].shape[-1], _p(sorted_route),
                         _p(tile_expert), _p(tile_row0), _p(tile_rows), _p(n_tiles), max_tiles, tile_m, K, self.I, H,
                         self.clamp, _p(a), _stream())
                     _lib.check(rc, "fi_gguf_moe_gate_up_q8")
-                    rc = lib.fi_gguf_moe_down_q8(_p(a), _p(self.raw["down"]), self.types["down"],
-                                                 self.raw["down"].shape[-1], _p(tile_expert), _p(tile_row0),
+                    rc = lib.fi_gguf_moe_down_q8(_p(a), _p(raw["down"]), self.types["down"],
+                                                 raw["down"].shape[-1], _p(tile_expert), _p(tile_row0),
                                                  _p(tile_rows), _p(n_tiles), max_tiles, tile_m, H, self.I, _p(y),
                                                  _stream())
                     _lib.check(rc, "fi_gguf_moe_down_q8")
                 else:
                     rc = lib.fi_gguf_moe_gate_up_grouped(
-                        _p(x), x.stride(0), _p(self.raw["gate"]), _p(self.raw["up"]), self.types["gate"],
-                        self.types["up"], self.raw["gate"].shape[-1], self.raw["up"].shape[-1], _p(sorted_route),
+                        _p(x), x.stride(0), _p(raw["gate"]), _p(raw["up"]), self.types["gate"],
+                        self.types["up"], raw["gate"].shape[-1], raw["up"].shape[-1], _p(sorted_route),
                         _p(tile_expert), _p(tile_row0), _p(tile_rows), _p(n_tiles), max_tiles, K, self.I, H, self.clamp,
                         _p(a), _stream())
                     _lib.check(rc, "fi_gguf_moe_gate_up_grouped")
-                    rc = lib.fi_gguf_moe_down_grouped(_p(a), _p(self.raw["down"]), self.types["down"],
-                                                      self.raw["down"].shape[-1], _p(tile_expert), _p(tile_row0),
+                    rc = lib.fi_gguf_moe_down_grouped(_p(a), _p(raw["down"]), self.types["down"],
+                                                      raw["down"].shape[-1], _p(tile_expert), _p(tile_row0),
                                                       _p(tile_rows), _p(n_tiles), max_tiles, H, self.I, _p(y), _stream())
                     _lib.check(rc, "fi_gguf_moe_down_grouped")
                 _count(1)
             else:
-                rc = lib.fi_gguf_moe_gate_up(_p(x), x.stride(0), _p(self.raw["gate"]), _p(self.raw["up"]),
-                                             self.types["gate"], self.types["up"], self.raw["gate"].shape[-1],
-                                             self.raw["up"].shape[-1], _p(ids_flat), n, K, self.e_lo, e_hi, self.I, H,
+                rc = lib.fi_gguf_moe_gate_up(_p(x), x.stride(0), _p(raw["gate"]), _p(raw["up"]),
+                                             self.types["gate"], self.types["up"], raw["gate"].shape[-1],
+                                             raw["up"].shape[-1], _p(ids_flat), n, K, e_lo, e_hi, self.I, H,
                                              self.clamp, _p(a), _stream())
                 _lib.check(rc, "fi_gguf_moe_gate_up")
-                rc = lib.fi_gguf_moe_down(_p(a), _p(self.raw["down"]), self.types["down"], self.raw["down"].shape[-1],
-                                          _p(ids_flat), n, self.e_lo, e_hi, H, self.I, _p(y), _stream())
+                rc = lib.fi_gguf_moe_down(_p(a), _p(raw["down"]), self.types["down"], raw["down"].shape[-1],
+                                          _p(ids_flat), n, e_lo, e_hi, H, self.I, _p(y), _stream())
                 _lib.check(rc, "fi_gguf_moe_down")
             out = torch.empty(T, H, dtype=x.dtype, device=x.device)
             heap = None
@@ -386,7 +449,7 @@ class RoutedExperts(nn.Module):
         return out
 
 
-    def _forward_tensor_core(self, x, ids_flat, weights, a, y, T, K, H):
+    def _forward_tensor_core(self, x, ids_flat, weights, a, y, T, K, H, raw, e_lo, e_local, reduce):
         """Large prefill steps (on average dozens of routes per expert): the routes are sorted by expert, the
         activation rows gathered in that order, and every expert with work is dequantised into a 16-bit scratch
         matrix and applied with the tcgen05 GEMM (gate|up, SiLU * up, down).  Streaming the 2-bit blocks once per
@@ -395,43 +458,43 @@ class RoutedExperts(nn.Module):
         lib = _lib.kernels()
         n = T * K
         dev, dt = x.device, x.dtype
-        ints = scratch("ds_moe_ints", (2 * n + self.e_local + 1 + 3 * (n // 128 + self.e_local) + 8) * 4, dev).view(torch.int32)
-        mt = n // 128 + self.e_local
+        ints = scratch("ds_moe_ints", (2 * n + e_local + 1 + 3 * (n // 128 + e_local) + 8) * 4, dev).view(torch.int32)
+        mt = n // 128 + e_local
         o = 0
         sorted_route = ints[o:o + n]; o += n
         slot_of = ints[o:o + n]; o += n
-        offsets = ints[o:o + self.e_local + 1]; o += self.e_local + 1
+        offsets = ints[o:o + e_local + 1]; o += e_local + 1
         tile_expert = ints[o:o + mt]; o += mt
         tile_row0 = ints[o:o + mt]; o += mt
         tile_rows = ints[o:o + mt]; o += mt
         n_tiles = ints[o:o + 1]
-        rc = lib.fi_moe_align(_p(ids_flat), n, self.e_lo, self.e_lo + self.e_local, 128, _p(sorted_route), _p(slot_of),
+        rc = lib.fi_moe_align(_p(ids_flat), n, e_lo, e_lo + e_local, 128, _p(sorted_route), _p(slot_of),
                               _p(offsets), _p(tile_expert), _p(tile_row0), _p(tile_rows), _p(n_tiles), _stream())
         _lib.check(rc, "fi_moe_align")
         xs = scratch("ds_moe_xs", n * H * x.element_size() + 256, dev)[: n * H * x.element_size()].view(dt).view(n, H)
-        rc = lib.fi_moe_gather(_p(x), _p(sorted_route), _p(offsets), self.e_local, n, K, H, _p(xs), ops._DT[dt], _stream())
+        rc = lib.fi_moe_gather(_p(x), _p(sorted_route), _p(offsets), e_local, n, K, H, _p(xs), ops._DT[dt], _stream())
         _lib.check(rc, "fi_moe_gather")
         off = offsets.tolist()
         I = self.I
         wgu = scratch("ds_moe_wgu", 2 * I * H * 2 + 256, dev)[: 2 * I * H * 2].view(dt).view(2 * I, H)
         wd = scratch("ds_moe_wd", H * I * 2 + 256, dev)[: H * I * 2].view(dt).view(H, I)
-        gu = scratch("ds_moe_gu", max(off[e + 1] - off[e] for e in range(self.e_local)) * 2 * I * 2 + 256, dev)
-        for e in range(self.e_local):
+        gu = scratch("ds_moe_gu", max(off[e + 1] - off[e] for e in range(e_local)) * 2 * I * 2 + 256, dev)
+        for e in range(e_local):
             r0, r1 = off[e], off[e + 1]
             if r1 <= r0:
                 continue
-            gq.dequantize_cuda(self.raw["gate"][e], self.types["gate"], H, dt, out=wgu[:I])
-            gq.dequantize_cuda(self.raw["up"][e], self.types["up"], H, dt, out=wgu[I:])
+            gq.dequantize_cuda(raw["gate"][e], self.types["gate"], H, dt, out=wgu[:I])
+            gq.dequantize_cuda(raw["up"][e], self.types["up"], H, dt, out=wgu[I:])
             g = gu[: (r1 - r0) * 2 * I * 2].view(dt).view(r1 - r0, 2 * I)
             ops.linear(xs[r0:r1], wgu, out=g, static_weight=False)
             ops.act_mul(g, "silu", out=a[r0:r1])
-            gq.dequantize_cuda(self.raw["down"][e], self.types["down"], I, dt, out=wd)
+            gq.dequantize_cuda(raw["down"][e], self.types["down"], I, dt, out=wd)
             ops.linear(a[r0:r1], wd, out=y[r0:r1], static_weight=False)
         out = torch.empty(T, H, dtype=dt, device=dev)
         rc = lib.fi_moe_combine(_p(y), _p(slot_of), _p(weights), None, _p(out), T, K, H, ops._DT[dt], _stream())
         _lib.check(rc, "fi_moe_combine")
         _count(3)
-        if pstate.ep_size() > 1:
+        if pstate.ep_size() > 1 and reduce:
             from ..parallel import fused_ops
             out = fused_ops.all_reduce_activations(out)
         return out
@@ -494,6 +557,8 @@ class DeepseekMLAForCausalLM(nn.Module):
         from ..parallel import ep_alltoall
         if ep_alltoall.ENABLED and pstate.ep_size() > 1:
             self.supports_cuda_graph = False      # the all-to-all split sizes are read on the host every step
+        if arch.moe is not None and _block_staging_budget(arch) is not None:
+            self.supports_cuda_graph = False      # staged experts: the routed ids are read on the host every block
         self.embed_tokens = nn.Parameter(torch.empty(arch.vocab_size, arch.hidden_size, dtype=mc.dtype), requires_grad=False)
         self.layers = nn.ModuleList([DeepseekDecoderLayer(arch, i, mc.dtype, qc) for i in range(arch.num_layers)])
         self.norm = RMSNormWeight(arch.hidden_size, arch.rms_eps, mc.dtype)

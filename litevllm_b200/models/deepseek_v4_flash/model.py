@@ -352,7 +352,7 @@ class DeepseekV4FlashForCausalLM(nn.Module):
             from types import SimpleNamespace
             from ..deepseek_mla import RoutedExperts
             c = self.cfg
-            shim = SimpleNamespace(hidden_size=c.hidden, extra={"swiglu_clamp": c.swiglu_clamp},
+            shim = SimpleNamespace(hidden_size=c.hidden, extra={"swiglu_clamp": c.swiglu_clamp, "moe_blocks": len(self.layers)},
                                    moe=SimpleNamespace(num_experts=c.experts, expert_intermediate=c.expert_inter,
                                                        top_k=c.top_k))
             layer.routed = RoutedExperts(shim, torch.bfloat16)
@@ -879,7 +879,7 @@ class DeepseekV4FlashForCausalLM(nn.Module):
     def _decode_graphs_ok(self, rows: list) -> bool:
         # dense (non-block) experts group their routes with a host read, which a capture cannot contain
         return (_DECODE_GRAPHS and self.embed.is_cuda and 1 <= len(rows) <= _DECODE_GRAPH_MAX_T
-                and len({id(r) for r in rows}) == len(rows) and all(l.routed is not None for l in self.layers))
+                and len({id(r) for r in rows}) == len(rows) and all(l.routed is not None and l.routed.stage_budget is None for l in self.layers))
 
     def _layer_tail(self, li: int, out: torch.Tensor, g: dict) -> None:
         """Static stretch after layer ``li``'s rows: output projection, the feed-forward half, and either the next

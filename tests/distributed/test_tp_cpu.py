@@ -61,6 +61,38 @@ def test_ep2_matches_single_rank(preset):
     assert got[0] == want
 
 
+def _staged_ep_worker(rank, world, out_dir, preset, budget_gb):
+    os.environ["FI_EXPERT_STAGING_GB"] = budget_gb
+    from litevllm_b200 import LLM, SamplingParams
+    llm = LLM(f"synthetic:{preset}", dtype="float32", device="cpu", max_num_seqs=4, max_model_len=128,
+              expert_parallel_size=world, comm_backend="nccl")
+    outs = llm.generate(_prompts(), SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))
+    with open(os.path.join(out_dir, f"rank{rank}.json"), "w") as f:
+        json.dump({"tokens": [o.outputs[0].token_ids for o in outs], "staging": llm.engine.stats()["expert_staging"]}, f)
+    llm.shutdown()
+
+
+def test_ep2_with_staged_experts_matches_single_rank():
+    """Each rank owns four of the eight experts and keeps two of them on the device at a time."""
+    from litevllm_b200 import LLM, SamplingParams
+    from litevllm_b200.models.deepseek_mla import RoutedExperts
+    preset = "tiny-deepseek-test"
+    ref = LLM(f"synthetic:{preset}", dtype="float32", device="cpu", max_num_seqs=4, max_model_len=128)
+    want = [o.outputs[0].token_ids for o in
+            ref.generate(_prompts(), SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))]
+    blocks = [m for m in ref.engine.model.modules() if isinstance(m, RoutedExperts)]
+    per_expert = sum(int(t[0].numel()) * t.element_size() for t in blocks[0].raw.values())
+    ref.shutdown()
+    budget = repr(2.5 * per_expert * len(blocks) / 2 ** 30)
+    with tempfile.TemporaryDirectory() as d:
+        spawn(_staged_ep_worker, 2, args=(d, preset, budget), port=29548)
+        got = [json.load(open(os.path.join(d, f"rank{r}.json"))) for r in range(2)]
+    assert got[0]["tokens"] == got[1]["tokens"] == want
+    for g in got:
+        assert g["staging"]["slots_per_block"] == 2 and g["staging"]["experts_per_block"] == 4
+        assert g["staging"]["evictions"] > 0
+
+
 def _tpep_worker(rank, world, out_dir, preset):
     from litevllm_b200 import LLM, SamplingParams
     llm = LLM(f"synthetic:{preset}", dtype="float32", device="cpu", max_num_seqs=4, max_model_len=128,

@@ -480,3 +480,25 @@ def test_async_clients_leave_no_rows_behind():
     done, left, ev = asyncio.run(run())
     assert left == {} and sum(done) >= 6
     assert ev["rows_allocated"] == ev["rows_released"] == 9
+
+
+def test_staged_experts_of_a_gguf_checkpoint_match_resident_ones(llm, tmp_path, monkeypatch):
+    """The two-bit routed experts of a `deepseek4` file behind a device budget of three experts per block: the
+    tokens equal those of the fully resident model, and the slots saw hits, misses and evictions."""
+    path = tmp_path / "tiny-v4-2bit.gguf"
+    _write_v4_gguf(llm.engine.model, path, two_bit_experts=True)
+    monkeypatch.delenv("FI_EXPERT_STAGING_GB", raising=False)
+    resident = LLM(str(path), device="cpu", max_model_len=128, dtype="float32")
+    want = _tokens(resident, PROMPTS[:2], 6)
+    blocks = [l.routed for l in resident.engine.model.layers]
+    assert all(b is not None and b.stager is None for b in blocks)
+    per_expert = sum(int(t[0].numel()) * t.element_size() for t in blocks[0].raw.values())
+    resident.shutdown()
+    monkeypatch.setenv("FI_EXPERT_STAGING_GB", repr(3.5 * per_expert * len(blocks) / 2 ** 30))
+    staged = LLM(str(path), device="cpu", max_model_len=128, dtype="float32")
+    assert _tokens(staged, PROMPTS[:2], 6) == want
+    for l in staged.engine.model.layers:
+        snap = l.routed.stager.snapshot()
+        assert snap["slots"] == 3 and snap["misses"] > 0 and snap["hits"] > 0 and snap["evictions"] > 0
+        assert not l.routed.raw
+    staged.shutdown()
