@@ -112,3 +112,54 @@ def test_grid_with_an_environment_axis_runs_child_processes(capsys):
     rep = _json_line(capsys)
     assert rep["child_processes"] is True and [p["env"] for p in rep["points"]] == [{"FI_BOUNDS_CHECK": "0"}, {"FI_BOUNDS_CHECK": "1"}]
     assert all(p["median_tps"] > 0 for p in rep["points"])
+
+
+def test_ngram_replay_counts_what_a_verify_step_would_accept():
+    from litevllm_b200.diagnostics import speculative_ngram as sn
+    prompt = [1, 2, 3, 4, 5, 6]
+    assert sn.propose(prompt + [9, 1, 2], 3, 3) == [3, 4, 5]            # suffix (1, 2) seen in the prompt
+    assert sn.propose(prompt + [9], 1, 3) == []                          # too little output for a 2-gram
+    assert sn.propose([7, 8, 9, 7, 8], 2, 4) == [9, 7, 8]               # most recent earlier occurrence
+    rep = sn.replay(prompt, [1, 2, 3, 4, 5, 6, 1, 2], k=3)
+    # steps: 1 | 2 | (draft 3 4 5: all accepted) 3 4 5 6 | (draft 1 2 3: 2 accepted, then the output ends) 1 2
+    assert rep == {"tokens": 8, "verify_steps": 4, "steps_with_draft": 2, "proposed": 6, "accepted": 5}
+    assert sn.replay(prompt, [], 3)["verify_steps"] == 0
+    noisy = sn.replay([1, 2, 3], [9, 8, 7, 6, 5], 3)
+    assert noisy["accepted"] == 0 and noisy["verify_steps"] == 5
+    s = sn.summarise([rep, noisy], verify_cost=1.5)
+    assert s["tokens"] == 13 and s["tokens_per_step"] == round(13 / 9, 4) and s["acceptance"] == round(5 / 6, 4)
+    assert s["projected_speedup"] == round(13 / (7 + 1.5 * 2), 4)
+
+
+def test_ngram_tool_runs_on_a_model(capsys):
+    from litevllm_b200.diagnostics import speculative_ngram as sn
+    assert sn.main(["--model", "synthetic:tiny-llama-test", "--engine", json.dumps({"device": "cpu", "dtype": "float32",
+                    "max_model_len": 128}), "--max-tokens", "24", "-k", "3"]) == 0
+    rep = _json_line(capsys)
+    assert rep["tokens"] == sum(p["tokens"] for p in rep["per_prompt"]) and rep["tokens"] > 0
+    assert 1.0 <= rep["tokens_per_step"] <= 4.0 and 0.0 <= rep["acceptance"] <= 1.0
+
+
+def test_quality_cases_are_judged_by_their_expectations(tmp_path, capsys):
+    from litevllm_b200.diagnostics import quality_spotcheck as qs
+    ok = qs.judge_case({"expect_any": ["Paris", "Lyon"], "expect_all": ["france"], "expect_regex": r"capital\s+of",
+                        "forbid": ["berlin"]}, "The capital of France is paris.", [1, 2, 3], "stop")
+    assert ok == []
+    why = qs.judge_case({"expect_any": ["Paris"], "forbid": ["the"]}, "The answer", [1, 2], "abort")
+    assert len(why) == 3 and any("finish reason" in w for w in why)
+    assert qs.judge_case({}, "", [], "stop") == ["empty answer"]
+    assert any("degenerate" in w for w in qs.judge_case({}, "x" * 20, [5] * 15 + [6] * 5, "length"))
+    assert qs.judge_case({}, "fine", list(range(20)), "length") == []
+    fixtures = tmp_path / "cases.json"
+    fixtures.write_text(json.dumps([
+        {"name": "anything", "prompt_token_ids": [5, 6, 7, 8], "max_tokens": 6, "expect_regex": "."},
+        {"name": "impossible", "prompt_token_ids": [9, 10, 11], "max_tokens": 6, "expect_all": ["no such text ☃"]}]))
+    args = ["--model", "synthetic:tiny-llama-test", "--fixtures", str(fixtures),
+            "--engine", json.dumps({"device": "cpu", "dtype": "float32", "max_model_len": 64})]
+    assert qs.main(args) == 1
+    rep = _json_line(capsys)
+    assert rep["pass_rate"] == 0.5 and [r["passed"] for r in rep["results"]] == [True, False]
+    assert qs.main(args + ["--min-pass-rate", "0.5"]) == 0
+    empty = tmp_path / "empty.json"
+    empty.write_text("[]")
+    assert qs.main(["--model", "synthetic:tiny-llama-test", "--fixtures", str(empty)]) == 2
