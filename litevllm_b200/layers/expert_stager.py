@@ -36,6 +36,19 @@ def budget_bytes_from_env(default: float | None = None) -> int | None:
     return int(value * 2 ** 30)
 
 
+def auto_pin_from_env() -> tuple[int, int]:
+    """``FI_EXPERT_STAGING_PIN_HOT="n"`` or ``"n@steps"``: after ``steps`` staged steps of a block (default 64)
+    its ``n`` most used experts are pinned.  (0, 0): no automatic pinning."""
+    raw = os.environ.get("FI_EXPERT_STAGING_PIN_HOT", "").strip()
+    if not raw:
+        return 0, 0
+    n, _, after = raw.partition("@")
+    n, after = int(n), int(after or 64)
+    if n < 0 or after < 1:
+        raise ValueError("FI_EXPERT_STAGING_PIN_HOT: expected n or n@steps with n >= 0 and steps >= 1")
+    return n, after
+
+
 class ExpertStager:
     """Device slots for the experts of one MoE block.
 
@@ -64,6 +77,14 @@ class ExpertStager:
         self._pinned: set[int] = set()
         self.use_counts = [0] * self.num_experts
         self.stats = {"hits": 0, "misses": 0, "evictions": 0, "bytes_staged": 0, "waves": 0, "steps": 0}
+        self.auto_pin = auto_pin_from_env()
+
+    def begin_step(self) -> None:
+        """Counts a step of the block and applies the automatic pinning once its step count is reached."""
+        self.stats["steps"] += 1
+        n, after = self.auto_pin
+        if n and self.stats["steps"] == after + 1:
+            self.pin_hot(n)
 
     # ---- residency ------------------------------------------------------------------------------------------
     @property

@@ -307,7 +307,7 @@ class RoutedExperts(nn.Module):
         """The step's experts become resident in waves; each wave runs on the slab with its routes renumbered
         to slots and every other route dropped.  One host read of the routed ids per block."""
         st = self.stager
-        st.stats["steps"] += 1
+        st.begin_step()
         named = torch.unique(ids).tolist()
         local = [e - self.e_lo for e in named if self.e_lo <= e < self.e_lo + self.e_local]
         out = None

@@ -184,3 +184,26 @@ def test_a_budget_that_holds_everything_turns_staging_off(monkeypatch):
     ref, want = _generate("tiny-deepseek-test")
     ref.shutdown()
     assert got == want
+
+
+def test_hot_experts_are_pinned_automatically_after_the_configured_steps(monkeypatch):
+    from litevllm_b200.layers.expert_stager import auto_pin_from_env
+    monkeypatch.delenv("FI_EXPERT_STAGING_PIN_HOT", raising=False)
+    assert auto_pin_from_env() == (0, 0)
+    monkeypatch.setenv("FI_EXPERT_STAGING_PIN_HOT", "2")
+    assert auto_pin_from_env() == (2, 64)
+    monkeypatch.setenv("FI_EXPERT_STAGING_PIN_HOT", "2@3")
+    st = ExpertStager(_host(), "cpu", 4 * 96)
+    for need in ([1, 5], [5, 6], [5, 1]):
+        st.begin_step()
+        st.stage(need)
+        assert st.pinned() == []
+    st.begin_step()                                  # the fourth step: three steps of traffic decide
+    assert st.pinned() == [1, 5]
+    for e in (0, 2, 3, 4, 6, 7):
+        st.begin_step()
+        st.stage([e])
+    assert {1, 5} <= set(st.resident()) and st.pinned() == [1, 5]
+    monkeypatch.setenv("FI_EXPERT_STAGING_PIN_HOT", "-1")
+    with pytest.raises(ValueError):
+        auto_pin_from_env()
