@@ -22,6 +22,7 @@ from torch import nn
 
 from .. import ops
 from ..layers.linear import LiteLinear
+from ..logger import init_logger
 from ..layers.rope import get_cos_sin
 from ..ops import gguf_quant as gq
 from ..ops import moe as moe_ops
@@ -30,6 +31,8 @@ from ..parallel import state as pstate
 from ..utils.profiling import stage
 from .arch import ModelArch
 from .llama import RMSNormWeight
+
+logger = init_logger(__name__)
 
 # Routed experts from GGUF blocks: "auto" sorts the routes by expert and runs the grouped kernels when a
 # step has at least as many routes as local experts, "on" / "off" force one form.
@@ -286,7 +289,12 @@ class RoutedExperts(nn.Module):
             self.raw[which] = blocks.to(self.device)
         else:
             blocks = blocks.cpu()
-            self.host[which] = blocks.pin_memory() if torch.device(self.device).type == "cuda" else blocks
+            if torch.device(self.device).type == "cuda":
+                try:
+                    blocks = blocks.pin_memory()
+                except RuntimeError as e:     # the host refuses to lock that much: pageable copies still work, slower
+                    logger.warning("expert payload %s stays in pageable host memory (%s)", which, e)
+            self.host[which] = blocks
             self.stager = None
 
     def _ensure_stager(self):
