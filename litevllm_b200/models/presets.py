@@ -94,6 +94,8 @@ PRESETS["tiny-deepseek-v4-flash-test"] = {
     "vocab_size": 512, "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "max_position_embeddings": 512,
     "intermediate_size": 256, "eos_token_id": 1,
 }
+# the same with random weights in the checkpoint's block formats (IQ2_XXS / Q2_K routed experts, Q8_0 projections)
+PRESETS["tiny-deepseek-v4-flash-blocks-test"] = dict(PRESETS["tiny-deepseek-v4-flash-test"], synthetic_block_weights=True)
 # the full-size geometry of the DeepSeek-V4-Flash checkpoint family; as a synthetic model its weights are random
 # blocks in the checkpoint's formats (IQ2_XXS / Q2_K experts, Q8_0 projections: about 90 GB)
 PRESETS["deepseek-v4-flash"] = {

@@ -584,3 +584,12 @@ def test_queued_requests_expire_with_a_rejection():
     finally:
         loop.close()
         llm.shutdown()
+
+
+@pytest.mark.parametrize("preset,seed", [("tiny-deepseek-test", 9), ("tiny-deepseek-v4-flash-blocks-test", 10)])
+def test_the_storm_with_routed_experts_behind_a_device_budget(preset, seed, monkeypatch):
+    """The same storm while each MoE block keeps two of its eight experts on the device: residency changes from
+    step to step with the mix of requests, results and bookkeeping do not."""
+    monkeypatch.setenv("FI_EXPERT_STAGING_GB", "1e-9")          # below one expert: the minimum number of slots
+    monkeypatch.setenv("FI_EXPERT_STAGING_PIN_HOT", "1@20")
+    test_random_arrivals_and_aborts_keep_every_invariant(preset, seed)
