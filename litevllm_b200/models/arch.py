@@ -204,6 +204,8 @@ def arch_from_hf_config(cfg: dict) -> ModelArch:
                            renormalize=bool(text.get("norm_topk_prob", True)),
                            routed_scaling=float(text.get("routed_scaling_factor", 1.0)),
                            first_dense_layers=int(text.get("first_k_dense_replace", 0)))
+        if text.get("expert_staging_gb"):       # e.g. hf_overrides={"expert_staging_gb": 40}
+            arch.extra["expert_staging_gb"] = float(text["expert_staging_gb"])
     if family == "deepseek_v4_flash":
         arch.extra["v4_rows"] = {k: text[k] for k in ("num_hidden_layers", "head_dim", "sliding_window",
                                                       "compress_ratio_coarse", "layer_compress_ratios")

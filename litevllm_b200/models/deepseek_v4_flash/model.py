@@ -81,6 +81,7 @@ class V4Config:
     rope_beta_fast: float = 32.0
     rope_beta_slow: float = 1.0
     block_experts: bool = False      # routed experts only ever exist as GGUF blocks (no dense expert parameters)
+    expert_staging_gb: float = 0.0   # device budget for routed experts (0: the environment switch, else all resident)
 
     @classmethod
     def from_hf(cls, cfg: dict) -> "V4Config":
@@ -102,6 +103,7 @@ class V4Config:
                    rope_factor=float(g("rope_scaling_factor", 16.0)),
                    rope_original_context=int(g("rope_original_context", 65536)),
                    rope_beta_fast=float(g("rope_beta_fast", 32.0)), rope_beta_slow=float(g("rope_beta_slow", 1.0)),
+                   expert_staging_gb=float(g("expert_staging_gb", 0.0) or 0.0),
                    block_experts=bool(g("synthetic_block_weights", False)) or
                    (g("quantization_config") or {}).get("quant_method") == "gguf")
 
@@ -352,7 +354,8 @@ class DeepseekV4FlashForCausalLM(nn.Module):
             from types import SimpleNamespace
             from ..deepseek_mla import RoutedExperts
             c = self.cfg
-            shim = SimpleNamespace(hidden_size=c.hidden, extra={"swiglu_clamp": c.swiglu_clamp, "moe_blocks": len(self.layers)},
+            shim = SimpleNamespace(hidden_size=c.hidden, extra={"swiglu_clamp": c.swiglu_clamp, "moe_blocks": len(self.layers),
+                                                                "expert_staging_gb": c.expert_staging_gb or None},
                                    moe=SimpleNamespace(num_experts=c.experts, expert_intermediate=c.expert_inter,
                                                        top_k=c.top_k))
             layer.routed = RoutedExperts(shim, torch.bfloat16)

@@ -207,3 +207,15 @@ def test_hot_experts_are_pinned_automatically_after_the_configured_steps(monkeyp
     monkeypatch.setenv("FI_EXPERT_STAGING_PIN_HOT", "-1")
     with pytest.raises(ValueError):
         auto_pin_from_env()
+
+
+@pytest.mark.parametrize("name", ["tiny-deepseek-test", "tiny-deepseek-v4-flash-blocks-test"])
+def test_the_budget_can_come_with_the_model_configuration(name, monkeypatch):
+    monkeypatch.delenv("FI_EXPERT_STAGING_GB", raising=False)
+    ref, want = _generate(name)
+    ref.shutdown()
+    llm, got = _generate(name, hf_overrides={"expert_staging_gb": 1e-9})
+    assert got == want
+    st = llm.engine.stats()["expert_staging"]
+    assert st["blocks"] >= 1 and st["slots_per_block"] == 2 and st["evictions"] > 0
+    llm.shutdown()
