@@ -84,3 +84,14 @@ def test_every_test_needing_a_gpu_is_marked():
             if name.endswith("_gpu") or "_on_gpu" in name or "_on_the_gpu" in name:
                 head = text[max(0, m.start() - 400): m.start()]
                 assert "pytest.mark.gpu" in head or "pytestmark" in text, f"{p.name}::{name} lacks the gpu mark"
+
+
+def test_the_regression_ladder_script_parses_and_names_existing_files():
+    import subprocess
+    script = ROOT / "tests" / "run_regression_suite.sh"
+    assert subprocess.run(["bash", "-n", str(script)]).returncode == 0
+    out = subprocess.run(["bash", str(script), "--help"], capture_output=True, text=True)
+    assert out.returncode == 0 and "--gpu" in out.stdout
+    assert subprocess.run(["bash", str(script), "--bogus"], capture_output=True).returncode == 2
+    for name in re.findall(r"tests/test_\w+\.py", script.read_text()):
+        assert (ROOT / name).is_file(), name
