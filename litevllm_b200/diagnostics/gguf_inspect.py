@@ -66,6 +66,19 @@ def inspect(path: str, pattern: str | None = None) -> dict:
             "metadata": g.metadata, "listed": listed}
 
 
+def slots_for_budget(info: dict, budget_gb: float) -> dict:
+    """What a staging budget of ``budget_gb`` buys: slots per MoE block and the share of the experts they hold."""
+    blocks = len({re.match(r"blk\.(\d+)\.", e["name"]).group(1) for e in info["expert_tensors"]
+                  if re.match(r"blk\.(\d+)\.", e["name"])}) or 1
+    per_slot = info["expert_bytes_per_slot_per_block"]
+    experts = max((e["experts"] for e in info["expert_tensors"]), default=0)
+    if not per_slot or not experts:
+        return {"blocks": 0, "slots_per_block": 0, "experts_per_block": 0, "resident_share": 1.0}
+    slots = min(experts, int(budget_gb * 2 ** 30 // blocks // per_slot))
+    return {"blocks": blocks, "slots_per_block": slots, "experts_per_block": experts,
+            "resident_share": round(slots / experts, 4)}
+
+
 def render(info: dict, show_metadata: bool = False) -> str:
     gb = 2 ** 30
     out = [f"{info['path']}: architecture {info['architecture'] or '?'}, {info['tensors']} tensors, "
@@ -104,13 +117,21 @@ def main(argv=None) -> int:
     ap.add_argument("--json", action="store_true", help="print everything as one JSON object")
     ap.add_argument("--tensors", default=None, help="also list the tensors whose name matches this regular expression")
     ap.add_argument("--metadata", action="store_true", help="also print the metadata keys")
+    ap.add_argument("--device-budget-gb", type=float, default=0.0,
+                    help="also print how many expert slots per block this staging budget holds")
     a = ap.parse_args(argv)
     try:
         info = inspect(a.path, a.tensors)
     except (ValueError, OSError) as e:
         print(f"error: {e}", file=sys.stderr)
         return 2
+    if a.device_budget_gb > 0:
+        info["staging"] = slots_for_budget(info, a.device_budget_gb)
     print(json.dumps(info, default=str) if a.json else render(info, a.metadata))
+    if a.device_budget_gb > 0 and not a.json:
+        st = info["staging"]
+        print(f"a budget of {a.device_budget_gb:g} GiB holds {st['slots_per_block']} of {st['experts_per_block']} experts "
+              f"in each of {st['blocks']} blocks ({100 * st['resident_share']:.1f} % resident)")
     return 1 if info["unsupported"] or info["config_error"] else 0
 
 

@@ -64,6 +64,12 @@ def test_gguf_inspection_reads_the_header(tmp_path, capsys):
     assert [t["name"] for t in info["listed"]] == ["blk.0.attn_norm.weight"] and info["unsupported"] == []
     text = gguf_inspect.render(info, show_metadata=True)
     assert "Q8_0" in text and "routed experts" in text and "general.architecture" in text
+    budget = 3.5 * 2 * per / 2 ** 30
+    assert gguf_inspect.slots_for_budget(info, budget) == {"blocks": 1, "slots_per_block": 3, "experts_per_block": 4,
+                                                           "resident_share": 0.75}
+    assert gguf_inspect.slots_for_budget(info, 1.0)["slots_per_block"] == 4
+    gguf_inspect.main([str(path), "--device-budget-gb", repr(budget)])
+    assert "holds 3 of 4 experts in each of 1 blocks" in capsys.readouterr().out
     assert gguf_inspect.main([str(tmp_path / "missing.gguf")]) == 2
     assert "error" in capsys.readouterr().err
 
